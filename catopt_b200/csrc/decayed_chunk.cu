@@ -1,0 +1,67 @@
+// C-ABI front of the chunked decayed-attention executor: argument checks and
+// the choice between the tensor-core kernel (bf16, chunk = dk = dv = 128 or 64,
+// state kept on chip) and the fp32 FMA path (everything else, state in scratch).
+#include "common.cuh"
+
+namespace cb2 {
+size_t decayed_ffma_scratch_bytes(int B, int H, int T, int dk, int dv, int C);
+int decayed_ffma_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
+                     int H, int T, int dk, int dv, int C, float scale, int dtype, void* scratch,
+                     cudaStream_t st);
+bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype);
+int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
+                   int H, int T, int dk, int dv, int C, float scale, int* dev_status,
+                   cudaStream_t st);
+
+namespace {
+int check_shape(int B, int H, int T, int dk, int dv, int C) {
+  if (B <= 0 || H <= 0 || T <= 0 || dk <= 0 || dv <= 0 || C <= 0) return CB2_BAD_SHAPE;
+  if (T % C != 0) return CB2_BAD_SHAPE;
+  return CB2_OK;
+}
+}  // namespace
+}  // namespace cb2
+
+extern "C" size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv, int chunk,
+                                                  int dtype) {
+  if (cb2::check_shape(B, H, T, dk, dv, chunk) != CB2_OK) return 0;
+  if (cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)) return 0;
+  return cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
+}
+
+extern "C" int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
+                                     const float* gamma, int B, int H, int T, int dk, int dv,
+                                     int chunk, float scale, int dtype, void* scratch,
+                                     size_t scratch_bytes, int* dev_status, void* stream) {
+  if (!q || !k || !v || !o || !gamma) return CB2_NULL_PTR;
+  const int rc = cb2::check_shape(B, H, T, dk, dv, chunk);
+  if (rc != CB2_OK) return rc;
+  if (dtype != CB2_F32 && dtype != CB2_BF16) return CB2_UNSUPPORTED_DTYPE;
+  if (!(scale != 0.f)) return CB2_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)) {
+    if (!cb2::aligned16(q) || !cb2::aligned16(k) || !cb2::aligned16(v) || !cb2::aligned16(o))
+      return CB2_BAD_ALIGN;
+    return cb2::decayed_tc_run(q, k, v, o, gamma, B, H, T, dk, dv, chunk, scale, dev_status, st);
+  }
+  const size_t need = cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
+  if (!scratch || scratch_bytes < need) return CB2_SCRATCH_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(scratch) & 15u) return CB2_BAD_ALIGN;
+  return cb2::decayed_ffma_run(q, k, v, o, gamma, B, H, T, dk, dv, chunk, scale, dtype, scratch, st);
+}
+
+extern "C" int cb2_version(void) { return 100; }
+
+extern "C" const char* cb2_status_str(int status) {
+  switch (status) {
+    case CB2_OK: return "ok";
+    case CB2_BAD_SHAPE: return "bad shape";
+    case CB2_BAD_ALIGN: return "bad alignment";
+    case CB2_UNSUPPORTED_DTYPE: return "unsupported dtype";
+    case CB2_LAUNCH_FAIL: return "kernel launch failed";
+    case CB2_WAIT_TIMEOUT: return "device wait timed out";
+    case CB2_NULL_PTR: return "null pointer";
+    case CB2_SCRATCH_TOO_SMALL: return "scratch too small";
+    default: return "unknown status";
+  }
+}

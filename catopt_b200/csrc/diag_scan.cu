@@ -1,0 +1,313 @@
+// Diagonal linear recurrence with readout,
+//   h_t[n] = a_t[n] * h_{t-1}[n] + b[n] * x_t,   y_t = sum_n c[n] * h_t[n],
+// one step of which is the reference's applyd(aff_diag(a_t, b*x_t), h)
+// (catopt_torch/torch_bridge.py:1895-1900).
+//
+// Bandwidth kernel: `a` ([B,T,D,N]) is read exactly once and dominates the
+// traffic (algorithmic bytes per (b,t) position = D*(N+2)*sizeof(elem)).
+//
+// Layout / mapping.  A CTA owns one batch entry and a block of kCh channels
+// for the whole sequence; a thread owns kNpt consecutive n of one channel
+// (16 bytes of bf16), its states live in registers for all T steps, and the
+// n-sum of the readout finishes with warp shuffles across the kLpc lanes that
+// share a channel.  The T axis is streamed through a kStages-deep ring of
+// shared-memory tiles of kRows time steps, filled by the TMA engine with one
+// bulk copy per row (a row of the block is kCh*N contiguous elements) and
+// tracked by one mbarrier per stage, so kStages-1 tiles per CTA are always in
+// flight while the serial recurrence runs on the resident one.  y is staged in
+// shared memory and written with 16-byte stores.
+#include "common.cuh"
+
+namespace cb2 {
+namespace {
+
+template <int DTYPE>
+struct Elem;
+template <>
+struct Elem<CB2_BF16> {
+  using T = __nv_bfloat16;
+  static constexpr int kSize = 2;
+  __device__ static float ld(const void* p, int i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  }
+  __device__ static void st(void* p, int i, float v) {
+    static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  }
+};
+template <>
+struct Elem<CB2_F32> {
+  using T = float;
+  static constexpr int kSize = 4;
+  __device__ static float ld(const void* p, int i) { return static_cast<const float*>(p)[i]; }
+  __device__ static void st(void* p, int i, float v) { static_cast<float*>(p)[i] = v; }
+};
+
+template <int DTYPE, int N>
+struct ScanCfg {
+  static constexpr int kEsz = Elem<DTYPE>::kSize;
+  static constexpr int kNpt = N < 8 ? N : 8;          // n per thread
+  static constexpr int kLpc = N / kNpt;               // lanes per channel
+  static constexpr int kThreads = 64;
+  static constexpr int kCh = kThreads / kLpc;         // channels per CTA
+  static constexpr int kRows = DTYPE == CB2_BF16 ? 16 : 8;  // time steps per tile
+  static constexpr int kStages = 4;
+  static constexpr int kARow = kCh * N * kEsz;        // bytes of `a` per time step
+  static constexpr int kXRow = kCh * kEsz;            // bytes of x (and y) per time step
+  static constexpr int kStageBytes = kRows * (kARow + kXRow);
+  static constexpr int kYBytes = kRows * kXRow;
+  static constexpr int kSmem = kStages * kStageBytes + 2 * kYBytes + kStages * 8 + 16;
+};
+
+// Widen kNpt consecutive elements starting at byte pointer p into f[].
+template <int DTYPE, int NPT>
+__device__ __forceinline__ void load_row(const unsigned char* p, float (&f)[NPT]) {
+  if constexpr (DTYPE == CB2_BF16) {
+    if constexpr (NPT == 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(p);
+      f[0] = bf16lo_to_f32(v.x); f[1] = bf16hi_to_f32(v.x);
+      f[2] = bf16lo_to_f32(v.y); f[3] = bf16hi_to_f32(v.y);
+      f[4] = bf16lo_to_f32(v.z); f[5] = bf16hi_to_f32(v.z);
+      f[6] = bf16lo_to_f32(v.w); f[7] = bf16hi_to_f32(v.w);
+    } else if constexpr (NPT == 4) {
+      const uint2 v = *reinterpret_cast<const uint2*>(p);
+      f[0] = bf16lo_to_f32(v.x); f[1] = bf16hi_to_f32(v.x);
+      f[2] = bf16lo_to_f32(v.y); f[3] = bf16hi_to_f32(v.y);
+    } else if constexpr (NPT == 2) {
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+      f[0] = bf16lo_to_f32(v); f[1] = bf16hi_to_f32(v);
+    } else {
+      f[0] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+    }
+  } else {
+    if constexpr (NPT == 8) {
+      const float4 v0 = *reinterpret_cast<const float4*>(p);
+      const float4 v1 = *reinterpret_cast<const float4*>(p + 16);
+      f[0] = v0.x; f[1] = v0.y; f[2] = v0.z; f[3] = v0.w;
+      f[4] = v1.x; f[5] = v1.y; f[6] = v1.z; f[7] = v1.w;
+    } else if constexpr (NPT == 4) {
+      const float4 v0 = *reinterpret_cast<const float4*>(p);
+      f[0] = v0.x; f[1] = v0.y; f[2] = v0.z; f[3] = v0.w;
+    } else if constexpr (NPT == 2) {
+      const float2 v0 = *reinterpret_cast<const float2*>(p);
+      f[0] = v0.x; f[1] = v0.y;
+    } else {
+      f[0] = *reinterpret_cast<const float*>(p);
+    }
+  }
+}
+
+template <int DTYPE, int N>
+__global__ void __launch_bounds__(64)
+diag_scan_kernel(const unsigned char* __restrict__ a, const unsigned char* __restrict__ x,
+                 const void* __restrict__ bvec, const void* __restrict__ cvec,
+                 const float* __restrict__ h0, unsigned char* __restrict__ y,
+                 float* __restrict__ hT, int T, int D, int* dev_status) {
+  using C = ScanCfg<DTYPE, N>;
+  using E = Elem<DTYPE>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* s_stage = smem;                                   // kStages x [a rows | x rows]
+  unsigned char* s_y = smem + C::kStages * C::kStageBytes;         // 2 x kYBytes
+  uint64_t* s_full = reinterpret_cast<uint64_t*>(s_y + 2 * C::kYBytes);
+
+  const int tid = threadIdx.x;
+  const int blocks_per_b = (D + C::kCh - 1) / C::kCh;
+  const int b = blockIdx.x / blocks_per_b;
+  const int d0 = (blockIdx.x % blocks_per_b) * C::kCh;
+  const int nch = min(C::kCh, D - d0);                             // channels this CTA owns
+  const int ch = tid / C::kLpc, sub = tid % C::kLpc;
+  const bool live = ch < nch;
+  const int d = d0 + ch;
+  const uint32_t a_row_bytes = uint32_t(nch) * N * C::kEsz;
+  const uint32_t x_row_bytes = uint32_t(nch) * C::kEsz;
+  const size_t a_row_stride = size_t(D) * N * C::kEsz;
+  const size_t x_row_stride = size_t(D) * C::kEsz;
+  const unsigned char* a_base = a + (size_t(b) * T * D + d0) * N * C::kEsz;
+  const unsigned char* x_base = x + (size_t(b) * T * D + d0) * C::kEsz;
+  unsigned char* y_base = y + (size_t(b) * T * D + d0) * C::kEsz;
+  const int ntiles = (T + C::kRows - 1) / C::kRows;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) mbar_init(&s_full[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // Producer: warp 0 fills stage (tile % kStages) with tile's rows.
+  auto issue_tile = [&](int tile) {
+    const int s = tile % C::kStages;
+    const int t0 = tile * C::kRows;
+    const int rows = min(C::kRows, T - t0);
+    unsigned char* sa = s_stage + s * C::kStageBytes;
+    unsigned char* sx = sa + C::kRows * C::kARow;
+    if (tid == 0) mbar_arrive_expect_tx(&s_full[s], uint32_t(rows) * (a_row_bytes + x_row_bytes));
+    __syncwarp();
+    if (tid < rows) {
+      bulk_g2s(sa + tid * C::kARow, a_base + size_t(t0 + tid) * a_row_stride, a_row_bytes,
+               &s_full[s]);
+      bulk_g2s(sx + tid * C::kXRow, x_base + size_t(t0 + tid) * x_row_stride, x_row_bytes,
+               &s_full[s]);
+    }
+  };
+  if (tid < 32) {
+    for (int i = 0; i < C::kStages && i < ntiles; ++i) issue_tile(i);
+  }
+
+  float h[C::kNpt], bw[C::kNpt], cw[C::kNpt];
+#pragma unroll
+  for (int j = 0; j < C::kNpt; ++j) {
+    const int n = sub * C::kNpt + j;
+    bw[j] = live ? E::ld(bvec, d * N + n) : 0.f;
+    cw[j] = live ? E::ld(cvec, d * N + n) : 0.f;
+    h[j] = (live && h0) ? h0[(size_t(b) * D + d) * N + n] : 0.f;
+  }
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int s = tile % C::kStages;
+    const uint32_t parity = (tile / C::kStages) & 1;
+    const int t0 = tile * C::kRows;
+    const int rows = min(C::kRows, T - t0);
+    const bool ok = mbar_wait_bounded(&s_full[s], parity);
+    const unsigned char* sa = s_stage + s * C::kStageBytes + tid * (C::kNpt * C::kEsz);
+    const unsigned char* sx = s_stage + s * C::kStageBytes + C::kRows * C::kARow + ch * C::kEsz;
+    unsigned char* sy = s_y + (tile & 1) * C::kYBytes;
+    if (ok) {
+#pragma unroll 4
+      for (int r = 0; r < C::kRows; ++r) {
+        if (r < rows) {
+          float av[C::kNpt];
+          load_row<DTYPE, C::kNpt>(sa + r * C::kARow, av);
+          const float xv = E::ld(sx + r * C::kXRow, 0);
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < C::kNpt; ++j) {
+            h[j] = fmaf(av[j], h[j], bw[j] * xv);
+            acc = fmaf(cw[j], h[j], acc);
+          }
+#pragma unroll
+          for (int off = C::kLpc >> 1; off > 0; off >>= 1)
+            acc += __shfl_xor_sync(0xffffffffu, acc, off);
+          if (sub == 0) E::st(sy + r * C::kXRow, ch, acc);
+        }
+      }
+    }
+    // Everyone is done with stage s and has written its y rows; a failed wait
+    // anywhere in the CTA ends the loop for all of its threads.
+    if (__syncthreads_or(!ok)) {
+      if (tid == 0 && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+      return;
+    }
+    if (tid < 32 && tile + C::kStages < ntiles) issue_tile(tile + C::kStages);
+    // y tile -> global, 16 bytes per thread per pass.
+    const int vec_per_row = int(x_row_bytes) / 16;
+    for (int i = tid; i < rows * vec_per_row; i += C::kThreads) {
+      const int r = i / vec_per_row, piece = i % vec_per_row;
+      const uint4 v = *reinterpret_cast<const uint4*>(sy + r * C::kXRow + piece * 16);
+      *reinterpret_cast<uint4*>(y_base + size_t(t0 + r) * x_row_stride + piece * 16) = v;
+    }
+  }
+
+  if (hT && live) {
+#pragma unroll
+    for (int j = 0; j < C::kNpt; ++j)
+      hT[(size_t(b) * D + d) * N + sub * C::kNpt + j] = h[j];
+  }
+}
+
+// `a` shared over n ([B,T,D]): one thread per (b, channel) keeps all N states.
+template <int DTYPE, int N>
+__global__ void __launch_bounds__(128)
+diag_scan_bcast_kernel(const void* __restrict__ a, const void* __restrict__ x,
+                       const void* __restrict__ bvec, const void* __restrict__ cvec,
+                       const float* __restrict__ h0, void* __restrict__ y,
+                       float* __restrict__ hT, int B, int T, int D) {
+  using E = Elem<DTYPE>;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * D) return;
+  const int b = idx / D, d = idx % D;
+  float h[N], bw[N], cw[N];
+#pragma unroll
+  for (int n = 0; n < N; ++n) {
+    bw[n] = E::ld(bvec, d * N + n);
+    cw[n] = E::ld(cvec, d * N + n);
+    h[n] = h0 ? h0[(size_t(b) * D + d) * N + n] : 0.f;
+  }
+  const size_t base = size_t(b) * T * D + d;
+#pragma unroll 8
+  for (int t = 0; t < T; ++t) {
+    const float av = E::ld(a, 0 + (base + size_t(t) * D));
+    const float xv = E::ld(x, 0 + (base + size_t(t) * D));
+    float acc = 0.f;
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      h[n] = fmaf(av, h[n], bw[n] * xv);
+      acc = fmaf(cw[n], h[n], acc);
+    }
+    E::st(y, base + size_t(t) * D, acc);
+  }
+  if (hT) {
+#pragma unroll
+    for (int n = 0; n < N; ++n) hT[(size_t(b) * D + d) * N + n] = h[n];
+  }
+}
+
+template <int DTYPE, int N>
+int launch_scan(const void* a, const void* x, const void* b, const void* c, const float* h0,
+                void* y, float* hT, int B, int T, int D, int a_bcast_n, int* dev_status,
+                cudaStream_t st) {
+  using C = ScanCfg<DTYPE, N>;
+  if (a_bcast_n) {
+    const int total = B * D;
+    diag_scan_bcast_kernel<DTYPE, N><<<(total + 127) / 128, 128, 0, st>>>(a, x, b, c, h0, y, hT,
+                                                                         B, T, D);
+    CB2_LAUNCH_CHECK();
+    return CB2_OK;
+  }
+  if ((size_t(D) * N * C::kEsz) % 16 || (size_t(D) * C::kEsz) % 16) return CB2_BAD_SHAPE;
+  auto kern = diag_scan_kernel<DTYPE, N>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) !=
+      cudaSuccess)
+    return CB2_LAUNCH_FAIL;
+  const int blocks_per_b = (D + C::kCh - 1) / C::kCh;
+  kern<<<B * blocks_per_b, C::kThreads, C::kSmem, st>>>(
+      static_cast<const unsigned char*>(a), static_cast<const unsigned char*>(x), b, c, h0,
+      static_cast<unsigned char*>(y), hT, T, D, dev_status);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
+template <int DTYPE>
+int dispatch_n(const void* a, const void* x, const void* b, const void* c, const float* h0,
+               void* y, float* hT, int B, int T, int D, int N, int a_bcast_n, int* dev_status,
+               cudaStream_t st) {
+#define CB2_SCAN_CASE(NN) \
+  case NN:                \
+    return launch_scan<DTYPE, NN>(a, x, b, c, h0, y, hT, B, T, D, a_bcast_n, dev_status, st);
+  switch (N) {
+    CB2_SCAN_CASE(1)
+    CB2_SCAN_CASE(2)
+    CB2_SCAN_CASE(4)
+    CB2_SCAN_CASE(8)
+    CB2_SCAN_CASE(16)
+    CB2_SCAN_CASE(32)
+    default:
+      return CB2_BAD_SHAPE;
+  }
+#undef CB2_SCAN_CASE
+}
+
+}  // namespace
+}  // namespace cb2
+
+extern "C" int cb2_diag_scan_fwd(const void* a, const void* x, const void* b, const void* c,
+                                 const float* h0, void* y, float* hT, int B, int T, int D, int N,
+                                 int a_bcast_n, int dtype, int* dev_status, void* stream) {
+  if (!a || !x || !b || !c || !y) return CB2_NULL_PTR;
+  if (B <= 0 || T <= 0 || D <= 0 || N <= 0) return CB2_BAD_SHAPE;
+  if (!cb2::aligned16(a) || !cb2::aligned16(x) || !cb2::aligned16(y)) return CB2_BAD_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CB2_BF16)
+    return cb2::dispatch_n<CB2_BF16>(a, x, b, c, h0, y, hT, B, T, D, N, a_bcast_n, dev_status, st);
+  if (dtype == CB2_F32)
+    return cb2::dispatch_n<CB2_F32>(a, x, b, c, h0, y, hT, B, T, D, N, a_bcast_n, dev_status, st);
+  return CB2_UNSUPPORTED_DTYPE;
+}

@@ -1,0 +1,175 @@
+"""Lowered executors as ``nn.Module``s over the sm_100a kernels.
+
+Each class keeps the surface the reference's batched modules expose
+(``catopt_core.ports.BatchedExecutor``: ``forward``, a plain ``_plan`` dict,
+``is_batched``; plus ``capture_cuda_graph`` / ``drop_cuda_graph`` /
+``is_graph_captured`` of ``catopt_torch.executors.base.BatchedExecutorBase``,
+base.py:146-224) so catopt's runners and autotuner can drive them unchanged.
+They need no catopt install: ``sink.py`` adapts them to catopt's executor table
+when catopt is importable.
+
+There is no fallback arithmetic here: inputs must be CUDA tensors and every
+forward is one C-ABI call.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from . import ops
+from ._lib import B200Error
+
+
+class _GraphMixin:
+    """CUDA-graph capture/replay with the reference's calling convention:
+    inputs are copied into static buffers and the returned tensor is a static
+    output buffer overwritten by the next call (base.py:180-220)."""
+
+    def _init_graph_state(self) -> None:
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self._graph_inputs: tuple[torch.Tensor, ...] = ()
+        self._graph_out: Any = None
+
+    @property
+    def is_graph_captured(self) -> bool:
+        return self._graph is not None
+
+    def drop_cuda_graph(self) -> None:
+        self._init_graph_state()
+
+    def capture_cuda_graph(self, *example_inputs: torch.Tensor, warmup: int = 3):
+        if not example_inputs or not all(isinstance(t, torch.Tensor) and t.is_cuda for t in example_inputs):
+            raise ValueError("capture_cuda_graph needs CUDA tensor inputs")
+        self._graph_inputs = tuple(t.clone() for t in example_inputs)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(warmup, 1)):  # also sizes every scratch buffer
+                self._forward_impl(*self._graph_inputs)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph), torch.no_grad():
+            self._graph_out = self._forward_impl(*self._graph_inputs)
+        self._graph = graph
+        return self
+
+    def _replay_if_captured(self, xs: tuple) -> Any:
+        g = self._graph
+        if g is None or len(xs) != len(self._graph_inputs):
+            return None
+        if not all(isinstance(t, torch.Tensor) and t.shape == b.shape and t.dtype == b.dtype
+                   and t.device == b.device for t, b in zip(xs, self._graph_inputs)):
+            return None
+        for buf, t in zip(self._graph_inputs, xs):
+            buf.copy_(t, non_blocking=True)
+        g.replay()
+        return self._graph_out
+
+    def forward(self, *xs: Any) -> Any:
+        out = self._replay_if_captured(xs)
+        return out if out is not None else self._forward_impl(*xs)
+
+
+class B200FoldedLinear(_GraphMixin, torch.nn.Module):
+    """A chain of bias-free Linear maps folded into one weight at construction
+    (``IRModule._fold_weight_chains``, torch_bridge.py:2456-2510) and applied
+    with a single fp32 GEMM per call (``linear`` binding, 1251-1253).
+
+    ``weights`` are in application order (first layer first), nn.Linear layout
+    ``[out, in]``.  The fold runs on the GPU through ``cb2_chain_fold_f32``; the
+    result is registered as parameter ``fused_<index>`` the way the reference
+    names its folded weights, so ``state_dict()`` keeps working.
+    """
+
+    def __init__(self, weights: list[torch.Tensor], bias: torch.Tensor | None = None,
+                 fused_index: int | None = None) -> None:
+        super().__init__()
+        if not weights:
+            raise ValueError("B200FoldedLinear needs at least one weight")
+        ws = [w.detach().to(torch.float32).contiguous() for w in weights]
+        if not all(w.is_cuda for w in ws):
+            raise B200Error("B200FoldedLinear folds on the GPU: weights must be CUDA tensors")
+        fused = ops.chain_fold_f32(ws)
+        # the reference numbers fused params after the k originals and the k-2 intermediates
+        idx = 2 * len(ws) - 2 if fused_index is None else fused_index
+        self.fused_name = f"fused_{idx}"
+        self.register_parameter(self.fused_name, torch.nn.Parameter(fused, requires_grad=False))
+        self.bias = None if bias is None else torch.nn.Parameter(
+            bias.detach().to(torch.float32).contiguous(), requires_grad=False)
+        self._plan: dict | None = {"kind": "folded_linear", "k": len(ws),
+                                   "in": ws[0].shape[1], "out": ws[-1].shape[0]}
+        self._init_graph_state()
+
+    @property
+    def is_batched(self) -> bool:
+        return True
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return getattr(self, self.fused_name)
+
+    def _forward_impl(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear_f32(x, self.weight, self.bias)
+
+
+class B200ChunkedDecay(_GraphMixin, torch.nn.Module):
+    """Decayed causal linear attention on ``q, k, v`` of shape ``[B,H,T,d]``:
+    ``o_t = sum_{s<=t} gamma_h^(t-s) (q_t . k_s) v_s / scale``, the value of the
+    reference's ``ChunkedDecayModule`` (decayed_lower.py:381-724) on the
+    uniform chunk term, computed with a carried fp32 state instead of all-pairs
+    cross products.  ``gamma`` is a scalar or one rate per head.
+    """
+
+    def __init__(self, gamma: torch.Tensor | float, n_heads: int, chunk: int, scale: float = 1.0) -> None:
+        super().__init__()
+        g = torch.as_tensor(gamma, dtype=torch.float32).detach().reshape(-1)
+        if g.numel() == 1:
+            g = g.expand(n_heads)
+        if g.numel() != n_heads:
+            raise ValueError(f"gamma has {g.numel()} rates for {n_heads} heads")
+        self.register_buffer("gamma", g.contiguous().clone())
+        self.chunk = int(chunk)
+        self.scale = float(scale)
+        self._plan: dict | None = {"kind": "decayed_state_carry", "chunk": self.chunk, "scale": self.scale}
+        self._init_graph_state()
+
+    @property
+    def is_batched(self) -> bool:
+        return True
+
+    @property
+    def n_blocks(self) -> int:
+        return 0 if self._plan is None else int(self._plan.get("n", 0))
+
+    def _forward_impl(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        if self._plan is not None:
+            self._plan["n"] = q.shape[-2] // self.chunk
+        return ops.decayed_chunk_fwd(q, k, v, self.gamma, self.chunk, self.scale)
+
+
+class B200DiagScan(_GraphMixin, torch.nn.Module):
+    """Diagonal linear recurrence with readout,
+    ``h_t = a_t*h_{t-1} + b*x_t``, ``y_t = sum_n c*h_t`` — T applications of the
+    reference's ``applyd(aff_diag(a_t, b*x_t), h)`` (torch_bridge.py:1895-1900),
+    the sequence its ``BatchedScanModule`` reduces level by level
+    (scan_lower.py:569-698).  ``forward(a, x, h0=None)`` returns ``y`` (and the
+    final state when ``return_state``).
+    """
+
+    def __init__(self, b: torch.Tensor, c: torch.Tensor, return_state: bool = False) -> None:
+        super().__init__()
+        if b.shape != c.shape or b.dim() != 2:
+            raise ValueError("b and c must both be [D, N]")
+        self.register_buffer("b", b.detach().contiguous().clone())
+        self.register_buffer("c", c.detach().contiguous().clone())
+        self.return_state = bool(return_state)
+        self._plan: dict | None = {"kind": "diag_scan", "D": b.shape[0], "N": b.shape[1]}
+        self._init_graph_state()
+
+    @property
+    def is_batched(self) -> bool:
+        return True
+
+    def _forward_impl(self, a: torch.Tensor, x: torch.Tensor, h0: torch.Tensor | None = None):
+        return ops.diag_scan_fwd(a, x, self.b, self.c, h0, want_state=self.return_state)

@@ -1,0 +1,200 @@
+"""Functional wrappers: torch CUDA tensors in, one C-ABI call each.
+
+torch is used for device memory and streams only; every arithmetic step runs in
+``libcatopt_b200.so``.  Scratch buffers are torch allocations cached per
+(device, purpose) and grown on demand, so steady-state calls allocate nothing
+and can be captured in a CUDA graph after a warm-up call.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import B200Error, check, dtype_code, require_cuda, stream_ptr
+
+_scratch: dict[tuple, torch.Tensor] = {}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _scratch_buf(purpose: str, nbytes: int, device: torch.device) -> torch.Tensor | None:
+    """A cached uint8 scratch buffer of at least ``nbytes`` (``None`` for 0)."""
+    if nbytes <= 0:
+        return None
+    key = (purpose, device.index)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """The per-device int32 word kernels write CB2_WAIT_TIMEOUT into."""
+    w = _status_words.get(device.index)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device.index] = w
+    return w
+
+
+def check_device_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if a kernel recorded a bounded-wait timeout."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    w = _status_words.get(device.index)
+    if w is None:
+        return
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise B200Error(f"device status: {_lib.status_str(code)} (status {code})")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------- verify
+def verify_reduce(ref: torch.Tensor, out: torch.Tensor, n_seg: int = 1,
+                  result: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-segment ``[max|ref-out|, max|ref|, nan_in_diff, nan_in_ref]``.
+
+    ``ref``/``out`` hold ``n_seg`` equally sized comparisons back to back.
+    Returns a float32 CUDA tensor ``[n_seg, 4]`` (no host synchronisation).
+    """
+    require_cuda(ref, out, result)
+    if ref.shape != out.shape or ref.dtype != out.dtype:
+        raise B200Error("verify_reduce needs identical shape and dtype on both sides")
+    numel = ref.numel()
+    if n_seg <= 0 or numel == 0 or numel % n_seg:
+        raise B200Error(f"cannot split {numel} elements into {n_seg} equal segments")
+    if result is None:
+        result = torch.empty(n_seg, 4, dtype=torch.float32, device=ref.device)
+    elif result.shape != (n_seg, 4) or result.dtype != torch.float32:
+        raise B200Error("result must be float32 [n_seg, 4]")
+    rc = _lib.load().cb2_verify_reduce(ref.data_ptr(), out.data_ptr(), numel // n_seg, n_seg,
+                                       dtype_code(ref.dtype), result.data_ptr(), stream_ptr())
+    check(rc, "cb2_verify_reduce")
+    return result
+
+
+# --------------------------------------------------------------------------- chain
+def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for fp32 ``x[..., in]``, ``w[out, in]``."""
+    require_cuda(x, w, bias, out)
+    if x.dtype != torch.float32 or w.dtype != torch.float32:
+        raise B200Error("linear_f32 takes float32 tensors")
+    if w.dim() != 2 or x.shape[-1] != w.shape[1]:
+        raise B200Error(f"linear_f32 shape mismatch: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    rows = x.numel() // x.shape[-1]
+    n_in, n_out = w.shape[1], w.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n_out, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    need = lib.cb2_linear_f32_scratch_bytes(rows, n_in, n_out)
+    scratch = _scratch_buf("linear", need, x.device)
+    rc = lib.cb2_linear_f32(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), rows, n_in,
+                            n_out, _ptr(scratch), need, stream_ptr())
+    check(rc, "cb2_linear_f32")
+    return out
+
+
+def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b`` for two dense fp32 matrices."""
+    require_cuda(a, b)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.dim() != 2 or b.dim() != 2:
+        raise B200Error("matmul_f32 takes two float32 matrices")
+    if a.shape[1] != b.shape[0]:
+        raise B200Error(f"matmul_f32 shape mismatch: {tuple(a.shape)} @ {tuple(b.shape)}")
+    c = torch.empty(a.shape[0], b.shape[1], dtype=torch.float32, device=a.device)
+    rc = _lib.load().cb2_matmul_f32(a.data_ptr(), b.data_ptr(), c.data_ptr(), a.shape[0],
+                                    b.shape[1], a.shape[1], stream_ptr())
+    check(rc, "cb2_matmul_f32")
+    return c
+
+
+def chain_fold_f32(weights: list[torch.Tensor]) -> torch.Tensor:
+    """``W[k-1] @ (... @ (W[1] @ W[0]))`` for nn.Linear-layout fp32 weights."""
+    if not weights:
+        raise B200Error("chain_fold_f32 needs at least one weight")
+    require_cuda(*weights)
+    k = len(weights)
+    dims = [weights[0].shape[1]]
+    for w in weights:
+        if w.dtype != torch.float32 or w.dim() != 2 or w.shape[1] != dims[-1]:
+            raise B200Error("chain_fold_f32: weights must be float32 [out_i, in_i] and chain")
+        dims.append(w.shape[0])
+    lib = _lib.load()
+    dims_c = (C.c_int * (k + 1))(*dims)
+    ptrs = (C.c_void_p * k)(*[w.data_ptr() for w in weights])
+    need = lib.cb2_chain_fold_f32_scratch_bytes(dims_c, k)
+    scratch = _scratch_buf("fold", need, weights[0].device)
+    out = torch.empty(dims[-1], dims[0], dtype=torch.float32, device=weights[0].device)
+    rc = lib.cb2_chain_fold_f32(ptrs, dims_c, k, out.data_ptr(), _ptr(scratch), need, stream_ptr())
+    check(rc, "cb2_chain_fold_f32")
+    return out
+
+
+# --------------------------------------------------------------------------- decayed
+def decayed_chunk_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor,
+                      chunk: int, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Decayed causal linear attention ``[B,H,T,d]`` with per-head ``gamma[H]`` (fp32)."""
+    require_cuda(q, k, v, gamma, out)
+    if q.dim() != 4 or q.shape != k.shape or v.shape[:3] != q.shape[:3]:
+        raise B200Error("decayed_chunk_fwd takes q,k [B,H,T,dk] and v [B,H,T,dv]")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise B200Error("q, k, v must share one dtype")
+    B, H, T, dk = q.shape
+    dv = v.shape[-1]
+    if gamma.dtype != torch.float32 or gamma.numel() != H:
+        raise B200Error("gamma must be float32 with one rate per head")
+    if T % chunk:
+        raise B200Error(f"T={T} is not a multiple of chunk={chunk}")
+    if out is None:
+        out = torch.empty_like(v)
+    code = dtype_code(q.dtype)
+    lib = _lib.load()
+    need = lib.cb2_decayed_chunk_scratch_bytes(B, H, T, dk, dv, chunk, code)
+    scratch = _scratch_buf("decayed", need, q.device)
+    status = device_status(q.device)
+    rc = lib.cb2_decayed_chunk_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                   gamma.data_ptr(), B, H, T, dk, dv, chunk, float(scale), code,
+                                   _ptr(scratch), need, status.data_ptr(), stream_ptr())
+    check(rc, "cb2_decayed_chunk_fwd")
+    return out
+
+
+# --------------------------------------------------------------------------- scan
+def diag_scan_fwd(a: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+                  h0: torch.Tensor | None = None, want_state: bool = False,
+                  out: torch.Tensor | None = None):
+    """``h_t = a_t*h_{t-1} + b*x_t``, ``y_t = sum_n c*h_t``.
+
+    ``a`` is ``[B,T,D,N]`` or ``[B,T,D]`` (shared over n); ``x`` ``[B,T,D]``;
+    ``b``, ``c`` ``[D,N]``; ``h0`` float32 ``[B,D,N]`` or ``None``.
+    Returns ``y`` or ``(y, h_T)`` when ``want_state``.
+    """
+    require_cuda(a, x, b, c, h0, out)
+    if x.dim() != 3 or b.dim() != 2 or b.shape != c.shape:
+        raise B200Error("diag_scan_fwd takes x [B,T,D] and b,c [D,N]")
+    B, T, D = x.shape
+    N = b.shape[1]
+    if b.shape[0] != D:
+        raise B200Error("b,c must be [D,N]")
+    bcast = a.dim() == 3
+    if tuple(a.shape) != ((B, T, D) if bcast else (B, T, D, N)):
+        raise B200Error(f"a has shape {tuple(a.shape)}; expected [B,T,D,N] or [B,T,D]")
+    if not (a.dtype == x.dtype == b.dtype == c.dtype):
+        raise B200Error("a, x, b, c must share one dtype")
+    if h0 is not None and (h0.dtype != torch.float32 or tuple(h0.shape) != (B, D, N)):
+        raise B200Error("h0 must be float32 [B,D,N]")
+    y = out if out is not None else torch.empty_like(x)
+    hT = torch.empty(B, D, N, dtype=torch.float32, device=x.device) if want_state else None
+    status = device_status(x.device)
+    rc = _lib.load().cb2_diag_scan_fwd(a.data_ptr(), x.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                       _ptr(h0), y.data_ptr(), _ptr(hT), B, T, D, N, int(bcast),
+                                       dtype_code(x.dtype), status.data_ptr(), stream_ptr())
+    check(rc, "cb2_diag_scan_fwd")
+    return (y, hT) if want_state else y

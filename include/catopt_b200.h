@@ -1,0 +1,158 @@
+/*
+ * catopt_b200.h — C ABI of libcatopt_b200.so: sm_100a executors for the
+ * lowered-module hot path of catopt (the modules that run after the e-graph
+ * has chosen a rewrite).
+ *
+ * The reference has no foreign-function boundary for this path: its lowered
+ * modules are torch.nn.Modules that call eager torch ops.  Each entry point
+ * below therefore cites the reference *forward* it replaces (paths relative to
+ * the catopt project root).  Conventions shared by every entry point:
+ *
+ *   - plain pointers and sizes only; every data pointer is DEVICE memory owned
+ *     by the caller unless the comment says "host";
+ *   - tensors are dense, row-major, in the layouts stated per function;
+ *   - the call enqueues work on `stream` (a cudaStream_t passed as void*) and
+ *     returns without synchronising; the return value is a CB2_* status that
+ *     reports argument and launch errors only;
+ *   - no entry point allocates device memory: scratch is caller-provided and
+ *     sized by the matching *_scratch_bytes() query;
+ *   - kernels that wait on an asynchronous copy bound the wait; when a wait
+ *     runs out they store CB2_WAIT_TIMEOUT into `*dev_status` (device int,
+ *     may be NULL) and return early instead of spinning.
+ */
+#ifndef CATOPT_B200_H
+#define CATOPT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+enum {
+  CB2_OK = 0,
+  CB2_BAD_SHAPE = 1,         /* a size is zero/negative or violates a stated rule   */
+  CB2_BAD_ALIGN = 2,         /* a pointer misses the stated alignment               */
+  CB2_UNSUPPORTED_DTYPE = 3, /* dtype code not handled by this entry point          */
+  CB2_LAUNCH_FAIL = 4,       /* the CUDA runtime refused the launch                 */
+  CB2_WAIT_TIMEOUT = 5,      /* written to *dev_status by a kernel, never returned  */
+  CB2_NULL_PTR = 6,          /* a required pointer is NULL                          */
+  CB2_SCRATCH_TOO_SMALL = 7  /* scratch_bytes below the *_scratch_bytes() answer    */
+};
+
+/* ---- element types ------------------------------------------------------ */
+enum { CB2_F32 = 0, CB2_BF16 = 1 };
+
+/* Library version (major*10000 + minor*100 + patch). */
+int cb2_version(void);
+
+/* Static string for a status code. */
+const char* cb2_status_str(int status);
+
+/* -------------------------------------------------------------------------
+ * (d) verify reduction.
+ * Replaces the four eager passes of `_verify_pair`
+ * (packages/catopt-torch/src/catopt_torch/report.py:128-140):
+ *     max_abs = (ref - out).abs().max();  max_ref = ref.abs().max()
+ * for `n_seg` independent comparisons of `numel_per_seg` elements each,
+ * stored back to back.  The difference is formed the way torch forms it for
+ * the tensor dtype (bf16: fp32 subtract, round-to-nearest-even to bf16), so
+ * the maxima are bit-identical to the reference's.
+ *
+ * result: float[n_seg][4] =
+ *   { max|ref-out|, max|ref|, 1.0 if any (ref-out) is NaN else 0.0,
+ *     1.0 if any ref is NaN else 0.0 }
+ * NaNs are excluded from the two maxima and reported through the flags; the
+ * host turns a set flag into the NaN that torch's max() would propagate.
+ * The call overwrites `result` (no pre-clearing needed).
+ * ref/out must be 16-byte aligned; numel_per_seg * sizeof(element) must be a
+ * multiple of 16 unless n_seg == 1.
+ * ------------------------------------------------------------------------- */
+int cb2_verify_reduce(const void* ref, const void* out, int64_t numel_per_seg,
+                      int64_t n_seg, int dtype, float* result, void* stream);
+
+/* -------------------------------------------------------------------------
+ * (a) folded weight chain.
+ * cb2_linear_f32 replaces the `linear` binding on the folded root
+ * `linear(input, fused_N)` (packages/catopt-torch/src/catopt_torch/
+ * torch_bridge.py:1251-1253):  y[R,out] = x[R,in] . w[out,in]^T  (+ bias[out]
+ * when bias != NULL).  fp32 in, fp32 accumulate.
+ * scratch: split-K partial sums, cb2_linear_f32_scratch_bytes(R,in,out) bytes
+ * (may be 0, in which case scratch may be NULL).
+ * ------------------------------------------------------------------------- */
+size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_features);
+int cb2_linear_f32(const float* x, const float* w, const float* bias, float* y,
+                   int R, int in_features, int out_features, void* scratch,
+                   size_t scratch_bytes, void* stream);
+
+/* cb2_matmul_f32: c[M,N] = a[M,K] . b[K,N], the `matmul` binding
+ * (torch_bridge.py:1147) for two dense fp32 matrices. */
+int cb2_matmul_f32(const float* a, const float* b, float* c, int M, int N, int K,
+                   void* stream);
+
+/* cb2_chain_fold_f32 replaces the matmul arm of `IRModule._fold_weight_chains`
+ * (torch_bridge.py:2485-2510) for a chain of k bias-free Linear weights:
+ *     out = W[k-1] . ( ... (W[2] . (W[1] . W[0])) )
+ * evaluated innermost-first, the association the extracted right-nested term
+ * carries.  W[i] has shape [dims[i+1], dims[i]] (nn.Linear's [out,in]);
+ * `weights` is a HOST array of k device pointers, `dims` a HOST array of k+1
+ * ints; out has shape [dims[k], dims[0]].
+ * scratch: two intermediate products, cb2_chain_fold_f32_scratch_bytes(). */
+size_t cb2_chain_fold_f32_scratch_bytes(const int* dims, int k);
+int cb2_chain_fold_f32(const float* const* weights, const int* dims, int k,
+                       float* out, void* scratch, size_t scratch_bytes,
+                       void* stream);
+
+/* -------------------------------------------------------------------------
+ * (b) chunked decayed attention,  o[t] = sum_{s<=t} gamma_h^(t-s) (q_t.k_s) v_s / scale.
+ * Replaces `ChunkedDecayModule._forward_impl`
+ * (packages/catopt-carriers/src/catopt_carriers/decayed_lower.py:702-724:
+ * `_forward_intra` 609-639 + `_forward_cross` 671-700) for the uniform
+ * K-chunk term of `om_decayed_kway_blocks` (om.py:3076-3152), with the O(K^2)
+ * pair products replaced by the state carry
+ *     O_i = (Q_i K_i^T . D) V_i + diag(g^(r+1)) Q_i S_i ;
+ *     S_{i+1} = g^C S_i + (K_i . g^(C-1-r))^T V_i
+ * (the recurrence the reference spells in lab/probes/retnet_baseline_probe.py:
+ * 77-110).  Only chunk-local exponents appear, so nothing overflows.
+ *
+ * q,k: [B,H,T,dk]; v,o: [B,H,T,dv]; gamma: float[H] (device, fp32, 0<g<=1);
+ * T % chunk == 0.  dtype is the element type of q,k,v,o; products accumulate
+ * and the state is carried in fp32.
+ * scratch: cb2_decayed_chunk_scratch_bytes() bytes (per-chunk K^T V products
+ * for the fp32 path; 0 for paths that keep the state on chip).
+ * ------------------------------------------------------------------------- */
+size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv,
+                                       int chunk, int dtype);
+int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
+                          const float* gamma, int B, int H, int T, int dk, int dv,
+                          int chunk, float scale, int dtype, void* scratch,
+                          size_t scratch_bytes, int* dev_status, void* stream);
+
+/* -------------------------------------------------------------------------
+ * (c) diagonal linear recurrence with readout,
+ *     h_t[n] = a_t[n] * h_{t-1}[n] + b[n] * x_t ;  y_t = sum_n c[n] * h_t[n].
+ * One step is the reference's `applyd(aff_diag(a_t, b*x_t), h)`
+ * (torch_bridge.py:1895-1900); the whole sequence replaces the level-batched
+ * reduction of `BatchedScanModule._forward_impl`
+ * (packages/catopt-carriers/src/catopt_carriers/scan_lower.py:569-698) and
+ * the all-prefix form `BatchedOmdModule._prefix_scan` (omd_lower.py:771-824).
+ *
+ * a: [B,T,D,N] (a_bcast_n == 0) or [B,T,D] shared over n (a_bcast_n == 1);
+ * x,y: [B,T,D]; b,c: [D,N]; h0 (may be NULL = zeros) and hT (may be NULL):
+ * float[B,D,N].  dtype is the element type of a,x,b,c,y; every element is
+ * widened to fp32 before any arithmetic, the state and the n-sum stay fp32
+ * and y is rounded once.  N must be one of 1,2,4,8,16,32; D*N*sizeof(element)
+ * and D*sizeof(element) must be multiples of 16 and all pointers 16-byte
+ * aligned.
+ * ------------------------------------------------------------------------- */
+int cb2_diag_scan_fwd(const void* a, const void* x, const void* b, const void* c,
+                      const float* h0, void* y, float* hT, int B, int T, int D,
+                      int N, int a_bcast_n, int dtype, int* dev_status,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CATOPT_B200_H */

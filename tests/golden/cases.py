@@ -1,0 +1,107 @@
+"""Seeded inputs shared by the fixture generator and the parity tests.
+
+Everything is drawn from numpy's PCG64 generator (bit-stable across machines
+and library versions), in fp64, then cast; the fixtures store only outputs.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+# name -> (B, H, T, d, chunk, dtype, per_head_gamma, scale)
+DECAYED_CASES = {
+    "tiny_f64": (2, 2, 32, 8, 8, torch.float64, True, 1.0),
+    "tiny_f32_scalar": (2, 3, 48, 16, 16, torch.float32, False, 2.0),
+    "odd_f32": (1, 2, 96, 32, 32, torch.float32, True, 1.0),
+    # BASELINE config 2 (full size); the fixture keeps every 37th time step.
+    "c2_f32": (2, 4, 1024, 64, 64, torch.float32, False, 1.0),
+    # two heads of BASELINE config 4's shape, bf16-rounded inputs, fp32 arithmetic
+    "c4_slice": (1, 2, 512, 128, 128, torch.float32, True, 1.0),
+}
+# fixtures of the large cases keep every n-th time step only
+ROW_STRIDE = {"c2_f32": 37, "c4_slice": 7}
+
+
+def rng(seed: int) -> np.random.Generator:
+    return np.random.default_rng(seed)
+
+
+def decayed_inputs(name: str):
+    """q, k, v ~ N(0,1)/sqrt(d) and gamma for a named case."""
+    B, H, T, d, C, dtype, per_head, scale = DECAYED_CASES[name]
+    g = rng(1000 + sorted(DECAYED_CASES).index(name))
+    q, k, v = (torch.from_numpy(g.standard_normal((B, H, T, d)) / np.sqrt(d)) for _ in range(3))
+    if name == "c4_slice":
+        # config 4's rates for heads 0 and 31 of 32: 1 - 2^(-5 - 8h/32)
+        gamma = torch.tensor([1 - 2.0 ** (-5 - 8 * h / 32) for h in (0, 31)], dtype=torch.float64)
+        q, k, v = (t.to(torch.bfloat16).to(torch.float64) for t in (q, k, v))
+    elif per_head:
+        gamma = torch.tensor([0.9 + 0.09 * h / max(H - 1, 1) for h in range(H)], dtype=torch.float64)
+    else:
+        gamma = torch.tensor(0.97, dtype=torch.float64)
+    return q.to(dtype), k.to(dtype), v.to(dtype), gamma.to(dtype), C, scale
+
+
+# name -> (k, d_in/out, rows)
+CHAIN_CASES = {"small": (4, 32, 8), "c1": (8, 512, 64)}
+
+
+def chain_inputs(name: str):
+    """k bias-free Linear weights ~N(0,1/d) and x ~N(0,1), fp32 (config 1)."""
+    k, d, rows = CHAIN_CASES[name]
+    g = rng(2000 + sorted(CHAIN_CASES).index(name))
+    ws = [torch.from_numpy(g.standard_normal((d, d)) / np.sqrt(d)).float() for _ in range(k)]
+    x = torch.from_numpy(g.standard_normal((rows, d))).float()
+    return ws, x
+
+
+# name -> (B, T, D, N, dtype, a_shared_over_n, with_h0)
+SCAN_CASES = {
+    "tiny_f32": (2, 37, 8, 4, torch.float32, False, True),
+    "n16_bf16": (2, 50, 64, 16, torch.bfloat16, False, False),
+    "shared_a_f32": (1, 33, 16, 8, torch.float32, True, True),
+    "n1_f32": (2, 19, 8, 1, torch.float32, False, False),
+}
+
+
+def scan_inputs(name: str):
+    """Config 3's distributions: x~N(0,1), a=sigmoid(N(4,0.5)), b,c~N(0,1/16)."""
+    B, T, D, N, dtype, shared, with_h0 = SCAN_CASES[name]
+    g = rng(3000 + sorted(SCAN_CASES).index(name))
+    x = torch.from_numpy(g.standard_normal((B, T, D)))
+    ashape = (B, T, D) if shared else (B, T, D, N)
+    a = torch.sigmoid(torch.from_numpy(4 + 0.5 * g.standard_normal(ashape)))
+    b = torch.from_numpy(g.standard_normal((D, N)) / 4)
+    c = torch.from_numpy(g.standard_normal((D, N)) / 4)
+    h0 = torch.from_numpy(g.standard_normal((B, D, N))).float() if with_h0 else None
+    return a.to(dtype), x.to(dtype), b.to(dtype), c.to(dtype), h0
+
+
+def verify_cases():
+    """(name, ref, out, rtol, atol) pairs incl. the reference tests' edge cases."""
+    g = rng(4000)
+    cases = []
+    r = torch.from_numpy(g.standard_normal((4, 33, 17))).float()
+    cases.append(("f32_close", r, r + 1e-6 * torch.from_numpy(g.standard_normal(r.shape)).float(), 1e-4, None))
+    cases.append(("f32_far", r, r * 1.01, 1e-4, None))
+    cases.append(("f32_atol", r, r + 1e-3, 1e-2, 1e-4))
+    rb = torch.from_numpy(g.standard_normal((4, 512, 64))).to(torch.bfloat16)
+    ob = (rb.float() * (1 + 4e-3 * torch.from_numpy(g.standard_normal(rb.shape)).float())).to(torch.bfloat16)
+    cases.append(("bf16_noise", rb, ob, 2e-2, None))
+    # the bf16 difference is rounded to bf16: -3 - 2^-9 reports 3.0, not 3.00195
+    cases.append(("bf16_round", torch.tensor([-3.0, 1.0] * 8, dtype=torch.bfloat16),
+                  torch.tensor([2.0 ** -9, 1.0] * 8, dtype=torch.bfloat16), 1e-4, None))
+    z = torch.zeros(64)
+    cases.append(("zero_ref", z, z + 1e-9, 1e-4, None))       # the 1e-8 floor
+    cases.append(("identical", r, r.clone(), 1e-4, 0.0))
+    n = r.clone()
+    n[1, 2, 3] = float("nan")
+    cases.append(("nan_out", r, n, 1e-4, None))
+    cases.append(("nan_ref", n, r, 1e-4, None))
+    i1 = r.clone()
+    i1[0, 0, 0] = float("inf")
+    cases.append(("inf_both", i1, i1.clone(), 1e-4, None))      # inf - inf = nan
+    cases.append(("inf_ref", i1, r, 1e-4, None))
+    cases.append(("odd_len_bf16", rb.flatten()[:1003], ob.flatten()[:1003], 2e-2, None))
+    cases.append(("single", torch.tensor([2.0]), torch.tensor([2.5]), 1e-4, None))
+    return cases
