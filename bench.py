@@ -1,0 +1,413 @@
+"""Benchmark of the lowered-executor hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this repo's CUDA path
+    python bench.py --impl reference --steps K --warmup W    # the reference algorithm on host cores
+
+Headline workload (``config.workload``): BASELINE config 4, decayed causal linear
+attention B=16 H=32 T=8192 d=128 bf16, per-head gamma, chunk 128 — per GPU; at
+N>1 every rank owns its own contiguous range of the flattened batch x head axis
+of a global batch of 16*N (weak scaling, no collective on the path).  A "token"
+is one (batch, time) position; a step is one pass of the executor over the
+rank's shard.  ``value`` is measured with inputs resident in HBM, ``e2e`` through
+the public module with pinned host buffers copied in and the result copied out
+inside the timed region.  ``kernels`` carries the same measurement for the other
+lowered executors (configs 1, 2, 3, 5).  One JSON line on stdout (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+C4 = dict(B=16, H=32, T=8192, d=128, chunk=128)
+L2_BYTES = 126 * 2**20
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+def c4_gamma(H: int) -> torch.Tensor:
+    return torch.tensor([1 - 2.0 ** (-5 - 8 * h / H) for h in range(H)], dtype=torch.float32)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thr: threading.Thread | None = None
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                     "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thr:
+            self._thr.join(timeout=10)
+
+    def summary(self) -> dict:
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+# --------------------------------------------------------------------------- timing
+def dist_info():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, local, world
+
+
+def barrier(world: int) -> None:
+    if world > 1:
+        torch.distributed.barrier()
+
+
+def max_over_ranks(ms: float, world: int) -> float:
+    if world == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(step, steps: int, warmup: int, world: int, flush: torch.Tensor | None = None) -> float:
+    """Total device milliseconds of exactly ``steps`` calls, max over ranks.
+
+    Large workloads (inputs > L2) are timed as one region; with ``flush`` given,
+    each step is timed by its own event pair and L2 is overwritten in between.
+    """
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    torch.cuda.synchronize()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    else:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(steps)]
+        for a, b in evs:
+            flush.add_(1)
+            a.record()
+            step()
+            b.record()
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in evs)
+    barrier(world)
+    return max_over_ranks(ms, world)
+
+
+# --------------------------------------------------------------------------- CPU legs
+def cpu_reference_step_fn(heads: int = 1):
+    """One bounded sample of the headline workload on the host cores: the
+    reference's pairwise-chunked executor algorithm (restated in oracle/), fp32
+    on bf16-rounded inputs, for ``heads`` of the 512 (batch, head) slices."""
+    from oracle import oracle
+
+    T, d, C, H = C4["T"], C4["d"], C4["chunk"], C4["H"]
+    g = torch.Generator().manual_seed(1234)
+    q, k, v = (torch.randn(1, heads, T, d, generator=g).div_(math.sqrt(d)).bfloat16().float()
+               for _ in range(3))
+    gamma = c4_gamma(H)[:heads]
+
+    def step():
+        with torch.no_grad():
+            return oracle.decayed_chunked_pairwise(q, k, v, gamma, C, 1.0)
+
+    tokens = heads * T / H  # token-equivalents: a token is one (b,t) position over all 32 heads
+    return step, tokens
+
+
+def time_cpu(step, steps: int, warmup: int) -> float:
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    return (time.perf_counter() - t0) * 1e3
+
+
+def run_reference(args) -> None:
+    rank, _, world = dist_info()
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    step, tokens = cpu_reference_step_fn(heads=4)
+    ms = time_cpu(step, args.steps, args.warmup)
+    value = tokens * args.steps / (ms / 1e3)
+    sample = ("4 of 512 (batch,head) slices of config 4 per step (T=8192, d=128, chunk 128), fp32 on "
+              "bf16-rounded inputs, pairwise-chunked executor algorithm; tokens = slice share of a "
+              "32-head position")
+    line = {
+        "impl": "reference", "metric": "tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "config4_decayed_attention_B16_H32_T8192_d128_bf16_chunk128_per_gpu",
+            "global_batch": C4["B"] * n_gpus, "heads": C4["H"], "seq_len": C4["T"], "d_head": C4["d"],
+            "chunk": C4["chunk"], "parallelism": f"batch x head shards over {n_gpus} GPU(s), no collective",
+            "l2_policy": "inputs (4.3 GB per GPU) exceed L2; small kernels flush L2 between steps"}
+
+
+# --------------------------------------------------------------------------- GPU side
+def _randn_bf16(shape, gen, scale=1.0, dev="cuda"):
+    """Seeded N(0,1)*scale in bf16, generated slab by slab to bound fp32 temporaries."""
+    out = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+    flat = out.view(shape[0], -1)
+    for i in range(shape[0]):
+        flat[i].copy_(torch.randn(flat.shape[1], device=dev, generator=gen).mul_(scale))
+    return out
+
+
+def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> dict:
+    """The other lowered executors (configs 1, 2, 3, 5), same timing contract."""
+    from catopt_b200 import ops
+    from catopt_b200.executors import B200FoldedLinear
+    from catopt_b200.sharding import shard_range
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+    K, W = args.steps, args.warmup
+    hbm = pk["hbm_gbs"] * 1e9
+    out = {}
+
+    def entry(ms_total, tokens, abytes, launches, note, flops=None):
+        t = ms_total / K / 1e3
+        e = {"tokens_per_s": world * tokens / t, "us_per_step": t * 1e6,
+             "roofline": {"bound": "hbm", "achieved": abytes / t / 1e9, "peak": pk["hbm_gbs"],
+                          "unit": "GB/s", "frac": abytes / t / hbm, "traffic": None},
+             "gpu_launches_per_step": launches, "note": note}
+        if flops:
+            e["tflops"] = flops / t / 1e12
+        return e
+
+    # config 1: 8 x Linear(512,512) fp32 folded once, then one GEMM on x[64,512]
+    ws = [torch.randn(512, 512, device=dev, generator=gen) / math.sqrt(512) for _ in range(8)]
+    mod = B200FoldedLinear(ws)
+    x = torch.randn(64, 512, device=dev, generator=gen)
+    y = torch.empty(64, 512, device=dev)
+    ms = time_steps(lambda: ops.linear_f32(x, mod.weight, out=y), K, W, world, flush)
+    out["config1_folded_chain_fp32"] = entry(ms, 64, (512 * 512 + 2 * 64 * 512) * 4, 2,
+                                             "latency-bound: 64 rows; L2 flushed between steps",
+                                             flops=2 * 64 * 512 * 512)
+    # the reference's published shape: R=4096 rows through the folded weight
+    x4 = torch.randn(4096, 512, device=dev, generator=gen)
+    y4 = torch.empty(4096, 512, device=dev)
+    ms = time_steps(lambda: ops.linear_f32(x4, mod.weight, out=y4), K, W, world, flush)
+    out["folded_chain_fp32_R4096"] = entry(ms, 4096, (512 * 512 + 2 * 4096 * 512) * 4, 1,
+                                           "reference's published cell k8_d512_R4096",
+                                           flops=2 * 4096 * 512 * 512)
+    del ws, x4, y4
+
+    # config 2: B=2 H=4 T=1024 d=64 fp32, gamma 0.97, chunk 64
+    q, k, v = (torch.randn(2, 4, 1024, 64, device=dev, generator=gen) / 8 for _ in range(3))
+    g2 = torch.full((4,), 0.97, device=dev)
+    o2 = torch.empty_like(v)
+    ms = time_steps(lambda: ops.decayed_chunk_fwd(q, k, v, g2, 64, 1.0, out=o2), K, W, world, flush)
+    out["config2_decayed_fp32"] = entry(ms, 2 * 1024, 4 * 2 * 4 * 1024 * 64 * 4, 5,
+                                        "latency-bound: 8 heads; L2 flushed between steps",
+                                        flops=8 * 1024 * (4 * 64 * 64 + 4 * 64 * 64))
+    del q, k, v, o2
+
+    # config 3: scan B=8 D=1024 N=16 T=4096 bf16; ranks own channel blocks of the (b,d) axis
+    B, T, D, N = 8, 4096, 1024, 16
+    x3 = _randn_bf16((B, T, D), gen)
+    a3 = torch.empty(B, T, D, N, dtype=torch.bfloat16, device=dev)
+    for b in range(B):
+        a3[b].copy_(torch.sigmoid(4 + 0.5 * torch.randn(T, D, N, device=dev, generator=gen)))
+    b3 = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
+    c3 = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
+    y3 = torch.empty_like(x3)
+    ms = time_steps(lambda: ops.diag_scan_fwd(a3, x3, b3, c3, None, out=y3), K, W, world)
+    out["config3_diag_scan_bf16"] = entry(ms, B * T, (B * T * D * (N + 2) + 2 * D * N) * 2, 1,
+                                          "inputs 1.2 GB exceed L2", flops=5 * B * T * D * N)
+    del a3, x3, y3
+
+    # config 5: verify 13 checks x 256 probes x [4,512,1024] bf16; probes sharded over ranks
+    p0, p1 = shard_range(256, rank, world)
+    probes = p1 - p0
+    ref = _randn_bf16((13, probes * 4 * 512 * 1024), gen)
+    outp = ref.clone()
+    outp[:, ::4099] += 0.0625
+    res = torch.empty(13, 4, device=dev)
+
+    def verify_step():
+        ops.verify_reduce(ref, outp, 13, result=res)
+        if world > 1:
+            torch.distributed.all_reduce(res, op=torch.distributed.ReduceOp.MAX)
+
+    ms = time_steps(verify_step, K, W, world)
+    e = entry(ms, probes * 4 * 512, 2 * ref.numel() * 2, 2,
+              "13 checks per step; ends with one max all-reduce when sharded")
+    e["tokens_per_s"] = 256 * 4 * 512 * 13 / (ms / K / 1e3)  # probe tokens x checks, whole job
+    out["config5_verify_bf16"] = e
+    del ref, outp
+    ops.check_device_status(dev)
+    return out
+
+
+def run_ours(args) -> None:
+    rank, local, world = dist_info()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    from catopt_b200 import _lib, build, ops
+    from catopt_b200.host_api import DecayedHostPipeline
+
+    if not _lib.LIB_PATH.exists() and rank == 0:
+        build.build()
+    barrier(world)
+    pk = peaks()
+    B, H, T, d, C = (C4[k] for k in ("B", "H", "T", "d", "chunk"))
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v = (_randn_bf16((B * H, T * d), gen, 1 / math.sqrt(d)).view(B, H, T, d) for _ in range(3))
+    gamma = c4_gamma(H).to(dev)
+    o = torch.empty_like(v)
+    code = _lib.CB2_BF16
+    path = "tcgen05" if _lib.load().cb2_decayed_chunk_scratch_bytes(B, H, T, d, d, C, code) == 0 else "ffma"
+    launches_per_step = 1 if path == "tcgen05" else 5
+
+    def step():
+        ops.decayed_chunk_fwd(q, k, v, gamma, C, 1.0, out=o)
+
+    with ClockSampler(local) as clk:
+        ms = time_steps(step, args.steps, args.warmup, world)
+    ops.check_device_status(dev)
+    tokens = B * T
+    t_step = ms / args.steps / 1e3
+    abytes = 4 * B * H * T * d * 2
+    flops = B * H * T * (4 * C * d + 4 * d * d)
+
+    # end to end: pinned host buffers in, result out, every step
+    pipe = DecayedHostPipeline(B, H, T, d, d, torch.bfloat16, gamma, C, 1.0, n_slabs=16, device=dev)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(B, H, T, d, dtype=torch.bfloat16).pin_memory()
+    del q, k, v
+    ms_e2e = time_steps(lambda: pipe.run(hq, hk, hv, ho), args.steps, args.warmup, world)
+    if not torch.equal(ho.view(torch.int16), o.cpu().view(torch.int16)):
+        raise SystemExit("e2e result differs from the device-resident result")
+    e2e_launches = launches_per_step * len(pipe.bounds)
+    del pipe, hq, hk, hv, ho, o
+    torch.cuda.empty_cache()
+
+    flush = torch.zeros(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+    extras = bench_extras(args, rank, world, pk, flush) if not args.no_extras else {}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        cstep, ctok = cpu_reference_step_fn(heads=4)
+        cms = time_cpu(cstep, 3, 1)
+        cpu = {"value": ctok * 3 / (cms / 1e3), "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": "3 timed passes over 4 of 512 (batch,head) slices of config 4, fp32 on "
+                         "bf16-rounded inputs, the reference's pairwise-chunked algorithm"}
+    if rank != 0:
+        return
+    line = {
+        "metric": "tokens/s", "value": world * tokens / t_step, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(world),
+        "roofline": {"bound": "hbm", "achieved": abytes / t_step / 1e9, "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": abytes / t_step / (pk["hbm_gbs"] * 1e9), "traffic": None,
+                     "peak_source": pk["source"], "kernel": f"decayed_chunk ({path})",
+                     "tensor_tflops": flops / t_step / 1e12,
+                     "tensor_frac_of_sustained": flops / t_step / (pk["bf16_tflops_sustained"] * 1e12)},
+        "e2e": {"value": world * tokens / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": 3 * B * H * T * d * 2, "d2h_bytes_per_step": B * H * T * d * 2,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": args.steps * launches_per_step,
+        "e2e_gpu_launches": args.steps * e2e_launches,
+        "clocks": clk.summary(),
+        "kernels": extras,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel lines")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

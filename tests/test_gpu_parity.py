@@ -1,0 +1,286 @@
+"""Parity of the CUDA path (through the C ABI) against the oracle and against the
+reference's stored outputs.  Needs a B200: run with ``-m gpu``.
+
+Tolerances (relative to the largest reference magnitude, the reference's own
+verify metric): 1e-5 for fp32, 2e-2 for bf16; the verify reduction is exact.
+"""
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+FP32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+def rel_to_max(got: torch.Tensor, want: torch.Tensor) -> float:
+    got, want = got.double().cpu(), want.double().cpu()
+    return ((got - want).abs().max() / (want.abs().max() + 1e-8)).item()
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from catopt_b200 import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+# --------------------------------------------------------------------------- (d) verify
+@pytest.mark.parametrize("case", cases.verify_cases(), ids=lambda c: c[0])
+def test_verify_exact_vs_reference_fixture(dev, case):
+    from catopt_b200 import verify
+
+    name, ref, out, rtol, atol = case
+    want = np.load(GOLD / "verify.npz")[name]
+    rep = verify.verify_equiv(ref.to(dev), out.to(dev), rtol=rtol, atol=atol)
+    for got, exp in ((rep.max_abs, want[0]), (rep.max_rel, want[1])):
+        assert (math.isnan(got) and math.isnan(exp)) or got == exp, (name, got, exp)
+    assert rep.passed == bool(want[2])
+
+
+def test_verify_tuple_and_mismatch(dev):
+    from catopt_b200 import verify
+
+    g = np.load(GOLD / "verify.npz")
+    cs = cases.verify_cases()
+    r = (cs[0][1].to(dev), cs[3][1].to(dev))
+    o = (cs[0][2].to(dev), cs[3][2].to(dev))
+    rep = verify.verify_equiv(r, o, rtol=2e-2)
+    assert [rep.max_abs, rep.max_rel, float(rep.passed), *rep.per_output] == list(g["tuple"])
+    rep = verify.verify_equiv(r, o[:1], rtol=2e-2)
+    assert rep.max_abs == math.inf and not rep.passed
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(3, 4, 512, 64), (5, 1, 77, 8), (2, 1, 1, 3)])
+def test_verify_batched_vs_oracle(dev, dtype, shape):
+    """Segmented reduction (one segment per check) incl. odd, unaligned sizes."""
+    from catopt_b200 import verify
+
+    g = torch.Generator().manual_seed(7)
+    ref = torch.randn(shape, generator=g).to(dtype)
+    out = (ref.float() + 0.01 * torch.randn(shape, generator=g)).to(dtype)
+    reps = verify.verify_batched(ref.to(dev), out.to(dev), shape[0], rtol=2e-2)
+    for i, rep in enumerate(reps):
+        want = oracle.verify_pair(ref[i], out[i], rtol=2e-2)
+        assert (rep.max_abs, rep.max_rel, rep.passed) == (want.max_abs, want.max_rel, want.passed)
+
+
+def test_verify_full_probe_size_properties(dev):
+    """BASELINE config 5's tensor size ([4,512,1024] bf16 per probe, 8 probes x 3
+    checks here): planted maxima are found exactly; untouched checks report 0."""
+    from catopt_b200 import ops
+
+    n_checks, probes = 3, 8
+    ref = torch.randn(n_checks, probes, 4, 512, 1024, device=dev).to(torch.bfloat16)
+    out = ref.clone()
+    out[1, 5, 3, 100, 77] = ref[1, 5, 3, 100, 77] + 8.0
+    ref[2, 0, 0, 0, 0] = 1000.0
+    out[2, 0, 0, 0, 0] = 1000.0
+    res = ops.verify_reduce(ref, out, n_checks).cpu()
+    want1 = (ref[1, 5, 3, 100, 77].float() - out[1, 5, 3, 100, 77].float()).to(torch.bfloat16).abs().item()
+    assert res[0, 0] == 0 and res[2, 0] == 0 and res[1, 0] == want1
+    assert res[2, 1] == 1000.0
+    assert res[0, 1] == ref[0].abs().max().item()
+    assert res[:, 2:].sum() == 0
+
+
+# --------------------------------------------------------------------------- (a) chain
+@pytest.mark.parametrize("name", list(cases.CHAIN_CASES))
+def test_chain_fold_and_linear_vs_reference(dev, name):
+    from catopt_b200.executors import B200FoldedLinear
+
+    g = np.load(GOLD / "chain.npz")
+    ws, x = cases.chain_inputs(name)
+    mod = B200FoldedLinear([w.to(dev) for w in ws])
+    assert mod.is_batched and mod.fused_name == f"fused_{2 * len(ws) - 2}"
+    wf_ref = oracle.fold_chain(ws)
+    assert rel_to_max(mod.weight, wf_ref) <= FP32_TOL
+    y = mod(x.to(dev))
+    assert rel_to_max(y, torch.from_numpy(g[f"{name}.y_folded"])) <= FP32_TOL
+    assert rel_to_max(y, torch.from_numpy(g[f"{name}.y_eager"])) <= FP32_TOL
+
+
+@pytest.mark.parametrize("rows,n_in,n_out", [(1, 7, 5), (64, 512, 512), (300, 130, 70), (4096, 512, 512)])
+def test_linear_shapes_and_bias(dev, rows, n_in, n_out):
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, n_in, generator=g)
+    w = torch.randn(n_out, n_in, generator=g) / math.sqrt(n_in)
+    b = torch.randn(n_out, generator=g)
+    want = torch.nn.functional.linear(x.double(), w.double(), b.double())
+    got = ops.linear_f32(x.to(dev), w.to(dev), b.to(dev))
+    assert rel_to_max(got, want) <= FP32_TOL
+    got = ops.matmul_f32(x.to(dev), w.t().contiguous().to(dev))
+    assert rel_to_max(got, want - b.double()) <= FP32_TOL
+
+
+def test_linear_is_linear_at_published_size(dev):
+    """R=65536 rows (the reference's largest published cell): linearity
+    f(ax+by) = a f(x) + b f(y) holds to fp32 rounding."""
+    from catopt_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(65536, 512, device=dev, generator=g)
+    y = torch.randn(65536, 512, device=dev, generator=g)
+    w = torch.randn(512, 512, device=dev, generator=g) / math.sqrt(512)
+    lhs = ops.linear_f32(2.0 * x - 3.0 * y, w)
+    rhs = 2.0 * ops.linear_f32(x, w) - 3.0 * ops.linear_f32(y, w)
+    assert rel_to_max(lhs, rhs) <= FP32_TOL
+
+
+# --------------------------------------------------------------------------- (b) decayed
+@pytest.mark.parametrize("name", [n for n in cases.DECAYED_CASES if n != "tiny_f64"])
+def test_decayed_fp32_vs_reference_fixture(dev, name):
+    from catopt_b200.executors import B200ChunkedDecay
+
+    g = np.load(GOLD / "decayed.npz")
+    q, k, v, gamma, C, scale = cases.decayed_inputs(name)
+    mod = B200ChunkedDecay(gamma, q.shape[1], C, scale).to(dev)
+    out = mod(q.to(dev), k.to(dev), v.to(dev))
+    stride = cases.ROW_STRIDE.get(name, 1)
+    want = torch.from_numpy(g[f"{name}.chunked"])
+    assert rel_to_max(out[:, :, ::stride], want) <= FP32_TOL
+    assert rel_to_max(out[:, :, ::stride], torch.from_numpy(g[f"{name}.quadratic"])) <= FP32_TOL
+
+
+def test_decayed_f64_case_in_fp32(dev):
+    """The reference's fp64 test shape, run in fp32 against its fp64 output."""
+    from catopt_b200 import ops
+
+    g = np.load(GOLD / "decayed.npz")
+    q, k, v, gamma, C, scale = cases.decayed_inputs("tiny_f64")
+    out = ops.decayed_chunk_fwd(q.float().to(dev), k.float().to(dev), v.float().to(dev),
+                                gamma.float().to(dev), C, scale)
+    assert rel_to_max(out, torch.from_numpy(g["tiny_f64.chunked"])) <= FP32_TOL
+
+
+@pytest.mark.parametrize("B,H,T,d,C", [(1, 2, 512, 128, 128), (2, 3, 256, 64, 64), (1, 1, 128, 128, 128),
+                                       (1, 2, 96, 32, 32)])
+def test_decayed_bf16_vs_oracle(dev, B, H, T, d, C):
+    """bf16 tensors: the oracle runs the reference's pairwise executor in fp32 on
+    the bf16-rounded inputs (a pure-bf16 reference run is unusable: gamma_h
+    rounds to 1.0)."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(B * 1000 + T)
+    q, k, v = (torch.randn(B, H, T, d, generator=g) / math.sqrt(d) for _ in range(3))
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    gamma = torch.tensor([1 - 2.0 ** (-5 - 8 * h / max(H, 1)) for h in range(H)], dtype=torch.float32)
+    want = oracle.decayed_chunked_pairwise(q.float(), k.float(), v.float(), gamma, C, 1.0)
+    out = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), C, 1.0)
+    assert out.dtype == torch.bfloat16
+    assert rel_to_max(out, want) <= BF16_TOL
+
+
+def test_decayed_chunk_size_invariance(dev):
+    """Size-independent property: the result does not depend on the chunk size."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(2, 2, 256, 64, generator=g).to(dev) / 8 for _ in range(3))
+    gamma = torch.tensor([0.95, 0.99], device=dev)
+    outs = [ops.decayed_chunk_fwd(q, k, v, gamma, C, 1.0) for C in (16, 64, 128, 256)]
+    for o in outs[1:]:
+        assert rel_to_max(o, outs[0]) <= FP32_TOL
+
+
+def test_decayed_rejects_ragged_T(dev):
+    from catopt_b200 import B200Error, ops
+
+    q = torch.zeros(1, 1, 100, 16, device=dev)
+    with pytest.raises(B200Error):
+        ops.decayed_chunk_fwd(q, q, q, torch.ones(1, device=dev), 64)
+
+
+# --------------------------------------------------------------------------- (c) scan
+@pytest.mark.parametrize("name", list(cases.SCAN_CASES))
+def test_scan_vs_reference_fixture(dev, name):
+    from catopt_b200.executors import B200DiagScan
+
+    g = np.load(GOLD / "scan.npz")
+    a, x, b, c, h0 = cases.scan_inputs(name)
+    mod = B200DiagScan(b, c, return_state=True).to(dev)
+    y, hT = mod(a.to(dev), x.to(dev), None if h0 is None else h0.to(dev))
+    tol = BF16_TOL if x.dtype == torch.bfloat16 else FP32_TOL
+    assert y.dtype == x.dtype
+    assert rel_to_max(y, torch.from_numpy(g[f"{name}.y"])) <= tol
+    assert rel_to_max(y, torch.from_numpy(g[f"{name}.y_prefix"])) <= tol
+    assert rel_to_max(hT, torch.from_numpy(g[f"{name}.hT"])) <= FP32_TOL
+    assert rel_to_max(hT, torch.from_numpy(g[f"{name}.hT_tree"])) <= FP32_TOL
+
+
+@pytest.mark.parametrize("B,T,D,N,dtype", [
+    (2, 1, 8, 16, torch.bfloat16), (1, 15, 64, 16, torch.bfloat16), (1, 16, 40, 16, torch.bfloat16),
+    (2, 17, 32, 16, torch.bfloat16), (1, 130, 96, 16, torch.bfloat16), (1, 65, 8, 32, torch.float32),
+    (1, 64, 16, 2, torch.bfloat16), (3, 33, 8, 8, torch.float32),
+])
+def test_scan_edges_vs_oracle(dev, B, T, D, N, dtype):
+    """Ragged tiles (T around the 16-step tile), partial channel blocks, every N."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(T * 100 + D)
+    x = torch.randn(B, T, D, generator=g).to(dtype)
+    a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, N, generator=g)).to(dtype)
+    b = (torch.randn(D, N, generator=g) / 4).to(dtype)
+    c = (torch.randn(D, N, generator=g) / 4).to(dtype)
+    h0 = torch.randn(B, D, N, generator=g)
+    want_y, want_h = oracle.diag_scan_serial(a, x, b, c, h0)
+    y, hT = ops.diag_scan_fwd(a.to(dev), x.to(dev), b.to(dev), c.to(dev), h0.to(dev), want_state=True)
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert rel_to_max(y, want_y) <= tol
+    assert rel_to_max(hT, want_h) <= FP32_TOL
+
+
+def test_scan_segment_composition_at_full_width(dev):
+    """Size-independent property at config 3's width (D=1024, N=16, bf16):
+    scanning [0,T) equals scanning [0,T/2) then [T/2,T) from the carried state —
+    bit for bit, since each step's arithmetic is identical."""
+    from catopt_b200 import ops
+
+    B, T, D, N = 2, 512, 1024, 16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(B, T, D, device=dev, generator=g).to(torch.bfloat16)
+    a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, N, device=dev, generator=g)).to(torch.bfloat16)
+    b = (torch.randn(D, N, device=dev, generator=g) / 4).to(torch.bfloat16)
+    c = (torch.randn(D, N, device=dev, generator=g) / 4).to(torch.bfloat16)
+    y, hT = ops.diag_scan_fwd(a, x, b, c, None, want_state=True)
+    h = T // 2
+    y1, h1 = ops.diag_scan_fwd(a[:, :h].contiguous(), x[:, :h].contiguous(), b, c, None, want_state=True)
+    y2, h2 = ops.diag_scan_fwd(a[:, h:].contiguous(), x[:, h:].contiguous(), b, c, h1, want_state=True)
+    assert torch.equal(torch.cat([y1, y2], 1), y) and torch.equal(h2, hT)
+    want_y, _ = oracle.diag_scan_serial(a[:1, :, :64].cpu(), x[:1, :, :64].cpu(), b[:64].cpu(), c[:64].cpu())
+    assert rel_to_max(y[:1, :, :64], want_y) <= BF16_TOL
+
+
+def test_device_status_clean(dev):
+    """No kernel in this file ran into a bounded-wait timeout."""
+    from catopt_b200 import ops
+
+    ops.check_device_status(dev)
+
+
+# --------------------------------------------------------------------------- graphs
+def test_cuda_graph_replay_matches_eager(dev):
+    from catopt_b200.executors import B200ChunkedDecay
+
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(1, 2, 128, 32, generator=g).to(dev) for _ in range(3))
+    mod = B200ChunkedDecay(0.97, 2, 32).to(dev)
+    eager = mod(q, k, v).clone()
+    mod.capture_cuda_graph(q, k, v)
+    assert mod.is_graph_captured
+    assert torch.equal(mod(q, k, v), eager)
+    q2 = q * 0.5
+    assert torch.equal(mod(q2, k, v), mod._forward_impl(q2, k, v))
+    mod.drop_cuda_graph()
+    assert not mod.is_graph_captured
