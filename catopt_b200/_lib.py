@@ -40,6 +40,11 @@ SIGNATURES: dict[str, tuple] = {
         [C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_void_p, C.c_void_p,
          C.c_size_t, C.c_void_p],
     ),
+    "cb2_chain_fold_f32_noalloc_max_bytes": (C.c_size_t, []),
+    "cb2_chain_fold_f32_noalloc": (
+        C.c_int,
+        [C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_void_p, C.c_void_p],
+    ),
     "cb2_decayed_chunk_scratch_bytes": (
         C.c_size_t,
         [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],

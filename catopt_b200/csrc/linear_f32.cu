@@ -212,3 +212,59 @@ extern "C" int cb2_chain_fold_f32(const float* const* weights, const int* dims, 
   }
   return CB2_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the chain fold.
+//
+// Some callers cannot allocate device memory at the point where they fold a
+// weight chain: a lowering pass that runs inside a region where the caching
+// allocator is frozen (for example while another module's CUDA graph is being
+// captured on the same device), a host runtime that was handed a fixed memory
+// budget at start-up, or a plugin that only receives raw pointers and has no
+// allocator of its own.  For them the two ping-pong intermediates of the fold
+// live in a file-scope device array that every GPU loading this library holds
+// until exit (2 MiB), instead of in caller-provided scratch.
+//
+// The array's name is only a host-side handle: the device address is looked up
+// with cudaGetSymbolAddress, once per device, with that device current, on the
+// entry point's first call on that device.  Make that first call outside any
+// stream capture.  All calls share the one array, so two calls that overlap on
+// the GPU (different streams, or graphs replayed concurrently) race; calls on
+// one stream are ordered and safe.  The fold writes every intermediate element
+// before it reads it, so nothing has to be cleared between calls.
+// ---------------------------------------------------------------------------
+namespace cb2 {
+namespace {
+constexpr size_t kStaticFoldFloats = 2u * 512u * 512u;  // two 512x512 fp32 intermediates
+constexpr int kMaxDevices = 64;
+}  // namespace
+}  // namespace cb2
+
+static __device__ __align__(256) float g_cb2_fold_scratch[cb2::kStaticFoldFloats];
+static float* g_cb2_fold_scratch_addr[cb2::kMaxDevices] = {};
+
+extern "C" size_t cb2_chain_fold_f32_noalloc_max_bytes(void) {
+  return cb2::kStaticFoldFloats * sizeof(float);
+}
+
+extern "C" int cb2_chain_fold_f32_noalloc(const float* const* weights, const int* dims, int k,
+                                          float* out, void* stream) {
+  if (!weights || !dims || !out) return CB2_NULL_PTR;
+  if (k < 1) return CB2_BAD_SHAPE;
+  for (int i = 0; i <= k; ++i)
+    if (dims[i] <= 0) return CB2_BAD_SHAPE;
+  const size_t need = cb2_chain_fold_f32_scratch_bytes(dims, k);
+  if (need > cb2::kStaticFoldFloats * sizeof(float)) return CB2_SCRATCH_TOO_SMALL;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= cb2::kMaxDevices) return CB2_LAUNCH_FAIL;
+  float* scratch = g_cb2_fold_scratch_addr[dev];
+  if (!scratch) {
+    // Set-up, once per device: resolve this device's copy of the array.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_cb2_fold_scratch) != cudaSuccess || !p) return CB2_LAUNCH_FAIL;
+    scratch = static_cast<float*>(p);
+    g_cb2_fold_scratch_addr[dev] = scratch;  // idempotent: a racing thread stores the same value
+  }
+  return cb2_chain_fold_f32(weights, dims, k, out, scratch, cb2::kStaticFoldFloats * sizeof(float),
+                            stream);
+}

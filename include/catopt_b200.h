@@ -105,6 +105,22 @@ int cb2_chain_fold_f32(const float* const* weights, const int* dims, int k,
                        float* out, void* scratch, size_t scratch_bytes,
                        void* stream);
 
+/* cb2_chain_fold_f32_noalloc: the same fold for callers that cannot allocate
+ * device memory (a lowering pass running while the allocator is frozen, a host
+ * runtime with a fixed memory budget, a plugin that only sees raw pointers).
+ * It has no counterpart in the reference.  The two intermediates live in a
+ * static device array inside the library (cb2_chain_fold_f32_noalloc_max_bytes()
+ * = 2 MiB per GPU, held until exit), so the chain must satisfy
+ * cb2_chain_fold_f32_scratch_bytes(dims,k) <= that limit (e.g. any chain of
+ * Linear maps up to 512x512); larger chains return CB2_SCRATCH_TOO_SMALL.
+ * The first call on a device looks up the array's device address and should be
+ * made outside any stream capture.  Every call shares the array: calls that
+ * overlap on the GPU race, calls on one stream are safe.  Result identical to
+ * cb2_chain_fold_f32. */
+size_t cb2_chain_fold_f32_noalloc_max_bytes(void);
+int cb2_chain_fold_f32_noalloc(const float* const* weights, const int* dims, int k,
+                               float* out, void* stream);
+
 /* -------------------------------------------------------------------------
  * (b) chunked decayed attention,  o[t] = sum_{s<=t} gamma_h^(t-s) (q_t.k_s) v_s / scale.
  * Replaces `ChunkedDecayModule._forward_impl`
