@@ -92,6 +92,31 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar,
   return false;
 }
 
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Wait for kernels whose roles wait on one another: gives up after
+// `budget_ns` of wall time, or as soon as another role has raised `*abort`
+// (so one expired wait ends the whole CTA quickly instead of cascading).
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity,
+                                                    volatile int* abort,
+                                                    uint64_t budget_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 0) {
+      if (*abort) return false;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        *abort = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // ---- bulk asynchronous copies (TMA engine, untiled form) -------------------
 // global -> shared, completion counted in bytes on `bar`.  Both addresses must
 // be 16-byte aligned and `bytes` a multiple of 16.

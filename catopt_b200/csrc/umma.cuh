@@ -1,0 +1,166 @@
+// Blackwell (sm_100a) building blocks for the tensor-core kernels: tcgen05
+// MMA issue / commit, tensor-memory (TMEM) allocation and access, shared-memory
+// matrix descriptors for 128-byte-swizzled bf16 tiles, and tiled TMA loads.
+//
+// Tile convention used throughout: a [rows x 128] bf16 operand tile lives in
+// shared memory as two 16 KiB sub-tiles (columns 0-63 and 64-127), each a stack
+// of 128-byte rows with the 16-byte chunk index XORed by (row % 8) — exactly
+// what a TMA load with a {64,128} box and SWIZZLE_128B writes.  The same bytes
+// can be handed to the MMA either K-major (row = M/N index, column = K index)
+// or MN-major (row = K index, column = M/N index), which is what lets K and V
+// chunks feed both Q.K^T / P.V and K^T.V without a transposed copy.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace cb2 {
+namespace umma {
+
+constexpr uint32_t kSubTileBytes = 128 * 128;   // 128 rows x 64 bf16
+constexpr uint32_t kTileBytes = 2 * kSubTileBytes;
+
+// Byte offset of the 16-byte chunk holding elements [col, col+8) of `row` in a
+// swizzled [128 x 128] bf16 tile (col a multiple of 8).
+__host__ __device__ __forceinline__ uint32_t tile_chunk_offset(uint32_t row, uint32_t col) {
+  return (col >> 6) * kSubTileBytes + row * 128u + ((((col & 63u) >> 3) ^ (row & 7u)) << 4);
+}
+
+// ---- instruction descriptor: bf16 x bf16 -> fp32, M x N ------------------
+__host__ __device__ constexpr uint32_t instr_desc_bf16(uint32_t M, uint32_t N, bool a_mn_major,
+                                                       bool b_mn_major) {
+  return (1u << 4)                       // D format: fp32
+         | (1u << 7) | (1u << 10)        // A, B format: bf16
+         | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16)
+         | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// ---- shared-memory matrix descriptors (SWIZZLE_128B, descriptor version 1) --
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) |
+         (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// K-major operand, k-step ks (16 elements of K each) of a swizzled tile:
+// 8-row groups 1024 B apart; K advances 32 B inside the 128-byte row and moves
+// to the second sub-tile after four steps.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int ks) {
+  return smem_desc(tile_addr + (ks >> 2) * kSubTileBytes + (ks & 3) * 32u, 16u, 1024u);
+}
+// MN-major operand, k-step ks: 16 K-rows = 2048 B per step; 8-row K groups
+// 1024 B apart (stride offset); the second 64 MN elements sit in the second
+// sub-tile (leading offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int ks) {
+  return smem_desc(tile_addr + ks * 2048u, kSubTileBytes, 1024u);
+}
+
+// ---- tcgen05 ---------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate))
+      : "memory");
+}
+// Arrive on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// Whole-warp calls (.sync.aligned).
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// 32 lanes x 32 columns of 32-bit: thread t of the warp gets lane (base+t).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---- tiled TMA load (no multicast): one {64 x 128} box into a sub-tile ------
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// ---- host: tensor map for a row-major [rows x 128] bf16 matrix ---------------
+// Box {64 columns, 128 rows}, 128-byte swizzle.  Uses the driver entry point
+// through the runtime so the library does not link libcuda.
+inline int make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols) {
+  using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                          const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                          CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                          CUtensorMapFloatOOBfill);
+  static Fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !p)
+      return CB2_LAUNCH_FAIL;
+    fn = reinterpret_cast<Fn>(p);
+  }
+  const cuuint64_t gdim[2] = {cols, rows};
+  const cuuint64_t gstride[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim,
+                        gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? CB2_OK : CB2_LAUNCH_FAIL;
+}
+
+}  // namespace umma
+}  // namespace cb2
