@@ -390,8 +390,55 @@ def run_ours(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_profile_case(args) -> None:
+    """A small, L2-exceeding case of ONE kernel, a few launches, for ncu captures."""
+    from catopt_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    n = max(args.steps, 1)
+    if args.profile_case == "decayed":      # 148 heads x T=2048: 310 MB of q,k,v,o
+        B, H, T, d = 2, 74, 2048, 128
+        q, k, v = (_randn_bf16((B * H, T * d), gen, 1 / math.sqrt(d)).view(B, H, T, d) for _ in range(3))
+        gamma = c4_gamma(H).to(dev)
+        o = torch.empty_like(v)
+        fn = lambda: ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0, out=o)  # noqa: E731
+    elif args.profile_case == "scan":       # config 3 at T=1024: 302 MB
+        B, T, D, N = 8, 1024, 1024, 16
+        x = _randn_bf16((B, T * D), gen).view(B, T, D)
+        a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, N, device=dev, generator=gen)).bfloat16()
+        b = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
+        c = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
+        y = torch.empty_like(x)
+        fn = lambda: ops.diag_scan_fwd(a, x, b, c, None, out=y)  # noqa: E731
+    elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
+        ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
+        outp = ref.clone()
+        res = torch.empty(13, 4, device=dev)
+        fn = lambda: ops.verify_reduce(ref, outp, 13, result=res)  # noqa: E731
+    else:                                   # folded chain, R=65536 rows: 269 MB
+        x = torch.randn(65536, 512, device=dev, generator=gen)
+        w = torch.randn(512, 512, device=dev, generator=gen) / math.sqrt(512)
+        y = torch.empty(65536, 512, device=dev)
+        fn = lambda: ops.linear_f32(x, w, out=y)  # noqa: E731
+    for _ in range(n):
+        fn()
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": args.profile_case, "launch_ms": e0.elapsed_time(e1) / n}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile-case", default=None, choices=["decayed", "scan", "verify", "linear"],
+                    help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -399,6 +446,9 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

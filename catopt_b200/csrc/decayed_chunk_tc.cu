@@ -7,7 +7,7 @@
 //   WG    P  = bf16( S . tril(g^(r-c)) )  -> smem ;  K_i <- K_i . g^(C-1-r) in place
 //   MMA2  O1 = P V_i                                       (TMEM cols 128..255)
 //   MMA3  O2 = Q_i Sb_i        (Sb_i = bf16 copy of the state, i > 0)   (256..383)
-//   WG    o_i = (O1 + g^(r+1) O2) / scale  -> global
+//   WG    o_i = (O1 + g^(r+1) O2) / scale  -> staged in the P tile, TMA store
 //   MMA4  St = [g^C St] + Kw_i^T V_i                       (TMEM cols 384..511)
 //   WG    Sb_{i+1} = bf16(St) -> smem ;  St <- g^C St  (ready for the next MMA4)
 // which is the state-carry recurrence the reference spells in
@@ -16,7 +16,8 @@
 // appear.
 //
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM owner),
-// warps 2..5 = the 128-thread compute group (thread = one TMEM lane = one row).
+// warps 2..9 = the 256-thread compute group (thread = one TMEM lane = one row,
+// half of the columns).
 // Operand tiles (32 KiB each, K_i / Q_i / V_i in that order) stream through a
 // 5-slot shared-memory ring with full/empty mbarriers; a slot is released by
 // the tcgen05.commit of the last MMA that reads it, so up to two tiles of the
@@ -27,9 +28,22 @@
 namespace cb2 {
 namespace {
 
+// Optional phase timeline of CTA 0 (compute-group thread 0), for tuning builds
+// only: compile with -DCB2_TIMELINE and read g_timeline back from the host.
+#ifdef CB2_TIMELINE
+__device__ long long g_timeline[64][8];
+#define CB2_TL(i, k)                                                   \
+  do {                                                                 \
+    if (blockIdx.x == 0 && threadIdx.x == 64 && (i) < 64) g_timeline[i][k] = clock64(); \
+  } while (0)
+#else
+#define CB2_TL(i, k) do {} while (0)
+#endif
+
 constexpr int kC = 128;                 // chunk rows = dk = dv
 constexpr int kSlots = 5;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;                 // 2 single-lane role warps + 8 compute warps
+constexpr int kComputeThreads = 256;
 constexpr uint32_t kTile = umma::kTileBytes;      // 32 KiB
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffRing = 0;
@@ -37,7 +51,7 @@ constexpr uint32_t kOffP = kSlots * kTile;
 constexpr uint32_t kOffSb = kOffP + kTile;
 constexpr uint32_t kOffPow = kOffSb + kTile;                 // float[kC + 1]
 constexpr uint32_t kOffBars = kOffPow + 528;                 // 8-byte aligned
-constexpr int kNumBars = 2 * kSlots + 7;
+constexpr int kNumBars = 2 * kSlots + 8;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;       // tmem base, abort flag
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slack
 
@@ -48,17 +62,18 @@ struct Bars {
   uint64_t* full;      // [kSlots] TMA -> MMA
   uint64_t* empty;     // [kSlots] MMA -> TMA
   uint64_t* s_ready;   // MMA1 done            (MMA -> WG)
-  uint64_t* p_ready;   // P written            (WG -> MMA, 128 arrivals)
-  uint64_t* kw_ready;  // K scaled in place    (WG -> MMA, 128)
+  uint64_t* p_ready;   // P written            (WG -> MMA, 256 arrivals)
+  uint64_t* kw_ready;  // K scaled in place    (WG -> MMA, 256)
   uint64_t* o_ready;   // MMA2+MMA3 done       (MMA -> WG)
-  uint64_t* o_free;    // O1/O2 read out       (WG -> MMA, 128)
+  uint64_t* o_free;    // O1/O2 read out       (WG -> MMA, 256)
   uint64_t* st_ready;  // MMA4 done            (MMA -> WG)
-  uint64_t* sb_ready;  // Sb written, St scaled (WG -> MMA, 128)
+  uint64_t* sb_ready;  // Sb written, St scaled (WG -> MMA, 256)
+  uint64_t* wg_sync;   // barrier among the 256 compute threads
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
 decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ o,
+                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const float* __restrict__ gamma, int H, int T, float inv_scale, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem =
@@ -68,7 +83,8 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
   Bars B{bars, bars + kSlots, bars + 2 * kSlots, bars + 2 * kSlots + 1, bars + 2 * kSlots + 2,
-         bars + 2 * kSlots + 3, bars + 2 * kSlots + 4, bars + 2 * kSlots + 5, bars + 2 * kSlots + 6};
+         bars + 2 * kSlots + 3, bars + 2 * kSlots + 4, bars + 2 * kSlots + 5, bars + 2 * kSlots + 6,
+         bars + 2 * kSlots + 7};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x;
@@ -84,12 +100,13 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_init(&B.empty[s], 1);
     }
     mbar_init(B.s_ready, 1);
-    mbar_init(B.p_ready, 128);
-    mbar_init(B.kw_ready, 128);
+    mbar_init(B.p_ready, kComputeThreads);
+    mbar_init(B.kw_ready, kComputeThreads);
     mbar_init(B.o_ready, 1);
-    mbar_init(B.o_free, 128);
+    mbar_init(B.o_free, kComputeThreads);
     mbar_init(B.st_ready, 1);
-    mbar_init(B.sb_ready, 128);
+    mbar_init(B.sb_ready, kComputeThreads);
+    mbar_init(B.wg_sync, kComputeThreads);
     *s_abort = 0;
     mbar_fence_init();
   }
@@ -97,7 +114,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     __syncwarp();
     umma::tmem_alloc(s_tmem, 512);
   }
-  if (tid >= 64) {  // powers of gamma for this head: g^0 .. g^128
+  if (tid >= 64 && tid < 192) {  // powers of gamma for this head: g^0 .. g^128
     const int j = tid - 64;
     s_pow[j] = powf(g, float(j));
     if (j == 0) s_pow[kC] = powf(g, float(kC));
@@ -113,6 +130,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       umma::tma_prefetch_desc(&map_q);
       umma::tma_prefetch_desc(&map_k);
       umma::tma_prefetch_desc(&map_v);
+      umma::tma_prefetch_desc(&map_o);
       const int ntiles = 3 * nchunk;
       for (int t = 0; t < ntiles; ++t) {
         const int slot = t % kSlots, use = t / kSlots;
@@ -181,7 +199,11 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ compute group
-    const int q4 = warp & 3;                 // TMEM lane quarter this warp may touch
+    // 256 threads: thread = (row r, column half).  A warp may only touch the
+    // TMEM lane quarter (warp % 4), so the two warps that share a quarter split
+    // the 128 columns between them.
+    const int q4 = warp & 3;                 // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;        // 0: columns 0..63, 1: columns 64..127
     const int r = q4 * 32 + lane;            // row of the chunk / lane of TMEM
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
     const float g_row = s_pow[r + 1];        // g^(r+1)
@@ -189,114 +211,153 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const float g_chunk = s_pow[kC];         // g^C
     unsigned char* p_tile = smem + kOffP;
     unsigned char* sb_tile = smem + kOffSb;
-    uint32_t v[32];
+    uint32_t va[32], vb[32];
+    uint32_t wg_phase = 0;
+    // write 32 packed columns [col0, col0+32) of row r into a swizzled tile
+    auto store_block = [&](unsigned char* tile, int col0, const uint32_t (&w)[16]) {
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8)
+        *reinterpret_cast<uint4*>(tile + umma::tile_chunk_offset(r, col0 + c8 * 8)) =
+            make_uint4(w[4 * c8], w[4 * c8 + 1], w[4 * c8 + 2], w[4 * c8 + 3]);
+    };
     for (int i = 0; i < nchunk; ++i) {
       const uint32_t ph = i & 1;
+      CB2_TL(i, 0);
       bool ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
-      // (a) P = bf16(S . decay), written K-major into the P tile
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        if (cb <= q4) {
-          umma::tmem_ld32(lane_base + kColS + cb * 32, v);
-          umma::tmem_wait_ld();
-        }
+      CB2_TL(i, 1);
+      // The P tile doubles as the staging buffer of the previous chunk's output:
+      // its TMA store must have finished reading before P is rewritten.
+      if (i > 0) {
+        if (tid == 64) bulk_wait_read<0>();
+        mbar_arrive(B.wg_sync);
+        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+        wg_phase ^= 1;
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      // (a) P = bf16(S . decay), written K-major into the P tile.  Branch-free:
+      // the power is always loaded (clamped index) and masked by a select.
+      {
+        const int cb0 = half * 2, cb1 = cb0 + 1;
+        if (cb0 <= q4) umma::tmem_ld32(lane_base + kColS + cb0 * 32, va);  // warp-uniform:
+        if (cb1 <= q4) umma::tmem_ld32(lane_base + kColS + cb1 * 32, vb);  // blocks right of the
+        if (cb0 <= q4) umma::tmem_wait_ld();                               // diagonal are zero
+        auto decay_block = [&](int cb, const uint32_t (&v)[32]) {
+          uint32_t w[16];
+          if (cb <= q4) {
+            const int e0 = r - cb * 32;  // exponent of the block's first column
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int c = cb * 32 + c8 * 8 + 2 * j;
-            float lo = 0.f, hi = 0.f;
-            if (cb <= q4) {
-              if (c <= r) lo = __uint_as_float(v[c8 * 8 + 2 * j]) * s_pow[r - c];
-              if (c + 1 <= r) hi = __uint_as_float(v[c8 * 8 + 2 * j + 1]) * s_pow[r - c - 1];
+            for (int j = 0; j < 32; j += 2) {
+              const int ea = e0 - j, eb = e0 - j - 1;
+              const float fa = s_pow[max(ea, 0)], fb = s_pow[max(eb, 0)];
+              const float lo = ea >= 0 ? __uint_as_float(v[j]) * fa : 0.f;
+              const float hi = eb >= 0 ? __uint_as_float(v[j + 1]) * fb : 0.f;
+              w[j >> 1] = pack_bf16x2(lo, hi);
             }
-            w[j] = pack_bf16x2(lo, hi);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[j] = 0u;
           }
-          *reinterpret_cast<uint4*>(p_tile + umma::tile_chunk_offset(r, cb * 32 + c8 * 8)) =
-              make_uint4(w[0], w[1], w[2], w[3]);
-        }
+          store_block(p_tile, cb * 32, w);
+        };
+        decay_block(cb0, va);
+        decay_block(cb1, vb);
       }
       umma::fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(B.p_ready);
-      // (b) K_i <- K_i . g^(C-1-r), in place (MMA1 has finished reading it)
+      CB2_TL(i, 2);
+      // (b) K_i <- K_i . g^(C-1-r), in place (MMA1 has finished reading it);
+      // this thread owns the 8 chunks of row r that lie in its column half.
       {
         unsigned char* k_tile = smem + kOffRing + ((3 * i) % kSlots) * kTile;
+        uint4 x[8];
 #pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-          const int col = ((jj & 7) ^ (r & 7)) * 8 + (jj >> 3) * 64;   // conflict-free chunk order
-          uint4* pch = reinterpret_cast<uint4*>(k_tile + umma::tile_chunk_offset(r, col));
-          uint4 x = *pch;
-          x.x = pack_bf16x2(bf16lo_to_f32(x.x) * g_col, bf16hi_to_f32(x.x) * g_col);
-          x.y = pack_bf16x2(bf16lo_to_f32(x.y) * g_col, bf16hi_to_f32(x.y) * g_col);
-          x.z = pack_bf16x2(bf16lo_to_f32(x.z) * g_col, bf16hi_to_f32(x.z) * g_col);
-          x.w = pack_bf16x2(bf16lo_to_f32(x.w) * g_col, bf16hi_to_f32(x.w) * g_col);
-          *pch = x;
+        for (int j = 0; j < 8; ++j)
+          x[j] = *reinterpret_cast<const uint4*>(k_tile + umma::tile_chunk_offset(r, half * 64 + j * 8));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          x[j].x = pack_bf16x2(bf16lo_to_f32(x[j].x) * g_col, bf16hi_to_f32(x[j].x) * g_col);
+          x[j].y = pack_bf16x2(bf16lo_to_f32(x[j].y) * g_col, bf16hi_to_f32(x[j].y) * g_col);
+          x[j].z = pack_bf16x2(bf16lo_to_f32(x[j].z) * g_col, bf16hi_to_f32(x[j].z) * g_col);
+          x[j].w = pack_bf16x2(bf16lo_to_f32(x[j].w) * g_col, bf16hi_to_f32(x[j].w) * g_col);
         }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(k_tile + umma::tile_chunk_offset(r, half * 64 + j * 8)) = x[j];
       }
       fence_proxy_async_smem();
       mbar_arrive(B.kw_ready);
-      // (c) o_i = (O1 + g^(r+1) O2) / scale
+      CB2_TL(i, 3);
+      // (c) o_i = (O1 + g^(r+1) O2) / scale, staged in the (now free) P tile in
+      // the swizzled layout the TMA store expects
       ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
-      {
-        __nv_bfloat16* orow = o + (size_t(bh) * T + size_t(i) * kC + r) * kC;
-        uint32_t v2[32];
+      CB2_TL(i, 4);
 #pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          umma::tmem_ld32(lane_base + kColO1 + cb * 32, v);
-          if (i > 0) umma::tmem_ld32(lane_base + kColO2 + cb * 32, v2);
-          umma::tmem_wait_ld();
+      for (int cbi = 0; cbi < 2; ++cbi) {
+        const int cb = half * 2 + cbi;
+        umma::tmem_ld32(lane_base + kColO1 + cb * 32, va);
+        if (i > 0) umma::tmem_ld32(lane_base + kColO2 + cb * 32, vb);
+        umma::tmem_wait_ld();
+        uint32_t w[16];
 #pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float lo = __uint_as_float(v[c8 * 8 + 2 * j]), hi = __uint_as_float(v[c8 * 8 + 2 * j + 1]);
-              if (i > 0) {
-                lo = fmaf(g_row, __uint_as_float(v2[c8 * 8 + 2 * j]), lo);
-                hi = fmaf(g_row, __uint_as_float(v2[c8 * 8 + 2 * j + 1]), hi);
-              }
-              w[j] = pack_bf16x2(lo * inv_scale, hi * inv_scale);
-            }
-            *reinterpret_cast<uint4*>(orow + cb * 32 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int j = 0; j < 32; j += 2) {
+          float lo = __uint_as_float(va[j]), hi = __uint_as_float(va[j + 1]);
+          if (i > 0) {
+            lo = fmaf(g_row, __uint_as_float(vb[j]), lo);
+            hi = fmaf(g_row, __uint_as_float(vb[j + 1]), hi);
           }
+          w[j >> 1] = pack_bf16x2(lo * inv_scale, hi * inv_scale);
         }
+        store_block(p_tile, cb * 32, w);
       }
       umma::fence_before_sync();
       mbar_arrive(B.o_free);
+      fence_proxy_async_smem();
+      mbar_arrive(B.wg_sync);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      wg_phase ^= 1;
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (tid == 64) {  // whole tile written: two {64 x 128} boxes go out asynchronously
+        const int row = bh * T + i * kC;
+        umma::tma_store_2d(&map_o, 0, row, p_tile);
+        umma::tma_store_2d(&map_o, 64, row, p_tile + umma::kSubTileBytes);
+        bulk_commit();
+      }
+      CB2_TL(i, 5);
       // (d) Sb_{i+1} = bf16(St);  St <- g^C St
       if (i + 1 < nchunk) {
         ok = mbar_wait_abortable(B.st_ready, ph, s_abort);
         if (!__all_sync(0xffffffffu, ok)) break;
         umma::fence_after_sync();
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          umma::tmem_ld32(lane_base + kColSt + cb * 32, v);
-          umma::tmem_wait_ld();
+        CB2_TL(i, 6);
+        const int cb0 = half * 2;
+        umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
+        umma::tmem_ld32(lane_base + kColSt + cb0 * 32 + 32, vb);
+        umma::tmem_wait_ld();
+        auto state_block = [&](int cb, uint32_t (&v)[32]) {
+          uint32_t w[16];
 #pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              w[j] = pack_bf16x2(__uint_as_float(v[c8 * 8 + 2 * j]), __uint_as_float(v[c8 * 8 + 2 * j + 1]));
-            *reinterpret_cast<uint4*>(sb_tile + umma::tile_chunk_offset(r, cb * 32 + c8 * 8)) =
-                make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          for (int j = 0; j < 32; j += 2)
+            w[j >> 1] = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+          store_block(sb_tile, cb * 32, w);
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g_chunk);
           umma::tmem_st32(lane_base + kColSt + cb * 32, v);
-        }
+        };
+        state_block(cb0, va);
+        state_block(cb0 + 1, vb);
         umma::tmem_wait_st();
         umma::fence_before_sync();
         fence_proxy_async_smem();
         mbar_arrive(B.sb_ready);
+        CB2_TL(i, 7);
       }
     }
+    if (tid == 64) bulk_wait_all<0>();  // the staged output has left shared memory
   }
 
   // Teardown: everyone meets, the last MMA4 is drained, TMEM goes back.
@@ -327,17 +388,18 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
                    int H, int T, int dk, int dv, int C, float scale, int* dev_status, cudaStream_t st) {
   (void)dk; (void)dv; (void)C;
   const uint64_t rows = uint64_t(B) * H * T;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   int rc = umma::make_tile_map(&mq, q, rows, kC);
   if (rc == CB2_OK) rc = umma::make_tile_map(&mk, k, rows, kC);
   if (rc == CB2_OK) rc = umma::make_tile_map(&mv, v, rows, kC);
+  if (rc == CB2_OK) rc = umma::make_tile_map(&mo, o, rows, kC);
   if (rc != CB2_OK) return rc;
   // per device, so set on every call (cheap) rather than cached per process
   if (cudaFuncSetAttribute(decayed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
-  decayed_tc_kernel<<<B * H, kThreads, kSmemBytes, st>>>(mq, mk, mv, static_cast<__nv_bfloat16*>(o),
-                                                        gamma, H, T, 1.0f / scale, dev_status);
+  decayed_tc_kernel<<<B * H, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, 1.0f / scale,
+                                                        dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

@@ -130,6 +130,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+// shared -> global store of one {64 x 128} box (tracked by the thread's bulk group)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int x, int y,
+                                             const void* smem_src) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap),
+      "r"(x), "r"(y), "r"(smem_u32(smem_src))
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
