@@ -4,10 +4,10 @@
 //
 // Per chunk i (C = 128 rows, g = gamma of the head):
 //   MMA1  S  = Q_i K_i^T                                  (TMEM cols   0..127)
-//   WG    P  = bf16( S . tril(g^(r-c)) )  -> smem ;  K_i <- K_i . g^(C-1-r) in place
-//   MMA2  O1 = P V_i                                       (TMEM cols 128..255)
+//   WG    P  = bf16( S . tril(g^(r-c)) )  -> TMEM (over S) ;  K_i <- K_i . g^(C-1-r) in place
+//   MMA2  O1 = P V_i        (A operand read from TMEM)      (TMEM cols 128..255)
 //   MMA3  O2 = Q_i Sb_i        (Sb_i = bf16 copy of the state, i > 0)   (256..383)
-//   WG    o_i = (O1 + g^(r+1) O2) / scale  -> staged in the P tile, TMA store
+//   WG    o_i = (O1 + g^(r+1) O2) / scale  -> staged in shared memory, TMA store
 //   MMA4  St = [g^C St] + Kw_i^T V_i                       (TMEM cols 384..511)
 //   WG    Sb_{i+1} = bf16(St) -> smem ;  St <- g^C St  (ready for the next MMA4)
 // which is the state-carry recurrence the reference spells in
@@ -47,8 +47,8 @@ constexpr int kComputeThreads = 256;
 constexpr uint32_t kTile = umma::kTileBytes;      // 32 KiB
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffRing = 0;
-constexpr uint32_t kOffP = kSlots * kTile;
-constexpr uint32_t kOffSb = kOffP + kTile;
+constexpr uint32_t kOffO = kSlots * kTile;          // output staging tile
+constexpr uint32_t kOffSb = kOffO + kTile;
 constexpr uint32_t kOffPow = kOffSb + kTile;                 // float[kC + 1]
 constexpr uint32_t kOffBars = kOffPow + 528;                 // 8-byte aligned
 constexpr int kNumBars = 2 * kSlots + 8;
@@ -57,6 +57,10 @@ constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slac
 
 // TMEM columns
 constexpr uint32_t kColS = 0, kColO1 = 128, kColO2 = 256, kColSt = 384;
+// P (bf16, two values per 32-bit column) overwrites S in place: the thread that
+// read S columns [64h, 64h+64) writes the packed P of those columns into
+// [64h, 64h+32), i.e. only over columns it has already loaded itself.
+__host__ __device__ constexpr uint32_t p_col(uint32_t c) { return (c & 64u) + ((c & 63u) >> 1); }
 
 struct Bars {
   uint64_t* full;      // [kSlots] TMA -> MMA
@@ -91,7 +95,6 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int nchunk = T / kC;
   const float g = gamma[bh % H];
   const uint32_t ring_addr = smem_u32(smem + kOffRing);
-  const uint32_t p_addr = smem_u32(smem + kOffP);
   const uint32_t sb_addr = smem_u32(smem + kOffSb);
 
   if (tid == 0) {
@@ -172,8 +175,8 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma::mma_bf16(tmem + kColO1, umma::desc_kmajor(p_addr, ks), umma::desc_mnmajor(v_addr, ks),
-                         idesc_kn, ks > 0);
+          umma::mma_bf16_ts(tmem + kColO1, tmem + kColS + p_col(ks * 16),
+                            umma::desc_mnmajor(v_addr, ks), idesc_kn, ks > 0);
         // MMA3: O2 = Q Sb   (the state is zero before the first chunk)
         if (i > 0) {
           if (!mbar_wait_abortable(B.sb_ready, (i - 1) & 1, s_abort)) break;
@@ -209,7 +212,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const float g_row = s_pow[r + 1];        // g^(r+1)
     const float g_col = s_pow[kC - 1 - r];   // g^(C-1-r)
     const float g_chunk = s_pow[kC];         // g^C
-    unsigned char* p_tile = smem + kOffP;
+    unsigned char* o_tile = smem + kOffO;
     unsigned char* sb_tile = smem + kOffSb;
     uint32_t va[32], vb[32];
     uint32_t wg_phase = 0;
@@ -227,17 +230,8 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       CB2_TL(i, 1);
-      // The P tile doubles as the staging buffer of the previous chunk's output:
-      // its TMA store must have finished reading before P is rewritten.
-      if (i > 0) {
-        if (tid == 64) bulk_wait_read<0>();
-        mbar_arrive(B.wg_sync);
-        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
-        wg_phase ^= 1;
-        if (!__all_sync(0xffffffffu, ok)) break;
-      }
-      // (a) P = bf16(S . decay), written K-major into the P tile.  Branch-free:
-      // the power is always loaded (clamped index) and masked by a select.
+      // (a) P = bf16(S . decay), packed into TMEM over S.  Branch-free: the power
+      // is always loaded (clamped index) and masked by a select.
       {
         const int cb0 = half * 2, cb1 = cb0 + 1;
         if (cb0 <= q4) umma::tmem_ld32(lane_base + kColS + cb0 * 32, va);  // warp-uniform:
@@ -259,13 +253,18 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 16; ++j) w[j] = 0u;
           }
-          store_block(p_tile, cb * 32, w);
+          umma::tmem_st16(lane_base + kColS + p_col(cb * 32), w);
         };
         decay_block(cb0, va);
         decay_block(cb1, vb);
+        umma::tmem_wait_st();
       }
+      // The staging tile of the previous chunk's output must have been read by
+      // its TMA store before (c) rewrites it; making the issuing thread wait
+      // here, before its p_ready arrival, orders that ahead of MMA2 and hence
+      // ahead of every thread's o_ready wait.
+      if (tid == 64) bulk_wait_read<0>();
       umma::fence_before_sync();
-      fence_proxy_async_smem();
       mbar_arrive(B.p_ready);
       CB2_TL(i, 2);
       // (b) K_i <- K_i . g^(C-1-r), in place (MMA1 has finished reading it);
@@ -290,8 +289,8 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       fence_proxy_async_smem();
       mbar_arrive(B.kw_ready);
       CB2_TL(i, 3);
-      // (c) o_i = (O1 + g^(r+1) O2) / scale, staged in the (now free) P tile in
-      // the swizzled layout the TMA store expects
+      // (c) o_i = (O1 + g^(r+1) O2) / scale, staged in shared memory in the
+      // swizzled layout the TMA store expects
       ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
@@ -312,7 +311,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           }
           w[j >> 1] = pack_bf16x2(lo * inv_scale, hi * inv_scale);
         }
-        store_block(p_tile, cb * 32, w);
+        store_block(o_tile, cb * 32, w);
       }
       umma::fence_before_sync();
       mbar_arrive(B.o_free);
@@ -323,8 +322,8 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (!__all_sync(0xffffffffu, ok)) break;
       if (tid == 64) {  // whole tile written: two {64 x 128} boxes go out asynchronously
         const int row = bh * T + i * kC;
-        umma::tma_store_2d(&map_o, 0, row, p_tile);
-        umma::tma_store_2d(&map_o, 64, row, p_tile + umma::kSubTileBytes);
+        umma::tma_store_2d(&map_o, 0, row, o_tile);
+        umma::tma_store_2d(&map_o, 64, row, o_tile + umma::kSubTileBytes);
         bulk_commit();
       }
       CB2_TL(i, 5);
