@@ -16,7 +16,7 @@
 // tracked by one mbarrier per stage, so kStages-1 tiles per CTA are always in
 // flight while the serial recurrence runs on the resident one.  y is staged in
 // shared memory and written with 16-byte stores.
-#include "common.cuh"
+#include "umma.cuh"
 
 namespace cb2 {
 namespace {
@@ -213,6 +213,186 @@ diag_scan_kernel(const unsigned char* __restrict__ a, const unsigned char* __res
   }
 }
 
+// ---------------------------------------------------------------------------
+// Fast path (D a multiple of 32, N >= 4): same mapping, but
+//  * tiles come in through tiled TMA (3-D tensor maps {D*N | D, T, B}; a tile of
+//    16 time steps is kNumBox + 1 copies instead of 32 row copies, and the T
+//    axis is clipped per batch entry by the map itself),
+//  * a thread owns kNpt = 4 n (four lanes per channel), which doubles the warps
+//    per SM for latency hiding, and the arithmetic runs on two-wide fp32 FMAs,
+//  * each group of four steps loads all its operands before it stores anything,
+//    so the loads of consecutive steps overlap,
+//  * y goes out with one TMA store per tile from a double-buffered staging area.
+// ---------------------------------------------------------------------------
+template <int DTYPE, int N, int NPT>
+struct FastCfg {
+  static constexpr int kEsz = Elem<DTYPE>::kSize;
+  static constexpr int kNpt = NPT;
+  static constexpr int kLpc = N / NPT;
+  static constexpr int kCh = 32;
+  static constexpr int kThreads = kCh * kLpc;
+  static constexpr int kRows = 16;
+  static constexpr int kStages = 4;
+  static constexpr int kRowElems = kCh * N;
+  static constexpr int kBoxCols = kRowElems < 256 ? kRowElems : 256;
+  static constexpr int kNumBox = kRowElems / kBoxCols;
+  static constexpr int kABytes = kRows * kRowElems * kEsz;
+  static constexpr int kXBytes = kRows * kCh * kEsz;
+  static constexpr int kStageBytes = kABytes + kXBytes;
+  static constexpr int kSmem = kStages * kStageBytes + 2 * kXBytes + kStages * 8 + 128;
+};
+
+template <int DTYPE, int N, int NPT>
+__global__ void __launch_bounds__(FastCfg<DTYPE, N, NPT>::kThreads)
+diag_scan_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_x,
+                     const __grid_constant__ CUtensorMap map_y, const void* __restrict__ bvec,
+                     const void* __restrict__ cvec, const float* __restrict__ h0,
+                     float* __restrict__ hT, int T, int D, int* dev_status) {
+  using C = FastCfg<DTYPE, N, NPT>;
+  using E = Elem<DTYPE>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* s_stage = smem;
+  unsigned char* s_y = smem + C::kStages * C::kStageBytes;
+  uint64_t* s_full = reinterpret_cast<uint64_t*>(s_y + 2 * C::kXBytes);
+
+  const int tid = threadIdx.x;
+  const int blocks_per_b = D / C::kCh;
+  const int b = blockIdx.x / blocks_per_b;
+  const int d0 = (blockIdx.x % blocks_per_b) * C::kCh;
+  const int ch = tid / C::kLpc, sub = tid % C::kLpc;
+  const int d = d0 + ch;
+  const int ntiles = (T + C::kRows - 1) / C::kRows;
+  // this thread's NPT elements inside a stage's `a` tile (box-major layout)
+  const int e = ch * N + sub * NPT;
+  const int a_off = (e / C::kBoxCols) * (C::kRows * C::kBoxCols * C::kEsz) + (e % C::kBoxCols) * C::kEsz;
+  constexpr int kAPitch = C::kBoxCols * C::kEsz;
+  constexpr int kXPitch = C::kCh * C::kEsz;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) mbar_init(&s_full[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  auto issue_tile = [&](int tile) {  // thread 0 only
+    const int s = tile % C::kStages;
+    unsigned char* sa = s_stage + s * C::kStageBytes;
+    mbar_arrive_expect_tx(&s_full[s], C::kStageBytes);
+#pragma unroll
+    for (int bx = 0; bx < C::kNumBox; ++bx)
+      umma::tma_load_3d(sa + bx * (C::kRows * C::kBoxCols * C::kEsz), &map_a,
+                        d0 * N + bx * C::kBoxCols, tile * C::kRows, b, &s_full[s]);
+    umma::tma_load_3d(sa + C::kABytes, &map_x, d0, tile * C::kRows, b, &s_full[s]);
+  };
+  if (tid == 0) {
+    umma::tma_prefetch_desc(&map_a);
+    umma::tma_prefetch_desc(&map_x);
+    umma::tma_prefetch_desc(&map_y);
+    for (int i = 0; i < C::kStages && i < ntiles; ++i) issue_tile(i);
+  }
+
+  constexpr int kPairs = NPT / 2;
+  uint64_t h2[kPairs], b2[kPairs], c2[kPairs];
+#pragma unroll
+  for (int p = 0; p < kPairs; ++p) {
+    const int n = sub * NPT + 2 * p;
+    b2[p] = umma::f2_pack(E::ld(bvec, d * N + n), E::ld(bvec, d * N + n + 1));
+    c2[p] = umma::f2_pack(E::ld(cvec, d * N + n), E::ld(cvec, d * N + n + 1));
+    const size_t hi = (size_t(b) * D + d) * N + n;
+    h2[p] = h0 ? umma::f2_pack(h0[hi], h0[hi + 1]) : umma::f2_pack(0.f, 0.f);
+  }
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int s = tile % C::kStages;
+    const int t0 = tile * C::kRows;
+    const int rows = min(C::kRows, T - t0);
+    const bool ok = mbar_wait_bounded(&s_full[s], (tile / C::kStages) & 1);
+    const unsigned char* sa = s_stage + s * C::kStageBytes + a_off;
+    const unsigned char* sx = s_stage + s * C::kStageBytes + C::kABytes + ch * C::kEsz;
+    unsigned char* sy = s_y + (tile & 1) * C::kXBytes;
+    if (ok) {
+#pragma unroll
+      for (int r0 = 0; r0 < C::kRows; r0 += 4) {
+        if (r0 < rows) {  // uniform over the CTA; rows past T are never applied
+          float av[4][NPT], xv[4], yv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            load_row<DTYPE, NPT>(sa + (r0 + q) * kAPitch, av[q]);
+            xv[q] = E::ld(sx + (r0 + q) * kXPitch, 0);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (r0 + q < rows) {
+              const uint64_t x2 = umma::f2_pack(xv[q], xv[q]);
+              uint64_t acc = umma::f2_pack(0.f, 0.f);
+#pragma unroll
+              for (int p = 0; p < kPairs; ++p) {
+                const uint64_t a2 = umma::f2_pack(av[q][2 * p], av[q][2 * p + 1]);
+                h2[p] = umma::f2_fma(a2, h2[p], umma::f2_mul(b2[p], x2));
+                acc = umma::f2_fma(c2[p], h2[p], acc);
+              }
+              float lo, hi;
+              umma::f2_unpack(acc, lo, hi);
+              yv[q] = lo + hi;
+            } else {
+              yv[q] = 0.f;
+            }
+          }
+#pragma unroll
+          for (int off = C::kLpc >> 1; off > 0; off >>= 1) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) yv[q] += __shfl_xor_sync(0xffffffffu, yv[q], off);
+          }
+          if (sub == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) E::st(sy + (r0 + q) * kXPitch, ch, yv[q]);
+          }
+        }
+      }
+    }
+    fence_proxy_async_smem();            // y rows -> visible to the TMA store
+    if (tid == 0) bulk_wait_read<0>();   // the previous tile's store has left the other y buffer
+    if (__syncthreads_or(!ok)) {
+      if (tid == 0 && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+      return;
+    }
+    if (tid == 0) {
+      if (tile + C::kStages < ntiles) issue_tile(tile + C::kStages);
+      umma::tma_store_3d(&map_y, d0, t0, b, sy);   // rows past T are clipped by the map
+      bulk_commit();
+    }
+  }
+  if (tid == 0) bulk_wait_all<0>();
+  if (hT) {
+#pragma unroll
+    for (int p = 0; p < kPairs; ++p) {
+      float lo, hi;
+      umma::f2_unpack(h2[p], lo, hi);
+      const size_t hi_idx = (size_t(b) * D + d) * N + sub * NPT + 2 * p;
+      hT[hi_idx] = lo;
+      hT[hi_idx + 1] = hi;
+    }
+  }
+}
+
+template <int DTYPE, int N, int NPT>
+int launch_scan_tma(const void* a, const void* x, const void* b, const void* c, const float* h0,
+                    void* y, float* hT, int B, int T, int D, int* dev_status, cudaStream_t st) {
+  using C = FastCfg<DTYPE, N, NPT>;
+  CUtensorMap ma, mx, my;
+  const bool bf = DTYPE == CB2_BF16;
+  int rc = umma::make_map_3d(&ma, a, bf, uint64_t(D) * N, T, B, C::kBoxCols, C::kRows);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mx, x, bf, D, T, B, C::kCh, C::kRows);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&my, y, bf, D, T, B, C::kCh, C::kRows);
+  if (rc != CB2_OK) return rc;
+  auto kern = diag_scan_tma_kernel<DTYPE, N, NPT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+    return CB2_LAUNCH_FAIL;
+  kern<<<B * (D / C::kCh), C::kThreads, C::kSmem, st>>>(ma, mx, my, b, c, h0, hT, T, D, dev_status);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
 // `a` shared over n ([B,T,D]): one thread per (b, channel) keeps all N states.
 template <int DTYPE, int N>
 __global__ void __launch_bounds__(128)
@@ -263,6 +443,9 @@ int launch_scan(const void* a, const void* x, const void* b, const void* c, cons
     return CB2_OK;
   }
   if ((size_t(D) * N * C::kEsz) % 16 || (size_t(D) * C::kEsz) % 16) return CB2_BAD_SHAPE;
+  if constexpr (N >= 4) {
+    if (D % 32 == 0) return launch_scan_tma<DTYPE, N, 4>(a, x, b, c, h0, y, hT, B, T, D, dev_status, st);
+  }
   auto kern = diag_scan_kernel<DTYPE, N>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) !=
       cudaSuccess)

@@ -23,7 +23,7 @@ from ._lib import B200Error
 _REL_FLOOR = 1e-8
 
 __all__ = ["VerifyReport", "rel_diff", "verify_equiv", "verify_module", "verify_batched",
-           "reports_from_result"]
+           "reports_from_result", "merge_across_ranks"]
 
 
 @dataclass(frozen=True)
@@ -139,9 +139,19 @@ def verify_batched(ref: torch.Tensor, out: torch.Tensor, n_checks: int, *, rtol:
     """
     if ref.shape != out.shape or ref.dtype != out.dtype or ref.shape[0] != n_checks:
         raise B200Error("verify_batched needs equal shapes [n_checks, ...] and dtypes")
-    res = ops.verify_reduce(ref, out, n_checks, result=result)
+    res = merge_across_ranks(ops.verify_reduce(ref, out, n_checks, result=result), group)
+    return reports_from_result(res, rtol, atol)
+
+
+def merge_across_ranks(result: torch.Tensor, group: Any = None) -> torch.Tensor:
+    """Combine per-rank ``[n_checks, 4]`` results in place with ONE collective.
+
+    All four fields (two maxima, two 0/1 NaN flags) are non-negative floats, so
+    ``all_reduce(MAX)`` merges them exactly and every rank ends with the same
+    tensor.  A no-op without an initialised process group.
+    """
     import torch.distributed as dist
 
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(res, op=dist.ReduceOp.MAX, group=group)
-    return reports_from_result(res, rtol, atol)
+        dist.all_reduce(result, op=dist.ReduceOp.MAX, group=group)
+    return result
