@@ -16,6 +16,9 @@
 // tracked by one mbarrier per stage, so kStages-1 tiles per CTA are always in
 // flight while the serial recurrence runs on the resident one.  y is staged in
 // shared memory and written with 16-byte stores.
+#include <cstdlib>
+#include <type_traits>
+
 #include "umma.cuh"
 
 namespace cb2 {
@@ -214,14 +217,18 @@ diag_scan_kernel(const unsigned char* __restrict__ a, const unsigned char* __res
 }
 
 // ---------------------------------------------------------------------------
-// Fast path (D a multiple of 32, N >= 4): same mapping, but
-//  * tiles come in through tiled TMA (3-D tensor maps {D*N | D, T, B}; a tile of
+// Fast path (D a multiple of 32, N >= 4): same ownership of channels and
+// states, but
+//  * tiles come in through tiled TMA (3-D tensor maps {D*N | D, T, B}: a tile of
 //    16 time steps is kNumBox + 1 copies instead of 32 row copies, and the T
-//    axis is clipped per batch entry by the map itself),
-//  * a thread owns kNpt = 4 n (four lanes per channel), which doubles the warps
-//    per SM for latency hiding, and the arithmetic runs on two-wide fp32 FMAs,
-//  * each group of four steps loads all its operands before it stores anything,
-//    so the loads of consecutive steps overlap,
+//    axis is clipped per batch entry by the map itself);
+//  * a dedicated producer warp issues every copy and the y stores; consumer
+//    warps hand stages back through an `empty` mbarrier and never meet at a
+//    CTA-wide barrier, so they drift apart and hide each other's latencies;
+//  * a thread owns NPT n (4 lanes per channel for N=16), the arithmetic runs on
+//    two-wide fp32 FMAs, operands of the next four steps are loaded while the
+//    current four are computed, and the n-sum is a transposing shuffle
+//    reduction that leaves each lane with the total of ONE step;
 //  * y goes out with one TMA store per tile from a double-buffered staging area.
 // ---------------------------------------------------------------------------
 template <int DTYPE, int N, int NPT>
@@ -230,7 +237,8 @@ struct FastCfg {
   static constexpr int kNpt = NPT;
   static constexpr int kLpc = N / NPT;
   static constexpr int kCh = 32;
-  static constexpr int kThreads = kCh * kLpc;
+  static constexpr int kConsumers = kCh * kLpc;
+  static constexpr int kThreads = kConsumers + 32;     // + producer warp
   static constexpr int kRows = 16;
   static constexpr int kStages = 4;
   static constexpr int kRowElems = kCh * N;
@@ -239,7 +247,8 @@ struct FastCfg {
   static constexpr int kABytes = kRows * kRowElems * kEsz;
   static constexpr int kXBytes = kRows * kCh * kEsz;
   static constexpr int kStageBytes = kABytes + kXBytes;
-  static constexpr int kSmem = kStages * kStageBytes + 2 * kXBytes + kStages * 8 + 128;
+  static constexpr int kNumBars = 2 * kStages + 2;
+  static constexpr int kSmem = kStages * kStageBytes + 2 * kXBytes + kNumBars * 8 + 16 + 128;
 };
 
 template <int DTYPE, int N, int NPT>
@@ -253,44 +262,70 @@ diag_scan_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_stage = smem;
   unsigned char* s_y = smem + C::kStages * C::kStageBytes;
-  uint64_t* s_full = reinterpret_cast<uint64_t*>(s_y + 2 * C::kXBytes);
+  uint64_t* s_full = reinterpret_cast<uint64_t*>(s_y + 2 * C::kXBytes);   // [kStages] TMA -> consumers
+  uint64_t* s_empty = s_full + C::kStages;                                // [kStages] consumers -> producer
+  uint64_t* s_yfree = s_empty + C::kStages;                               // [2] producer -> consumers
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_yfree + 2);
 
   const int tid = threadIdx.x;
   const int blocks_per_b = D / C::kCh;
   const int b = blockIdx.x / blocks_per_b;
   const int d0 = (blockIdx.x % blocks_per_b) * C::kCh;
-  const int ch = tid / C::kLpc, sub = tid % C::kLpc;
-  const int d = d0 + ch;
   const int ntiles = (T + C::kRows - 1) / C::kRows;
-  // this thread's NPT elements inside a stage's `a` tile (box-major layout)
-  const int e = ch * N + sub * NPT;
-  const int a_off = (e / C::kBoxCols) * (C::kRows * C::kBoxCols * C::kEsz) + (e % C::kBoxCols) * C::kEsz;
   constexpr int kAPitch = C::kBoxCols * C::kEsz;
   constexpr int kXPitch = C::kCh * C::kEsz;
 
   if (tid == 0) {
-    for (int s = 0; s < C::kStages; ++s) mbar_init(&s_full[s], 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], C::kConsumers);
+    }
+    mbar_init(&s_yfree[0], 1);
+    mbar_init(&s_yfree[1], 1);
+    *s_abort = 0;
     mbar_fence_init();
   }
   __syncthreads();
 
-  auto issue_tile = [&](int tile) {  // thread 0 only
-    const int s = tile % C::kStages;
-    unsigned char* sa = s_stage + s * C::kStageBytes;
-    mbar_arrive_expect_tx(&s_full[s], C::kStageBytes);
+  if (tid >= C::kConsumers) {
+    // ---------------------------------------------------------------- producer
+    if (tid == C::kConsumers) {
+      umma::tma_prefetch_desc(&map_a);
+      umma::tma_prefetch_desc(&map_x);
+      umma::tma_prefetch_desc(&map_y);
+      auto issue_tile = [&](int tile) {
+        const int s = tile % C::kStages;
+        unsigned char* sa = s_stage + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&s_full[s], C::kStageBytes);
 #pragma unroll
-    for (int bx = 0; bx < C::kNumBox; ++bx)
-      umma::tma_load_3d(sa + bx * (C::kRows * C::kBoxCols * C::kEsz), &map_a,
-                        d0 * N + bx * C::kBoxCols, tile * C::kRows, b, &s_full[s]);
-    umma::tma_load_3d(sa + C::kABytes, &map_x, d0, tile * C::kRows, b, &s_full[s]);
-  };
-  if (tid == 0) {
-    umma::tma_prefetch_desc(&map_a);
-    umma::tma_prefetch_desc(&map_x);
-    umma::tma_prefetch_desc(&map_y);
-    for (int i = 0; i < C::kStages && i < ntiles; ++i) issue_tile(i);
+        for (int bx = 0; bx < C::kNumBox; ++bx)
+          umma::tma_load_3d(sa + bx * (C::kRows * C::kBoxCols * C::kEsz), &map_a,
+                            d0 * N + bx * C::kBoxCols, tile * C::kRows, b, &s_full[s]);
+        umma::tma_load_3d(sa + C::kABytes, &map_x, d0, tile * C::kRows, b, &s_full[s]);
+      };
+      for (int i = 0; i < C::kStages && i < ntiles; ++i) issue_tile(i);
+      for (int tile = 0; tile < ntiles; ++tile) {
+        const int s = tile % C::kStages;
+        // every consumer has finished reading stage s and staging y for `tile`
+        if (!mbar_wait_abortable(&s_empty[s], (tile / C::kStages) & 1, s_abort)) break;
+        umma::tma_store_3d(&map_y, d0, tile * C::kRows, b, s_y + (tile & 1) * C::kXBytes);
+        bulk_commit();
+        if (tile + C::kStages < ntiles) issue_tile(tile + C::kStages);
+        // the store of the previous tile has left its staging buffer: hand it back
+        bulk_wait_read<1>();
+        if (tile >= 1) mbar_arrive(&s_yfree[(tile - 1) & 1]);
+      }
+      bulk_wait_all<0>();
+      if (*s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+    }
+    return;
   }
 
+  // ------------------------------------------------------------------ consumers
+  const int ch = tid / C::kLpc, sub = tid % C::kLpc;
+  const int d = d0 + ch;
+  const int e = ch * N + sub * NPT;   // this thread's elements inside a row of the `a` tile
+  const int a_off = (e / C::kBoxCols) * (C::kRows * C::kBoxCols * C::kEsz) + (e % C::kBoxCols) * C::kEsz;
   constexpr int kPairs = NPT / 2;
   uint64_t h2[kPairs], b2[kPairs], c2[kPairs];
 #pragma unroll
@@ -301,68 +336,96 @@ diag_scan_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const size_t hi = (size_t(b) * D + d) * N + n;
     h2[p] = h0 ? umma::f2_pack(h0[hi], h0[hi + 1]) : umma::f2_pack(0.f, 0.f);
   }
+  // After the transposing reduction a lane holds kKeep consecutive steps of a
+  // group of four, starting at q_base; lanes with dup != 0 hold duplicates.
+  constexpr int kXRounds = C::kLpc >= 4 ? 2 : (C::kLpc == 2 ? 1 : 0);
+  constexpr int kKeep = 4 >> kXRounds;
+  const int q_base = (kXRounds >= 1 && (sub & 1) ? 2 : 0) + (kXRounds >= 2 && (sub & 2) ? 1 : 0);
+  const bool dup = (sub >> kXRounds) != 0;
 
   for (int tile = 0; tile < ntiles; ++tile) {
     const int s = tile % C::kStages;
-    const int t0 = tile * C::kRows;
-    const int rows = min(C::kRows, T - t0);
-    const bool ok = mbar_wait_bounded(&s_full[s], (tile / C::kStages) & 1);
+    const int rows = min(C::kRows, T - tile * C::kRows);
+    bool ok = mbar_wait_abortable(&s_full[s], (tile / C::kStages) & 1, s_abort);
+    if (ok && tile >= 2) ok = mbar_wait_abortable(&s_yfree[tile & 1], ((tile >> 1) - 1) & 1, s_abort);
+    if (!ok) return;
     const unsigned char* sa = s_stage + s * C::kStageBytes + a_off;
     const unsigned char* sx = s_stage + s * C::kStageBytes + C::kABytes + ch * C::kEsz;
     unsigned char* sy = s_y + (tile & 1) * C::kXBytes;
-    if (ok) {
+
+    float av[2][4][NPT], xv[2][4];
+    auto load_group = [&](int buf, int r0) {
 #pragma unroll
-      for (int r0 = 0; r0 < C::kRows; r0 += 4) {
-        if (r0 < rows) {  // uniform over the CTA; rows past T are never applied
-          float av[4][NPT], xv[4], yv[4];
+      for (int q = 0; q < 4; ++q) {
+        load_row<DTYPE, NPT>(sa + (r0 + q) * kAPitch, av[buf][q]);
+        xv[buf][q] = E::ld(sx + (r0 + q) * kXPitch, 0);
+      }
+    };
+    // Four steps from registers.  `limit` = number of valid steps in the group
+    // (4 everywhere except in the ragged last tile, where the branch-free body
+    // is replaced by a guarded one so that steps past T never touch the state).
+    auto group = [&](int cur, int r0, auto full_tag, int limit) {
+      constexpr bool kFull = decltype(full_tag)::value;
+      float yv[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            load_row<DTYPE, NPT>(sa + (r0 + q) * kAPitch, av[q]);
-            xv[q] = E::ld(sx + (r0 + q) * kXPitch, 0);
+      for (int q = 0; q < 4; ++q) {
+        if (kFull || q < limit) {
+          const uint64_t x2 = umma::f2_pack(xv[cur][q], xv[cur][q]);
+          uint64_t acc = umma::f2_pack(0.f, 0.f);
+#pragma unroll
+          for (int p = 0; p < kPairs; ++p) {
+            const uint64_t a2 = umma::f2_pack(av[cur][q][2 * p], av[cur][q][2 * p + 1]);
+            h2[p] = umma::f2_fma(a2, h2[p], umma::f2_mul(b2[p], x2));
+            acc = umma::f2_fma(c2[p], h2[p], acc);
           }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (r0 + q < rows) {
-              const uint64_t x2 = umma::f2_pack(xv[q], xv[q]);
-              uint64_t acc = umma::f2_pack(0.f, 0.f);
-#pragma unroll
-              for (int p = 0; p < kPairs; ++p) {
-                const uint64_t a2 = umma::f2_pack(av[q][2 * p], av[q][2 * p + 1]);
-                h2[p] = umma::f2_fma(a2, h2[p], umma::f2_mul(b2[p], x2));
-                acc = umma::f2_fma(c2[p], h2[p], acc);
-              }
-              float lo, hi;
-              umma::f2_unpack(acc, lo, hi);
-              yv[q] = lo + hi;
-            } else {
-              yv[q] = 0.f;
-            }
-          }
-#pragma unroll
-          for (int off = C::kLpc >> 1; off > 0; off >>= 1) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) yv[q] += __shfl_xor_sync(0xffffffffu, yv[q], off);
-          }
-          if (sub == 0) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) E::st(sy + (r0 + q) * kXPitch, ch, yv[q]);
-          }
+          float lo, hi;
+          umma::f2_unpack(acc, lo, hi);
+          yv[q] = lo + hi;
+        } else {
+          yv[q] = 0.f;
         }
       }
+      // transposing reduction over the lanes of a channel
+      if constexpr (kXRounds >= 1) {
+        const bool up = sub & 1;
+        const float s0 = up ? yv[0] : yv[2], s1 = up ? yv[1] : yv[3];
+        const float k0 = up ? yv[2] : yv[0], k1 = up ? yv[3] : yv[1];
+        yv[0] = k0 + __shfl_xor_sync(0xffffffffu, s0, 1);
+        yv[1] = k1 + __shfl_xor_sync(0xffffffffu, s1, 1);
+      }
+      if constexpr (kXRounds >= 2) {
+        const bool up = sub & 2;
+        const float s0 = up ? yv[0] : yv[1];
+        const float k0 = up ? yv[1] : yv[0];
+        yv[0] = k0 + __shfl_xor_sync(0xffffffffu, s0, 2);
+      }
+#pragma unroll
+      for (int off = 1 << kXRounds; off < C::kLpc; off <<= 1) {   // lanes beyond four: plain butterfly
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) yv[j] += __shfl_xor_sync(0xffffffffu, yv[j], off);
+      }
+      if (!dup) {
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) E::st(sy + (r0 + q_base + j) * kXPitch, ch, yv[j]);
+      }
+    };
+    load_group(0, 0);
+    if (rows == C::kRows) {
+#pragma unroll
+      for (int gi = 0; gi < C::kRows / 4; ++gi) {
+        if (gi + 1 < C::kRows / 4) load_group((gi & 1) ^ 1, gi * 4 + 4);   // next four steps' operands
+        group(gi & 1, gi * 4, std::true_type{}, 4);
+      }
+    } else {
+#pragma unroll 1
+      for (int gi = 0; gi * 4 < rows; ++gi) {
+        if (gi > 0) load_group(0, gi * 4);
+        group(0, gi * 4, std::false_type{}, rows - gi * 4);
+      }
     }
-    fence_proxy_async_smem();            // y rows -> visible to the TMA store
-    if (tid == 0) bulk_wait_read<0>();   // the previous tile's store has left the other y buffer
-    if (__syncthreads_or(!ok)) {
-      if (tid == 0 && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
-      return;
-    }
-    if (tid == 0) {
-      if (tile + C::kStages < ntiles) issue_tile(tile + C::kStages);
-      umma::tma_store_3d(&map_y, d0, t0, b, sy);   // rows past T are clipped by the map
-      bulk_commit();
-    }
+    fence_proxy_async_smem();      // staged y rows -> visible to the TMA store
+    mbar_arrive(&s_empty[s]);      // stage s and this tile's y are the producer's now
   }
-  if (tid == 0) bulk_wait_all<0>();
   if (hT) {
 #pragma unroll
     for (int p = 0; p < kPairs; ++p) {
@@ -391,6 +454,16 @@ int launch_scan_tma(const void* a, const void* x, const void* b, const void* c, 
   kern<<<B * (D / C::kCh), C::kThreads, C::kSmem, st>>>(ma, mx, my, b, c, h0, hT, T, D, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
+}
+
+// Lanes per channel on the fast path: 4 n per thread by default; the
+// environment variable CB2_SCAN_NPT=8 selects 8 n per thread (a tuning knob).
+inline int scan_npt() {
+  static int v = [] {
+    const char* e = getenv("CB2_SCAN_NPT");
+    return (e && e[0] == '8') ? 8 : 4;
+  }();
+  return v;
 }
 
 // `a` shared over n ([B,T,D]): one thread per (b, channel) keeps all N states.
@@ -444,7 +517,13 @@ int launch_scan(const void* a, const void* x, const void* b, const void* c, cons
   }
   if ((size_t(D) * N * C::kEsz) % 16 || (size_t(D) * C::kEsz) % 16) return CB2_BAD_SHAPE;
   if constexpr (N >= 4) {
-    if (D % 32 == 0) return launch_scan_tma<DTYPE, N, 4>(a, x, b, c, h0, y, hT, B, T, D, dev_status, st);
+    if (D % 32 == 0) {
+      if constexpr (N >= 8) {
+        if (scan_npt() == 8)
+          return launch_scan_tma<DTYPE, N, 8>(a, x, b, c, h0, y, hT, B, T, D, dev_status, st);
+      }
+      return launch_scan_tma<DTYPE, N, 4>(a, x, b, c, h0, y, hT, B, T, D, dev_status, st);
+    }
   }
   auto kern = diag_scan_kernel<DTYPE, N>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) !=
