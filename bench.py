@@ -19,7 +19,6 @@ import argparse
 import json
 import math
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -51,34 +50,40 @@ def c4_gamma(H: int) -> torch.Tensor:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU while a region runs."""
-
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons of one GPU while a region runs
+    (NVML every 5 ms; read-only queries)."""
 
     def __init__(self, index: int) -> None:
         self.index = index
-        self.rows: list[list[str]] = []
+        self.mhz: list[int] = []
+        self.max_mhz: int | None = None
+        self.reason_bits = 0
         self._stop = threading.Event()
         self._thr: threading.Thread | None = None
 
     def _run(self) -> None:
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                     "--format=csv,noheader,nounits"],
-                    capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in vis.split(",") if v.strip().isdigit()]
+            phys = int(ids[self.index]) if self.index < len(ids) else self.index
+            h = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            while not self._stop.is_set():
+                self.mhz.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                self.reason_bits |= nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self._stop.wait(0.005)
+        except Exception:
+            pass
 
     def __enter__(self):
+        self._stop.clear()
         self._thr = threading.Thread(target=self._run, daemon=True)
         self._thr.start()
+        time.sleep(0.05)   # let NVML come up before the timed region starts
         return self
 
     def __exit__(self, *exc):
@@ -87,13 +92,12 @@ class ClockSampler:
             self._thr.join(timeout=10)
 
     def summary(self) -> dict:
-        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names)
-                   if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx,
-                "reasons": reasons, "samples": len(mhz)}
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                 0x4: "sw_power_cap"}
+        mhz = sorted(self.mhz)
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": self.max_mhz,
+                "reasons": [n for bit, n in names.items() if self.reason_bits & bit],
+                "samples": len(mhz)}
 
 
 # --------------------------------------------------------------------------- timing
@@ -313,6 +317,8 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # keep stdout for the one JSON line: NCCL's own banner/debug output goes to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         torch.distributed.init_process_group("nccl", device_id=dev)
     from catopt_b200 import _lib, build, ops
     from catopt_b200.host_api import DecayedHostPipeline
@@ -333,7 +339,8 @@ def run_ours(args) -> None:
     def step():
         ops.decayed_chunk_fwd(q, k, v, gamma, C, 1.0, out=o)
 
-    with ClockSampler(local) as clk:
+    clk = ClockSampler(local)
+    with clk:
         ms = time_steps(step, args.steps, args.warmup, world)
     ops.check_device_status(dev)
     tokens = B * T
@@ -346,7 +353,8 @@ def run_ours(args) -> None:
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty(B, H, T, d, dtype=torch.bfloat16).pin_memory()
     del q, k, v
-    ms_e2e = time_steps(lambda: pipe.run(hq, hk, hv, ho), args.steps, args.warmup, world)
+    with clk:   # the same sampler keeps collecting over the end-to-end region
+        ms_e2e = time_steps(lambda: pipe.run(hq, hk, hv, ho), args.steps, args.warmup, world)
     if not torch.equal(ho.view(torch.int16), o.cpu().view(torch.int16)):
         raise SystemExit("e2e result differs from the device-resident result")
     e2e_launches = launches_per_step * len(pipe.bounds)
@@ -440,7 +448,7 @@ def main() -> None:
     ap.add_argument("--profile-case", default=None, choices=["decayed", "scan", "verify", "linear"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel lines")
