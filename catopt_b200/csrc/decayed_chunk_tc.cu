@@ -31,10 +31,10 @@ namespace {
 // Optional phase timeline of CTA 0 (compute-group thread 0), for tuning builds
 // only: compile with -DCB2_TIMELINE and read g_timeline back from the host.
 #ifdef CB2_TIMELINE
-__device__ long long g_timeline[64][8];
+__device__ long long g_timeline[64][12];
 #define CB2_TL(i, k)                                                   \
   do {                                                                 \
-    if (blockIdx.x == 0 && threadIdx.x == 64 && (i) < 64) g_timeline[i][k] = clock64(); \
+    if (blockIdx.x == 0 && threadIdx.x == 96 && (i) < 64) g_timeline[i][k] = clock64(); \
   } while (0)
 #else
 #define CB2_TL(i, k) do {} while (0)
@@ -49,8 +49,8 @@ constexpr uint32_t kTile = umma::kTileBytes;      // 32 KiB
 constexpr uint32_t kOffRing = 0;
 constexpr uint32_t kOffO = kSlots * kTile;          // output staging tile
 constexpr uint32_t kOffSb = kOffO + kTile;
-constexpr uint32_t kOffPow = kOffSb + kTile;                 // float[kC + 1]
-constexpr uint32_t kOffBars = kOffPow + 528;                 // 8-byte aligned
+constexpr uint32_t kOffPow = kOffSb + kTile;                 // float[32 zeros | g^0 .. g^128]
+constexpr uint32_t kOffBars = kOffPow + 704;                 // 8-byte aligned
 constexpr int kNumBars = 2 * kSlots + 8;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;       // tmem base, abort flag
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slack
@@ -80,9 +80,12 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const float* __restrict__ gamma, int H, int T, float inv_scale, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem =
-      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
+  // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
+  // __shared__ array keeps every access a shared-space (LDS/STS) access
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  // s_pow[j] = g^j for j in [-32, 128]; negative exponents hold 0, so the causal
+  // mask of the diagonal block needs neither a clamp nor a select
+  float* s_pow = reinterpret_cast<float*>(smem + kOffPow) + 32;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
@@ -121,6 +124,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int j = tid - 64;
     s_pow[j] = powf(g, float(j));
     if (j == 0) s_pow[kC] = powf(g, float(kC));
+    if (j < 32) s_pow[j - 32] = 0.f;
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -230,25 +234,21 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       CB2_TL(i, 1);
-      // (a) P = bf16(S . decay), packed into TMEM over S.  Branch-free: the power
-      // is always loaded (clamped index) and masked by a select.
+      // (a) P = bf16(S . decay), packed into TMEM over S: one table load and one
+      // multiply per element (the table is 0 for negative exponents = masked).
       {
         const int cb0 = half * 2, cb1 = cb0 + 1;
         if (cb0 <= q4) umma::tmem_ld32(lane_base + kColS + cb0 * 32, va);  // warp-uniform:
         if (cb1 <= q4) umma::tmem_ld32(lane_base + kColS + cb1 * 32, vb);  // blocks right of the
         if (cb0 <= q4) umma::tmem_wait_ld();                               // diagonal are zero
+        CB2_TL(i, 8);
         auto decay_block = [&](int cb, const uint32_t (&v)[32]) {
           uint32_t w[16];
           if (cb <= q4) {
-            const int e0 = r - cb * 32;  // exponent of the block's first column
+            const float* pw = s_pow + (r - cb * 32);  // exponent of the block's first column
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const int ea = e0 - j, eb = e0 - j - 1;
-              const float fa = s_pow[max(ea, 0)], fb = s_pow[max(eb, 0)];
-              const float lo = ea >= 0 ? __uint_as_float(v[j]) * fa : 0.f;
-              const float hi = eb >= 0 ? __uint_as_float(v[j + 1]) * fb : 0.f;
-              w[j >> 1] = pack_bf16x2(lo, hi);
-            }
+            for (int j = 0; j < 32; j += 2)
+              w[j >> 1] = pack_bf16x2(__uint_as_float(v[j]) * pw[-j], __uint_as_float(v[j + 1]) * pw[-j - 1]);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) w[j] = 0u;
@@ -257,7 +257,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         };
         decay_block(cb0, va);
         decay_block(cb1, vb);
+        CB2_TL(i, 9);
         umma::tmem_wait_st();
+        CB2_TL(i, 10);
       }
       // The staging tile of the previous chunk's output must have been read by
       // its TMA store before (c) rewrites it; making the issuing thread wait
