@@ -20,6 +20,7 @@ SOURCES = [
     "verify_reduce.cu",
     "diag_scan.cu",
     "linear_f32.cu",
+    "linear_tf32x3.cu",
     "decayed_chunk_ffma.cu",
     "decayed_chunk_tc.cu",
     "decayed_chunk.cu",
@@ -73,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if failed:
         raise RuntimeError("nvcc failed")
     if procs or not LIB.exists():
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+        cmd = [_nvcc(), "-Wno-deprecated-gpu-targets", "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
         subprocess.check_call(cmd)
     return LIB
 

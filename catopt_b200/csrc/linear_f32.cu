@@ -14,6 +14,12 @@
 #include "common.cuh"
 
 namespace cb2 {
+// tensor-core path for large row counts (linear_tf32x3.cu)
+bool linear_tf32x3_supported(const float* x, const float* w, const float* bias, const float* y, int R,
+                             int n_in, int n_out);
+int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* y, int R, int n_in,
+                      int n_out, int* dev_status, cudaStream_t st);
+
 namespace {
 
 constexpr int kTile = 64;
@@ -159,6 +165,9 @@ extern "C" int cb2_linear_f32(const float* x, const float* w, const float* bias,
                               size_t scratch_bytes, void* stream) {
   if (!x || !w || !y) return CB2_NULL_PTR;
   if (R <= 0 || in_features <= 0 || out_features <= 0) return CB2_BAD_SHAPE;
+  if (cb2::linear_tf32x3_supported(x, w, bias, y, R, in_features, out_features))
+    return cb2::linear_tf32x3_run(x, w, bias, y, R, in_features, out_features, nullptr,
+                                  static_cast<cudaStream_t>(stream));
   if (cb2_linear_f32_scratch_bytes(R, in_features, out_features) > 0 && !scratch)
     return CB2_SCRATCH_TOO_SMALL;
   return cb2::gemm<true>(x, w, bias, y, R, out_features, in_features,
