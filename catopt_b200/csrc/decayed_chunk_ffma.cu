@@ -12,10 +12,10 @@
 //   3. O_i  = ( P_i V_i + diag(g^(r+1)) Q_i S_i ) / scale -> o
 // Steps 1 and 3 are independent over (b, h, chunk) and fill the GPU even when
 // B*H is small; step 2 is an elementwise scan over the chunk axis.  Powers of
-// gamma come from a per-head table computed in fp64 and rounded once, so they
-// are the correctly rounded fp32 values.
+// gamma are tabulated per CTA in shared memory (powf, fp32).  Three launches:
+// one kernel does every P and KV tile of step 1, one the scan, one step 3.
 //
-// scratch layout (floats): [H][C+1] powers | [B*H*K][C][C] P | [B*H*K][dk][dv] KV/S
+// scratch layout (floats): [B*H*K][C][C] P | [B*H*K][dk][dv] KV/S
 #include "common.cuh"
 
 namespace cb2 {
@@ -38,12 +38,12 @@ __device__ __forceinline__ void st_elem(void* p, size_t i, float v) {
     static_cast<float*>(p)[i] = v;
 }
 
-__global__ void pow_table_kernel(const float* __restrict__ gamma, float* __restrict__ tab, int H,
-                                 int C) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= H * (C + 1)) return;
-  const int h = i / (C + 1), k = i % (C + 1);
-  tab[i] = float(pow(double(gamma[h]), double(k)));
+constexpr int kMaxChunk = 1024;   // size of the per-CTA power table
+
+// s_pw[k] = g^k for k in [0, C]; ends with a CTA barrier.
+__device__ __forceinline__ void fill_pow_table(float* s_pw, float g, int C) {
+  for (int k = threadIdx.x; k <= C; k += blockDim.x) s_pw[k] = powf(g, float(k));
+  __syncthreads();
 }
 
 // acc += A_tile . B_tile over k in [0,kdim), 64x64 output tile at (m0,n0).
@@ -90,56 +90,52 @@ __device__ __forceinline__ void tile_gemm(float (&acc)[4][4], int kdim, FA fa, F
   }
 }
 
-// Step 1a: P[z] = (Q_i K_i^T) . tril(g^(r-c)).   grid (batch, C/64, C/64)
+// Step 1, one launch: blockIdx.y < ct*ct is a 64x64 tile of
+//   P[z] = (Q_i K_i^T) . tril(g^(r-c))
+// and the remaining blockIdx.y values are 64x64 tiles of
+//   KV[z] = (K_i . g^(C-1-r))^T V_i.
 template <int DTYPE>
 __global__ void __launch_bounds__(kThreads)
-score_kernel(const void* __restrict__ q, const void* __restrict__ k, const float* __restrict__ tab,
-             float* __restrict__ P, int H, int T, int dk, int C) {
+chunk_local_kernel(const void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v,
+                   const float* __restrict__ gamma, float* __restrict__ P, float* __restrict__ KV, int H,
+                   int T, int dk, int dv, int C, int ct, int vt) {
   __shared__ __align__(16) float As[kSlice][kTile + 4];
   __shared__ __align__(16) float Bs[kSlice][kTile + 4];
+  __shared__ float s_pw[kMaxChunk + 1];
   const int nchunk = T / C;
   const int z = blockIdx.x, bh = z / nchunk, i = z % nchunk, h = bh % H;
-  const int m0 = blockIdx.y * kTile, n0 = blockIdx.z * kTile;
-  float acc[4][4] = {};
-  float* out = P + size_t(z) * C * C;
+  fill_pow_table(s_pw, gamma[h], C);
+  const float* pw = s_pw;
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
-  if (n0 <= m0 + kTile - 1) {  // tiles strictly above the diagonal are all zero
-    const size_t base = (size_t(bh) * T + size_t(i) * C) * dk;
-    auto fa = [&](int m, int kk) {
-      return (m0 + m < C && kk < dk) ? ld_elem<DTYPE>(q, base + size_t(m0 + m) * dk + kk) : 0.f;
-    };
-    auto fb = [&](int kk, int n) {
-      return (n0 + n < C && kk < dk) ? ld_elem<DTYPE>(k, base + size_t(n0 + n) * dk + kk) : 0.f;
-    };
-    tile_gemm<true, false>(acc, dk, fa, fb, As, Bs);
-  }
-  const float* pw = tab + size_t(h) * (C + 1);
-#pragma unroll
-  for (int ii = 0; ii < 4; ++ii) {
-    const int r = m0 + ty * 4 + ii;
-    if (r >= C) continue;
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-      const int c = n0 + tx * 4 + jj;
-      if (c < C) out[size_t(r) * C + c] = (c <= r) ? acc[ii][jj] * pw[r - c] : 0.f;
-    }
-  }
-}
-
-// Step 1b: KV[z] = (K_i . g^(C-1-r))^T V_i.   grid (batch, dk/64, dv/64)
-template <int DTYPE>
-__global__ void __launch_bounds__(kThreads)
-kv_kernel(const void* __restrict__ k, const void* __restrict__ v, const float* __restrict__ tab,
-          float* __restrict__ KV, int H, int T, int dk, int dv, int C) {
-  __shared__ __align__(16) float As[kSlice][kTile + 4];
-  __shared__ __align__(16) float Bs[kSlice][kTile + 4];
-  const int nchunk = T / C;
-  const int z = blockIdx.x, bh = z / nchunk, i = z % nchunk, h = bh % H;
-  const int m0 = blockIdx.y * kTile, n0 = blockIdx.z * kTile;
-  const float* pw = tab + size_t(h) * (C + 1);
+  float acc[4][4] = {};
   const size_t kbase = (size_t(bh) * T + size_t(i) * C) * dk;
   const size_t vbase = (size_t(bh) * T + size_t(i) * C) * dv;
-  float acc[4][4] = {};
+  if (int(blockIdx.y) < ct * ct) {
+    const int m0 = (blockIdx.y / ct) * kTile, n0 = (blockIdx.y % ct) * kTile;
+    float* out = P + size_t(z) * C * C;
+    if (n0 <= m0 + kTile - 1) {  // tiles strictly above the diagonal are all zero
+      auto fa = [&](int m, int kk) {
+        return (m0 + m < C && kk < dk) ? ld_elem<DTYPE>(q, kbase + size_t(m0 + m) * dk + kk) : 0.f;
+      };
+      auto fb = [&](int kk, int n) {
+        return (n0 + n < C && kk < dk) ? ld_elem<DTYPE>(k, kbase + size_t(n0 + n) * dk + kk) : 0.f;
+      };
+      tile_gemm<true, false>(acc, dk, fa, fb, As, Bs);
+    }
+#pragma unroll
+    for (int ii = 0; ii < 4; ++ii) {
+      const int r = m0 + ty * 4 + ii;
+      if (r >= C) continue;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int c = n0 + tx * 4 + jj;
+        if (c < C) out[size_t(r) * C + c] = (c <= r) ? acc[ii][jj] * pw[r - c] : 0.f;
+      }
+    }
+    return;
+  }
+  const int t = blockIdx.y - ct * ct;
+  const int m0 = (t / vt) * kTile, n0 = (t % vt) * kTile;
   auto fa = [&](int m, int r) {  // A[m=e][k=r] = K[r][e] * g^(C-1-r)
     return (m0 + m < dk && r < C) ? ld_elem<DTYPE>(k, kbase + size_t(r) * dk + m0 + m) * pw[C - 1 - r]
                                   : 0.f;
@@ -149,7 +145,6 @@ kv_kernel(const void* __restrict__ k, const void* __restrict__ v, const float* _
   };
   tile_gemm<false, true>(acc, C, fa, fb, As, Bs);
   float* out = KV + size_t(z) * dk * dv;
-  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
 #pragma unroll
   for (int ii = 0; ii < 4; ++ii) {
     const int e = m0 + ty * 4 + ii;
@@ -162,34 +157,42 @@ kv_kernel(const void* __restrict__ k, const void* __restrict__ v, const float* _
   }
 }
 
-// Step 2: exclusive decayed scan over chunks, in place (KV_i <- S_i).
-__global__ void state_scan_kernel(float* __restrict__ KV, const float* __restrict__ tab, int H,
+// Step 2: exclusive decayed scan over chunks, in place (KV_i <- S_i).  Eight
+// chunks are loaded before the dependent FMA chain runs, so the loads overlap.
+__global__ void state_scan_kernel(float* __restrict__ KV, const float* __restrict__ gamma, int H,
                                   int nchunk, int C, size_t per_chunk, size_t total_bh) {
   const size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
   if (idx >= total_bh * per_chunk) return;
   const size_t bh = idx / per_chunk, e = idx % per_chunk;
-  const float gC = tab[size_t(bh % H) * (C + 1) + C];
+  const float gC = powf(gamma[bh % H], float(C));
   float* p = KV + bh * nchunk * per_chunk + e;
   float state = 0.f;
-  for (int i = 0; i < nchunk; ++i) {
-    const float kv = p[size_t(i) * per_chunk];
-    p[size_t(i) * per_chunk] = state;
-    state = fmaf(gC, state, kv);
+  for (int i0 = 0; i0 < nchunk; i0 += 8) {
+    float kv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) kv[j] = (i0 + j < nchunk) ? p[size_t(i0 + j) * per_chunk] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (i0 + j < nchunk) p[size_t(i0 + j) * per_chunk] = state;
+      state = fmaf(gC, state, kv[j]);
+    }
   }
 }
 
 // Step 3: O_i = (P_i V_i + diag(g^(r+1)) Q_i S_i) / scale.  grid (batch, C/64, dv/64)
 template <int DTYPE>
 __global__ void __launch_bounds__(kThreads)
-output_kernel(const void* __restrict__ q, const void* __restrict__ v, const float* __restrict__ tab,
+output_kernel(const void* __restrict__ q, const void* __restrict__ v, const float* __restrict__ gamma,
               const float* __restrict__ P, const float* __restrict__ S, void* __restrict__ o, int H,
               int T, int dk, int dv, int C, float scale) {
   __shared__ __align__(16) float As[kSlice][kTile + 4];
   __shared__ __align__(16) float Bs[kSlice][kTile + 4];
+  __shared__ float s_pw[kMaxChunk + 1];
   const int nchunk = T / C;
   const int z = blockIdx.x, bh = z / nchunk, i = z % nchunk, h = bh % H;
   const int m0 = blockIdx.y * kTile, n0 = blockIdx.z * kTile;
-  const float* pw = tab + size_t(h) * (C + 1);
+  fill_pow_table(s_pw, gamma[h], C);
+  const float* pw = s_pw;
   const size_t qbase = (size_t(bh) * T + size_t(i) * C) * dk;
   const size_t vbase = (size_t(bh) * T + size_t(i) * C) * dv;
   const float* Pz = P + size_t(z) * C * C;
@@ -228,7 +231,8 @@ output_kernel(const void* __restrict__ q, const void* __restrict__ v, const floa
 
 size_t ffma_scratch_floats(int B, int H, int T, int dk, int dv, int C) {
   const size_t nz = size_t(B) * H * (T / C);
-  return size_t(H) * (C + 1) + nz * C * C + nz * dk * dv;
+  (void)H;
+  return nz * C * C + nz * dk * dv;
 }
 
 template <int DTYPE>
@@ -236,23 +240,19 @@ int run_ffma(const void* q, const void* k, const void* v, void* o, const float* 
              int T, int dk, int dv, int C, float scale, float* scratch, cudaStream_t st) {
   const int nchunk = T / C;
   const size_t nz = size_t(B) * H * nchunk;
-  float* tab = scratch;
-  float* P = tab + size_t(H) * (C + 1);
+  if (C > kMaxChunk) return CB2_BAD_SHAPE;
+  float* P = scratch;
   float* KV = P + nz * C * C;
-  const int ntab = H * (C + 1);
-  pow_table_kernel<<<(ntab + 255) / 256, 256, 0, st>>>(gamma, tab, H, C);
-  CB2_LAUNCH_CHECK();
   const unsigned ct = (C + kTile - 1) / kTile, kt = (dk + kTile - 1) / kTile,
                  vt = (dv + kTile - 1) / kTile;
-  score_kernel<DTYPE><<<dim3(unsigned(nz), ct, ct), kThreads, 0, st>>>(q, k, tab, P, H, T, dk, C);
-  CB2_LAUNCH_CHECK();
-  kv_kernel<DTYPE><<<dim3(unsigned(nz), kt, vt), kThreads, 0, st>>>(k, v, tab, KV, H, T, dk, dv, C);
+  chunk_local_kernel<DTYPE><<<dim3(unsigned(nz), ct * ct + kt * vt), kThreads, 0, st>>>(
+      q, k, v, gamma, P, KV, H, T, dk, dv, C, int(ct), int(vt));
   CB2_LAUNCH_CHECK();
   const size_t per_chunk = size_t(dk) * dv, total = size_t(B) * H * per_chunk;
-  state_scan_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(KV, tab, H, nchunk, C, per_chunk,
+  state_scan_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(KV, gamma, H, nchunk, C, per_chunk,
                                                                   size_t(B) * H);
   CB2_LAUNCH_CHECK();
-  output_kernel<DTYPE><<<dim3(unsigned(nz), ct, vt), kThreads, 0, st>>>(q, v, tab, P, KV, o, H, T, dk,
+  output_kernel<DTYPE><<<dim3(unsigned(nz), ct, vt), kThreads, 0, st>>>(q, v, gamma, P, KV, o, H, T, dk,
                                                                        dv, C, scale);
   CB2_LAUNCH_CHECK();
   return CB2_OK;

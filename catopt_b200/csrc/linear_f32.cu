@@ -11,6 +11,10 @@
 // (the headline case is a 64x512 output), the reduction axis is split across
 // grid.z; partial tiles go to caller-provided scratch and a second kernel sums
 // them in a fixed order (deterministic) and adds the bias.
+#include <cooperative_groups.h>
+
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace cb2 {
@@ -97,6 +101,128 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ Bm, float* _
   }
 }
 
+// Split-K without a second launch or scratch: the CTAs that share an output
+// tile form a thread-block cluster along grid.z (2, 4 or 8 ranks).  Each rank
+// accumulates its slice of K into a 64x64 partial tile in its own shared
+// memory; after a cluster barrier, rank r sums rows [r*64/S, (r+1)*64/S) of all
+// S partial tiles through distributed shared memory in rank order (so the result
+// is deterministic), adds the bias and writes y.
+constexpr int kSliceC = 64;   // the cluster kernel loads a whole 64-deep slice at once
+template <bool B_NK>
+__global__ void __launch_bounds__(kGemmThreads)
+sgemm_cluster_kernel(const float* __restrict__ A, const float* __restrict__ Bm,
+                     const float* __restrict__ bias, float* __restrict__ out, int M, int N, int K,
+                     int k_per_split) {
+  namespace cg = cooperative_groups;
+  // As[k][m], Bs[k][n]; the partial tile later reuses the As storage
+  __shared__ __align__(16) float As[kSliceC][kTile + 4];
+  __shared__ __align__(16) float Bs[kSliceC][kTile + 4];
+  float (*part)[kTile + 4] = As;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+  const int kb = blockIdx.z * k_per_split;
+  const int ke = min(K, kb + k_per_split);
+  const int tx = tid % 16, ty = tid / 16;
+  const bool vec = (K % 4 == 0) && aligned16(A) && aligned16(Bm) && (!B_NK ? (N % 4 == 0) : true);
+  float acc[4][4] = {};
+  for (int k0 = kb; k0 < ke; k0 += kSliceC) {
+    // One exposed memory latency per slice: every load of the slice is issued
+    // before anything is consumed.  Rows of 64 k = 16 float4; 256 threads cover
+    // 16 rows per pass.
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      const int r = pass * 16 + tid / 16, kq = (tid % 16) * 4;
+      const int gm = m0 + r, gk = k0 + kq;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (gm < M) {
+        if (vec && gk + 3 < ke) {
+          v = *reinterpret_cast<const float4*>(A + size_t(gm) * K + gk);
+        } else {
+          if (gk < ke) v.x = A[size_t(gm) * K + gk];
+          if (gk + 1 < ke) v.y = A[size_t(gm) * K + gk + 1];
+          if (gk + 2 < ke) v.z = A[size_t(gm) * K + gk + 2];
+          if (gk + 3 < ke) v.w = A[size_t(gm) * K + gk + 3];
+        }
+      }
+      As[kq][r] = v.x; As[kq + 1][r] = v.y; As[kq + 2][r] = v.z; As[kq + 3][r] = v.w;
+    }
+    if (B_NK) {
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        const int r = pass * 16 + tid / 16, kq = (tid % 16) * 4;
+        const int gn = n0 + r, gk = k0 + kq;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gn < N) {
+          if (vec && gk + 3 < ke) {
+            v = *reinterpret_cast<const float4*>(Bm + size_t(gn) * K + gk);
+          } else {
+            if (gk < ke) v.x = Bm[size_t(gn) * K + gk];
+            if (gk + 1 < ke) v.y = Bm[size_t(gn) * K + gk + 1];
+            if (gk + 2 < ke) v.z = Bm[size_t(gn) * K + gk + 2];
+            if (gk + 3 < ke) v.w = Bm[size_t(gn) * K + gk + 3];
+          }
+        }
+        Bs[kq][r] = v.x; Bs[kq + 1][r] = v.y; Bs[kq + 2][r] = v.z; Bs[kq + 3][r] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        const int kk = pass * 16 + tid / 16, nq = (tid % 16) * 4;
+        const int gk = k0 + kk, gn = n0 + nq;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gk < ke) {
+          if (vec && gn + 3 < N) {
+            v = *reinterpret_cast<const float4*>(Bm + size_t(gk) * N + gn);
+          } else {
+            if (gn < N) v.x = Bm[size_t(gk) * N + gn];
+            if (gn + 1 < N) v.y = Bm[size_t(gk) * N + gn + 1];
+            if (gn + 2 < N) v.z = Bm[size_t(gk) * N + gn + 2];
+            if (gn + 3 < N) v.w = Bm[size_t(gk) * N + gn + 3];
+          }
+        }
+        *reinterpret_cast<float4*>(&Bs[kk][nq]) = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll 16
+    for (int kk = 0; kk < kSliceC; ++kk) {
+      const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+      const float a4[4] = {av.x, av.y, av.z, av.w};
+      const float b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a4[i], b4[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4*>(&part[ty * 4 + i][tx * 4]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+  cluster.sync();   // every rank's partial tile is complete and visible cluster-wide
+  const unsigned S = cluster.num_blocks(), rank = cluster.block_rank();
+  const int rows_per = kTile / int(S);
+  for (int e = tid; e < rows_per * (kTile / 4); e += kGemmThreads) {
+    const int row = int(rank) * rows_per + e / (kTile / 4), c4 = (e % (kTile / 4)) * 4;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (unsigned z = 0; z < S; ++z) {
+      const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(&part[row][c4], z));
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    const int gm = m0 + row;
+    if (gm < M) {
+      const float o4[4] = {sum.x, sum.y, sum.z, sum.w};
+      for (int j = 0; j < 4; ++j) {
+        const int gn = n0 + c4 + j;
+        if (gn < N) out[size_t(gm) * N + gn] = o4[j] + (bias ? bias[gn] : 0.f);
+      }
+    }
+  }
+  cluster.sync();   // nobody leaves while a peer may still read its shared memory
+}
+
 // y[m,n] = sum_z partial[z][m,n] (+ bias[n]); fixed summation order.
 __global__ void splitk_sum_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
                                   float* __restrict__ y, int M, int N, int splits) {
@@ -121,33 +247,58 @@ int pick_splits(int M, int N, int K) {
   int splits = kNumSMs / tiles;
   const int max_by_k = (K + 2 * kSlice - 1) / (2 * kSlice);  // keep >= 32 k per split
   if (splits > max_by_k) splits = max_by_k;
+  if (splits > 8) splits = 8;                                // portable cluster size
   return splits < 1 ? 1 : splits;
 }
 
 template <bool B_NK>
 int gemm(const float* A, const float* Bm, const float* bias, float* C, int M, int N, int K,
          float* scratch, size_t scratch_bytes, cudaStream_t st) {
-  int splits = scratch ? pick_splits(M, N, K) : 1;
-  if (splits > 1 && scratch_bytes < size_t(splits) * M * N * sizeof(float)) return CB2_SCRATCH_TOO_SMALL;
-  int kps = (K + splits - 1) / splits;
-  kps = ((kps + kSlice - 1) / kSlice) * kSlice;
-  splits = (K + kps - 1) / kps;
-  dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile, splits);
-  if (splits == 1) {
-    sgemm_kernel<B_NK><<<grid, kGemmThreads, 0, st>>>(A, Bm, C, M, N, K, K);
-    CB2_LAUNCH_CHECK();
-    if (bias) {
-      const size_t mn = size_t(M) * N;
-      add_bias_kernel<<<unsigned((mn + 255) / 256), 256, 0, st>>>(bias, C, M, N);
-      CB2_LAUNCH_CHECK();
+  const int splits = pick_splits(M, N, K);
+  dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile, 1);
+  if (splits > 1) {
+    // 2/4/8 K-slices: one launch, reduction through distributed shared memory
+    int cs = 2;
+    while (cs < splits) cs <<= 1;
+    const int kps = (((K + cs - 1) / cs + 3) / 4) * 4;   // multiples of 4 keep float4 loads aligned
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid.x, grid.y, cs);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = cs;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t ce = cudaLaunchKernelEx(&cfg, sgemm_cluster_kernel<B_NK>, A, Bm, bias, C, M, N, K, kps);
+    if (ce == cudaSuccess) return CB2_OK;
+    (void)cudaGetLastError();  // cluster launch refused: fall back to the plain kernels below
+    static bool warned = false;
+    if (!warned) {
+      warned = true;
+      fprintf(stderr, "catopt_b200: cluster launch refused (%s); using the two-pass split-K path\n",
+              cudaGetErrorString(ce));
     }
-    return CB2_OK;
+    if (scratch && scratch_bytes >= size_t(cs) * M * N * sizeof(float)) {
+      grid.z = cs;
+      sgemm_kernel<B_NK><<<grid, kGemmThreads, 0, st>>>(A, Bm, scratch, M, N, K, kps);
+      CB2_LAUNCH_CHECK();
+      const size_t mn = size_t(M) * N;
+      splitk_sum_kernel<<<unsigned((mn + 255) / 256), 256, 0, st>>>(scratch, bias, C, M, N, cs);
+      CB2_LAUNCH_CHECK();
+      return CB2_OK;
+    }
+    grid.z = 1;
   }
-  sgemm_kernel<B_NK><<<grid, kGemmThreads, 0, st>>>(A, Bm, scratch, M, N, K, kps);
+  sgemm_kernel<B_NK><<<grid, kGemmThreads, 0, st>>>(A, Bm, C, M, N, K, K);
   CB2_LAUNCH_CHECK();
-  const size_t mn = size_t(M) * N;
-  splitk_sum_kernel<<<unsigned((mn + 255) / 256), 256, 0, st>>>(scratch, bias, C, M, N, splits);
-  CB2_LAUNCH_CHECK();
+  if (bias) {
+    const size_t mn = size_t(M) * N;
+    add_bias_kernel<<<unsigned((mn + 255) / 256), 256, 0, st>>>(bias, C, M, N);
+    CB2_LAUNCH_CHECK();
+  }
   return CB2_OK;
 }
 
@@ -156,8 +307,11 @@ int gemm(const float* A, const float* Bm, const float* bias, float* C, int M, in
 
 extern "C" size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_features) {
   if (R <= 0 || in_features <= 0 || out_features <= 0) return 0;
+  // Split-K partials are normally reduced through distributed shared memory
+  // (clusters of up to 8 CTAs); the scratch is only used if a cluster launch is
+  // refused, and the call works without it.
   const int splits = cb2::pick_splits(R, out_features, in_features);
-  return splits > 1 ? size_t(splits) * R * out_features * sizeof(float) : 0;
+  return splits > 1 ? size_t(8) * R * out_features * sizeof(float) : 0;
 }
 
 extern "C" int cb2_linear_f32(const float* x, const float* w, const float* bias, float* y, int R,
@@ -168,8 +322,6 @@ extern "C" int cb2_linear_f32(const float* x, const float* w, const float* bias,
   if (cb2::linear_tf32x3_supported(x, w, bias, y, R, in_features, out_features))
     return cb2::linear_tf32x3_run(x, w, bias, y, R, in_features, out_features, nullptr,
                                   static_cast<cudaStream_t>(stream));
-  if (cb2_linear_f32_scratch_bytes(R, in_features, out_features) > 0 && !scratch)
-    return CB2_SCRATCH_TOO_SMALL;
   return cb2::gemm<true>(x, w, bias, y, R, out_features, in_features,
                          static_cast<float*>(scratch), scratch_bytes,
                          static_cast<cudaStream_t>(stream));

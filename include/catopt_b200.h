@@ -79,8 +79,11 @@ int cb2_verify_reduce(const void* ref, const void* out, int64_t numel_per_seg,
  * `linear(input, fused_N)` (packages/catopt-torch/src/catopt_torch/
  * torch_bridge.py:1251-1253):  y[R,out] = x[R,in] . w[out,in]^T  (+ bias[out]
  * when bias != NULL).  fp32 in, fp32 accumulate.
- * scratch: split-K partial sums, cb2_linear_f32_scratch_bytes(R,in,out) bytes
- * (may be 0, in which case scratch may be NULL).
+ * Large row counts (R >= 256, in/out multiples of 4, 16-byte aligned pointers)
+ * run on the tensor cores with three-pass TF32 splitting; small ones on the
+ * fp32 FMA pipes with the reduction axis split across a thread-block cluster.
+ * scratch: optional split-K partial sums (cb2_linear_f32_scratch_bytes bytes),
+ * used only if the cluster launch is refused; may be NULL.
  * ------------------------------------------------------------------------- */
 size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_features);
 int cb2_linear_f32(const float* x, const float* w, const float* bias, float* y,
