@@ -231,8 +231,11 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 // Used by cb2_linear_f32: large row counts with TMA-compatible strides.
 bool linear_tf32x3_supported(const float* x, const float* w, const float* bias, const float* y, int R,
                              int n_in, int n_out) {
-  return R >= 256 && n_in % 4 == 0 && n_out % 4 == 0 && aligned16(x) && aligned16(w) && aligned16(y) &&
-         (!bias || aligned16(bias));
+  // The tensor-core accumulator adds with truncation, a bias that grows with the
+  // reduction depth: measured rel-err 3e-6 at in=512, 5e-6 at 1024, 1.1e-5 at
+  // 2048.  Deeper reductions stay on the FMA pipes to keep the 1e-5 promise.
+  return R >= 256 && n_in <= 1024 && n_in % 4 == 0 && n_out % 4 == 0 && aligned16(x) && aligned16(w) &&
+         aligned16(y) && (!bias || aligned16(bias));
 }
 
 int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* y, int R, int n_in,

@@ -262,7 +262,7 @@ def test_scan_segment_composition_at_full_width(dev):
     assert rel_to_max(y[:1, :, :64], want_y) <= BF16_TOL
 
 
-def test_device_status_clean(dev):
+def test_device_status_clean_midway(dev):
     """No kernel in this file ran into a bounded-wait timeout."""
     from catopt_b200 import ops
 
@@ -284,3 +284,103 @@ def test_cuda_graph_replay_matches_eager(dev):
     assert torch.equal(mod(q2, k, v), mod._forward_impl(q2, k, v))
     mod.drop_cuda_graph()
     assert not mod.is_graph_captured
+
+
+# --------------------------------------------------------------------------- more edges
+@pytest.mark.parametrize("gam", [1.0, 0.5, 0.01, 1e-4])
+def test_decayed_bf16_extreme_rates(dev, gam):
+    """Rates from no decay to almost total decay on the tensor-core path; the
+    oracle is the spelled quadratic form (the reference's chunked form divides by
+    gamma^r and overflows for tiny rates)."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(31)
+    B, H, T, d = 1, 2, 384, 128
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(math.sqrt(d)).bfloat16() for _ in range(3))
+    gamma = torch.tensor([gam, gam], dtype=torch.float32)
+    want = oracle.decayed_quadratic(q.float(), k.float(), v.float(), gamma, 1.0)
+    out = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 128, 1.0)
+    assert torch.isfinite(out.float()).all()
+    assert rel_to_max(out, want) <= BF16_TOL
+
+
+def test_decayed_bf16_many_heads_and_scale(dev):
+    """More heads than SMs (several waves of CTAs) and a non-unit divisor."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(32)
+    B, H, T, d = 4, 80, 256, 128
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(math.sqrt(d)).bfloat16() for _ in range(3))
+    gamma = torch.linspace(0.9, 0.999, H)
+    out = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 128, 3.0).cpu()
+    for b, h in ((0, 0), (1, 17), (3, 79)):
+        want = oracle.decayed_state_carry(q[b:b + 1, h:h + 1].float(), k[b:b + 1, h:h + 1].float(),
+                                          v[b:b + 1, h:h + 1].float(), gamma[h:h + 1], 128, 3.0)
+        assert rel_to_max(out[b:b + 1, h:h + 1], want) <= BF16_TOL
+
+
+def test_decayed_bf16_long_sequence_state_accuracy(dev):
+    """T = 8192 (config 4's length, 64 chunks): the fp32 state in tensor memory
+    does not drift — compared against the fp64 state-carry recurrence."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(33)
+    B, H, T, d = 1, 2, 8192, 128
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(math.sqrt(d)).bfloat16() for _ in range(3))
+    gamma = torch.tensor([1 - 2.0 ** -5, 1 - 2.0 ** -12.75], dtype=torch.float32)
+    want = oracle.decayed_state_carry(q.double(), k.double(), v.double(), gamma.double(), 128, 1.0)
+    out = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 128, 1.0)
+    assert rel_to_max(out, want) <= BF16_TOL
+    assert rel_to_max(out[:, :, -128:], want[:, :, -128:]) <= BF16_TOL
+
+
+def test_verify_many_small_segments(dev):
+    """3328 segments (13 checks x 256 probes) of a few KiB each."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(34)
+    n_seg, n = 3328, 1536
+    ref = torch.randn(n_seg, n, generator=g).bfloat16()
+    out = (ref.float() + 0.01 * torch.randn(n_seg, n, generator=g)).bfloat16()
+    res = ops.verify_reduce(ref.to(dev), out.to(dev), n_seg).cpu()
+    want_abs = (ref - out).abs().amax(dim=1).float()
+    want_ref = ref.abs().amax(dim=1).float()
+    assert torch.equal(res[:, 0], want_abs) and torch.equal(res[:, 1], want_ref)
+    assert res[:, 2:].sum() == 0
+
+
+def test_scan_long_sequence(dev):
+    """T = 4096 (config 3's length) on a narrow slice, against the serial oracle."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(35)
+    B, T, D, N = 1, 4096, 32, 16
+    x = torch.randn(B, T, D, generator=g).bfloat16()
+    a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, N, generator=g)).bfloat16()
+    b = (torch.randn(D, N, generator=g) / 4).bfloat16()
+    c = (torch.randn(D, N, generator=g) / 4).bfloat16()
+    want_y, want_h = oracle.diag_scan_serial(a, x, b, c)
+    y, hT = ops.diag_scan_fwd(a.to(dev), x.to(dev), b.to(dev), c.to(dev), None, want_state=True)
+    assert rel_to_max(y, want_y) <= BF16_TOL
+    assert rel_to_max(hT, want_h) <= FP32_TOL
+
+
+@pytest.mark.parametrize("rows,n_in,n_out", [(256, 512, 512), (1000, 64, 1000), (300, 136, 72), (513, 1024, 128), (513, 2048, 128)])
+def test_linear_tensor_core_path(dev, rows, n_in, n_out):
+    """Shapes that take the three-pass TF32 kernel (ragged tiles, deep K, bias)."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + n_in)
+    x = torch.randn(rows, n_in, generator=g)
+    w = torch.randn(n_out, n_in, generator=g) / math.sqrt(n_in)
+    b = torch.randn(n_out, generator=g)
+    want = torch.nn.functional.linear(x.double(), w.double(), b.double())
+    got = ops.linear_f32(x.to(dev), w.to(dev), b.to(dev))
+    assert rel_to_max(got, want) <= FP32_TOL
+
+
+def test_device_status_clean(dev):
+    """No kernel in this file ran into a bounded-wait timeout."""
+    from catopt_b200 import ops
+
+    ops.check_device_status(dev)
