@@ -55,6 +55,11 @@ SIGNATURES: dict[str, tuple] = {
          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int,
          C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p],
     ),
+    "cb2_om_causal_fwd": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+         C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p],
+    ),
     "cb2_diag_scan_fwd": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

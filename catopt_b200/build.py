@@ -24,6 +24,7 @@ SOURCES = [
     "decayed_chunk_ffma.cu",
     "decayed_chunk_tc.cu",
     "decayed_chunk.cu",
+    "om_causal.cu",
 ]
 
 NVCC_FLAGS = [

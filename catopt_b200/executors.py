@@ -173,3 +173,23 @@ class B200DiagScan(_GraphMixin, torch.nn.Module):
 
     def _forward_impl(self, a: torch.Tensor, x: torch.Tensor, h0: torch.Tensor | None = None):
         return ops.diag_scan_fwd(a, x, self.b, self.c, h0, want_state=self.return_state)
+
+
+class B200CausalSoftmax(_GraphMixin, torch.nn.Module):
+    """Causal softmax attention evaluated block by block with the online-softmax
+    monoid — the value of the reference's ``BatchedOMModule`` / ``StreamingOMModule``
+    (catopt_carriers/om_lower.py:729-835, 996-1040) on a causal ``om`` carrier.
+    ``forward(q, k, v)`` on ``[B,H,T,d]`` tensors; ``scale=None`` means ``1/sqrt(d)``."""
+
+    def __init__(self, scale: float | None = None) -> None:
+        super().__init__()
+        self.scale = scale
+        self._plan: dict | None = {"kind": "om_causal", "scale": scale}
+        self._init_graph_state()
+
+    @property
+    def is_batched(self) -> bool:
+        return True
+
+    def _forward_impl(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        return ops.om_causal_fwd(q, k, v, self.scale)

@@ -166,6 +166,29 @@ def decayed_chunk_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: 
     return out
 
 
+# --------------------------------------------------------------------------- om causal
+def om_causal_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal softmax attention ``[B,H,Tq,dk] x [B,H,Tk,dk] x [B,H,Tk,dv]``; key j is
+    hidden from query t when j > t.  ``scale`` defaults to ``1/sqrt(dk)``."""
+    require_cuda(q, k, v, out)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise B200Error("om_causal_fwd takes rank-4 q, k, v")
+    B, H, Tq, dk = q.shape
+    if k.shape[:2] != (B, H) or k.shape[3] != dk or v.shape[:3] != k.shape[:3]:
+        raise B200Error("om_causal_fwd: q [B,H,Tq,dk], k [B,H,Tk,dk], v [B,H,Tk,dv]")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise B200Error("q, k, v must share one dtype")
+    Tk, dv = k.shape[2], v.shape[3]
+    if out is None:
+        out = torch.empty(B, H, Tq, dv, dtype=q.dtype, device=q.device)
+    sc = float(scale) if scale is not None else 1.0 / float(dk) ** 0.5
+    rc = _lib.load().cb2_om_causal_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                       B, H, Tq, Tk, dk, dv, sc, dtype_code(q.dtype), stream_ptr())
+    check(rc, "cb2_om_causal_fwd")
+    return out
+
+
 # --------------------------------------------------------------------------- scan
 def diag_scan_fwd(a: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
                   h0: torch.Tensor | None = None, want_state: bool = False,

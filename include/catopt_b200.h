@@ -171,6 +171,24 @@ int cb2_diag_scan_fwd(const void* a, const void* x, const void* b, const void* c
                       int N, int a_bcast_n, int dtype, int* dev_status,
                       void* stream);
 
+/* -------------------------------------------------------------------------
+ * (b') causal softmax attention through the online-softmax monoid,
+ *     o_t = sum_{j<=t} softmax_j(scale * q_t.k_j) v_j      per (batch, head).
+ * Replaces `BatchedOMModule._forward_impl` / `StreamingOMModule`
+ * (packages/catopt-carriers/src/catopt_carriers/om_lower.py:729-835, 996-1040)
+ * on the causal carrier: `om_apply` of an `om_compose` tree of `om_elem` blocks
+ * (torch_bridge.py:1974-2006, 1887-1890) whose scores carry the `cmask`
+ * strict-upper-triangle mask (om.py:1023-1029; key j hidden from query t when
+ * j > t, including the Tq = 1 case that sees only key 0).  Entirely masked
+ * blocks contribute 0; a row without any visible key yields NaN (0/0).
+ * q: [B,H,Tq,dk]; k: [B,H,Tk,dk]; v: [B,H,Tk,dv]; o: [B,H,Tq,dv]; dk,dv <= 128;
+ * `scale` multiplies the scores (the reference folds it into q).  dtype is the
+ * element type of all four tensors; arithmetic is fp32.
+ * ------------------------------------------------------------------------- */
+int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B,
+                      int H, int Tq, int Tk, int dk, int dv, float scale, int dtype,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

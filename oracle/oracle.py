@@ -186,6 +186,53 @@ def decayed_state_carry(q, k, v, gamma, chunk: int, scale: float = 1.0) -> torch
     return ((inner + cross) / scale).reshape(B, H, T, dv)
 
 
+# --------------------------------------------------------------------------- (b') om causal
+def om_elem(s, v):
+    """`_om_elem` (torch_bridge.py:1974-1981): (rowmax s, sum exp(s-m), exp(s-m) @ v)."""
+    m = s.amax(dim=-1, keepdim=True)
+    e = torch.exp(s - m)
+    return (m, e.sum(dim=-1, keepdim=True), e @ v)
+
+
+def om_compose(f, g):
+    """`_om_compose` (torch_bridge.py:1984-2006): the FlashAttention combine with
+    the isfinite guard for entirely masked blocks."""
+    m1, l1, a1 = f
+    m2, l2, a2 = g
+    mx = torch.maximum(m1, m2)
+    fin1, fin2 = torch.isfinite(m1), torch.isfinite(m2)
+    e1 = torch.where(fin1, torch.exp(m1 - mx), torch.zeros_like(mx))
+    e2 = torch.where(fin2, torch.exp(m2 - mx), torch.zeros_like(mx))
+    lv = torch.where(fin1, l1 * e1, torch.zeros_like(l1)) + torch.where(fin2, l2 * e2, torch.zeros_like(l2))
+    a = torch.where(fin1, a1 * e1, torch.zeros_like(a1)) + torch.where(fin2, a2 * e2, torch.zeros_like(a2))
+    return (mx, lv, a)
+
+
+def cmask(x: torch.Tensor, off: int = 0) -> torch.Tensor:
+    """`_cmask_torch` (catopt_carriers/om.py:1023-1029): True where key j+off > query t."""
+    t, k = x.shape[-2], x.shape[-1]
+    keep = torch.ones(t, k, dtype=torch.bool).tril(-off)
+    return keep.logical_not().expand(x.shape)
+
+
+def om_causal_chunked(q, k, v, sizes, scale: float | None = None):
+    """`om_apply` over a left fold of `om_elem` key blocks of the given sizes
+    (the streaming schedule of om_lower.py:996-1040): scale folded into q, each
+    block's scores masked with the causal mask shifted by the block offset,
+    read-out a / l (torch_bridge.py:1887-1890)."""
+    sc = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    qs = q * sc
+    state, off = None, 0
+    for n in sizes:
+        kb, vb = k[..., off:off + n, :], v[..., off:off + n, :]
+        s = qs @ kb.transpose(-1, -2)
+        s = s.masked_fill(cmask(s, off), float("-inf"))
+        el = om_elem(s, vb)
+        state = el if state is None else om_compose(state, el)
+        off += n
+    return state[2] / state[1]
+
+
 # --------------------------------------------------------------------------- (c) scan
 def affd_compose(f, g):
     """`affd_compose` binding (torch_bridge.py:1896-1899): f after g."""

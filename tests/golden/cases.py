@@ -77,6 +77,33 @@ def scan_inputs(name: str):
     return a.to(dtype), x.to(dtype), b.to(dtype), c.to(dtype), h0
 
 
+# name -> (B, H, Tq, Tk, dk, dv, key block sizes, scale)
+OM_CAUSAL_CASES = {
+    "two_blocks": (1, 1, 9, 9, 4, 5, [3, 6], None),
+    "three_uneven": (1, 1, 9, 9, 4, 5, [2, 3, 4], None),
+    "single_key_block": (1, 1, 9, 9, 4, 5, [1, 8], None),
+    "decode_row": (1, 1, 1, 7, 4, 5, [3, 4], None),
+    "custom_scale": (1, 1, 9, 9, 4, 5, [3, 6], 0.5),
+    "batched_heads": (2, 3, 12, 12, 8, 8, [4, 4, 4], None),
+    "wide": (2, 2, 200, 200, 64, 64, [64, 64, 72], None),
+    "more_queries_than_keys": (1, 2, 70, 40, 16, 24, [16, 24], None),
+}
+
+
+# fixtures of the large cases keep every n-th query row only
+OM_ROW_STRIDE = {"wide": 7}
+
+
+def om_causal_inputs(name: str):
+    """fp64 q, k, v ~ N(0,1) for a named causal-softmax case."""
+    B, H, Tq, Tk, dk, dv, sizes, scale = OM_CAUSAL_CASES[name]
+    g = rng(5000 + sorted(OM_CAUSAL_CASES).index(name))
+    q = torch.from_numpy(g.standard_normal((B, H, Tq, dk)))
+    k = torch.from_numpy(g.standard_normal((B, H, Tk, dk)))
+    v = torch.from_numpy(g.standard_normal((B, H, Tk, dv)))
+    return q, k, v, sizes, scale
+
+
 def verify_cases():
     """(name, ref, out, rtol, atol) pairs incl. the reference tests' edge cases."""
     g = rng(4000)

@@ -183,6 +183,37 @@ def gen_scan() -> None:
     np.savez_compressed(HERE / "scan.npz", **out)
 
 
+# --------------------------------------------------------------------------- om causal
+def gen_om_causal() -> None:
+    """Left fold of the reference's own `om_elem` / `om_compose` bindings over key
+    blocks masked with its `cmask` binding, read out as a / l; also dense sdpa."""
+    import math
+
+    from catopt_carriers.om import TORCH_BINDINGS as OMB
+    from catopt_torch.torch_bridge import _IR_TO_TORCH as BIND
+
+    out = {}
+    for name in cases.OM_CAUSAL_CASES:
+        q, k, v, sizes, scale = cases.om_causal_inputs(name)
+        sc = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        qs = q * sc
+        state, off = None, 0
+        for n in sizes:
+            s = qs @ k[..., off:off + n, :].transpose(-1, -2)
+            s = s.masked_fill(OMB["cmask"](s, off=off), float("-inf"))
+            el = BIND["om_elem"](s, v[..., off:off + n, :])
+            state = el if state is None else BIND["om_compose"](state, el)
+            off += n
+        o = BIND["om_apply"](state)
+        st = cases.OM_ROW_STRIDE.get(name, 1)
+        out[f"{name}.chunked"] = _np(o[..., ::st, :].contiguous())
+        if q.shape[-2] == k.shape[-2]:
+            dense = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, scale=sc)
+            out[f"{name}.sdpa"] = _np(dense[..., ::st, :].contiguous())
+            print(f"om_causal {name}: chunked-vs-sdpa {(o - dense).abs().max().item():.3e}")
+    np.savez_compressed(HERE / "om_causal.npz", **out)
+
+
 # --------------------------------------------------------------------------- verify
 def gen_verify() -> None:
     from catopt_torch.report import verify_equiv
@@ -209,6 +240,7 @@ if __name__ == "__main__":
     _add_reference(sys.argv[1])
     torch.manual_seed(0)
     only = set(sys.argv[2:])
-    for nm, fn in (("verify", gen_verify), ("scan", gen_scan), ("decayed", gen_decayed), ("chain", gen_chain)):
+    for nm, fn in (("verify", gen_verify), ("scan", gen_scan), ("om_causal", gen_om_causal),
+                   ("decayed", gen_decayed), ("chain", gen_chain)):
         if not only or nm in only:
             fn()

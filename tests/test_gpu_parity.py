@@ -379,6 +379,39 @@ def test_linear_tensor_core_path(dev, rows, n_in, n_out):
     assert rel_to_max(got, want) <= FP32_TOL
 
 
+# --------------------------------------------------------------------------- (b') om causal
+@pytest.mark.parametrize("name", list(cases.OM_CAUSAL_CASES))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_om_causal_vs_reference_fixture(dev, name, dtype):
+    from catopt_b200.executors import B200CausalSoftmax
+
+    g = np.load(GOLD / "om_causal.npz")
+    q, k, v, sizes, scale = cases.om_causal_inputs(name)
+    q, k, v = (t.to(dtype) for t in (q, k, v))
+    out = B200CausalSoftmax(scale).to(dev)(q.to(dev), k.to(dev), v.to(dev))
+    assert out.dtype == dtype
+    if dtype == torch.float32:
+        st = cases.OM_ROW_STRIDE.get(name, 1)
+        assert rel_to_max(out[..., ::st, :], torch.from_numpy(g[f"{name}.chunked"])) <= FP32_TOL
+    else:  # oracle on the bf16-rounded inputs
+        want = oracle.om_causal_chunked(q.double(), k.double(), v.double(), sizes, scale)
+        assert rel_to_max(out, want) <= BF16_TOL
+
+
+def test_om_causal_long_block_invariance(dev):
+    """T = 1000 (ragged against the 64-wide blocks), d = 128: equal to the oracle's
+    fold whatever block sizes the oracle uses."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(41)
+    q, k, v = (torch.randn(1, 2, 1000, 128, generator=g) for _ in range(3))
+    out = ops.om_causal_fwd(q.to(dev), k.to(dev), v.to(dev))
+    want = oracle.om_causal_chunked(q.double(), k.double(), v.double(), [300, 700])
+    assert rel_to_max(out, want) <= FP32_TOL
+    want2 = oracle.om_causal_chunked(q.double(), k.double(), v.double(), [1000])
+    assert rel_to_max(out, want2) <= FP32_TOL
+
+
 def test_device_status_clean(dev):
     """No kernel in this file ran into a bounded-wait timeout."""
     from catopt_b200 import ops

@@ -107,3 +107,21 @@ def test_scan_tree_and_prefix_forms(name):
     y, hT = oracle.diag_scan_serial(a, x, b, c, h0)
     assert (y - y_prefix).abs().max() <= 1e-5 * max(1.0, y.abs().max().item())
     assert (hT - hT_tree).abs().max() <= 1e-5 * max(1.0, hT.abs().max().item())
+
+
+# --------------------------------------------------------------------------- om causal
+@pytest.mark.parametrize("name", list(cases.OM_CAUSAL_CASES))
+def test_om_causal_oracle_bitwise_vs_reference_bindings(name):
+    g = _load("om_causal.npz")
+    q, k, v, sizes, scale = cases.om_causal_inputs(name)
+    o = oracle.om_causal_chunked(q, k, v, sizes, scale)[..., :: cases.OM_ROW_STRIDE.get(name, 1), :]
+    assert np.array_equal(o.numpy(), g[f"{name}.chunked"])
+    if f"{name}.sdpa" in g:
+        assert np.abs(o.numpy() - g[f"{name}.sdpa"]).max() < 1e-12
+
+
+def test_om_decode_row_sees_only_key_zero():
+    """T_q = 1: the causal mask hides every key but key 0 (reference behaviour)."""
+    q, k, v, sizes, scale = cases.om_causal_inputs("decode_row")
+    o = oracle.om_causal_chunked(q, k, v, sizes, scale)
+    assert torch.allclose(o[..., 0, :], v[..., 0, :], atol=1e-12)
