@@ -3,7 +3,7 @@
 catopt routes an extracted term to the first ``ExecutorSpec`` of
 ``Sink.executors`` whose ``carrier`` is not ``None`` and whose ``accepts(term)``
 is true (catopt_orchestrator/optimize.py:485-495); mapping order is routing
-order.  ``B200Sink`` puts two B200 specs in front of the torch ones:
+order.  ``B200Sink`` puts three B200 specs in front of the torch ones:
 
 * ``b200_om_decayed_chunked`` — the uniform K-chunk decayed term of
   ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152).  ``accepts``
@@ -14,6 +14,10 @@ order.  ``B200Sink`` puts two B200 specs in front of the torch ones:
   ``decay_vec(g, t=C, offset=(i-j)C)`` and column gate ``decay_vec(g, t=C,
   sign=-1)``, one constant scale.  Anything else is declined, so the reference's
   pairwise executor (or the generic module) still takes it.
+* ``b200_scan`` — diagonal ``applyd(<aff_diag tree>, h)`` scan applications (the
+  terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
+  leaf stacking are reused, the composed-map reduction runs in
+  ``cb2_diag_scan_fwd``.
 * ``b200_linear_chain`` — ``linear(x, <matmul tree of weight Params>)``, the
   term ``assoc_linear`` leaves behind for a chain of bias-free Linear maps
   (catopt_core/laws/tensor.py:1293-1300) before ``_fold_weight_chains``
@@ -40,7 +44,7 @@ from . import verify as b200_verify
 from ._lib import B200Error
 from .executors import _GraphMixin
 
-__all__ = ["B200Sink", "b200_backend", "decayed_state_carry_plan", "linear_chain_plan",
+__all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "linear_chain_plan", "scan_diag_plan",
            "B200ChunkedDecayModule", "B200LinearChainModule"]
 
 
@@ -265,6 +269,56 @@ class B200LinearChainModule(_EvalBase):
         return ops.linear_f32(x.contiguous(), self.fused_weight, self.bias)
 
 
+# --------------------------------------------------------------------------- scan
+def scan_diag_plan(root: Any) -> dict | None:
+    """The reference's scan plan (``build_scan_plan``, scan_lower.py:339-424)
+    when the term is a *diagonal* ``applyd(<aff_diag tree>, h)`` application."""
+    from catopt_carriers.scan_lower import build_scan_plan
+
+    plan = build_scan_plan(root)
+    return plan if plan is not None and plan.get("diagonal") else None
+
+
+def _make_scan_module():
+    from catopt_carriers.scan_lower import BatchedScanModule
+
+    class B200ScanModule(BatchedScanModule):
+        """``BatchedScanModule`` (scan_lower.py:427-807) with the composed-map
+        reduction replaced by ``cb2_diag_scan_fwd``.
+
+        Term analysis, leaf stacking and the re-application of stripped output
+        views stay the reference's own code; only the step that folds the leaf
+        maps over the initial state is swapped (the hook the reference's
+        ``fused=`` mode uses, ``_forward_fused``, scan_lower.py:785-807).  The
+        leaves arrive in product order (latest step first); the kernel runs them
+        chronologically as ``h <- a_t * h + u_t`` over the flattened state
+        (channels = state elements, N = 1, b = c = 1) and returns the final state.
+        fp64 tensors or state sizes the kernel cannot address degrade to the
+        reference's own eager reduction on the same device.
+        """
+
+        def __init__(self, ir: IR, param_values: dict | None = None) -> None:
+            super().__init__(ir, param_values, fused="eager")
+            self.kernel_calls = 0
+
+        def _forward_fused(self, a_vals, b_vals, ev):
+            plan = self._plan
+            if not plan["diagonal"]:
+                return super()._forward_fused(a_vals, b_vals, ev)
+            if not a_vals.is_cuda:
+                raise B200Error("B200ScanModule runs on CUDA tensors only (no CPU fallback)")
+            occ = self._occ_index(a_vals)
+            if occ is not None:
+                a_vals, b_vals = a_vals.index_select(0, occ), b_vals.index_select(0, occ)
+            out = ops.diag_compose_apply(a_vals, b_vals, ev(plan["h"]))
+            if out is None:   # fp64 / unaddressable state size: the reference's own reduction
+                return super()._forward_fused(a_vals, b_vals, ev)
+            self.kernel_calls += 1
+            return out
+
+    return B200ScanModule
+
+
 # --------------------------------------------------------------------------- sink
 def _engaged(m: Any) -> bool:
     return bool(getattr(m, "is_batched", False))
@@ -285,6 +339,13 @@ class B200Sink(TorchSink):
                     (frozenset({"concat"}), frozenset({"add", "mul", "div", "matmul"}),
                      frozenset({"om_decayed", "decay", "decay_vec"})),
                 ),
+                "b200_scan": ExecutorSpec(
+                    "b200_scan",
+                    lambda ir, p: _make_scan_module()(ir, param_values=p),
+                    lambda term: scan_diag_plan(term) is not None,
+                    _engaged,
+                    (frozenset({"applyd"}), frozenset({"affd_compose"}), frozenset({"aff_diag"})),
+                ),
                 "b200_linear_chain": ExecutorSpec(
                     "b200_linear_chain",
                     lambda ir, p: B200LinearChainModule(ir, param_values=p),
@@ -299,6 +360,17 @@ class B200Sink(TorchSink):
 
     def verify(self, ref: Any, opt: Any, inputs: Any, *, rtol: float = 1e-4, atol: float | None = None):
         return b200_verify.verify_module(ref, opt, inputs, rtol=rtol, atol=atol)
+
+
+def b200_target_profile():
+    """The measured B200 ``TargetProfile`` shipped with this package
+    (catopt_core/profile.py:75-150), for catopt's roofline cost model:
+    ``roofline_cost_for(b200_target_profile())``."""
+    from pathlib import Path
+
+    from catopt_core.profile import TargetProfile
+
+    return TargetProfile.from_json((Path(__file__).with_name("target_profile_b200.json")).read_text())
 
 
 def b200_backend():

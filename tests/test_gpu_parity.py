@@ -379,6 +379,24 @@ def test_linear_tensor_core_path(dev, rows, n_in, n_out):
     assert rel_to_max(got, want) <= FP32_TOL
 
 
+@pytest.mark.parametrize("n,state", [(6, (8,)), (37, (2, 12)), (128, (4, 4, 4)), (5, (3,))])
+def test_scan_composed_map_vs_reference_tree(dev, n, state):
+    """The reduction the catopt scan adapter swaps in: leaves in product order,
+    compared with the reference's level-batched `fused_diag_levels`."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(n)
+    a = torch.sigmoid(3 + torch.randn(n, *state, generator=g))
+    b = torch.randn(n, *state, generator=g)
+    h = torch.randn(*state, generator=g)
+    want = oracle.fused_diag_levels(a, b, h)
+    got = ops.diag_compose_apply(a.to(dev), b.to(dev), h.to(dev))
+    if (math.prod(state) * 4) % 16:
+        assert got is None            # not addressable by the kernel: caller keeps its reduction
+    else:
+        assert rel_to_max(got, want) <= FP32_TOL
+
+
 # --------------------------------------------------------------------------- (b') om causal
 @pytest.mark.parametrize("name", list(cases.OM_CAUSAL_CASES))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -32,7 +32,7 @@ def _route(sink, term):
 def test_b200_specs_come_first_and_are_executor_specs():
     s = b200.B200Sink()
     names = list(s.executors)
-    assert names[:2] == ["b200_om_decayed_chunked", "b200_linear_chain"]
+    assert names[:3] == ["b200_om_decayed_chunked", "b200_scan", "b200_linear_chain"]
     assert "om_decayed_chunked" in names and names[-1] == "generic"
     assert all(isinstance(v, ExecutorSpec) for v in s.executors.values())
 
@@ -106,3 +106,40 @@ def test_non_matching_ir_degrades_to_eval_mod():
     assert not mod.is_batched and mod.n_blocks == 0
     t = torch.ones(2, 3)
     assert torch.equal(mod(t), t + t)
+
+
+def _scan_term(T=6, d=8):
+    """applyd(affd_compose(... aff_diag(a_t, select(u, 0, t)) ...), h) over T steps."""
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    u = Var("u", tt(T, d))
+    a = Param("a", tt(d))
+    h = Param("h0", tt(d))
+    leaf = lambda t: Op.make("aff_diag", a, Op.make("select", u, dim=0, index=t))  # noqa: E731
+    tree = leaf(T - 1)                      # latest step outermost
+    for t in range(T - 2, -1, -1):
+        tree = Op.make("affd_compose", tree, leaf(t))
+    root = Op.make("applyd", tree, h)
+    ir = IR(root=root, inputs=[u], input_names={"u"}, params={"a": a, "h0": h})
+    return ir
+
+
+def test_scan_term_routes_to_b200_scan_and_keeps_reference_plan():
+    ir = _scan_term()
+    s = b200.B200Sink()
+    assert list(s.executors)[:3] == ["b200_om_decayed_chunked", "b200_scan", "b200_linear_chain"]
+    spec = _route(s, ir.root)
+    assert spec.name == "b200_scan"
+    vals = {"a": torch.full((8,), 0.9), "h0": torch.ones(8)}
+    mod = spec.lower(ir, vals)
+    assert isinstance(mod, BatchedExecutor) and spec.engaged(mod) and mod._plan["diagonal"]
+    from catopt_b200 import B200Error
+
+    with pytest.raises(B200Error):      # the kernel path refuses host tensors
+        mod(torch.randn(6, 8))
+
+
+def test_b200_target_profile_prices_with_the_reference_cost_model():
+    prof = b200.b200_target_profile()
+    assert prof.gbps > 6000 and prof.tflops > 50 and prof.name.startswith("b200")
+    cost = prof.cost_fn()
+    assert callable(cost)
