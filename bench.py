@@ -323,9 +323,13 @@ def run_ours(args) -> None:
     rank, local, world = dist_info()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # Keep stdout for the ONE JSON line: anything libraries print on fd 1 (NCCL's
+    # version banner, for one) is sent to stderr; the line is written to the saved
+    # descriptor at the end.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        # keep stdout for the one JSON line: NCCL's own banner/debug output goes to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         torch.distributed.init_process_group("nccl", device_id=dev)
     from catopt_b200 import _lib, build, ops
     from catopt_b200.host_api import DecayedHostPipeline
@@ -403,7 +407,8 @@ def run_ours(args) -> None:
     }
     if cpu:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    os.write(json_fd, (json.dumps(line) + "\n").encode())
 
 
 def run_profile_case(args) -> None:

@@ -1,6 +1,7 @@
 // C-ABI front of the chunked decayed-attention executor: argument checks and
-// the choice between the tensor-core kernel (bf16, chunk = dk = dv = 128 or 64,
-// state kept on chip) and the fp32 FMA path (everything else, state in scratch).
+// the choice between the tensor-core kernel (bf16, dk and dv up to 128, T a
+// multiple of 128; state kept on chip) and the fp32 FMA path (everything else,
+// state in scratch).
 #include "common.cuh"
 
 namespace cb2 {

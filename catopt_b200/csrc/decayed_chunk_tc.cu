@@ -1,6 +1,10 @@
 // Chunked decayed attention on the 5th-generation tensor cores (bf16 tensors,
-// chunk = dk = dv = 128): one CTA per (batch, head) walks the chunks in order
-// and keeps the fp32 inter-chunk state in tensor memory for the whole sequence.
+// dk, dv <= 128, T a multiple of 128): one CTA per (batch, head) walks 128-row
+// chunks in order and keeps the fp32 inter-chunk state in tensor memory for the
+// whole sequence.  The value does not depend on the chunking, so the kernel
+// always uses 128-row chunks whatever chunk size the lowered term was cut into;
+// head dimensions below 128 are zero-padded for free by the TMA (columns past
+// dk / dv are out of range of the tensor map and arrive as zeros).
 //
 // Per chunk i (C = 128 rows, g = gamma of the head):
 //   MMA1  S  = Q_i K_i^T                                  (TMEM cols   0..127)
@@ -78,7 +82,7 @@ struct Bars {
 __global__ void __launch_bounds__(kThreads, 1)
 decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                  const float* __restrict__ gamma, int H, int T, float inv_scale, int* dev_status) {
+                  const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
   // __shared__ array keeps every access a shared-space (LDS/STS) access
@@ -325,7 +329,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (tid == 64) {  // whole tile written: two {64 x 128} boxes go out asynchronously
         const int row = bh * T + i * kC;
         umma::tma_store_2d(&map_o, 0, row, o_tile);
-        umma::tma_store_2d(&map_o, 64, row, o_tile + umma::kSubTileBytes);
+        if (dv > 64) umma::tma_store_2d(&map_o, 64, row, o_tile + umma::kSubTileBytes);
         bulk_commit();
       }
       CB2_TL(i, 5);
@@ -381,25 +385,26 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
 bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype) {
   // TMA row coordinates are 32-bit signed
-  return dtype == CB2_BF16 && dk == kC && dv == kC && C == kC && T % kC == 0 && T >= kC &&
-         int64_t(B) * H * T < (int64_t(1) << 31);
+  (void)C;  // the result is independent of the chunk size: 128-row chunks are used
+  return dtype == CB2_BF16 && dk >= 8 && dk <= kC && dk % 8 == 0 && dv >= 8 && dv <= kC && dv % 8 == 0 &&
+         T % kC == 0 && T >= kC && int64_t(B) * H * T < (int64_t(1) << 31);
 }
 
 int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
                    int H, int T, int dk, int dv, int C, float scale, int* dev_status, cudaStream_t st) {
-  (void)dk; (void)dv; (void)C;
+  (void)C;
   const uint64_t rows = uint64_t(B) * H * T;
   CUtensorMap mq, mk, mv, mo;
-  int rc = umma::make_tile_map(&mq, q, rows, kC);
-  if (rc == CB2_OK) rc = umma::make_tile_map(&mk, k, rows, kC);
-  if (rc == CB2_OK) rc = umma::make_tile_map(&mv, v, rows, kC);
-  if (rc == CB2_OK) rc = umma::make_tile_map(&mo, o, rows, kC);
+  int rc = umma::make_tile_map(&mq, q, rows, dk);
+  if (rc == CB2_OK) rc = umma::make_tile_map(&mk, k, rows, dk);
+  if (rc == CB2_OK) rc = umma::make_tile_map(&mv, v, rows, dv);
+  if (rc == CB2_OK) rc = umma::make_tile_map(&mo, o, rows, dv);
   if (rc != CB2_OK) return rc;
   // per device, so set on every call (cheap) rather than cached per process
   if (cudaFuncSetAttribute(decayed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
-  decayed_tc_kernel<<<B * H, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, 1.0f / scale,
+  decayed_tc_kernel<<<B * H, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
                                                         dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;

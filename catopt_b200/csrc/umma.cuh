@@ -162,8 +162,9 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
-// ---- host: tensor map for a row-major [rows x 128] bf16 matrix ---------------
-// Box {64 columns, 128 rows}, 128-byte swizzle.  Uses the driver entry point
+// ---- host: tensor map for a row-major [rows x cols] bf16 matrix (cols <= 128) --
+// Box {64 columns, 128 rows}, 128-byte swizzle; a box that reaches past `cols`
+// is filled with zeros on load and clipped on store.  Uses the driver entry point
 // through the runtime so the library does not link libcuda.
 inline int make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols) {
   using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

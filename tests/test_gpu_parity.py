@@ -165,7 +165,8 @@ def test_decayed_f64_case_in_fp32(dev):
 
 
 @pytest.mark.parametrize("B,H,T,d,C", [(1, 2, 512, 128, 128), (2, 3, 256, 64, 64), (1, 1, 128, 128, 128),
-                                       (1, 2, 96, 32, 32)])
+                                       (1, 2, 96, 32, 32), (2, 2, 1024, 64, 64), (1, 3, 384, 16, 32),
+                                       (1, 2, 256, 96, 128), (1, 1, 256, 8, 64)])
 def test_decayed_bf16_vs_oracle(dev, B, H, T, d, C):
     """bf16 tensors: the oracle runs the reference's pairwise executor in fp32 on
     the bf16-rounded inputs (a pure-bf16 reference run is unusable: gamma_h
