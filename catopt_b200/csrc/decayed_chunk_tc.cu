@@ -13,7 +13,7 @@
 //   MMA3  O2 = Q_i Sb_i        (Sb_i = bf16 copy of the state, i > 0)   (256..383)
 //   WG    o_i = (O1 + g^(r+1) O2) / scale  -> staged in shared memory, TMA store
 //   MMA4  St = [g^C St] + Kw_i^T V_i                       (TMEM cols 384..511)
-//   WG    Sb_{i+1} = bf16(St) -> smem ;  St <- g^C St  (ready for the next MMA4)
+//   WG    (during the next chunk's MMA2)  Sb_{i+1} = bf16(St) -> smem ;  St <- g^C St
 // which is the state-carry recurrence the reference spells in
 // lab/probes/retnet_baseline_probe.py:77-110 and equals its pairwise executor
 // (decayed_lower.py:671-700) up to reassociation.  Only chunk-local powers of g
@@ -273,6 +273,36 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       umma::fence_before_sync();
       mbar_arrive(B.p_ready);
       CB2_TL(i, 2);
+      // (d) state pass of the previous chunk, placed here so that it runs while
+      // MMA2 (P.V) of this chunk executes and MMA3 (Q.Sb) can follow it directly:
+      // Sb_i = bf16(St);  St <- g^C St  (ready for this chunk's MMA4)
+      if (i > 0) {
+        ok = mbar_wait_abortable(B.st_ready, (i - 1) & 1, s_abort);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        umma::fence_after_sync();
+        CB2_TL(i, 6);
+        const int cb0 = half * 2;
+        umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
+        umma::tmem_ld32(lane_base + kColSt + cb0 * 32 + 32, vb);
+        umma::tmem_wait_ld();
+        auto state_block = [&](int cb, uint32_t (&v)[32]) {
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2)
+            w[j >> 1] = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+          store_block(sb_tile, cb * 32, w);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g_chunk);
+          umma::tmem_st32(lane_base + kColSt + cb * 32, v);
+        };
+        state_block(cb0, va);
+        state_block(cb0 + 1, vb);
+        umma::tmem_wait_st();
+        umma::fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(B.sb_ready);
+        CB2_TL(i, 7);
+      }
       // (b) K_i <- K_i . g^(C-1-r), in place (MMA1 has finished reading it);
       // this thread owns the 8 chunks of row r that lie in its column half.
       {
@@ -333,34 +363,6 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         bulk_commit();
       }
       CB2_TL(i, 5);
-      // (d) Sb_{i+1} = bf16(St);  St <- g^C St
-      if (i + 1 < nchunk) {
-        ok = mbar_wait_abortable(B.st_ready, ph, s_abort);
-        if (!__all_sync(0xffffffffu, ok)) break;
-        umma::fence_after_sync();
-        CB2_TL(i, 6);
-        const int cb0 = half * 2;
-        umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
-        umma::tmem_ld32(lane_base + kColSt + cb0 * 32 + 32, vb);
-        umma::tmem_wait_ld();
-        auto state_block = [&](int cb, uint32_t (&v)[32]) {
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2)
-            w[j >> 1] = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-          store_block(sb_tile, cb * 32, w);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g_chunk);
-          umma::tmem_st32(lane_base + kColSt + cb * 32, v);
-        };
-        state_block(cb0, va);
-        state_block(cb0 + 1, vb);
-        umma::tmem_wait_st();
-        umma::fence_before_sync();
-        fence_proxy_async_smem();
-        mbar_arrive(B.sb_ready);
-        CB2_TL(i, 7);
-      }
     }
     if (tid == 64) bulk_wait_all<0>();  // the staged output has left shared memory
   }
