@@ -3,7 +3,7 @@
     python bench.py --gpus N --steps K --warmup W            # this repo's CUDA path
     python bench.py --impl reference --steps K --warmup W    # the reference algorithm on host cores
 
-Headline workload (``config.workload``): BASELINE config 4, decayed causal linear
+Headline workload (``config.workload``): benchmark config 4, decayed causal linear
 attention B=16 H=32 T=8192 d=128 bf16, per-head gamma, chunk 128 — per GPU; at
 N>1 every rank owns its own contiguous range of the flattened batch x head axis
 of a global batch of 16*N (weak scaling, no collective on the path).  A "token"

@@ -10,7 +10,7 @@
 // NaN, like dense softmax.
 //
 // fp32 arithmetic on the FMA pipes for both element types (correctness-first
-// kernel: no BASELINE configuration measures this executor).  CTA = 64 queries
+// kernel: no benchmark configuration measures this executor).  CTA = 64 queries
 // of one (batch, head); key blocks of 64 up to the diagonal; each thread owns a
 // 4x4 patch of the 64x64 score block and 4 x (dv/16) output accumulators.
 #include "common.cuh"

@@ -13,9 +13,9 @@ DECAYED_CASES = {
     "tiny_f64": (2, 2, 32, 8, 8, torch.float64, True, 1.0),
     "tiny_f32_scalar": (2, 3, 48, 16, 16, torch.float32, False, 2.0),
     "odd_f32": (1, 2, 96, 32, 32, torch.float32, True, 1.0),
-    # BASELINE config 2 (full size); the fixture keeps every 37th time step.
+    # benchmark config 2 (full size); the fixture keeps every 37th time step.
     "c2_f32": (2, 4, 1024, 64, 64, torch.float32, False, 1.0),
-    # two heads of BASELINE config 4's shape, bf16-rounded inputs, fp32 arithmetic
+    # two heads of benchmark config 4's shape, bf16-rounded inputs, fp32 arithmetic
     "c4_slice": (1, 2, 512, 128, 128, torch.float32, True, 1.0),
 }
 # fixtures of the large cases keep every n-th time step only

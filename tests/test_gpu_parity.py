@@ -75,7 +75,7 @@ def test_verify_batched_vs_oracle(dev, dtype, shape):
 
 
 def test_verify_full_probe_size_properties(dev):
-    """BASELINE config 5's tensor size ([4,512,1024] bf16 per probe, 8 probes x 3
+    """Benchmark config 5's tensor size ([4,512,1024] bf16 per probe, 8 probes x 3
     checks here): planted maxima are found exactly; untouched checks report 0."""
     from catopt_b200 import ops
 

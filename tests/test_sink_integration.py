@@ -7,7 +7,8 @@ import sys
 import pytest
 import torch
 
-_REF = os.environ.get("CATOPT_SRC", "/root/reference")
+# catopt's source tree: $CATOPT_SRC, else a "reference" checkout next to this repository
+_REF = os.environ.get("CATOPT_SRC") or os.path.join(os.path.dirname(__file__), "..", "..", "reference")
 for _p in glob.glob(os.path.join(_REF, "packages", "*", "src")):
     if _p not in sys.path:
         sys.path.insert(0, _p)
