@@ -296,6 +296,16 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
                                           traffic_key="diag_scan")
     del a3, x3, y3
 
+    # causal online-softmax executor (no config of its own in the benchmark spec): B=2 H=8 T=2048 d=128 bf16
+    qo, ko, vo = (_randn_bf16((16, 2048 * 128), gen).view(2, 8, 2048, 128) for _ in range(3))
+    oo = torch.empty_like(vo)
+    ms = time_steps(lambda: ops.om_causal_fwd(qo, ko, vo, out=oo), K, W, world, flush)
+    e = entry(ms, 2 * 2048, 4 * 16 * 2048 * 128 * 2, 1, "fp32 FMA kernel (parity build); compute-bound",
+              flops=4 * 16 * (2048 * 2049 // 2) * 128)
+    e["roofline"]["bound"] = "tensor"
+    out["om_causal_bf16_B2_H8_T2048_d128"] = e
+    del qo, ko, vo, oo
+
     # config 5: verify 13 checks x 256 probes x [4,512,1024] bf16; probes sharded over ranks
     p0, p1 = shard_range(256, rank, world)
     probes = p1 - p0
