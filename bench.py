@@ -294,7 +294,15 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     out["config3_diag_scan_bf16"] = entry(ms, B * T, (B * T * D * (N + 2) + 2 * D * N) * 2, 1,
                                           "inputs 1.2 GB exceed L2", flops=5 * B * T * D * N,
                                           traffic_key="diag_scan")
-    del a3, x3, y3
+    # config 3 with the decay shared over n (a is [B,T,D]): 201 MB
+    a3s = torch.empty(B, T, D, dtype=torch.bfloat16, device=dev)
+    for b in range(B):
+        a3s[b].copy_(torch.sigmoid(4 + 0.5 * torch.randn(T, D, device=dev, generator=gen)))
+    ms = time_steps(lambda: ops.diag_scan_fwd(a3s, x3, b3, c3, None, out=y3), K, W, world)
+    out["config3_shared_decay_bf16"] = entry(ms, B * T, (3 * B * T * D + 2 * D * N) * 2, 1,
+                                             "a broadcast over n: collapsed scalar recurrence; 201 MB exceed L2",
+                                             flops=4 * B * T * D)
+    del a3, a3s, x3, y3
 
     # causal online-softmax executor (no config of its own in the benchmark spec): B=2 H=8 T=2048 d=128 bf16
     qo, ko, vo = (_randn_bf16((16, 2048 * 128), gen).view(2, 8, 2048, 128) for _ in range(3))

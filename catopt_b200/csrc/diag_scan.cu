@@ -466,7 +466,199 @@ inline int scan_npt() {
   return v;
 }
 
-// `a` shared over n ([B,T,D]): one thread per (b, channel) keeps all N states.
+// ---------------------------------------------------------------------------
+// `a` shared over n ([B,T,D]), fast path (D a multiple of 32).  With one decay
+// per channel the N states are all multiples of ONE scalar recurrence:
+//   h_t[n] = b[n] * G_t + P_t * h0[n],   G_t = a_t G_{t-1} + x_t,   P_t = a_t P_{t-1}
+// so  y_t = (sum_n c[n] b[n]) * G_t + (sum_n c[n] h0[n]) * P_t  needs a few FMAs
+// per step instead of 2N.  Traffic is a, x, y only (6 bytes of bf16 per (b,t,d)).
+//
+// Only B*D/32 warps' worth of channels exist, too few to hide latency, so the
+// T axis is cut into 64-step tiles dealt round-robin to the four consumer warps
+// of a CTA (lane = channel).  A warp first runs its tile from the identity
+// (local G_t, P_t kept in registers), then receives the carry (G, P) at the
+// tile's start from the owner of the previous tile through shared memory and an
+// mbarrier, publishes its own carry-out with two FMAs — the only serial step —
+// and finally corrects and stores its 64 outputs.  A producer warp streams the
+// a / x tiles through an 8-stage ring with tiled TMA and stores the y tiles.
+// ---------------------------------------------------------------------------
+template <int DTYPE>
+struct SharedACfg {
+  static constexpr int kEsz = Elem<DTYPE>::kSize;
+  static constexpr int kCh = 32;
+  static constexpr int kRows = 64;
+  static constexpr int kWarps = 4;                          // consumer warps = tiles in flight
+  static constexpr int kYBufs = 8;                          // y staging tiles (two per consumer warp)
+  static constexpr int kStages = 8;
+  static constexpr int kThreads = (kWarps + 1) * 32;
+  static constexpr int kTileBytes = kRows * kCh * kEsz;     // one operand, one tile
+  static constexpr int kStageBytes = 2 * kTileBytes;        // a | x
+  static constexpr int kNumBars = 2 * kStages + kYBufs + kWarps;
+  static constexpr int kSmem = kStages * kStageBytes + kYBufs * kTileBytes + kWarps * 2 * kCh * 4 +
+                               kNumBars * 8 + 16 + 128;
+};
+
+template <int DTYPE>
+__global__ void __launch_bounds__(SharedACfg<DTYPE>::kThreads)
+diag_scan_shared_a_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_x,
+                          const __grid_constant__ CUtensorMap map_y, const void* __restrict__ bvec,
+                          const void* __restrict__ cvec, const float* __restrict__ h0,
+                          float* __restrict__ hT, int T, int D, int N, int* dev_status) {
+  using C = SharedACfg<DTYPE>;
+  using E = Elem<DTYPE>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* s_stage = smem;
+  unsigned char* s_y = smem + C::kStages * C::kStageBytes;                    // kYBufs staging tiles
+  float* s_carry = reinterpret_cast<float*>(s_y + C::kYBufs * C::kTileBytes); // [kWarps][2][32]
+  uint64_t* s_full = reinterpret_cast<uint64_t*>(s_carry + C::kWarps * 2 * C::kCh);
+  uint64_t* s_empty = s_full + C::kStages;
+  uint64_t* s_yfree = s_empty + C::kStages;     // [kYBufs] producer -> consumers: staging tile reusable
+  uint64_t* s_cbar = s_yfree + C::kYBufs;       // [kWarps] carry of warp w published
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_cbar + C::kWarps);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int blocks_per_b = D / C::kCh;
+  const int b = blockIdx.x / blocks_per_b;
+  const int d0 = (blockIdx.x % blocks_per_b) * C::kCh;
+  const int ntiles = (T + C::kRows - 1) / C::kRows;
+  constexpr int kPitch = C::kCh * C::kEsz;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 32);
+    }
+    for (int w = 0; w < C::kYBufs; ++w) mbar_init(&s_yfree[w], 1);
+    for (int w = 0; w < C::kWarps; ++w) mbar_init(&s_cbar[w], 32);
+    *s_abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == C::kWarps) {
+    if (lane == 0) {  // producer
+      umma::tma_prefetch_desc(&map_a);
+      umma::tma_prefetch_desc(&map_x);
+      umma::tma_prefetch_desc(&map_y);
+      auto issue_tile = [&](int tile) {
+        const int s = tile % C::kStages;
+        unsigned char* st = s_stage + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&s_full[s], C::kStageBytes);
+        umma::tma_load_3d(st, &map_a, d0, tile * C::kRows, b, &s_full[s]);
+        umma::tma_load_3d(st + C::kTileBytes, &map_x, d0, tile * C::kRows, b, &s_full[s]);
+      };
+      for (int i = 0; i < C::kStages && i < ntiles; ++i) issue_tile(i);
+      for (int tile = 0; tile < ntiles; ++tile) {
+        const int s = tile % C::kStages;
+        if (!mbar_wait_abortable(&s_empty[s], (tile / C::kStages) & 1, s_abort)) break;
+        umma::tma_store_3d(&map_y, d0, tile * C::kRows, b, s_y + (tile % C::kYBufs) * C::kTileBytes);
+        bulk_commit();
+        if (tile + C::kStages < ntiles) issue_tile(tile + C::kStages);
+        // all but the newest 3 stores have left their staging tiles; a tile is reused
+        // kYBufs tiles later, so consumers never wait on a neighbour's store
+        bulk_wait_read<3>();
+        if (tile >= 3) mbar_arrive(&s_yfree[(tile - 3) % C::kYBufs]);
+      }
+      bulk_wait_all<0>();
+      if (*s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+    }
+    return;
+  }
+
+  // consumer warps: lane = channel, warp w owns tiles w, w + kWarps, ...
+  const int d = d0 + lane;
+  float cb = 0.f, ch0 = 0.f;
+  for (int n = 0; n < N; ++n) {
+    const float cn = E::ld(cvec, d * N + n);
+    cb = fmaf(cn, E::ld(bvec, d * N + n), cb);
+    if (h0) ch0 = fmaf(cn, h0[(size_t(b) * D + d) * N + n], ch0);
+  }
+  const int prev = (warp + C::kWarps - 1) % C::kWarps;
+  float g_end = 0.f, p_end = 1.f;   // carry after this warp's latest tile
+  for (int tile = warp, round = 0; tile < ntiles; tile += C::kWarps, ++round) {
+    const int s = tile % C::kStages;
+    const int rows = min(C::kRows, T - tile * C::kRows);
+    bool ok = mbar_wait_abortable(&s_full[s], (tile / C::kStages) & 1, s_abort);
+    if (!__all_sync(0xffffffffu, ok)) return;
+    const unsigned char* sa = s_stage + s * C::kStageBytes + lane * C::kEsz;
+    const unsigned char* sx = sa + C::kTileBytes;
+    // pass 1: the tile from the identity; rows past T act as the identity map (a=1, x=0)
+    float gl[C::kRows], pl[C::kRows];
+    float g = 0.f, p = 1.f;
+#pragma unroll
+    for (int r0 = 0; r0 < C::kRows; r0 += 8) {
+      float av[8], xv[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const bool in = r0 + q < rows;
+        av[q] = in ? E::ld(sa + (r0 + q) * kPitch, 0) : 1.f;
+        xv[q] = in ? E::ld(sx + (r0 + q) * kPitch, 0) : 0.f;
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        g = fmaf(av[q], g, xv[q]);
+        p *= av[q];
+        gl[r0 + q] = g;
+        pl[r0 + q] = p;
+      }
+    }
+    // carry-in from the owner of the previous tile
+    float g_in = 0.f, p_in = 1.f;
+    if (tile > 0) {
+      const int pr = warp == 0 ? round - 1 : round;   // round in which `prev` published it
+      ok = mbar_wait_abortable(&s_cbar[prev], pr & 1, s_abort);
+      if (!__all_sync(0xffffffffu, ok)) return;
+      g_in = s_carry[(prev * 2 + 0) * C::kCh + lane];
+      p_in = s_carry[(prev * 2 + 1) * C::kCh + lane];
+    }
+    g_end = fmaf(pl[C::kRows - 1], g_in, gl[C::kRows - 1]);
+    p_end = pl[C::kRows - 1] * p_in;
+    s_carry[(warp * 2 + 0) * C::kCh + lane] = g_end;
+    s_carry[(warp * 2 + 1) * C::kCh + lane] = p_end;
+    mbar_arrive(&s_cbar[warp]);  // release: the next tile's owner may go on
+    // pass 2: corrected outputs into this warp's staging tile
+    if (tile >= C::kYBufs) {
+      ok = mbar_wait_abortable(&s_yfree[tile % C::kYBufs], ((tile / C::kYBufs) - 1) & 1, s_abort);
+      if (!__all_sync(0xffffffffu, ok)) return;
+    }
+    unsigned char* sy = s_y + (tile % C::kYBufs) * C::kTileBytes;
+    const float cg = cb * g_in, cp = ch0 * p_in;
+#pragma unroll
+    for (int r = 0; r < C::kRows; ++r) {
+      // y = cb*(gl + pl*g_in) + ch0*(pl*p_in)
+      const float yv = fmaf(cb, gl[r], pl[r] * (cg + cp));
+      E::st(sy + r * kPitch, lane, yv);
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(&s_empty[s]);
+  }
+  // the owner of the last tile holds the final carry
+  if (hT && warp == (ntiles - 1) % C::kWarps) {
+    for (int n = 0; n < N; ++n) {
+      const size_t i = (size_t(b) * D + d) * N + n;
+      hT[i] = fmaf(E::ld(bvec, d * N + n), g_end, h0 ? p_end * h0[i] : 0.f);
+    }
+  }
+}
+
+template <int DTYPE>
+int launch_scan_shared_a(const void* a, const void* x, const void* b, const void* c, const float* h0,
+                         void* y, float* hT, int B, int T, int D, int N, int* dev_status, cudaStream_t st) {
+  using C = SharedACfg<DTYPE>;
+  CUtensorMap ma, mx, my;
+  const bool bf = DTYPE == CB2_BF16;
+  int rc = umma::make_map_3d(&ma, a, bf, D, T, B, C::kCh, C::kRows);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mx, x, bf, D, T, B, C::kCh, C::kRows);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&my, y, bf, D, T, B, C::kCh, C::kRows);
+  if (rc != CB2_OK) return rc;
+  auto kern = diag_scan_shared_a_kernel<DTYPE>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+    return CB2_LAUNCH_FAIL;
+  kern<<<B * (D / C::kCh), C::kThreads, C::kSmem, st>>>(ma, mx, my, b, c, h0, hT, T, D, N, dev_status);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
+// `a` shared over n, generic path: one thread per (b, channel) keeps all N states.
 template <int DTYPE, int N>
 __global__ void __launch_bounds__(128)
 diag_scan_bcast_kernel(const void* __restrict__ a, const void* __restrict__ x,
@@ -509,6 +701,8 @@ int launch_scan(const void* a, const void* x, const void* b, const void* c, cons
                 cudaStream_t st) {
   using C = ScanCfg<DTYPE, N>;
   if (a_bcast_n) {
+    if (D % 32 == 0 && aligned16(a) && aligned16(x) && aligned16(y))
+      return launch_scan_shared_a<DTYPE>(a, x, b, c, h0, y, hT, B, T, D, N, dev_status, st);
     const int total = B * D;
     diag_scan_bcast_kernel<DTYPE, N><<<(total + 127) / 128, 128, 0, st>>>(a, x, b, c, h0, y, hT,
                                                                          B, T, D);

@@ -242,6 +242,30 @@ def test_scan_edges_vs_oracle(dev, B, T, D, N, dtype):
     assert rel_to_max(hT, want_h) <= FP32_TOL
 
 
+@pytest.mark.parametrize("B,T,D,N,dtype,with_h0", [
+    (2, 100, 64, 16, torch.bfloat16, True), (1, 33, 32, 8, torch.float32, False),
+    (1, 32, 96, 16, torch.bfloat16, False), (2, 257, 32, 1, torch.float32, True),
+    (1, 2048, 32, 16, torch.bfloat16, True),
+])
+def test_scan_shared_decay_vs_oracle(dev, B, T, D, N, dtype, with_h0):
+    """`a` shared over n ([B,T,D]): the collapsed scalar recurrence equals the
+    N-state serial fold of the oracle."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(T + D)
+    x = torch.randn(B, T, D, generator=g).to(dtype)
+    a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, generator=g)).to(dtype)
+    b = (torch.randn(D, N, generator=g) / 4).to(dtype)
+    c = (torch.randn(D, N, generator=g) / 4).to(dtype)
+    h0 = torch.randn(B, D, N, generator=g) if with_h0 else None
+    want_y, want_h = oracle.diag_scan_serial(a, x, b, c, h0)
+    y, hT = ops.diag_scan_fwd(a.to(dev), x.to(dev), b.to(dev), c.to(dev),
+                              None if h0 is None else h0.to(dev), want_state=True)
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert rel_to_max(y, want_y) <= tol
+    assert rel_to_max(hT, want_h) <= FP32_TOL
+
+
 def test_scan_segment_composition_at_full_width(dev):
     """Size-independent property at config 3's width (D=1024, N=16, bf16):
     scanning [0,T) equals scanning [0,T/2) then [T/2,T) from the carried state —
