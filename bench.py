@@ -308,9 +308,11 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     qo, ko, vo = (_randn_bf16((16, 2048 * 128), gen).view(2, 8, 2048, 128) for _ in range(3))
     oo = torch.empty_like(vo)
     ms = time_steps(lambda: ops.om_causal_fwd(qo, ko, vo, out=oo), K, W, world, flush)
-    e = entry(ms, 2 * 2048, 4 * 16 * 2048 * 128 * 2, 1, "fp32 FMA kernel (parity build); compute-bound",
-              flops=4 * 16 * (2048 * 2049 // 2) * 128)
-    e["roofline"]["bound"] = "tensor"
+    e = entry(ms, 2 * 2048, 4 * 16 * 2048 * 128 * 2, 1,
+              "tcgen05 online-softmax kernel; causal FLOPs (lower triangle) against the burst bf16 peak; "
+              "L2 flushed between steps", flops=4 * 16 * (2048 * 2049 // 2) * 128)
+    e["roofline"] = {"bound": "tensor", "achieved": e["tflops"], "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": e["tflops"] / pk["bf16_tflops"], "traffic": None}
     out["om_causal_bf16_B2_H8_T2048_d128"] = e
     del qo, ko, vo, oo
 

@@ -58,7 +58,7 @@ SIGNATURES: dict[str, tuple] = {
     "cb2_om_causal_fwd": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
-         C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p],
+         C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_void_p],
     ),
     "cb2_diag_scan_fwd": (
         C.c_int,

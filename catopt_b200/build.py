@@ -25,6 +25,7 @@ SOURCES = [
     "decayed_chunk_tc.cu",
     "decayed_chunk.cu",
     "om_causal.cu",
+    "om_causal_tc.cu",
 ]
 
 NVCC_FLAGS = [

@@ -9,13 +9,18 @@
 // reference's isfinite guard); a row with no visible key at all ends as 0/0 =
 // NaN, like dense softmax.
 //
-// fp32 arithmetic on the FMA pipes for both element types (correctness-first
-// kernel: no benchmark configuration measures this executor).  CTA = 64 queries
+// This file: fp32 arithmetic on the FMA pipes, used for fp32 tensors and for
+// bf16 shapes the tensor-core kernel (om_causal_tc.cu) does not take.  CTA = 64 queries
 // of one (batch, head); key blocks of 64 up to the diagonal; each thread owns a
 // 4x4 patch of the 64x64 score block and 4 x (dv/16) output accumulators.
 #include "common.cuh"
 
 namespace cb2 {
+// tensor-core kernel for bf16 tensors (om_causal_tc.cu)
+bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dtype);
+int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
+                     int dk, int dv, float scale, int* dev_status, cudaStream_t st);
+
 namespace {
 
 constexpr int kBlk = 64;
@@ -160,7 +165,8 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 }  // namespace cb2
 
 extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int H,
-                                 int Tq, int Tk, int dk, int dv, float scale, int dtype, void* stream) {
+                                 int Tq, int Tk, int dk, int dv, float scale, int dtype,
+                                 int* dev_status, void* stream) {
   using namespace cb2;
   if (!q || !k || !v || !o) return CB2_NULL_PTR;
   if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0) return CB2_BAD_SHAPE;
@@ -169,6 +175,9 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
   const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
   const dim3 grid((Tq + kBlk - 1) / kBlk, B * H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) &&
+      aligned16(o))
+    return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, dev_status, st);
   if (dtype == CB2_BF16) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)

@@ -1,0 +1,297 @@
+// Causal softmax attention on the tensor cores (bf16, dk, dv <= 128): the
+// online-softmax monoid of the reference (`_om_elem` / `_om_compose`,
+// catopt_torch/torch_bridge.py:1974-2006) folded over 128-key blocks, with the
+// running (max, sum) pair in registers and the weighted sum in tensor memory.
+//
+// CTA = 128 queries of one (batch, head).  Per key block j (causal: j <= i):
+//   MMA1  S_j = Q K_j^T                         -> TMEM, double-buffered
+//   WG    m' = max(m, rowmax S_j); P = exp(S_j - m') as bf16, written over S_j;
+//         l = l e^(m-m') + rowsum P;  O <- O e^(m-m')   (skipped by a warp whose
+//         rows all kept their maximum)
+//   MMA2  O += P V_j      (A operand read from TMEM, V_j MN-major from its tile)
+// and finally o = O / l through a staging tile and a TMA store.  Entirely masked
+// blocks are never visited; a partially masked block (the diagonal one, or the
+// last one when Tk is ragged) masks per element.  Thread = one query row (one
+// TMEM lane), so the row maxima and sums need no cross-thread traffic.
+//
+// Roles: warp 0 = TMA producer (Q once, then K_j / V_j tiles through a 5-slot
+// ring; 3-D tensor maps clip and zero-fill per head), warp 1 = MMA issuer and
+// TMEM owner, warps 2..5 = softmax group.  Every wait is bounded.
+#include "umma.cuh"
+
+namespace cb2 {
+namespace {
+
+constexpr int kQ = 128;                   // queries per CTA = keys per block
+constexpr int kSlots = 5;
+constexpr int kThreads = 192;
+constexpr uint32_t kTile = umma::kTileBytes;
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffRing = kTile;
+constexpr uint32_t kOffO = kOffRing + kSlots * kTile;
+constexpr uint32_t kOffBars = kOffO + kTile;
+constexpr int kNumBars = 2 * kSlots + 6;
+constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                    int Tq, int Tk, int dv, float scale_log2e, int* dev_status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  uint64_t* full = bars;                         // [kSlots] TMA -> MMA
+  uint64_t* empty = bars + kSlots;               // [kSlots] MMA -> TMA
+  uint64_t* q_full = bars + 2 * kSlots;
+  uint64_t* s_ready = bars + 2 * kSlots + 1;     // [2] MMA1 done (per S buffer)
+  uint64_t* p_ready = bars + 2 * kSlots + 3;     // P written, O rescaled (128 arrivals)
+  uint64_t* o_done = bars + 2 * kSlots + 4;      // MMA2 done
+  uint64_t* wg_sync = bars + 2 * kSlots + 5;     // barrier among the 128 softmax threads
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int qb = gridDim.x - 1 - blockIdx.x;     // heaviest (latest) query blocks first
+  const int q0 = qb * kQ;
+  const int nkb = min((Tk + kQ - 1) / kQ, qb + 1);   // key blocks with at least one visible key
+
+  if (tid == 0) {
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(&s_ready[0], 1);
+    mbar_init(&s_ready[1], 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    mbar_init(wg_sync, 128);
+    *s_abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    umma::tmem_alloc(s_tmem, 512);
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t q_addr = smem_u32(smem + kOffQ);
+  const uint32_t ring_addr = smem_u32(smem + kOffRing);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      umma::tma_prefetch_desc(&map_q);
+      umma::tma_prefetch_desc(&map_k);
+      umma::tma_prefetch_desc(&map_v);
+      umma::tma_prefetch_desc(&map_o);
+      mbar_arrive_expect_tx(q_full, kTile);
+      umma::tma_load_3d(smem + kOffQ, &map_q, 0, q0, bh, q_full);
+      umma::tma_load_3d(smem + kOffQ + umma::kSubTileBytes, &map_q, 64, q0, bh, q_full);
+      for (int t = 0; t < 2 * nkb; ++t) {        // K_0, V_0, K_1, V_1, ...
+        const int slot = t % kSlots, use = t / kSlots;
+        if (use > 0 && !mbar_wait_abortable(&empty[slot], (use - 1) & 1, s_abort)) break;
+        const CUtensorMap* m = (t & 1) ? &map_v : &map_k;
+        unsigned char* dst = smem + kOffRing + slot * kTile;
+        mbar_arrive_expect_tx(&full[slot], kTile);
+        umma::tma_load_3d(dst, m, 0, (t >> 1) * kQ, bh, &full[slot]);
+        umma::tma_load_3d(dst + umma::kSubTileBytes, m, 64, (t >> 1) * kQ, bh, &full[slot]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = umma::instr_desc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_kn = umma::instr_desc_bf16(128, 128, false, true);
+      auto issue_scores = [&](int j) -> bool {
+        const int t = 2 * j, slot = t % kSlots;
+        if (!mbar_wait_abortable(&full[slot], (t / kSlots) & 1, s_abort)) return false;
+        umma::fence_after_sync();
+        const uint32_t k_addr = ring_addr + slot * kTile;
+        const uint32_t col = (j & 1) ? kColS1 : kColS0;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_bf16(tmem + col, umma::desc_kmajor(q_addr, ks), umma::desc_kmajor(k_addr, ks), idesc_kk,
+                         ks > 0);
+        umma::mma_commit(&s_ready[j & 1]);
+        umma::mma_commit(&empty[slot]);
+        return true;
+      };
+      bool ok = mbar_wait_abortable(q_full, 0, s_abort);
+      ok = ok && issue_scores(0);
+      for (int j = 0; ok && j < nkb; ++j) {
+        if (j + 1 < nkb && !issue_scores(j + 1)) break;   // overlaps the softmax of block j
+        const int t = 2 * j + 1, slot = t % kSlots;
+        if (!mbar_wait_abortable(p_ready, j & 1, s_abort)) break;
+        if (!mbar_wait_abortable(&full[slot], (t / kSlots) & 1, s_abort)) break;
+        umma::fence_after_sync();
+        const uint32_t v_addr = ring_addr + slot * kTile;
+        const uint32_t pcol = (j & 1) ? kColS1 : kColS0;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_bf16_ts(tmem + kColO, tmem + pcol + ks * 8, umma::desc_mnmajor(v_addr, ks), idesc_kn,
+                            (j > 0) || (ks > 0));
+        umma::mma_commit(o_done);
+        umma::mma_commit(&empty[slot]);
+      }
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;                  // query row of the block = TMEM lane
+    const int tq = q0 + r;                         // global query index
+    const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
+    unsigned char* o_tile = smem + kOffO;
+    float m_run = -INFINITY, l_run = 0.f;          // in units of scale*log2(e)
+    uint32_t v[32];
+    for (int j = 0; j < nkb; ++j) {
+      const uint32_t scol = (j & 1) ? kColS1 : kColS0;
+      bool ok = mbar_wait_abortable(&s_ready[j & 1], (j >> 1) & 1, s_abort);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      umma::fence_after_sync();
+      const int k0 = j * kQ;
+      const bool partial = (k0 + kQ - 1 > q0) || (k0 + kQ > Tk);   // uniform over the CTA
+      // pass 1: row maximum of the visible scores
+      float mb = -INFINITY;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        umma::tmem_ld32(lane_base + scol + cb * 32, v);
+        umma::tmem_wait_ld();
+        if (partial) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int key = k0 + cb * 32 + c;
+            if (key <= tq && key < Tk) mb = fmaxf(mb, __uint_as_float(v[c]));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) mb = fmaxf(mb, __uint_as_float(v[c]));
+        }
+      }
+      const float m_new = fmaxf(m_run, mb * scale_log2e);
+      // m_new is finite here: key 0 of block 0 is visible to every query, and a block
+      // that hides all of its keys from this row leaves m unchanged
+      const float alpha = ex2(m_run - m_new);                // 0 on the first block
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+      // pass 2: P = exp2(s*c - m') packed over S, running sum
+      float ps = 0.f;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        umma::tmem_ld32(lane_base + scol + cb * 32, v);
+        umma::tmem_wait_ld();
+        uint32_t w[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float p0 = ex2(fmaf(__uint_as_float(v[c]), scale_log2e, neg_m));
+          float p1 = ex2(fmaf(__uint_as_float(v[c + 1]), scale_log2e, neg_m));
+          if (partial) {
+            const int key = k0 + cb * 32 + c;
+            if (!(key <= tq && key < Tk)) p0 = 0.f;
+            if (!(key + 1 <= tq && key + 1 < Tk)) p1 = 0.f;
+          }
+          ps += p0 + p1;
+          w[c >> 1] = pack_bf16x2(p0, p1);
+        }
+        umma::tmem_st16(lane_base + scol + cb * 16, w);       // over columns this thread has consumed
+      }
+      umma::tmem_wait_st();
+      l_run = fmaf(l_run, alpha, ps);
+      m_run = m_new;
+      // O <- O * alpha, once the previous block's P.V has landed; skipped by a warp
+      // whose 32 rows all kept their maximum
+      if (j > 0) {
+        ok = mbar_wait_abortable(o_done, (j - 1) & 1, s_abort);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        umma::fence_after_sync();
+        if (!__all_sync(0xffffffffu, alpha == 1.f)) {
+#pragma unroll 1
+          for (int cb = 0; cb < 4; ++cb) {
+            umma::tmem_ld32(lane_base + kColO + cb * 32, v);
+            umma::tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+            umma::tmem_st32(lane_base + kColO + cb * 32, v);
+          }
+          umma::tmem_wait_st();
+        }
+      }
+      umma::fence_before_sync();
+      mbar_arrive(p_ready);
+    }
+    // read-out o = O / l  (0/0 = NaN for a row that saw no key, as the reference)
+    bool ok = mbar_wait_abortable(o_done, (nkb - 1) & 1, s_abort);
+    if (__all_sync(0xffffffffu, ok)) {
+      umma::fence_after_sync();
+      const float inv_l = 1.f / l_run;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        umma::tmem_ld32(lane_base + kColO + cb * 32, v);
+        umma::tmem_wait_ld();
+        uint32_t w[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2)
+          w[c >> 1] = pack_bf16x2(__uint_as_float(v[c]) * inv_l, __uint_as_float(v[c + 1]) * inv_l);
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8)
+          *reinterpret_cast<uint4*>(o_tile + umma::tile_chunk_offset(r, cb * 32 + c8 * 8)) =
+              make_uint4(w[4 * c8], w[4 * c8 + 1], w[4 * c8 + 2], w[4 * c8 + 3]);
+      }
+      fence_proxy_async_smem();
+      // the four softmax warps meet (bounded wait), then one thread stores the tile
+      mbar_arrive(wg_sync);
+      ok = mbar_wait_abortable(wg_sync, 0, s_abort);
+      if (ok && tid == 64) {
+        umma::tma_store_3d(&map_o, 0, q0, bh, o_tile);
+        if (dv > 64) umma::tma_store_3d(&map_o, 64, q0, bh, o_tile + umma::kSubTileBytes);
+        bulk_commit();
+        bulk_wait_all<0>();
+      }
+    }
+  }
+
+  __syncwarp();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  if (tid == 0 && *s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+  if (warp == 1) {
+    __syncwarp();
+    umma::tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dtype) {
+  return dtype == CB2_BF16 && dk >= 8 && dk <= 128 && dk % 8 == 0 && dv >= 8 && dv <= 128 && dv % 8 == 0 &&
+         Tq >= 1 && Tk >= 1 && int64_t(B) * H <= 65535;
+}
+
+int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
+                     int dk, int dv, float scale, int* dev_status, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mo;
+  const uint64_t bh = uint64_t(B) * H;
+  int rc = umma::make_map_3d(&mq, q, true, dk, Tq, bh, 64, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mk, k, true, dk, Tk, bh, 64, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mv, v, true, dv, Tk, bh, 64, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mo, o, true, dv, Tq, bh, 64, 128, true);
+  if (rc != CB2_OK) return rc;
+  if (cudaFuncSetAttribute(om_causal_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           int(kSmemBytes)) != cudaSuccess)
+    return CB2_LAUNCH_FAIL;
+  const dim3 grid((Tq + kQ - 1) / kQ, unsigned(bh));
+  om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dv,
+                                                         scale * 1.4426950408889634f, dev_status);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
+}  // namespace cb2

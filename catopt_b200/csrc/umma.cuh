@@ -191,9 +191,9 @@ inline int make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, uint
   return r == CUDA_SUCCESS ? CB2_OK : CB2_LAUNCH_FAIL;
 }
 
-// ---- host: un-swizzled 3-D tensor map {d0 (inner), d1, d2}, box {b0, b1, 1} --
+// ---- host: 3-D tensor map {d0 (inner), d1, d2}, box {b0, b1, 1}, optional 128-byte swizzle --
 inline int make_map_3d(CUtensorMap* out, const void* base, bool is_bf16, uint64_t d0, uint64_t d1,
-                       uint64_t d2, uint32_t b0, uint32_t b1) {
+                       uint64_t d2, uint32_t b0, uint32_t b1, bool swizzle128 = false) {
   using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -214,7 +214,8 @@ inline int make_map_3d(CUtensorMap* out, const void* base, bool is_bf16, uint64_
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                         3, const_cast<void*>(base), gdim, gstride, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? CB2_OK : CB2_LAUNCH_FAIL;
 }

@@ -184,7 +184,8 @@ def om_causal_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
         out = torch.empty(B, H, Tq, dv, dtype=q.dtype, device=q.device)
     sc = float(scale) if scale is not None else 1.0 / float(dk) ** 0.5
     rc = _lib.load().cb2_om_causal_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                       B, H, Tq, Tk, dk, dv, sc, dtype_code(q.dtype), stream_ptr())
+                                       B, H, Tq, Tk, dk, dv, sc, dtype_code(q.dtype),
+                                       device_status(q.device).data_ptr(), stream_ptr())
     check(rc, "cb2_om_causal_fwd")
     return out
 

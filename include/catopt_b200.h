@@ -183,11 +183,13 @@ int cb2_diag_scan_fwd(const void* a, const void* x, const void* b, const void* c
  * blocks contribute 0; a row without any visible key yields NaN (0/0).
  * q: [B,H,Tq,dk]; k: [B,H,Tk,dk]; v: [B,H,Tk,dv]; o: [B,H,Tq,dv]; dk,dv <= 128;
  * `scale` multiplies the scores (the reference folds it into q).  dtype is the
- * element type of all four tensors; arithmetic is fp32.
+ * element type of all four tensors.  bf16 tensors with dk, dv multiples of 8 run
+ * on the tensor cores (bf16 products, fp32 softmax statistics and accumulator);
+ * fp32 tensors on the fp32 FMA pipes.
  * ------------------------------------------------------------------------- */
 int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B,
                       int H, int Tq, int Tk, int dk, int dv, float scale, int dtype,
-                      void* stream);
+                      int* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -455,6 +455,24 @@ def test_om_causal_long_block_invariance(dev):
     assert rel_to_max(out, want2) <= FP32_TOL
 
 
+@pytest.mark.parametrize("B,H,Tq,Tk,dk,dv", [(1, 2, 1000, 1000, 128, 128), (2, 3, 2048, 2048, 64, 64),
+                                            (1, 1, 300, 130, 128, 64), (1, 2, 128, 128, 128, 128),
+                                            (1, 1, 1, 257, 32, 32)])
+def test_om_causal_bf16_tensor_core_path(dev, B, H, Tq, Tk, dk, dv):
+    """bf16 shapes of the tensor-core kernel: ragged lengths, Tq != Tk, many key
+    blocks (running max / rescale path), against fp64 on the bf16-rounded inputs."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(Tq + dk)
+    q = torch.randn(B, H, Tq, dk, generator=g).bfloat16()
+    k = torch.randn(B, H, Tk, dk, generator=g).bfloat16()
+    v = torch.randn(B, H, Tk, dv, generator=g).bfloat16()
+    out = ops.om_causal_fwd(q.to(dev), k.to(dev), v.to(dev))
+    want = oracle.om_causal_chunked(q.double(), k.double(), v.double(), [Tk])
+    assert out.dtype == torch.bfloat16 and torch.isfinite(out.float()).all()
+    assert rel_to_max(out, want) <= BF16_TOL
+
+
 def test_device_status_clean(dev):
     """No kernel in this file ran into a bounded-wait timeout."""
     from catopt_b200 import ops
