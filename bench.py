@@ -453,6 +453,18 @@ def run_profile_case(args) -> None:
         c = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
         y = torch.empty_like(x)
         fn = lambda: ops.diag_scan_fwd(a, x, b, c, None, out=y)  # noqa: E731
+    elif args.profile_case == "scan_shared":  # config 3 with the decay shared over n, full size: 201 MB
+        B, T, D, N = 8, 4096, 1024, 16
+        x = _randn_bf16((B, T * D), gen).view(B, T, D)
+        a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, device=dev, generator=gen)).bfloat16()
+        b = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
+        c = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
+        y = torch.empty_like(x)
+        fn = lambda: ops.diag_scan_fwd(a, x, b, c, None, out=y)  # noqa: E731
+    elif args.profile_case == "om_causal":    # B=2 H=8 T=2048 d=128 bf16 (34 MB; compute-bound)
+        q, k, v = (_randn_bf16((16, 2048 * 128), gen).view(2, 8, 2048, 128) for _ in range(3))
+        o = torch.empty_like(v)
+        fn = lambda: ops.om_causal_fwd(q, k, v, out=o)  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
         ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
         outp = ref.clone()
@@ -478,7 +490,8 @@ def run_profile_case(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile-case", default=None, choices=["decayed", "scan", "verify", "linear"],
+    ap.add_argument("--profile-case", default=None,
+                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
