@@ -12,8 +12,11 @@ order.  ``B200Sink`` puts three B200 specs in front of the torch ones:
   chunks ``split(q|k|v, dim=-2, sizes=[C]*K)`` of three shared bases, one shared
   ``decay(g, t=C)``, every pair ``i > j`` present once with row gate
   ``decay_vec(g, t=C, offset=(i-j)C)`` and column gate ``decay_vec(g, t=C,
-  sign=-1)``, one constant scale.  Anything else is declined, so the reference's
-  pairwise executor (or the generic module) still takes it.
+  sign=-1)``, one constant scale.  Terms over a ragged partition — what
+  extraction really returns when the K-way law fires at two levels, e.g. pieces
+  of 32,32,32,32,128,128,128 rows, which the reference's executor declines — are
+  recognised by ``decayed_ragged_plan``.  Anything else is declined, so the
+  reference's pairwise executor (or the generic module) still takes it.
 * ``b200_scan`` — diagonal ``applyd(<aff_diag tree>, h)`` scan applications (the
   terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
   leaf stacking are reused, the composed-map reduction runs in
@@ -36,6 +39,7 @@ from catopt_carriers.decayed_lower import build_decayed_plan
 from catopt_carriers.om_lower import _slice_index
 from catopt_core.ir import IR, Const, Op, Param
 from catopt_core.ports import ExecutorSpec
+from catopt_core.typing import _shape_of
 from catopt_torch.adapters import TorchSink
 from catopt_torch.torch_bridge import IRModule
 
@@ -44,7 +48,8 @@ from . import verify as b200_verify
 from ._lib import B200Error
 from .executors import _GraphMixin
 
-__all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "linear_chain_plan", "scan_diag_plan",
+__all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "decayed_ragged_plan",
+           "decayed_plan", "linear_chain_plan", "scan_diag_plan",
            "B200ChunkedDecayModule", "B200LinearChainModule"]
 
 
@@ -133,6 +138,315 @@ def decayed_state_carry_plan(root: Any) -> dict | None:
     return {"q": q, "k": k, "v": v, "gamma": gamma, "chunk": C, "n": K, "scale": scales.pop()}
 
 
+# ---- ragged / hierarchical partitions: what the search really extracts -------------------
+def _norm_dim(term: Any, dim: Any, memo: dict) -> int | None:
+    """Axis as a negative index (needs the operand's rank when given as a positive one)."""
+    if not isinstance(dim, int):
+        return None
+    if dim < 0:
+        return dim
+    shape = _shape_of(term, memo)
+    return dim - len(shape) if isinstance(shape, tuple) and dim < len(shape) else None
+
+
+def _split_piece(term: Any, memo: dict) -> tuple | None:
+    """``split(x, dim, index, sizes)`` -> (x, negative dim, start, length, total)."""
+    if not (isinstance(term, Op) and term.op == "split" and len(term.args) == 1):
+        return None
+    a = term.attrs
+    sizes, idx = a.get("sizes"), a.get("index", 0)
+    dim = _norm_dim(term.args[0], a.get("dim"), memo)
+    if dim is None or not isinstance(idx, int) or not isinstance(sizes, (tuple, list)):
+        return None
+    if not all(isinstance(z, int) and z > 0 for z in sizes) or not 0 <= idx < len(sizes):
+        return None
+    return term.args[0], dim, sum(sizes[:idx]), sizes[idx], sum(sizes)
+
+
+def _range_of(term: Any, dim: int, memo: dict | None = None) -> tuple | None:
+    """Resolve (possibly nested) row/column slices of one base tensor to
+    ``(base, start, length, total)`` along ``dim``; ``None`` for anything else."""
+    memo = {} if memo is None else memo
+    p = _split_piece(term, memo)
+    if p is None or p[1] != dim:
+        return None
+    x, _, start, length, total = p
+    inner = _range_of(x, dim, memo)
+    if inner is None:
+        return x, start, length, total
+    base, s0, l0, t0 = inner
+    return (base, s0 + start, length, t0) if total == l0 else None
+
+
+def _is_swap_last_two(t: Any) -> bool:
+    return (isinstance(t, Op) and t.op == "transpose" and len(t.args) == 1
+            and {t.attrs.get("dim0"), t.attrs.get("dim1")} == {-1, -2})
+
+
+def _gate(t: Any, dim: int) -> tuple | None:
+    """``unsqueeze(decay_vec(g, t, sign, offset), dim)`` -> (g, t, sign, offset)."""
+    if not (isinstance(t, Op) and t.op == "unsqueeze" and t.attrs.get("dim") == dim):
+        return None
+    dv = t.args[0]
+    if not (isinstance(dv, Op) and dv.op == "decay_vec"):
+        return None
+    a = dv.attrs
+    return dv.args[0], int(a.get("t", 0) or 0), int(a["sign"]) if "sign" in a else 1, int(a.get("offset", 0) or 0)
+
+
+class _Coverage:
+    """Abstract interpretation of a chunked decayed term.
+
+    Every sub-term is read as a list of row pieces ``[a, s, cov]``: rows
+    ``[a, a+s)`` of the output, with ``cov`` a list of ``(b, l, kind, scale)``
+    saying which keys ``[b, b+l)`` those rows already attend to:
+
+    * ``"diag"``: the causal decayed block of the rows with their own keys
+      (``om_decayed(q_r k_r^T, decay(g, s), v_r)``; b = a, l = s);
+    * ``"pend"``: an earlier key block weighted by ``g^(-c)`` (c the key's index in
+      the block) — a cross product that still lacks its row gate;
+    * ``"full"``: an earlier key block with the complete weight ``g^(t - s)``.
+
+    ``add`` merges coverages on the common refinement of the row pieces,
+    ``concat`` appends pieces, a row gate ``decay_vec(g, t, offset)`` completes
+    pending blocks when ``offset`` is the distance from the key block's start to
+    the gated rows' start, ``div`` by a constant multiplies the scale, a row
+    ``split`` restricts pieces (cutting a diagonal block into an earlier full part
+    and a smaller diagonal).  The term is decayed attention of the whole sequence
+    iff at the end the pieces tile ``[0, T)`` and each piece holds its diagonal
+    block plus full blocks tiling ``[0, a)``, all with one scale."""
+
+    def __init__(self) -> None:
+        self.q = self.k = self.v = self.gamma = None
+        self.total: int | None = None
+        self.memo: dict = {}
+        self.cache: dict = {}
+
+    def _same(self, name: str, val: Any) -> bool:
+        cur = getattr(self, name)
+        if cur is None:
+            setattr(self, name, val)
+            return True
+        return cur == val
+
+    def _rows(self, t: Any, dim: int, slot: str, transposed: bool = False) -> tuple | None:
+        r = _range_of(t, dim, self.memo)
+        if r is None:
+            return None
+        base, start, length, total = r
+        if transposed:
+            if not _is_swap_last_two(base):
+                return None
+            base = base.args[0]
+        if not self._same(slot, base) or not self._same("total", total):
+            return None
+        return start, length
+
+    # -- leaves ---------------------------------------------------------------------------
+    def _om_decayed(self, t: Op) -> list | None:
+        score, dec, vv = t.args
+        if not (isinstance(score, Op) and score.op == "matmul" and len(score.args) == 2 and isinstance(dec, Op)):
+            return None
+        rq = self._rows(score.args[0], -2, "q")
+        rk = self._rows(score.args[1], -1, "k", transposed=True)
+        rv = self._rows(vv, -2, "v")
+        if None in (rq, rk, rv) or rk != rv:
+            return None
+        (a, s), (b, l) = rq, rk
+        if dec.op == "decay":
+            if not self._same("gamma", dec.args[0]) or int(dec.attrs.get("t", 0) or 0) != s or (a, s) != (b, l):
+                return None
+            return [[a, s, [(a, s, "diag", 1.0)]]]
+        col = _gate(dec, -2)          # (s_ij * g^(-c)[None, :]) @ v_j spelled as om_decayed
+        if col is None or not self._same("gamma", col[0]) or col[1:] != (l, -1, 0) or b + l > a:
+            return None
+        return [[a, s, [(b, l, "pend", 1.0)]]]
+
+    def _state_product(self, t: Op) -> list | None:
+        """``q_r @ ((k_b * g^(-c)[:, None])^T @ v_b)``."""
+        rq, state = self._rows(t.args[0], -2, "q"), t.args[1]
+        if rq is None or not (isinstance(state, Op) and state.op == "matmul" and len(state.args) == 2):
+            return None
+        kt = state.args[0]
+        if not _is_swap_last_two(kt):
+            return None
+        kg = kt.args[0]
+        if not (isinstance(kg, Op) and kg.op == "mul" and len(kg.args) == 2):
+            return None
+        col, kk = _gate(kg.args[1], -1), kg.args[0]
+        if col is None:
+            col, kk = _gate(kg.args[0], -1), kg.args[1]
+        if col is None or not self._same("gamma", col[0]):
+            return None
+        rk, rv = self._rows(kk, -2, "k"), self._rows(state.args[1], -2, "v")
+        if rk is None or rk != rv or col[1:] != (rk[1], -1, 0) or rk[0] + rk[1] > rq[0]:
+            return None
+        return [[rq[0], rq[1], [(rk[0], rk[1], "pend", 1.0)]]]
+
+    # -- combinators ----------------------------------------------------------------------
+    @staticmethod
+    def _restrict(pieces: list, lo: int, hi: int) -> list | None:
+        """Rows [lo, hi) of a piece list that covers them."""
+        out = []
+        for a, s, cov in pieces:
+            x, y = max(a, lo), min(a + s, hi)
+            if x >= y:
+                continue
+            c2 = []
+            for b, l, kind, sc in cov:
+                if kind == "diag" and (x, y - x) != (b, l):
+                    if x > b:
+                        c2.append((b, x - b, "full", sc))
+                    c2.append((x, y - x, "diag", sc))
+                else:
+                    c2.append((b, l, kind, sc))
+            out.append([x, y - x, c2])
+        if not out or out[0][0] != lo or out[-1][0] + out[-1][1] != hi:
+            return None
+        return out
+
+    @staticmethod
+    def _span(pieces: list) -> tuple:
+        return pieces[0][0], pieces[-1][0] + pieces[-1][1]
+
+    def _add(self, parts: list) -> list | None:
+        span = self._span(parts[0])
+        if any(self._span(p) != span for p in parts[1:]):
+            return None
+        cuts = sorted({span[0], span[1]} | {a for p in parts for a, _, _ in p})
+        out = []
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            cov = []
+            for p in parts:
+                r = self._restrict(p, lo, hi)
+                if r is None or len(r) != 1:
+                    return None
+                cov.extend(r[0][2])
+            out.append([lo, hi - lo, cov])
+        return out
+
+    def interp(self, t: Any) -> list | None:
+        if not isinstance(t, Op):
+            return None
+        if t in self.cache:
+            return self.cache[t]
+        out = self._interp(t)
+        self.cache[t] = out
+        return out
+
+    def _interp(self, t: Op) -> list | None:
+        op, args = t.op, t.args
+        if op == "div" and len(args) == 2 and _const_value(args[1]) is not None:
+            x, c = self.interp(args[0]), _const_value(args[1])
+            return None if x is None else [[a, s, [(b, l, kd, sc * c) for b, l, kd, sc in cov]] for a, s, cov in x]
+        if op == "mul" and len(args) == 2:
+            g, other = _gate(args[0], -1), args[1]
+            if g is None:
+                g, other = _gate(args[1], -1), args[0]
+            if g is None or g[2] != 1 or not self._same("gamma", g[0]):
+                return None
+            x = self.interp(other)
+            if x is None:
+                return None
+            lo, hi = self._span(x)
+            if g[1] != hi - lo:
+                return None
+            out = []
+            for a, s, cov in x:
+                if any(kd != "pend" or lo - b != g[3] for b, _, kd, _ in cov):
+                    return None
+                out.append([a, s, [(b, l, "full", sc) for b, l, _, sc in cov]])
+            return out
+        if op == "add":
+            parts = [self.interp(a) for a in args]
+            return None if any(p is None for p in parts) else self._add(parts)
+        if op == "concat" and _norm_dim(t, t.attrs.get("dim"), self.memo) == -2:
+            out: list = []
+            for a in args:
+                p = self.interp(a)
+                if p is None or (out and self._span(out)[1] != p[0][0]):
+                    return None
+                out = out + p
+            return out or None
+        if op == "om_decayed" and len(args) == 3:
+            return self._om_decayed(t)
+        if op == "matmul" and len(args) == 2:
+            return self._state_product(t)
+        if op == "split":
+            p = _split_piece(t, self.memo)
+            if p is None or p[1] != -2:
+                return None
+            x = self.interp(p[0])
+            if x is None:
+                return None
+            lo, hi = self._span(x)
+            if hi - lo != p[4]:
+                return None
+            return self._restrict(x, lo + p[2], lo + p[2] + p[3])
+        return None
+
+
+def decayed_ragged_plan(root: Any) -> dict | None:
+    """Recognise chunked decayed attention over an ARBITRARY, possibly
+    hierarchical partition of the sequence — what extraction returns when the
+    K-way law (``om_decayed_kway_blocks``, catopt_carriers/om.py:3155-3201) fires
+    at more than one level: nested ``concat``s over pieces such as
+    (32,32,32,32,128,128,128) rows, cross terms that reach back to coarser source
+    blocks, a coarse cross term added to a ``concat`` of finer arms or shared by
+    several arms through row slices, cross products spelled either as
+    ``q_i @ ((k_j * col)^T @ v_j)`` or as ``om_decayed(q_i k_j^T, col, v_j)``.  The
+    reference's own executor declines all of these (non-uniform shapes,
+    decayed_lower.py:198-207) and the generic module evaluates them op by op.
+
+    The term is accepted iff its coverage (see ``_Coverage``) is exactly: every
+    row attends to all earlier keys and itself with weight ``g^(t-s)``, under one
+    constant scale — i.e. it equals decayed attention of the whole sequence,
+    which is all the kernel needs: it picks its own chunking.  Returns
+    ``{q, k, v, gamma, sizes, scale, n, chunk: None}`` or ``None``."""
+    if not (isinstance(root, Op) and root.op == "concat"):
+        return None
+    cv = _Coverage()
+    pieces = cv.interp(root)
+    if pieces is None or cv.total is None or None in (cv.q, cv.k, cv.v, cv.gamma):
+        return None
+    if cv._span(pieces) != (0, cv.total) or len(pieces) < 2:
+        return None
+    scales = set()
+    for a, s, cov in pieces:
+        diag = [c for c in cov if c[2] == "diag"]
+        if len(diag) != 1 or diag[0][:2] != (a, s) or any(c[2] == "pend" for c in cov):
+            return None
+        pos = 0
+        for b, l, _, _ in sorted(c for c in cov if c[2] == "full"):
+            if b != pos:
+                return None
+            pos = b + l
+        if pos != a:
+            return None
+        scales.update(c[3] for c in cov)
+    if len(scales) != 1:
+        return None
+    return {"q": cv.q, "k": cv.k, "v": cv.v, "gamma": cv.gamma, "sizes": tuple(s for _, s, _ in pieces),
+            "n": len(pieces), "chunk": None, "scale": scales.pop()}
+
+
+def decayed_plan(root: Any) -> dict | None:
+    """Uniform K-chunk term first (the reference's own parser), then any ragged partition."""
+    plan = decayed_state_carry_plan(root)
+    return plan if plan is not None else decayed_ragged_plan(root)
+
+
+def _kernel_chunk(T: int, plan_chunk: int | None) -> int | None:
+    """Chunk length handed to the kernel: the plan's own when uniform, else the
+    largest divisor of T up to 128 (the value does not depend on it)."""
+    if plan_chunk:
+        return plan_chunk
+    for c in range(min(128, T), 0, -1):
+        if T % c == 0:
+            return c if (c >= 16 or T <= 64) else None
+    return None
+
+
 class _EvalBase(_GraphMixin, torch.nn.Module):
     """Shared plumbing: embedded ``IRModule`` + operand evaluation."""
 
@@ -166,7 +480,7 @@ class B200ChunkedDecayModule(_EvalBase):
 
     def __init__(self, ir: IR, param_values: dict | None = None) -> None:
         super().__init__(ir, param_values)
-        self._plan = decayed_state_carry_plan(self.eval_mod._root)
+        self._plan = decayed_plan(self.eval_mod._root)
 
     @property
     def is_batched(self) -> bool:
@@ -188,8 +502,13 @@ class B200ChunkedDecayModule(_EvalBase):
         H = lead[-1]
         g = torch.as_tensor(g, dtype=torch.float32, device=q.device).reshape(-1)
         g = (g.expand(H) if g.numel() == 1 else g).contiguous()
+        if not q.is_cuda:
+            raise B200Error("decayed executor runs on CUDA tensors only (no CPU fallback)")
+        chunk = _kernel_chunk(q.shape[-2], plan["chunk"])
+        if chunk is None or q.dtype not in (torch.float32, torch.bfloat16):
+            return self.eval_mod(*xs)      # awkward length / fp64: the generic module, same device
         q4, k4, v4 = (t.reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous() for t in (q, k, v))
-        out = ops.decayed_chunk_fwd(q4, k4, v4, g, plan["chunk"], plan["scale"])
+        out = ops.decayed_chunk_fwd(q4, k4, v4, g, chunk, plan["scale"])
         return out.reshape(*lead, out.shape[-2], out.shape[-1])
 
 
@@ -334,7 +653,7 @@ class B200Sink(TorchSink):
                 "b200_om_decayed_chunked": ExecutorSpec(
                     "b200_om_decayed_chunked",
                     lambda ir, p: B200ChunkedDecayModule(ir, param_values=p),
-                    lambda term: decayed_state_carry_plan(term) is not None,
+                    lambda term: decayed_plan(term) is not None,
                     _engaged,
                     (frozenset({"concat"}), frozenset({"add", "mul", "div", "matmul"}),
                      frozenset({"om_decayed", "decay", "decay_vec"})),

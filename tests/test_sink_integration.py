@@ -144,3 +144,207 @@ def test_b200_target_profile_prices_with_the_reference_cost_model():
     assert prof.gbps > 6000 and prof.tflops > 50 and prof.name.startswith("b200")
     cost = prof.cost_fn()
     assert callable(cost)
+
+
+# --------------------------------------------------------------------------- ragged partitions
+def _ragged_term(T, d, arms, sources, scale=2.0, nested=False, per_head=False, B=2, H=2):
+    """Hand-built chunked decayed term over a non-uniform partition.
+
+    ``arms``: row counts of the output pieces; ``sources[i]``: row counts of the
+    source blocks arm i reaches back to (they must add up to the arm's start).
+    Slices are written as ``split`` with whichever size tuple names the range —
+    the fine partition for arms, a coarse (start, len, rest) one for sources — and
+    optionally as a split of a split, as saturation leaves them."""
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    q, k, v = (Var(n, tt(B, H, T, d)) for n in "qkv")
+    g = Param("g", tt(H)) if per_head else Param("g", tt())
+    kT = Op.make("transpose", k, dim0=-1, dim1=-2)
+
+    def piece(base, dim, start, length):
+        sizes = tuple(z for z in (start, length, T - start - length) if z > 0)
+        idx = 1 if start > 0 else 0
+        if nested and length % 2 == 0 and start == 0 and length < T:
+            # first half-open range expressed as split(split(base, [2*length, rest]), [length, length])
+            outer = tuple(z for z in (2 * length, T - 2 * length) if z > 0)
+            if sum(outer) == T and 2 * length <= T:
+                return Op.make("split", Op.make("split", base, dim=dim, index=0, sizes=outer),
+                               dim=dim, index=0, sizes=(length, length))
+        return Op.make("split", base, dim=dim, index=idx, sizes=sizes)
+
+    def fine(base, dim, i):
+        return Op.make("split", base, dim=dim, index=i, sizes=tuple(arms))
+
+    c = Const(scale)
+    out, a = [], 0
+    for i, s in enumerate(arms):
+        qi = fine(q, -2, i)
+        t = Op.make("div", Op.make("om_decayed", Op.make("matmul", qi, fine(kT, -1, i)),
+                                   Op.make("decay", g, t=s), fine(v, -2, i)), c)
+        b = 0
+        for l in sources[i]:
+            col = Op.make("unsqueeze", Op.make("decay_vec", g, t=l, sign=-1), dim=-1)
+            row = Op.make("unsqueeze", Op.make("decay_vec", g, t=s, offset=a - b), dim=-1)
+            state = Op.make("matmul", Op.make("transpose", Op.make("mul", piece(k, -2, b, l), col), dim0=-1, dim1=-2),
+                            piece(v, -2, b, l))
+            t = Op.make("add", t, Op.make("mul", row, Op.make("div", Op.make("matmul", qi, state), c)))
+            b += l
+        assert b == a
+        out.append(t)
+        a += s
+    root = out[-1]
+    for t in reversed(out[:-1]):                       # right-nested concat, as extracted
+        root = Op.make("concat", t, root, dim=-2)
+    ir = IR(root=root, inputs=[q, k, v], input_names={"q", "k", "v"}, params={"g": g})
+    return ir
+
+
+from catopt_core.ir import Const  # noqa: E402
+
+_RAGGED = [
+    ((8, 8, 16, 32), [(), (8,), (8, 8), (16, 16)]),           # sources coarser than the arms
+    ((32, 32, 32, 32, 128, 128, 128), [(), (32,), (32, 32), (32, 32, 32), (128,), (128, 128), (128, 128, 128)]),
+    ((24, 40), [(), (24,)]),
+    ((16, 16, 16), [(), (16,), (16, 16)]),                    # uniform: also legal for the ragged parser
+]
+
+
+@pytest.mark.parametrize("arms,sources", _RAGGED, ids=lambda z: "-".join(map(str, z)) if z and isinstance(z[0], int) else None)
+@pytest.mark.parametrize("nested", [False, True])
+def test_ragged_partition_is_recognised_and_equals_whole_sequence_attention(arms, sources, nested):
+    from catopt_torch.torch_bridge import IRModule
+    from oracle import oracle
+
+    T, d = sum(arms), 8
+    ir = _ragged_term(T, d, arms, sources, scale=2.0, nested=nested)
+    plan = b200.decayed_ragged_plan(ir.root)
+    assert plan is not None and plan["sizes"] == tuple(arms) and plan["scale"] == 2.0
+    assert [getattr(plan[n], "name", None) for n in "qkv"] == ["q", "k", "v"] and plan["gamma"].name == "g"
+    s = b200.B200Sink()
+    assert _route(s, ir.root).name == "b200_om_decayed_chunked"
+    # the recognised term really is decayed attention of the whole sequence (reference bindings, fp64)
+    gen = torch.Generator().manual_seed(7)
+    q, k, v = (torch.randn(2, 2, T, d, dtype=torch.float64, generator=gen) / 3 for _ in range(3))
+    g = torch.tensor(0.93, dtype=torch.float64)
+    with torch.no_grad():
+        want = IRModule(ir, {"g": g})(q, k, v)
+    got = oracle.decayed_quadratic(q, k, v, g, 2.0)
+    assert (want - got).abs().max().item() < 1e-12
+
+
+def _mutate(ir, fn):
+    """Rebuild the term bottom-up, letting ``fn(op_node)`` replace nodes."""
+    def walk(t):
+        if not isinstance(t, Op):
+            return t
+        new = Op.make(t.op, *[walk(a) for a in t.args], **dict(t.attrs))
+        return fn(new)
+    return walk(ir.root)
+
+
+def test_ragged_lookalikes_are_declined():
+    arms, sources = _RAGGED[0]
+    ir = _ragged_term(sum(arms), 8, arms, sources)
+    assert b200.decayed_ragged_plan(ir.root) is not None
+
+    def bump_offset(n):   # one row gate off by one
+        if n.op == "decay_vec" and n.attrs.get("offset") == 16 and n.attrs.get("t") == 16:
+            return Op.make("decay_vec", *n.args, t=16, offset=17)
+        return n
+
+    def flip_sign(n):     # a column gate with the wrong sign
+        if n.op == "decay_vec" and n.attrs.get("sign") == -1 and n.attrs.get("t") == 16:
+            return Op.make("decay_vec", *n.args, t=16, sign=1)
+        return n
+
+    def other_scale(n):   # one summand divided by a different constant
+        if n.op == "div" and isinstance(n.args[0], Op) and n.args[0].op == "om_decayed" \
+                and n.args[0].args[1].attrs.get("t") == 32:
+            return Op.make("div", n.args[0], Const(3.0))
+        return n
+
+    def wrong_decay_len(n):
+        if n.op == "decay" and n.attrs.get("t") == 32:
+            return Op.make("decay", *n.args, t=16)
+        return n
+
+    for fn in (bump_offset, flip_sign, other_scale, wrong_decay_len):
+        bad = _mutate(ir, fn)
+        assert bad != ir.root
+        assert b200.decayed_ragged_plan(bad) is None, fn.__name__
+    # a source block missing (gap in [0, a)) and arms in the wrong order
+    gap = _ragged_term(64, 8, arms, [(), (8,), (8, 8), (16, 16)]).root
+    last_arm = gap.args[1].args[1].args[1]
+    assert last_arm.op == "add"
+    broken = Op.make("concat", gap.args[0], Op.make("concat", gap.args[1].args[0],
+                     Op.make("concat", gap.args[1].args[1].args[0], last_arm.args[0], dim=-2), dim=-2), dim=-2)
+    assert b200.decayed_ragged_plan(broken) is None
+    swapped = Op.make("concat", gap.args[1].args[0], Op.make("concat", gap.args[0], gap.args[1].args[1], dim=-2), dim=-2)
+    assert b200.decayed_ragged_plan(swapped) is None
+
+
+def test_kernel_chunk_choice():
+    assert b200._kernel_chunk(512, None) == 128 and b200._kernel_chunk(512, 64) == 64
+    assert b200._kernel_chunk(96, None) == 96 and b200._kernel_chunk(320, None) == 80
+    assert b200._kernel_chunk(1021, None) is None and b200._kernel_chunk(61, None) == 61
+
+
+def test_real_extraction_of_the_kway_carrier_routes_to_b200():
+    """Saturate the export of a decay-masked attention module with the K-way law
+    the way the reference's own delivery test does
+    (tests/test_om_decayed_kway_deliver.py:72-103) and check that what extraction
+    returns — a nested concat over a ragged partition, declined by the
+    reference's executor — is routed to the B200 executor."""
+    from catopt_carriers.decayed_lower import build_decayed_plan
+    from catopt_carriers.om import OM_CHUNKIFY, OM_LAWS, om_kway_laws
+    from catopt_core.cost import flops_cost
+    from catopt_core.egraph import EGraph
+    from catopt_core.laws import tensor as tl
+    from catopt_torch.adapters import TorchSource
+
+    class Retention(torch.nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            self.q, self.k, self.v = (torch.nn.Linear(d, d) for _ in range(3))
+
+        def forward(self, x):
+            t = x.shape[-2]
+            pos = torch.arange(t, dtype=x.dtype)
+            decay = torch.tril(torch.pow(torch.tensor(0.9, dtype=x.dtype),
+                                         (pos.unsqueeze(1) - pos.unsqueeze(0)).clamp_min(0)))
+            return ((self.q(x) @ self.k(x).transpose(-1, -2) / (t ** 0.5)) * decay) @ self.v(x)
+
+    torch.manual_seed(0)
+    kk, T = 2, 256
+    rules = (list(OM_LAWS) + list(OM_CHUNKIFY) + list(tl.SPLIT_SCALAR_RULES)
+             + [tl.MUL_DIV_SWAP, tl.MATMUL_DIV_DISTRIBUTE, tl.ASSOC_MATMUL_REV, tl.FACTOR_MUL, tl.FACTOR_MUL_ADD,
+                tl.DIV_ADD_FACTOR] + om_kway_laws(kk))
+    model = Retention(16).double()
+    x = torch.randn(2, T, 16, dtype=torch.float64)
+    ir, leaves = TorchSource().to_ir(model, x)
+    eg = EGraph()
+    root = eg.add_term(ir.root)
+    eg.run(rules, root, max_iterations=16, max_nodes=200_000, patience=8,
+           rule_budgets={"om_decayed_chunkify_rows": 60, "om_decayed_chunkify_keys": 60,
+                         f"om_decayed_kway_blocks_{kk}": 200})
+    best = eg.extract_best(eg.find(root), flops_cost)
+    assert best.op == "concat"
+    plan = b200.decayed_plan(best)
+    assert plan is not None and sum(plan["sizes"] if "sizes" in plan else [plan["chunk"]] * plan["n"]) == T
+    assert _route(b200.B200Sink(), best).name == "b200_om_decayed_chunked"
+    if build_decayed_plan(best) is None:       # the partition was ragged: only the B200 spec takes it
+        assert len(set(plan["sizes"])) > 1
+    # the three bases are the projections of the one input, gamma the lifted constant
+    assert all(getattr(plan[n], "op", None) == "linear" for n in "qkv")
+    # what the module would hand to the kernel reproduces the source model (fp64, CPU oracle)
+    from oracle import oracle
+
+    ex_ir = IR(root=best, inputs=list(ir.inputs), input_names=set(ir.input_names), params=dict(ir.params))
+    mod = b200.B200ChunkedDecayModule(ex_ir, leaves)
+    assert mod.is_batched and mod.n_blocks == plan["n"]
+    with torch.no_grad():
+        ev = mod._ev((x,))
+        mp = mod._plan          # built from the module's own (constant-folded) root
+        q, k, v, g = (ev(mp[n]) for n in ("q", "k", "v", "gamma"))
+        want = model(x)
+    got = oracle.decayed_quadratic(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), g.reshape(()), plan["scale"])[0]
+    assert (got - want).abs().max().item() < 1e-10
