@@ -193,3 +193,56 @@ class B200CausalSoftmax(_GraphMixin, torch.nn.Module):
 
     def _forward_impl(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         return ops.om_causal_fwd(q, k, v, self.scale)
+
+
+# --------------------------------------------------------------------------- tensor-level entry points
+# What the catopt-facing modules of ``sink.py`` run once their operand terms are
+# evaluated; kept free of catopt imports so the GPU parity tests can call them.
+def kernel_chunk(T: int, plan_chunk: int | None = None) -> int | None:
+    """Chunk length handed to the decayed kernel: the plan's own when the term was
+    uniform, else the largest divisor of T up to 128 (the value does not depend on
+    it); ``None`` when T only has tiny divisors (a long prime-ish sequence)."""
+    if plan_chunk:
+        return plan_chunk
+    for c in range(min(128, T), 0, -1):
+        if T % c == 0:
+            return c if (c >= 16 or T <= 64) else None
+    return None
+
+
+def decayed_whole_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: Any, chunk: int | None,
+                           scale: float) -> torch.Tensor | None:
+    """Decayed attention of ``[..., H, T, d]`` tensors (any number of leading axes,
+    the last one indexing the decay rates) through ``cb2_decayed_chunk_fwd``.
+    Returns ``None`` when the kernel has no path (fp64, awkward length)."""
+    if not q.is_cuda:
+        raise B200Error("decayed executor runs on CUDA tensors only (no CPU fallback)")
+    lead = q.shape[:-2]
+    if len(lead) == 0:
+        raise B200Error("decayed executor needs at least one leading (head) axis")
+    c = kernel_chunk(q.shape[-2], chunk)
+    if c is None or q.dtype not in (torch.float32, torch.bfloat16):
+        return None
+    H = lead[-1]
+    g = torch.as_tensor(gamma, dtype=torch.float32, device=q.device).reshape(-1)
+    g = (g.expand(H) if g.numel() == 1 else g).contiguous()
+    q4, k4, v4 = (t.reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous() for t in (q, k, v))
+    out = ops.decayed_chunk_fwd(q4, k4, v4, g, c, scale)
+    return out.reshape(*lead, out.shape[-2], out.shape[-1])
+
+
+def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale: float) -> torch.Tensor | None:
+    """Causal softmax attention of ``q [..., Tq, d]`` over key/value blocks joined
+    along the key axis, through ``cb2_om_causal_fwd``; ``None`` for fp64."""
+    if not q.is_cuda:
+        raise B200Error("causal softmax executor runs on CUDA tensors only (no CPU fallback)")
+    if q.dtype not in (torch.float32, torch.bfloat16):
+        return None
+    k = k_blocks[0] if len(k_blocks) == 1 else torch.cat(list(k_blocks), dim=-2)
+    v = v_blocks[0] if len(v_blocks) == 1 else torch.cat(list(v_blocks), dim=-2)
+    lead = q.shape[:-2]
+    H = lead[-1] if lead else 1
+    q4, k4, v4 = (t.expand(*lead, *t.shape[-2:]).reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous()
+                  for t in (q, k, v))
+    out = ops.om_causal_fwd(q4, k4, v4, scale)
+    return out.reshape(*lead, out.shape[-2], out.shape[-1])

@@ -3,7 +3,7 @@
 catopt routes an extracted term to the first ``ExecutorSpec`` of
 ``Sink.executors`` whose ``carrier`` is not ``None`` and whose ``accepts(term)``
 is true (catopt_orchestrator/optimize.py:485-495); mapping order is routing
-order.  ``B200Sink`` puts three B200 specs in front of the torch ones:
+order.  ``B200Sink`` puts four B200 specs in front of the torch ones:
 
 * ``b200_om_decayed_chunked`` — the uniform K-chunk decayed term of
   ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152).  ``accepts``
@@ -17,6 +17,9 @@ order.  ``B200Sink`` puts three B200 specs in front of the torch ones:
   of 32,32,32,32,128,128,128 rows, which the reference's executor declines — are
   recognised by ``decayed_ragged_plan``.  Anything else is declined, so the
   reference's pairwise executor (or the generic module) still takes it.
+* ``b200_om_causal`` — causal softmax attention over a sequence of key/value blocks in
+  its online-softmax carrier form ``om_apply(<om_compose tree of om_elem(masked
+  scores_i, v_i)>)`` (``om_causal_plan``); one ``cb2_om_causal_fwd``.
 * ``b200_scan`` — diagonal ``applyd(<aff_diag tree>, h)`` scan applications (the
   terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
   leaf stacking are reused, the composed-map reduction runs in
@@ -46,11 +49,11 @@ from catopt_torch.torch_bridge import IRModule
 from . import ops
 from . import verify as b200_verify
 from ._lib import B200Error
-from .executors import _GraphMixin
+from .executors import _GraphMixin, causal_softmax_blocks, decayed_whole_sequence
 
 __all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "decayed_ragged_plan",
-           "decayed_plan", "linear_chain_plan", "scan_diag_plan",
-           "B200ChunkedDecayModule", "B200LinearChainModule"]
+           "decayed_plan", "om_causal_plan", "linear_chain_plan", "scan_diag_plan",
+           "B200ChunkedDecayModule", "B200CausalSoftmaxModule", "B200LinearChainModule"]
 
 
 # --------------------------------------------------------------------------- decayed
@@ -436,17 +439,6 @@ def decayed_plan(root: Any) -> dict | None:
     return plan if plan is not None else decayed_ragged_plan(root)
 
 
-def _kernel_chunk(T: int, plan_chunk: int | None) -> int | None:
-    """Chunk length handed to the kernel: the plan's own when uniform, else the
-    largest divisor of T up to 128 (the value does not depend on it)."""
-    if plan_chunk:
-        return plan_chunk
-    for c in range(min(128, T), 0, -1):
-        if T % c == 0:
-            return c if (c >= 16 or T <= 64) else None
-    return None
-
-
 class _EvalBase(_GraphMixin, torch.nn.Module):
     """Shared plumbing: embedded ``IRModule`` + operand evaluation."""
 
@@ -496,20 +488,122 @@ class B200ChunkedDecayModule(_EvalBase):
             return self.eval_mod(*xs)
         ev = self._ev(xs)
         q, k, v, g = ev(plan["q"]), ev(plan["k"]), ev(plan["v"]), ev(plan["gamma"])
-        lead = q.shape[:-2]
-        if len(lead) == 0:
-            raise B200Error("decayed executor needs at least one leading (head) axis")
-        H = lead[-1]
-        g = torch.as_tensor(g, dtype=torch.float32, device=q.device).reshape(-1)
-        g = (g.expand(H) if g.numel() == 1 else g).contiguous()
-        if not q.is_cuda:
-            raise B200Error("decayed executor runs on CUDA tensors only (no CPU fallback)")
-        chunk = _kernel_chunk(q.shape[-2], plan["chunk"])
-        if chunk is None or q.dtype not in (torch.float32, torch.bfloat16):
-            return self.eval_mod(*xs)      # awkward length / fp64: the generic module, same device
-        q4, k4, v4 = (t.reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous() for t in (q, k, v))
-        out = ops.decayed_chunk_fwd(q4, k4, v4, g, chunk, plan["scale"])
-        return out.reshape(*lead, out.shape[-2], out.shape[-1])
+        out = decayed_whole_sequence(q, k, v, g, plan["chunk"], plan["scale"])
+        return self.eval_mod(*xs) if out is None else out     # fp64 / awkward length: generic module, same device
+
+
+# --------------------------------------------------------------------------- om causal
+def _scaled_scores(t: Any) -> tuple | None:
+    """Scores of one key block -> (q, k, scale).  Spellings: ``matmul(q, k^T)``
+    (scale 1) and the one the sdpa-over-concat laws leave behind,
+    ``om_decayed(q, fill(q, value=scale), k^T)`` = ``(q * scale) @ k^T``."""
+    if not isinstance(t, Op):
+        return None
+    if t.op == "matmul" and len(t.args) == 2 and _is_swap_last_two(t.args[1]):
+        return t.args[0], t.args[1].args[0], 1.0
+    if t.op == "om_decayed" and len(t.args) == 3 and _is_swap_last_two(t.args[2]):
+        q, f = t.args[0], t.args[1]
+        if isinstance(f, Op) and f.op == "fill" and len(f.args) == 1 and f.args[0] == q \
+                and isinstance(f.attrs.get("value"), (int, float)):
+            return q, t.args[2].args[0], float(f.attrs["value"])
+    return None
+
+
+def om_causal_plan(root: Any) -> dict | None:
+    """Recognise causal softmax attention over a sequence of key/value blocks in
+    its online-softmax carrier form (the member the ``sdpa_cat_causal`` laws add,
+    tests/test_om_causal.py:286-330 of the reference):
+
+        om_apply(<om_compose tree of om_elem(masked_fill(S_i, M_i, -inf), v_i)>)
+
+    with ``S_i = (q * scale) @ k_i^T`` and ``M_i`` the columns ``[o_i, o_i + n_i)``
+    of ``cmask(<any [.., Tq, sum n] tensor>)`` (bad where ``j > t``; o_i the keys
+    before block i).  Leaves are read left to right = key order; every block must
+    share q and the scale and appear once.  Returns ``{q, k_blocks, v_blocks,
+    sizes, scale, n}`` or ``None`` (unmasked carriers, offset masks, explicit
+    attention biases: the reference's own om executors keep them)."""
+    if not (isinstance(root, Op) and root.op == "om_apply" and len(root.args) == 1):
+        return None
+    leaves = _flatten(root.args[0], "om_compose")
+    if len(leaves) < 2 or len(set(leaves)) != len(leaves):
+        return None
+    memo: dict = {}
+    q = scale = None
+    ks, vs, sizes, pos, total = [], [], [], 0, None
+    for leaf in leaves:
+        if not (isinstance(leaf, Op) and leaf.op == "om_elem" and len(leaf.args) == 2):
+            return None
+        mf, v = leaf.args
+        if not (isinstance(mf, Op) and mf.op == "masked_fill" and len(mf.args) == 3
+                and _const_value(mf.args[2]) == float("-inf")):
+            return None
+        sc = _scaled_scores(mf.args[0])
+        kshape = None if sc is None else _shape_of(sc[1], memo)
+        if sc is None or not isinstance(kshape, tuple) or len(kshape) < 2 or not isinstance(kshape[-2], int):
+            return None
+        n_i = kshape[-2]
+        if q is None:
+            q, scale = sc[0], sc[2]
+        elif sc[0] != q or sc[2] != scale:
+            return None
+        # the mask: columns [pos, pos + n_i) of one cmask over the whole score tensor
+        m = mf.args[1]
+        r = _range_of(m, -1, memo)
+        if r is None:
+            return None
+        base, start, length, tot = r
+        if not (isinstance(base, Op) and base.op == "cmask" and int(base.attrs.get("off", 0) or 0) == 0):
+            return None
+        if (start, length) != (pos, n_i) or (total is not None and tot != total):
+            return None
+        total = tot
+        ks.append(sc[1])
+        vs.append(v)
+        sizes.append(n_i)
+        pos += n_i
+    if pos != total:
+        return None
+    return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(ks)}
+
+
+def _flatten(t: Any, op: str) -> list:
+    """Leaves of a nested tree of ``op`` nodes, left to right."""
+    if isinstance(t, Op) and t.op == op:
+        out: list = []
+        for a in t.args:
+            out.extend(_flatten(a, op))
+        return out
+    return [t]
+
+
+class B200CausalSoftmaxModule(_EvalBase):
+    """Drop-in for ``BatchedOMModule`` / ``StreamingOMModule``
+    (catopt_carriers/om_lower.py:729-835, 996-1040) on the causal carrier: the
+    key/value blocks are joined along the key axis (they are the pieces of a
+    ``concat`` in the source program) and one ``cb2_om_causal_fwd`` replaces the
+    per-block softmax triples and their pairwise merges.  A non-matching IR
+    degrades to ``eval_mod``."""
+
+    def __init__(self, ir: IR, param_values: dict | None = None) -> None:
+        super().__init__(ir, param_values)
+        self._plan = om_causal_plan(self.eval_mod._root)
+
+    @property
+    def is_batched(self) -> bool:
+        return self._plan is not None
+
+    @property
+    def n_blocks(self) -> int:
+        return 0 if self._plan is None else self._plan["n"]
+
+    def _forward_impl(self, *xs: torch.Tensor) -> Any:
+        plan = self._plan
+        if plan is None:
+            return self.eval_mod(*xs)
+        ev = self._ev(xs)
+        out = causal_softmax_blocks(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
+                                    [ev(t) for t in plan["v_blocks"]], plan["scale"])
+        return self.eval_mod(*xs) if out is None else out     # fp64: generic module, same device
 
 
 # --------------------------------------------------------------------------- linear chain
@@ -657,6 +751,13 @@ class B200Sink(TorchSink):
                     _engaged,
                     (frozenset({"concat"}), frozenset({"add", "mul", "div", "matmul"}),
                      frozenset({"om_decayed", "decay", "decay_vec"})),
+                ),
+                "b200_om_causal": ExecutorSpec(
+                    "b200_om_causal",
+                    lambda ir, p: B200CausalSoftmaxModule(ir, param_values=p),
+                    lambda term: om_causal_plan(term) is not None,
+                    _engaged,
+                    (frozenset({"om_apply"}), frozenset({"om_compose"}), frozenset({"om", "om_elem"})),
                 ),
                 "b200_scan": ExecutorSpec(
                     "b200_scan",

@@ -473,6 +473,48 @@ def test_om_causal_bf16_tensor_core_path(dev, B, H, Tq, Tk, dk, dv):
     assert rel_to_max(out, want) <= BF16_TOL
 
 
+def test_causal_softmax_blocks_entry_point(dev):
+    """What the catopt-facing causal module runs after evaluating its operands:
+    key/value blocks of uneven sizes joined on the key axis, rank-3 and rank-4
+    operands, fp32 and bf16."""
+    from catopt_b200.executors import causal_softmax_blocks
+
+    g = torch.Generator().manual_seed(11)
+    for lead, sizes, Tq, dt, tol in (((2, 3), (5, 9, 130), 144, torch.float32, FP32_TOL),
+                                     ((4,), (128, 128), 256, torch.bfloat16, BF16_TOL),
+                                     ((), (3, 4), 1, torch.float32, FP32_TOL)):
+        q = torch.randn(*lead, Tq, 32, generator=g).to(dt)
+        ks = [torch.randn(*lead, n, 32, generator=g).to(dt) for n in sizes]
+        vs = [torch.randn(*lead, n, 16, generator=g).to(dt) for n in sizes]
+        out = causal_softmax_blocks(q.to(dev), [t.to(dev) for t in ks], [t.to(dev) for t in vs], 0.25)
+        want = oracle.om_causal_chunked(q.double(), torch.cat(ks, -2).double(), torch.cat(vs, -2).double(),
+                                        list(sizes), 0.25)
+        assert out.shape == want.shape and out.dtype == dt
+        assert rel_to_max(out, want) <= tol
+    assert causal_softmax_blocks(q.double().to(dev), [t.double().to(dev) for t in ks],
+                                 [t.double().to(dev) for t in vs], 0.25) is None
+
+
+def test_decayed_whole_sequence_entry_point(dev):
+    """What the catopt-facing decayed module runs for a ragged partition: no chunk
+    from the plan (the kernel picks one), rank-3 operands with a scalar rate,
+    rank-4 with per-head rates."""
+    from catopt_b200.executors import decayed_whole_sequence
+
+    g = torch.Generator().manual_seed(12)
+    q, k, v = (torch.randn(2, 320, 16, generator=g) / 2 for _ in range(3))       # [B, T, d]: T = 320 -> chunk 80
+    out = decayed_whole_sequence(q.to(dev), k.to(dev), v.to(dev), torch.tensor(0.9), None, 4.0)
+    want = oracle.decayed_quadratic(q.double()[None], k.double()[None], v.double()[None],
+                                    torch.tensor(0.9, dtype=torch.float64), 4.0)[0]
+    assert out.shape == (2, 320, 16) and rel_to_max(out, want) <= FP32_TOL
+    q, k, v = (torch.randn(2, 3, 256, 64, generator=g).bfloat16() for _ in range(3))
+    gam = torch.tensor([0.9, 0.97, 0.995])
+    out = decayed_whole_sequence(q.to(dev), k.to(dev), v.to(dev), gam.to(dev), None, 8.0)
+    want = oracle.decayed_quadratic(q.double(), k.double(), v.double(), gam.double(), 8.0)
+    assert rel_to_max(out, want) <= BF16_TOL
+    assert decayed_whole_sequence(q.double().to(dev), k.double().to(dev), v.double().to(dev), gam, None, 1.0) is None
+
+
 def test_device_status_clean(dev):
     """No kernel in this file ran into a bounded-wait timeout."""
     from catopt_b200 import ops

@@ -33,7 +33,7 @@ def _route(sink, term):
 def test_b200_specs_come_first_and_are_executor_specs():
     s = b200.B200Sink()
     names = list(s.executors)
-    assert names[:3] == ["b200_om_decayed_chunked", "b200_scan", "b200_linear_chain"]
+    assert names[:4] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_scan", "b200_linear_chain"]
     assert "om_decayed_chunked" in names and names[-1] == "generic"
     assert all(isinstance(v, ExecutorSpec) for v in s.executors.values())
 
@@ -127,7 +127,7 @@ def _scan_term(T=6, d=8):
 def test_scan_term_routes_to_b200_scan_and_keeps_reference_plan():
     ir = _scan_term()
     s = b200.B200Sink()
-    assert list(s.executors)[:3] == ["b200_om_decayed_chunked", "b200_scan", "b200_linear_chain"]
+    assert "b200_scan" in list(s.executors)[:4]
     spec = _route(s, ir.root)
     assert spec.name == "b200_scan"
     vals = {"a": torch.full((8,), 0.9), "h0": torch.ones(8)}
@@ -283,9 +283,11 @@ def test_ragged_lookalikes_are_declined():
 
 
 def test_kernel_chunk_choice():
-    assert b200._kernel_chunk(512, None) == 128 and b200._kernel_chunk(512, 64) == 64
-    assert b200._kernel_chunk(96, None) == 96 and b200._kernel_chunk(320, None) == 80
-    assert b200._kernel_chunk(1021, None) is None and b200._kernel_chunk(61, None) == 61
+    from catopt_b200.executors import kernel_chunk
+
+    assert kernel_chunk(512, None) == 128 and kernel_chunk(512, 64) == 64
+    assert kernel_chunk(96, None) == 96 and kernel_chunk(320, None) == 80
+    assert kernel_chunk(1021, None) is None and kernel_chunk(61, None) == 61
 
 
 def test_real_extraction_of_the_kway_carrier_routes_to_b200():
@@ -348,3 +350,118 @@ def test_real_extraction_of_the_kway_carrier_routes_to_b200():
         want = model(x)
     got = oracle.decayed_quadratic(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), g.reshape(()), plan["scale"])[0]
     assert (got - want).abs().max().item() < 1e-10
+
+
+# --------------------------------------------------------------------------- om causal carrier
+def _om_causal_term(ksizes, Tq, d=4, dv=6, batch=(2, 3), scale=0.5, right_nested=True, off=None):
+    """Hand-built carrier of causal attention over key blocks, in the form the
+    sdpa-over-concat laws produce."""
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    q = Var("q", tt(*batch, Tq, d))
+    ks = [Var(f"k{i}", tt(*batch, n, d)) for i, n in enumerate(ksizes)]
+    vs = [Var(f"v{i}", tt(*batch, n, dv)) for i, n in enumerate(ksizes)]
+
+    def scores(k):
+        return Op.make("om_decayed", q, Op.make("fill", q, value=scale), Op.make("transpose", k, dim0=-2, dim1=-1))
+
+    kall = ks[0]
+    for k in ks[1:]:
+        kall = Op.make("concat", kall, k, dim=-2)
+    cm = Op.make("cmask", scores(kall)) if off is None else Op.make("cmask", scores(kall), off=off)
+    rank = len(batch) + 2
+    leaves = [Op.make("om_elem", Op.make("masked_fill", scores(k), Op.make("split", cm, dim=rank - 1, index=i,
+                                                                         sizes=tuple(ksizes)), Const(float("-inf"))), v)
+              for i, (k, v) in enumerate(zip(ks, vs))]
+    if right_nested:
+        tree = leaves[-1]
+        for lf in reversed(leaves[:-1]):
+            tree = Op.make("om_compose", lf, tree)
+    else:
+        tree = leaves[0]
+        for lf in leaves[1:]:
+            tree = Op.make("om_compose", tree, lf)
+    inputs = [q, *ks, *vs]
+    return IR(root=Op.make("om_apply", tree), inputs=inputs, input_names={v.name for v in inputs}, params={}), leaves
+
+
+@pytest.mark.parametrize("ksizes,Tq", [((4, 4, 4), 12), ((3, 6), 5), ((1, 8), 9), ((2, 3, 4), 1)])
+@pytest.mark.parametrize("right_nested", [True, False])
+def test_om_causal_carrier_is_recognised_and_means_causal_attention(ksizes, Tq, right_nested):
+    import torch.nn.functional as F
+    from catopt_torch.torch_bridge import IRModule
+
+    ir, _ = _om_causal_term(ksizes, Tq, right_nested=right_nested)
+    plan = b200.om_causal_plan(ir.root)
+    assert plan is not None and plan["sizes"] == tuple(ksizes) and plan["scale"] == 0.5
+    assert plan["q"].name == "q" and [k.name for k in plan["k_blocks"]] == [f"k{i}" for i in range(len(ksizes))]
+    assert [v.name for v in plan["v_blocks"]] == [f"v{i}" for i in range(len(ksizes))]
+    assert _route(b200.B200Sink(), ir.root).name == "b200_om_causal"
+    # the hand-built term evaluates (reference bindings, fp64) to torch's causal attention
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(2, 3, Tq, 4, dtype=torch.float64, generator=gen)
+    ks = [torch.randn(2, 3, n, 4, dtype=torch.float64, generator=gen) for n in ksizes]
+    vs = [torch.randn(2, 3, n, 6, dtype=torch.float64, generator=gen) for n in ksizes]
+    with torch.no_grad():
+        got = IRModule(ir, None)(q, *ks, *vs)
+    want = F.scaled_dot_product_attention(q, torch.cat(ks, -2), torch.cat(vs, -2), is_causal=True, scale=0.5)
+    assert (got - want).abs().max().item() < 1e-12
+    # and the oracle the GPU kernel is tested against agrees on the joined blocks
+    from oracle import oracle
+
+    o = oracle.om_causal_chunked(q, torch.cat(ks, -2), torch.cat(vs, -2), list(ksizes), 0.5)
+    assert (o - want).abs().max().item() < 1e-12
+
+
+def test_om_causal_lookalikes_are_declined():
+    ir, leaves = _om_causal_term((4, 4, 4), 12)
+    s = b200.B200Sink()
+    # masks in the wrong order, a duplicated block, an offset mask, an unmasked carrier
+    a, b_, c = leaves
+    assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", b_, Op.make("om_compose", a, c)))) is None
+    assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", a, Op.make("om_compose", a, c)))) is None
+    assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", a, b_))) is None      # keys 8..12 missing
+    shifted, _ = _om_causal_term((4, 4, 4), 12, off=1)
+    assert b200.om_causal_plan(shifted.root) is None
+    plain = Op.make("om_apply", Op.make("om_compose", *[Op.make("om_elem", lf.args[0].args[0], lf.args[1])
+                                                         for lf in leaves[:2]]))
+    assert b200.om_causal_plan(plain) is None
+    assert _route(s, plain).name in ("om_batched", "om_streaming")
+    # different scale on one block
+    other, ol = _om_causal_term((4, 4, 4), 12, scale=0.25)
+    assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", a, Op.make("om_compose", ol[1], c)))) is None
+
+
+def test_om_causal_module_conforms_and_refuses_cpu():
+    ir, _ = _om_causal_term((4, 4), 8)
+    spec = b200.B200Sink().executors["b200_om_causal"]
+    mod = spec.lower(ir, None)
+    assert isinstance(mod, BatchedExecutor) and spec.engaged(mod) and mod.n_blocks == 2
+    from catopt_b200 import B200Error
+
+    q = torch.randn(2, 3, 8, 4)
+    ks = [torch.randn(2, 3, 4, 4) for _ in range(2)]
+    vs = [torch.randn(2, 3, 4, 6) for _ in range(2)]
+    with pytest.raises(B200Error):
+        mod(q, *ks, *vs)
+
+
+def test_om_causal_real_saturation_member_is_accepted():
+    """Saturate sdpa(q, cat k, cat v, is_causal) with the reference's om laws
+    and force-extract the chunked carrier with the reference's own test helper
+    (tests/test_om_causal.py:128-160 there); the B200 spec must take it."""
+    import importlib.util
+
+    path = os.path.join(_REF, "tests", "test_om_causal.py")
+    if not os.path.exists(path):
+        pytest.skip("reference test helpers not available")
+    spec = importlib.util.spec_from_file_location("_ref_test_om_causal", path)
+    helper = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(helper)
+    for ksizes, kw in (((3, 6), {}), ((2, 3, 4), {}), ((2, 5), {"batch": (2, 3)}), ((3, 6), {"scale": 0.25})):
+        _, term, _, _, _ = helper._causal_chunked_ok(list(ksizes), **kw)
+        plan = b200.om_causal_plan(term)
+        assert plan is not None and plan["sizes"] == tuple(ksizes), (ksizes, kw)
+        assert _route(b200.B200Sink(), term).name == "b200_om_causal"
+    # the unmasked companion carrier stays with the reference's executors
+    _, term, _, _, _ = helper._causal_chunked_ok([3, 6], causal=False)
+    assert b200.om_causal_plan(term) is None
