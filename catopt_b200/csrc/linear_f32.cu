@@ -20,9 +20,10 @@
 namespace cb2 {
 // tensor-core path for large row counts (linear_tf32x3.cu)
 bool linear_tf32x3_supported(const float* x, const float* w, const float* bias, const float* y, int R,
-                             int n_in, int n_out);
+                             int n_in, int n_out, const void* scratch, size_t scratch_bytes);
+size_t linear_tf32x3_scratch_bytes(int n_in, int n_out);
 int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* y, int R, int n_in,
-                      int n_out, int* dev_status, cudaStream_t st);
+                      int n_out, void* scratch, int* dev_status, cudaStream_t st);
 
 namespace {
 
@@ -310,6 +311,10 @@ extern "C" size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_f
   // Split-K partials are normally reduced through distributed shared memory
   // (clusters of up to 8 CTAs); the scratch is only used if a cluster launch is
   // refused, and the call works without it.
+  // The tensor-core path (large R) needs scratch for w split into its TF32 hi/lo
+  // parts; without it the call runs on the FMA pipes.
+  if (R >= 256 && in_features <= 1024 && in_features % 4 == 0 && out_features % 4 == 0)
+    return cb2::linear_tf32x3_scratch_bytes(in_features, out_features);
   const int splits = cb2::pick_splits(R, out_features, in_features);
   return splits > 1 ? size_t(8) * R * out_features * sizeof(float) : 0;
 }
@@ -319,8 +324,8 @@ extern "C" int cb2_linear_f32(const float* x, const float* w, const float* bias,
                               size_t scratch_bytes, void* stream) {
   if (!x || !w || !y) return CB2_NULL_PTR;
   if (R <= 0 || in_features <= 0 || out_features <= 0) return CB2_BAD_SHAPE;
-  if (cb2::linear_tf32x3_supported(x, w, bias, y, R, in_features, out_features))
-    return cb2::linear_tf32x3_run(x, w, bias, y, R, in_features, out_features, nullptr,
+  if (cb2::linear_tf32x3_supported(x, w, bias, y, R, in_features, out_features, scratch, scratch_bytes))
+    return cb2::linear_tf32x3_run(x, w, bias, y, R, in_features, out_features, scratch, nullptr,
                                   static_cast<cudaStream_t>(stream));
   return cb2::gemm<true>(x, w, bias, y, R, out_features, in_features,
                          static_cast<float*>(scratch), scratch_bytes,

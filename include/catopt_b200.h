@@ -82,8 +82,10 @@ int cb2_verify_reduce(const void* ref, const void* out, int64_t numel_per_seg,
  * Large row counts (R >= 256, in <= 1024, in/out multiples of 4, 16-byte aligned pointers)
  * run on the tensor cores with three-pass TF32 splitting; small ones on the
  * fp32 FMA pipes with the reduction axis split across a thread-block cluster.
- * scratch: optional split-K partial sums (cb2_linear_f32_scratch_bytes bytes),
- * used only if the cluster launch is refused; may be NULL.
+ * scratch (cb2_linear_f32_scratch_bytes bytes, 16-byte aligned) may be NULL:
+ * the tensor-core path needs it (w split into TF32 hi/lo parts once per call)
+ * and without it the call runs on the FMA pipes, slower but to the same
+ * tolerance; the FMA path uses it only if a cluster launch is refused.
  * ------------------------------------------------------------------------- */
 size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_features);
 int cb2_linear_f32(const float* x, const float* w, const float* bias, float* y,
