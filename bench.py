@@ -304,17 +304,21 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
                                              flops=4 * B * T * D)
     del a3, a3s, x3, y3
 
-    # causal online-softmax executor (no config of its own in the benchmark spec): B=2 H=8 T=2048 d=128 bf16
-    qo, ko, vo = (_randn_bf16((16, 2048 * 128), gen).view(2, 8, 2048, 128) for _ in range(3))
-    oo = torch.empty_like(vo)
-    ms = time_steps(lambda: ops.om_causal_fwd(qo, ko, vo, out=oo), K, W, world, flush)
-    e = entry(ms, 2 * 2048, 4 * 16 * 2048 * 128 * 2, 1,
-              "tcgen05 online-softmax kernel; causal FLOPs (lower triangle) against the burst bf16 peak; "
-              "L2 flushed between steps", flops=4 * 16 * (2048 * 2049 // 2) * 128)
-    e["roofline"] = {"bound": "tensor", "achieved": e["tflops"], "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": e["tflops"] / pk["bf16_tflops"], "traffic": None}
-    out["om_causal_bf16_B2_H8_T2048_d128"] = e
-    del qo, ko, vo, oo
+    # causal online-softmax executor (no config of its own in the benchmark spec), bf16, d=128:
+    # a long-sequence case that fills the GPU (268 MB > L2) and a short one (256 CTAs: tail-bound)
+    for (Bo, Ho, To) in ((1, 32, 8192), (2, 8, 2048)):
+        qo, ko, vo = (_randn_bf16((Bo * Ho, To * 128), gen).view(Bo, Ho, To, 128) for _ in range(3))
+        oo = torch.empty_like(vo)
+        ms = time_steps(lambda: ops.om_causal_fwd(qo, ko, vo, out=oo), K, W, world,
+                        flush if To < 8192 else None)
+        e = entry(ms, Bo * To, 4 * Bo * Ho * To * 128 * 2, 1,
+                  "tcgen05 online-softmax kernel; causal FLOPs (lower triangle) against the burst bf16 peak; "
+                  + ("inputs exceed L2" if To >= 8192 else "L2 flushed between steps"),
+                  flops=4 * Bo * Ho * (To * (To + 1) // 2) * 128)
+        e["roofline"] = {"bound": "tensor", "achieved": e["tflops"], "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": e["tflops"] / pk["bf16_tflops"], "traffic": None}
+        out[f"om_causal_bf16_B{Bo}_H{Ho}_T{To}_d128"] = e
+        del qo, ko, vo, oo
 
     # config 5: verify 13 checks x 256 probes x [4,512,1024] bf16; probes sharded over ranks
     p0, p1 = shard_range(256, rank, world)
@@ -461,8 +465,8 @@ def run_profile_case(args) -> None:
         c = (torch.randn(D, N, device=dev, generator=gen) / 4).bfloat16()
         y = torch.empty_like(x)
         fn = lambda: ops.diag_scan_fwd(a, x, b, c, None, out=y)  # noqa: E731
-    elif args.profile_case == "om_causal":    # B=2 H=8 T=2048 d=128 bf16 (34 MB; compute-bound)
-        q, k, v = (_randn_bf16((16, 2048 * 128), gen).view(2, 8, 2048, 128) for _ in range(3))
+    elif args.profile_case == "om_causal":    # B=1 H=32 T=8192 d=128 bf16 (268 MB; tensor-bound)
+        q, k, v = (_randn_bf16((32, 8192 * 128), gen).view(1, 32, 8192, 128) for _ in range(3))
         o = torch.empty_like(v)
         fn = lambda: ops.om_causal_fwd(q, k, v, out=o)  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB

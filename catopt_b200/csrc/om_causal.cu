@@ -175,8 +175,8 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
   const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
   const dim3 grid((Tq + kBlk - 1) / kBlk, B * H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) &&
-      aligned16(o))
+  if (om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) && aligned16(k) &&
+      aligned16(v) && aligned16(o))
     return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, dev_status, st);
   if (dtype == CB2_BF16) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -3,37 +3,43 @@
 // catopt_torch/torch_bridge.py:1974-2006) folded over 128-key blocks, with the
 // running (max, sum) pair in registers and the weighted sum in tensor memory.
 //
-// CTA = 128 queries of one (batch, head).  Per key block j (causal: j <= i):
-//   MMA1  S_j = Q K_j^T                         -> TMEM, double-buffered
-//   WG    m' = max(m, rowmax S_j); P = exp(S_j - m') as bf16, written over S_j;
-//         l = l e^(m-m') + rowsum P;  O <- O e^(m-m')   (skipped by a warp whose
-//         rows all kept their maximum)
+// CTA = 128 queries of one (batch, head); two CTAs share an SM (each takes half
+// of the tensor memory and of the shared memory), so one CTA's softmax runs
+// while the other's products are on the tensor core.  Per key block j (causal:
+// j <= i):
+//   MMA1  S_j = Q K_j^T                         -> TMEM
+//   WG    the row's 128 scores come to registers in one batch of TMEM loads;
+//         m' = max(m, rowmax S_j); P = exp(S_j - m') as bf16, written over S_j;
+//         l = l e^(m-m') + rowsum P;  O <- O e^(m-m').  The reference point m
+//         follows the maximum lazily (only after it moved by 2^8), so the O
+//         rescale is rare; a warp whose rows all kept theirs skips it
 //   MMA2  O += P V_j      (A operand read from TMEM, V_j MN-major from its tile)
 // and finally o = O / l through a staging tile and a TMA store.  Entirely masked
 // blocks are never visited; a partially masked block (the diagonal one, or the
 // last one when Tk is ragged) masks per element.  Thread = one query row (one
 // TMEM lane), so the row maxima and sums need no cross-thread traffic.
 //
-// Roles: warp 0 = TMA producer (Q once, then K_j / V_j tiles through a 5-slot
-// ring; 3-D tensor maps clip and zero-fill per head), warp 1 = MMA issuer and
-// TMEM owner, warps 2..5 = softmax group.  Every wait is bounded.
+// Roles: warp 0 = TMA producer (Q once, then K_j / V_j tiles alternating between
+// two slots; 3-D tensor maps clip and zero-fill per head), warp 1 = MMA issuer
+// and TMEM owner, warps 2..5 = softmax group.  Every wait is bounded.
 #include "umma.cuh"
 
 namespace cb2 {
 namespace {
 
 constexpr int kQ = 128;                   // queries per CTA = keys per block
-constexpr int kSlots = 5;
+constexpr int kSlots = 2;                 // slot 0: K_j, slot 1: V_j
 constexpr int kThreads = 192;
 constexpr uint32_t kTile = umma::kTileBytes;
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffRing = kTile;
-constexpr uint32_t kOffO = kOffRing + kSlots * kTile;
-constexpr uint32_t kOffBars = kOffO + kTile;
-constexpr int kNumBars = 2 * kSlots + 6;
+constexpr uint32_t kOffO = kOffQ;         // the output is staged over Q once the last scores are out
+constexpr uint32_t kOffBars = kOffRing + kSlots * kTile;
+constexpr int kNumBars = 2 * kSlots + 5;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
-constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;   // 97.4 KiB: two CTAs per SM
+constexpr uint32_t kColS = 0, kColO = 128;
+constexpr uint32_t kTmemCols = 256;
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -41,26 +47,29 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                    int Tq, int Tk, int dv, float scale_log2e, int* dev_status) {
+                    int Tq, int Tk, int dk, int dv, int n_bh, float scale_log2e, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint64_t* full = bars;                         // [kSlots] TMA -> MMA
   uint64_t* empty = bars + kSlots;               // [kSlots] MMA -> TMA
   uint64_t* q_full = bars + 2 * kSlots;
-  uint64_t* s_ready = bars + 2 * kSlots + 1;     // [2] MMA1 done (per S buffer)
-  uint64_t* p_ready = bars + 2 * kSlots + 3;     // P written, O rescaled (128 arrivals)
-  uint64_t* o_done = bars + 2 * kSlots + 4;      // MMA2 done
-  uint64_t* wg_sync = bars + 2 * kSlots + 5;     // barrier among the 128 softmax threads
+  uint64_t* s_ready = bars + 2 * kSlots + 1;     // MMA1 done
+  uint64_t* p_ready = bars + 2 * kSlots + 2;     // P written, O rescaled (128 arrivals)
+  uint64_t* o_done = bars + 2 * kSlots + 3;      // MMA2 done
+  uint64_t* wg_sync = bars + 2 * kSlots + 4;     // barrier among the 128 softmax threads
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int qb = gridDim.x - 1 - blockIdx.x;     // heaviest (latest) query blocks first
+  // CTAs are handed out in launch order: the latest query blocks of EVERY head
+  // first (they visit the most key blocks), the cheap early ones last, which keeps
+  // the tail of the grid short
+  const int bh = blockIdx.x % n_bh;
+  const int qb = int(gridDim.x / n_bh) - 1 - int(blockIdx.x / n_bh);
   const int q0 = qb * kQ;
   const int nkb = min((Tk + kQ - 1) / kQ, qb + 1);   // key blocks with at least one visible key
 
@@ -70,8 +79,7 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_init(&empty[s], 1);
     }
     mbar_init(q_full, 1);
-    mbar_init(&s_ready[0], 1);
-    mbar_init(&s_ready[1], 1);
+    mbar_init(s_ready, 1);
     mbar_init(p_ready, 128);
     mbar_init(o_done, 1);
     mbar_init(wg_sync, 128);
@@ -80,7 +88,7 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   }
   if (warp == 1) {
     __syncwarp();
-    umma::tmem_alloc(s_tmem, 512);
+    umma::tmem_alloc(s_tmem, kTmemCols);
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -110,38 +118,41 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // narrow heads: only the 16-deep steps that hold real columns of q/k, and an
+      // output as wide as v (a multiple of 16 columns)
+      const int ksteps = (dk + 15) >> 4;
       constexpr uint32_t idesc_kk = umma::instr_desc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_kn = umma::instr_desc_bf16(128, 128, false, true);
+      const uint32_t idesc_kn = umma::instr_desc_bf16(128, uint32_t(dv + 15) & ~15u, false, true);
       auto issue_scores = [&](int j) -> bool {
         const int t = 2 * j, slot = t % kSlots;
         if (!mbar_wait_abortable(&full[slot], (t / kSlots) & 1, s_abort)) return false;
         umma::fence_after_sync();
         const uint32_t k_addr = ring_addr + slot * kTile;
-        const uint32_t col = (j & 1) ? kColS1 : kColS0;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma::mma_bf16(tmem + col, umma::desc_kmajor(q_addr, ks), umma::desc_kmajor(k_addr, ks), idesc_kk,
-                         ks > 0);
-        umma::mma_commit(&s_ready[j & 1]);
+          if (ks < ksteps)
+            umma::mma_bf16(tmem + kColS, umma::desc_kmajor(q_addr, ks), umma::desc_kmajor(k_addr, ks), idesc_kk,
+                           ks > 0);
+        umma::mma_commit(s_ready);
         umma::mma_commit(&empty[slot]);
         return true;
       };
       bool ok = mbar_wait_abortable(q_full, 0, s_abort);
       ok = ok && issue_scores(0);
       for (int j = 0; ok && j < nkb; ++j) {
-        if (j + 1 < nkb && !issue_scores(j + 1)) break;   // overlaps the softmax of block j
         const int t = 2 * j + 1, slot = t % kSlots;
         if (!mbar_wait_abortable(p_ready, j & 1, s_abort)) break;
         if (!mbar_wait_abortable(&full[slot], (t / kSlots) & 1, s_abort)) break;
         umma::fence_after_sync();
         const uint32_t v_addr = ring_addr + slot * kTile;
-        const uint32_t pcol = (j & 1) ? kColS1 : kColS0;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma::mma_bf16_ts(tmem + kColO, tmem + pcol + ks * 8, umma::desc_mnmajor(v_addr, ks), idesc_kn,
+          umma::mma_bf16_ts(tmem + kColO, tmem + kColS + ks * 8, umma::desc_mnmajor(v_addr, ks), idesc_kn,
                             (j > 0) || (ks > 0));
         umma::mma_commit(o_done);
         umma::mma_commit(&empty[slot]);
+        // the tensor pipe runs in issue order, so the next scores may overwrite P right away
+        if (j + 1 < nkb && !issue_scores(j + 1)) break;
       }
     }
   } else {
@@ -150,75 +161,80 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int tq = q0 + r;                         // global query index
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
     unsigned char* o_tile = smem + kOffO;
-    float m_run = -INFINITY, l_run = 0.f;          // in units of scale*log2(e)
-    uint32_t v[32];
+    // m_ref: the reference point of the exponentials (units of scale*log2(e)); it
+    // follows the running maximum lazily, only when the maximum has moved by more
+    // than kLazy, so P stays below 2^kLazy and the O rescale becomes rare.  Any
+    // common reference gives the same o = O / l.
+    constexpr float kLazy = 8.f;
+    float m_ref = -INFINITY, l_run = 0.f;
+    uint32_t sv[4][32];                            // this row's 128 scores, then its O row
+    const int ncb = (dv + 31) >> 5;                // 32-column groups of O that hold output
     for (int j = 0; j < nkb; ++j) {
-      const uint32_t scol = (j & 1) ? kColS1 : kColS0;
-      bool ok = mbar_wait_abortable(&s_ready[j & 1], (j >> 1) & 1, s_abort);
+      constexpr uint32_t scol = kColS;
+      bool ok = mbar_wait_abortable(s_ready, j & 1, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       const int k0 = j * kQ;
       const bool partial = (k0 + kQ - 1 > q0) || (k0 + kQ > Tk);   // uniform over the CTA
-      // pass 1: row maximum of the visible scores
-      float mb = -INFINITY;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        umma::tmem_ld32(lane_base + scol + cb * 32, v);
-        umma::tmem_wait_ld();
-        if (partial) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int key = k0 + cb * 32 + c;
-            if (key <= tq && key < Tk) mb = fmaxf(mb, __uint_as_float(v[c]));
-          }
-        } else {
+      for (int cb = 0; cb < 4; ++cb) umma::tmem_ld32(lane_base + scol + cb * 32, sv[cb]);
+      umma::tmem_wait_ld();
+      // hidden keys (beyond the diagonal or beyond Tk) score -inf: they never win the
+      // maximum and exponentiate to exactly 0 (scale > 0 on this path)
+      if (partial) {
+        const int lim = min(tq, Tk - 1) - k0;                // last visible column of the block
 #pragma unroll
-          for (int c = 0; c < 32; ++c) mb = fmaxf(mb, __uint_as_float(v[c]));
-        }
+        for (int cb = 0; cb < 4; ++cb)
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (cb * 32 + c > lim) sv[cb][c] = 0xff800000u;
       }
-      const float m_new = fmaxf(m_run, mb * scale_log2e);
-      // m_new is finite here: key 0 of block 0 is visible to every query, and a block
-      // that hides all of its keys from this row leaves m unchanged
-      const float alpha = ex2(m_run - m_new);                // 0 on the first block
-      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
-      // pass 2: P = exp2(s*c - m') packed over S, running sum
-      float ps = 0.f;
-#pragma unroll 1
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sv[cb][c]));
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+      float alpha = 1.f;
+      if (m_blk > m_ref + kLazy || m_ref == -INFINITY) {   // (the second test also covers m_blk = -inf)
+        const float m_new = fmaxf(m_ref, m_blk);
+        alpha = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);   // 0 on the first visible block
+        m_ref = m_new;
+      }
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
       for (int cb = 0; cb < 4; ++cb) {
-        umma::tmem_ld32(lane_base + scol + cb * 32, v);
-        umma::tmem_wait_ld();
         uint32_t w[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(v[c]), scale_log2e, neg_m));
-          float p1 = ex2(fmaf(__uint_as_float(v[c + 1]), scale_log2e, neg_m));
-          if (partial) {
-            const int key = k0 + cb * 32 + c;
-            if (!(key <= tq && key < Tk)) p0 = 0.f;
-            if (!(key + 1 <= tq && key + 1 < Tk)) p1 = 0.f;
-          }
-          ps += p0 + p1;
+          const float p0 = ex2(fmaf(__uint_as_float(sv[cb][c]), scale_log2e, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[cb][c + 1]), scale_log2e, neg_m));
+          ps[(c >> 1) & 3] += p0 + p1;
           w[c >> 1] = pack_bf16x2(p0, p1);
         }
         umma::tmem_st16(lane_base + scol + cb * 16, w);       // over columns this thread has consumed
       }
+      l_run = fmaf(l_run, alpha, (ps[0] + ps[1]) + (ps[2] + ps[3]));
       umma::tmem_wait_st();
-      l_run = fmaf(l_run, alpha, ps);
-      m_run = m_new;
       // O <- O * alpha, once the previous block's P.V has landed; skipped by a warp
-      // whose 32 rows all kept their maximum
+      // whose 32 rows all kept their reference point
       if (j > 0) {
         ok = mbar_wait_abortable(o_done, (j - 1) & 1, s_abort);
         if (!__all_sync(0xffffffffu, ok)) break;
         umma::fence_after_sync();
         if (!__all_sync(0xffffffffu, alpha == 1.f)) {
-#pragma unroll 1
-          for (int cb = 0; cb < 4; ++cb) {
-            umma::tmem_ld32(lane_base + kColO + cb * 32, v);
-            umma::tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
-            umma::tmem_st32(lane_base + kColO + cb * 32, v);
+          for (int cb = 0; cb < 4; ++cb)
+            if (cb < ncb) umma::tmem_ld32(lane_base + kColO + cb * 32, sv[cb]);
+          umma::tmem_wait_ld();
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb) {
+            if (cb < ncb) {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) sv[cb][c] = __float_as_uint(__uint_as_float(sv[cb][c]) * alpha);
+              umma::tmem_st32(lane_base + kColO + cb * 32, sv[cb]);
+            }
           }
           umma::tmem_wait_st();
         }
@@ -231,14 +247,17 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (__all_sync(0xffffffffu, ok)) {
       umma::fence_after_sync();
       const float inv_l = 1.f / l_run;
-#pragma unroll 1
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb)
+        if (cb < ncb) umma::tmem_ld32(lane_base + kColO + cb * 32, sv[cb]);
+      umma::tmem_wait_ld();
+#pragma unroll
       for (int cb = 0; cb < 4; ++cb) {
-        umma::tmem_ld32(lane_base + kColO + cb * 32, v);
-        umma::tmem_wait_ld();
+        if (cb >= ncb) continue;
         uint32_t w[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2)
-          w[c >> 1] = pack_bf16x2(__uint_as_float(v[c]) * inv_l, __uint_as_float(v[c + 1]) * inv_l);
+          w[c >> 1] = pack_bf16x2(__uint_as_float(sv[cb][c]) * inv_l, __uint_as_float(sv[cb][c + 1]) * inv_l);
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8)
           *reinterpret_cast<uint4*>(o_tile + umma::tile_chunk_offset(r, cb * 32 + c8 * 8)) =
@@ -264,15 +283,16 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (tid == 0 && *s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
   if (warp == 1) {
     __syncwarp();
-    umma::tmem_dealloc(tmem, 512);
+    umma::tmem_dealloc(tmem, kTmemCols);
   }
 }
 
 }  // namespace
 
 bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dtype) {
+  // (the caller also requires scale > 0: hidden scores are set to -inf before scaling)
   return dtype == CB2_BF16 && dk >= 8 && dk <= 128 && dk % 8 == 0 && dv >= 8 && dv <= 128 && dv % 8 == 0 &&
-         Tq >= 1 && Tk >= 1 && int64_t(B) * H <= 65535;
+         Tq >= 1 && Tk >= 1 && int64_t(B) * H * ((Tq + 127) / 128) < (int64_t(1) << 31);
 }
 
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
@@ -287,8 +307,8 @@ int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B
   if (cudaFuncSetAttribute(om_causal_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
-  const dim3 grid((Tq + kQ - 1) / kQ, unsigned(bh));
-  om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dv,
+  const unsigned grid = unsigned(((Tq + kQ - 1) / kQ) * bh);
+  om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh),
                                                          scale * 1.4426950408889634f, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;

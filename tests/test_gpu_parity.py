@@ -457,7 +457,8 @@ def test_om_causal_long_block_invariance(dev):
 
 @pytest.mark.parametrize("B,H,Tq,Tk,dk,dv", [(1, 2, 1000, 1000, 128, 128), (2, 3, 2048, 2048, 64, 64),
                                             (1, 1, 300, 130, 128, 64), (1, 2, 128, 128, 128, 128),
-                                            (1, 1, 1, 257, 32, 32)])
+                                            (1, 1, 1, 257, 32, 32), (1, 2, 384, 384, 96, 48),
+                                            (1, 1, 256, 256, 8, 8), (2, 40, 1024, 1024, 128, 128)])
 def test_om_causal_bf16_tensor_core_path(dev, B, H, Tq, Tk, dk, dv):
     """bf16 shapes of the tensor-core kernel: ragged lengths, Tq != Tk, many key
     blocks (running max / rescale path), against fp64 on the bf16-rounded inputs."""
