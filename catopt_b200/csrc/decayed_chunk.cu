@@ -1,7 +1,7 @@
 // C-ABI front of the chunked decayed-attention executor: argument checks and
 // the choice between the tensor-core kernel (bf16, dk and dv up to 128, T a
-// multiple of 128; state kept on chip) and the fp32 FMA path (everything else,
-// state in scratch).
+// multiple of 128; state kept on chip, optional scratch for cutting heads into
+// segments) and the fp32 FMA path (everything else, state in scratch).
 #include "common.cuh"
 
 namespace cb2 {
@@ -10,9 +10,10 @@ int decayed_ffma_run(const void* q, const void* k, const void* v, void* o, const
                      int H, int T, int dk, int dv, int C, float scale, int dtype, void* scratch,
                      cudaStream_t st);
 bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype);
+size_t decayed_tc_scratch_bytes(int B, int H, int T);
 int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
-                   int H, int T, int dk, int dv, int C, float scale, int* dev_status,
-                   cudaStream_t st);
+                   int H, int T, int dk, int dv, int C, float scale, void* scratch, size_t scratch_bytes,
+                   int* dev_status, cudaStream_t st);
 
 namespace {
 int check_shape(int B, int H, int T, int dk, int dv, int C) {
@@ -26,7 +27,7 @@ int check_shape(int B, int H, int T, int dk, int dv, int C) {
 extern "C" size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv, int chunk,
                                                   int dtype) {
   if (cb2::check_shape(B, H, T, dk, dv, chunk) != CB2_OK) return 0;
-  if (cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)) return 0;
+  if (cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)) return cb2::decayed_tc_scratch_bytes(B, H, T);
   return cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
 }
 
@@ -43,7 +44,8 @@ extern "C" int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v
   if (cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)) {
     if (!cb2::aligned16(q) || !cb2::aligned16(k) || !cb2::aligned16(v) || !cb2::aligned16(o))
       return CB2_BAD_ALIGN;
-    return cb2::decayed_tc_run(q, k, v, o, gamma, B, H, T, dk, dv, chunk, scale, dev_status, st);
+    return cb2::decayed_tc_run(q, k, v, o, gamma, B, H, T, dk, dv, chunk, scale, scratch, scratch_bytes,
+                               dev_status, st);
   }
   const size_t need = cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
   if (!scratch || scratch_bytes < need) return CB2_SCRATCH_TOO_SMALL;

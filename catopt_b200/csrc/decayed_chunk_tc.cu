@@ -19,6 +19,14 @@
 // (decayed_lower.py:671-700) up to reassociation.  Only chunk-local powers of g
 // appear.
 //
+// Heads are equal-sized, so B*H CTAs on 148 SMs leave the last wave partly
+// empty (512 heads: 3.46 waves cost 4).  When the caller provides scratch, each
+// head is therefore cut into n_seg consecutive segments of chunks, one CTA
+// each, launched segment-major: segment s of a head takes the fp32 state that
+// segment s-1 left in scratch (64 KiB) once a flag says it is there.  A CTA's
+// predecessor has a lower block index, so it is running or finished whenever
+// the CTA itself runs; the wait is bounded like every other.
+//
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM owner),
 // warps 2..9 = the 256-thread compute group (thread = one TMEM lane = one row,
 // half of the columns).
@@ -79,10 +87,31 @@ struct Bars {
   uint64_t* wg_sync;   // barrier among the 256 compute threads
 };
 
+// Bounded wait for a flag another CTA of this launch sets (acquire).  On expiry
+// (or when a sibling thread already gave up) the shared abort word is set.
+__device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile int* abort,
+                                                    unsigned long long budget_ns = 2000000000ull) {
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; ++it) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v != 0) return true;
+    if (*abort) return false;
+    if ((it & 63u) == 63u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) { *abort = 1; return false; }
+      __nanosleep(200);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                  const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int* dev_status) {
+                  const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int n_bh, int n_seg,
+                  float* __restrict__ seg_state, int* __restrict__ seg_flag, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
   // __shared__ array keeps every access a shared-space (LDS/STS) access
@@ -98,8 +127,11 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
          bars + 2 * kSlots + 7};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.x;
-  const int nchunk = T / kC;
+  const int bh = blockIdx.x % n_bh;
+  const int seg = blockIdx.x / n_bh;               // segment-major launch order
+  const int nchunk = T / kC / n_seg;               // chunks of this segment
+  const int chunk0 = seg * nchunk;                 // first chunk of the segment in the sequence
+  const bool has_in = seg > 0;                     // starts from a predecessor's state
   const float g = gamma[bh % H];
   const uint32_t ring_addr = smem_u32(smem + kOffRing);
   const uint32_t sb_addr = smem_u32(smem + kOffSb);
@@ -149,7 +181,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int i = t / 3, which = t % 3;  // 0: K, 1: Q, 2: V
         const CUtensorMap* m = which == 0 ? &map_k : (which == 1 ? &map_q : &map_v);
         unsigned char* dst = smem + kOffRing + slot * kTile;
-        const int row = bh * T + i * kC;
+        const int row = bh * T + (chunk0 + i) * kC;
         mbar_arrive_expect_tx(&B.full[slot], kTile);
         umma::tma_load_2d(dst, m, 0, row, &B.full[slot]);
         umma::tma_load_2d(dst + umma::kSubTileBytes, m, 64, row, &B.full[slot]);
@@ -185,9 +217,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int ks = 0; ks < 8; ++ks)
           umma::mma_bf16_ts(tmem + kColO1, tmem + kColS + p_col(ks * 16),
                             umma::desc_mnmajor(v_addr, ks), idesc_kn, ks > 0);
-        // MMA3: O2 = Q Sb   (the state is zero before the first chunk)
-        if (i > 0) {
-          if (!mbar_wait_abortable(B.sb_ready, (i - 1) & 1, s_abort)) break;
+        // MMA3: O2 = Q Sb   (the state is zero before the first chunk of the sequence)
+        if (i > 0 || has_in) {
+          if (!mbar_wait_abortable(B.sb_ready, (has_in ? i : i - 1) & 1, s_abort)) break;
           umma::fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
@@ -202,7 +234,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma::mma_bf16(tmem + kColSt, umma::desc_mnmajor(k_addr, ks), umma::desc_mnmajor(v_addr, ks),
-                         idesc_nn, (i > 0) || (ks > 0));
+                         idesc_nn, (i > 0) || has_in || (ks > 0));
         umma::mma_commit(B.st_ready);
         umma::mma_commit(&B.empty[tk % kSlots]);
         umma::mma_commit(&B.empty[tv % kSlots]);
@@ -276,15 +308,32 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       // (d) state pass of the previous chunk, placed here so that it runs while
       // MMA2 (P.V) of this chunk executes and MMA3 (Q.Sb) can follow it directly:
       // Sb_i = bf16(St);  St <- g^C St  (ready for this chunk's MMA4)
-      if (i > 0) {
-        ok = mbar_wait_abortable(B.st_ready, (i - 1) & 1, s_abort);
-        if (!__all_sync(0xffffffffu, ok)) break;
-        umma::fence_after_sync();
-        CB2_TL(i, 6);
+      if (i > 0 || has_in) {
         const int cb0 = half * 2;
-        umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
-        umma::tmem_ld32(lane_base + kColSt + cb0 * 32 + 32, vb);
-        umma::tmem_wait_ld();
+        if (i > 0) {
+          ok = mbar_wait_abortable(B.st_ready, (i - 1) & 1, s_abort);
+          if (!__all_sync(0xffffffffu, ok)) break;
+          umma::fence_after_sync();
+          umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
+          umma::tmem_ld32(lane_base + kColSt + cb0 * 32 + 32, vb);
+          umma::tmem_wait_ld();
+        } else {
+          // first chunk of a later segment: the state comes from the predecessor CTA
+          const int* flag = seg_flag + size_t(seg - 1) * n_bh + bh;
+          ok = wait_flag_abortable(flag, s_abort);
+          if (!__all_sync(0xffffffffu, ok)) break;
+          const float4* src = reinterpret_cast<const float4*>(
+              seg_state + (size_t(seg - 1) * n_bh + bh) * (kC * kC) + r * kC + cb0 * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 x = __ldcg(src + j), y = __ldcg(src + 8 + j);
+            va[4 * j] = __float_as_uint(x.x); va[4 * j + 1] = __float_as_uint(x.y);
+            va[4 * j + 2] = __float_as_uint(x.z); va[4 * j + 3] = __float_as_uint(x.w);
+            vb[4 * j] = __float_as_uint(y.x); vb[4 * j + 1] = __float_as_uint(y.y);
+            vb[4 * j + 2] = __float_as_uint(y.z); vb[4 * j + 3] = __float_as_uint(y.w);
+          }
+        }
+        CB2_TL(i, 6);
         auto state_block = [&](int cb, uint32_t (&v)[32]) {
           uint32_t w[16];
 #pragma unroll
@@ -335,13 +384,13 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       for (int cbi = 0; cbi < 2; ++cbi) {
         const int cb = half * 2 + cbi;
         umma::tmem_ld32(lane_base + kColO1 + cb * 32, va);
-        if (i > 0) umma::tmem_ld32(lane_base + kColO2 + cb * 32, vb);
+        if (i > 0 || has_in) umma::tmem_ld32(lane_base + kColO2 + cb * 32, vb);
         umma::tmem_wait_ld();
         uint32_t w[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           float lo = __uint_as_float(va[j]), hi = __uint_as_float(va[j + 1]);
-          if (i > 0) {
+          if (i > 0 || has_in) {
             lo = fmaf(g_row, __uint_as_float(vb[j]), lo);
             hi = fmaf(g_row, __uint_as_float(vb[j + 1]), hi);
           }
@@ -357,12 +406,39 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       wg_phase ^= 1;
       if (!__all_sync(0xffffffffu, ok)) break;
       if (tid == 64) {  // whole tile written: two {64 x 128} boxes go out asynchronously
-        const int row = bh * T + i * kC;
+        const int row = bh * T + (chunk0 + i) * kC;
         umma::tma_store_2d(&map_o, 0, row, o_tile);
         if (dv > 64) umma::tma_store_2d(&map_o, 64, row, o_tile + umma::kSubTileBytes);
         bulk_commit();
       }
       CB2_TL(i, 5);
+    }
+    // hand the state to the next segment of this head: St after the last MMA4
+    if (seg + 1 < n_seg) {
+      bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
+      if (__all_sync(0xffffffffu, ok)) {
+        umma::fence_after_sync();
+        const int cb0 = half * 2;
+        umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
+        umma::tmem_ld32(lane_base + kColSt + cb0 * 32 + 32, vb);
+        umma::tmem_wait_ld();
+        float4* dst = reinterpret_cast<float4*>(seg_state + (size_t(seg) * n_bh + bh) * (kC * kC) + r * kC + cb0 * 32);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          __stcg(dst + j, make_float4(__uint_as_float(va[4 * j]), __uint_as_float(va[4 * j + 1]),
+                                      __uint_as_float(va[4 * j + 2]), __uint_as_float(va[4 * j + 3])));
+          __stcg(dst + 8 + j, make_float4(__uint_as_float(vb[4 * j]), __uint_as_float(vb[4 * j + 1]),
+                                          __uint_as_float(vb[4 * j + 2]), __uint_as_float(vb[4 * j + 3])));
+        }
+        __threadfence();
+        mbar_arrive(B.wg_sync);
+        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+        wg_phase ^= 1;
+        if (ok && tid == 64) {
+          int* flag = seg_flag + size_t(seg) * n_bh + bh;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+        }
+      }
     }
     if (tid == 64) bulk_wait_all<0>();  // the staged output has left shared memory
   }
@@ -392,8 +468,43 @@ bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype)
          T % kC == 0 && T >= kC && int64_t(B) * H * T < (int64_t(1) << 31);
 }
 
+// Segments per head: the smallest count in {1, 2, 4, 8} that fills the last wave
+// of CTAs to 97 % (or the best of them), keeping at least 4 chunks per segment.
+int decayed_tc_segments(int n_bh, int nchunk, int sms) {
+  // a head's segments run one after the other, so cutting only pays when there is
+  // more than one wave of heads to balance
+  if (n_bh <= sms) return 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int n = 1; n <= 8; n *= 2) {
+    if (nchunk % n != 0 || nchunk / n < 4) break;
+    const double waves = double(n_bh) * n / sms;
+    const double eff = waves / double((long long)((waves + 0.999999)));
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = n; }
+    if (eff >= 0.97) break;
+  }
+  return best;
+}
+
+namespace {
+int device_sms() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+}  // namespace
+
+// Scratch that lets heads be cut into segments: (n_seg - 1) * B*H states of
+// 128 x 128 fp32, then as many flags.
+size_t decayed_tc_scratch_bytes(int B, int H, int T) {
+  const int n_seg = decayed_tc_segments(B * H, T / kC, device_sms());
+  return size_t(n_seg - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
+}
+
 int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
-                   int H, int T, int dk, int dv, int C, float scale, int* dev_status, cudaStream_t st) {
+                   int H, int T, int dk, int dv, int C, float scale, void* scratch, size_t scratch_bytes,
+                   int* dev_status, cudaStream_t st) {
   (void)C;
   const uint64_t rows = uint64_t(B) * H * T;
   CUtensorMap mq, mk, mv, mo;
@@ -406,8 +517,18 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
   if (cudaFuncSetAttribute(decayed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
-  decayed_tc_kernel<<<B * H, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
-                                                        dev_status);
+  const int n_bh = B * H;
+  int n_seg = decayed_tc_segments(n_bh, T / kC, device_sms());
+  const size_t state_bytes = size_t(n_seg - 1) * n_bh * size_t(kC) * kC * sizeof(float);
+  const size_t flag_bytes = size_t(n_seg - 1) * n_bh * sizeof(int);
+  if (n_seg > 1 && (!scratch || !aligned16(scratch) || scratch_bytes < state_bytes + flag_bytes ||
+                    int64_t(n_bh) * n_seg >= (int64_t(1) << 31)))
+    n_seg = 1;   // no room for the hand-off: one CTA per head
+  float* seg_state = static_cast<float*>(scratch);
+  int* seg_flag = n_seg > 1 ? reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + state_bytes) : nullptr;
+  if (n_seg > 1 && cudaMemsetAsync(seg_flag, 0, flag_bytes, st) != cudaSuccess) return CB2_LAUNCH_FAIL;
+  decayed_tc_kernel<<<n_bh * n_seg, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
+                                                               n_bh, n_seg, seg_state, seg_flag, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

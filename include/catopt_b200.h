@@ -141,8 +141,13 @@ int cb2_chain_fold_f32_noalloc(const float* const* weights, const int* dims, int
  * q,k: [B,H,T,dk]; v,o: [B,H,T,dv]; gamma: float[H] (device, fp32, 0<g<=1);
  * T % chunk == 0.  dtype is the element type of q,k,v,o; products accumulate
  * and the state is carried in fp32.
- * scratch: cb2_decayed_chunk_scratch_bytes() bytes (per-chunk K^T V products
- * for the fp32 path; 0 for paths that keep the state on chip).
+ * scratch: cb2_decayed_chunk_scratch_bytes() bytes.  fp32 path: per-chunk K^T V
+ * products (required).  Tensor-core path (bf16): optional; with it, heads are
+ * cut into consecutive segments handled by different CTAs so that the grid
+ * fills the GPU's last wave, the fp32 state crossing from one segment to the
+ * next through scratch; without it (NULL / too small) one CTA runs each head.
+ * The answer is 0 when no cut would help.  Calls that share scratch must not
+ * overlap on the GPU.
  * ------------------------------------------------------------------------- */
 size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv,
                                        int chunk, int dtype);

@@ -344,6 +344,37 @@ def test_decayed_bf16_many_heads_and_scale(dev):
         assert rel_to_max(out[b:b + 1, h:h + 1], want) <= BF16_TOL
 
 
+def test_decayed_bf16_segmented_heads(dev):
+    """More heads than SMs: the tensor-core kernel cuts every head into segments
+    that different CTAs run, the state crossing through scratch.  Same result as
+    one CTA per head (scratch withheld) and as the oracle."""
+    from catopt_b200 import _lib, ops
+
+    B, H, T, d = 3, 64, 1024, 128                      # 192 heads, 8 chunks -> 2 segments of 4
+    lib = _lib.load()
+    assert lib.cb2_decayed_chunk_scratch_bytes(B, H, T, d, d, 128, 1) >= 192 * (128 * 128 * 4 + 4)
+    assert lib.cb2_decayed_chunk_scratch_bytes(1, 64, T, d, d, 128, 1) == 0      # one wave: no cut
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(B, H, T, d, generator=g).bfloat16() / 4 for _ in range(3))
+    gam = (1 - torch.exp2(-5 - 8 * torch.arange(H) / H)).float()
+    qd, kd, vd, gd = q.to(dev), k.to(dev), v.to(dev), gam.to(dev)
+    out = ops.decayed_chunk_fwd(qd, kd, vd, gd, 128, 2.0)
+    # the same call with no scratch: one CTA per head
+    o1 = torch.empty_like(out)
+    st = ops.device_status(qd.device)
+    rc = lib.cb2_decayed_chunk_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o1.data_ptr(), gd.data_ptr(),
+                                   B, H, T, d, d, 128, 2.0, 1, None, 0, st.data_ptr(), ops.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert rel_to_max(out, o1.double()) <= 1e-6      # same arithmetic, state round-trips exactly in fp32
+    for (b, h) in ((0, 0), (1, 17), (2, 63)):
+        want = oracle.decayed_quadratic(q[b:b + 1, h:h + 1].double(), k[b:b + 1, h:h + 1].double(),
+                                        v[b:b + 1, h:h + 1].double(), gam[h:h + 1].double(), 2.0)
+        assert rel_to_max(out[b:b + 1, h:h + 1], want) <= BF16_TOL
+    ops.check_device_status(dev)
+
+
+
 def test_decayed_bf16_long_sequence_state_accuracy(dev):
     """T = 8192 (config 4's length, 64 chunks): the fp32 state in tensor memory
     does not drift — compared against the fp64 state-carry recurrence."""
