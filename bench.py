@@ -368,7 +368,7 @@ def run_ours(args) -> None:
     gamma = c4_gamma(H).to(dev)
     o = torch.empty_like(v)
     code = _lib.CB2_BF16
-    path = "tcgen05" if _lib.load().cb2_decayed_chunk_scratch_bytes(B, H, T, d, d, C, code) == 0 else "ffma"
+    path = "tcgen05" if _lib.load().cb2_decayed_chunk_on_tensor_cores(B, H, T, d, d, C, code) else "ffma"
     launches_per_step = 1 if path == "tcgen05" else 3
 
     def step():

@@ -49,6 +49,10 @@ SIGNATURES: dict[str, tuple] = {
         C.c_size_t,
         [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
     ),
+    "cb2_decayed_chunk_on_tensor_cores": (
+        C.c_int,
+        [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
+    ),
     "cb2_decayed_chunk_fwd": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -31,6 +31,13 @@ extern "C" size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, i
   return cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
 }
 
+extern "C" int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, int dv, int chunk, int dtype) {
+  return cb2::check_shape(B, H, T, dk, dv, chunk) == CB2_OK &&
+                 cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)
+             ? 1
+             : 0;
+}
+
 extern "C" int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
                                      const float* gamma, int B, int H, int T, int dk, int dv,
                                      int chunk, float scale, int dtype, void* scratch,

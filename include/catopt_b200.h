@@ -151,6 +151,10 @@ int cb2_chain_fold_f32_noalloc(const float* const* weights, const int* dims, int
  * ------------------------------------------------------------------------- */
 size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv,
                                        int chunk, int dtype);
+/* 1 when cb2_decayed_chunk_fwd runs these sizes on the tensor cores (one launch,
+ * state on chip), 0 when it takes the fp32 FMA path (three launches). */
+int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, int dv,
+                                      int chunk, int dtype);
 int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
                           const float* gamma, int B, int H, int T, int dk, int dv,
                           int chunk, float scale, int dtype, void* scratch,

@@ -51,7 +51,9 @@ def test_argument_errors_without_a_device(lib_path):
     assert lib.cb2_decayed_chunk_fwd(16, 16, 16, 16, 16, 1, 1, 100, 8, 8, 64, 1.0, 0, None, 0, None, None) == 1
     assert lib.cb2_diag_scan_fwd(16, 16, 16, 16, None, 16, None, 1, 4, 8, 3, 0, 0, None, None) == 1
     assert lib.cb2_linear_f32_scratch_bytes(64, 512, 512) > 0
-    assert lib.cb2_linear_f32_scratch_bytes(4096, 512, 512) == 0
+    assert lib.cb2_linear_f32_scratch_bytes(4096, 512, 512) == 2 * 512 * 512 * 4   # w split into hi + lo
+    assert lib.cb2_decayed_chunk_on_tensor_cores(16, 32, 8192, 128, 128, 128, 1) == 1
+    assert lib.cb2_decayed_chunk_on_tensor_cores(2, 4, 1024, 64, 64, 64, 0) == 0
 
 
 def test_no_cpu_fallback():
