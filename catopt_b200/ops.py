@@ -250,3 +250,36 @@ def diag_compose_apply(a_seq: torch.Tensor, b_seq: torch.Tensor, h: torch.Tensor
     h0 = h.expand(state_shape).to(torch.float32).reshape(1, D, 1).contiguous()
     _, hT = diag_scan_fwd(a, u, ones, ones, h0, want_state=True)
     return hT.reshape(state_shape).to(dt)
+
+
+def diag_prefix_maps(a_seq: torch.Tensor, b_seq: torch.Tensor):
+    """All prefix maps of a chronological sequence of diagonal affine steps.
+
+    ``a_seq``/``b_seq`` are ``[T, *state]`` (broadcastable against each other);
+    step t is ``h -> a_t*h + b_t``.  Returns ``(Pa, Pb)`` with
+    ``h_t = Pa[t]*h_0 + Pb[t]``, i.e. ``Pa[t] = a_t ... a_0`` and ``Pb`` the scan
+    of the offsets — what the reference's ``BatchedOmdModule._prefix_scan``
+    (catopt_carriers/omd_lower.py:771-824) builds from blocked compose steps.
+    Two passes of ``cb2_diag_scan_fwd`` over the flattened state (channels =
+    state elements, N = 1, b = c = 1): offsets with ``h_0 = 0`` give ``Pb``, zero
+    offsets with ``h_0 = 1`` give ``Pa``.  Returns ``None`` when the kernel cannot
+    take the case (dtype other than float32/bfloat16, or a state whose byte size
+    is not a multiple of 16) so the caller keeps its own scan.
+    """
+    require_cuda(a_seq, b_seq)
+    state_shape = torch.broadcast_shapes(a_seq.shape[1:], b_seq.shape[1:])
+    T, D = a_seq.shape[0], 1
+    for sdim in state_shape:
+        D *= sdim
+    dt = a_seq.dtype
+    esz = 2 if dt == torch.bfloat16 else 4
+    if dt not in (torch.float32, torch.bfloat16) or b_seq.dtype != dt or (D * esz) % 16 or T == 0 \
+            or b_seq.shape[0] != T:
+        return None
+    a = a_seq.expand(T, *state_shape).reshape(1, T, D, 1).contiguous()
+    u = b_seq.expand(T, *state_shape).reshape(1, T, D).contiguous()
+    ones = torch.ones(D, 1, dtype=dt, device=a.device)
+    pb = diag_scan_fwd(a, u, ones, ones, None)
+    h1 = torch.ones(1, D, 1, dtype=torch.float32, device=a.device)
+    pa = diag_scan_fwd(a, torch.zeros_like(u), ones, ones, h1)
+    return pa.reshape(T, *state_shape), pb.reshape(T, *state_shape)

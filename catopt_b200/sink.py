@@ -3,7 +3,7 @@
 catopt routes an extracted term to the first ``ExecutorSpec`` of
 ``Sink.executors`` whose ``carrier`` is not ``None`` and whose ``accepts(term)``
 is true (catopt_orchestrator/optimize.py:485-495); mapping order is routing
-order.  ``B200Sink`` puts four B200 specs in front of the torch ones:
+order.  ``B200Sink`` puts five B200 specs in front of the torch ones:
 
 * ``b200_om_decayed_chunked`` — the uniform K-chunk decayed term of
   ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152).  ``accepts``
@@ -24,6 +24,9 @@ order.  ``B200Sink`` puts four B200 specs in front of the torch ones:
   terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
   leaf stacking are reused, the composed-map reduction runs in
   ``cb2_diag_scan_fwd``.
+* ``b200_omd`` — deferred-affine attention ``omd_apply(<omd tree>, h)``: the
+  reference's ``BatchedOmdModule`` with its all-prefix scan of the diagonal step
+  maps (``_prefix_scan``) running in ``cb2_diag_scan_fwd``.
 * ``b200_linear_chain`` — ``linear(x, <matmul tree of weight Params>)``, the
   term ``assoc_linear`` leaves behind for a chain of bias-free Linear maps
   (catopt_core/laws/tensor.py:1293-1300) before ``_fold_weight_chains``
@@ -732,6 +735,59 @@ def _make_scan_module():
     return B200ScanModule
 
 
+# --------------------------------------------------------------------------- omd (deferred-affine attention)
+def _make_omd_module():
+    from catopt_carriers.omd_lower import BatchedOmdModule
+
+    class B200OmdModule(BatchedOmdModule):
+        """``BatchedOmdModule`` (omd_lower.py:560-1020) with the all-prefix scan of
+        the scanned values' step maps (``_prefix_scan``, omd_lower.py:771-824: blocks
+        of sqrt(T) compose steps) replaced by ``cb2_diag_scan_fwd``, which streams
+        the sequence once per map component and emits every prefix.  Term analysis,
+        the omd tree reduction and every other path stay the reference's own code;
+        dense maps, fp64 tensors and states the kernel cannot address keep the
+        reference's scan on the same device."""
+
+        def __init__(self, ir: IR, param_values: dict | None = None) -> None:
+            super().__init__(ir, param_values)
+            self.kernel_calls = 0
+            self._kernel_error: Exception | None = None
+
+        def _forward_impl(self, *xs):
+            # The reference's forward degrades to the generic module on ANY exception
+            # (omd_lower.py:1015-1019); a kernel-path failure must not disappear that way.
+            if self._plan is not None and any(isinstance(t, torch.Tensor) and not t.is_cuda for t in xs):
+                raise B200Error("B200OmdModule runs on CUDA tensors only (no CPU fallback)")
+            self._kernel_error = None
+            out = super()._forward_impl(*xs)
+            if self._kernel_error is not None:
+                raise self._kernel_error
+            return out
+
+        def _prefix_scan(self, A, B, domain):
+            if domain != "diag" or A.shape[0] < 2 or not A.is_cuda:
+                return super()._prefix_scan(A, B, domain)
+            try:
+                out = ops.diag_prefix_maps(A, B)
+            except B200Error as e:
+                self._kernel_error = e
+                raise
+            if out is None:
+                return super()._prefix_scan(A, B, domain)
+            self.kernel_calls += 1
+            return out
+
+    return B200OmdModule
+
+
+def omd_plan(root: Any) -> dict | None:
+    """The reference's omd plan (``build_omd_plan``, omd_lower.py) for
+    ``omd_apply[m](<omd tree>, h)`` terms, ``None`` otherwise."""
+    from catopt_carriers.omd_lower import build_omd_plan, is_omd_apply_term
+
+    return build_omd_plan(root) if is_omd_apply_term(root) else None
+
+
 # --------------------------------------------------------------------------- sink
 def _engaged(m: Any) -> bool:
     return bool(getattr(m, "is_batched", False))
@@ -765,6 +821,13 @@ class B200Sink(TorchSink):
                     lambda term: scan_diag_plan(term) is not None,
                     _engaged,
                     (frozenset({"applyd"}), frozenset({"affd_compose"}), frozenset({"aff_diag"})),
+                ),
+                "b200_omd": ExecutorSpec(
+                    "b200_omd",
+                    lambda ir, p: _make_omd_module()(ir, param_values=p),
+                    lambda term: omd_plan(term) is not None,
+                    _engaged,
+                    (frozenset({"omd_apply", "omd_applym"}), frozenset({"omd_compose"}), frozenset({"omd", "omd_elem"})),
                 ),
                 "b200_linear_chain": ExecutorSpec(
                     "b200_linear_chain",

@@ -547,6 +547,29 @@ def test_decayed_whole_sequence_entry_point(dev):
     assert decayed_whole_sequence(q.double().to(dev), k.double().to(dev), v.double().to(dev), gam, None, 1.0) is None
 
 
+def test_diag_prefix_maps_vs_reference_prefix_scan(dev):
+    """All-prefix maps of a diagonal step sequence (the omd executor's hot step)
+    against the oracle's restatement of the reference's blocked prefix scan, which
+    the golden fixtures pin to the real ``_prefix_scan``."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(21)
+    for T, shape in ((37, (8, 12)), (256, (4, 64)), (5, (16,))):
+        A = torch.sigmoid(2 + torch.randn(T, *shape, generator=g))
+        Bv = torch.randn(T, *shape, generator=g)
+        pa, pb = ops.diag_prefix_maps(A.to(dev), Bv.to(dev))
+        wa, wb = oracle.prefix_scan_diag(A.double(), Bv.double())
+        assert pa.shape == wa.shape and pb.shape == wb.shape
+        assert rel_to_max(pa, wa) <= FP32_TOL and rel_to_max(pb, wb) <= FP32_TOL
+    # a shared (broadcast) gate, as LTI scans have
+    A = torch.sigmoid(torch.randn(40, 1, 8, generator=g)).expand(40, 3, 8)
+    Bv = torch.randn(40, 3, 8, generator=g)
+    pa, pb = ops.diag_prefix_maps(A.to(dev), Bv.to(dev))
+    wa, wb = oracle.prefix_scan_diag(A.double().contiguous(), Bv.double())
+    assert rel_to_max(pa, wa) <= FP32_TOL and rel_to_max(pb, wb) <= FP32_TOL
+    assert ops.diag_prefix_maps(A.double().to(dev), Bv.double().to(dev)) is None     # fp64: caller keeps its scan
+
+
 def test_device_status_clean(dev):
     """No kernel in this file ran into a bounded-wait timeout."""
     from catopt_b200 import ops

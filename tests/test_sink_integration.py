@@ -33,7 +33,7 @@ def _route(sink, term):
 def test_b200_specs_come_first_and_are_executor_specs():
     s = b200.B200Sink()
     names = list(s.executors)
-    assert names[:4] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_scan", "b200_linear_chain"]
+    assert names[:5] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_scan", "b200_omd", "b200_linear_chain"]
     assert "om_decayed_chunked" in names and names[-1] == "generic"
     assert all(isinstance(v, ExecutorSpec) for v in s.executors.values())
 
@@ -465,3 +465,41 @@ def test_om_causal_real_saturation_member_is_accepted():
     # the unmasked companion carrier stays with the reference's executors
     _, term, _, _, _ = helper._causal_chunked_ok([3, 6], causal=False)
     assert b200.om_causal_plan(term) is None
+
+
+# --------------------------------------------------------------------------- omd: prefix-scan hook
+def _omd_chain_term(T=8, Tq=3, d=4):
+    """omd_apply(omd_elem(s, stack(affd_a f_i), stack(affd_b f_i)), h) over the shared
+    prefix chain f_i = affd_compose(aff_diag(a[i], x[i]), f_{i-1}) — the form an
+    unrolled scan under softmax attention extracts to (reference tests/test_omd_lower.py:52-75)."""
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    a_p, x_v = Param("p_a", tt(T, d)), Var("x", tt(T, d))
+    s, h = Param("s", tt(Tq, T)), Param("h", tt(d))
+    leaves = [Op.make("aff_diag", Op.make("select", a_p, dim=0, index=t), Op.make("select", x_v, dim=0, index=t))
+              for t in range(T)]
+    fs = [leaves[0]]
+    for t in range(1, T):
+        fs.append(Op.make("affd_compose", leaves[t], fs[-1]))
+    a_map = Op.make("stack", *(Op.make("affd_a", f) for f in fs), dim=0)
+    b_map = Op.make("stack", *(Op.make("affd_b", f) for f in fs), dim=0)
+    root = Op.make("omd_apply", Op.make("omd_elem", s, a_map, b_map), h)
+    return IR(root=root, inputs=[x_v], input_names={"x"}, params={"p_a": a_p, "s": s, "h": h})
+
+
+def test_omd_term_routes_to_b200_omd_and_keeps_reference_plan():
+    ir = _omd_chain_term()
+    s = b200.B200Sink()
+    spec = _route(s, ir.root)
+    assert spec.name == "b200_omd"
+    vals = {"p_a": torch.rand(8, 4) * 0.5 + 0.5, "s": torch.randn(3, 8), "h": torch.randn(4)}
+    mod = spec.lower(ir, vals)
+    assert isinstance(mod, BatchedExecutor) and spec.engaged(mod)
+    assert mod._plan["map_mode"] == "chain"          # the all-prefix scan is what runs
+    from catopt_b200 import B200Error
+
+    with pytest.raises(B200Error):                   # the prefix scan refuses host tensors
+        mod(torch.randn(8, 4))
+    # dense maps and single-step sequences stay with the reference's own scan
+    A, B = torch.rand(5, 3, 3), torch.rand(5, 3)
+    pa, pb = mod._prefix_scan(A, B, "dense")
+    assert pa.shape == (5, 3, 3) and pb.shape == (5, 3) and mod.kernel_calls == 0
