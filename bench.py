@@ -305,6 +305,22 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
                                              flops=4 * B * T * D)
     del a3, a3s, x3, y3
 
+    # config 3 as the reference's scan executor sees it (a tree of 4096 leaf maps over the state
+    # [8,1024,16], final state only): stacked leaves in product order, fp32, 2 x 2.1 GB
+    Tt, St = 4096, 8 * 1024 * 16
+    al = torch.empty(Tt, St, device=dev)
+    bl = torch.empty(Tt, St, device=dev)
+    for t0 in range(0, Tt, 512):
+        al[t0:t0 + 512].copy_(torch.sigmoid(4 + 0.5 * torch.randn(512, St, device=dev, generator=gen)))
+        bl[t0:t0 + 512].copy_(torch.randn(512, St, device=dev, generator=gen))
+    hl = torch.zeros(St, device=dev)
+    ms = time_steps(lambda: ops.diag_compose_apply(al, bl, hl), K, W, world)
+    out["config3_scan_tree_final_state_fp32"] = entry(
+        ms, 8 * Tt, 2 * Tt * St * 4, 2,
+        "composed map of 4096 stacked leaf maps (what BatchedScanModule reduces level by level); 4.3 GB exceed L2",
+        flops=3 * Tt * St)
+    del al, bl, hl
+
     # causal online-softmax executor (no config of its own in the benchmark spec), bf16, d=128:
     # a long-sequence case that fills the GPU (268 MB > L2) and a short one (256 CTAs: tail-bound)
     for (Bo, Ho, To) in ((1, 32, 8192), (2, 8, 2048)):

@@ -49,6 +49,12 @@ SIGNATURES: dict[str, tuple] = {
         C.c_size_t,
         [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
     ),
+    "cb2_diag_compose_scratch_bytes": (C.c_size_t, [C.c_longlong, C.c_longlong, C.c_int]),
+    "cb2_diag_compose_apply": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int,
+         C.c_void_p, C.c_size_t, C.c_void_p],
+    ),
     "cb2_decayed_chunk_on_tensor_cores": (
         C.c_int,
         [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],

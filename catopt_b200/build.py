@@ -19,6 +19,7 @@ LIB = HERE / "libcatopt_b200.so"
 SOURCES = [
     "verify_reduce.cu",
     "diag_scan.cu",
+    "diag_compose.cu",
     "linear_f32.cu",
     "linear_tf32x3.cu",
     "decayed_chunk_ffma.cu",

@@ -1,0 +1,191 @@
+// Final state of a diagonal scan from its leaf maps, without re-ordering them:
+//     out = a_root * h + b_root,   (a_root, b_root) = f_0 . f_1 . ... . f_{n-1},
+// f_j(h) = a_j*h + b_j, leaves stored in PRODUCT order (f_0 is the latest step),
+// the order in which the reference stacks them for `fused_diag_levels`
+// (catopt_carriers/scan_fused.py:100-120) inside
+// `BatchedScanModule._forward_fused` (scan_lower.py:785-807).
+//
+// The reference halves the leaf stack log2(n) times (two kernels per level,
+// about twice the leaf bytes of traffic).  Composition is associative, so the
+// same map comes out of ONE pass in stored order with the recurrence
+//     B += A * b_j ;  A *= a_j          (A = 1, B = 0 at the start)
+// per state element: the leaves are read once, nothing is flipped or copied.
+// HBM-bound streaming: a thread owns 16 bytes of the state row and walks n with
+// eight steps of loads in flight; when the state alone gives too few threads to
+// fill the GPU, n is cut into segments whose partial maps (fp32, in caller
+// scratch) a second small kernel folds in order and applies to h.
+#include "common.cuh"
+
+namespace cb2 {
+namespace {
+
+constexpr int kComposeThreads = 256;
+constexpr int kUnroll = 8;
+
+template <int DTYPE>
+struct Vec;
+template <>
+struct Vec<CB2_F32> {
+  static constexpr int kElems = 4;
+  __device__ static void ld(const void* p, size_t i, float (&v)[4]) {
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  __device__ static float ld1(const void* p, size_t i) { return __ldcs(static_cast<const float*>(p) + i); }
+  __device__ static void st1(void* p, size_t i, float v) { static_cast<float*>(p)[i] = v; }
+};
+template <>
+struct Vec<CB2_BF16> {
+  static constexpr int kElems = 8;
+  __device__ static void ld(const void* p, size_t i, float (&v)[8]) {
+    const uint4 x = __ldcs(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + i));
+    v[0] = bf16lo_to_f32(x.x); v[1] = bf16hi_to_f32(x.x);
+    v[2] = bf16lo_to_f32(x.y); v[3] = bf16hi_to_f32(x.y);
+    v[4] = bf16lo_to_f32(x.z); v[5] = bf16hi_to_f32(x.z);
+    v[6] = bf16lo_to_f32(x.w); v[7] = bf16hi_to_f32(x.w);
+  }
+  __device__ static float ld1(const void* p, size_t i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  }
+  __device__ static void st1(void* p, size_t i, float v) {
+    static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  }
+};
+
+// Partial map of leaves [j0, j1) for the state elements of this thread.
+// VEC: 16-byte vector loads (S a multiple of the vector width, aligned rows).
+template <int DTYPE, bool VEC>
+__global__ void __launch_bounds__(kComposeThreads)
+compose_partial_kernel(const void* __restrict__ a, const void* __restrict__ b, long long n, long long S,
+                       long long seg_len, float* __restrict__ part_a, float* __restrict__ part_b) {
+  using V = Vec<DTYPE>;
+  constexpr int E = VEC ? V::kElems : 1;
+  const long long c0 = (blockIdx.x * (long long)kComposeThreads + threadIdx.x) * E;
+  if (c0 >= S) return;
+  const long long j0 = blockIdx.y * seg_len;
+  const long long j1 = j0 + seg_len < n ? j0 + seg_len : n;
+  float A[E], B[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) { A[e] = 1.f; B[e] = 0.f; }
+  long long j = j0;
+  for (; j + kUnroll <= j1; j += kUnroll) {
+    float av[kUnroll][E], bv[kUnroll][E];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t off = size_t(j + u) * size_t(S) + size_t(c0);
+      if constexpr (VEC) {
+        V::ld(a, off, av[u]);
+        V::ld(b, off, bv[u]);
+      } else {
+        av[u][0] = V::ld1(a, off);
+        bv[u][0] = V::ld1(b, off);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        B[e] = fmaf(A[e], bv[u][e], B[e]);
+        A[e] *= av[u][e];
+      }
+  }
+  for (; j < j1; ++j) {
+    const size_t off = size_t(j) * size_t(S) + size_t(c0);
+    float av[E], bv[E];
+    if constexpr (VEC) {
+      V::ld(a, off, av);
+      V::ld(b, off, bv);
+    } else {
+      av[0] = V::ld1(a, off);
+      bv[0] = V::ld1(b, off);
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      B[e] = fmaf(A[e], bv[e], B[e]);
+      A[e] *= av[e];
+    }
+  }
+  const size_t base = size_t(blockIdx.y) * size_t(S) + size_t(c0);
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    part_a[base + e] = A[e];
+    part_b[base + e] = B[e];
+  }
+}
+
+// Fold the segment maps in order (segment 0 holds the latest steps) and apply to h.
+template <int DTYPE>
+__global__ void __launch_bounds__(kComposeThreads)
+compose_apply_kernel(const float* __restrict__ part_a, const float* __restrict__ part_b,
+                     const void* __restrict__ h, void* __restrict__ out, int nseg, long long S) {
+  using V = Vec<DTYPE>;
+  const long long c = blockIdx.x * (long long)kComposeThreads + threadIdx.x;
+  if (c >= S) return;
+  float A = 1.f, B = 0.f;
+  for (int s = 0; s < nseg; ++s) {
+    const size_t i = size_t(s) * size_t(S) + size_t(c);
+    B = fmaf(A, part_b[i], B);
+    A *= part_a[i];
+  }
+  V::st1(out, size_t(c), fmaf(A, V::ld1(h, size_t(c)), B));
+}
+
+int pick_segments(long long n, long long S, int elems_per_thread) {
+  long long ctas = (S / elems_per_thread + kComposeThreads - 1) / kComposeThreads;
+  if (ctas < 1) ctas = 1;
+  long long want = (4 * 148 + ctas - 1) / ctas;          // about four CTAs per SM in total
+  const long long most = n / 64 > 0 ? n / 64 : 1;        // segments of at least 64 leaves
+  if (want > most) want = most;
+  if (want < 1) want = 1;
+  if (want > 65535) want = 65535;
+  return int(want);
+}
+
+template <int DTYPE>
+int run(const void* a, const void* b, const void* h, void* out, long long n, long long S, void* scratch,
+        size_t scratch_bytes, cudaStream_t st) {
+  using V = Vec<DTYPE>;
+  const bool vec = S % V::kElems == 0 && aligned16(a) && aligned16(b);
+  const int E = vec ? V::kElems : 1;
+  const int nseg = pick_segments(n, S, E);
+  const size_t need = size_t(2) * nseg * size_t(S) * sizeof(float);
+  if (!scratch || scratch_bytes < need) return CB2_SCRATCH_TOO_SMALL;
+  float* part_a = static_cast<float*>(scratch);
+  float* part_b = part_a + size_t(nseg) * size_t(S);
+  const long long seg_len = (n + nseg - 1) / nseg;
+  const long long threads = (S + E - 1) / E;
+  const dim3 grid(unsigned((threads + kComposeThreads - 1) / kComposeThreads), unsigned(nseg));
+  if (vec)
+    compose_partial_kernel<DTYPE, true><<<grid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, part_a, part_b);
+  else
+    compose_partial_kernel<DTYPE, false><<<grid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, part_a, part_b);
+  CB2_LAUNCH_CHECK();
+  compose_apply_kernel<DTYPE><<<unsigned((S + kComposeThreads - 1) / kComposeThreads), kComposeThreads, 0, st>>>(
+      part_a, part_b, h, out, nseg, S);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
+}  // namespace
+}  // namespace cb2
+
+extern "C" size_t cb2_diag_compose_scratch_bytes(long long n, long long S, int dtype) {
+  if (n <= 0 || S <= 0) return 0;
+  // enough for either layout: the 16-byte-vector one has fewer threads per segment
+  // and therefore cuts n into more segments
+  const int ve = dtype == CB2_BF16 ? 8 : 4;
+  const int a = cb2::pick_segments(n, S, 1), b = cb2::pick_segments(n, S, ve);
+  return size_t(2) * (a > b ? a : b) * size_t(S) * sizeof(float);
+}
+
+extern "C" int cb2_diag_compose_apply(const void* a_seq, const void* b_seq, const void* h, void* out,
+                                      long long n, long long S, int dtype, void* scratch,
+                                      size_t scratch_bytes, void* stream) {
+  if (!a_seq || !b_seq || !h || !out) return CB2_NULL_PTR;
+  if (n <= 0 || S <= 0 || S > (1ll << 40) / n) return CB2_BAD_SHAPE;
+  if ((S + cb2::kComposeThreads - 1) / cb2::kComposeThreads > 0x7fffffffll) return CB2_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CB2_F32) return cb2::run<CB2_F32>(a_seq, b_seq, h, out, n, S, scratch, scratch_bytes, st);
+  if (dtype == CB2_BF16) return cb2::run<CB2_BF16>(a_seq, b_seq, h, out, n, S, scratch, scratch_bytes, st);
+  return CB2_UNSUPPORTED_DTYPE;
+}

@@ -700,6 +700,7 @@ int launch_scan(const void* a, const void* x, const void* b, const void* c, cons
                 void* y, float* hT, int B, int T, int D, int a_bcast_n, int* dev_status,
                 cudaStream_t st) {
   using C = ScanCfg<DTYPE, N>;
+  if (N == 1) a_bcast_n = 1;   // [B,T,D,1] is [B,T,D]: the collapsed-recurrence kernel applies
   if (a_bcast_n) {
     if (D % 32 == 0 && aligned16(a) && aligned16(x) && aligned16(y))
       return launch_scan_shared_a<DTYPE>(a, x, b, c, h0, y, hT, B, T, D, N, dev_status, st);

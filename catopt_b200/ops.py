@@ -229,27 +229,32 @@ def diag_compose_apply(a_seq: torch.Tensor, b_seq: torch.Tensor, h: torch.Tensor
 
     ``a_seq``/``b_seq`` are ``[n, *state]`` in PRODUCT order (latest step first),
     the order the reference's ``fused_diag_levels`` (scan_fused.py:100-120)
-    takes; the result is its value ``a_root*h + b_root``.  The kernel runs the
-    steps chronologically over the flattened state (channels = state elements,
-    N = 1, b = c = 1).  Returns ``None`` when the kernel cannot take the case
-    (dtype other than float32/bfloat16, or a state whose byte size is not a
-    multiple of 16) so the caller can keep its own reduction.
+    takes; the result is its value ``a_root*h + b_root``.  One pass of
+    ``cb2_diag_compose_apply`` over the leaves in stored order (no flip, no copy
+    when the stacks already have the full state shape).  Returns ``None`` when
+    the kernel cannot take the case (dtype other than float32/bfloat16) so the
+    caller can keep its own reduction.
     """
     require_cuda(a_seq, b_seq, h)
     state_shape = torch.broadcast_shapes(a_seq.shape[1:], b_seq.shape[1:], h.shape)
-    n, D = a_seq.shape[0], 1
+    n, S = a_seq.shape[0], 1
     for sdim in state_shape:
-        D *= sdim
+        S *= sdim
     dt = a_seq.dtype
-    esz = 2 if dt == torch.bfloat16 else 4
-    if dt not in (torch.float32, torch.bfloat16) or b_seq.dtype != dt or (D * esz) % 16 or n == 0:
+    if dt not in (torch.float32, torch.bfloat16) or b_seq.dtype != dt or n == 0 or S == 0 or b_seq.shape[0] != n:
         return None
-    a = a_seq.expand(n, *state_shape).flip(0).reshape(1, n, D, 1).contiguous()
-    u = b_seq.expand(n, *state_shape).flip(0).reshape(1, n, D).contiguous()
-    ones = torch.ones(D, 1, dtype=dt, device=a.device)
-    h0 = h.expand(state_shape).to(torch.float32).reshape(1, D, 1).contiguous()
-    _, hT = diag_scan_fwd(a, u, ones, ones, h0, want_state=True)
-    return hT.reshape(state_shape).to(dt)
+    a = a_seq.expand(n, *state_shape).reshape(n, S).contiguous()
+    b = b_seq.expand(n, *state_shape).reshape(n, S).contiguous()
+    hh = h.expand(state_shape).to(dt).reshape(S).contiguous()
+    out = torch.empty(S, dtype=dt, device=a.device)
+    lib = _lib.load()
+    code = dtype_code(dt)
+    need = lib.cb2_diag_compose_scratch_bytes(n, S, code)
+    scratch = _scratch_buf("compose", need, a.device)
+    rc = lib.cb2_diag_compose_apply(a.data_ptr(), b.data_ptr(), hh.data_ptr(), out.data_ptr(), n, S, code,
+                                    _ptr(scratch), need, stream_ptr())
+    check(rc, "cb2_diag_compose_apply")
+    return out.reshape(state_shape)
 
 
 def diag_prefix_maps(a_seq: torch.Tensor, b_seq: torch.Tensor):

@@ -23,7 +23,7 @@ order.  ``B200Sink`` puts five B200 specs in front of the torch ones:
 * ``b200_scan`` — diagonal ``applyd(<aff_diag tree>, h)`` scan applications (the
   terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
   leaf stacking are reused, the composed-map reduction runs in
-  ``cb2_diag_scan_fwd``.
+  ``cb2_diag_compose_apply`` (one pass over the stacked leaves).
 * ``b200_omd`` — deferred-affine attention ``omd_apply(<omd tree>, h)``: the
   reference's ``BatchedOmdModule`` with its all-prefix scan of the diagonal step
   maps (``_prefix_scan``) running in ``cb2_diag_scan_fwd``.
@@ -706,11 +706,10 @@ def _make_scan_module():
         views stay the reference's own code; only the step that folds the leaf
         maps over the initial state is swapped (the hook the reference's
         ``fused=`` mode uses, ``_forward_fused``, scan_lower.py:785-807).  The
-        leaves arrive in product order (latest step first); the kernel runs them
-        chronologically as ``h <- a_t * h + u_t`` over the flattened state
-        (channels = state elements, N = 1, b = c = 1) and returns the final state.
-        fp64 tensors or state sizes the kernel cannot address degrade to the
-        reference's own eager reduction on the same device.
+        leaves arrive in product order (latest step first) and are composed in
+        that stored order in one pass (``cb2_diag_compose_apply``: B += A*b_j,
+        A *= a_j per state element), then applied to the initial state.  fp64
+        tensors degrade to the reference's own eager reduction on the same device.
         """
 
         def __init__(self, ir: IR, param_values: dict | None = None) -> None:
@@ -727,7 +726,7 @@ def _make_scan_module():
             if occ is not None:
                 a_vals, b_vals = a_vals.index_select(0, occ), b_vals.index_select(0, occ)
             out = ops.diag_compose_apply(a_vals, b_vals, ev(plan["h"]))
-            if out is None:   # fp64 / unaddressable state size: the reference's own reduction
+            if out is None:   # fp64: the reference's own reduction
                 return super()._forward_fused(a_vals, b_vals, ev)
             self.kernel_calls += 1
             return out

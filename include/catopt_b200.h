@@ -182,6 +182,21 @@ int cb2_diag_scan_fwd(const void* a, const void* x, const void* b, const void* c
                       int N, int a_bcast_n, int dtype, int* dev_status,
                       void* stream);
 
+/* Final state of a diagonal scan straight from its stacked leaf maps:
+ *     out = a_root*h + b_root,  (a_root, b_root) = f_0 . f_1 . ... . f_{n-1},
+ *     f_j(h) = a_seq[j]*h + b_seq[j],
+ * leaves in product order (f_0 = latest step), as `BatchedScanModule.
+ * _forward_fused` (scan_lower.py:785-807) hands them to `fused_diag_levels`
+ * (packages/catopt-carriers/src/catopt_carriers/scan_fused.py:100-120), whose
+ * log2(n) halving levels this replaces by one pass over the leaves (fp32
+ * accumulation).  a_seq, b_seq: [n, S] dense; h, out: [S]; element type `dtype`.
+ * scratch: cb2_diag_compose_scratch_bytes() bytes (partial maps when n is cut
+ * into segments to fill the GPU). */
+size_t cb2_diag_compose_scratch_bytes(long long n, long long S, int dtype);
+int cb2_diag_compose_apply(const void* a_seq, const void* b_seq, const void* h, void* out,
+                           long long n, long long S, int dtype, void* scratch,
+                           size_t scratch_bytes, void* stream);
+
 /* -------------------------------------------------------------------------
  * (b') causal softmax attention through the online-softmax monoid,
  *     o_t = sum_{j<=t} softmax_j(scale * q_t.k_j) v_j      per (batch, head).

@@ -435,22 +435,32 @@ def test_linear_tensor_core_path(dev, rows, n_in, n_out):
     assert rel_to_max(got, want) <= FP32_TOL
 
 
-@pytest.mark.parametrize("n,state", [(6, (8,)), (37, (2, 12)), (128, (4, 4, 4)), (5, (3,))])
+@pytest.mark.parametrize("n,state", [(6, (8,)), (37, (2, 12)), (128, (4, 4, 4)), (5, (3,)), (4096, (64,)),
+                                     (1000, (7, 9)), (300, (8, 1024))])
 def test_scan_composed_map_vs_reference_tree(dev, n, state):
     """The reduction the catopt scan adapter swaps in: leaves in product order,
-    compared with the reference's level-batched `fused_diag_levels`."""
+    compared with the reference's level-batched `fused_diag_levels` — short and
+    long stacks (n cut into segments), vector and scalar state widths."""
     from catopt_b200 import ops
 
     g = torch.Generator().manual_seed(n)
     a = torch.sigmoid(3 + torch.randn(n, *state, generator=g))
     b = torch.randn(n, *state, generator=g)
     h = torch.randn(*state, generator=g)
-    want = oracle.fused_diag_levels(a, b, h)
+    want = oracle.fused_diag_levels(a.double(), b.double(), h.double())
     got = ops.diag_compose_apply(a.to(dev), b.to(dev), h.to(dev))
-    if (math.prod(state) * 4) % 16:
-        assert got is None            # not addressable by the kernel: caller keeps its reduction
-    else:
-        assert rel_to_max(got, want) <= FP32_TOL
+    assert got.shape == want.shape and rel_to_max(got, want) <= FP32_TOL
+    # bf16 stacks (fp32 accumulation, one rounding at the end) and a gate shared over the batch axis
+    ab, bb, hb = a.bfloat16(), b.bfloat16(), h.bfloat16()
+    wantb = oracle.fused_diag_levels(ab.double(), bb.double(), hb.double())
+    gotb = ops.diag_compose_apply(ab.to(dev), bb.to(dev), hb.to(dev))
+    assert gotb.dtype == torch.bfloat16 and rel_to_max(gotb, wantb) <= BF16_TOL
+    if len(state) == 2:
+        a1 = a[:, :1].contiguous()
+        want1 = oracle.fused_diag_levels(a1.double().expand_as(a).contiguous(), b.double(), h.double())
+        got1 = ops.diag_compose_apply(a1.to(dev), b.to(dev), h.to(dev))
+        assert rel_to_max(got1, want1) <= FP32_TOL
+    assert ops.diag_compose_apply(a.double().to(dev), b.double().to(dev), h.double().to(dev)) is None
 
 
 # --------------------------------------------------------------------------- (b') om causal
