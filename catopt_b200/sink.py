@@ -566,7 +566,21 @@ def om_causal_plan(root: Any) -> dict | None:
         pos += n_i
     if pos != total:
         return None
-    return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(ks)}
+
+    def whole(blocks):
+        """The one tensor the blocks are consecutive row slices of, if they tile it: no join needed."""
+        base, at = None, 0
+        for t, n_i in zip(blocks, sizes):
+            r = _range_of(t, -2, memo)
+            if r is None or (base is not None and r[0] != base) or r[1] != at or r[2] != n_i or r[3] != total:
+                return None
+            base, at = r[0], at + n_i
+        return base
+
+    kb, vb = whole(ks), whole(vs)
+    if kb is not None and vb is not None:
+        ks, vs = [kb], [vb]
+    return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(sizes)}
 
 
 def _flatten(t: Any, op: str) -> list:

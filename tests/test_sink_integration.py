@@ -503,3 +503,26 @@ def test_omd_term_routes_to_b200_omd_and_keeps_reference_plan():
     A, B = torch.rand(5, 3, 3), torch.rand(5, 3)
     pa, pb = mod._prefix_scan(A, B, "dense")
     assert pa.shape == (5, 3, 3) and pb.shape == (5, 3) and mod.kernel_calls == 0
+
+
+def test_om_causal_blocks_that_slice_one_tensor_are_not_joined():
+    """Key/value blocks written as consecutive row slices of one K and one V (a
+    chunked attention over resident tensors): the plan hands the whole tensors to
+    the kernel instead of re-joining the slices."""
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    sizes, T, d = (4, 8, 4), 16, 4
+    q, k, v = Var("q", tt(2, T, d)), Var("k", tt(2, T, d)), Var("v", tt(2, T, d))
+    kall = k
+
+    def scores(kk):
+        return Op.make("om_decayed", q, Op.make("fill", q, value=0.5), Op.make("transpose", kk, dim0=-2, dim1=-1))
+
+    cm = Op.make("cmask", scores(kall))
+    leaves = [Op.make("om_elem",
+                      Op.make("masked_fill", scores(Op.make("split", k, dim=-2, index=i, sizes=sizes)),
+                              Op.make("split", cm, dim=2, index=i, sizes=sizes), Const(float("-inf"))),
+                      Op.make("split", v, dim=-2, index=i, sizes=sizes)) for i in range(3)]
+    root = Op.make("om_apply", Op.make("om_compose", leaves[0], Op.make("om_compose", leaves[1], leaves[2])))
+    plan = b200.om_causal_plan(root)
+    assert plan is not None and plan["n"] == 3 and plan["sizes"] == sizes
+    assert plan["k_blocks"] == [k] and plan["v_blocks"] == [v]
