@@ -70,6 +70,11 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
          C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_void_p],
     ),
+    "cb2_om_fwd": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+         C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
+    ),
     "cb2_diag_scan_fwd": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -19,7 +19,7 @@ namespace cb2 {
 // tensor-core kernel for bf16 tensors (om_causal_tc.cu)
 bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dtype);
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
-                     int dk, int dv, float scale, int* dev_status, cudaStream_t st);
+                     int dk, int dv, float scale, int causal, int* dev_status, cudaStream_t st);
 
 namespace {
 
@@ -44,7 +44,7 @@ __device__ __forceinline__ void st_e(void* p, size_t i, float v) {
 template <int DTYPE>
 __global__ void __launch_bounds__(kOmThreads)
 om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v,
-                 void* __restrict__ o, int Tq, int Tk, int dk, int dv, float scale) {
+                 void* __restrict__ o, int Tq, int Tk, int dk, int dv, float scale, int causal) {
   extern __shared__ __align__(16) float sm[];
   constexpr int kLd = kBlk + 4;
   float* Qt = sm;
@@ -70,8 +70,8 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][h][j] = 0.f;
   }
-  // keys beyond the last query of this block are hidden from every row of it
-  const int k_end = min(Tk, q0 + kBlk);
+  // causal: keys beyond the last query of this block are hidden from every row of it
+  const int k_end = causal ? min(Tk, q0 + kBlk) : Tk;
   for (int k0 = 0; k0 < k_end; k0 += kBlk) {
     __syncthreads();  // previous block's Pt / Kt / Vs fully consumed (and Qt written)
     for (int i = tid; i < kBlk * dk; i += kOmThreads) {
@@ -102,7 +102,7 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c = k0 + tx * 4 + j;
-        if (c > t || c >= Tk) s[i][j] = -INFINITY;
+        if ((causal && c > t) || c >= Tk) s[i][j] = -INFINITY;
         mb = fmaxf(mb, s[i][j]);
       }
 #pragma unroll
@@ -164,9 +164,9 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 }  // namespace
 }  // namespace cb2
 
-extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int H,
-                                 int Tq, int Tk, int dk, int dv, float scale, int dtype,
-                                 int* dev_status, void* stream) {
+extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq,
+                          int Tk, int dk, int dv, float scale, int causal, int dtype, int* dev_status,
+                          void* stream) {
   using namespace cb2;
   if (!q || !k || !v || !o) return CB2_NULL_PTR;
   if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0) return CB2_BAD_SHAPE;
@@ -177,20 +177,26 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) && aligned16(k) &&
       aligned16(v) && aligned16(o))
-    return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, dev_status, st);
+    return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, dev_status, st);
   if (dtype == CB2_BF16) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
-    om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale);
+    om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0);
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
-    om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale);
+    om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0);
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }
   CB2_LAUNCH_CHECK();
   return CB2_OK;
+}
+
+extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int H,
+                                 int Tq, int Tk, int dk, int dv, float scale, int dtype,
+                                 int* dev_status, void* stream) {
+  return cb2_om_fwd(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, 1, dtype, dev_status, stream);
 }

@@ -1,4 +1,4 @@
-// Causal softmax attention on the tensor cores (bf16, dk, dv <= 128): the
+// Softmax attention, causal or unmasked, on the tensor cores (bf16, dk, dv <= 128): the
 // online-softmax monoid of the reference (`_om_elem` / `_om_compose`,
 // catopt_torch/torch_bridge.py:1974-2006) folded over 128-key blocks, with the
 // running (max, sum) pair in registers and the weighted sum in tensor memory.
@@ -50,7 +50,7 @@ __device__ __forceinline__ float ex2(float x) {
 __global__ void __launch_bounds__(kThreads, 2)
 om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                    int Tq, int Tk, int dk, int dv, int n_bh, float scale_log2e, int* dev_status) {
+                    int Tq, int Tk, int dk, int dv, int n_bh, int causal, float scale_log2e, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -71,7 +71,8 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int bh = blockIdx.x % n_bh;
   const int qb = int(gridDim.x / n_bh) - 1 - int(blockIdx.x / n_bh);
   const int q0 = qb * kQ;
-  const int nkb = min((Tk + kQ - 1) / kQ, qb + 1);   // key blocks with at least one visible key
+  // key blocks with at least one visible key (all of them without the causal mask)
+  const int nkb = causal ? min((Tk + kQ - 1) / kQ, qb + 1) : (Tk + kQ - 1) / kQ;
 
   if (tid == 0) {
     for (int s = 0; s < kSlots; ++s) {
@@ -175,14 +176,14 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       const int k0 = j * kQ;
-      const bool partial = (k0 + kQ - 1 > q0) || (k0 + kQ > Tk);   // uniform over the CTA
+      const bool partial = (causal && k0 + kQ - 1 > q0) || (k0 + kQ > Tk);   // uniform over the CTA
 #pragma unroll
       for (int cb = 0; cb < 4; ++cb) umma::tmem_ld32(lane_base + scol + cb * 32, sv[cb]);
       umma::tmem_wait_ld();
       // hidden keys (beyond the diagonal or beyond Tk) score -inf: they never win the
       // maximum and exponentiate to exactly 0 (scale > 0 on this path)
       if (partial) {
-        const int lim = min(tq, Tk - 1) - k0;                // last visible column of the block
+        const int lim = (causal ? min(tq, Tk - 1) : Tk - 1) - k0;   // last visible column of the block
 #pragma unroll
         for (int cb = 0; cb < 4; ++cb)
 #pragma unroll
@@ -296,7 +297,7 @@ bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dt
 }
 
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
-                     int dk, int dv, float scale, int* dev_status, cudaStream_t st) {
+                     int dk, int dv, float scale, int causal, int* dev_status, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mo;
   const uint64_t bh = uint64_t(B) * H;
   int rc = umma::make_map_3d(&mq, q, true, dk, Tq, bh, 64, 128, true);
@@ -308,7 +309,7 @@ int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
   const unsigned grid = unsigned(((Tq + kQ - 1) / kQ) * bh);
-  om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh),
+  om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh), causal,
                                                          scale * 1.4426950408889634f, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;

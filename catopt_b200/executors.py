@@ -181,10 +181,11 @@ class B200CausalSoftmax(_GraphMixin, torch.nn.Module):
     (catopt_carriers/om_lower.py:729-835, 996-1040) on a causal ``om`` carrier.
     ``forward(q, k, v)`` on ``[B,H,T,d]`` tensors; ``scale=None`` means ``1/sqrt(d)``."""
 
-    def __init__(self, scale: float | None = None) -> None:
+    def __init__(self, scale: float | None = None, causal: bool = True) -> None:
         super().__init__()
         self.scale = scale
-        self._plan: dict | None = {"kind": "om_causal", "scale": scale}
+        self.causal = bool(causal)
+        self._plan: dict | None = {"kind": "om_causal" if causal else "om", "scale": scale}
         self._init_graph_state()
 
     @property
@@ -192,7 +193,7 @@ class B200CausalSoftmax(_GraphMixin, torch.nn.Module):
         return True
 
     def _forward_impl(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-        return ops.om_causal_fwd(q, k, v, self.scale)
+        return ops.om_causal_fwd(q, k, v, self.scale, causal=self.causal)
 
 
 # --------------------------------------------------------------------------- tensor-level entry points
@@ -231,9 +232,10 @@ def decayed_whole_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ga
     return out.reshape(*lead, out.shape[-2], out.shape[-1])
 
 
-def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale: float) -> torch.Tensor | None:
-    """Causal softmax attention of ``q [..., Tq, d]`` over key/value blocks joined
-    along the key axis, through ``cb2_om_causal_fwd``; ``None`` for fp64."""
+def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale: float,
+                          causal: bool = True) -> torch.Tensor | None:
+    """Softmax attention (causal by default) of ``q [..., Tq, d]`` over key/value
+    blocks joined along the key axis, through ``cb2_om_fwd``; ``None`` for fp64."""
     if not q.is_cuda:
         raise B200Error("causal softmax executor runs on CUDA tensors only (no CPU fallback)")
     if q.dtype not in (torch.float32, torch.bfloat16):
@@ -244,5 +246,5 @@ def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale
     H = lead[-1] if lead else 1
     q4, k4, v4 = (t.expand(*lead, *t.shape[-2:]).reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous()
                   for t in (q, k, v))
-    out = ops.om_causal_fwd(q4, k4, v4, scale)
+    out = ops.om_causal_fwd(q4, k4, v4, scale, causal=causal)
     return out.reshape(*lead, out.shape[-2], out.shape[-1])

@@ -167,10 +167,16 @@ def decayed_chunk_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: 
 
 
 # --------------------------------------------------------------------------- om causal
+def om_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
+           out: torch.Tensor | None = None, causal: bool = False) -> torch.Tensor:
+    """Softmax attention, unmasked by default (``om_causal_fwd`` with the mask as an argument)."""
+    return om_causal_fwd(q, k, v, scale, out, causal)
+
+
 def om_causal_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
-                  out: torch.Tensor | None = None) -> torch.Tensor:
-    """Causal softmax attention ``[B,H,Tq,dk] x [B,H,Tk,dk] x [B,H,Tk,dv]``; key j is
-    hidden from query t when j > t.  ``scale`` defaults to ``1/sqrt(dk)``."""
+                  out: torch.Tensor | None = None, causal: bool = True) -> torch.Tensor:
+    """Softmax attention ``[B,H,Tq,dk] x [B,H,Tk,dk] x [B,H,Tk,dv]``; with ``causal``
+    key j is hidden from query t when j > t.  ``scale`` defaults to ``1/sqrt(dk)``."""
     require_cuda(q, k, v, out)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise B200Error("om_causal_fwd takes rank-4 q, k, v")
@@ -183,10 +189,10 @@ def om_causal_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
     if out is None:
         out = torch.empty(B, H, Tq, dv, dtype=q.dtype, device=q.device)
     sc = float(scale) if scale is not None else 1.0 / float(dk) ** 0.5
-    rc = _lib.load().cb2_om_causal_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                       B, H, Tq, Tk, dk, dv, sc, dtype_code(q.dtype),
-                                       device_status(q.device).data_ptr(), stream_ptr())
-    check(rc, "cb2_om_causal_fwd")
+    rc = _lib.load().cb2_om_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                B, H, Tq, Tk, dk, dv, sc, 1 if causal else 0, dtype_code(q.dtype),
+                                device_status(q.device).data_ptr(), stream_ptr())
+    check(rc, "cb2_om_fwd")
     return out
 
 

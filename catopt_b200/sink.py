@@ -513,18 +513,20 @@ def _scaled_scores(t: Any) -> tuple | None:
 
 
 def om_causal_plan(root: Any) -> dict | None:
-    """Recognise causal softmax attention over a sequence of key/value blocks in
-    its online-softmax carrier form (the member the ``sdpa_cat_causal`` laws add,
-    tests/test_om_causal.py:286-330 of the reference):
+    """Recognise softmax attention over a sequence of key/value blocks in its
+    online-softmax carrier form (the members the ``sdpa_cat`` /
+    ``sdpa_cat_causal`` laws add, tests/test_om_causal.py:286-345 of the
+    reference):
 
-        om_apply(<om_compose tree of om_elem(masked_fill(S_i, M_i, -inf), v_i)>)
+        om_apply(<om_compose tree of om_elem(masked_fill(S_i, M_i, -inf), v_i)>)     causal
+        om_apply(<om_compose tree of om_elem(S_i, v_i)>)                             unmasked
 
     with ``S_i = (q * scale) @ k_i^T`` and ``M_i`` the columns ``[o_i, o_i + n_i)``
     of ``cmask(<any [.., Tq, sum n] tensor>)`` (bad where ``j > t``; o_i the keys
     before block i).  Leaves are read left to right = key order; every block must
     share q and the scale and appear once.  Returns ``{q, k_blocks, v_blocks,
-    sizes, scale, n}`` or ``None`` (unmasked carriers, offset masks, explicit
-    attention biases: the reference's own om executors keep them)."""
+    sizes, scale, n, causal}`` or ``None`` (offset masks, explicit attention
+    biases, mixed trees: the reference's own om executors keep them)."""
     if not (isinstance(root, Op) and root.op == "om_apply" and len(root.args) == 1):
         return None
     leaves = _flatten(root.args[0], "om_compose")
@@ -533,14 +535,19 @@ def om_causal_plan(root: Any) -> dict | None:
     memo: dict = {}
     q = scale = None
     ks, vs, sizes, pos, total = [], [], [], 0, None
+    causal = None
     for leaf in leaves:
         if not (isinstance(leaf, Op) and leaf.op == "om_elem" and len(leaf.args) == 2):
             return None
-        mf, v = leaf.args
-        if not (isinstance(mf, Op) and mf.op == "masked_fill" and len(mf.args) == 3
-                and _const_value(mf.args[2]) == float("-inf")):
+        sterm, v = leaf.args
+        masked = isinstance(sterm, Op) and sterm.op == "masked_fill"
+        if causal is None:
+            causal = masked
+        elif causal != masked:
             return None
-        sc = _scaled_scores(mf.args[0])
+        if masked and not (len(sterm.args) == 3 and _const_value(sterm.args[2]) == float("-inf")):
+            return None
+        sc = _scaled_scores(sterm.args[0] if masked else sterm)
         kshape = None if sc is None else _shape_of(sc[1], memo)
         if sc is None or not isinstance(kshape, tuple) or len(kshape) < 2 or not isinstance(kshape[-2], int):
             return None
@@ -549,21 +556,23 @@ def om_causal_plan(root: Any) -> dict | None:
             q, scale = sc[0], sc[2]
         elif sc[0] != q or sc[2] != scale:
             return None
-        # the mask: columns [pos, pos + n_i) of one cmask over the whole score tensor
-        m = mf.args[1]
-        r = _range_of(m, -1, memo)
-        if r is None:
-            return None
-        base, start, length, tot = r
-        if not (isinstance(base, Op) and base.op == "cmask" and int(base.attrs.get("off", 0) or 0) == 0):
-            return None
-        if (start, length) != (pos, n_i) or (total is not None and tot != total):
-            return None
-        total = tot
+        if masked:
+            # the mask: columns [pos, pos + n_i) of one cmask over the whole score tensor
+            r = _range_of(sterm.args[1], -1, memo)
+            if r is None:
+                return None
+            base, start, length, tot = r
+            if not (isinstance(base, Op) and base.op == "cmask" and int(base.attrs.get("off", 0) or 0) == 0):
+                return None
+            if (start, length) != (pos, n_i) or (total is not None and tot != total):
+                return None
+            total = tot
         ks.append(sc[1])
         vs.append(v)
         sizes.append(n_i)
         pos += n_i
+    if not causal:
+        total = pos
     if pos != total:
         return None
 
@@ -580,7 +589,8 @@ def om_causal_plan(root: Any) -> dict | None:
     kb, vb = whole(ks), whole(vs)
     if kb is not None and vb is not None:
         ks, vs = [kb], [vb]
-    return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(sizes)}
+    return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(sizes),
+            "causal": bool(causal)}
 
 
 def _flatten(t: Any, op: str) -> list:
@@ -619,7 +629,7 @@ class B200CausalSoftmaxModule(_EvalBase):
             return self.eval_mod(*xs)
         ev = self._ev(xs)
         out = causal_softmax_blocks(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
-                                    [ev(t) for t in plan["v_blocks"]], plan["scale"])
+                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"])
         return self.eval_mod(*xs) if out is None else out     # fp64: generic module, same device
 
 

@@ -216,6 +216,14 @@ int cb2_diag_compose_apply(const void* a_seq, const void* b_seq, const void* h, 
 int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B,
                       int H, int Tq, int Tk, int dk, int dv, float scale, int dtype,
                       int* dev_status, void* stream);
+/* The same executor with the mask as an argument: causal != 0 hides key j from
+ * query t when j > t (cb2_om_causal_fwd), causal == 0 is plain softmax
+ * attention — the unmasked carrier the reference's sdpa-over-concat law
+ * produces (`om_apply(<om_compose tree of om_elem(scores_i, v_i)>)`,
+ * catopt_carriers/om_lower.py:729-835). */
+int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int H,
+               int Tq, int Tk, int dk, int dv, float scale, int causal, int dtype,
+               int* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

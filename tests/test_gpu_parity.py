@@ -515,6 +515,24 @@ def test_om_causal_bf16_tensor_core_path(dev, B, H, Tq, Tk, dk, dv):
     assert rel_to_max(out, want) <= BF16_TOL
 
 
+@pytest.mark.parametrize("B,H,Tq,Tk,dk,dv,dtype", [(1, 2, 300, 300, 64, 64, torch.bfloat16),
+                                                   (2, 3, 128, 1000, 128, 128, torch.bfloat16),
+                                                   (1, 1, 70, 33, 16, 24, torch.float32),
+                                                   (1, 2, 1, 257, 32, 32, torch.bfloat16)])
+def test_om_unmasked_softmax_attention(dev, B, H, Tq, Tk, dk, dv, dtype):
+    """cb2_om_fwd with causal = 0 (the unmasked om carrier): plain softmax attention
+    on both kernels, ragged lengths, Tq != Tk, against fp64."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(Tq * 7 + Tk)
+    q = torch.randn(B, H, Tq, dk, generator=g).to(dtype)
+    k = torch.randn(B, H, Tk, dk, generator=g).to(dtype)
+    v = torch.randn(B, H, Tk, dv, generator=g).to(dtype)
+    out = ops.om_fwd(q.to(dev), k.to(dev), v.to(dev), 0.3)
+    want = torch.softmax((q.double() * 0.3) @ k.double().transpose(-1, -2), -1) @ v.double()
+    assert out.dtype == dtype and rel_to_max(out, want) <= (BF16_TOL if dtype == torch.bfloat16 else FP32_TOL)
+
+
 def test_causal_softmax_blocks_entry_point(dev):
     """What the catopt-facing causal module runs after evaluating its operands:
     key/value blocks of uneven sizes joined on the key axis, rank-3 and rank-4

@@ -392,7 +392,7 @@ def test_om_causal_carrier_is_recognised_and_means_causal_attention(ksizes, Tq, 
 
     ir, _ = _om_causal_term(ksizes, Tq, right_nested=right_nested)
     plan = b200.om_causal_plan(ir.root)
-    assert plan is not None and plan["sizes"] == tuple(ksizes) and plan["scale"] == 0.5
+    assert plan is not None and plan["sizes"] == tuple(ksizes) and plan["scale"] == 0.5 and plan["causal"]
     assert plan["q"].name == "q" and [k.name for k in plan["k_blocks"]] == [f"k{i}" for i in range(len(ksizes))]
     assert [v.name for v in plan["v_blocks"]] == [f"v{i}" for i in range(len(ksizes))]
     assert _route(b200.B200Sink(), ir.root).name == "b200_om_causal"
@@ -424,8 +424,11 @@ def test_om_causal_lookalikes_are_declined():
     assert b200.om_causal_plan(shifted.root) is None
     plain = Op.make("om_apply", Op.make("om_compose", *[Op.make("om_elem", lf.args[0].args[0], lf.args[1])
                                                          for lf in leaves[:2]]))
-    assert b200.om_causal_plan(plain) is None
-    assert _route(s, plain).name in ("om_batched", "om_streaming")
+    pp = b200.om_causal_plan(plain)              # the unmasked carrier is plain softmax attention
+    assert pp is not None and pp["causal"] is False and pp["sizes"] == (4, 4)
+    mixed = Op.make("om_apply", Op.make("om_compose", a, Op.make("om_elem", b_.args[0].args[0], b_.args[1])))
+    assert b200.om_causal_plan(mixed) is None    # one masked and one unmasked leaf: not ours
+    assert _route(s, mixed).name in ("om_batched", "om_streaming")
     # different scale on one block
     other, ol = _om_causal_term((4, 4, 4), 12, scale=0.25)
     assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", a, Op.make("om_compose", ol[1], c)))) is None
@@ -462,9 +465,10 @@ def test_om_causal_real_saturation_member_is_accepted():
         plan = b200.om_causal_plan(term)
         assert plan is not None and plan["sizes"] == tuple(ksizes), (ksizes, kw)
         assert _route(b200.B200Sink(), term).name == "b200_om_causal"
-    # the unmasked companion carrier stays with the reference's executors
+    # the unmasked companion carrier is taken as plain softmax attention
     _, term, _, _, _ = helper._causal_chunked_ok([3, 6], causal=False)
-    assert b200.om_causal_plan(term) is None
+    plan = b200.om_causal_plan(term)
+    assert plan is not None and plan["causal"] is False and plan["sizes"] == (3, 6)
 
 
 # --------------------------------------------------------------------------- omd: prefix-scan hook
