@@ -487,6 +487,11 @@ def run_profile_case(args) -> None:
         q, k, v = (_randn_bf16((32, 8192 * 128), gen).view(1, 32, 8192, 128) for _ in range(3))
         o = torch.empty_like(v)
         fn = lambda: ops.om_causal_fwd(q, k, v, out=o)  # noqa: E731
+    elif args.profile_case == "compose":      # 1024 stacked leaf maps over config 3's state, fp32: 1.07 GB
+        al = torch.sigmoid(4 + 0.5 * torch.randn(1024, 8 * 1024 * 16, device=dev, generator=gen))
+        bl = torch.randn(1024, 8 * 1024 * 16, device=dev, generator=gen)
+        hl = torch.zeros(8 * 1024 * 16, device=dev)
+        fn = lambda: ops.diag_compose_apply(al, bl, hl)  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
         ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
         outp = ref.clone()
@@ -513,7 +518,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal"],
+                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
