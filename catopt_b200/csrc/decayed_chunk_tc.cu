@@ -1,10 +1,11 @@
 // Chunked decayed attention on the 5th-generation tensor cores (bf16 tensors,
-// dk, dv <= 128, T a multiple of 128): one CTA per (batch, head) walks 128-row
+// dk, dv <= 128, any T): one CTA per (batch, head) walks 128-row
 // chunks in order and keeps the fp32 inter-chunk state in tensor memory for the
 // whole sequence.  The value does not depend on the chunking, so the kernel
 // always uses 128-row chunks whatever chunk size the lowered term was cut into;
-// head dimensions below 128 are zero-padded for free by the TMA (columns past
-// dk / dv are out of range of the tensor map and arrive as zeros).
+// head dimensions below 128 and a ragged last chunk are zero-padded for free by
+// the TMA (columns past dk / dv and rows past T are out of range of the per-head
+// tensor map: they arrive as zeros, contribute nothing, and are clipped on store).
 //
 // Per chunk i (C = 128 rows, g = gamma of the head):
 //   MMA1  S  = Q_i K_i^T                                  (TMEM cols   0..127)
@@ -129,7 +130,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x % n_bh;
   const int seg = blockIdx.x / n_bh;               // segment-major launch order
-  const int nchunk = T / kC / n_seg;               // chunks of this segment
+  const int nchunk = (T + kC - 1) / kC / n_seg;    // chunks of this segment
   const int chunk0 = seg * nchunk;                 // first chunk of the segment in the sequence
   const bool has_in = seg > 0;                     // starts from a predecessor's state
   const float g = gamma[bh % H];
@@ -181,10 +182,10 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int i = t / 3, which = t % 3;  // 0: K, 1: Q, 2: V
         const CUtensorMap* m = which == 0 ? &map_k : (which == 1 ? &map_q : &map_v);
         unsigned char* dst = smem + kOffRing + slot * kTile;
-        const int row = bh * T + (chunk0 + i) * kC;
+        const int row = (chunk0 + i) * kC;   // rows past T (ragged last chunk) arrive as zeros
         mbar_arrive_expect_tx(&B.full[slot], kTile);
-        umma::tma_load_2d(dst, m, 0, row, &B.full[slot]);
-        umma::tma_load_2d(dst + umma::kSubTileBytes, m, 64, row, &B.full[slot]);
+        umma::tma_load_3d(dst, m, 0, row, bh, &B.full[slot]);
+        umma::tma_load_3d(dst + umma::kSubTileBytes, m, 64, row, bh, &B.full[slot]);
       }
     }
   } else if (warp == 1) {
@@ -406,9 +407,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       wg_phase ^= 1;
       if (!__all_sync(0xffffffffu, ok)) break;
       if (tid == 64) {  // whole tile written: two {64 x 128} boxes go out asynchronously
-        const int row = bh * T + (chunk0 + i) * kC;
-        umma::tma_store_2d(&map_o, 0, row, o_tile);
-        if (dv > 64) umma::tma_store_2d(&map_o, 64, row, o_tile + umma::kSubTileBytes);
+        const int row = (chunk0 + i) * kC;   // the store is clipped at T
+        umma::tma_store_3d(&map_o, 0, row, bh, o_tile);
+        if (dv > 64) umma::tma_store_3d(&map_o, 64, row, bh, o_tile + umma::kSubTileBytes);
         bulk_commit();
       }
       CB2_TL(i, 5);
@@ -465,7 +466,7 @@ bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype)
   // TMA row coordinates are 32-bit signed
   (void)C;  // the result is independent of the chunk size: 128-row chunks are used
   return dtype == CB2_BF16 && dk >= 8 && dk <= kC && dk % 8 == 0 && dv >= 8 && dv <= kC && dv % 8 == 0 &&
-         T % kC == 0 && T >= kC && int64_t(B) * H * T < (int64_t(1) << 31);
+         T >= 1 && T < (1 << 30) && int64_t(B) * H < (int64_t(1) << 31);
 }
 
 // Segments per head: the smallest count in {1, 2, 4, 8} that fills the last wave
@@ -498,7 +499,7 @@ int device_sms() {
 // Scratch that lets heads be cut into segments: (n_seg - 1) * B*H states of
 // 128 x 128 fp32, then as many flags.
 size_t decayed_tc_scratch_bytes(int B, int H, int T) {
-  const int n_seg = decayed_tc_segments(B * H, T / kC, device_sms());
+  const int n_seg = decayed_tc_segments(B * H, (T + kC - 1) / kC, device_sms());
   return size_t(n_seg - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
 }
 
@@ -506,19 +507,21 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
                    int H, int T, int dk, int dv, int C, float scale, void* scratch, size_t scratch_bytes,
                    int* dev_status, cudaStream_t st) {
   (void)C;
-  const uint64_t rows = uint64_t(B) * H * T;
+  // one map row = one position of one head; the head axis is the third coordinate, so
+  // a ragged last chunk is zero-filled on load and clipped on store per head
+  const uint64_t heads = uint64_t(B) * H;
   CUtensorMap mq, mk, mv, mo;
-  int rc = umma::make_tile_map(&mq, q, rows, dk);
-  if (rc == CB2_OK) rc = umma::make_tile_map(&mk, k, rows, dk);
-  if (rc == CB2_OK) rc = umma::make_tile_map(&mv, v, rows, dv);
-  if (rc == CB2_OK) rc = umma::make_tile_map(&mo, o, rows, dv);
+  int rc = umma::make_map_3d(&mq, q, true, dk, T, heads, 64, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mk, k, true, dk, T, heads, 64, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mv, v, true, dv, T, heads, 64, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mo, o, true, dv, T, heads, 64, 128, true);
   if (rc != CB2_OK) return rc;
   // per device, so set on every call (cheap) rather than cached per process
   if (cudaFuncSetAttribute(decayed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
   const int n_bh = B * H;
-  int n_seg = decayed_tc_segments(n_bh, T / kC, device_sms());
+  int n_seg = decayed_tc_segments(n_bh, (T + kC - 1) / kC, device_sms());
   const size_t state_bytes = size_t(n_seg - 1) * n_bh * size_t(kC) * kC * sizeof(float);
   const size_t flag_bytes = size_t(n_seg - 1) * n_bh * sizeof(int);
   if (n_seg > 1 && (!scratch || !aligned16(scratch) || scratch_bytes < state_bytes + flag_bytes ||

@@ -344,6 +344,24 @@ def test_decayed_bf16_many_heads_and_scale(dev):
         assert rel_to_max(out[b:b + 1, h:h + 1], want) <= BF16_TOL
 
 
+@pytest.mark.parametrize("B,H,T,d,C", [(1, 2, 1000, 128, 125), (2, 3, 200, 64, 8), (1, 1, 77, 32, 77),
+                                       (1, 160, 1100, 128, 100)])
+def test_decayed_bf16_sequence_lengths_off_the_tile_grid(dev, B, H, T, d, C):
+    """bf16 sequences whose length is not a multiple of the kernel's 128-row tile:
+    the last tile is zero-filled on load and clipped on store, per head (the last
+    case also cuts 160 heads into segments of an odd number of tiles)."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(T + d)
+    q, k, v = (torch.randn(B, H, T, d, generator=g).bfloat16() / 4 for _ in range(3))
+    gam = (1 - torch.exp2(-4 - 6 * torch.arange(H) / H)).float()
+    out = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gam.to(dev), C, 1.5)
+    sel = list(range(H)) if H <= 3 else [0, H // 2, H - 1]   # a store past T would land in the next head
+    want = oracle.decayed_quadratic(q[:, sel].double(), k[:, sel].double(), v[:, sel].double(), gam[sel].double(), 1.5)
+    assert rel_to_max(out[:, sel], want) <= BF16_TOL
+    ops.check_device_status(dev)
+
+
 def test_decayed_bf16_segmented_heads(dev):
     """More heads than SMs: the tensor-core kernel cuts every head into segments
     that different CTAs run, the state crossing through scratch.  Same result as
