@@ -1,7 +1,7 @@
 // C-ABI front of the chunked decayed-attention executor: argument checks and
-// the choice between the tensor-core kernel (bf16, dk and dv up to 128, T a
-// multiple of 128; state kept on chip, optional scratch for cutting heads into
-// segments) and the fp32 FMA path (everything else, state in scratch).
+// the choice between the tensor-core kernel (bf16, dk and dv multiples of 8 up to
+// 128; state kept on chip, optional scratch for cutting heads into segments) and
+// the fp32 FMA path (everything else, state in scratch).
 #include "common.cuh"
 
 namespace cb2 {
