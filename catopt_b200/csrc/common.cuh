@@ -128,14 +128,6 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src,
       "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// shared -> global, tracked by the issuing thread's bulk async-group.
-__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src,
-                                         uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::
-                   "l"(gmem_dst),
-               "r"(smem_u32(smem_src)), "r"(bytes)
-               : "memory");
-}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

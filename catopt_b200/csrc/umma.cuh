@@ -150,48 +150,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
-// shared -> global store of one {64 x 128} box (tracked by the thread's bulk group)
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int x, int y,
-                                             const void* smem_src) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap),
-      "r"(x), "r"(y), "r"(smem_u32(smem_src))
-      : "memory");
-}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
-// ---- host: tensor map for a row-major [rows x cols] bf16 matrix (cols <= 128) --
-// Box {64 columns, 128 rows}, 128-byte swizzle; a box that reaches past `cols`
-// is filled with zeros on load and clipped on store.  Uses the driver entry point
-// through the runtime so the library does not link libcuda.
-inline int make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols) {
-  using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                          const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                          CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                          CUtensorMapFloatOOBfill);
-  static Fn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess || !p)
-      return CB2_LAUNCH_FAIL;
-    fn = reinterpret_cast<Fn>(p);
-  }
-  const cuuint64_t gdim[2] = {cols, rows};
-  const cuuint64_t gstride[1] = {cols * 2};
-  const cuuint32_t box[2] = {64, 128};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim,
-                        gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? CB2_OK : CB2_LAUNCH_FAIL;
-}
-
 // ---- host: 3-D tensor map {d0 (inner), d1, d2}, box {b0, b1, 1}, optional 128-byte swizzle --
+// A box that reaches past an extent is filled with zeros on load and clipped on store.  The
+// encoder is taken from the driver through the runtime's entry-point query, so the library
+// does not link against the driver library directly.
 inline int make_map_3d(CUtensorMap* out, const void* base, bool is_bf16, uint64_t d0, uint64_t d1,
                        uint64_t d2, uint32_t b0, uint32_t b1, bool swizzle128 = false) {
   using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
