@@ -530,3 +530,49 @@ def test_om_causal_blocks_that_slice_one_tensor_are_not_joined():
     plan = b200.om_causal_plan(root)
     assert plan is not None and plan["n"] == 3 and plan["sizes"] == sizes
     assert plan["k_blocks"] == [k] and plan["v_blocks"] == [v]
+
+
+def test_ragged_recogniser_on_random_partitions():
+    """Seeded random partitions: arms of random sizes, each reaching back to a random
+    coarsening of the rows before it.  Every such term is decayed attention of the whole
+    sequence and must be accepted with the arms' sizes; shifting any one row gate must
+    be declined."""
+    import random
+
+    rnd = random.Random(20240607)
+    for _ in range(25):
+        n_arms = rnd.randint(2, 6)
+        arms = tuple(rnd.choice((4, 8, 12, 16, 24)) for _ in range(n_arms))
+        sources, start = [], 0
+        for i, s in enumerate(arms):
+            # random coarsening of the previous arms' boundaries
+            cuts = [0]
+            acc = 0
+            for prev in arms[:i]:
+                acc += prev
+                if acc < start and rnd.random() < 0.5:
+                    cuts.append(acc)
+            cuts.append(start)
+            sources.append(tuple(b - a for a, b in zip(cuts[:-1], cuts[1:]) if b > a))
+            start += s
+        ir = _ragged_term(sum(arms), 4, arms, sources, scale=1.0, nested=rnd.random() < 0.5)
+        plan = b200.decayed_ragged_plan(ir.root)
+        assert plan is not None and plan["sizes"] == arms, (arms, sources)
+        # break it: one row gate off by one (wherever that gate occurs)
+        gates = []
+
+        def collect(n):
+            if n.op == "decay_vec" and int(n.attrs.get("offset", 0) or 0) > 0:
+                gates.append((n.attrs.get("t"), n.attrs.get("offset")))
+            return n
+
+        _mutate(ir, collect)
+        t_bad, off_bad = rnd.choice(sorted(set(gates)))
+
+        def bump(n):
+            if n.op == "decay_vec" and n.attrs.get("t") == t_bad and n.attrs.get("offset") == off_bad:
+                return Op.make("decay_vec", *n.args, t=t_bad, offset=off_bad + 1)
+            return n
+
+        bad = _mutate(ir, bump)
+        assert bad != ir.root and b200.decayed_ragged_plan(bad) is None
