@@ -551,6 +551,27 @@ def test_om_unmasked_softmax_attention(dev, B, H, Tq, Tk, dk, dv, dtype):
     assert out.dtype == dtype and rel_to_max(out, want) <= (BF16_TOL if dtype == torch.bfloat16 else FP32_TOL)
 
 
+def test_om_causal_bf16_growing_and_peaked_scores(dev):
+    """Score patterns that stress the lazily updated reference point of the
+    tensor-core softmax: maxima that creep up block after block (just under and
+    just over the update threshold), and very peaked rows."""
+    from catopt_b200 import ops
+
+    T, d = 1024, 64
+    g = torch.Generator().manual_seed(99)
+    base = torch.randn(1, 2, T, d, generator=g)
+    for ramp, gain in ((0.004, 1.0), (0.02, 1.0), (0.0, 12.0)):
+        # keys grow along the sequence in the direction of the queries -> row maxima keep rising
+        dirn = torch.ones(d) / math.sqrt(d)
+        k = (base * 0.3 + ramp * torch.arange(T).view(1, 1, T, 1) * dirn).bfloat16()
+        q = ((torch.randn(1, 2, T, d, generator=g) * 0.3 + 4.0 * dirn) * gain).bfloat16()
+        v = torch.randn(1, 2, T, d, generator=g).bfloat16()
+        out = ops.om_causal_fwd(q.to(dev), k.to(dev), v.to(dev))
+        want = oracle.om_causal_chunked(q.double(), k.double(), v.double(), [T])
+        assert torch.isfinite(out.float()).all()
+        assert rel_to_max(out, want) <= BF16_TOL, (ramp, gain)
+
+
 def test_causal_softmax_blocks_entry_point(dev):
     """What the catopt-facing causal module runs after evaluating its operands:
     key/value blocks of uneven sizes joined on the key axis, rank-3 and rank-4
