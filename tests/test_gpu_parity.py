@@ -311,6 +311,32 @@ def test_cuda_graph_replay_matches_eager(dev):
     assert not mod.is_graph_captured
 
 
+def test_cuda_graph_replay_of_segmented_heads_and_other_executors(dev):
+    """Graph capture of the launches that do more than one thing per call: the
+    tensor-core decayed kernel with heads cut into segments (flag reset + kernel),
+    the 3xTF32 GEMM (weight split + GEMM) and the composed scan map (two kernels).
+    Replays on new inputs must equal eager runs bit for bit."""
+    from catopt_b200 import ops
+    from catopt_b200.executors import B200CausalSoftmax, B200ChunkedDecay, B200FoldedLinear
+
+    g = torch.Generator().manual_seed(8)
+    q, k, v = (torch.randn(3, 64, 1024, 64, generator=g).bfloat16().to(dev) / 4 for _ in range(3))
+    gam = (1 - torch.exp2(-5 - 8 * torch.arange(64) / 64)).float()
+    mod = B200ChunkedDecay(gam, 64, 128).to(dev)
+    mod.capture_cuda_graph(q, k, v)
+    for scale in (1.0, 0.5, 0.25):                     # several replays: the segment flags must be reset each time
+        qq = q * scale
+        assert torch.equal(mod(qq, k, v), mod._forward_impl(qq, k, v))
+    lin = B200FoldedLinear([torch.randn(256, 256, generator=g).to(dev) / 16 for _ in range(3)])
+    x = torch.randn(512, 256, generator=g).to(dev)
+    lin.capture_cuda_graph(x)
+    assert torch.equal(lin(x * 2), lin._forward_impl(x * 2))
+    att = B200CausalSoftmax().to(dev)
+    att.capture_cuda_graph(q[:1, :4], k[:1, :4], v[:1, :4])
+    assert torch.equal(att(q[1:2, :4], k[:1, :4], v[:1, :4]), att._forward_impl(q[1:2, :4], k[:1, :4], v[:1, :4]))
+    ops.check_device_status(dev)
+
+
 # --------------------------------------------------------------------------- more edges
 @pytest.mark.parametrize("gam", [1.0, 0.5, 0.01, 1e-4])
 def test_decayed_bf16_extreme_rates(dev, gam):
