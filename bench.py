@@ -277,7 +277,7 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     g2 = torch.full((4,), 0.97, device=dev)
     o2 = torch.empty_like(v)
     ms = time_steps(lambda: ops.decayed_chunk_fwd(q, k, v, g2, 64, 1.0, out=o2), K, W, world, flush)
-    out["config2_decayed_fp32"] = entry(ms, 2 * 1024, 4 * 2 * 4 * 1024 * 64 * 4, 3,
+    out["config2_decayed_fp32"] = entry(ms, 2 * 1024, 4 * 2 * 4 * 1024 * 64 * 4, 1,
                                         "latency-bound: 8 heads; L2 flushed between steps",
                                         flops=8 * 1024 * (4 * 64 * 64 + 4 * 64 * 64))
     del q, k, v, o2

@@ -23,6 +23,7 @@ SOURCES = [
     "linear_f32.cu",
     "linear_tf32x3.cu",
     "decayed_chunk_ffma.cu",
+    "decayed_chunk_small.cu",
     "decayed_chunk_tc.cu",
     "decayed_chunk.cu",
     "om_causal.cu",

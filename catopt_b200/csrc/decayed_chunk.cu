@@ -1,7 +1,8 @@
 // C-ABI front of the chunked decayed-attention executor: argument checks and
 // the choice between the tensor-core kernel (bf16, dk and dv multiples of 8 up to
 // 128; state kept on chip, optional scratch for cutting heads into segments) and
-// the fp32 FMA path (everything else, state in scratch).
+// the fp32 FMA paths (everything else): one fused launch for a few small chunks,
+// three launches with the state in scratch otherwise.
 #include "common.cuh"
 
 namespace cb2 {
@@ -9,6 +10,11 @@ size_t decayed_ffma_scratch_bytes(int B, int H, int T, int dk, int dv, int C);
 int decayed_ffma_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
                      int H, int T, int dk, int dv, int C, float scale, int dtype, void* scratch,
                      cudaStream_t st);
+bool decayed_small_supported(int B, int H, int T, int dk, int dv, int C);
+size_t decayed_small_scratch_bytes(int B, int H, int T, int C);
+int decayed_small_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B, int H,
+                      int T, int dk, int dv, int C, float scale, int dtype, void* scratch, int* dev_status,
+                      cudaStream_t st);
 bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype);
 size_t decayed_tc_scratch_bytes(int B, int H, int T);
 int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
@@ -28,6 +34,7 @@ extern "C" size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, i
                                                   int dtype) {
   if (cb2::check_shape(B, H, T, dk, dv, chunk) != CB2_OK) return 0;
   if (cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)) return cb2::decayed_tc_scratch_bytes(B, H, T);
+  if (cb2::decayed_small_supported(B, H, T, dk, dv, chunk)) return cb2::decayed_small_scratch_bytes(B, H, T, chunk);
   return cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
 }
 
@@ -53,6 +60,11 @@ extern "C" int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v
       return CB2_BAD_ALIGN;
     return cb2::decayed_tc_run(q, k, v, o, gamma, B, H, T, dk, dv, chunk, scale, scratch, scratch_bytes,
                                dev_status, st);
+  }
+  if (cb2::decayed_small_supported(B, H, T, dk, dv, chunk)) {   // few small chunks: one launch
+    if (!scratch || scratch_bytes < cb2::decayed_small_scratch_bytes(B, H, T, chunk)) return CB2_SCRATCH_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(scratch) & 15u) return CB2_BAD_ALIGN;
+    return cb2::decayed_small_run(q, k, v, o, gamma, B, H, T, dk, dv, chunk, scale, dtype, scratch, dev_status, st);
   }
   const size_t need = cb2::decayed_ffma_scratch_bytes(B, H, T, dk, dv, chunk);
   if (!scratch || scratch_bytes < need) return CB2_SCRATCH_TOO_SMALL;
