@@ -75,6 +75,10 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
          C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
     ),
+    "cb2_om_step": (
+        C.c_int,
+        [C.c_void_p] * 9 + [C.c_int] * 6 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p],
+    ),
     "cb2_diag_scan_fwd": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -44,7 +44,10 @@ __device__ __forceinline__ void st_e(void* p, size_t i, float v) {
 template <int DTYPE>
 __global__ void __launch_bounds__(kOmThreads)
 om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v,
-                 void* __restrict__ o, int Tq, int Tk, int dk, int dv, float scale, int causal) {
+                 void* __restrict__ o, int Tq, int Tk, int dk, int dv, float scale, int causal,
+                 int key_offset, const float* __restrict__ m_in, const float* __restrict__ l_in,
+                 const float* __restrict__ a_in, float* __restrict__ m_out, float* __restrict__ l_out,
+                 float* __restrict__ a_out) {
   extern __shared__ __align__(16) float sm[];
   constexpr int kLd = kBlk + 4;
   float* Qt = sm;
@@ -60,18 +63,26 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
     const int r = i / dk, e = i % dk;
     Qt[e * kLd + r] = (q0 + r < Tq) ? ld_e<DTYPE>(q, qbase + size_t(q0 + r) * dk + e) * scale : 0.f;
   }
+  // running carrier (m, l, a) per row: the identity (-inf, 0, 0), or the caller's state
   float m_run[4], l_run[4], acc[4][2][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    m_run[i] = -INFINITY;
-    l_run[i] = 0.f;
+    const int t = q0 + ty * 4 + i;
+    const bool have = m_in != nullptr && t < Tq;
+    const size_t srow = size_t(bh) * Tq + (have ? t : 0);
+    m_run[i] = have ? m_in[srow] : -INFINITY;
+    l_run[i] = have ? l_in[srow] : 0.f;
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][h][j] = 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const int f = h * 64 + tx * 4 + j;
+        acc[i][h][j] = (have && h < nf && f < dv) ? a_in[srow * dv + f] : 0.f;
+      }
   }
-  // causal: keys beyond the last query of this block are hidden from every row of it
-  const int k_end = causal ? min(Tk, q0 + kBlk) : Tk;
+  // causal: key j of this call is key (key_offset + j) of the whole sequence and is hidden
+  // from query t when key_offset + j > t; blocks past the last query's horizon are skipped
+  const int k_end = causal ? max(0, min(Tk, q0 + kBlk - key_offset)) : Tk;
   for (int k0 = 0; k0 < k_end; k0 += kBlk) {
     __syncthreads();  // previous block's Pt / Kt / Vs fully consumed (and Qt written)
     for (int i = tid; i < kBlk * dk; i += kOmThreads) {
@@ -102,7 +113,7 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c = k0 + tx * 4 + j;
-        if ((causal && c > t) || c >= Tk) s[i][j] = -INFINITY;
+        if ((causal && c + key_offset > t) || c >= Tk) s[i][j] = -INFINITY;
         mb = fmaxf(mb, s[i][j]);
       }
 #pragma unroll
@@ -151,12 +162,22 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
   for (int i = 0; i < 4; ++i) {
     const int t = q0 + ty * 4 + i;
     if (t >= Tq) continue;
+    const size_t srow = size_t(bh) * Tq + t;
+    if (m_out != nullptr && tx == 0) {
+      m_out[srow] = m_run[i];
+      l_out[srow] = l_run[i];
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int f = h * 64 + tx * 4 + j;
-        if (h < nf && f < dv) st_e<DTYPE>(o, (size_t(bh) * Tq + t) * dv + f, acc[i][h][j] / l_run[i]);
+        if (h < nf && f < dv) {
+          if (m_out != nullptr)
+            a_out[srow * dv + f] = acc[i][h][j];                        // the raw carrier
+          else
+            st_e<DTYPE>(o, srow * dv + f, acc[i][h][j] / l_run[i]);     // the om_apply readout a / l
+        }
       }
   }
 }
@@ -182,12 +203,14 @@ extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, 
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
-    om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0);
+    om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr, nullptr,
+                                                               nullptr, nullptr);
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
-    om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0);
+    om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr, nullptr,
+                                                               nullptr, nullptr);
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }
@@ -199,4 +222,35 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
                                  int Tq, int Tk, int dk, int dv, float scale, int dtype,
                                  int* dev_status, void* stream) {
   return cb2_om_fwd(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, 1, dtype, dev_status, stream);
+}
+
+extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
+                           const float* a_in, float* m_out, float* l_out, float* a_out, int B, int H, int Tq,
+                           int Tk, int dk, int dv, float scale, int causal, int key_offset, int dtype,
+                           void* stream) {
+  using namespace cb2;
+  if (!q || !k || !v || !m_out || !l_out || !a_out) return CB2_NULL_PTR;
+  if ((m_in == nullptr) != (l_in == nullptr) || (m_in == nullptr) != (a_in == nullptr)) return CB2_NULL_PTR;
+  if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0 || key_offset < 0) return CB2_BAD_SHAPE;
+  if (dk > kMaxD || dv > kMaxD || size_t(B) * H > 65535) return CB2_BAD_SHAPE;
+  const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
+  const dim3 grid((Tq + kBlk - 1) / kBlk, B * H);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CB2_BF16) {
+    if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(smem)) != cudaSuccess)
+      return CB2_LAUNCH_FAIL;
+    om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
+                                                               key_offset, m_in, l_in, a_in, m_out, l_out, a_out);
+  } else if (dtype == CB2_F32) {
+    if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(smem)) != cudaSuccess)
+      return CB2_LAUNCH_FAIL;
+    om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
+                                                              key_offset, m_in, l_in, a_in, m_out, l_out, a_out);
+  } else {
+    return CB2_UNSUPPORTED_DTYPE;
+  }
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
 }

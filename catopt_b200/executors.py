@@ -248,3 +248,26 @@ def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale
                   for t in (q, k, v))
     out = ops.om_causal_fwd(q4, k4, v4, scale, causal=causal)
     return out.reshape(*lead, out.shape[-2], out.shape[-1])
+
+
+def softmax_blocks_state(q: torch.Tensor, k_blocks: list, v_blocks: list, scale: float, causal: bool = True,
+                         state: tuple | None = None, key_offset: int = 0) -> tuple:
+    """Streaming fold of key/value blocks into the online-softmax carrier
+    ``(m, l, a)`` (fp32), one ``cb2_om_step`` per block — the state a decode loop
+    checkpoints (``StreamingOMModule.forward_state``, catopt_carriers/om_lower.py:
+    1003-1040).  Read it out with ``ops.om_apply_state``; feed it back as ``state``
+    (with ``key_offset`` = keys already folded) when more blocks arrive."""
+    if not q.is_cuda:
+        raise B200Error("streaming softmax executor runs on CUDA tensors only (no CPU fallback)")
+    lead = q.shape[:-2]
+    H = lead[-1] if lead else 1
+
+    def r4(t):
+        return t.expand(*lead, *t.shape[-2:]).reshape(-1, H, t.shape[-2], t.shape[-1])
+
+    if state is not None:
+        state = tuple(r4(t) for t in state)
+    for kb, vb in zip(k_blocks, v_blocks):
+        state = ops.om_step_qk(state, r4(q), r4(kb), r4(vb), scale, causal, key_offset)
+        key_offset += kb.shape[-2]
+    return tuple(t.reshape(*lead, *t.shape[-2:]) for t in state)

@@ -196,6 +196,54 @@ def om_causal_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
     return out
 
 
+def om_empty_state(shape: tuple, dv: int, device: torch.device | str) -> tuple:
+    """The identity carrier ``(m, l, a) = (-inf, 0, 0)`` for queries of leading shape
+    ``shape = (B, H, Tq)`` (``om_empty_state``, catopt_carriers/om_lower.py:871-893);
+    fp32: ``m, l [B,H,Tq,1]``, ``a [B,H,Tq,dv]``."""
+    m = torch.full((*shape, 1), float("-inf"), dtype=torch.float32, device=device)
+    return m, torch.zeros(*shape, 1, dtype=torch.float32, device=device), \
+        torch.zeros(*shape, dv, dtype=torch.float32, device=device)
+
+
+def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float = 1.0,
+               causal: bool = False, key_offset: int = 0) -> tuple:
+    """``state (+) om_elem(scale * q @ k^T, v)``: fold one block of keys/values into
+    the running carrier (``om_step_qk``, om_lower.py:911-922; the reference takes
+    unscaled, unmasked scores — ``scale`` and the causal mask with its key offset
+    are the arguments its carrier terms spell around the product).  ``q [B,H,Tq,dk]``,
+    ``k [B,H,Tk,dk]``, ``v [B,H,Tk,dv]``; returns a new fp32 ``(m, l, a)``."""
+    require_cuda(q, k, v)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise B200Error("om_step_qk takes rank-4 q, k, v")
+    B, H, Tq, dk = q.shape
+    if k.shape[:2] != (B, H) or k.shape[3] != dk or v.shape[:3] != k.shape[:3] or not (q.dtype == k.dtype == v.dtype):
+        raise B200Error("om_step_qk: q [B,H,Tq,dk], k [B,H,Tk,dk], v [B,H,Tk,dv] of one dtype")
+    Tk, dv = k.shape[2], v.shape[3]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    m_out, l_out, a_out = (torch.empty(B, H, Tq, 1, dtype=torch.float32, device=q.device),
+                           torch.empty(B, H, Tq, 1, dtype=torch.float32, device=q.device),
+                           torch.empty(B, H, Tq, dv, dtype=torch.float32, device=q.device))
+    if state is not None:
+        m_in, l_in, a_in = (t.to(torch.float32).contiguous() for t in state)
+        require_cuda(m_in, l_in, a_in)
+        if m_in.shape != m_out.shape or l_in.shape != l_out.shape or a_in.shape != a_out.shape:
+            raise B200Error("om_step_qk: state shapes do not match q and v")
+        ptrs = (m_in.data_ptr(), l_in.data_ptr(), a_in.data_ptr())
+    else:
+        ptrs = (None, None, None)
+    rc = _lib.load().cb2_om_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), *ptrs, m_out.data_ptr(),
+                                 l_out.data_ptr(), a_out.data_ptr(), B, H, Tq, Tk, dk, dv, float(scale),
+                                 1 if causal else 0, int(key_offset), dtype_code(q.dtype), stream_ptr())
+    check(rc, "cb2_om_step")
+    return m_out, l_out, a_out
+
+
+def om_apply_state(state: tuple) -> torch.Tensor:
+    """The ``om_apply`` readout ``a / l`` (unclamped: a row that saw no key is NaN),
+    ``om_apply_state`` (om_lower.py:925-927)."""
+    return state[2] / state[1]
+
+
 # --------------------------------------------------------------------------- scan
 def diag_scan_fwd(a: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
                   h0: torch.Tensor | None = None, want_state: bool = False,

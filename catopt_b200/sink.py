@@ -52,7 +52,7 @@ from catopt_torch.torch_bridge import IRModule
 from . import ops
 from . import verify as b200_verify
 from ._lib import B200Error
-from .executors import _GraphMixin, causal_softmax_blocks, decayed_whole_sequence
+from .executors import _GraphMixin, causal_softmax_blocks, decayed_whole_sequence, softmax_blocks_state
 
 __all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "decayed_ragged_plan",
            "decayed_plan", "om_causal_plan", "linear_chain_plan", "scan_diag_plan",
@@ -622,6 +622,21 @@ class B200CausalSoftmaxModule(_EvalBase):
     @property
     def n_blocks(self) -> int:
         return 0 if self._plan is None else self._plan["n"]
+
+    @property
+    def is_streaming(self) -> bool:
+        return self._plan is not None
+
+    def forward_state(self, *xs: torch.Tensor) -> Any:
+        """The raw carrier ``(m, l, a)`` (fp32) after folding the blocks one kernel
+        call at a time — ``StreamingOMModule.forward_state`` (om_lower.py:1003-1040);
+        ``ops.om_apply_state`` reads it out, ``ops.om_step_qk`` extends it."""
+        plan = self._plan
+        if plan is None:
+            return self.eval_mod(*xs)
+        ev = self._ev(xs)
+        return softmax_blocks_state(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
+                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"])
 
     def _forward_impl(self, *xs: torch.Tensor) -> Any:
         plan = self._plan

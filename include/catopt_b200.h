@@ -225,6 +225,23 @@ int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int 
                int Tq, int Tk, int dk, int dv, float scale, int causal, int dtype,
                int* dev_status, void* stream);
 
+/* One streaming step of the same monoid: fold a block of keys/values into a
+ * running carrier (m, l, a) — `om_step_qk` / `StreamingOMModule.forward_state`
+ * (packages/catopt-carriers/src/catopt_carriers/om_lower.py:896-922, 996-1040):
+ *     state' = state (+) om_elem(scale * q k^T [masked], v)
+ * with `_om_compose`'s rule m' = max(m, m_blk), l' = l e^(m-m') + l_blk e^(m_blk-m'),
+ * a likewise (an all-hidden side contributes exactly 0).  The readout
+ * `om_apply_state` is a / l.
+ * State tensors are fp32 whatever `dtype` is: m, l: float[B,H,Tq]; a: float[B,H,Tq,dv].
+ * m_in = l_in = a_in = NULL starts from the identity (-inf, 0, 0); the outputs may
+ * alias the inputs.  causal != 0 hides key j of this call from query t when
+ * key_offset + j > t (key_offset = keys folded in before this call). */
+int cb2_om_step(const void* q, const void* k, const void* v,
+                const float* m_in, const float* l_in, const float* a_in,
+                float* m_out, float* l_out, float* a_out,
+                int B, int H, int Tq, int Tk, int dk, int dv, float scale,
+                int causal, int key_offset, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -598,6 +598,52 @@ def test_om_causal_bf16_growing_and_peaked_scores(dev):
         assert rel_to_max(out, want) <= BF16_TOL, (ramp, gain)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_om_streaming_steps_match_reference_monoid(dev, dtype):
+    """The decode / growing-cache schedule: fold key blocks one call at a time into
+    the carrier (m, l, a) and compare every intermediate state and the final
+    readout with the oracle's `om_elem` / `om_compose` (the reference's bindings);
+    uneven blocks, a causal mask with its key offset, a block that is entirely
+    hidden from some rows, and the identity start."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(17)
+    B, H, Tq, dk, dv = 2, 3, 70, 32, 24
+    sizes = (5, 64, 1, 90)
+    q = torch.randn(B, H, Tq, dk, generator=g).to(dtype)
+    ks = [torch.randn(B, H, n, dk, generator=g).to(dtype) for n in sizes]
+    vs = [torch.randn(B, H, n, dv, generator=g).to(dtype) for n in sizes]
+    tol = FP32_TOL if dtype == torch.float32 else 1e-5    # the state is fp32 for both element types
+    for causal in (False, True):
+        state = ops.om_empty_state((B, H, Tq), dv, dev) if causal else None     # both ways of starting
+        want, off = None, 0
+        for kb, vb in zip(ks, vs):
+            state = ops.om_step_qk(state, q.to(dev), kb.to(dev), vb.to(dev), scale=0.3, causal=causal, key_offset=off)
+            sc = (q.double() * 0.3) @ kb.double().transpose(-1, -2)
+            if causal:
+                t = torch.arange(Tq).view(Tq, 1)
+                j = torch.arange(kb.shape[2]).view(1, -1) + off
+                sc = sc.masked_fill(j > t, float("-inf"))
+            e = oracle.om_elem(sc, vb.double())
+            want = e if want is None else oracle.om_compose(want, e)
+            off += kb.shape[2]
+            m, l, a = (x.double().cpu() for x in state)
+            fin = torch.isfinite(want[0])
+            assert torch.equal(torch.isfinite(m), fin)                    # rows that saw no key yet stay at -inf
+            assert (m[fin] - want[0][fin]).abs().max() <= 1e-5
+            # l and a are relative to m: compare the m-independent readout and l e^m
+            assert rel_to_max((l * torch.exp(m))[fin], (want[1] * torch.exp(want[0]))[fin]) <= max(tol, 1e-5)
+        got = ops.om_apply_state(state)
+        ref = want[2] / want[1]
+        assert torch.equal(torch.isnan(got.cpu()), torch.isnan(ref))
+        ok = ~torch.isnan(ref)
+        assert (got.double().cpu()[ok] - ref[ok]).abs().max() / ref[ok].abs().max() <= max(tol, 2e-6)
+        # one-shot attention over the joined blocks agrees with the streamed readout
+        one = ops.om_causal_fwd(q.to(dev), torch.cat(ks, 2).to(dev), torch.cat(vs, 2).to(dev), 0.3, causal=causal)
+        lim = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+        assert rel_to_max(one.double().cpu()[ok], ref[ok]) <= lim
+
+
 def test_causal_softmax_blocks_entry_point(dev):
     """What the catopt-facing causal module runs after evaluating its operands:
     key/value blocks of uneven sizes joined on the key axis, rank-3 and rank-4
@@ -618,6 +664,21 @@ def test_causal_softmax_blocks_entry_point(dev):
         assert rel_to_max(out, want) <= tol
     assert causal_softmax_blocks(q.double().to(dev), [t.double().to(dev) for t in ks],
                                  [t.double().to(dev) for t in vs], 0.25) is None
+    # the streaming form of the same fold: state after the first block, then the rest
+    from catopt_b200 import ops
+    from catopt_b200.executors import softmax_blocks_state
+
+    lead, sizes, Tq = (2, 3), (5, 9, 130), 144
+    q = torch.randn(*lead, Tq, 32, generator=g)
+    ks = [torch.randn(*lead, n, 32, generator=g) for n in sizes]
+    vs = [torch.randn(*lead, n, 16, generator=g) for n in sizes]
+    st = softmax_blocks_state(q.to(dev), [ks[0].to(dev)], [vs[0].to(dev)], 0.25)
+    st = softmax_blocks_state(q.to(dev), [t.to(dev) for t in ks[1:]], [t.to(dev) for t in vs[1:]], 0.25,
+                              state=st, key_offset=sizes[0])
+    assert st[0].shape == (*lead, Tq, 1) and st[2].shape == (*lead, Tq, 16)
+    want = oracle.om_causal_chunked(q.double(), torch.cat(ks, -2).double(), torch.cat(vs, -2).double(),
+                                    list(sizes), 0.25)
+    assert rel_to_max(ops.om_apply_state(st), want) <= FP32_TOL
 
 
 def test_decayed_whole_sequence_entry_point(dev):
