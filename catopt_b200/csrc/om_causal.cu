@@ -47,7 +47,7 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
                  void* __restrict__ o, int Tq, int Tk, int dk, int dv, float scale, int causal,
                  int key_offset, const float* __restrict__ m_in, const float* __restrict__ l_in,
                  const float* __restrict__ a_in, float* __restrict__ m_out, float* __restrict__ l_out,
-                 float* __restrict__ a_out) {
+                 float* __restrict__ a_out, int split_len) {
   extern __shared__ __align__(16) float sm[];
   constexpr int kLd = kBlk + 4;
   float* Qt = sm;
@@ -82,16 +82,22 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
   }
   // causal: key j of this call is key (key_offset + j) of the whole sequence and is hidden
   // from query t when key_offset + j > t; blocks past the last query's horizon are skipped
-  const int k_end = causal ? max(0, min(Tk, q0 + kBlk - key_offset)) : Tk;
-  for (int k0 = 0; k0 < k_end; k0 += kBlk) {
+  // With split_len > 0 (decode: few queries, many keys) blockIdx.z owns keys
+  // [z*split_len, (z+1)*split_len) and writes a partial carrier to slice z of the outputs;
+  // the partials are folded afterwards (om_combine_kernel).
+  const int k_beg = split_len > 0 ? int(blockIdx.z) * split_len : 0;
+  const int k_lim = split_len > 0 ? min(Tk, k_beg + split_len) : Tk;      // keys of this CTA end here
+  const int k_end = causal ? max(k_beg, int(min((long long)k_lim, (long long)q0 + kBlk - key_offset))) : k_lim;
+  const size_t z_rows = split_len > 0 ? size_t(blockIdx.z) * gridDim.y * Tq : 0;
+  for (int k0 = k_beg; k0 < k_end; k0 += kBlk) {
     __syncthreads();  // previous block's Pt / Kt / Vs fully consumed (and Qt written)
     for (int i = tid; i < kBlk * dk; i += kOmThreads) {
       const int c = i / dk, e = i % dk;
-      Kt[e * kLd + c] = (k0 + c < Tk) ? ld_e<DTYPE>(k, kbase + size_t(k0 + c) * dk + e) : 0.f;
+      Kt[e * kLd + c] = (k0 + c < k_lim) ? ld_e<DTYPE>(k, kbase + size_t(k0 + c) * dk + e) : 0.f;
     }
     for (int i = tid; i < kBlk * dv; i += kOmThreads) {
       const int c = i / dv, f = i % dv;
-      Vs[c * dv + f] = (k0 + c < Tk) ? ld_e<DTYPE>(v, vbase + size_t(k0 + c) * dv + f) : 0.f;
+      Vs[c * dv + f] = (k0 + c < k_lim) ? ld_e<DTYPE>(v, vbase + size_t(k0 + c) * dv + f) : 0.f;
     }
     __syncthreads();
     // scores of this thread's 4x4 patch
@@ -113,7 +119,7 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c = k0 + tx * 4 + j;
-        if ((causal && c + key_offset > t) || c >= Tk) s[i][j] = -INFINITY;
+        if ((causal && c + key_offset > t) || c >= k_lim) s[i][j] = -INFINITY;
         mb = fmaxf(mb, s[i][j]);
       }
 #pragma unroll
@@ -162,7 +168,7 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
   for (int i = 0; i < 4; ++i) {
     const int t = q0 + ty * 4 + i;
     if (t >= Tq) continue;
-    const size_t srow = size_t(bh) * Tq + t;
+    const size_t srow = z_rows + size_t(bh) * Tq + t;
     if (m_out != nullptr && tx == 0) {
       m_out[srow] = m_run[i];
       l_out[srow] = l_run[i];
@@ -180,6 +186,60 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
         }
       }
   }
+}
+
+// Fold the caller's state (optional) and Z partial carriers, in key order, with the
+// monoid's compose rule; one warp per query row, lanes over the value columns.
+__global__ void om_combine_kernel(const float* __restrict__ m_in, const float* __restrict__ l_in,
+                                  const float* __restrict__ a_in, const float* __restrict__ pm,
+                                  const float* __restrict__ pl, const float* __restrict__ pa,
+                                  float* __restrict__ m_out, float* __restrict__ l_out,
+                                  float* __restrict__ a_out, size_t rows, int dv, int Z) {
+  const size_t row = (blockIdx.x * size_t(blockDim.x) + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (row >= rows) return;
+  float m = m_in ? m_in[row] : -INFINITY, l = m_in ? l_in[row] : 0.f;
+  float a[4];   // dv <= 128: four columns per lane
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int f = lane + 32 * u;
+    a[u] = (m_in && f < dv) ? a_in[row * dv + f] : 0.f;
+  }
+  for (int z = 0; z < Z; ++z) {
+    const size_t zr = size_t(z) * rows + row;
+    const float m2 = pm[zr], l2 = pl[zr];
+    const float mn = fmaxf(m, m2);
+    // a side that has seen no key (m = -inf) contributes exactly 0
+    const float w1 = (m == -INFINITY) ? 0.f : expf(m - mn);
+    const float w2 = (m2 == -INFINITY) ? 0.f : expf(m2 - mn);
+    l = l * w1 + l2 * w2;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int f = lane + 32 * u;
+      if (f < dv) a[u] = a[u] * w1 + pa[zr * dv + f] * w2;
+    }
+    m = mn;
+  }
+  if (lane == 0) {
+    m_out[row] = m;
+    l_out[row] = l;
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int f = lane + 32 * u;
+    if (f < dv) a_out[row * dv + f] = a[u];
+  }
+}
+
+// Key splits for a step: only when the query tiles alone leave most SMs idle.
+int om_step_splits(int B, int H, int Tq, int Tk) {
+  const long long ctas = (long long)((Tq + kBlk - 1) / kBlk) * B * H;
+  if (ctas >= 148 || Tk < 4 * kBlk) return 1;
+  long long z = (2 * 148 + ctas - 1) / ctas;
+  const long long most = (Tk + 2 * kBlk - 1) / (2 * kBlk);      // at least two key blocks per split
+  if (z > most) z = most;
+  if (z > 65535) z = 65535;
+  return z < 2 ? 1 : int(z);
 }
 
 }  // namespace
@@ -204,13 +264,13 @@ extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, 
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr, nullptr,
-                                                               nullptr, nullptr);
+                                                               nullptr, nullptr, 0);
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr, nullptr,
-                                                               nullptr, nullptr);
+                                                               nullptr, nullptr, 0);
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }
@@ -224,33 +284,62 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
   return cb2_om_fwd(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, 1, dtype, dev_status, stream);
 }
 
+extern "C" size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv) {
+  if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dv <= 0) return 0;
+  const int z = cb2::om_step_splits(B, H, Tq, Tk);
+  return z > 1 ? size_t(z) * B * H * Tq * (size_t(dv) + 2) * sizeof(float) : 0;
+}
+
 extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
                            const float* a_in, float* m_out, float* l_out, float* a_out, int B, int H, int Tq,
                            int Tk, int dk, int dv, float scale, int causal, int key_offset, int dtype,
-                           void* stream) {
+                           void* scratch, size_t scratch_bytes, void* stream) {
   using namespace cb2;
   if (!q || !k || !v || !m_out || !l_out || !a_out) return CB2_NULL_PTR;
   if ((m_in == nullptr) != (l_in == nullptr) || (m_in == nullptr) != (a_in == nullptr)) return CB2_NULL_PTR;
-  if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0 || key_offset < 0) return CB2_BAD_SHAPE;
+  if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0) return CB2_BAD_SHAPE;
   if (dk > kMaxD || dv > kMaxD || size_t(B) * H > 65535) return CB2_BAD_SHAPE;
   const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
-  const dim3 grid((Tq + kBlk - 1) / kBlk, B * H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // decode shapes: cut the keys over extra CTAs, then fold the partial carriers
+  int Z = om_step_splits(B, H, Tq, Tk);
+  const size_t rows = size_t(B) * H * Tq;
+  if (Z > 1 && (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) ||
+                scratch_bytes < size_t(Z) * rows * (size_t(dv) + 2) * sizeof(float)))
+    Z = 1;
+  const int split_len = Z > 1 ? ((Tk + Z - 1) / Z + kBlk - 1) / kBlk * kBlk : 0;
+  if (Z > 1) Z = (Tk + split_len - 1) / split_len;
+  float* pm = static_cast<float*>(scratch);
+  float* pl = Z > 1 ? pm + size_t(Z) * rows : nullptr;
+  float* pa = Z > 1 ? pl + size_t(Z) * rows : nullptr;
+  const dim3 grid((Tq + kBlk - 1) / kBlk, B * H, Z > 1 ? Z : 1);
+  const float* mi = Z > 1 ? nullptr : m_in;
+  const float* li = Z > 1 ? nullptr : l_in;
+  const float* ai = Z > 1 ? nullptr : a_in;
+  float* mo = Z > 1 ? pm : m_out;
+  float* lo = Z > 1 ? pl : l_out;
+  float* ao = Z > 1 ? pa : a_out;
   if (dtype == CB2_BF16) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
-                                                               key_offset, m_in, l_in, a_in, m_out, l_out, a_out);
+                                                               key_offset, mi, li, ai, mo, lo, ao, split_len);
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
-                                                              key_offset, m_in, l_in, a_in, m_out, l_out, a_out);
+                                                              key_offset, mi, li, ai, mo, lo, ao, split_len);
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }
   CB2_LAUNCH_CHECK();
+  if (Z > 1) {
+    const size_t threads = rows * 32;
+    om_combine_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(m_in, l_in, a_in, pm, pl, pa, m_out, l_out,
+                                                                      a_out, rows, dv, Z);
+    CB2_LAUNCH_CHECK();
+  }
   return CB2_OK;
 }

@@ -211,7 +211,11 @@ def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.T
     the running carrier (``om_step_qk``, om_lower.py:911-922; the reference takes
     unscaled, unmasked scores — ``scale`` and the causal mask with its key offset
     are the arguments its carrier terms spell around the product).  ``q [B,H,Tq,dk]``,
-    ``k [B,H,Tk,dk]``, ``v [B,H,Tk,dv]``; returns a new fp32 ``(m, l, a)``."""
+    ``k [B,H,Tk,dk]``, ``v [B,H,Tk,dv]``; returns a new fp32 ``(m, l, a)``.
+    With ``causal`` key j of this block is hidden from query row t when
+    ``key_offset + j > t``: ``key_offset`` = keys folded in before this block minus
+    the sequence position of query row 0 (negative in a decode step whose queries
+    are the newest positions)."""
     require_cuda(q, k, v)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise B200Error("om_step_qk takes rank-4 q, k, v")
@@ -231,9 +235,13 @@ def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.T
         ptrs = (m_in.data_ptr(), l_in.data_ptr(), a_in.data_ptr())
     else:
         ptrs = (None, None, None)
-    rc = _lib.load().cb2_om_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), *ptrs, m_out.data_ptr(),
-                                 l_out.data_ptr(), a_out.data_ptr(), B, H, Tq, Tk, dk, dv, float(scale),
-                                 1 if causal else 0, int(key_offset), dtype_code(q.dtype), stream_ptr())
+    lib = _lib.load()
+    need = lib.cb2_om_step_scratch_bytes(B, H, Tq, Tk, dv)
+    scratch = _scratch_buf("om_step", need, q.device)
+    rc = lib.cb2_om_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), *ptrs, m_out.data_ptr(),
+                         l_out.data_ptr(), a_out.data_ptr(), B, H, Tq, Tk, dk, dv, float(scale),
+                         1 if causal else 0, int(key_offset), dtype_code(q.dtype), _ptr(scratch), need,
+                         stream_ptr())
     check(rc, "cb2_om_step")
     return m_out, l_out, a_out
 

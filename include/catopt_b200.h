@@ -234,13 +234,20 @@ int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int 
  * `om_apply_state` is a / l.
  * State tensors are fp32 whatever `dtype` is: m, l: float[B,H,Tq]; a: float[B,H,Tq,dv].
  * m_in = l_in = a_in = NULL starts from the identity (-inf, 0, 0); the outputs may
- * alias the inputs.  causal != 0 hides key j of this call from query t when
- * key_offset + j > t (key_offset = keys folded in before this call). */
+ * alias the inputs.  causal != 0 hides key j of this call from query row t when
+ * key_offset + j > t, where key_offset = (keys folded in before this call) -
+ * (sequence position of query row 0); it is negative in a decode step whose
+ * queries are the newest positions.
+ * scratch (cb2_om_step_scratch_bytes bytes, may be NULL): with few queries and
+ * many keys (decode) the keys are cut over extra CTAs that each build a partial
+ * carrier there, folded in key order afterwards — the monoid is associative. */
+size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv);
 int cb2_om_step(const void* q, const void* k, const void* v,
                 const float* m_in, const float* l_in, const float* a_in,
                 float* m_out, float* l_out, float* a_out,
                 int B, int H, int Tq, int Tk, int dk, int dv, float scale,
-                int causal, int key_offset, int dtype, void* stream);
+                int causal, int key_offset, int dtype, void* scratch,
+                size_t scratch_bytes, void* stream);
 
 #ifdef __cplusplus
 }

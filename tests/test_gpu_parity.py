@@ -644,6 +644,39 @@ def test_om_streaming_steps_match_reference_monoid(dev, dtype):
         assert rel_to_max(one.double().cpu()[ok], ref[ok]) <= lim
 
 
+@pytest.mark.parametrize("Tq,Tk,causal", [(1, 2000, False), (3, 1500, True), (64, 4096, False)])
+def test_om_step_decode_shapes_split_the_keys(dev, Tq, Tk, causal):
+    """Few queries, many keys: the step cuts the keys over extra CTAs and folds their
+    partial carriers.  Same carrier as the oracle's one-block `om_elem` composed onto
+    an incoming state."""
+    from catopt_b200 import _lib, ops
+
+    B, H, dk, dv = 1, 4, 64, 48
+    assert _lib.load().cb2_om_step_scratch_bytes(B, H, Tq, Tk, dv) > 0
+    g = torch.Generator().manual_seed(Tq + Tk)
+    q = torch.randn(B, H, Tq, dk, generator=g)
+    k0, v0 = torch.randn(B, H, 37, dk, generator=g), torch.randn(B, H, 37, dv, generator=g)
+    k1, v1 = torch.randn(B, H, Tk, dk, generator=g), torch.randn(B, H, Tk, dv, generator=g)
+    off = 37
+    q_base = off + Tk - Tq if causal else 0          # decode: the queries are the newest positions
+    qpos = torch.arange(Tq).view(Tq, 1) + q_base
+
+    def scores(kb, base):
+        sc = (q.double() * 0.2) @ kb.double().transpose(-1, -2)
+        if causal:
+            j = torch.arange(kb.shape[2]).view(1, -1) + base
+            sc = sc.masked_fill(j > qpos, float("-inf"))
+        return sc
+
+    st = ops.om_step_qk(None, q.to(dev), k0.to(dev), v0.to(dev), 0.2, causal, 0 - q_base)
+    st = ops.om_step_qk(st, q.to(dev), k1.to(dev), v1.to(dev), 0.2, causal, off - q_base)
+    want = oracle.om_compose(oracle.om_elem(scores(k0, 0), v0.double()), oracle.om_elem(scores(k1, off), v1.double()))
+    got = ops.om_apply_state(st).double().cpu()
+    ref = want[2] / want[1]
+    assert rel_to_max(got, ref) <= FP32_TOL
+    assert (st[0].double().cpu() - want[0]).abs().max() <= 1e-5
+
+
 def test_causal_softmax_blocks_entry_point(dev):
     """What the catopt-facing causal module runs after evaluating its operands:
     key/value blocks of uneven sizes joined on the key axis, rank-3 and rank-4
