@@ -188,6 +188,182 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
   }
 }
 
+// Decode shapes (at most kDecRows query rows, many keys): the step is a stream over
+// K and V, so it is laid out for memory bandwidth instead of for tiles.  A warp
+// takes 32 keys at a time.  Scores: lane = key, the lane walks its key's row in
+// 16-byte pieces against the query rows kept in shared memory (no cross-lane
+// traffic, ~6 instructions per key).  Softmax: one warp max and one warp sum per
+// query row and batch.  Values: lane = four value columns, the 32 probabilities are
+// broadcast one by one with a shuffle while the value rows stream in coalesced.
+// The eight warps of a CTA fold their carriers in shared memory and write one
+// partial carrier per key split.
+constexpr int kDecRows = 8;
+constexpr int kDecWarps = 8;
+
+template <int DTYPE>
+struct DecLd;
+template <>
+struct DecLd<CB2_BF16> {
+  static constexpr int kPiece = 8;    // elements per 16-byte piece
+  __device__ static void piece(const void* p, size_t i, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + i);
+    x[0] = bf16lo_to_f32(u.x); x[1] = bf16hi_to_f32(u.x); x[2] = bf16lo_to_f32(u.y); x[3] = bf16hi_to_f32(u.y);
+    x[4] = bf16lo_to_f32(u.z); x[5] = bf16hi_to_f32(u.z); x[6] = bf16lo_to_f32(u.w); x[7] = bf16hi_to_f32(u.w);
+  }
+  __device__ static void four(const void* p, size_t i, float (&x)[4]) {
+    const uint2 u = __ldcs(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i));
+    x[0] = bf16lo_to_f32(u.x); x[1] = bf16hi_to_f32(u.x); x[2] = bf16lo_to_f32(u.y); x[3] = bf16hi_to_f32(u.y);
+  }
+  __device__ static float one(const void* p, size_t i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  }
+};
+template <>
+struct DecLd<CB2_F32> {
+  static constexpr int kPiece = 4;
+  __device__ static void piece(const void* p, size_t i, float (&x)[4]) {
+    const float4 u = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+    x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+  }
+  __device__ static void four(const void* p, size_t i, float (&x)[4]) {
+    const float4 u = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+    x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+  }
+  __device__ static float one(const void* p, size_t i) { return static_cast<const float*>(p)[i]; }
+};
+
+// dk a multiple of the 16-byte piece (8 bf16 / 4 fp32), dv a multiple of 4, both <= 128;
+// Tq <= ROWS (1, 2, 4 or 8).
+template <int DTYPE, int ROWS>
+__global__ void __launch_bounds__(kDecWarps * 32)
+om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v, int Tq,
+                 int Tk, int dk, int dv, float scale, int causal, int key_offset, int split_len,
+                 float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pa) {
+  using L = DecLd<DTYPE>;
+  constexpr int P = L::kPiece;
+  __shared__ __align__(16) float s_q[ROWS][128];
+  __shared__ float s_m[kDecWarps][ROWS], s_l[kDecWarps][ROWS];
+  __shared__ float s_a[kDecWarps][ROWS][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, z = blockIdx.x;
+  const int c0 = lane * 4;
+  const bool vcol = c0 < dv;
+  const int k_beg = z * split_len, k_lim = min(Tk, k_beg + split_len);
+  const size_t kbase = size_t(bh) * Tk * dk, vbase = size_t(bh) * Tk * dv;
+  for (int x = threadIdx.x; x < ROWS * 128; x += blockDim.x) {
+    const int r = x / 128, c = x % 128;
+    s_q[r][c] = (r < Tq && c < dk) ? L::one(q, (size_t(bh) * Tq + r) * dk + c) * scale : 0.f;
+  }
+  __syncthreads();
+  float m[ROWS], l[ROWS], a[ROWS][4];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[r][e] = 0.f;
+  }
+  const int npiece = dk / P;
+  for (int j0 = k_beg + warp * 32; j0 < k_lim; j0 += kDecWarps * 32) {
+    // ---- scores of this lane's key against every query row
+    const int j = j0 + lane;
+    const bool live = j < k_lim;
+    const size_t krow = kbase + size_t(live ? j : k_lim - 1) * dk;
+    float sc[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) sc[r] = 0.f;
+#pragma unroll 4
+    for (int pc = 0; pc < npiece; ++pc) {
+      float x[P];
+      L::piece(k, krow + size_t(pc) * P, x);
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+        for (int e4 = 0; e4 < P; e4 += 4) {
+          const float4 qq = *reinterpret_cast<const float4*>(&s_q[r][pc * P + e4]);   // broadcast read
+          sc[r] = fmaf(qq.x, x[e4], fmaf(qq.y, x[e4 + 1], fmaf(qq.z, x[e4 + 2], fmaf(qq.w, x[e4 + 3], sc[r]))));
+        }
+      }
+    }
+    // ---- softmax bookkeeping per row: p of this lane's key, running (m, l), rescaled a
+    float p[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const bool hidden = !live || r >= Tq || (causal && j + key_offset > r);
+      float sv = hidden ? -INFINITY : sc[r];
+      float mb = sv;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, off));
+      const float mn = fmaxf(m[r], mb);
+      const float alpha = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn);
+      p[r] = hidden ? 0.f : expf(sv - mn);
+      float ps = p[r];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+      l[r] = l[r] * alpha + ps;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[r][e] *= alpha;
+      m[r] = mn;
+    }
+    // ---- values: a[r][lane's 4 columns] += sum_jj p_jj[r] * v_jj[columns]
+    const int nlive = min(32, k_lim - j0);
+#pragma unroll 1
+    for (int jj0 = 0; jj0 < nlive; jj0 += 8) {
+      float vx[8][4];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int jr = min(j0 + jj0 + u, k_lim - 1);
+        if (vcol) L::four(v, vbase + size_t(jr) * dv + c0, vx[u]);
+        else vx[u][0] = vx[u][1] = vx[u][2] = vx[u][3] = 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          const float pj = __shfl_sync(0xffffffffu, p[r], jj0 + u);   // 0 for keys past the end
+#pragma unroll
+          for (int e = 0; e < 4; ++e) a[r][e] = fmaf(pj, vx[u][e], a[r][e]);
+        }
+      }
+    }
+  }
+  // fold the eight warps' carriers (in warp order, so the result is deterministic)
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    if (lane == 0) {
+      s_m[warp][r] = m[r];
+      s_l[warp][r] = l[r];
+    }
+    if (vcol) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_a[warp][r][c0 + e] = a[r][e];
+    }
+  }
+  __syncthreads();
+  const size_t rows = size_t(gridDim.y) * Tq;
+  for (int idx = threadIdx.x; idx < Tq * 32; idx += blockDim.x) {
+    const int r = idx / 32, ln = idx % 32;
+    float mm = -INFINITY;
+    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, s_m[w][r]);
+    float ll = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float wgt = (s_m[w][r] == -INFINITY) ? 0.f : expf(s_m[w][r] - mm);
+      ll += s_l[w][r] * wgt;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (ln * 4 + e < dv) acc[e] += s_a[w][r][ln * 4 + e] * wgt;
+    }
+    const size_t row = size_t(z) * rows + size_t(bh) * Tq + r;
+    if (ln == 0) {
+      pm[row] = mm;
+      pl[row] = ll;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (ln * 4 + e < dv) pa[row * dv + ln * 4 + e] = acc[e];
+  }
+}
+
 // Fold the caller's state (optional) and Z partial carriers, in key order, with the
 // monoid's compose rule; one warp per query row, lanes over the value columns.
 __global__ void om_combine_kernel(const float* __restrict__ m_in, const float* __restrict__ l_in,
@@ -229,6 +405,18 @@ __global__ void om_combine_kernel(const float* __restrict__ m_in, const float* _
     const int f = lane + 32 * u;
     if (f < dv) a_out[row * dv + f] = a[u];
   }
+}
+
+// Key splits of the decode kernel: about four CTAs per SM, at least 256 keys each.
+int om_decode_splits(int B, int H, int Tk) {
+  long long z = (4 * 148 + (long long)B * H - 1) / ((long long)B * H);
+  const long long most = (Tk + 255) / 256;
+  if (z > most) z = most;
+  if (z > 65535) z = 65535;
+  return z < 1 ? 1 : int(z);
+}
+bool om_decode_shape(int Tq, int Tk, int dk, int dv, int dtype) {
+  return Tq <= kDecRows && Tk >= 256 && dk % (dtype == CB2_BF16 ? 8 : 4) == 0 && dv % 4 == 0;
 }
 
 // Key splits for a step: only when the query tiles alone leave most SMs idle.
@@ -286,8 +474,8 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
 
 extern "C" size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv) {
   if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dv <= 0) return 0;
-  const int z = cb2::om_step_splits(B, H, Tq, Tk);
-  return z > 1 ? size_t(z) * B * H * Tq * (size_t(dv) + 2) * sizeof(float) : 0;
+  const int z = Tq <= cb2::kDecRows && Tk >= 256 ? cb2::om_decode_splits(B, H, Tk) : cb2::om_step_splits(B, H, Tq, Tk);
+  return (z > 1 || (Tq <= cb2::kDecRows && Tk >= 256)) ? size_t(z) * B * H * Tq * (size_t(dv) + 2) * sizeof(float) : 0;
 }
 
 extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
@@ -301,9 +489,37 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
   if (dk > kMaxD || dv > kMaxD || size_t(B) * H > 65535) return CB2_BAD_SHAPE;
   const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // decode shapes: cut the keys over extra CTAs, then fold the partial carriers
-  int Z = om_step_splits(B, H, Tq, Tk);
   const size_t rows = size_t(B) * H * Tq;
+  // a handful of query rows against many keys: the streaming (memory-bound) kernel
+  if (om_decode_shape(Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && scratch &&
+      !(reinterpret_cast<uintptr_t>(scratch) & 15u)) {
+    int Zd = om_decode_splits(B, H, Tk);
+    if (scratch_bytes >= size_t(Zd) * rows * (size_t(dv) + 2) * sizeof(float)) {
+      const int len = (Tk + Zd - 1) / Zd;
+      Zd = (Tk + len - 1) / len;
+      float* dm = static_cast<float*>(scratch);
+      float* dl = dm + size_t(Zd) * rows;
+      float* da = dl + size_t(Zd) * rows;
+      const dim3 dgrid(Zd, B * H);
+      if (dtype != CB2_BF16 && dtype != CB2_F32) return CB2_UNSUPPORTED_DTYPE;
+#define CB2_DECODE(DT, R)                                                                                  \
+  om_decode_kernel<DT, R><<<dgrid, kDecWarps * 32, 0, st>>>(q, k, v, Tq, Tk, dk, dv, scale, causal ? 1 : 0, \
+                                                            key_offset, len, dm, dl, da)
+      const bool bf = dtype == CB2_BF16;
+      if (Tq == 1) { if (bf) CB2_DECODE(CB2_BF16, 1); else CB2_DECODE(CB2_F32, 1); }
+      else if (Tq == 2) { if (bf) CB2_DECODE(CB2_BF16, 2); else CB2_DECODE(CB2_F32, 2); }
+      else if (Tq <= 4) { if (bf) CB2_DECODE(CB2_BF16, 4); else CB2_DECODE(CB2_F32, 4); }
+      else { if (bf) CB2_DECODE(CB2_BF16, 8); else CB2_DECODE(CB2_F32, 8); }
+#undef CB2_DECODE
+      CB2_LAUNCH_CHECK();
+      om_combine_kernel<<<unsigned((rows * 32 + 255) / 256), 256, 0, st>>>(m_in, l_in, a_in, dm, dl, da, m_out,
+                                                                          l_out, a_out, rows, dv, Zd);
+      CB2_LAUNCH_CHECK();
+      return CB2_OK;
+    }
+  }
+  // few query tiles: cut the keys over extra CTAs, then fold the partial carriers
+  int Z = om_step_splits(B, H, Tq, Tk);
   if (Z > 1 && (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) ||
                 scratch_bytes < size_t(Z) * rows * (size_t(dv) + 2) * sizeof(float)))
     Z = 1;
