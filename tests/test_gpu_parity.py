@@ -562,7 +562,9 @@ def test_om_causal_bf16_tensor_core_path(dev, B, H, Tq, Tk, dk, dv):
 @pytest.mark.parametrize("B,H,Tq,Tk,dk,dv,dtype", [(1, 2, 300, 300, 64, 64, torch.bfloat16),
                                                    (2, 3, 128, 1000, 128, 128, torch.bfloat16),
                                                    (1, 1, 70, 33, 16, 24, torch.float32),
-                                                   (1, 2, 1, 257, 32, 32, torch.bfloat16)])
+                                                   (1, 2, 1, 257, 32, 32, torch.bfloat16),
+                                                   (2, 4, 3, 5000, 64, 64, torch.bfloat16),
+                                                   (1, 2, 8, 1500, 32, 48, torch.float32)])
 def test_om_unmasked_softmax_attention(dev, B, H, Tq, Tk, dk, dv, dtype):
     """cb2_om_fwd with causal = 0 (the unmasked om carrier): plain softmax attention
     on both kernels, ragged lengths, Tq != Tk, against fp64."""
