@@ -337,6 +337,17 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
         out[f"om_causal_bf16_B{Bo}_H{Ho}_T{To}_d128"] = e
         del qo, ko, vo, oo
 
+    # streaming step of the same monoid in the decode regime: one query row per head against 65536
+    # cached keys (bf16, d=128): K and V are read once (1.07 GB)
+    qd = _randn_bf16((32, 128), gen).view(1, 32, 1, 128)
+    kd, vd = (_randn_bf16((32, 65536 * 128), gen).view(1, 32, 65536, 128) for _ in range(2))
+    ms = time_steps(lambda: ops.om_step_qk(None, qd, kd, vd, 0.09, True, -65535), K, W, world)
+    out["om_step_decode_bf16_H32_Tk65536_d128"] = entry(
+        ms, 32, 2 * 32 * 65536 * 128 * 2, 2,
+        "one decode step (Tq = 1) folding 65536 keys into the carrier (m, l, a); K + V read once (1.07 GB > L2)",
+        flops=4 * 32 * 65536 * 128)
+    del qd, kd, vd
+
     # config 5: verify 13 checks x 256 probes x [4,512,1024] bf16; probes sharded over ranks
     p0, p1 = shard_range(256, rank, world)
     probes = p1 - p0

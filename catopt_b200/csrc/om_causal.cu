@@ -272,7 +272,7 @@ om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
     float sc[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) sc[r] = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int pc = 0; pc < npiece; ++pc) {
       float x[P];
       L::piece(k, krow + size_t(pc) * P, x);
@@ -407,9 +407,10 @@ __global__ void om_combine_kernel(const float* __restrict__ m_in, const float* _
   }
 }
 
-// Key splits of the decode kernel: about four CTAs per SM, at least 256 keys each.
+// Key splits of the decode kernel: as many as fit in ONE wave of four CTAs per SM
+// (rounding up would leave a second, nearly empty wave), at least 256 keys each.
 int om_decode_splits(int B, int H, int Tk) {
-  long long z = (4 * 148 + (long long)B * H - 1) / ((long long)B * H);
+  long long z = (4 * 148) / ((long long)B * H);
   const long long most = (Tk + 255) / 256;
   if (z > most) z = most;
   if (z > 65535) z = 65535;
