@@ -133,7 +133,7 @@ compose_apply_kernel(const float* __restrict__ part_a, const float* __restrict__
 int pick_segments(long long n, long long S, int elems_per_thread) {
   long long ctas = (S / elems_per_thread + kComposeThreads - 1) / kComposeThreads;
   if (ctas < 1) ctas = 1;
-  long long want = (4 * 148 + ctas - 1) / ctas;          // about four CTAs per SM in total
+  long long want = (4 * 148) / ctas;                     // at most one wave of four CTAs per SM
   const long long most = n / 64 > 0 ? n / 64 : 1;        // segments of at least 64 leaves
   if (want > most) want = most;
   if (want < 1) want = 1;
