@@ -79,7 +79,7 @@ SIGNATURES: dict[str, tuple] = {
     "cb2_om_step": (
         C.c_int,
         [C.c_void_p] * 9 + [C.c_int] * 6 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
-                                            C.c_void_p],
+                                            C.c_void_p, C.c_void_p],
     ),
     "cb2_diag_scan_fwd": (
         C.c_int,

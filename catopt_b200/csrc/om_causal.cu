@@ -19,7 +19,9 @@ namespace cb2 {
 // tensor-core kernel for bf16 tensors (om_causal_tc.cu)
 bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dtype);
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
-                     int dk, int dv, float scale, int causal, int* dev_status, cudaStream_t st);
+                     int dk, int dv, float scale, int causal, int key_offset, const float* m_in,
+                     const float* l_in, const float* a_in, float* m_out, float* l_out, float* a_out,
+                     int* dev_status, cudaStream_t st);
 
 namespace {
 
@@ -447,7 +449,8 @@ extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) && aligned16(k) &&
       aligned16(v) && aligned16(o))
-    return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, dev_status, st);
+    return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr,
+                            nullptr, nullptr, nullptr, dev_status, st);
   if (dtype == CB2_BF16) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
@@ -482,7 +485,7 @@ extern "C" size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv
 extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
                            const float* a_in, float* m_out, float* l_out, float* a_out, int B, int H, int Tq,
                            int Tk, int dk, int dv, float scale, int causal, int key_offset, int dtype,
-                           void* scratch, size_t scratch_bytes, void* stream) {
+                           void* scratch, size_t scratch_bytes, int* dev_status, void* stream) {
   using namespace cb2;
   if (!q || !k || !v || !m_out || !l_out || !a_out) return CB2_NULL_PTR;
   if ((m_in == nullptr) != (l_in == nullptr) || (m_in == nullptr) != (a_in == nullptr)) return CB2_NULL_PTR;
@@ -519,6 +522,11 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
       return CB2_OK;
     }
   }
+  // bf16 with whole query tiles' worth of rows: the tensor-core kernel carries the state
+  if (Tq > kDecRows && om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) &&
+      aligned16(k) && aligned16(v) && aligned16(a_out) && (!a_in || aligned16(a_in)))
+    return om_causal_tc_run(q, k, v, nullptr, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, key_offset, m_in, l_in,
+                            a_in, m_out, l_out, a_out, dev_status, st);
   // few query tiles: cut the keys over extra CTAs, then fold the partial carriers
   int Z = om_step_splits(B, H, Tq, Tk);
   if (Z > 1 && (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) ||

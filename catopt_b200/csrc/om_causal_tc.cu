@@ -50,7 +50,9 @@ __device__ __forceinline__ float ex2(float x) {
 __global__ void __launch_bounds__(kThreads, 2)
 om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                    int Tq, int Tk, int dk, int dv, int n_bh, int causal, float scale_log2e, int* dev_status) {
+                    int Tq, int Tk, int dk, int dv, int n_bh, int causal, float scale_log2e, int key_offset,
+                    const float* __restrict__ m_in, const float* __restrict__ l_in, const float* __restrict__ a_in,
+                    float* __restrict__ m_out, float* __restrict__ l_out, float* __restrict__ a_out, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -71,8 +73,13 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int bh = blockIdx.x % n_bh;
   const int qb = int(gridDim.x / n_bh) - 1 - int(blockIdx.x / n_bh);
   const int q0 = qb * kQ;
-  // key blocks with at least one visible key (all of them without the causal mask)
-  const int nkb = causal ? min((Tk + kQ - 1) / kQ, qb + 1) : (Tk + kQ - 1) / kQ;
+  // key blocks with at least one visible key (all of them without the causal mask): key j of
+  // this call is hidden from query row t when key_offset + j > t.  Possibly none (a streaming
+  // step whose keys all lie in the future of this query block).
+  const int nkb_all = (Tk + kQ - 1) / kQ;
+  const int last_vis = q0 + kQ - 1 - key_offset;           // last key the block's last row may see
+  const int nkb = causal ? (last_vis < 0 ? 0 : min(nkb_all, last_vis / kQ + 1)) : nkb_all;
+  const bool has_state = m_in != nullptr;                  // continue from the caller's carrier
 
   if (tid == 0) {
     for (int s = 0; s < kSlots; ++s) {
@@ -139,7 +146,7 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         return true;
       };
       bool ok = mbar_wait_abortable(q_full, 0, s_abort);
-      ok = ok && issue_scores(0);
+      ok = ok && (nkb == 0 || issue_scores(0));
       for (int j = 0; ok && j < nkb; ++j) {
         const int t = 2 * j + 1, slot = t % kSlots;
         if (!mbar_wait_abortable(p_ready, j & 1, s_abort)) break;
@@ -149,7 +156,7 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma::mma_bf16_ts(tmem + kColO, tmem + kColS + ks * 8, umma::desc_mnmajor(v_addr, ks), idesc_kn,
-                            (j > 0) || (ks > 0));
+                            (j > 0) || has_state || (ks > 0));
         umma::mma_commit(o_done);
         umma::mma_commit(&empty[slot]);
         // the tensor pipe runs in issue order, so the next scores may overwrite P right away
@@ -167,7 +174,13 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // than kLazy, so P stays below 2^kLazy and the O rescale becomes rare.  Any
     // common reference gives the same o = O / l.
     constexpr float kLazy = 8.f;
-    float m_ref = -INFINITY, l_run = 0.f;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const size_t srow = size_t(bh) * Tq + min(tq, Tq - 1);          // this row in the state tensors
+    const bool row_in = tq < Tq;
+    // a carrier handed in by the caller is (m, l, a) with m in natural-log units
+    float m_ref = (has_state && row_in) ? m_in[srow] * kLog2e : -INFINITY;
+    float l_run = (has_state && row_in) ? l_in[srow] : 0.f;
+    float m_true = m_ref;                                          // the running maximum itself
     uint32_t sv[4][32];                            // this row's 128 scores, then its O row
     const int ncb = (dv + 31) >> 5;                // 32-column groups of O that hold output
     for (int j = 0; j < nkb; ++j) {
@@ -176,14 +189,14 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       const int k0 = j * kQ;
-      const bool partial = (causal && k0 + kQ - 1 > q0) || (k0 + kQ > Tk);   // uniform over the CTA
+      const bool partial = (causal && k0 + kQ - 1 + key_offset > q0) || (k0 + kQ > Tk);   // uniform over the CTA
 #pragma unroll
       for (int cb = 0; cb < 4; ++cb) umma::tmem_ld32(lane_base + scol + cb * 32, sv[cb]);
       umma::tmem_wait_ld();
       // hidden keys (beyond the diagonal or beyond Tk) score -inf: they never win the
       // maximum and exponentiate to exactly 0 (scale > 0 on this path)
       if (partial) {
-        const int lim = (causal ? min(tq, Tk - 1) : Tk - 1) - k0;   // last visible column of the block
+        const int lim = (causal ? min(tq - key_offset, Tk - 1) : Tk - 1) - k0;   // last visible column of the block
 #pragma unroll
         for (int cb = 0; cb < 4; ++cb)
 #pragma unroll
@@ -196,6 +209,7 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sv[cb][c]));
       const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+      m_true = fmaxf(m_true, m_blk);
       float alpha = 1.f;
       if (m_blk > m_ref + kLazy || m_ref == -INFINITY) {   // (the second test also covers m_blk = -inf)
         const float m_new = fmaxf(m_ref, m_blk);
@@ -220,6 +234,22 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tmem_wait_st();
       // O <- O * alpha, once the previous block's P.V has landed; skipped by a warp
       // whose 32 rows all kept their reference point
+      if (j == 0 && has_state) {
+        // O starts from the caller's a (scaled to this block's reference point); columns past dv
+        // that the MMA still covers are zero
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+          if (cb < ncb) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int f = cb * 32 + c;
+              sv[cb][c] = __float_as_uint((row_in && f < dv) ? a_in[srow * dv + f] * alpha : 0.f);
+            }
+            umma::tmem_st32(lane_base + kColO + cb * 32, sv[cb]);
+          }
+        }
+        umma::tmem_wait_st();
+      }
       if (j > 0) {
         ok = mbar_wait_abortable(o_done, (j - 1) & 1, s_abort);
         if (!__all_sync(0xffffffffu, ok)) break;
@@ -243,36 +273,69 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::fence_before_sync();
       mbar_arrive(p_ready);
     }
-    // read-out o = O / l  (0/0 = NaN for a row that saw no key, as the reference)
-    bool ok = mbar_wait_abortable(o_done, (nkb - 1) & 1, s_abort);
+    // read-out: o = O / l  (0/0 = NaN for a row that saw no key, as the reference), or the raw
+    // carrier when the caller continues the fold
+    bool ok = nkb == 0 || mbar_wait_abortable(o_done, (nkb - 1) & 1, s_abort);
     if (__all_sync(0xffffffffu, ok)) {
       umma::fence_after_sync();
-      const float inv_l = 1.f / l_run;
+      if (nkb > 0) {
 #pragma unroll
-      for (int cb = 0; cb < 4; ++cb)
-        if (cb < ncb) umma::tmem_ld32(lane_base + kColO + cb * 32, sv[cb]);
-      umma::tmem_wait_ld();
+        for (int cb = 0; cb < 4; ++cb)
+          if (cb < ncb) umma::tmem_ld32(lane_base + kColO + cb * 32, sv[cb]);
+        umma::tmem_wait_ld();
+      } else {
+        // no visible key block: the accumulator is the incoming a (or zero)
 #pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        if (cb >= ncb) continue;
-        uint32_t w[16];
+        for (int cb = 0; cb < 4; ++cb)
 #pragma unroll
-        for (int c = 0; c < 32; c += 2)
-          w[c >> 1] = pack_bf16x2(__uint_as_float(sv[cb][c]) * inv_l, __uint_as_float(sv[cb][c + 1]) * inv_l);
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8)
-          *reinterpret_cast<uint4*>(o_tile + umma::tile_chunk_offset(r, cb * 32 + c8 * 8)) =
-              make_uint4(w[4 * c8], w[4 * c8 + 1], w[4 * c8 + 2], w[4 * c8 + 3]);
+          for (int c = 0; c < 32; ++c) {
+            const int f = cb * 32 + c;
+            sv[cb][c] = __float_as_uint((has_state && row_in && f < dv) ? a_in[srow * dv + f] : 0.f);
+          }
       }
-      fence_proxy_async_smem();
-      // the four softmax warps meet (bounded wait), then one thread stores the tile
-      mbar_arrive(wg_sync);
-      ok = mbar_wait_abortable(wg_sync, 0, s_abort);
-      if (ok && tid == 64) {
-        umma::tma_store_3d(&map_o, 0, q0, bh, o_tile);
-        if (dv > 64) umma::tma_store_3d(&map_o, 64, q0, bh, o_tile + umma::kSubTileBytes);
-        bulk_commit();
-        bulk_wait_all<0>();
+      if (m_out != nullptr) {
+        // (m, l, a) relative to the true running maximum, m back in natural-log units
+        if (row_in) {
+          const float fix = (m_true == -INFINITY) ? 1.f : ex2(m_ref - m_true);
+          m_out[srow] = m_true / kLog2e;
+          l_out[srow] = l_run * fix;
+          float4* dst = reinterpret_cast<float4*>(a_out + srow * dv);
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb) {
+            if (cb >= ncb) continue;
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              const int f = cb * 32 + c;
+              if (f < dv)      // dv is a multiple of 8
+                dst[f >> 2] = make_float4(__uint_as_float(sv[cb][c]) * fix, __uint_as_float(sv[cb][c + 1]) * fix,
+                                          __uint_as_float(sv[cb][c + 2]) * fix, __uint_as_float(sv[cb][c + 3]) * fix);
+            }
+          }
+        }
+      } else {
+        const float inv_l = 1.f / l_run;
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+          if (cb >= ncb) continue;
+          uint32_t w[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2)
+            w[c >> 1] = pack_bf16x2(__uint_as_float(sv[cb][c]) * inv_l, __uint_as_float(sv[cb][c + 1]) * inv_l);
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8)
+            *reinterpret_cast<uint4*>(o_tile + umma::tile_chunk_offset(r, cb * 32 + c8 * 8)) =
+                make_uint4(w[4 * c8], w[4 * c8 + 1], w[4 * c8 + 2], w[4 * c8 + 3]);
+        }
+        fence_proxy_async_smem();
+        // the four softmax warps meet (bounded wait), then one thread stores the tile
+        mbar_arrive(wg_sync);
+        ok = mbar_wait_abortable(wg_sync, 0, s_abort);
+        if (ok && tid == 64) {
+          umma::tma_store_3d(&map_o, 0, q0, bh, o_tile);
+          if (dv > 64) umma::tma_store_3d(&map_o, 64, q0, bh, o_tile + umma::kSubTileBytes);
+          bulk_commit();
+          bulk_wait_all<0>();
+        }
       }
     }
   }
@@ -296,21 +359,28 @@ bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dt
          Tq >= 1 && Tk >= 1 && int64_t(B) * H * ((Tq + 127) / 128) < (int64_t(1) << 31);
 }
 
+// o == nullptr with m_out/l_out/a_out set: streaming step (raw fp32 carrier out, optional carrier in).
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
-                     int dk, int dv, float scale, int causal, int* dev_status, cudaStream_t st) {
+                     int dk, int dv, float scale, int causal, int key_offset, const float* m_in,
+                     const float* l_in, const float* a_in, float* m_out, float* l_out, float* a_out,
+                     int* dev_status, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mo;
   const uint64_t bh = uint64_t(B) * H;
   int rc = umma::make_map_3d(&mq, q, true, dk, Tq, bh, 64, 128, true);
   if (rc == CB2_OK) rc = umma::make_map_3d(&mk, k, true, dk, Tk, bh, 64, 128, true);
   if (rc == CB2_OK) rc = umma::make_map_3d(&mv, v, true, dv, Tk, bh, 64, 128, true);
-  if (rc == CB2_OK) rc = umma::make_map_3d(&mo, o, true, dv, Tq, bh, 64, 128, true);
+  if (rc == CB2_OK) {
+    if (o) rc = umma::make_map_3d(&mo, o, true, dv, Tq, bh, 64, 128, true);
+    else mo = mq;                                   // unused in the streaming form
+  }
   if (rc != CB2_OK) return rc;
   if (cudaFuncSetAttribute(om_causal_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
   const unsigned grid = unsigned(((Tq + kQ - 1) / kQ) * bh);
   om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh), causal,
-                                                         scale * 1.4426950408889634f, dev_status);
+                                                         scale * 1.4426950408889634f, key_offset, m_in, l_in, a_in,
+                                                         m_out, l_out, a_out, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

@@ -249,7 +249,7 @@ def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.T
     rc = lib.cb2_om_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), *ptrs, m_out.data_ptr(),
                          l_out.data_ptr(), a_out.data_ptr(), B, H, Tq, Tk, dk, dv, float(scale),
                          1 if causal else 0, int(key_offset), dtype_code(q.dtype), _ptr(scratch), need,
-                         stream_ptr())
+                         device_status(q.device).data_ptr(), stream_ptr())
     check(rc, "cb2_om_step")
     return m_out, l_out, a_out
 

@@ -247,7 +247,7 @@ int cb2_om_step(const void* q, const void* k, const void* v,
                 float* m_out, float* l_out, float* a_out,
                 int B, int H, int Tq, int Tk, int dk, int dv, float scale,
                 int causal, int key_offset, int dtype, void* scratch,
-                size_t scratch_bytes, void* stream);
+                size_t scratch_bytes, int* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -615,7 +615,9 @@ def test_om_streaming_steps_match_reference_monoid(dev, dtype):
     q = torch.randn(B, H, Tq, dk, generator=g).to(dtype)
     ks = [torch.randn(B, H, n, dk, generator=g).to(dtype) for n in sizes]
     vs = [torch.randn(B, H, n, dv, generator=g).to(dtype) for n in sizes]
-    tol = FP32_TOL if dtype == torch.float32 else 1e-5    # the state is fp32 for both element types
+    # fp32 tensors: FMA kernel, fp32 throughout.  bf16: the tensor-core kernel carries the state
+    # (P rounded to bf16 for the P.V product, fp32 accumulation and fp32 state)
+    tol = FP32_TOL if dtype == torch.float32 else BF16_TOL
     for causal in (False, True):
         state = ops.om_empty_state((B, H, Tq), dv, dev) if causal else None     # both ways of starting
         want, off = None, 0
@@ -632,7 +634,7 @@ def test_om_streaming_steps_match_reference_monoid(dev, dtype):
             m, l, a = (x.double().cpu() for x in state)
             fin = torch.isfinite(want[0])
             assert torch.equal(torch.isfinite(m), fin)                    # rows that saw no key yet stay at -inf
-            assert (m[fin] - want[0][fin]).abs().max() <= 1e-5
+            assert (m[fin] - want[0][fin]).abs().max() <= (1e-5 if dtype == torch.float32 else 1e-4)
             # l and a are relative to m: compare the m-independent readout and l e^m
             assert rel_to_max((l * torch.exp(m))[fin], (want[1] * torch.exp(want[0]))[fin]) <= max(tol, 1e-5)
         got = ops.om_apply_state(state)
@@ -677,6 +679,33 @@ def test_om_step_decode_shapes_split_the_keys(dev, Tq, Tk, causal):
     ref = want[2] / want[1]
     assert rel_to_max(got, ref) <= FP32_TOL
     assert (st[0].double().cpu() - want[0]).abs().max() <= 1e-5
+
+
+def test_om_streaming_prefill_chunks_on_the_tensor_cores(dev):
+    """bf16 prefill in chunks against a growing cache: every chunk of queries is folded
+    against the cached keys and its own keys with the carrier passed along, on the
+    tensor-core kernel (state in and out, causal mask with key offset, a chunk whose
+    keys all lie in the future of an earlier query tile)."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(23)
+    B, H, T, d = 1, 3, 640, 64
+    q, k, v = (torch.randn(B, H, T, d, generator=g).bfloat16() for _ in range(3))
+    want = oracle.om_causal_chunked(q.double(), k.double(), v.double(), [T], 0.2)
+    # all queries at once, keys arriving in three uneven pieces
+    st, off = None, 0
+    for n in (200, 300, 140):
+        st = ops.om_step_qk(st, q.to(dev), k[:, :, off:off + n].to(dev), v[:, :, off:off + n].to(dev), 0.2, True, off)
+        off += n
+    assert rel_to_max(ops.om_apply_state(st), want) <= BF16_TOL
+    # query chunks of 256 rows, each against everything cached so far (key_offset = -first row)
+    outs = []
+    for q0 in range(0, T, 256):
+        q1 = min(T, q0 + 256)
+        st = ops.om_step_qk(None, q[:, :, q0:q1].to(dev), k[:, :, :q1].to(dev), v[:, :, :q1].to(dev), 0.2, True, -q0)
+        outs.append(ops.om_apply_state(st))
+    assert rel_to_max(torch.cat(outs, 2), want) <= BF16_TOL
+    ops.check_device_status(dev)
 
 
 def test_causal_softmax_blocks_entry_point(dev):
