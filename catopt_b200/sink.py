@@ -3,7 +3,7 @@
 catopt routes an extracted term to the first ``ExecutorSpec`` of
 ``Sink.executors`` whose ``carrier`` is not ``None`` and whose ``accepts(term)``
 is true (catopt_orchestrator/optimize.py:485-495); mapping order is routing
-order.  ``B200Sink`` puts five B200 specs in front of the torch ones:
+order.  ``B200Sink`` puts six B200 specs in front of the torch ones:
 
 * ``b200_om_decayed_chunked`` — the uniform K-chunk decayed term of
   ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152).  ``accepts``
@@ -19,7 +19,10 @@ order.  ``B200Sink`` puts five B200 specs in front of the torch ones:
   reference's pairwise executor (or the generic module) still takes it.
 * ``b200_om_causal`` — causal softmax attention over a sequence of key/value blocks in
   its online-softmax carrier form ``om_apply(<om_compose tree of om_elem(masked
-  scores_i, v_i)>)`` (``om_causal_plan``); one ``cb2_om_causal_fwd``.
+  scores_i, v_i)>)`` (``om_causal_plan``), causal or unmasked; one ``cb2_om_fwd``.
+  ``b200_om_streaming`` names the same module for callers that want the raw
+  carrier (``forward_state``: one ``cb2_om_step`` per block), as the reference
+  lists its batched and streaming om executors separately.
 * ``b200_scan`` — diagonal ``applyd(<aff_diag tree>, h)`` scan applications (the
   terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
   leaf stacking are reused, the composed-map reduction runs in
@@ -851,6 +854,13 @@ class B200Sink(TorchSink):
                     lambda ir, p: B200CausalSoftmaxModule(ir, param_values=p),
                     lambda term: om_causal_plan(term) is not None,
                     _engaged,
+                    (frozenset({"om_apply"}), frozenset({"om_compose"}), frozenset({"om", "om_elem"})),
+                ),
+                "b200_om_streaming": ExecutorSpec(
+                    "b200_om_streaming",
+                    lambda ir, p: B200CausalSoftmaxModule(ir, param_values=p),
+                    lambda term: om_causal_plan(term) is not None,
+                    lambda m: bool(getattr(m, "is_streaming", False)),
                     (frozenset({"om_apply"}), frozenset({"om_compose"}), frozenset({"om", "om_elem"})),
                 ),
                 "b200_scan": ExecutorSpec(

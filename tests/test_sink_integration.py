@@ -33,7 +33,8 @@ def _route(sink, term):
 def test_b200_specs_come_first_and_are_executor_specs():
     s = b200.B200Sink()
     names = list(s.executors)
-    assert names[:5] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_scan", "b200_omd", "b200_linear_chain"]
+    assert names[:6] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_om_streaming", "b200_scan", "b200_omd",
+                         "b200_linear_chain"]
     assert "om_decayed_chunked" in names and names[-1] == "generic"
     assert all(isinstance(v, ExecutorSpec) for v in s.executors.values())
 
@@ -127,7 +128,7 @@ def _scan_term(T=6, d=8):
 def test_scan_term_routes_to_b200_scan_and_keeps_reference_plan():
     ir = _scan_term()
     s = b200.B200Sink()
-    assert "b200_scan" in list(s.executors)[:4]
+    assert "b200_scan" in list(s.executors)[:5]
     spec = _route(s, ir.root)
     assert spec.name == "b200_scan"
     vals = {"a": torch.full((8,), 0.9), "h0": torch.ones(8)}
@@ -439,6 +440,8 @@ def test_om_causal_module_conforms_and_refuses_cpu():
     spec = b200.B200Sink().executors["b200_om_causal"]
     mod = spec.lower(ir, None)
     assert isinstance(mod, BatchedExecutor) and spec.engaged(mod) and mod.n_blocks == 2
+    sspec = b200.B200Sink().executors["b200_om_streaming"]
+    assert sspec.engaged(sspec.lower(ir, None)) and mod.is_streaming
     from catopt_b200 import B200Error
 
     q = torch.randn(2, 3, 8, 4)
