@@ -240,7 +240,11 @@ int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int 
  * queries are the newest positions.
  * scratch (cb2_om_step_scratch_bytes bytes, may be NULL): with few queries and
  * many keys (decode) the keys are cut over extra CTAs that each build a partial
- * carrier there, folded in key order afterwards — the monoid is associative. */
+ * carrier there, folded in key order afterwards — the monoid is associative.
+ * Paths: at most 8 query rows and >= 256 keys: a streaming, memory-bound kernel
+ * (needs scratch); bf16 with more rows: the tensor-core kernel, state carried in
+ * tensor memory; everything else: the fp32 FMA tile kernel.
+ * dev_status: as for the other tensor-core entry points (may be NULL). */
 size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv);
 int cb2_om_step(const void* q, const void* k, const void* v,
                 const float* m_in, const float* l_in, const float* a_in,
