@@ -579,3 +579,51 @@ def test_ragged_recogniser_on_random_partitions():
 
         bad = _mutate(ir, bump)
         assert bad != ir.root and b200.decayed_ragged_plan(bad) is None
+
+
+def test_equivalent_spellings_of_the_cross_gate_are_accepted_and_other_functions_declined():
+    """The spellings the reference's own executor tests vary (tests/test_decayed_lower.py:
+    139-166 there): the row gate on either side of the product, or inside the division,
+    is the same function and is taken; a missing gate, a row-gated intra arm or a
+    second decay rate is a different function and is left to the reference's executor."""
+    chunked, _ = make_golden._decayed_terms(1, 2, 48, 8, 16, True, 2.0)
+    base = b200.decayed_plan(chunked.root)
+    assert base is not None
+
+    def is_gate(t):
+        return isinstance(t, Op) and t.op == "unsqueeze" and isinstance(t.args[0], Op) and t.args[0].op == "decay_vec" \
+            and int(t.args[0].attrs.get("sign", 1)) == 1
+
+    def swap(n):       # mul(row, x) -> mul(x, row)
+        if n.op == "mul" and len(n.args) == 2 and is_gate(n.args[0]):
+            return Op.make("mul", n.args[1], n.args[0])
+        return n
+
+    def gate_inside(n):   # mul(row, div(body, c)) -> div(mul(row, body), c)
+        if n.op == "mul" and len(n.args) == 2 and is_gate(n.args[0]) and isinstance(n.args[1], Op) \
+                and n.args[1].op == "div":
+            body, c = n.args[1].args
+            return Op.make("div", Op.make("mul", n.args[0], body), c)
+        return n
+
+    for fn in (swap, gate_inside):
+        variant = _mutate(chunked, fn)
+        assert variant != chunked.root
+        plan = b200.decayed_plan(variant)
+        assert plan is not None, fn.__name__
+        assert (plan["q"], plan["k"], plan["v"], plan["gamma"], plan["scale"]) == \
+            (base["q"], base["k"], base["v"], base["gamma"], base["scale"])
+
+    def drop_gate(n):     # mul(row, x) -> x : gateless cross terms are another function
+        if n.op == "mul" and len(n.args) == 2 and is_gate(n.args[0]):
+            return n.args[1]
+        return n
+
+    def second_rate(n):   # decay(g, t) of the later arms replaced by another parameter's
+        if n.op == "decay":
+            return Op.make("decay", Param("g2", n.args[0].typ), **dict(n.attrs))
+        return n
+
+    for fn in (drop_gate, second_rate):
+        other = _mutate(chunked, fn)
+        assert other != chunked.root and b200.decayed_plan(other) is None, fn.__name__
