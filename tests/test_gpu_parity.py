@@ -388,6 +388,36 @@ def test_decayed_bf16_sequence_lengths_off_the_tile_grid(dev, B, H, T, d, C):
     ops.check_device_status(dev)
 
 
+def test_decayed_config4_full_size_is_invariant_under_head_segmentation(dev):
+    """Benchmark config 4 at full size (B=16, H=32, T=8192, d=128, bf16, 4.3 GB): the
+    result with heads cut into segments (the shipped path: 1024 CTAs, state handed over
+    in scratch) equals the one-CTA-per-head result bit for bit, and the chunk argument
+    does not change it either."""
+    from catopt_b200 import _lib, ops
+
+    B, H, T, d = 16, 32, 8192, 128
+    lib = _lib.load()
+    g = torch.Generator(device=dev).manual_seed(4)
+    q, k, v = (torch.randn(B * H, T * d, device=dev, generator=g).mul_(1 / math.sqrt(d)).bfloat16().view(B, H, T, d)
+               for _ in range(3))
+    gam = (1 - torch.exp2(-5 - 8 * torch.arange(H, device=dev) / H)).float()
+    assert lib.cb2_decayed_chunk_scratch_bytes(B, H, T, d, d, 128, 1) > 0
+    seg = ops.decayed_chunk_fwd(q, k, v, gam, 128, 1.0)
+    one = torch.empty_like(seg)
+    st = ops.device_status(dev)
+    rc = lib.cb2_decayed_chunk_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), one.data_ptr(), gam.data_ptr(),
+                                   B, H, T, d, d, 128, 1.0, 1, None, 0, st.data_ptr(), ops.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(seg.view(torch.int16), one.view(torch.int16))
+    other = ops.decayed_chunk_fwd(q, k, v, gam, 64, 1.0)
+    assert torch.equal(seg.view(torch.int16), other.view(torch.int16))
+    assert torch.isfinite(seg[::5, ::7].float()).all()
+    ops.check_device_status(dev)
+    del q, k, v, seg, one, other
+    torch.cuda.empty_cache()
+
+
 def test_decayed_bf16_segmented_heads(dev):
     """More heads than SMs: the tensor-core kernel cuts every head into segments
     that different CTAs run, the state crossing through scratch.  Same result as
