@@ -3,7 +3,9 @@
 torch is used for device memory and streams only; every arithmetic step runs in
 ``libcatopt_b200.so``.  Scratch buffers are torch allocations cached per
 (device, purpose) and grown on demand, so steady-state calls allocate nothing
-and can be captured in a CUDA graph after a warm-up call.
+and can be captured in a CUDA graph after a warm-up call.  Calls of one purpose
+share their buffer: issue them on one stream (or order the streams), as the
+kernels that hand state through scratch would otherwise race.
 """
 from __future__ import annotations
 
