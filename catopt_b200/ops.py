@@ -3,9 +3,9 @@
 torch is used for device memory and streams only; every arithmetic step runs in
 ``libcatopt_b200.so``.  Scratch buffers are torch allocations cached per
 (device, purpose) and grown on demand, so steady-state calls allocate nothing
-and can be captured in a CUDA graph after a warm-up call.  Calls of one purpose
-share their buffer: issue them on one stream (or order the streams), as the
-kernels that hand state through scratch would otherwise race.
+and can be captured in a CUDA graph after a warm-up call.  The cache is keyed by
+the current stream as well, so concurrent streams never share a buffer; calls on
+one stream do, which stream order makes safe.
 """
 from __future__ import annotations
 
@@ -21,10 +21,11 @@ _status_words: dict[int, torch.Tensor] = {}
 
 
 def _scratch_buf(purpose: str, nbytes: int, device: torch.device) -> torch.Tensor | None:
-    """A cached uint8 scratch buffer of at least ``nbytes`` (``None`` for 0)."""
+    """A cached uint8 scratch buffer of at least ``nbytes`` (``None`` for 0), one per
+    (purpose, device, current stream): calls on different streams never share one."""
     if nbytes <= 0:
         return None
-    key = (purpose, device.index)
+    key = (purpose, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
