@@ -55,6 +55,19 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int,
          C.c_void_p, C.c_size_t, C.c_void_p],
     ),
+    "cb2_diag_fold_apply": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
+         C.c_longlong, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p],
+    ),
+    "cb2_gated_contract_on_tensor_cores": (
+        C.c_int, [C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int],
+    ),
+    "cb2_gated_contract_fwd": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_int,
+         C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
+    ),
     "cb2_decayed_chunk_on_tensor_cores": (
         C.c_int,
         [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],

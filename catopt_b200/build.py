@@ -26,6 +26,8 @@ SOURCES = [
     "decayed_chunk_small.cu",
     "decayed_chunk_tc.cu",
     "decayed_chunk.cu",
+    "gated_contract.cu",
+    "gated_contract_tc.cu",
     "om_causal.cu",
     "om_causal_tc.cu",
 ]

@@ -54,10 +54,15 @@ struct Vec<CB2_BF16> {
 
 // Partial map of leaves [j0, j1) for the state elements of this thread.
 // VEC: 16-byte vector loads (S a multiple of the vector width, aligned rows).
-template <int DTYPE, bool VEC>
+// CHRONO: the rows are stored in time order (row 0 = first step) instead of product
+// order; the partial map then grows on the left, B = a_j*B + b_j.
+// a_stride / b_stride: elements between consecutive rows (S, or 0 for a row shared by
+// every step).
+template <int DTYPE, bool VEC, bool CHRONO>
 __global__ void __launch_bounds__(kComposeThreads)
 compose_partial_kernel(const void* __restrict__ a, const void* __restrict__ b, long long n, long long S,
-                       long long seg_len, float* __restrict__ part_a, float* __restrict__ part_b) {
+                       long long seg_len, float* __restrict__ part_a, float* __restrict__ part_b,
+                       long long a_stride, long long b_stride) {
   using V = Vec<DTYPE>;
   constexpr int E = VEC ? V::kElems : 1;
   const long long c0 = (blockIdx.x * (long long)kComposeThreads + threadIdx.x) * E;
@@ -72,36 +77,46 @@ compose_partial_kernel(const void* __restrict__ a, const void* __restrict__ b, l
     float av[kUnroll][E], bv[kUnroll][E];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const size_t off = size_t(j + u) * size_t(S) + size_t(c0);
+      const size_t offa = size_t(j + u) * size_t(a_stride) + size_t(c0);
+      const size_t offb = size_t(j + u) * size_t(b_stride) + size_t(c0);
       if constexpr (VEC) {
-        V::ld(a, off, av[u]);
-        V::ld(b, off, bv[u]);
+        V::ld(a, offa, av[u]);
+        V::ld(b, offb, bv[u]);
       } else {
-        av[u][0] = V::ld1(a, off);
-        bv[u][0] = V::ld1(b, off);
+        av[u][0] = V::ld1(a, offa);
+        bv[u][0] = V::ld1(b, offb);
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u)
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        B[e] = fmaf(A[e], bv[u][e], B[e]);
+        if constexpr (CHRONO) {
+          B[e] = fmaf(av[u][e], B[e], bv[u][e]);
+        } else {
+          B[e] = fmaf(A[e], bv[u][e], B[e]);
+        }
         A[e] *= av[u][e];
       }
   }
   for (; j < j1; ++j) {
-    const size_t off = size_t(j) * size_t(S) + size_t(c0);
+    const size_t offa = size_t(j) * size_t(a_stride) + size_t(c0);
+    const size_t offb = size_t(j) * size_t(b_stride) + size_t(c0);
     float av[E], bv[E];
     if constexpr (VEC) {
-      V::ld(a, off, av);
-      V::ld(b, off, bv);
+      V::ld(a, offa, av);
+      V::ld(b, offb, bv);
     } else {
-      av[0] = V::ld1(a, off);
-      bv[0] = V::ld1(b, off);
+      av[0] = V::ld1(a, offa);
+      bv[0] = V::ld1(b, offb);
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      B[e] = fmaf(A[e], bv[e], B[e]);
+      if constexpr (CHRONO) {
+        B[e] = fmaf(av[e], B[e], bv[e]);
+      } else {
+        B[e] = fmaf(A[e], bv[e], B[e]);
+      }
       A[e] *= av[e];
     }
   }
@@ -113,18 +128,19 @@ compose_partial_kernel(const void* __restrict__ a, const void* __restrict__ b, l
   }
 }
 
-// Fold the segment maps in order (segment 0 holds the latest steps) and apply to h.
+// Fold the segment maps in order (segment 0 holds the latest steps, or with chrono
+// the earliest) and apply to h.
 template <int DTYPE>
 __global__ void __launch_bounds__(kComposeThreads)
 compose_apply_kernel(const float* __restrict__ part_a, const float* __restrict__ part_b,
-                     const void* __restrict__ h, void* __restrict__ out, int nseg, long long S) {
+                     const void* __restrict__ h, void* __restrict__ out, int nseg, long long S, int chrono) {
   using V = Vec<DTYPE>;
   const long long c = blockIdx.x * (long long)kComposeThreads + threadIdx.x;
   if (c >= S) return;
   float A = 1.f, B = 0.f;
   for (int s = 0; s < nseg; ++s) {
     const size_t i = size_t(s) * size_t(S) + size_t(c);
-    B = fmaf(A, part_b[i], B);
+    B = chrono ? fmaf(part_a[i], B, part_b[i]) : fmaf(A, part_b[i], B);
     A *= part_a[i];
   }
   V::st1(out, size_t(c), fmaf(A, V::ld1(h, size_t(c)), B));
@@ -143,7 +159,10 @@ int pick_segments(long long n, long long S, int elems_per_thread) {
 
 template <int DTYPE>
 int run(const void* a, const void* b, const void* h, void* out, long long n, long long S, void* scratch,
-        size_t scratch_bytes, cudaStream_t st) {
+        size_t scratch_bytes, cudaStream_t st, bool chrono = false, long long a_stride = -1,
+        long long b_stride = -1) {
+  if (a_stride < 0) a_stride = S;
+  if (b_stride < 0) b_stride = S;
   using V = Vec<DTYPE>;
   const bool vec = S % V::kElems == 0 && aligned16(a) && aligned16(b);
   const int E = vec ? V::kElems : 1;
@@ -155,13 +174,17 @@ int run(const void* a, const void* b, const void* h, void* out, long long n, lon
   const long long seg_len = (n + nseg - 1) / nseg;
   const long long threads = (S + E - 1) / E;
   const dim3 grid(unsigned((threads + kComposeThreads - 1) / kComposeThreads), unsigned(nseg));
-  if (vec)
-    compose_partial_kernel<DTYPE, true><<<grid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, part_a, part_b);
-  else
-    compose_partial_kernel<DTYPE, false><<<grid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, part_a, part_b);
+#define CB2_COMPOSE_LAUNCH(VEC_, CHRONO_)                                                        \
+  compose_partial_kernel<DTYPE, VEC_, CHRONO_><<<grid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, \
+                                                                                part_a, part_b, a_stride, b_stride)
+  if (vec && chrono) CB2_COMPOSE_LAUNCH(true, true);
+  else if (vec) CB2_COMPOSE_LAUNCH(true, false);
+  else if (chrono) CB2_COMPOSE_LAUNCH(false, true);
+  else CB2_COMPOSE_LAUNCH(false, false);
+#undef CB2_COMPOSE_LAUNCH
   CB2_LAUNCH_CHECK();
   compose_apply_kernel<DTYPE><<<unsigned((S + kComposeThreads - 1) / kComposeThreads), kComposeThreads, 0, st>>>(
-      part_a, part_b, h, out, nseg, S);
+      part_a, part_b, h, out, nseg, S, chrono ? 1 : 0);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }
@@ -187,5 +210,31 @@ extern "C" int cb2_diag_compose_apply(const void* a_seq, const void* b_seq, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == CB2_F32) return cb2::run<CB2_F32>(a_seq, b_seq, h, out, n, S, scratch, scratch_bytes, st);
   if (dtype == CB2_BF16) return cb2::run<CB2_BF16>(a_seq, b_seq, h, out, n, S, scratch, scratch_bytes, st);
+  return CB2_UNSUPPORTED_DTYPE;
+}
+
+// The same fold for rows stored in TIME order (row 0 = first step):
+//     out = f_{n-1}( ... f_1( f_0(h) ) ),   f_j(h) = a_rows[j]*h + b_rows[j],
+// the sequence form `applyd(aff_diag(a, b), h)` folded along the step axis that the
+// reference's generated scan kernels compute (`_seq_triton_source` / `_seq_binding`,
+// catopt_discovery/genkernel.py:1031-1060, 1208-1233).  a_step_stride / b_step_stride:
+// elements between consecutive rows, S for one row per step or 0 for a row every step
+// shares (a decay that does not depend on the step).
+extern "C" int cb2_diag_fold_apply(const void* a_rows, const void* b_rows, const void* h, void* out,
+                                   long long n, long long S, long long a_step_stride,
+                                   long long b_step_stride, int dtype, void* scratch, size_t scratch_bytes,
+                                   void* stream) {
+  if (!a_rows || !b_rows || !h || !out) return CB2_NULL_PTR;
+  if (n <= 0 || S <= 0 || S > (1ll << 40) / n) return CB2_BAD_SHAPE;
+  if ((S + cb2::kComposeThreads - 1) / cb2::kComposeThreads > 0x7fffffffll) return CB2_BAD_SHAPE;
+  if ((a_step_stride != 0 && a_step_stride != S) || (b_step_stride != 0 && b_step_stride != S))
+    return CB2_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CB2_F32)
+    return cb2::run<CB2_F32>(a_rows, b_rows, h, out, n, S, scratch, scratch_bytes, st, true, a_step_stride,
+                             b_step_stride);
+  if (dtype == CB2_BF16)
+    return cb2::run<CB2_BF16>(a_rows, b_rows, h, out, n, S, scratch, scratch_bytes, st, true, a_step_stride,
+                              b_step_stride);
   return CB2_UNSUPPORTED_DTYPE;
 }

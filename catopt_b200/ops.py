@@ -361,3 +361,119 @@ def diag_prefix_maps(a_seq: torch.Tensor, b_seq: torch.Tensor):
     h1 = torch.ones(1, D, 1, dtype=torch.float32, device=a.device)
     pa = diag_scan_fwd(a, torch.zeros_like(u), ones, ones, h1)
     return pa.reshape(T, *state_shape), pb.reshape(T, *state_shape)
+
+
+def diag_fold_apply(a_rows: torch.Tensor, b_rows: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """Fold ``h <- a_t*h + b_t`` over rows in TIME order and return the last state.
+
+    ``a_rows``/``b_rows`` are ``[n, *state]`` or ``[*state]`` (one row shared by every
+    step), broadcastable against ``h``'s shape — the sequence form
+    ``applyd(aff_diag(a, b), h)`` that the reference's generated scan kernel folds
+    along the step axis (catopt_discovery/genkernel.py:1031-1060).  One pass of
+    ``cb2_diag_fold_apply``; a row shared by all steps is read through a zero step
+    stride instead of being repeated in memory.
+    """
+    require_cuda(h)
+    state_shape = tuple(h.shape)
+    S = h.numel()
+    dt = h.dtype
+    n = None
+    for r in (a_rows, b_rows):
+        if r.dim() == len(state_shape) + 1:
+            n = r.shape[0] if n is None else n
+            if r.shape[0] != n:
+                raise B200Error("diag_fold_apply: a and b disagree on the number of steps")
+    if n is None:
+        raise B200Error("diag_fold_apply: neither operand carries a step axis")
+    if n == 0 or S == 0:
+        raise B200Error("diag_fold_apply: empty fold")
+
+    def rows(r: torch.Tensor) -> tuple[torch.Tensor, int]:
+        r = r.to(dt)
+        if r.dim() == len(state_shape) + 1:
+            return r.expand(n, *state_shape).reshape(n, S).contiguous(), S
+        return r.expand(state_shape).reshape(S).contiguous(), 0
+
+    a, a_stride = rows(a_rows)
+    b, b_stride = rows(b_rows)
+    hh = h.reshape(S).contiguous()
+    out = torch.empty(S, dtype=dt, device=h.device)
+    lib = _lib.load()
+    code = dtype_code(dt)
+    need = lib.cb2_diag_compose_scratch_bytes(n, S, code)
+    scratch = _scratch_buf("compose", need, h.device)
+    rc = lib.cb2_diag_fold_apply(a.data_ptr(), b.data_ptr(), hh.data_ptr(), out.data_ptr(), n, S, a_stride,
+                                 b_stride, code, _ptr(scratch), need, stream_ptr())
+    check(rc, "cb2_diag_fold_apply")
+    return out.reshape(state_shape)
+
+
+# --------------------------------------------------------------------------- gated contraction
+def _gate_index_rule(gate_batch: tuple, batch: tuple) -> tuple[int, int] | None:
+    """(div, mod) with gate(b) = (b // div) % mod for a gate whose batch dims are each 1
+    or full, when its full dims form one contiguous run; ``None`` otherwise."""
+    full = [i for i, (gd, bd) in enumerate(zip(gate_batch, batch)) if gd == bd and bd != 1]
+    if not full:
+        return 1, 1
+    if full != list(range(full[0], full[-1] + 1)):
+        return None
+    if any(gate_batch[i] != 1 for i in range(len(batch)) if i not in full):
+        return None
+    div = 1
+    for bd in batch[full[-1] + 1:]:
+        div *= bd
+    mod = 1
+    for i in full:
+        mod *= batch[i]
+    return div, mod
+
+
+def gated_contract(s: torch.Tensor, g: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """``(s * g) @ v`` in one kernel — the ``om_decayed`` element on materialised scores.
+
+    ``s``: ``[..., T, K]`` scores, ``g``: a gate broadcastable to ``s`` (decay mask,
+    causal mask, ...), ``v``: ``[..., K, dv]``.  Semantics of the reference's binding
+    ``_om_decayed_torch`` (catopt_carriers/om.py:1053-1057): the product is rounded to
+    the tensor dtype, the contraction accumulates in fp32.  A gate shared over leading
+    batch dims (``[T,K]``, ``[H,T,K]`` under ``[B,H,T,K]``, ``[B,1,T,K]``) is indexed in
+    place; other broadcast patterns are expanded first.
+    """
+    require_cuda()
+    for t in (s, g, v):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise B200Error("catopt_b200 executors take CUDA tensors only (no CPU fallback)")
+    if s.dim() < 2 or v.dim() < 2 or s.shape[-1] != v.shape[-2]:
+        raise B200Error(f"gated_contract shape mismatch: s {tuple(s.shape)}, v {tuple(v.shape)}")
+    dt = s.dtype
+    if v.dtype != dt or g.dtype != dt:
+        dt = torch.promote_types(torch.promote_types(s.dtype, g.dtype), v.dtype)
+    code = dtype_code(dt)
+    T, K, dv = s.shape[-2], s.shape[-1], v.shape[-1]
+    gate_tail = torch.broadcast_shapes(g.shape[-2:] if g.dim() >= 2 else g.shape, (T, K))
+    if tuple(gate_tail) != (T, K):
+        raise B200Error(f"gate {tuple(g.shape)} does not broadcast to the scores {tuple(s.shape)}")
+    g_batch_raw = tuple(g.shape[:-2]) if g.dim() >= 2 else ()
+    batch = tuple(torch.broadcast_shapes(s.shape[:-2], v.shape[:-2], g_batch_raw))
+    nb = 1
+    for bd in batch:
+        nb *= bd
+    out = torch.empty(*batch, T, dv, dtype=dt, device=s.device)
+    if nb * T * dv == 0:
+        return out
+    if K == 0:
+        return out.zero_()
+    ss = s.to(dt).expand(*batch, T, K).contiguous()
+    vv = v.to(dt).expand(*batch, K, dv).contiguous()
+    g_batch = (1,) * (len(batch) - len(g_batch_raw)) + g_batch_raw
+    rule = _gate_index_rule(g_batch, batch)
+    if rule is None:
+        gg = g.to(dt).expand(*batch, T, K).contiguous()
+        rule, ng = (1, nb), nb
+    else:
+        gg = g.to(dt).expand(*g_batch_raw, T, K).contiguous()
+        ng = rule[1]
+    status = device_status(s.device)
+    rc = _lib.load().cb2_gated_contract_fwd(ss.data_ptr(), gg.data_ptr(), vv.data_ptr(), out.data_ptr(), nb, ng,
+                                            T, K, dv, rule[0], rule[1], code, status.data_ptr(), stream_ptr())
+    check(rc, "cb2_gated_contract_fwd")
+    return out

@@ -197,6 +197,42 @@ int cb2_diag_compose_apply(const void* a_seq, const void* b_seq, const void* h, 
                            long long n, long long S, int dtype, void* scratch,
                            size_t scratch_bytes, void* stream);
 
+/* The same fold for rows stored in TIME order (row 0 = first step),
+ *     out = f_{n-1}( ... f_1( f_0(h) ) ),  f_j(h) = a_rows[j]*h + b_rows[j]:
+ * the sequence form `applyd(aff_diag(a, b), h)` folded along the step axis, which
+ * the reference's generated scan kernels compute (`_seq_triton_source` and
+ * `_seq_binding`, packages/catopt-discovery/src/catopt_discovery/genkernel.py:
+ * 1031-1060, 1208-1233).  a_step_stride / b_step_stride: elements between
+ * consecutive rows — S, or 0 for one row shared by every step.  Scratch as for
+ * cb2_diag_compose_apply. */
+int cb2_diag_fold_apply(const void* a_rows, const void* b_rows, const void* h, void* out,
+                        long long n, long long S, long long a_step_stride,
+                        long long b_step_stride, int dtype, void* scratch,
+                        size_t scratch_bytes, void* stream);
+
+/* -------------------------------------------------------------------------
+ * Gated contraction  o[b] = (s[b] * g[gate(b)]) @ v[b] :  the body of the
+ * reference's `om_decayed` element, `(s * d) @ v`
+ * (packages/catopt-carriers/src/catopt_carriers/om.py:1053-1057), for scores
+ * that are already materialised.  Replaces the generated fused-contraction
+ * kernel of the reference's codegen tier (`_decayed_triton_source`,
+ * `_decayed_binding`, `decayed_triton_bindings`; genkernel.py:1582-1631,
+ * 1784-1861, 1903-1925), which this library's sink binds to minted
+ * `decayed_<i>_k` ops in its place.
+ * s: [nb,T,K]; g: [ng,T,K]; v: [nb,K,dv]; o: [nb,T,dv]; the gate of batch b is
+ * g[(b / g_div) % g_mod] (g_mod <= ng): (1,1) one gate for all, (1,H) one per
+ * head of a [B,H] batch, (H,B) one per batch entry, (1,nb) one per (b,h).
+ * The product s*g is rounded to the tensor dtype as the reference's multiply
+ * is, the contraction accumulates in fp32, o is rounded once.
+ * bf16 with K, dv multiples of 8, dv <= 128 and 16-byte aligned pointers runs
+ * on the tensor cores (cb2_gated_contract_on_tensor_cores() == 1); everything
+ * else on the fp32 FMA pipes.  No scratch.
+ * ------------------------------------------------------------------------- */
+int cb2_gated_contract_on_tensor_cores(long long nb, int T, int K, int dv, int dtype);
+int cb2_gated_contract_fwd(const void* s, const void* g, const void* v, void* o,
+                           long long nb, long long ng, int T, int K, int dv, int g_div,
+                           int g_mod, int dtype, int* dev_status, void* stream);
+
 /* -------------------------------------------------------------------------
  * (b') causal softmax attention through the online-softmax monoid,
  *     o_t = sum_{j<=t} softmax_j(scale * q_t.k_j) v_j      per (batch, head).

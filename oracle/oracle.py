@@ -127,6 +127,13 @@ def decayed_quadratic(q, k, v, gamma, scale: float = 1.0) -> torch.Tensor:
     return torch.matmul(s * d, v) / scale
 
 
+def om_decayed(s: torch.Tensor, d: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """`_om_decayed_torch` (catopt_carriers/om.py:1053-1057): `(s * d) @ v` on
+    materialised scores — the element the reference's generated fused-contraction
+    kernel computes (catopt_discovery/genkernel.py:1582-1631)."""
+    return torch.matmul(s * d, v)
+
+
 def decayed_chunked_pairwise(q, k, v, gamma, chunk: int, scale: float = 1.0) -> torch.Tensor:
     """`ChunkedDecayModule._forward_impl` (decayed_lower.py:702-724) on the
     uniform K-chunk term of `om_decayed_kway_blocks` (om.py:3076-3152):
@@ -264,6 +271,20 @@ def diag_scan_serial(a, x, b, c, h0=None):
         h = applyd((a[:, t], u), h)
         y[:, t] = (h * c).sum(-1)
     return y, h
+
+
+def seq_fold(a_rows, b_rows, h, axis: int = 0):
+    """The sequence form `applyd(aff_diag(a, b), h)` folded along the step axis:
+    `acc = a_t * acc + b_t` for t in time order, the loop of the reference's
+    generated scan kernel (`_seq_triton_source`, catopt_discovery/genkernel.py:
+    1031-1060) with its right-aligned broadcasting (`_seq_args`, 1173-1205): an
+    operand without a step axis is shared by every step."""
+    full = torch.broadcast_shapes(a_rows.shape, b_rows.shape)
+    a_rows, b_rows = a_rows.expand(full), b_rows.expand(full)
+    acc = h
+    for t in range(full[axis]):
+        acc = applyd((a_rows.select(axis, t), b_rows.select(axis, t)), acc)
+    return acc
 
 
 def fused_diag_levels(a_seq, b_seq, h):

@@ -132,3 +132,50 @@ def verify_cases():
     cases.append(("odd_len_bf16", rb.flatten()[:1003], ob.flatten()[:1003], 2e-2, None))
     cases.append(("single", torch.tensor([2.0]), torch.tensor([2.5]), 1e-4, None))
     return cases
+
+
+# name -> (batch shape, gate batch shape, T, K, dv, dtype)
+GATED_CASES = {
+    "shared_gate_f32": ((2, 3), (), 40, 40, 16, torch.float32),
+    "per_head_f32": ((2, 3), (3,), 33, 47, 20, torch.float32),
+    "per_batch_f32": ((2, 3), (2, 1), 16, 24, 8, torch.float32),
+    "full_gate_bf16": ((2, 2), (2, 2), 128, 192, 64, torch.bfloat16),
+    "decay_mask_bf16": ((1, 4), (4,), 200, 200, 128, torch.bfloat16),
+    "ragged_bf16": ((3,), (), 130, 72, 24, torch.bfloat16),
+    "odd_bf16": ((2,), (), 19, 21, 5, torch.bfloat16),
+}
+
+
+def gated_inputs(name: str):
+    """Scores ~N(0,1), values ~N(0,1); the gate is a decay mask tril(g^(i-j)) for the
+    `decay_mask` case (rates 0.9 .. 0.99) and uniform(0,1) otherwise."""
+    batch, gbatch, T, K, dv, dtype = GATED_CASES[name]
+    g = rng(6000 + sorted(GATED_CASES).index(name))
+    s = torch.from_numpy(g.standard_normal((*batch, T, K)))
+    v = torch.from_numpy(g.standard_normal((*batch, K, dv)))
+    if name.startswith("decay_mask"):
+        rates = torch.linspace(0.9, 0.99, gbatch[0], dtype=torch.float64)
+        pos = torch.arange(T, dtype=torch.float64)
+        gate = torch.tril(rates[:, None, None] ** (pos[:, None] - pos[None, :]).clamp_min(0))
+    else:
+        gate = torch.from_numpy(g.random((*gbatch, T, K)))
+    return s.to(dtype), gate.to(dtype), v.to(dtype)
+
+
+# name -> (step count, state shape, a has a step axis, b has a step axis, dtype)
+FOLD_CASES = {
+    "per_step_f32": (37, (2, 5), True, True, torch.float32),
+    "shared_decay_f32": (50, (3, 8), False, True, torch.float32),
+    "long_f32": (700, (4, 16), True, True, torch.float32),
+    "per_step_bf16": (64, (2, 16), True, True, torch.bfloat16),
+}
+
+
+def fold_inputs(name: str):
+    """Rows in time order: a = sigmoid(N(2,1)), b ~N(0,1), h ~N(0,1)."""
+    n, state, a_step, b_step, dtype = FOLD_CASES[name]
+    g = rng(7000 + sorted(FOLD_CASES).index(name))
+    a = torch.sigmoid(torch.from_numpy(2 + g.standard_normal((n, *state) if a_step else state)))
+    b = torch.from_numpy(g.standard_normal((n, *state) if b_step else state))
+    h = torch.from_numpy(g.standard_normal(state))
+    return a.to(dtype), b.to(dtype), h.to(dtype)

@@ -214,6 +214,33 @@ def gen_om_causal() -> None:
     np.savez_compressed(HERE / "om_causal.npz", **out)
 
 
+# --------------------------------------------------------------------------- generated-kernel tier
+def gen_gated() -> None:
+    """The `om_decayed` binding `(s*d)@v` on materialised scores, and the sequence
+    form `applyd(aff_diag(a_t, b_t), h)` folded in time order with the reference's
+    own bindings — the two functions its generated kernels compute."""
+    from catopt_carriers.om import TORCH_BINDINGS as OMB
+    from catopt_torch.torch_bridge import _IR_TO_TORCH as BIND
+
+    out = {}
+    for name in cases.GATED_CASES:
+        s, gate, v = cases.gated_inputs(name)
+        o = OMB["om_decayed"](s, gate, v)
+        out[f"gated.{name}"] = _np(o.contiguous())
+        print(f"gated {name}: {tuple(o.shape)} {o.dtype}")
+    for name in cases.FOLD_CASES:
+        a, b, h = cases.fold_inputs(name)
+        n = cases.FOLD_CASES[name][0]
+        acc = h
+        for t in range(n):
+            at = a[t] if a.dim() == h.dim() + 1 else a
+            bt = b[t] if b.dim() == h.dim() + 1 else b
+            acc = BIND["applyd"](BIND["aff_diag"](at, bt), acc)
+        out[f"fold.{name}"] = _np(acc.contiguous())
+        print(f"fold {name}: {tuple(acc.shape)} {acc.dtype}")
+    np.savez_compressed(HERE / "gated.npz", **out)
+
+
 # --------------------------------------------------------------------------- verify
 def gen_verify() -> None:
     from catopt_torch.report import verify_equiv
@@ -240,7 +267,7 @@ if __name__ == "__main__":
     _add_reference(sys.argv[1])
     torch.manual_seed(0)
     only = set(sys.argv[2:])
-    for nm, fn in (("verify", gen_verify), ("scan", gen_scan), ("om_causal", gen_om_causal),
+    for nm, fn in (("verify", gen_verify), ("scan", gen_scan), ("om_causal", gen_om_causal), ("gated", gen_gated),
                    ("decayed", gen_decayed), ("chain", gen_chain)):
         if not only or nm in only:
             fn()

@@ -823,3 +823,99 @@ def test_device_status_clean(dev):
     from catopt_b200 import ops
 
     ops.check_device_status(dev)
+
+
+# --------------------------------------------------------------------------- generated-kernel tier
+def _gold_tensor(arr, dtype):
+    t = torch.from_numpy(arr)
+    return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+
+@pytest.mark.parametrize("name", list(cases.GATED_CASES))
+def test_gated_contract_vs_reference_fixture(dev, name):
+    """(s*g)@v against what the reference's `om_decayed` binding returned."""
+    from catopt_b200 import ops
+
+    s, gate, v = cases.gated_inputs(name)
+    want = _gold_tensor(np.load(GOLD / "gated.npz")[f"gated.{name}"], s.dtype)
+    got = ops.gated_contract(s.to(dev), gate.to(dev), v.to(dev))
+    ops.check_device_status(dev)
+    assert got.shape == want.shape and got.dtype == want.dtype
+    tol = BF16_TOL if s.dtype == torch.bfloat16 else FP32_TOL
+    assert rel_to_max(got, want) <= tol, name
+    # against the same element evaluated in fp64 on the rounded product: much tighter
+    p = (s * gate).double()
+    exact = p @ v.double()
+    assert rel_to_max(got, exact) <= (4e-3 if s.dtype == torch.bfloat16 else 2e-6), name
+
+
+@pytest.mark.parametrize("B,H,T,K,dv,gate_kind", [(2, 4, 1024, 1024, 128, "head"), (1, 3, 384, 640, 64, "one"),
+                                                  (2, 2, 200, 136, 96, "full"), (3, 1, 129, 64, 8, "batch")])
+def test_gated_contract_tensor_core_path_vs_oracle(dev, B, H, T, K, dv, gate_kind):
+    from catopt_b200 import _lib, ops
+
+    assert _lib.load().cb2_gated_contract_on_tensor_cores(B * H, T, K, dv, _lib.CB2_BF16) == 1
+    g = torch.Generator().manual_seed(31)
+    s = torch.randn(B, H, T, K, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H, K, dv, generator=g).to(torch.bfloat16)
+    gshape = {"head": (H, T, K), "one": (T, K), "full": (B, H, T, K), "batch": (B, 1, T, K)}[gate_kind]
+    gate = torch.rand(gshape, generator=g).to(torch.bfloat16)
+    got = ops.gated_contract(s.to(dev), gate.to(dev), v.to(dev))
+    ops.check_device_status(dev)
+    want = ((s * gate).double() @ v.double())
+    assert got.shape == (B, H, T, dv)
+    assert rel_to_max(got, want) <= 4e-3      # only the output rounding separates them
+    # neighbouring batches must not leak into one another: each batch alone gives the same bits
+    one = ops.gated_contract(s[:1, :1].to(dev), (gate if gate_kind == "one" else
+                                                 gate[:1] if gate_kind == "head" else gate[:1, :1]).to(dev),
+                             v[:1, :1].to(dev))
+    assert torch.equal(one[0, 0], got[0, 0])
+
+
+def test_gated_contract_is_the_quadratic_decayed_form(dev):
+    """With s = q k^T and g = decay(gamma, T) the element is the decayed attention the
+    chunked kernel computes (two routes to one function)."""
+    from catopt_b200 import ops
+
+    B, H, T, d = 1, 4, 512, 64
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(B, H, T, d, generator=g) / d ** 0.5 for _ in range(3))
+    gamma = torch.tensor([0.9, 0.95, 0.98, 0.995])
+    s = q @ k.transpose(-1, -2)
+    gate = oracle.decay_matrix(gamma, T)
+    got = ops.gated_contract(s.to(dev), gate.to(dev), v.to(dev))
+    want = oracle.decayed_quadratic(q.double(), k.double(), v.double(), gamma.double())
+    assert rel_to_max(got, want) <= FP32_TOL
+    chunked = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 64)
+    assert rel_to_max(chunked, got) <= FP32_TOL
+
+
+@pytest.mark.parametrize("name", list(cases.FOLD_CASES))
+def test_seq_fold_vs_reference_fixture(dev, name):
+    from catopt_b200 import ops
+
+    a, b, h = cases.fold_inputs(name)
+    want = _gold_tensor(np.load(GOLD / "gated.npz")[f"fold.{name}"], h.dtype)
+    got = ops.diag_fold_apply(a.to(dev), b.to(dev), h.to(dev))
+    tol = BF16_TOL if h.dtype == torch.bfloat16 else FP32_TOL
+    assert got.shape == want.shape and got.dtype == want.dtype
+    assert rel_to_max(got, want) <= tol, name
+
+
+def test_seq_fold_equals_product_order_fold_at_width(dev):
+    """Time order and product order are two storage orders of one fold: flipping the rows
+    and calling the product-order entry point gives the same state (fp32, 1e-6)."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(11)
+    n, S = 4096, 8 * 1024
+    a = torch.sigmoid(4 + 0.5 * torch.randn(n, S, generator=g)).to(dev)
+    b = (0.1 * torch.randn(n, S, generator=g)).to(dev)
+    h = torch.randn(S, generator=g).to(dev)
+    t_order = ops.diag_fold_apply(a, b, h)
+    p_order = ops.diag_compose_apply(a.flip(0).contiguous(), b.flip(0).contiguous(), h)
+    assert rel_to_max(t_order, p_order) <= 2e-6
+    # a decay row shared by every step is read in place
+    shared = ops.diag_fold_apply(a[0], b, h)
+    full = ops.diag_fold_apply(a[0].expand(n, S).contiguous(), b, h)
+    assert torch.equal(shared, full)

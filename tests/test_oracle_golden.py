@@ -125,3 +125,26 @@ def test_om_decode_row_sees_only_key_zero():
     q, k, v, sizes, scale = cases.om_causal_inputs("decode_row")
     o = oracle.om_causal_chunked(q, k, v, sizes, scale)
     assert torch.allclose(o[..., 0, :], v[..., 0, :], atol=1e-12)
+
+
+# --------------------------------------------------------------------------- generated-kernel tier
+def _from_gold(arr, dtype):
+    t = torch.from_numpy(arr)
+    return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+
+@pytest.mark.parametrize("name", list(cases.GATED_CASES))
+def test_om_decayed_element_bitwise_vs_reference(name):
+    s, gate, v = cases.gated_inputs(name)
+    want = _from_gold(_load("gated.npz")[f"gated.{name}"], s.dtype)
+    assert torch.equal(oracle.om_decayed(s, gate, v), want)
+
+
+@pytest.mark.parametrize("name", list(cases.FOLD_CASES))
+def test_seq_fold_bitwise_vs_reference(name):
+    a, b, h = cases.fold_inputs(name)
+    want = _from_gold(_load("gated.npz")[f"fold.{name}"], h.dtype)
+    n = cases.FOLD_CASES[name][0]
+    ar = a if a.dim() == h.dim() + 1 else a.expand(n, *a.shape)
+    br = b if b.dim() == h.dim() + 1 else b.expand(n, *b.shape)
+    assert torch.equal(oracle.seq_fold(ar, br, h), want)
