@@ -348,6 +348,18 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
         flops=4 * 32 * 65536 * 128)
     del qd, kd, vd
 
+    # the om_decayed element on materialised scores, (s*g)@v (the site the reference's generated
+    # fused-contraction kernel lowers): B=2 H=16 T=K=4096 dv=128 bf16, one gate for all heads
+    sg = _randn_bf16((32, 4096 * 4096), gen).view(2, 16, 4096, 4096)
+    vg = _randn_bf16((32, 4096 * 128), gen).view(2, 16, 4096, 128)
+    gg = torch.rand(4096, 4096, device=dev, generator=gen).bfloat16()
+    ms = time_steps(lambda: ops.gated_contract(sg, gg, vg), K, W, world)
+    out["gated_contract_bf16_B2_H16_T4096_K4096_dv128"] = entry(
+        ms, 2 * 4096, (sg.numel() + gg.numel() + 2 * vg.numel()) * 2, 1,
+        "scores 1.07 GB read once, gate (33.5 MB) shared by all heads; P = s*g kept in tensor memory",
+        flops=2 * 32 * 4096 * 4096 * 128)
+    del sg, vg, gg
+
     # config 5: verify 13 checks x 256 probes x [4,512,1024] bf16; probes sharded over ranks
     p0, p1 = shard_range(256, rank, world)
     probes = p1 - p0
@@ -503,6 +515,11 @@ def run_profile_case(args) -> None:
         bl = torch.randn(1024, 8 * 1024 * 16, device=dev, generator=gen)
         hl = torch.zeros(8 * 1024 * 16, device=dev)
         fn = lambda: ops.diag_compose_apply(al, bl, hl)  # noqa: E731
+    elif args.profile_case == "gated":      # (s*g)@v, B=2 H=16 T=K=2048 dv=128 bf16, one gate: 285 MB
+        sg = _randn_bf16((32, 2048 * 2048), gen).view(2, 16, 2048, 2048)
+        vg = _randn_bf16((32, 2048 * 128), gen).view(2, 16, 2048, 128)
+        gg = torch.rand(2048, 2048, device=dev, generator=gen).bfloat16()
+        fn = lambda: ops.gated_contract(sg, gg, vg)  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
         ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
         outp = ref.clone()
@@ -529,7 +546,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose"],
+                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -9,18 +9,23 @@
 //   s: [nb, T, K]   g: [ng, T, K]   v: [nb, K, dv]   o: [nb, T, dv]
 //   gate of batch b = g[(b / g_div) % g_mod]
 //
-// The product s . g is rounded to bf16 (as the reference's elementwise multiply
-// does) and never leaves the SM: scores and gate arrive by TMA in the same
-// 128-byte-swizzled layout, so the multiply is position-wise on the raw bytes
-// and the result, written over the score tile, is the K-major A operand of
-// O += P V_j (V_j read MN-major, fp32 accumulator in tensor memory).  HBM-bound:
-// s is read once (2 bytes per 2*dv flops), the gate usually comes from L2.
+// HBM-bound by its algorithmic bytes (s is read once: 2 bytes per 2*dv flops), but a
+// 128-row CTA pulls three bytes through the L2 fabric for every score byte (scores,
+// gate, and the values every row tile of a batch re-reads): about 12.6 TB/s from L2
+// to the SMs at the measured pace of 0.5 us per stage, which deeper rings, a product
+// kept out of shared memory and overlapped multiply groups all left unchanged.
+// Scores and gate arrive by TMA (16 KiB
+// each per 64-key stage; the gate usually from L2), a thread reads its row of both,
+// and P = bf16(s . g) — rounded as the reference's elementwise multiply rounds it —
+// is written to TENSOR MEMORY and is the A operand of O += P V_j from there; only V_j
+// (MN-major B operand) is read from shared memory by the MMA.  fp32 accumulator in
+// tensor memory.
 //
-// CTA = one 128-row tile of one batch.  Keys stream in 64-column stages
-// (scores 16 KiB + gate 16 KiB + values 16 KiB) through a 4-slot ring.
-// Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
-// warps 2..9 = the multiply / epilogue group.  Rows past T and keys past K are
-// out of range of the per-batch tensor maps: zero on load, clipped on store.
+// CTA = one 128-row tile of one batch; keys stream in 64-column stages (scores
+// 16 KiB + gate 16 KiB + values 16 KiB) through a 4-slot ring.  Roles: warp 0 = TMA producer,
+// warp 1 = MMA issuer and TMEM owner, warps 2..9 = multiply / epilogue group
+// (thread = one row and one half of a stage's keys).  Rows past T and keys past K
+// are out of range of the per-batch tensor maps: zero on load, clipped on store.
 #include "umma.cuh"
 
 namespace cb2 {
@@ -31,14 +36,18 @@ constexpr int kKeys = 64;                     // keys per stage
 constexpr int kStages = 4;
 constexpr int kGcThreads = 320;
 constexpr int kGcCompute = 256;
-constexpr uint32_t kSBytes = kRows * kKeys * 2;          // 16 KiB score (or gate) sub-tile
+constexpr uint32_t kSBytes = kRows * kKeys * 2;          // 16 KiB score sub-tile
 constexpr uint32_t kVHalf = kKeys * 128;                 // 8 KiB: 64 keys x 64 value columns
-constexpr uint32_t kStageBytes = 2 * kSBytes + 2 * kVHalf;   // 48 KiB
+constexpr uint32_t kStageBytes = 2 * kSBytes + 2 * kVHalf;   // 48 KiB: scores, gate, values
 constexpr uint32_t kGcOffOut = kStages * kStageBytes;    // output staging: [128 x 128] bf16
 constexpr uint32_t kGcOffBars = kGcOffOut + umma::kTileBytes;
 constexpr int kGcNumBars = 3 * kStages + 2;
 constexpr uint32_t kGcOffMisc = kGcOffBars + kGcNumBars * 8;
 constexpr uint32_t kGcSmemBytes = kGcOffMisc + 16 + 1024;
+// tensor memory: accumulator in columns 0..127, then one 32-column P buffer per slot
+// (64 keys of bf16, two per 32-bit column)
+constexpr uint32_t kColP = 128;
+constexpr uint32_t kGcTmemCols = 512;
 
 __global__ void __launch_bounds__(kGcThreads, 1)
 gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_g,
@@ -47,7 +56,7 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kGcOffBars);
-  uint64_t* full = bars;                    // [kStages] TMA -> compute group
+  uint64_t* full = bars;                    // [kStages] TMA -> compute group, MMA
   uint64_t* p_ready = bars + kStages;       // [kStages] compute group -> MMA (256 arrivals)
   uint64_t* empty = bars + 2 * kStages;     // [kStages] MMA -> TMA
   uint64_t* acc_ready = bars + 3 * kStages; // last MMA done
@@ -75,7 +84,7 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
   }
   if (warp == 1) {
     __syncwarp();
-    umma::tmem_alloc(s_tmem, 128);
+    umma::tmem_alloc(s_tmem, kGcTmemCols);
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -110,59 +119,64 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
       bool ok = true;
       for (int i = 0; i < nstage && ok; ++i) {
         const int slot = i % kStages, use = i / kStages;
-        ok = mbar_wait_abortable(&p_ready[slot], use & 1, s_abort);
+        ok = mbar_wait_abortable(&full[slot], use & 1, s_abort) &&      // V_j landed
+             mbar_wait_abortable(&p_ready[slot], use & 1, s_abort);     // P_j in tensor memory
         if (!ok) break;
         umma::fence_after_sync();
-        const uint32_t p_addr = ring + slot * kStageBytes;
-        const uint32_t v_addr = p_addr + 2 * kSBytes;
+        const uint32_t v_addr = ring + slot * kStageBytes + 2 * kSBytes;
+        const uint32_t p_addr = tmem + kColP + slot * 32;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          // A: K-major rows of 128 bytes, 8-row groups 1024 B apart, 32 B per k-step.
+          // A: tensor memory, 8 columns per 16-key step.
           // B: MN-major, 16 keys = 2048 B per k-step, 8-key groups 1024 B apart,
           //    value columns 64..127 in the second 8 KiB half.
-          const uint64_t adesc = umma::smem_desc(p_addr + ks * 32u, 16u, 1024u);
           const uint64_t bdesc = umma::smem_desc(v_addr + ks * 2048u, kVHalf, 1024u);
-          umma::mma_bf16(tmem, adesc, bdesc, idesc, i > 0 || ks > 0);
+          umma::mma_bf16_ts(tmem, p_addr + ks * 8, bdesc, idesc, i > 0 || ks > 0);
         }
         umma::mma_commit(&empty[slot]);
       }
       if (ok) umma::mma_commit(acc_ready);
     }
   } else {
-    const int ct = tid - 64;                 // 0..255
+    // thread = (row r of the tile, half of a stage's 64 keys); a warp may only touch
+    // the TMEM lane quarter (warp % 4)
+    const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
     for (int i = 0; i < nstage; ++i) {
       const int slot = i % kStages, use = i / kStages;
       bool ok = mbar_wait_abortable(&full[slot], use & 1, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
-      // P = bf16(s * g): both tiles share one swizzled layout, so the multiply is
-      // position-wise; 1024 16-byte pieces per stage, four per thread.
-      uint4* sp = reinterpret_cast<uint4*>(smem + slot * kStageBytes);
-      const uint4* gp = reinterpret_cast<const uint4*>(smem + slot * kStageBytes + kSBytes);
-      uint4 x[4], y[4];
+      // P = bf16(s * g) for this thread's 32 keys of row r -> 16 packed columns of TMEM
+      // (scores and gate share one swizzled layout; rows of a warp hit distinct banks)
+      const unsigned char* s_tile = smem + slot * kStageBytes;
+      uint4 xs[4], ys[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        x[j] = sp[ct + j * kGcCompute];
-        y[j] = gp[ct + j * kGcCompute];
+        const uint32_t off = umma::tile_chunk_offset(r, half * 32 + j * 8);
+        xs[j] = *reinterpret_cast<const uint4*>(s_tile + off);
+        ys[j] = *reinterpret_cast<const uint4*>(s_tile + kSBytes + off);
       }
+      uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        __nv_bfloat162* xa = reinterpret_cast<__nv_bfloat162*>(&x[j]);
-        const __nv_bfloat162* ya = reinterpret_cast<const __nv_bfloat162*>(&y[j]);
+        uint4 x = xs[j];
+        __nv_bfloat162* xa = reinterpret_cast<__nv_bfloat162*>(&x);
+        const __nv_bfloat162* ya = reinterpret_cast<const __nv_bfloat162*>(&ys[j]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) xa[e] = __hmul2(xa[e], ya[e]);
-        sp[ct + j * kGcCompute] = x[j];
+        w[4 * j] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
       }
-      fence_proxy_async_smem();
+      umma::tmem_st16(lane_base + kColP + slot * 32 + half * 16, w);
+      umma::tmem_wait_st();
+      umma::fence_before_sync();
       mbar_arrive(&p_ready[slot]);
     }
     // epilogue: thread = (row, column half); accumulator -> bf16 -> staged tile -> TMA store
     bool ok = mbar_wait_abortable(acc_ready, 0, s_abort);
     if (__all_sync(0xffffffffu, ok)) {
       umma::fence_after_sync();
-      const int q4 = warp & 3;
-      const int half = (warp - 2) >> 2;
-      const int r = q4 * 32 + lane;
-      const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
       unsigned char* o_tile = smem + kGcOffOut;
       if (half == 0 || wide) {
         uint32_t va[32], vb[32];
@@ -204,7 +218,7 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
   if (tid == 0 && *s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
   if (warp == 1) {
     __syncwarp();
-    umma::tmem_dealloc(tmem, 128);
+    umma::tmem_dealloc(tmem, kGcTmemCols);
   }
 }
 
