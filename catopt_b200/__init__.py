@@ -8,6 +8,8 @@ built by ``python -m catopt_b200.build``); this package is the thin host side:
 * ``verify``     the verify gate (``verify_equiv`` / ``verify_module`` / batched)
 * ``sharding``   the batch x head / batch x channel / probe partition over ranks
 * ``sink``       adapter into catopt's ``Sink.executors`` table (needs catopt)
+* ``gen``        bindings for the ops catopt's generated-kernel tiers mint (scan and
+                 decayed-contraction handlers), in place of its Triton code generation
 
 Importing the package does not load the library; the first call does, and
 raises ``B200Error`` if it is missing — there is no CPU fallback.
