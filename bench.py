@@ -321,6 +321,18 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
         flops=3 * Tt * St)
     del al, bl, hl
 
+    # all prefix maps of 1024 diagonal steps over config 3's state (what the omd executor's
+    # _prefix_scan builds), fp32: a and b read once, both maps written once (4 x 0.54 GB)
+    Tp = 1024
+    ap = torch.sigmoid(4 + 0.5 * torch.randn(Tp, St, device=dev, generator=gen))
+    bp = torch.randn(Tp, St, device=dev, generator=gen)
+    ms = time_steps(lambda: ops.diag_prefix_maps(ap, bp), K, W, world)
+    out["config3_all_prefix_maps_fp32_T1024"] = entry(
+        ms, 8 * Tp, 4 * Tp * St * 4, 1,
+        "one pass: 2 reads + 2 writes of [1024, 8*1024*16] fp32 (2.1 GB > L2); includes the allocation of the two outputs",
+        flops=3 * Tp * St)
+    del ap, bp
+
     # causal online-softmax executor (no config of its own in the benchmark spec), bf16, d=128:
     # a long-sequence case that fills the GPU (268 MB > L2) and a short one (256 CTAs: tail-bound)
     for (Bo, Ho, To) in ((1, 32, 8192), (2, 8, 2048)):

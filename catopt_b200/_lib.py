@@ -60,6 +60,12 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
          C.c_longlong, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p],
     ),
+    "cb2_diag_prefix_maps_scratch_bytes": (C.c_size_t, [C.c_longlong, C.c_longlong, C.c_int]),
+    "cb2_diag_prefix_maps": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
+         C.c_longlong, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p],
+    ),
     "cb2_gated_contract_on_tensor_cores": (
         C.c_int, [C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int],
     ),

@@ -33,6 +33,9 @@ struct Vec<CB2_F32> {
   }
   __device__ static float ld1(const void* p, size_t i) { return __ldcs(static_cast<const float*>(p) + i); }
   __device__ static void st1(void* p, size_t i, float v) { static_cast<float*>(p)[i] = v; }
+  __device__ static void st(void* p, size_t i, const float (&v)[4]) {
+    __stcs(reinterpret_cast<float4*>(static_cast<float*>(p) + i), make_float4(v[0], v[1], v[2], v[3]));
+  }
 };
 template <>
 struct Vec<CB2_BF16> {
@@ -49,6 +52,11 @@ struct Vec<CB2_BF16> {
   }
   __device__ static void st1(void* p, size_t i, float v) {
     static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  }
+  __device__ static void st(void* p, size_t i, const float (&v)[8]) {
+    __stcs(reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p) + i),
+           make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                      pack_bf16x2(v[6], v[7])));
   }
 };
 
@@ -146,6 +154,135 @@ compose_apply_kernel(const float* __restrict__ part_a, const float* __restrict__
   V::st1(out, size_t(c), fmaf(A, V::ld1(h, size_t(c)), B));
 }
 
+// All prefix maps of rows in time order, one pass: Pa[t] = a_t * Pa[t-1], Pb[t] = a_t * Pb[t-1] + b_t
+// (Pa[-1] = 1, Pb[-1] = 0), both written for every step.  A thread owns 16 bytes of the state row
+// and walks the steps with eight steps of loads in flight; fp32 running maps, rounded on store.
+// When the state alone gives too few threads, the steps are cut into segments (blockIdx.y): the
+// segments' total maps come from compose_partial_kernel<CHRONO> first, and a segment starts from
+// the fold of the totals before it instead of the identity (a and b are then read twice).
+template <int DTYPE, bool VEC>
+__global__ void __launch_bounds__(128)
+prefix_maps_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ pa,
+                   void* __restrict__ pb, long long n, long long S, long long a_stride, long long b_stride,
+                   long long seg_len, const float* __restrict__ part_a, const float* __restrict__ part_b) {
+  using V = Vec<DTYPE>;
+  constexpr int E = VEC ? V::kElems : 1;
+  const long long c0 = (blockIdx.x * 128ll + threadIdx.x) * E;
+  if (c0 >= S) return;
+  const long long j0 = blockIdx.y * seg_len;
+  n = j0 + seg_len < n ? j0 + seg_len : n;     // this segment's steps are [j0, n)
+  float A[E], B[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) { A[e] = 1.f; B[e] = 0.f; }
+  for (unsigned sgm = 0; sgm < blockIdx.y; ++sgm) {
+    const size_t i = size_t(sgm) * size_t(S) + size_t(c0);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      B[e] = fmaf(part_a[i + e], B[e], part_b[i + e]);
+      A[e] *= part_a[i + e];
+    }
+  }
+  auto step = [&](const float (&av)[E], const float (&bv)[E], long long j) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      B[e] = fmaf(av[e], B[e], bv[e]);
+      A[e] *= av[e];
+    }
+    const size_t off = size_t(j) * size_t(S) + size_t(c0);
+    if constexpr (VEC) {
+      V::st(pa, off, A);
+      V::st(pb, off, B);
+    } else {
+      V::st1(pa, off, A[0]);
+      V::st1(pb, off, B[0]);
+    }
+  };
+  long long j = j0;
+  for (; j + kUnroll <= n; j += kUnroll) {
+    float av[kUnroll][E], bv[kUnroll][E];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t offa = size_t(j + u) * size_t(a_stride) + size_t(c0);
+      const size_t offb = size_t(j + u) * size_t(b_stride) + size_t(c0);
+      if constexpr (VEC) {
+        V::ld(a, offa, av[u]);
+        V::ld(b, offb, bv[u]);
+      } else {
+        av[u][0] = V::ld1(a, offa);
+        bv[u][0] = V::ld1(b, offb);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) step(av[u], bv[u], j + u);
+  }
+  for (; j < n; ++j) {
+    float av[E], bv[E];
+    const size_t offa = size_t(j) * size_t(a_stride) + size_t(c0);
+    const size_t offb = size_t(j) * size_t(b_stride) + size_t(c0);
+    if constexpr (VEC) {
+      V::ld(a, offa, av);
+      V::ld(b, offb, bv);
+    } else {
+      av[0] = V::ld1(a, offa);
+      bv[0] = V::ld1(b, offb);
+    }
+    step(av, bv, j);
+  }
+}
+
+// Segments for the all-prefix pass: enough CTAs of 128 threads for about eight per SM,
+// at least 64 steps per segment; 1 = plain single pass.  Segments cost a second read of a
+// and b (6 units of traffic instead of 4), which pays only while one pass would leave most
+// SMs idle: measured, 64 CTAs stream 3.4 TB/s in one pass and 4.0 TB/s segmented, 128 CTAs
+// 4.05 against 3.8.
+int prefix_segments(long long n, long long S, int elems_per_thread) {
+  long long ctas = (S / elems_per_thread + 127) / 128;
+  if (ctas < 1) ctas = 1;
+  if (ctas >= 96) return 1;
+  long long want = (8 * 148 + ctas - 1) / ctas;
+  const long long most = n / 64 > 0 ? n / 64 : 1;
+  if (want > most) want = most;
+  if (want < 1) want = 1;
+  if (want > 65535) want = 65535;
+  return int(want);
+}
+
+template <int DTYPE>
+int run_prefix(const void* a, const void* b, void* pa, void* pb, long long n, long long S, long long a_stride,
+               long long b_stride, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  using V = Vec<DTYPE>;
+  const bool vec = S % V::kElems == 0 && aligned16(a) && aligned16(b) && aligned16(pa) && aligned16(pb);
+  const int E = vec ? V::kElems : 1;
+  const long long threads = S / E;
+  const long long blocks = (threads + 127) / 128;
+  if (blocks > 0x7fffffffll) return CB2_BAD_SHAPE;
+  int nseg = prefix_segments(n, S, E);
+  if (nseg > 1 && (!scratch || !aligned16(scratch) || scratch_bytes < size_t(2) * nseg * size_t(S) * sizeof(float)))
+    nseg = 1;   // no room for the segment totals: one pass over all steps per thread
+  const long long seg_len = (n + nseg - 1) / nseg;
+  float* part_a = static_cast<float*>(scratch);
+  float* part_b = nseg > 1 ? part_a + size_t(nseg) * size_t(S) : nullptr;
+  if (nseg > 1) {
+    const dim3 pgrid{unsigned((threads + kComposeThreads - 1) / kComposeThreads), unsigned(nseg), 1u};
+    if (vec)
+      compose_partial_kernel<DTYPE, true, true><<<pgrid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, part_a,
+                                                                                 part_b, a_stride, b_stride);
+    else
+      compose_partial_kernel<DTYPE, false, true><<<pgrid, kComposeThreads, 0, st>>>(a, b, n, S, seg_len, part_a,
+                                                                                  part_b, a_stride, b_stride);
+    CB2_LAUNCH_CHECK();
+  }
+  const dim3 grid{unsigned(blocks), unsigned(nseg), 1u};
+  if (vec)
+    prefix_maps_kernel<DTYPE, true><<<grid, 128, 0, st>>>(a, b, pa, pb, n, S, a_stride, b_stride, seg_len,
+                                                          part_a, part_b);
+  else
+    prefix_maps_kernel<DTYPE, false><<<grid, 128, 0, st>>>(a, b, pa, pb, n, S, a_stride, b_stride, seg_len,
+                                                           part_a, part_b);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
 int pick_segments(long long n, long long S, int elems_per_thread) {
   long long ctas = (S / elems_per_thread + kComposeThreads - 1) / kComposeThreads;
   if (ctas < 1) ctas = 1;
@@ -236,5 +373,37 @@ extern "C" int cb2_diag_fold_apply(const void* a_rows, const void* b_rows, const
   if (dtype == CB2_BF16)
     return cb2::run<CB2_BF16>(a_rows, b_rows, h, out, n, S, scratch, scratch_bytes, st, true, a_step_stride,
                               b_step_stride);
+  return CB2_UNSUPPORTED_DTYPE;
+}
+
+// All prefix maps (Pa[t], Pb[t]) of rows in time order, h_t = Pa[t]*h_0 + Pb[t]: what
+// `BatchedOmdModule._prefix_scan` (catopt_carriers/omd_lower.py:771-824) builds from blocks of
+// sqrt(T) serial compose steps plus a carry fold; here one pass that reads a and b once and
+// writes both maps once.  a_rows, b_rows: [n, S] (step stride S, or 0 for a shared row);
+// pa, pb: [n, S], element type `dtype`; fp32 running maps.  With scratch
+// (cb2_diag_prefix_maps_scratch_bytes) a state too small to fill the GPU is made up for by cutting
+// the steps into segments (totals first, then every segment from its carry-in).
+extern "C" size_t cb2_diag_prefix_maps_scratch_bytes(long long n, long long S, int dtype) {
+  if (n <= 0 || S <= 0) return 0;
+  const int ve = dtype == CB2_BF16 ? 8 : 4;
+  const int a = cb2::prefix_segments(n, S, 1), b = cb2::prefix_segments(n, S, ve);
+  const int m = a > b ? a : b;
+  return m > 1 ? size_t(2) * m * size_t(S) * sizeof(float) : 0;
+}
+
+extern "C" int cb2_diag_prefix_maps(const void* a_rows, const void* b_rows, void* pa, void* pb, long long n,
+                                    long long S, long long a_step_stride, long long b_step_stride,
+                                    int dtype, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!a_rows || !b_rows || !pa || !pb) return CB2_NULL_PTR;
+  if (n <= 0 || S <= 0 || S > (1ll << 40) / n) return CB2_BAD_SHAPE;
+  if ((a_step_stride != 0 && a_step_stride != S) || (b_step_stride != 0 && b_step_stride != S))
+    return CB2_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CB2_F32)
+    return cb2::run_prefix<CB2_F32>(a_rows, b_rows, pa, pb, n, S, a_step_stride, b_step_stride, scratch,
+                                    scratch_bytes, st);
+  if (dtype == CB2_BF16)
+    return cb2::run_prefix<CB2_BF16>(a_rows, b_rows, pa, pb, n, S, a_step_stride, b_step_stride, scratch,
+                                     scratch_bytes, st);
   return CB2_UNSUPPORTED_DTYPE;
 }

@@ -338,29 +338,41 @@ def diag_prefix_maps(a_seq: torch.Tensor, b_seq: torch.Tensor):
     ``h_t = Pa[t]*h_0 + Pb[t]``, i.e. ``Pa[t] = a_t ... a_0`` and ``Pb`` the scan
     of the offsets — what the reference's ``BatchedOmdModule._prefix_scan``
     (catopt_carriers/omd_lower.py:771-824) builds from blocked compose steps.
-    Two passes of ``cb2_diag_scan_fwd`` over the flattened state (channels =
-    state elements, N = 1, b = c = 1): offsets with ``h_0 = 0`` give ``Pb``, zero
-    offsets with ``h_0 = 1`` give ``Pa``.  Returns ``None`` when the kernel cannot
-    take the case (dtype other than float32/bfloat16, or a state whose byte size
-    is not a multiple of 16) so the caller keeps its own scan.
+    One pass of ``cb2_diag_prefix_maps``: both operands read once, both maps written
+    once (a small state is made up for by cutting the steps into segments: totals
+    first, then every segment from its carry-in); an operand shared by every step is
+    read in place (step stride 0).  Returns ``None`` when the kernel
+    cannot take the case (dtype other than float32/bfloat16, or no steps) so the
+    caller keeps its own scan.
     """
-    require_cuda(a_seq, b_seq)
+    for t in (a_seq, b_seq):      # any layout: broadcast (expanded) operands are welcome
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise B200Error("catopt_b200 executors take CUDA tensors only (no CPU fallback)")
     state_shape = torch.broadcast_shapes(a_seq.shape[1:], b_seq.shape[1:])
-    T, D = a_seq.shape[0], 1
+    T, S = a_seq.shape[0], 1
     for sdim in state_shape:
-        D *= sdim
+        S *= sdim
     dt = a_seq.dtype
-    esz = 2 if dt == torch.bfloat16 else 4
-    if dt not in (torch.float32, torch.bfloat16) or b_seq.dtype != dt or (D * esz) % 16 or T == 0 \
-            or b_seq.shape[0] != T:
+    if dt not in (torch.float32, torch.bfloat16) or b_seq.dtype != dt or T == 0 or S == 0 or b_seq.shape[0] != T:
         return None
-    a = a_seq.expand(T, *state_shape).reshape(1, T, D, 1).contiguous()
-    u = b_seq.expand(T, *state_shape).reshape(1, T, D).contiguous()
-    ones = torch.ones(D, 1, dtype=dt, device=a.device)
-    pb = diag_scan_fwd(a, u, ones, ones, None)
-    h1 = torch.ones(1, D, 1, dtype=torch.float32, device=a.device)
-    pa = diag_scan_fwd(a, torch.zeros_like(u), ones, ones, h1)
-    return pa.reshape(T, *state_shape), pb.reshape(T, *state_shape)
+
+    def rows(x: torch.Tensor) -> tuple[torch.Tensor, int]:
+        x = x.expand(T, *state_shape)
+        if T > 1 and x.stride(0) == 0:          # one row shared by every step
+            return x[0].reshape(S).contiguous(), 0
+        return x.reshape(T, S).contiguous(), S
+
+    a, a_stride = rows(a_seq)
+    b, b_stride = rows(b_seq)
+    pa = torch.empty(T, *state_shape, dtype=dt, device=a.device)
+    pb = torch.empty(T, *state_shape, dtype=dt, device=a.device)
+    lib = _lib.load()
+    need = lib.cb2_diag_prefix_maps_scratch_bytes(T, S, dtype_code(dt))
+    scratch = _scratch_buf("prefix", need, a.device)
+    rc = lib.cb2_diag_prefix_maps(a.data_ptr(), b.data_ptr(), pa.data_ptr(), pb.data_ptr(), T, S, a_stride,
+                                  b_stride, dtype_code(dt), _ptr(scratch), need, stream_ptr())
+    check(rc, "cb2_diag_prefix_maps")
+    return pa, pb
 
 
 def diag_fold_apply(a_rows: torch.Tensor, b_rows: torch.Tensor, h: torch.Tensor) -> torch.Tensor:

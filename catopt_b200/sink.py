@@ -29,7 +29,7 @@ order.  ``B200Sink`` puts six B200 specs in front of the torch ones:
   ``cb2_diag_compose_apply`` (one pass over the stacked leaves).
 * ``b200_omd`` — deferred-affine attention ``omd_apply(<omd tree>, h)``: the
   reference's ``BatchedOmdModule`` with its all-prefix scan of the diagonal step
-  maps (``_prefix_scan``) running in ``cb2_diag_scan_fwd``.
+  maps (``_prefix_scan``) running in ``cb2_diag_prefix_maps`` (one pass).
 * ``b200_linear_chain`` — ``linear(x, <matmul tree of weight Params>)``, the
   term ``assoc_linear`` leaves behind for a chain of bias-free Linear maps
   (catopt_core/laws/tensor.py:1293-1300) before ``_fold_weight_chains``
@@ -783,11 +783,10 @@ def _make_omd_module():
     class B200OmdModule(BatchedOmdModule):
         """``BatchedOmdModule`` (omd_lower.py:560-1020) with the all-prefix scan of
         the scanned values' step maps (``_prefix_scan``, omd_lower.py:771-824: blocks
-        of sqrt(T) compose steps) replaced by ``cb2_diag_scan_fwd``, which streams
-        the sequence once per map component and emits every prefix.  Term analysis,
+        of sqrt(T) compose steps) replaced by ``cb2_diag_prefix_maps``, which reads
+        the step maps once and writes every prefix of both components.  Term analysis,
         the omd tree reduction and every other path stay the reference's own code;
-        dense maps, fp64 tensors and states the kernel cannot address keep the
-        reference's scan on the same device."""
+        dense maps and fp64 tensors keep the reference's scan on the same device."""
 
         def __init__(self, ir: IR, param_values: dict | None = None) -> None:
             super().__init__(ir, param_values)

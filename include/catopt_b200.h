@@ -166,8 +166,8 @@ int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
  * One step is the reference's `applyd(aff_diag(a_t, b*x_t), h)`
  * (torch_bridge.py:1895-1900); the whole sequence replaces the level-batched
  * reduction of `BatchedScanModule._forward_impl`
- * (packages/catopt-carriers/src/catopt_carriers/scan_lower.py:569-698) and
- * the all-prefix form `BatchedOmdModule._prefix_scan` (omd_lower.py:771-824).
+ * (packages/catopt-carriers/src/catopt_carriers/scan_lower.py:569-698) when
+ * every step's readout is wanted (the prefix maps themselves: cb2_diag_prefix_maps).
  *
  * a: [B,T,D,N] (a_bcast_n == 0) or [B,T,D] shared over n (a_bcast_n == 1);
  * x,y: [B,T,D]; b,c: [D,N]; h0 (may be NULL = zeros) and hT (may be NULL):
@@ -209,6 +209,23 @@ int cb2_diag_fold_apply(const void* a_rows, const void* b_rows, const void* h, v
                         long long n, long long S, long long a_step_stride,
                         long long b_step_stride, int dtype, void* scratch,
                         size_t scratch_bytes, void* stream);
+
+/* All prefix maps of rows in time order: pa[t] = a_t * ... * a_0 and pb[t] with
+ * h_t = pa[t]*h_0 + pb[t] for every t, the all-prefix scan of
+ * `BatchedOmdModule._prefix_scan` (packages/catopt-carriers/src/catopt_carriers/
+ * omd_lower.py:771-824: blocks of sqrt(T) serial compose steps, a carry fold over
+ * the block totals and one batched compose) in one pass that reads a and b once
+ * and writes both maps once.  a_rows, b_rows: [n,S] with the step strides of
+ * cb2_diag_fold_apply; pa, pb: [n,S]; element type `dtype`, fp32 running maps.
+ * scratch (cb2_diag_prefix_maps_scratch_bytes bytes, 16-byte aligned, may be
+ * NULL): when the state alone cannot fill the GPU the steps are cut into
+ * segments whose total maps are computed first (in scratch), after which every
+ * segment runs from its carry-in; without scratch each thread walks all steps. */
+size_t cb2_diag_prefix_maps_scratch_bytes(long long n, long long S, int dtype);
+int cb2_diag_prefix_maps(const void* a_rows, const void* b_rows, void* pa, void* pb,
+                         long long n, long long S, long long a_step_stride,
+                         long long b_step_stride, int dtype, void* scratch,
+                         size_t scratch_bytes, void* stream);
 
 /* -------------------------------------------------------------------------
  * Gated contraction  o[b] = (s[b] * g[gate(b)]) @ v[b] :  the body of the

@@ -919,3 +919,33 @@ def test_seq_fold_equals_product_order_fold_at_width(dev):
     shared = ops.diag_fold_apply(a[0], b, h)
     full = ops.diag_fold_apply(a[0].expand(n, S).contiguous(), b, h)
     assert torch.equal(shared, full)
+
+
+@pytest.mark.parametrize("dtype,T,state", [(torch.float32, 700, (4, 16)), (torch.float32, 9, (7,)),
+                                           (torch.bfloat16, 130, (3, 40)), (torch.bfloat16, 33, (5,))])
+def test_diag_prefix_maps_one_pass_shapes(dev, dtype, T, state):
+    """Vector and scalar layouts, fp32 and bf16, step counts off the unroll grid; the last
+    prefix is the whole fold (cb2_diag_fold_apply) and a shared decay row is read in place."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(8)
+    A = torch.sigmoid(2 + torch.randn(T, *state, generator=g)).to(dtype)
+    Bv = torch.randn(T, *state, generator=g).to(dtype)
+    pa, pb = ops.diag_prefix_maps(A.to(dev), Bv.to(dev))
+    # exact recurrence in fp64 on the stored values
+    wa, wb = torch.empty(T, *state, dtype=torch.float64), torch.empty(T, *state, dtype=torch.float64)
+    ca, cb = torch.ones(state, dtype=torch.float64), torch.zeros(state, dtype=torch.float64)
+    for t in range(T):
+        cb = A[t].double() * cb + Bv[t].double()
+        ca = A[t].double() * ca
+        wa[t], wb[t] = ca, cb
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert pa.dtype == dtype and pa.shape == wa.shape
+    assert rel_to_max(pa, wa) <= tol and rel_to_max(pb, wb) <= tol
+    h = torch.randn(state, generator=g).to(dtype)
+    last = ops.diag_fold_apply(A.to(dev), Bv.to(dev), h.to(dev))
+    want = wa[-1] * h.double() + wb[-1]
+    assert rel_to_max(last, want) <= tol
+    sa, sb = ops.diag_prefix_maps(A[:1].expand(T, *state).to(dev).contiguous()[:1].expand(T, *state), Bv.to(dev))
+    fa, fb = ops.diag_prefix_maps(A[:1].expand(T, *state).contiguous().to(dev), Bv.to(dev))
+    assert torch.equal(sa, fa) and torch.equal(sb, fb)
