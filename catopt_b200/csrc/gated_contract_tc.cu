@@ -98,32 +98,16 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
       umma::tma_prefetch_desc(&map_v);
       umma::tma_prefetch_desc(&map_o);
       const uint32_t bytes = 2 * kSBytes + (wide ? 2 : 1) * kVHalf;
-      // Stages are issued two at a time, scores first: the second stage's score box covers
-      // the next 128 bytes of the same 128 rows, and requests that reach the memory
-      // controller together can share one opening of a DRAM page.
-      bool ok = true;
-      for (int i = 0; i < nstage && ok; i += 2) {
-        const int cnt = i + 1 < nstage ? 2 : 1;
-        for (int u = 0; u < cnt && ok; ++u) {
-          const int slot = (i + u) % kStages, use = (i + u) / kStages;
-          if (use > 0) ok = mbar_wait_abortable(&empty[slot], (use - 1) & 1, s_abort);
-          if (ok) mbar_arrive_expect_tx(&full[slot], bytes);
-        }
-        if (!ok) break;
-        for (int u = 0; u < cnt; ++u) {
-          const int slot = (i + u) % kStages;
-          umma::tma_load_3d(smem + slot * kStageBytes, &map_s, (i + u) * kKeys, row0, b, &full[slot]);
-        }
-        for (int u = 0; u < cnt; ++u) {
-          const int slot = (i + u) % kStages;
-          umma::tma_load_3d(smem + slot * kStageBytes + kSBytes, &map_g, (i + u) * kKeys, row0, gb, &full[slot]);
-        }
-        for (int u = 0; u < cnt; ++u) {
-          const int slot = (i + u) % kStages, k0 = (i + u) * kKeys;
-          unsigned char* dst = smem + slot * kStageBytes + 2 * kSBytes;
-          umma::tma_load_3d(dst, &map_v, 0, k0, b, &full[slot]);
-          if (wide) umma::tma_load_3d(dst + kVHalf, &map_v, 64, k0, b, &full[slot]);
-        }
+      for (int i = 0; i < nstage; ++i) {
+        const int slot = i % kStages, use = i / kStages;
+        if (use > 0 && !mbar_wait_abortable(&empty[slot], (use - 1) & 1, s_abort)) break;
+        unsigned char* dst = smem + slot * kStageBytes;
+        const int k0 = i * kKeys;
+        mbar_arrive_expect_tx(&full[slot], bytes);
+        umma::tma_load_3d(dst, &map_s, k0, row0, b, &full[slot]);
+        umma::tma_load_3d(dst + kSBytes, &map_g, k0, row0, gb, &full[slot]);
+        umma::tma_load_3d(dst + 2 * kSBytes, &map_v, 0, k0, b, &full[slot]);
+        if (wide) umma::tma_load_3d(dst + 2 * kSBytes + kVHalf, &map_v, 64, k0, b, &full[slot]);
       }
     }
   } else if (warp == 1) {
