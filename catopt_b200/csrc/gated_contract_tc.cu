@@ -22,7 +22,11 @@
 // tensor memory.
 //
 // CTA = one 128-row tile of one batch; keys stream in 64-column stages (scores
-// 16 KiB + gate 16 KiB + values 16 KiB) through a 4-slot ring.  Roles: warp 0 = TMA producer,
+// 16 KiB + gate 16 KiB + values 16 KiB) through a 2-slot ring, and two CTAs share an
+// SM (97 KiB of shared memory and 256 TMEM columns each), so one CTA's ring fill and
+// output store run under the other's steady state (measured: 4 slots x 1 CTA 247 us,
+// 2 slots x 2 CTAs 238 us, 3 slots x 1 CTA 272 us on B=2 H=16 T=K=4096).
+// Roles: warp 0 = TMA producer,
 // warp 1 = MMA issuer and TMEM owner, warps 2..9 = multiply / epilogue group
 // (thread = one row and one half of a stage's keys).  Rows past T and keys past K
 // are out of range of the per-batch tensor maps: zero on load, clipped on store.
@@ -47,23 +51,27 @@ __device__ long long g_gc_timeline[64][5];
 
 constexpr int kRows = 128;                    // query rows per CTA
 constexpr int kKeys = 64;                     // keys per stage
-constexpr int kStages = 4;
+#ifndef CB2_GC_STAGES
+#define CB2_GC_STAGES 2
+#define CB2_GC_CTAS_PER_SM 2
+#endif
+constexpr int kStages = CB2_GC_STAGES;
 constexpr int kGcThreads = 320;
 constexpr int kGcCompute = 256;
 constexpr uint32_t kSBytes = kRows * kKeys * 2;          // 16 KiB score sub-tile
 constexpr uint32_t kVHalf = kKeys * 128;                 // 8 KiB: 64 keys x 64 value columns
 constexpr uint32_t kStageBytes = 2 * kSBytes + 2 * kVHalf;   // 48 KiB: scores, gate, values
-constexpr uint32_t kGcOffOut = kStages * kStageBytes;    // output staging: [128 x 128] bf16
-constexpr uint32_t kGcOffBars = kGcOffOut + umma::kTileBytes;
+constexpr uint32_t kGcOffOut = 0;    // output staging [128 x 128] bf16: over slot 0 of the ring, idle by then
+constexpr uint32_t kGcOffBars = kStages * kStageBytes;
 constexpr int kGcNumBars = 3 * kStages + 2;
 constexpr uint32_t kGcOffMisc = kGcOffBars + kGcNumBars * 8;
 constexpr uint32_t kGcSmemBytes = kGcOffMisc + 16 + 1024;
 // tensor memory: accumulator in columns 0..127, then one 32-column P buffer per slot
 // (64 keys of bf16, two per 32-bit column)
 constexpr uint32_t kColP = 128;
-constexpr uint32_t kGcTmemCols = 512;
+constexpr uint32_t kGcTmemCols = 256;
 
-__global__ void __launch_bounds__(kGcThreads, 1)
+__global__ void __launch_bounds__(kGcThreads, CB2_GC_CTAS_PER_SM)
 gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_g,
                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                          int K, int dv, int row_tiles, int g_div, int g_mod, int* dev_status) {
