@@ -949,3 +949,29 @@ def test_diag_prefix_maps_one_pass_shapes(dev, dtype, T, state):
     sa, sb = ops.diag_prefix_maps(A[:1].expand(T, *state).to(dev).contiguous()[:1].expand(T, *state), Bv.to(dev))
     fa, fb = ops.diag_prefix_maps(A[:1].expand(T, *state).contiguous().to(dev), Bv.to(dev))
     assert torch.equal(sa, fa) and torch.equal(sb, fb)
+
+
+def test_gated_contract_past_two_billion_scores(dev):
+    """2^31 + 2^27 score elements (4.6 GB): batch and row offsets must not wrap.  The last batch,
+    computed alone, gives the same bits as inside the large call, and scaling one batch's values
+    scales only that batch's output (linearity in v)."""
+    from catopt_b200 import ops
+
+    nb, T, K, dv = 17, 8192, 16384, 128
+    g = torch.Generator(device=dev).manual_seed(13)
+    s = torch.empty(nb, T, K, dtype=torch.bfloat16, device=dev)
+    for b in range(nb):
+        s[b].copy_(torch.randn(T, K, device=dev, generator=g))
+    gate = torch.rand(T, K, device=dev, generator=g).bfloat16()
+    v = torch.randn(nb, K, dv, device=dev, generator=g).bfloat16()
+    assert s.numel() > 2 ** 31
+    out = ops.gated_contract(s, gate, v)
+    alone = ops.gated_contract(s[-1:], gate, v[-1:])
+    assert torch.equal(out[-1], alone[0])
+    v2 = v.clone()
+    v2[3] *= 2
+    out2 = ops.gated_contract(s, gate, v2)
+    assert torch.equal(out2[3], out[3] * 2) and torch.equal(out2[4], out[4]) and torch.equal(out2[0], out[0])
+    ref_rows = ((s[-1, -64:] * gate[-64:]).double() @ v[-1].double())
+    assert rel_to_max(out[-1, -64:], ref_rows) <= 4e-3
+    ops.check_device_status(dev)
