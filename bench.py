@@ -11,7 +11,9 @@ is one (batch, time) position; a step is one pass of the executor over the
 rank's shard.  ``value`` is measured with inputs resident in HBM, ``e2e`` through
 the public module with pinned host buffers copied in and the result copied out
 inside the timed region.  ``kernels`` carries the same measurement for the other
-lowered executors (configs 1, 2, 3, 5).  One JSON line on stdout (rank 0).
+lowered executors (configs 1, 2, 3, 5, each with a ``cpu_baseline`` of its own: the
+reference's algorithm on the host cores over a bounded sample) and for the kernels
+without a config of their own.  One JSON line on stdout (rank 0).
 """
 from __future__ import annotations
 
@@ -178,6 +180,46 @@ def cpu_reference_step_fn(heads: int = 1):
 
     tokens = heads * T / H  # token-equivalents: a token is one (b,t) position over all 32 heads
     return step, tokens
+
+
+def cpu_extras(cores: int) -> dict:
+    """The reference's CPU algorithm (oracle port, all host threads) on a bounded sample of the
+    other configs, keyed like ``bench_extras``'s entries; a few seconds in total."""
+    from oracle import oracle
+
+    g = torch.Generator().manual_seed(99)
+    out = {}
+
+    def entry(step, tokens, passes, sample):
+        ms = time_cpu(step, passes, 1)
+        return {"value": tokens * passes / (ms / 1e3), "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": sample}
+
+    with torch.no_grad():
+        # config 1: the folded module's forward, linear(x, W_folded)
+        wf = torch.randn(512, 512, generator=g) / math.sqrt(512)
+        x = torch.randn(64, 512, generator=g)
+        out["config1_folded_chain_fp32"] = entry(lambda: oracle.linear(x, wf), 64, 200,
+                                                 "200 forwards of the folded module at full size")
+        # config 2 at full size: the pairwise-chunked executor algorithm
+        q, k, v = (torch.randn(2, 4, 1024, 64, generator=g) / 8 for _ in range(3))
+        g2 = torch.tensor(0.97)
+        out["config2_decayed_fp32"] = entry(lambda: oracle.decayed_chunked_pairwise(q, k, v, g2, 64, 1.0),
+                                            2 * 1024, 5, "5 passes at full size")
+        # config 3: one of the 8 batch entries, serial fold of the reference's bindings with readout
+        a = torch.sigmoid(4 + 0.5 * torch.randn(1, 4096, 1024, 16, generator=g)).bfloat16()
+        xs = torch.randn(1, 4096, 1024, generator=g).bfloat16()
+        b3 = (torch.randn(1024, 16, generator=g) / 4).bfloat16()
+        c3 = (torch.randn(1024, 16, generator=g) / 4).bfloat16()
+        out["config3_diag_scan_bf16"] = entry(lambda: oracle.diag_scan_serial(a, xs, b3, c3), 4096, 1,
+                                              "1 pass over 1 of the 8 batch entries (T=4096, D=1024, N=16)")
+        # config 5: one check of 4 probes (the reference's four eager passes per pair)
+        ref = torch.randn(4, 4 * 512 * 1024, generator=g).bfloat16()
+        outp = (ref.float() * 1.003).bfloat16()
+        out["config5_verify_bf16"] = entry(
+            lambda: [oracle.verify_pair(ref[i], outp[i], rtol=2e-2) for i in range(4)], 4 * 4 * 512, 3,
+            "3 passes over 1 check x 4 probes of [4,512,1024] bf16 (of 13 x 256)")
+    return out
 
 
 def time_cpu(step, steps: int, warmup: int) -> float:
@@ -461,6 +503,10 @@ def run_ours(args) -> None:
         cpu = {"value": ctok * 3 / (cms / 1e3), "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": "3 timed passes over 4 of 512 (batch,head) slices of config 4, fp32 on "
                          "bf16-rounded inputs, the reference's pairwise-chunked algorithm"}
+        if extras:
+            for name, cb in cpu_extras(cores).items():
+                if name in extras:
+                    extras[name]["cpu_baseline"] = cb
     if rank != 0:
         return
     line = {
