@@ -578,6 +578,10 @@ def run_profile_case(args) -> None:
         vg = _randn_bf16((32, 2048 * 128), gen).view(2, 16, 2048, 128)
         gg = torch.rand(2048, 2048, device=dev, generator=gen).bfloat16()
         fn = lambda: ops.gated_contract(sg, gg, vg)  # noqa: E731
+    elif args.profile_case == "prefix":     # all prefix maps of 256 steps over config 3's state, fp32: 537 MB
+        ap_ = torch.sigmoid(4 + 0.5 * torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen))
+        bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
+        fn = lambda: ops.diag_prefix_maps(ap_, bp_)  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
         ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
         outp = ref.clone()
@@ -604,7 +608,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated"],
+                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
