@@ -312,7 +312,20 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     out["folded_chain_fp32_R4096"] = entry(ms, 4096, (512 * 512 + 2 * 4096 * 512) * 4, 1,
                                            "reference's published cell k8_d512_R4096",
                                            flops=2 * 4096 * 512 * 512)
-    del ws, x4, y4
+    # a wider folded chain (2048 -> 2048, R = 16384): the reduction is cut into four accumulator segments
+    xw = torch.randn(16384, 2048, device=dev, generator=gen)
+    ww = torch.randn(2048, 2048, device=dev, generator=gen) / math.sqrt(2048)
+    yw = torch.empty(16384, 2048, device=dev)
+    ms = time_steps(lambda: ops.linear_f32(xw, ww, out=yw), K, W, world)
+    e = entry(ms, 16384, (2048 * 2048 + 2 * 16384 * 2048) * 4, 2,
+              "3xTF32 tcgen05, four 512-deep accumulator segments added in fp32 (285 MB > L2); fp32-equivalent "
+              "FLOPs against a third of the bf16 burst peak's TF32 half (three passes)",
+              flops=2 * 16384 * 2048 * 2048)
+    tf32_equiv_peak = pk["bf16_tflops"] / 2 / 3
+    e["roofline"] = {"bound": "tensor", "achieved": e["tflops"], "peak": tf32_equiv_peak, "unit": "TFLOP/s",
+                     "frac": e["tflops"] / tf32_equiv_peak, "traffic": None}
+    out["folded_chain_fp32_R16384_2048x2048"] = e
+    del ws, x4, y4, xw, ww, yw
 
     # config 2: B=2 H=4 T=1024 d=64 fp32, gamma 0.97, chunk 64
     q, k, v = (torch.randn(2, 4, 1024, 64, device=dev, generator=gen) / 8 for _ in range(3))

@@ -313,7 +313,7 @@ extern "C" size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_f
   // refused, and the call works without it.
   // The tensor-core path (large R) needs scratch for w split into its TF32 hi/lo
   // parts; without it the call runs on the FMA pipes.
-  if (R >= 256 && in_features <= 1024 && in_features % 4 == 0 && out_features % 4 == 0)
+  if (R >= 256 && in_features % 4 == 0 && out_features % 4 == 0)
     return cb2::linear_tf32x3_scratch_bytes(in_features, out_features);
   const int splits = cb2::pick_splits(R, out_features, in_features);
   return splits > 1 ? size_t(8) * R * out_features * sizeof(float) : 0;

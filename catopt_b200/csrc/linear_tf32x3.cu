@@ -46,6 +46,13 @@ constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColX = 256;                        // x slots: 64 columns per stage
+// The tensor-core accumulator adds with truncation, which shrinks a sum by a factor that grows with
+// the number of additions (measured rel-err 3e-6 at 512 products per output, 5e-6 at 1024, 1.1e-5 at
+// 2048).  A tensor-memory accumulator therefore takes at most kSegBlocks 32-deep k-blocks; a deeper
+// reduction is cut into segments of half that (512 products) whose sums the epilogue adds in fp32
+// (the first segment stores y, the others add to it), which keeps the error at the 512-deep level
+// whatever the depth.
+constexpr int kSegBlocks = 32;
 #ifndef CB2_LIN_PROBE
 #define CB2_LIN_PROBE 0   // tuning builds only: 1 = skip the MMAs, 2 = skip the split arithmetic and TMEM stores
 #endif
@@ -138,6 +145,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nkb = (n_in + 31) / 32;
+  const int seg = nkb <= kSegBlocks ? kSegBlocks : kSegBlocks / 2;   // k-blocks per accumulator
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -186,28 +194,31 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       constexpr uint32_t idesc = instr_desc_tf32(128, 128);
       int it = 0, tl = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++tl) {
-        const int buf = tl & 1, use = tl >> 1;
-        if (use > 0 && !mbar_wait_abortable(&acc_empty[buf], (use - 1) & 1, s_abort)) break;
-        umma::fence_after_sync();
-        const uint32_t acc = tmem + buf * 128u;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % kStages;
-          if (!mbar_wait_abortable(&split[s], (it / kStages) & 1, s_abort)) { ok = false; break; }
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        for (int kb0 = 0; ok && kb0 < nkb; kb0 += seg, ++tl) {
+          const int buf = tl & 1, use = tl >> 1;
+          if (use > 0 && !mbar_wait_abortable(&acc_empty[buf], (use - 1) & 1, s_abort)) { ok = false; break; }
           umma::fence_after_sync();
-          const uint32_t wbase = smem_u32(smem + s * kStageB + kTileB);
-          const uint32_t xh = tmem + kColX + s * 64u, xl = xh + 32u;
+          const uint32_t acc = tmem + buf * 128u;
+          const int kb1 = min(nkb, kb0 + seg);
+          for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait_abortable(&split[s], (it / kStages) & 1, s_abort)) { ok = false; break; }
+            umma::fence_after_sync();
+            const uint32_t wbase = smem_u32(smem + s * kStageB + kTileB);
+            const uint32_t xh = tmem + kColX + s * 64u, xl = xh + 32u;
 #pragma unroll
-          for (int ks = 0; ks < (CB2_LIN_PROBE == 1 ? 0 : 4); ++ks) {
-            const uint64_t wh = umma::smem_desc(wbase + ks * 32u, 16u, 1024u);
-            const uint64_t wl = umma::smem_desc(wbase + kTileB + ks * 32u, 16u, 1024u);
-            mma_tf32_ts(acc, xl + ks * 8u, wh, idesc, (kb > 0) || (ks > 0));   // small terms first
-            mma_tf32_ts(acc, xh + ks * 8u, wl, idesc, true);
-            mma_tf32_ts(acc, xh + ks * 8u, wh, idesc, true);
+            for (int ks = 0; ks < (CB2_LIN_PROBE == 1 ? 0 : 4); ++ks) {
+              const uint64_t wh = umma::smem_desc(wbase + ks * 32u, 16u, 1024u);
+              const uint64_t wl = umma::smem_desc(wbase + kTileB + ks * 32u, 16u, 1024u);
+              mma_tf32_ts(acc, xl + ks * 8u, wh, idesc, (kb > kb0) || (ks > 0));   // small terms first
+              mma_tf32_ts(acc, xh + ks * 8u, wl, idesc, true);
+              mma_tf32_ts(acc, xh + ks * 8u, wh, idesc, true);
+            }
+            umma::mma_commit(&empty[s]);
           }
-          umma::mma_commit(&empty[s]);
+          if (ok) umma::mma_commit(&acc_full[buf]);
         }
-        if (ok) umma::mma_commit(&acc_full[buf]);
       }
     }
   } else if (warp < 6) {
@@ -254,42 +265,52 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int q4 = warp & 3;
     const int r = q4 * 32 + lane;
     int tl = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tl) {
-      const int buf = tl & 1;
-      bool ok = mbar_wait_abortable(&acc_full[buf], (tl >> 1) & 1, s_abort);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      umma::fence_after_sync();
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
       const int m0 = (tile / tiles_n) * 128, n0 = (tile % tiles_n) * 128;
-      const uint32_t lane_base = tmem + buf * 128u + (uint32_t(q4 * 32) << 16);
       const int gm = m0 + r;
-      uint32_t v[32];
+      for (int kb0 = 0; kb0 < nkb; kb0 += seg, ++tl) {
+        const int buf = tl & 1;
+        ok = mbar_wait_abortable(&acc_full[buf], (tl >> 1) & 1, s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        umma::fence_after_sync();
+        // the first segment of a tile stores y (+ bias); later ones add to what this same
+        // thread stored before
+        const bool add = kb0 > 0;
+        const uint32_t lane_base = tmem + buf * 128u + (uint32_t(q4 * 32) << 16);
+        uint32_t v[32];
 #pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        umma::tmem_ld32(lane_base + cb * 32, v);
-        umma::tmem_wait_ld();
-        if (gm < R) {
-          float* yrow = y + size_t(gm) * n_out + n0 + cb * 32;
+        for (int cb = 0; cb < 4; ++cb) {
+          umma::tmem_ld32(lane_base + cb * 32, v);
+          umma::tmem_wait_ld();
+          if (gm < R) {
+            float* yrow = y + size_t(gm) * n_out + n0 + cb * 32;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int gn = n0 + cb * 32 + j;
-            float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                   __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-            if (gn + 3 < n_out) {
-              if (bias) {
-                const float4 bb = *reinterpret_cast<const float4*>(bias + gn);
-                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+            for (int j = 0; j < 32; j += 4) {
+              const int gn = n0 + cb * 32 + j;
+              float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                     __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              if (gn + 3 < n_out) {
+                if (add) {
+                  const float4 p = *reinterpret_cast<const float4*>(yrow + j);
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                } else if (bias) {
+                  const float4 bb = *reinterpret_cast<const float4*>(bias + gn);
+                  o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                }
+                *reinterpret_cast<float4*>(yrow + j) = o;
+              } else {
+                const float oo[4] = {o.x, o.y, o.z, o.w};
+                for (int t = 0; t < 4; ++t)
+                  if (gn + t < n_out) yrow[j + t] = oo[t] + (add ? yrow[j + t] : (bias ? bias[gn + t] : 0.f));
               }
-              *reinterpret_cast<float4*>(yrow + j) = o;
-            } else {
-              const float oo[4] = {o.x, o.y, o.z, o.w};
-              for (int t = 0; t < 4; ++t)
-                if (gn + t < n_out) yrow[j + t] = oo[t] + (bias ? bias[gn + t] : 0.f);
             }
           }
         }
+        umma::fence_before_sync();
+        mbar_arrive(&acc_empty[buf]);
       }
-      umma::fence_before_sync();
-      mbar_arrive(&acc_empty[buf]);
     }
   }
   __syncwarp();
@@ -309,10 +330,8 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 // scratch for the split weight (without it the call stays on the FMA pipes).
 bool linear_tf32x3_supported(const float* x, const float* w, const float* bias, const float* y, int R,
                              int n_in, int n_out, const void* scratch, size_t scratch_bytes) {
-  // The tensor-core accumulator adds with truncation, a bias that grows with the
-  // reduction depth: measured rel-err 3e-6 at in=512, 5e-6 at 1024, 1.1e-5 at
-  // 2048.  Deeper reductions stay on the FMA pipes to keep the 1e-5 promise.
-  return R >= 256 && n_in <= 1024 && n_in % 4 == 0 && n_out % 4 == 0 && aligned16(x) && aligned16(w) &&
+  // any reduction depth: deep ones are cut into accumulator segments (kSegBlocks)
+  return R >= 256 && n_in % 4 == 0 && n_out % 4 == 0 && aligned16(x) && aligned16(w) &&
          aligned16(y) && (!bias || aligned16(bias)) && scratch && aligned16(scratch) &&
          scratch_bytes >= size_t(2) * n_in * n_out * sizeof(float);
 }

@@ -79,7 +79,7 @@ int cb2_verify_reduce(const void* ref, const void* out, int64_t numel_per_seg,
  * `linear(input, fused_N)` (packages/catopt-torch/src/catopt_torch/
  * torch_bridge.py:1251-1253):  y[R,out] = x[R,in] . w[out,in]^T  (+ bias[out]
  * when bias != NULL).  fp32 in, fp32 accumulate.
- * Large row counts (R >= 256, in <= 1024, in/out multiples of 4, 16-byte aligned pointers)
+ * Large row counts (R >= 256, in/out multiples of 4, 16-byte aligned pointers)
  * run on the tensor cores with three-pass TF32 splitting; small ones on the
  * fp32 FMA pipes with the reduction axis split across a thread-block cluster.
  * scratch (cb2_linear_f32_scratch_bytes bytes, 16-byte aligned) may be NULL:

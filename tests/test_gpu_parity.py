@@ -975,3 +975,24 @@ def test_gated_contract_past_two_billion_scores(dev):
     ref_rows = ((s[-1, -64:] * gate[-64:]).double() @ v[-1].double())
     assert rel_to_max(out[-1, -64:], ref_rows) <= 4e-3
     ops.check_device_status(dev)
+
+
+@pytest.mark.parametrize("rows,n_in,n_out", [(512, 2048, 256), (300, 4096, 132), (1024, 1056, 512), (256, 8192, 128)])
+def test_linear_deep_reductions_on_the_tensor_cores(dev, rows, n_in, n_out):
+    """Reductions deeper than one accumulator segment: the result stays within the fp32 budget
+    (the segments' sums are added in fp32), with bias, ragged tiles and a ragged last segment."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + n_in)
+    x = torch.randn(rows, n_in, generator=g)
+    w = torch.randn(n_out, n_in, generator=g) / math.sqrt(n_in)
+    b = torch.randn(n_out, generator=g)
+    want = x.double() @ w.double().t() + b.double()
+    got = ops.linear_f32(x.to(dev), w.to(dev), b.to(dev))
+    ops.check_device_status(dev)
+    assert rel_to_max(got, want) <= FP32_TOL, (rows, n_in, n_out, rel_to_max(got, want))
+    # the same inputs, all positive: the worst case for a truncating accumulator
+    xp, wp = x.abs(), w.abs()
+    wantp = xp.double() @ wp.double().t()
+    gotp = ops.linear_f32(xp.to(dev), wp.to(dev))
+    assert rel_to_max(gotp, wantp) <= FP32_TOL, (rows, n_in, n_out, rel_to_max(gotp, wantp))
