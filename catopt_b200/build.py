@@ -25,6 +25,7 @@ SOURCES = [
     "decayed_chunk_ffma.cu",
     "decayed_chunk_small.cu",
     "decayed_chunk_tc.cu",
+    "decayed_seg_state.cu",
     "decayed_chunk.cu",
     "gated_contract.cu",
     "gated_contract_tc.cu",

@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int n_bh, int n_seg,
-                  float* __restrict__ seg_state, int* __restrict__ seg_flag, int* dev_status) {
+                  float* __restrict__ seg_state, int* __restrict__ seg_flag, int prestaged, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
   // __shared__ array keeps every access a shared-space (LDS/STS) access
@@ -320,9 +320,12 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma::tmem_wait_ld();
         } else {
           // first chunk of a later segment: the state comes from the predecessor CTA
-          const int* flag = seg_flag + size_t(seg - 1) * n_bh + bh;
-          ok = wait_flag_abortable(flag, s_abort);
-          if (!__all_sync(0xffffffffu, ok)) break;
+          // (prestaged: every segment's start state was computed before this launch)
+          if (!prestaged) {
+            const int* flag = seg_flag + size_t(seg - 1) * n_bh + bh;
+            ok = wait_flag_abortable(flag, s_abort);
+            if (!__all_sync(0xffffffffu, ok)) break;
+          }
           const float4* src = reinterpret_cast<const float4*>(
               seg_state + (size_t(seg - 1) * n_bh + bh) * (kC * kC) + r * kC + cb0 * 32);
 #pragma unroll
@@ -415,7 +418,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       CB2_TL(i, 5);
     }
     // hand the state to the next segment of this head: St after the last MMA4
-    if (seg + 1 < n_seg) {
+    if (seg + 1 < n_seg && !prestaged) {
       bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
       if (__all_sync(0xffffffffu, ok)) {
         umma::fence_after_sync();
@@ -487,6 +490,24 @@ int decayed_tc_segments(int n_bh, int nchunk, int sms) {
   return best;
 }
 
+int decayed_seg_states_run(const void* k, const void* v, const float* gamma, int B, int H, int T, int dk,
+                           int dv, int n_seg, float* seg_state, int* dev_status, cudaStream_t st);
+
+// Parallel segments per head when heads are fewer than half the SMs: the largest power of
+// two that keeps all CTAs in one wave, divides the chunk count and leaves four chunks or
+// more per segment; 1 = not worth it (below 16 chunks the two extra launches cost more
+// than the idle SMs: 8 chunks measured 29 us in one pass, 41 us cut in four).  The segments' start states are computed first
+// (decayed_seg_state.cu), so the segments do not wait for one another.
+int decayed_tc_parallel_segments(int n_bh, int nchunk, int sms) {
+  if (n_bh * 2 > sms || nchunk < 16) return 1;
+  int best = 1;
+  for (int n = 2; n <= 16; n *= 2) {
+    if (n_bh * n > sms || nchunk % n != 0 || nchunk / n < 4) break;
+    best = n;
+  }
+  return best;
+}
+
 namespace {
 int device_sms() {
   int dev = 0, sms = 148;
@@ -499,6 +520,8 @@ int device_sms() {
 // Scratch that lets heads be cut into segments: (n_seg - 1) * B*H states of
 // 128 x 128 fp32, then as many flags.
 size_t decayed_tc_scratch_bytes(int B, int H, int T) {
+  const int n_par = decayed_tc_parallel_segments(B * H, (T + kC - 1) / kC, device_sms());
+  if (n_par > 1) return size_t(n_par - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
   const int n_seg = decayed_tc_segments(B * H, (T + kC - 1) / kC, device_sms());
   return size_t(n_seg - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
 }
@@ -521,6 +544,18 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
   const int n_bh = B * H;
+  // few heads: parallel segments, start states computed up front
+  const int n_par = decayed_tc_parallel_segments(n_bh, (T + kC - 1) / kC, device_sms());
+  if (n_par > 1 && scratch && aligned16(scratch) &&
+      scratch_bytes >= size_t(n_par - 1) * n_bh * size_t(kC) * kC * sizeof(float)) {
+    float* states = static_cast<float*>(scratch);
+    rc = decayed_seg_states_run(k, v, gamma, B, H, T, dk, dv, n_par, states, dev_status, st);
+    if (rc != CB2_OK) return rc;
+    decayed_tc_kernel<<<n_bh * n_par, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
+                                                                 n_bh, n_par, states, nullptr, 1, dev_status);
+    CB2_LAUNCH_CHECK();
+    return CB2_OK;
+  }
   int n_seg = decayed_tc_segments(n_bh, (T + kC - 1) / kC, device_sms());
   const size_t state_bytes = size_t(n_seg - 1) * n_bh * size_t(kC) * kC * sizeof(float);
   const size_t flag_bytes = size_t(n_seg - 1) * n_bh * sizeof(int);
@@ -531,7 +566,7 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
   int* seg_flag = n_seg > 1 ? reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + state_bytes) : nullptr;
   if (n_seg > 1 && cudaMemsetAsync(seg_flag, 0, flag_bytes, st) != cudaSuccess) return CB2_LAUNCH_FAIL;
   decayed_tc_kernel<<<n_bh * n_seg, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
-                                                               n_bh, n_seg, seg_state, seg_flag, dev_status);
+                                                               n_bh, n_seg, seg_state, seg_flag, 0, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

@@ -145,7 +145,10 @@ int cb2_chain_fold_f32_noalloc(const float* const* weights, const int* dims, int
  * products (required).  Tensor-core path (bf16): optional; with it, heads are
  * cut into consecutive segments handled by different CTAs so that the grid
  * fills the GPU's last wave, the fp32 state crossing from one segment to the
- * next through scratch; without it (NULL / too small) one CTA runs each head.
+ * next through scratch; with fewer heads than half the SMs and 16 chunks or
+ * more, the segments run at the same time instead, each from a start state that
+ * two small kernels compute up front (K and V are then read twice); without
+ * scratch (NULL / too small) one CTA runs each head.
  * The answer is 0 when no cut would help.  Calls that share scratch must not
  * overlap on the GPU.
  * ------------------------------------------------------------------------- */

@@ -996,3 +996,37 @@ def test_linear_deep_reductions_on_the_tensor_cores(dev, rows, n_in, n_out):
     wantp = xp.double() @ wp.double().t()
     gotp = ops.linear_f32(xp.to(dev), wp.to(dev))
     assert rel_to_max(gotp, wantp) <= FP32_TOL, (rows, n_in, n_out, rel_to_max(gotp, wantp))
+
+
+@pytest.mark.parametrize("B,H,T,d,gam", [(1, 4, 4096, 128, (0.97, 0.999, 0.5, 1.0)), (2, 3, 2048, 64, (0.9, 0.99, 0.9999)),
+                                          (1, 2, 3000, 128, (0.98, 0.995)), (1, 16, 8192, 128, None), (4, 8, 4096, 64, None)])
+def test_decayed_bf16_few_heads_run_their_segments_in_parallel(dev, B, H, T, d, gam):
+    """Fewer heads than half the SMs: the sequence is cut into segments that run at once, each from
+    a start state computed up front.  Same function as one CTA walking the head (the C ABI without
+    scratch), and within the bf16 budget of the fp64 recurrence."""
+    from catopt_b200 import _lib, ops
+
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(T + H)
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(math.sqrt(d)).bfloat16() for _ in range(3))
+    gamma = torch.tensor(gam, dtype=torch.float32) if gam else bench_gamma(H)
+    assert lib.cb2_decayed_chunk_scratch_bytes(B, H, T, d, d, 128 if T % 128 == 0 else T // 8, _lib.CB2_BF16) > 0
+    C = 128 if T % 128 == 0 else T // 8
+    qd, kd, vd, gd = q.to(dev), k.to(dev), v.to(dev), gamma.to(dev)
+    par = ops.decayed_chunk_fwd(qd, kd, vd, gd, C, 2.0)
+    ops.check_device_status(dev)
+    serial = torch.empty_like(vd)
+    rc = lib.cb2_decayed_chunk_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), serial.data_ptr(), gd.data_ptr(),
+                                   B, H, T, d, d, C, 2.0, _lib.CB2_BF16, None, 0,
+                                   ops.device_status(dev).data_ptr(), _lib.stream_ptr())
+    assert rc == 0
+    ops.check_device_status(dev)
+    assert rel_to_max(par, serial) <= 8e-3          # two bf16 roundings of one function
+    if T <= 4096:
+        want = oracle.decayed_state_carry(q.double(), k.double(), v.double(), gamma.double(), C, 2.0)
+        assert rel_to_max(par, want) <= BF16_TOL
+        assert rel_to_max(par[:, :, -128:], want[:, :, -128:]) <= BF16_TOL
+
+
+def bench_gamma(H):
+    return torch.tensor([1 - 2.0 ** (-5 - 8 * h / H) for h in range(H)], dtype=torch.float32)
