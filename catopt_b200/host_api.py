@@ -4,7 +4,8 @@ The lowered modules normally live on the device next to the model.  When the
 operands live in (pinned) host memory, the (batch x head) axis is cut into
 slabs and three streams overlap the host-to-device copy of slab i+1, the kernel
 on slab i and the device-to-host copy of slab i-1, with two device buffers per
-operand.  Units are independent, so slabbing changes no result bit.
+operand.  Units are independent and every slab takes the one-pass form of the kernel,
+so slabbing changes no result bit.
 """
 from __future__ import annotations
 
@@ -73,7 +74,8 @@ class DecayedHostPipeline:
                     self.s_comp.wait_event(self.ev_out[buf])  # slab i-2's result has left the buffer
                 ops.decayed_chunk_fwd(self.dq[buf][:n].unsqueeze(0), self.dk_[buf][:n].unsqueeze(0),
                                       self.dv_[buf][:n].unsqueeze(0), self.gamma_units[b:e],
-                                      self.chunk, self.scale, out=self.do[buf][:n].unsqueeze(0))
+                                      self.chunk, self.scale, out=self.do[buf][:n].unsqueeze(0),
+                                      one_pass=True)   # bits must not depend on the slab size
                 self.ev_comp[buf].record(self.s_comp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_comp[buf])

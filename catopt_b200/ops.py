@@ -142,8 +142,15 @@ def chain_fold_f32(weights: list[torch.Tensor]) -> torch.Tensor:
 
 # --------------------------------------------------------------------------- decayed
 def decayed_chunk_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor,
-                      chunk: int, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Decayed causal linear attention ``[B,H,T,d]`` with per-head ``gamma[H]`` (fp32)."""
+                      chunk: int, scale: float = 1.0, out: torch.Tensor | None = None,
+                      one_pass: bool = False) -> torch.Tensor:
+    """Decayed causal linear attention ``[B,H,T,d]`` with per-head ``gamma[H]`` (fp32).
+
+    ``one_pass``: on the tensor-core path, withhold the scratch that lets a call with few
+    heads run a head's segments in parallel from precomputed start states.  That form
+    rounds the carried state at other points than the one-pass walk (same function, other
+    last bits), so a caller that cuts one problem into calls of different sizes and wants
+    every head's bits independent of the cut asks for the one-pass form."""
     require_cuda(q, k, v, gamma, out)
     if q.dim() != 4 or q.shape != k.shape or v.shape[:3] != q.shape[:3]:
         raise B200Error("decayed_chunk_fwd takes q,k [B,H,T,dk] and v [B,H,T,dv]")
@@ -160,6 +167,8 @@ def decayed_chunk_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: 
     code = dtype_code(q.dtype)
     lib = _lib.load()
     need = lib.cb2_decayed_chunk_scratch_bytes(B, H, T, dk, dv, chunk, code)
+    if one_pass and lib.cb2_decayed_chunk_on_tensor_cores(B, H, T, dk, dv, chunk, code):
+        need = 0
     scratch = _scratch_buf("decayed", need, q.device)
     status = device_status(q.device)
     rc = lib.cb2_decayed_chunk_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
