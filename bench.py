@@ -312,20 +312,7 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     out["folded_chain_fp32_R4096"] = entry(ms, 4096, (512 * 512 + 2 * 4096 * 512) * 4, 1,
                                            "reference's published cell k8_d512_R4096",
                                            flops=2 * 4096 * 512 * 512)
-    # a wider folded chain (2048 -> 2048, R = 16384): the reduction is cut into four accumulator segments
-    xw = torch.randn(16384, 2048, device=dev, generator=gen)
-    ww = torch.randn(2048, 2048, device=dev, generator=gen) / math.sqrt(2048)
-    yw = torch.empty(16384, 2048, device=dev)
-    ms = time_steps(lambda: ops.linear_f32(xw, ww, out=yw), K, W, world)
-    e = entry(ms, 16384, (2048 * 2048 + 2 * 16384 * 2048) * 4, 2,
-              "3xTF32 tcgen05, four 512-deep accumulator segments added in fp32 (285 MB > L2); fp32-equivalent "
-              "FLOPs against a third of the bf16 burst peak's TF32 half (three passes)",
-              flops=2 * 16384 * 2048 * 2048)
-    tf32_equiv_peak = pk["bf16_tflops"] / 2 / 3
-    e["roofline"] = {"bound": "tensor", "achieved": e["tflops"], "peak": tf32_equiv_peak, "unit": "TFLOP/s",
-                     "frac": e["tflops"] / tf32_equiv_peak, "traffic": None}
-    out["folded_chain_fp32_R16384_2048x2048"] = e
-    del ws, x4, y4, xw, ww, yw
+    del ws, x4, y4
 
     # config 2: B=2 H=4 T=1024 d=64 fp32, gamma 0.97, chunk 64
     q, k, v = (torch.randn(2, 4, 1024, 64, device=dev, generator=gen) / 8 for _ in range(3))
@@ -415,6 +402,19 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
         flops=4 * 32 * 65536 * 128)
     del qd, kd, vd
 
+    # decayed attention with few heads (small batch, long sequence): 16 heads x T=8192, d=128 bf16;
+    # a head's segments run in parallel from start states computed up front (3 launches)
+    qf, kf, vf = (_randn_bf16((16, 8192 * 128), gen, 1 / math.sqrt(128)).view(2, 8, 8192, 128) for _ in range(3))
+    gf = c4_gamma(8).to(dev)
+    of = torch.empty_like(vf)
+    ms = time_steps(lambda: ops.decayed_chunk_fwd(qf, kf, vf, gf, 128, 1.0, out=of), K, W, world, flush)
+    out["decayed_bf16_few_heads_B2_H8_T8192_d128"] = entry(
+        ms, 2 * 8192, 4 * 16 * 8192 * 128 * 2, 3,
+        "16 heads on 148 SMs: 8 parallel segments per head, start states from decayed_seg_state (K and V read "
+        "twice); 134 MB, L2 flushed between steps; one CTA per head takes 189 us",
+        flops=16 * 8192 * (4 * 128 * 128 + 4 * 128 * 128))
+    del qf, kf, vf, of
+
     # the om_decayed element on materialised scores, (s*g)@v (the site the reference's generated
     # fused-contraction kernel lowers): B=2 H=16 T=K=4096 dv=128 bf16, one gate for all heads
     sg = _randn_bf16((32, 4096 * 4096), gen).view(2, 16, 4096, 4096)
@@ -446,6 +446,21 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     e["tokens_per_s"] = 256 * 4 * 512 * 13 / (ms / K / 1e3)  # probe tokens x checks, whole job
     out["config5_verify_bf16"] = e
     del ref, outp
+
+    # a wider folded chain (2048 -> 2048, R = 16384): the reduction is cut into four accumulator segments
+    xw = torch.randn(16384, 2048, device=dev, generator=gen)
+    ww = torch.randn(2048, 2048, device=dev, generator=gen) / math.sqrt(2048)
+    yw = torch.empty(16384, 2048, device=dev)
+    ms = time_steps(lambda: ops.linear_f32(xw, ww, out=yw), K, W, world)
+    e = entry(ms, 16384, (2048 * 2048 + 2 * 16384 * 2048) * 4, 2,
+              "3xTF32 tcgen05, four 512-deep accumulator segments added in fp32 (285 MB > L2); timed last, its sustained tensor load lowers the clocks of whatever follows; fp32-equivalent "
+              "FLOPs against a third of the bf16 burst peak's TF32 half (three passes)",
+              flops=2 * 16384 * 2048 * 2048)
+    tf32_equiv_peak = pk["bf16_tflops"] / 2 / 3
+    e["roofline"] = {"bound": "tensor", "achieved": e["tflops"], "peak": tf32_equiv_peak, "unit": "TFLOP/s",
+                     "frac": e["tflops"] / tf32_equiv_peak, "traffic": None}
+    out["folded_chain_fp32_R16384_2048x2048"] = e
+    del xw, ww, yw
     ops.check_device_status(dev)
     return out
 
