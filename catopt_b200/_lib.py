@@ -100,6 +100,12 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p] * 9 + [C.c_int] * 6 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
                                             C.c_void_p, C.c_void_p],
     ),
+    "cb2_diag_scan_seg_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "cb2_diag_scan_seg_starts": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+         C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p],
+    ),
     "cb2_diag_scan_fwd": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

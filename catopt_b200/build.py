@@ -20,6 +20,7 @@ SOURCES = [
     "verify_reduce.cu",
     "diag_scan.cu",
     "diag_compose.cu",
+    "diag_scan_seg.cu",
     "linear_f32.cu",
     "linear_tf32x3.cu",
     "decayed_chunk_ffma.cu",

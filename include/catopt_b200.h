@@ -185,6 +185,19 @@ int cb2_diag_scan_fwd(const void* a, const void* x, const void* b, const void* c
                       int N, int a_bcast_n, int dtype, int* dev_status,
                       void* stream);
 
+/* Start states of n_seg equal sequence segments of the scan above, so that a call with
+ * few (batch, channel-block) units can run as cb2_diag_scan_fwd over the
+ * [B*n_seg, T/n_seg, ...] view of the same tensors with h0 = starts (steps compose by
+ * the reference's `affd_compose`, torch_bridge.py:1896-1899: a segment's composed map
+ * (prod a_t, end state from zero) is taken in one pass over a and x, then
+ * S_s = A_(s-1) S_(s-1) + U_(s-1) from S_0 = h0).  a: [B,T,D,N]; x: [B,T,D]; b: [D,N];
+ * h0: float[B,D,N] or NULL; starts: float[B,n_seg,D,N]; T % n_seg == 0, N % 4 == 0.
+ * scratch: cb2_diag_scan_seg_scratch_bytes() bytes (the segments' maps). */
+size_t cb2_diag_scan_seg_scratch_bytes(int B, int D, int N, int n_seg);
+int cb2_diag_scan_seg_starts(const void* a, const void* x, const void* b, const float* h0,
+                             float* starts, int B, int T, int D, int N, int n_seg, int dtype,
+                             void* scratch, size_t scratch_bytes, void* stream);
+
 /* Final state of a diagonal scan straight from its stacked leaf maps:
  *     out = a_root*h + b_root,  (a_root, b_root) = f_0 . f_1 . ... . f_{n-1},
  *     f_j(h) = a_seq[j]*h + b_seq[j],

@@ -1030,3 +1030,36 @@ def test_decayed_bf16_few_heads_run_their_segments_in_parallel(dev, B, H, T, d, 
 
 def bench_gamma(H):
     return torch.tensor([1 - 2.0 ** (-5 - 8 * h / H) for h in range(H)], dtype=torch.float32)
+
+
+@pytest.mark.parametrize("B,T,D,N,dtype,with_h0", [(1, 2048, 64, 16, torch.float32, True), (1, 4096, 256, 8, torch.bfloat16, False),
+                                                    (2, 1024, 96, 4, torch.float32, False), (1, 3072, 32, 32, torch.bfloat16, True)])
+def test_scan_few_units_runs_segments_side_by_side(dev, B, T, D, N, dtype, with_h0):
+    """A scan with few (batch, channel-block) units is cut into segments that start from
+    states computed up front; same function as the one-pass kernel and as the serial oracle."""
+    from catopt_b200 import _lib, ops
+    from catopt_b200.ops import _scan_parallel_segments
+
+    assert _scan_parallel_segments(B, T, D, N) > 1
+    g = torch.Generator().manual_seed(T + D)
+    a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, N, generator=g)).to(dtype)
+    x = torch.randn(B, T, D, generator=g).to(dtype)
+    b = (torch.randn(D, N, generator=g) / 4).to(dtype)
+    c = (torch.randn(D, N, generator=g) / 4).to(dtype)
+    h0 = torch.randn(B, D, N, generator=g) if with_h0 else None
+    wy, wh = oracle.diag_scan_serial(a, x, b, c, h0)
+    ad, xd, bd, cd = a.to(dev), x.to(dev), b.to(dev), c.to(dev)
+    h0d = h0.to(dev) if with_h0 else None
+    y, hT = ops.diag_scan_fwd(ad, xd, bd, cd, h0d, want_state=True)
+    ops.check_device_status(dev)
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert rel_to_max(y, wy) <= tol and rel_to_max(hT, wh) <= FP32_TOL
+    # the one-pass kernel through the C ABI
+    y1 = torch.empty_like(xd)
+    h1 = torch.empty(B, D, N, device=dev)
+    rc = _lib.load().cb2_diag_scan_fwd(ad.data_ptr(), xd.data_ptr(), bd.data_ptr(), cd.data_ptr(),
+                                       h0d.data_ptr() if with_h0 else None, y1.data_ptr(), h1.data_ptr(), B, T, D, N, 0,
+                                       _lib.dtype_code(dtype), ops.device_status(dev).data_ptr(), _lib.stream_ptr())
+    assert rc == 0
+    assert rel_to_max(y.float(), y1.float()) <= (8e-3 if dtype == torch.bfloat16 else 2e-6)
+    assert rel_to_max(hT, h1) <= 2e-6
