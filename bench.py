@@ -606,6 +606,18 @@ def run_profile_case(args) -> None:
         vg = _randn_bf16((32, 2048 * 128), gen).view(2, 16, 2048, 128)
         gg = torch.rand(2048, 2048, device=dev, generator=gen).bfloat16()
         fn = lambda: ops.gated_contract(sg, gg, vg)  # noqa: E731
+    elif args.profile_case == "decayed_few":  # 16 heads x T=8192, d=128 bf16 (134 MB): parallel segments
+        q, k, v = (_randn_bf16((16, 8192 * 128), gen, 1 / math.sqrt(128)).view(2, 8, 8192, 128) for _ in range(3))
+        gamma = c4_gamma(8).to(dev)
+        o = torch.empty_like(v)
+        fn = lambda: ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0, out=o)  # noqa: E731
+    elif args.profile_case == "scan_few":     # config 3 with one batch entry (151 MB): 8 segments side by side
+        x = _randn_bf16((1, 4096 * 1024), gen).view(1, 4096, 1024)
+        a = torch.sigmoid(4 + 0.5 * torch.randn(1, 4096, 1024, 16, device=dev, generator=gen)).bfloat16()
+        b = (torch.randn(1024, 16, device=dev, generator=gen) / 4).bfloat16()
+        c = (torch.randn(1024, 16, device=dev, generator=gen) / 4).bfloat16()
+        y = torch.empty_like(x)
+        fn = lambda: ops.diag_scan_fwd(a, x, b, c, None, out=y)  # noqa: E731
     elif args.profile_case == "prefix":     # all prefix maps of 256 steps over config 3's state, fp32: 537 MB
         ap_ = torch.sigmoid(4 + 0.5 * torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen))
         bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
@@ -636,7 +648,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix"],
+                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

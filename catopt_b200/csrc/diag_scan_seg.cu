@@ -5,8 +5,9 @@
 // torch_bridge.py:1895-1900) and steps compose by `affd_compose` (:1896-1899), so the
 // state a segment starts from follows from the composed maps of the segments before it:
 //
-//   kernel 1: (A_s, U_s) = composed map of segment s: A_s = prod a_t, U_s = the state
-//             the segment ends in when started from zero; every thread owns four state
+//   kernel 1: (A_s, U_s) = composed map of a piece of a segment (up to 8 pieces per
+//             segment): A_s = prod a_t, U_s = the state the piece ends in when started
+//             from zero; every thread owns four state
 //             elements of one channel and walks the segment with eight steps of loads in
 //             flight (one pass over a and x);
 //   kernel 2: S_0 = h0 (or 0), S_s = A_(s-1) S_(s-1) + U_(s-1), fp32.
@@ -93,33 +94,47 @@ scan_seg_maps_kernel(const void* __restrict__ a, const void* __restrict__ x, con
   *reinterpret_cast<float4*>(seg_u + o) = make_float4(U[0], U[1], U[2], U[3]);
 }
 
-// starts[b][s][e]: S_0 = h0 (or 0), S_s = A_(s-1) S_(s-1) + U_(s-1)
+// starts[b][s][e]: S_0 = h0 (or 0), S_s = A_(s-1) S_(s-1) + U_(s-1).  The maps come in
+// pieces finer than the segments (`fine` pieces per segment, so that kernel 1 has enough
+// threads to stream at full rate); a start state is written at every segment boundary.
 __global__ void __launch_bounds__(256)
 scan_seg_starts_kernel(const float* __restrict__ seg_a, const float* __restrict__ seg_u,
-                       const float* __restrict__ h0, int DN, int n_seg, float* __restrict__ starts) {
+                       const float* __restrict__ h0, int DN, int n_seg, int fine, float* __restrict__ starts) {
   const int e = blockIdx.x * 256 + threadIdx.x;
   if (e >= DN) return;
   const int bb = blockIdx.y;
   float s = h0 ? h0[size_t(bb) * DN + e] : 0.f;
   for (int sg = 0; sg < n_seg; ++sg) {
-    const size_t o = (size_t(bb) * n_seg + sg) * DN + e;
-    starts[o] = s;
-    s = fmaf(seg_a[o], s, seg_u[o]);
+    starts[(size_t(bb) * n_seg + sg) * DN + e] = s;
+    for (int f = 0; f < fine; ++f) {
+      const size_t o = (size_t(bb) * n_seg * fine + size_t(sg) * fine + f) * DN + e;
+      s = fmaf(seg_a[o], s, seg_u[o]);
+    }
   }
+}
+
+// pieces per segment for kernel 1: up to 8, at least 64 steps each
+int fine_pieces(int seg_len) {
+  for (int f = 8; f > 1; f /= 2)
+    if (seg_len % f == 0 && seg_len / f >= 64) return f;
+  return 1;
 }
 
 template <int DTYPE>
 int run_seg(const void* a, const void* x, const void* b, const float* h0, int B, int T, int D, int N, int n_seg,
             float* starts, float* scratch, cudaStream_t st) {
   const int DN = D * N;
-  const int seg_len = T / n_seg;
+  const int fine = fine_pieces(T / n_seg);
+  const int n_fine = n_seg * fine;
+  if (n_fine > 65535) return CB2_BAD_SHAPE;
+  const int piece_len = T / n_fine;
   float* seg_a = scratch;
-  float* seg_u = scratch + size_t(B) * n_seg * DN;
-  const dim3 grid(unsigned((DN / 4 + kSegThreads - 1) / kSegThreads), unsigned(n_seg), unsigned(B));
-  scan_seg_maps_kernel<DTYPE><<<grid, kSegThreads, 0, st>>>(a, x, b, T, D, N, seg_len, seg_a, seg_u);
+  float* seg_u = scratch + size_t(B) * n_fine * DN;
+  const dim3 grid(unsigned((DN / 4 + kSegThreads - 1) / kSegThreads), unsigned(n_fine), unsigned(B));
+  scan_seg_maps_kernel<DTYPE><<<grid, kSegThreads, 0, st>>>(a, x, b, T, D, N, piece_len, seg_a, seg_u);
   CB2_LAUNCH_CHECK();
   scan_seg_starts_kernel<<<dim3(unsigned((DN + 255) / 256), unsigned(B)), 256, 0, st>>>(seg_a, seg_u, h0, DN, n_seg,
-                                                                                       starts);
+                                                                                       fine, starts);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }
@@ -129,7 +144,7 @@ int run_seg(const void* a, const void* x, const void* b, const float* h0, int B,
 
 extern "C" size_t cb2_diag_scan_seg_scratch_bytes(int B, int D, int N, int n_seg) {
   if (B <= 0 || D <= 0 || N <= 0 || n_seg <= 0) return 0;
-  return size_t(2) * B * n_seg * D * N * sizeof(float);
+  return size_t(2) * B * n_seg * 8 * D * N * sizeof(float);   // up to 8 pieces per segment
 }
 
 extern "C" int cb2_diag_scan_seg_starts(const void* a, const void* x, const void* b, const float* h0,

@@ -326,12 +326,11 @@ def diag_scan_fwd(a: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Te
 
 def _scan_parallel_segments(B: int, T: int, D: int, N: int) -> int:
     """Segments for a scan whose one-pass form (one CTA per batch entry and 32 channels)
-    would keep fewer than a quarter of the 148 SMs busy: the largest power of two that
-    brings the CTA count to about two per SM, divides T and leaves 256 steps or more per
-    segment; 1 = one pass.  (Measured, bf16 N=16 T=4096: 32 units 154 -> 86 us, 64 units
-    154 -> 164 us: the extra pass over a stops paying at a quarter of the SMs.)"""
+    would keep fewer than half of the 148 SMs busy: the largest power of two that brings
+    the CTA count to about two per SM, divides T and leaves 256 steps or more per segment;
+    1 = one pass.  (Measured, bf16 N=16 T=4096: 32 units 154 -> 72 us, 64 units 154 -> 116 us.)"""
     units = B * ((D + 31) // 32)
-    if units * 4 > 148 or N % 4 or T < 1024:
+    if units * 2 > 148 or N % 4 or T < 1024:
         return 1
     n = 1
     while units * n * 2 <= 296 and T % (n * 2) == 0 and T // (n * 2) >= 256:
