@@ -1063,3 +1063,32 @@ def test_scan_few_units_runs_segments_side_by_side(dev, B, T, D, N, dtype, with_
     assert rc == 0
     assert rel_to_max(y.float(), y1.float()) <= (8e-3 if dtype == torch.bfloat16 else 2e-6)
     assert rel_to_max(hT, h1) <= 2e-6
+
+
+def test_cuda_graph_replay_of_the_segment_parallel_paths(dev):
+    """The few-heads decayed path (end states, scan, attention) and the few-units scan path (maps,
+    starts, scan) are three launches each; captured and replayed on new inputs they must equal
+    eager runs bit for bit."""
+    from catopt_b200 import ops
+    from catopt_b200.executors import B200ChunkedDecay, B200DiagScan
+
+    g = torch.Generator().manual_seed(12)
+    q, k, v = (torch.randn(1, 4, 4096, 64, generator=g).bfloat16().to(dev) / 4 for _ in range(3))
+    mod = B200ChunkedDecay(torch.tensor([0.9, 0.97, 0.99, 0.999]), 4, 128).to(dev)
+    mod.capture_cuda_graph(q, k, v)
+    for scale in (1.0, 0.5):
+        kk = k * scale
+        assert torch.equal(mod(q, kk, v), mod._forward_impl(q, kk, v))
+    assert ops._scan_parallel_segments(1, 2048, 128, 16) > 1
+    a = torch.sigmoid(4 + 0.5 * torch.randn(1, 2048, 128, 16, generator=g)).bfloat16().to(dev)
+    x = torch.randn(1, 2048, 128, generator=g).bfloat16().to(dev)
+    b = (torch.randn(128, 16, generator=g) / 4).bfloat16().to(dev)
+    c = (torch.randn(128, 16, generator=g) / 4).bfloat16().to(dev)
+    scan = B200DiagScan(b, c, return_state=True).to(dev)
+    scan.capture_cuda_graph(a, x)
+    x2 = x * 0.5
+    y_r, h_r = scan(a, x2)
+    y_r, h_r = y_r.clone(), h_r.clone()
+    y_e, h_e = scan._forward_impl(a, x2)
+    assert torch.equal(y_r, y_e) and torch.equal(h_r, h_e)
+    ops.check_device_status(dev)
