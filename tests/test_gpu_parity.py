@@ -1092,3 +1092,21 @@ def test_cuda_graph_replay_of_the_segment_parallel_paths(dev):
     y_e, h_e = scan._forward_impl(a, x2)
     assert torch.equal(y_r, y_e) and torch.equal(h_r, h_e)
     ops.check_device_status(dev)
+
+
+def test_decayed_bf16_few_heads_unequal_head_dims(dev):
+    """Parallel segments with dk != dv below the tile width (zero-filled columns in both kernels)."""
+    from catopt_b200 import ops
+
+    B, H, T, dk, dv = 1, 3, 2048, 32, 96
+    g = torch.Generator().manual_seed(77)
+    q = torch.randn(B, H, T, dk, generator=g).div_(math.sqrt(dk)).bfloat16()
+    k = torch.randn(B, H, T, dk, generator=g).div_(math.sqrt(dk)).bfloat16()
+    v = torch.randn(B, H, T, dv, generator=g).bfloat16()
+    gamma = torch.tensor([0.95, 0.99, 0.999])
+    want = oracle.decayed_state_carry(q.double(), k.double(), v.double(), gamma.double(), 128, 1.0)
+    par = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 128, 1.0)
+    one = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 128, 1.0, one_pass=True)
+    ops.check_device_status(dev)
+    assert rel_to_max(par, want) <= BF16_TOL and rel_to_max(one, want) <= BF16_TOL
+    assert rel_to_max(par, one) <= 8e-3
