@@ -618,6 +618,11 @@ def run_profile_case(args) -> None:
         c = (torch.randn(1024, 16, device=dev, generator=gen) / 4).bfloat16()
         y = torch.empty_like(x)
         fn = lambda: ops.diag_scan_fwd(a, x, b, c, None, out=y)  # noqa: E731
+    elif args.profile_case == "linear_deep":  # 2048 -> 2048 at R = 16384: four accumulator segments (285 MB)
+        x = torch.randn(16384, 2048, device=dev, generator=gen)
+        w = torch.randn(2048, 2048, device=dev, generator=gen) / math.sqrt(2048)
+        y = torch.empty(16384, 2048, device=dev)
+        fn = lambda: ops.linear_f32(x, w, out=y)  # noqa: E731
     elif args.profile_case == "prefix":     # all prefix maps of 256 steps over config 3's state, fp32: 537 MB
         ap_ = torch.sigmoid(4 + 0.5 * torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen))
         bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
@@ -648,7 +653,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few"],
+                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
