@@ -171,6 +171,23 @@ def stream_ptr() -> int:
     return int(torch.cuda.current_stream().cuda_stream)
 
 
+def require_device(*tensors) -> None:
+    """Every tensor must be a CUDA tensor on the current device (any layout): the check
+    for operands that are made contiguous later.  A host tensor or one on another GPU
+    would hand the kernel a pointer it cannot legally touch."""
+    import torch
+
+    for t in tensors:
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise B200Error("catopt_b200 executors take CUDA tensors only (no CPU fallback)")
+        if t.device.index != torch.cuda.current_device():
+            raise B200Error(
+                f"tensor on {t.device} but the current device is cuda:{torch.cuda.current_device()}"
+            )
+
+
 def require_cuda(*tensors) -> None:
     """Every tensor must be a contiguous CUDA tensor on the current device."""
     import torch

@@ -218,9 +218,10 @@ def decayed_whole_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ga
     Returns ``None`` when the kernel has no path (fp64, awkward length)."""
     if not q.is_cuda:
         raise B200Error("decayed executor runs on CUDA tensors only (no CPU fallback)")
+    if q.dim() == 2:                       # one head, no batch: q [T, d] with a scalar rate
+        out = decayed_whole_sequence(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), gamma, chunk, scale)
+        return None if out is None else out.squeeze(0)
     lead = q.shape[:-2]
-    if len(lead) == 0:
-        raise B200Error("decayed executor needs at least one leading (head) axis")
     c = kernel_chunk(q.shape[-2], chunk)
     if c is None or q.dtype not in (torch.float32, torch.bfloat16):
         return None

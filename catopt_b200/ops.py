@@ -14,7 +14,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import B200Error, check, dtype_code, require_cuda, stream_ptr
+from ._lib import B200Error, check, dtype_code, require_cuda, require_device, stream_ptr
 
 _scratch: dict[tuple, torch.Tensor] = {}
 _status_words: dict[int, torch.Tensor] = {}
@@ -349,7 +349,7 @@ def diag_compose_apply(a_seq: torch.Tensor, b_seq: torch.Tensor, h: torch.Tensor
     the kernel cannot take the case (dtype other than float32/bfloat16) so the
     caller can keep its own reduction.
     """
-    require_cuda(a_seq, b_seq, h)
+    require_device(a_seq, b_seq, h)
     state_shape = torch.broadcast_shapes(a_seq.shape[1:], b_seq.shape[1:], h.shape)
     n, S = a_seq.shape[0], 1
     for sdim in state_shape:
@@ -386,9 +386,7 @@ def diag_prefix_maps(a_seq: torch.Tensor, b_seq: torch.Tensor):
     cannot take the case (dtype other than float32/bfloat16, or no steps) so the
     caller keeps its own scan.
     """
-    for t in (a_seq, b_seq):      # any layout: broadcast (expanded) operands are welcome
-        if not isinstance(t, torch.Tensor) or not t.is_cuda:
-            raise B200Error("catopt_b200 executors take CUDA tensors only (no CPU fallback)")
+    require_device(a_seq, b_seq)      # any layout: broadcast (expanded) operands are welcome
     state_shape = torch.broadcast_shapes(a_seq.shape[1:], b_seq.shape[1:])
     T, S = a_seq.shape[0], 1
     for sdim in state_shape:
@@ -426,7 +424,7 @@ def diag_fold_apply(a_rows: torch.Tensor, b_rows: torch.Tensor, h: torch.Tensor)
     ``cb2_diag_fold_apply``; a row shared by all steps is read through a zero step
     stride instead of being repeated in memory.
     """
-    require_cuda(h)
+    require_device(h, a_rows, b_rows)
     state_shape = tuple(h.shape)
     S = h.numel()
     dt = h.dtype
@@ -491,10 +489,7 @@ def gated_contract(s: torch.Tensor, g: torch.Tensor, v: torch.Tensor) -> torch.T
     batch dims (``[T,K]``, ``[H,T,K]`` under ``[B,H,T,K]``, ``[B,1,T,K]``) is indexed in
     place; other broadcast patterns are expanded first.
     """
-    require_cuda()
-    for t in (s, g, v):
-        if not isinstance(t, torch.Tensor) or not t.is_cuda:
-            raise B200Error("catopt_b200 executors take CUDA tensors only (no CPU fallback)")
+    require_device(s, g, v)
     if s.dim() < 2 or v.dim() < 2 or s.shape[-1] != v.shape[-2]:
         raise B200Error(f"gated_contract shape mismatch: s {tuple(s.shape)}, v {tuple(v.shape)}")
     dt = s.dtype

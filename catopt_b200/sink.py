@@ -46,7 +46,7 @@ from typing import Any
 import torch
 from catopt_carriers.decayed_lower import build_decayed_plan
 from catopt_carriers.om_lower import _slice_index
-from catopt_core.ir import IR, Const, Op, Param
+from catopt_core.ir import IR, Const, Op, Param, Var
 from catopt_core.ports import ExecutorSpec
 from catopt_core.typing import _shape_of
 from catopt_torch.adapters import TorchSink
@@ -470,15 +470,38 @@ class _EvalBase(_GraphMixin, torch.nn.Module):
         return lambda t: self.eval_mod._eval(t, env, x, memo)
 
 
+def _var_free(t: Any) -> bool:
+    """No input variable below ``t``: its value depends on parameters and constants only."""
+    if isinstance(t, Var):
+        return False
+    return all(_var_free(a) for a in t.args) if isinstance(t, Op) else True
+
+
 class B200ChunkedDecayModule(_EvalBase):
     """Drop-in for ``ChunkedDecayModule`` (decayed_lower.py:381-724): same
     constructor, ``_plan`` / ``is_batched`` / ``n_blocks`` / graph API; the
     forward evaluates the q, k, v bases through ``eval_mod`` and runs
-    ``cb2_decayed_chunk_fwd``.  A non-matching IR degrades to ``eval_mod``."""
+    ``cb2_decayed_chunk_fwd``.  A non-matching IR degrades to ``eval_mod``.
+    A decay rate that depends on parameters only is evaluated once per device and
+    kept as the kernel's per-head fp32 vector (the counterpart of the reference's
+    ``_const`` cache, decayed_lower.py:449-468)."""
 
     def __init__(self, ir: IR, param_values: dict | None = None) -> None:
         super().__init__(ir, param_values)
         self._plan = decayed_plan(self.eval_mod._root)
+        self._const_cache: dict = {}
+        self._gamma_is_const = self._plan is not None and _var_free(self._plan["gamma"])
+
+    def _const(self, term: Any, ev: Any, like: torch.Tensor, heads: int) -> torch.Tensor:
+        """``term`` (Var-free) as a contiguous fp32 vector with one rate per head on
+        ``like``'s device, evaluated once per (device, head count)."""
+        key = ("gamma", term, like.device, heads)
+        g = self._const_cache.get(key)
+        if g is None:
+            g = torch.as_tensor(ev(term), dtype=torch.float32, device=like.device).reshape(-1)
+            g = (g.expand(heads) if g.numel() == 1 else g).contiguous()
+            self._const_cache[key] = g
+        return g
 
     @property
     def is_batched(self) -> bool:
@@ -493,7 +516,11 @@ class B200ChunkedDecayModule(_EvalBase):
         if plan is None:
             return self.eval_mod(*xs)
         ev = self._ev(xs)
-        q, k, v, g = ev(plan["q"]), ev(plan["k"]), ev(plan["v"]), ev(plan["gamma"])
+        q, k, v = ev(plan["q"]), ev(plan["k"]), ev(plan["v"])
+        if self._gamma_is_const and isinstance(q, torch.Tensor) and q.dim() >= 3:
+            g = self._const(plan["gamma"], ev, q, q.shape[-3])
+        else:
+            g = ev(plan["gamma"])
         out = decayed_whole_sequence(q, k, v, g, plan["chunk"], plan["scale"])
         return self.eval_mod(*xs) if out is None else out     # fp64 / awkward length: generic module, same device
 
@@ -724,7 +751,12 @@ class B200LinearChainModule(_EvalBase):
         if self._plan is None:
             return self.eval_mod(*xs)
         x = self._ev(xs)(self._plan["x"])
-        return ops.linear_f32(x.contiguous(), self.fused_weight, self.bias)
+        if not (isinstance(x, torch.Tensor) and x.is_cuda):
+            raise B200Error("B200LinearChainModule runs on CUDA tensors only (no CPU fallback)")
+        if x.dtype != torch.float32 or x.device != self.fused_weight.device:
+            return self.eval_mod(*xs)       # bf16 / fp64 activations: generic module, same device
+        with torch.cuda.device(x.device):
+            return ops.linear_f32(x.contiguous(), self.fused_weight, self.bias)
 
 
 # --------------------------------------------------------------------------- scan
@@ -889,7 +921,15 @@ class B200Sink(TorchSink):
         return self._b200_executors
 
     def verify(self, ref: Any, opt: Any, inputs: Any, *, rtol: float = 1e-4, atol: float | None = None):
-        return b200_verify.verify_module(ref, opt, inputs, rtol=rtol, atol=atol)
+        """``TorchSink.verify`` (adapters.py:126-139) with the comparison of every
+        float32 / bfloat16 CUDA output pair in ``cb2_verify_reduce``.  Pairs the kernel
+        does not take (fp64, integer or host tensors) go to the reference's own gate
+        (``report.verify_equiv``) on the device they live on, so whatever the
+        reference verifies is still gated.  The gate's read-back is also where a
+        bounded device wait that ran out in an earlier kernel raises ``B200Error``."""
+        from catopt_torch.report import verify_equiv as reference_gate
+
+        return b200_verify.verify_module(ref, opt, inputs, rtol=rtol, atol=atol, delegate=reference_gate)
 
 
 def b200_target_profile():

@@ -23,7 +23,11 @@ from ._lib import B200Error
 _REL_FLOOR = 1e-8
 
 __all__ = ["VerifyReport", "rel_diff", "verify_equiv", "verify_module", "verify_batched",
-           "reports_from_result", "merge_across_ranks"]
+           "reports_from_result", "merge_across_ranks", "kernel_takes", "kernel_gate_calls"]
+
+#: how many comparisons ``cb2_verify_reduce`` has served in this process (tests read it to
+#: show that a gate ran on the kernel and not on a delegate)
+kernel_gate_calls = 0
 
 
 @dataclass(frozen=True)
@@ -72,11 +76,33 @@ def _prepare(ref: torch.Tensor, out: torch.Tensor) -> tuple[torch.Tensor, torch.
     return ref2, out2
 
 
-def _verify_pair(ref: torch.Tensor, out: torch.Tensor, rtol: float, atol: float | None) -> VerifyReport:
+def kernel_takes(ref: Any, out: Any) -> bool:
+    """Whether ``cb2_verify_reduce`` can compare this pair: two non-empty CUDA tensors on
+    one device whose difference is float32 or bfloat16."""
+    if not (isinstance(ref, torch.Tensor) and isinstance(out, torch.Tensor)):
+        return False
+    if not (ref.is_cuda and out.is_cuda) or ref.device != out.device:
+        return False
+    if ref.numel() == 0 or out.numel() == 0:
+        return False
+    return torch.result_type(ref, out) in (torch.float32, torch.bfloat16)
+
+
+def _verify_pair(ref: torch.Tensor, out: torch.Tensor, rtol: float, atol: float | None,
+                 delegate: Any = None) -> VerifyReport:
     # max|ref| is taken over ref's own elements; broadcasting ref does not change it.
+    global kernel_gate_calls
+    if delegate is not None and not kernel_takes(ref, out):
+        return delegate(ref, out, rtol=rtol, atol=atol)
     ref2, out2 = _prepare(ref, out)
-    res = ops.verify_reduce(ref2, out2, 1)
-    return reports_from_result(res, rtol, atol)[0]
+    with torch.cuda.device(ref2.device):
+        res = ops.verify_reduce(ref2, out2, 1)
+        rep = reports_from_result(res, rtol, atol)[0]
+        # the read-back above synchronised: a bounded wait that ran out in any kernel
+        # launched before this gate on the device surfaces here
+        ops.check_device_status(ref2.device)
+    kernel_gate_calls += 1
+    return rep
 
 
 def _flatten_outputs(x: Any) -> list:
@@ -88,19 +114,25 @@ def _flatten_outputs(x: Any) -> list:
     return [x]
 
 
-def verify_equiv(ref_out: Any, out: Any, rtol: float = 1e-4, atol: float | None = None) -> VerifyReport:
+def verify_equiv(ref_out: Any, out: Any, rtol: float = 1e-4, atol: float | None = None,
+                 delegate: Any = None) -> VerifyReport:
     """Compare two already-computed outputs (tensor or tuple/list of tensors).
 
     Multi-output: both sides are flattened; a different number of outputs fails
     closed with ``inf``; the scalars are the worst case and ``per_output`` lists
     each output's ``max_abs``.
+
+    ``delegate(ref, out, rtol=, atol=)``: who compares a pair the kernel does not take
+    (fp64, integer or host tensors).  Without one such a pair raises ``B200Error``; the
+    catopt-facing sink passes the reference's own gate, so a model the reference can
+    verify is still gated.
     """
     if not isinstance(ref_out, (tuple, list)):
-        return _verify_pair(ref_out, out, rtol, atol)
+        return _verify_pair(ref_out, out, rtol, atol, delegate)
     ref_flat, out_flat = _flatten_outputs(ref_out), _flatten_outputs(out)
     if not isinstance(out, (tuple, list)) or len(out_flat) != len(ref_flat):
         return VerifyReport(max_abs=float("inf"), max_rel=float("inf"), passed=False)
-    reports = [verify_equiv(r, o, rtol=rtol, atol=atol) for r, o in zip(ref_flat, out_flat)]
+    reports = [verify_equiv(r, o, rtol=rtol, atol=atol, delegate=delegate) for r, o in zip(ref_flat, out_flat)]
     return VerifyReport(
         max_abs=max(r.max_abs for r in reports),
         max_rel=max(r.max_rel for r in reports),
@@ -115,15 +147,16 @@ def rel_diff(a: torch.Tensor, b: torch.Tensor) -> float:
 
 
 def verify_module(ref_mod: torch.nn.Module, opt_mod: torch.nn.Module, inputs: Any,
-                  rtol: float = 1e-4, atol: float | None = None) -> VerifyReport:
-    """Run both modules on (cloned) ``inputs`` under ``no_grad`` and compare."""
+                  rtol: float = 1e-4, atol: float | None = None, delegate: Any = None) -> VerifyReport:
+    """Run both modules on (cloned) ``inputs`` under ``no_grad`` and compare
+    (``delegate``: see ``verify_equiv``)."""
     args = inputs if isinstance(inputs, tuple) else (inputs,)
     ref_mod.eval()
     opt_mod.eval()
     with torch.no_grad():
         ref = ref_mod(*[a.clone() if isinstance(a, torch.Tensor) else a for a in args])
         out = opt_mod(*[a.clone() if isinstance(a, torch.Tensor) else a for a in args])
-    return verify_equiv(ref, out, rtol=rtol, atol=atol)
+    return verify_equiv(ref, out, rtol=rtol, atol=atol, delegate=delegate)
 
 
 def verify_batched(ref: torch.Tensor, out: torch.Tensor, n_checks: int, *, rtol: float = 1e-4,

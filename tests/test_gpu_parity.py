@@ -414,7 +414,62 @@ def test_decayed_config4_full_size_is_invariant_under_head_segmentation(dev):
     assert torch.equal(seg.view(torch.int16), other.view(torch.int16))
     assert torch.isfinite(seg[::5, ::7].float()).all()
     ops.check_device_status(dev)
+    # 32 of the 512 (batch, head) slices of that full-size result against the reference's
+    # pairwise-chunked algorithm, computed in fp32 on the same bf16-rounded inputs: the first
+    # and the last batch entry at heads 0, 15 and 31 (slowest, middle and fastest decay),
+    # and 26 seeded draws from the rest
+    picks = [(b, h) for b in (0, B - 1) for h in (0, 15, 31)]
+    rng = np.random.default_rng(44)
+    while len(picks) < 32:
+        bh = (int(rng.integers(B)), int(rng.integers(H)))
+        if bh not in picks:
+            picks.append(bh)
+    worst = 0.0
+    for b, h in picks:
+        qs, ks, vs = (t[b:b + 1, h:h + 1].float().cpu() for t in (q, k, v))
+        want = oracle.decayed_chunked_pairwise(qs, ks, vs, gam[h:h + 1].cpu(), 128, 1.0)
+        r = rel_to_max(seg[b:b + 1, h:h + 1], want)
+        worst = max(worst, r)
+        assert r <= BF16_TOL, (b, h, r)
+    assert 0.0 < worst <= BF16_TOL
     del q, k, v, seg, one, other
+    torch.cuda.empty_cache()
+
+
+def test_scan_config3_full_size_sampled_against_the_serial_oracle(dev):
+    """Benchmark config 3 at full size (B=8, T=4096, D=1024, N=16, bf16 in, fp32 state;
+    a alone is 1 GiB): one launch, then 64 channels of EVERY batch entry — channel 0,
+    the last one, both sides of the first and the last 32-channel block boundary, and
+    seeded draws — against the serial fold of the reference's bindings, for every step
+    of y and for the final state."""
+    from catopt_b200 import ops
+
+    B, T, D, N = 8, 4096, 1024, 16
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(B, T, D, device=dev, generator=g).bfloat16()
+    a = torch.empty(B, T, D, N, device=dev, dtype=torch.bfloat16)
+    for bi in range(B):             # built per batch entry: the fp32 draw of the whole tensor would be 2 GiB
+        a[bi] = torch.sigmoid(4 + 0.5 * torch.randn(T, D, N, device=dev, generator=g)).bfloat16()
+    b = (torch.randn(D, N, device=dev, generator=g) / 4).bfloat16()
+    c = (torch.randn(D, N, device=dev, generator=g) / 4).bfloat16()
+    y, hT = ops.diag_scan_fwd(a, x, b, c, None, want_state=True)
+    ops.check_device_status(dev)
+    rng = np.random.default_rng(33)
+    ch = {0, 31, 32, 991, 992, D - 1}
+    while len(ch) < 64:
+        ch.add(int(rng.integers(D)))
+    ch = torch.tensor(sorted(ch), device=dev)
+    a_s, x_s = a.index_select(2, ch).cpu(), x.index_select(2, ch).cpu()
+    want_y, want_h = oracle.diag_scan_serial(a_s, x_s, b.index_select(0, ch).cpu(), c.index_select(0, ch).cpu())
+    got_y, got_h = y.index_select(2, ch), hT.index_select(1, ch)
+    for bi in range(B):
+        assert rel_to_max(got_y[bi], want_y[bi]) <= BF16_TOL, bi
+        assert rel_to_max(got_h[bi], want_h[bi]) <= FP32_TOL, bi
+    # element by element: y is the fp32 readout rounded once to bf16, so every value sits within one
+    # bf16 ulp of the oracle's fp32 value (plus the fp32 summation-order noise of the 16-term readout)
+    err = (got_y.float().cpu() - want_y).abs()
+    assert (err <= want_y.abs() * 2.0 ** -7 + 2e-5 * want_y.abs().max()).all()
+    del a, x, y
     torch.cuda.empty_cache()
 
 

@@ -1,19 +1,19 @@
 """Routing and plan extraction of catopt_b200.sink against the real catopt
 package.  CPU only (no kernel runs); skipped when catopt is not importable."""
-import glob
 import os
 import sys
 
 import pytest
 import torch
 
-# catopt's source tree: $CATOPT_SRC, else a "reference" checkout next to this repository
+sys.path.insert(0, os.path.dirname(__file__))
+import _catopt_path  # noqa: E402
+
+if _catopt_path.add_catopt_to_path() is None:
+    pytest.skip(_catopt_path.SKIP_REASON, allow_module_level=True)
+
+# a source checkout (not just an install) also carries the reference's own test helpers
 _REF = os.environ.get("CATOPT_SRC") or os.path.join(os.path.dirname(__file__), "..", "..", "reference")
-for _p in glob.glob(os.path.join(_REF, "packages", "*", "src")):
-    if _p not in sys.path:
-        sys.path.insert(0, _p)
-pytest.importorskip("catopt_core", reason="catopt source tree not available")
-pytest.importorskip("catopt_carriers")
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
 import make_golden  # noqa: E402
