@@ -66,6 +66,11 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
          C.c_longlong, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p],
     ),
+    "cb2_diag_scan_states": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
+         C.c_longlong, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p],
+    ),
     "cb2_gated_contract_on_tensor_cores": (
         C.c_int, [C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int],
     ),

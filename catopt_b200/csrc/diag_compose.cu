@@ -160,11 +160,14 @@ compose_apply_kernel(const float* __restrict__ part_a, const float* __restrict__
 // When the state alone gives too few threads, the steps are cut into segments (blockIdx.y): the
 // segments' total maps come from compose_partial_kernel<CHRONO> first, and a segment starts from
 // the fold of the totals before it instead of the identity (a and b are then read twice).
-template <int DTYPE, bool VEC>
+// STATES: the same walk started from an initial state h0 instead of the identity map, storing
+// only the running state (pb = every h_t; pa is not touched): 3 units of traffic per step.
+template <int DTYPE, bool VEC, bool STATES>
 __global__ void __launch_bounds__(128)
 prefix_maps_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ pa,
                    void* __restrict__ pb, long long n, long long S, long long a_stride, long long b_stride,
-                   long long seg_len, const float* __restrict__ part_a, const float* __restrict__ part_b) {
+                   long long seg_len, const float* __restrict__ part_a, const float* __restrict__ part_b,
+                   const void* __restrict__ h0) {
   using V = Vec<DTYPE>;
   constexpr int E = VEC ? V::kElems : 1;
   const long long c0 = (blockIdx.x * 128ll + threadIdx.x) * E;
@@ -173,7 +176,7 @@ prefix_maps_kernel(const void* __restrict__ a, const void* __restrict__ b, void*
   n = j0 + seg_len < n ? j0 + seg_len : n;     // this segment's steps are [j0, n)
   float A[E], B[E];
 #pragma unroll
-  for (int e = 0; e < E; ++e) { A[e] = 1.f; B[e] = 0.f; }
+  for (int e = 0; e < E; ++e) { A[e] = 1.f; B[e] = STATES ? V::ld1(h0, size_t(c0) + e) : 0.f; }
   for (unsigned sgm = 0; sgm < blockIdx.y; ++sgm) {
     const size_t i = size_t(sgm) * size_t(S) + size_t(c0);
 #pragma unroll
@@ -190,10 +193,10 @@ prefix_maps_kernel(const void* __restrict__ a, const void* __restrict__ b, void*
     }
     const size_t off = size_t(j) * size_t(S) + size_t(c0);
     if constexpr (VEC) {
-      V::st(pa, off, A);
+      if constexpr (!STATES) V::st(pa, off, A);
       V::st(pb, off, B);
     } else {
-      V::st1(pa, off, A[0]);
+      if constexpr (!STATES) V::st1(pa, off, A[0]);
       V::st1(pb, off, B[0]);
     }
   };
@@ -247,11 +250,11 @@ int prefix_segments(long long n, long long S, int elems_per_thread) {
   return int(want);
 }
 
-template <int DTYPE>
+template <int DTYPE, bool STATES = false>
 int run_prefix(const void* a, const void* b, void* pa, void* pb, long long n, long long S, long long a_stride,
-               long long b_stride, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+               long long b_stride, void* scratch, size_t scratch_bytes, cudaStream_t st, const void* h0 = nullptr) {
   using V = Vec<DTYPE>;
-  const bool vec = S % V::kElems == 0 && aligned16(a) && aligned16(b) && aligned16(pa) && aligned16(pb);
+  const bool vec = S % V::kElems == 0 && aligned16(a) && aligned16(b) && (STATES || aligned16(pa)) && aligned16(pb);
   const int E = vec ? V::kElems : 1;
   const long long threads = S / E;
   const long long blocks = (threads + 127) / 128;
@@ -274,11 +277,11 @@ int run_prefix(const void* a, const void* b, void* pa, void* pb, long long n, lo
   }
   const dim3 grid{unsigned(blocks), unsigned(nseg), 1u};
   if (vec)
-    prefix_maps_kernel<DTYPE, true><<<grid, 128, 0, st>>>(a, b, pa, pb, n, S, a_stride, b_stride, seg_len,
-                                                          part_a, part_b);
+    prefix_maps_kernel<DTYPE, true, STATES><<<grid, 128, 0, st>>>(a, b, pa, pb, n, S, a_stride, b_stride, seg_len,
+                                                                  part_a, part_b, h0);
   else
-    prefix_maps_kernel<DTYPE, false><<<grid, 128, 0, st>>>(a, b, pa, pb, n, S, a_stride, b_stride, seg_len,
-                                                           part_a, part_b);
+    prefix_maps_kernel<DTYPE, false, STATES><<<grid, 128, 0, st>>>(a, b, pa, pb, n, S, a_stride, b_stride,
+                                                                   seg_len, part_a, part_b, h0);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }
@@ -405,5 +408,28 @@ extern "C" int cb2_diag_prefix_maps(const void* a_rows, const void* b_rows, void
   if (dtype == CB2_BF16)
     return cb2::run_prefix<CB2_BF16>(a_rows, b_rows, pa, pb, n, S, a_step_stride, b_step_stride, scratch,
                                      scratch_bytes, st);
+  return CB2_UNSUPPORTED_DTYPE;
+}
+
+// Every state of a diagonal recurrence over time-ordered step rows: out[t] = a_t*out[t-1] + b_t with
+// out[-1] = h — the value of `applyd(aff_diag(stack(affd_a f_t), stack(affd_b f_t)), h)` over the
+// prefix maps f_t = leaf_t . f_(t-1), the stacked-map form `gather_applyd_stack` offers for an
+// unrolled scan (catopt_carriers/xcarrier.py:2252-2275), which the reference evaluates one compose
+// per step.  One pass: a and b read once, the states written once (fp32 running state); segments
+// through scratch as in cb2_diag_prefix_maps (same scratch query).
+extern "C" int cb2_diag_scan_states(const void* a_rows, const void* b_rows, const void* h, void* out, long long n,
+                                    long long S, long long a_step_stride, long long b_step_stride, int dtype,
+                                    void* scratch, size_t scratch_bytes, void* stream) {
+  if (!a_rows || !b_rows || !h || !out) return CB2_NULL_PTR;
+  if (n <= 0 || S <= 0 || S > (1ll << 40) / n) return CB2_BAD_SHAPE;
+  if ((a_step_stride != 0 && a_step_stride != S) || (b_step_stride != 0 && b_step_stride != S))
+    return CB2_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CB2_F32)
+    return cb2::run_prefix<CB2_F32, true>(a_rows, b_rows, nullptr, out, n, S, a_step_stride, b_step_stride, scratch,
+                                          scratch_bytes, st, h);
+  if (dtype == CB2_BF16)
+    return cb2::run_prefix<CB2_BF16, true>(a_rows, b_rows, nullptr, out, n, S, a_step_stride, b_step_stride,
+                                           scratch, scratch_bytes, st, h);
   return CB2_UNSUPPORTED_DTYPE;
 }

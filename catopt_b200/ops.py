@@ -414,6 +414,43 @@ def diag_prefix_maps(a_seq: torch.Tensor, b_seq: torch.Tensor):
     return pa, pb
 
 
+def diag_scan_states(a_seq: torch.Tensor, b_seq: torch.Tensor, h: torch.Tensor) -> torch.Tensor | None:
+    """Every state of ``h_t = a_t*h_(t-1) + b_t`` from ``h_(-1) = h``.
+
+    ``a_seq``/``b_seq`` are ``[T, *state]`` in time order (broadcastable against each
+    other and ``h``; an operand shared by every step is read in place), the result is
+    ``[T, *state]`` — the stacked-map form ``applyd(aff_diag(stack affd_a f_t, stack
+    affd_b f_t), h)`` that ``gather_applyd_stack`` (catopt_carriers/xcarrier.py:2252-2275)
+    offers for an unrolled scan.  One pass of ``cb2_diag_scan_states``.  ``None`` when the
+    kernel cannot take the case (dtype other than float32/bfloat16, no steps)."""
+    require_device(a_seq, b_seq, h)
+    state_shape = torch.broadcast_shapes(a_seq.shape[1:], b_seq.shape[1:], h.shape)
+    T, S = a_seq.shape[0], 1
+    for sdim in state_shape:
+        S *= sdim
+    dt = torch.promote_types(torch.promote_types(a_seq.dtype, b_seq.dtype), h.dtype)
+    if dt not in (torch.float32, torch.bfloat16) or T == 0 or S == 0 or b_seq.shape[0] != T:
+        return None
+
+    def rows(x: torch.Tensor) -> tuple[torch.Tensor, int]:
+        x = x.to(dt).expand(T, *state_shape)
+        if T > 1 and x.stride(0) == 0:          # one row shared by every step
+            return x[0].reshape(S).contiguous(), 0
+        return x.reshape(T, S).contiguous(), S
+
+    a, a_stride = rows(a_seq)
+    b, b_stride = rows(b_seq)
+    hh = h.to(dt).expand(state_shape).reshape(S).contiguous()
+    out = torch.empty(T, *state_shape, dtype=dt, device=a.device)
+    lib = _lib.load()
+    need = lib.cb2_diag_prefix_maps_scratch_bytes(T, S, dtype_code(dt))
+    scratch = _scratch_buf("prefix", need, a.device)
+    rc = lib.cb2_diag_scan_states(a.data_ptr(), b.data_ptr(), hh.data_ptr(), out.data_ptr(), T, S, a_stride,
+                                  b_stride, dtype_code(dt), _ptr(scratch), need, stream_ptr())
+    check(rc, "cb2_diag_scan_states")
+    return out
+
+
 def diag_fold_apply(a_rows: torch.Tensor, b_rows: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
     """Fold ``h <- a_t*h + b_t`` over rows in TIME order and return the last state.
 

@@ -3,7 +3,7 @@
 catopt routes an extracted term to the first ``ExecutorSpec`` of
 ``Sink.executors`` whose ``carrier`` is not ``None`` and whose ``accepts(term)``
 is true (catopt_orchestrator/optimize.py:485-495); mapping order is routing
-order.  ``B200Sink`` puts six B200 specs in front of the torch ones:
+order.  ``B200Sink`` puts seven B200 specs in front of the torch ones:
 
 * ``b200_om_decayed_chunked`` — the uniform K-chunk decayed term of
   ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152).  ``accepts``
@@ -27,6 +27,11 @@ order.  ``B200Sink`` puts six B200 specs in front of the torch ones:
   terms ``lift_scan_to_applyd`` creates); the reference's own plan builder and
   leaf stacking are reused, the composed-map reduction runs in
   ``cb2_diag_compose_apply`` (one pass over the stacked leaves).
+* ``b200_scan_all`` — every state of an unrolled diagonal scan in the stacked-map
+  form ``applyd(aff_diag(stack(affd_a f_t), stack(affd_b f_t)), h)`` that
+  ``gather_applyd_stack`` offers (xcarrier.py:2252-2275), one ``cb2_diag_scan_states``;
+  with the per-step readout ``sum(mul(., c), -1)`` around it, one ``cb2_diag_scan_fwd``.
+  Tried before ``b200_scan``, whose plan builder would take the form as a one-leaf tree.
 * ``b200_omd`` — deferred-affine attention ``omd_apply(<omd tree>, h)``: the
   reference's ``BatchedOmdModule`` with its all-prefix scan of the diagonal step
   maps (``_prefix_scan``) running in ``cb2_diag_prefix_maps`` (one pass).
@@ -59,7 +64,8 @@ from .executors import _GraphMixin, causal_softmax_blocks, decayed_whole_sequenc
 
 __all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "decayed_ragged_plan",
            "decayed_plan", "om_causal_plan", "linear_chain_plan", "scan_diag_plan",
-           "B200ChunkedDecayModule", "B200CausalSoftmaxModule", "B200LinearChainModule"]
+           "scan_states_plan", "B200ChunkedDecayModule", "B200CausalSoftmaxModule", "B200LinearChainModule",
+           "B200ScanStatesModule"]
 
 
 # --------------------------------------------------------------------------- decayed
@@ -808,6 +814,217 @@ def _make_scan_module():
     return B200ScanModule
 
 
+# --------------------------------------------------------------------------- scan, every state
+def _prefix_chain_leaves(fs: list) -> list | None:
+    """Maps ``f_t`` that are the running compositions of one leaf sequence —
+    ``f_0 = leaf_0``, ``f_t = affd_compose(leaf_t, f_(t-1))`` (any nesting of the same
+    product for short sequences) — to the leaves in time order; ``None`` otherwise."""
+    leaves: list = []
+    for t, f in enumerate(fs):
+        if t == 0:
+            if not (isinstance(f, Op) and f.op == "aff_diag" and len(f.args) == 2):
+                return None
+            leaves.append(f)
+            continue
+        if not (isinstance(f, Op) and f.op == "affd_compose" and len(f.args) == 2):
+            return None
+        new, rest = f.args
+        if rest == fs[t - 1] and isinstance(new, Op) and new.op == "aff_diag" and len(new.args) == 2:
+            leaves.append(new)
+            continue
+        if len(fs) > 256:
+            return None
+        flat = _flatten(f, "affd_compose")                 # product order: latest step first
+        if len(flat) != t + 1 or flat[1:] != leaves[::-1]:
+            return None
+        if not (isinstance(flat[0], Op) and flat[0].op == "aff_diag" and len(flat[0].args) == 2):
+            return None
+        leaves.append(flat[0])
+    return leaves
+
+
+def _per_step_operand(terms: list, memo: dict) -> tuple | None:
+    """How to hand T per-step operand terms to a kernel without T evaluations:
+    ``("shared", term)`` when every step uses the same term, ``("gather", base, dim)``
+    when step t is ``select(base, dim, t)`` of one tensor with T entries along ``dim``,
+    else ``("stack", terms)``."""
+    if all(t == terms[0] for t in terms[1:]) and len(terms) > 1:
+        return ("shared", terms[0])
+    base = dim = None
+    for i, t in enumerate(terms):
+        if not (isinstance(t, Op) and t.op == "select" and len(t.args) == 1 and t.attrs.get("index") == i):
+            base = None
+            break
+        d = _norm_dim(t.args[0], t.attrs.get("dim"), memo)
+        if d is None or (base is not None and (t.args[0] != base or d != dim)):
+            base = None
+            break
+        base, dim = t.args[0], d
+    if base is not None:
+        shape = _shape_of(base, memo)
+        if isinstance(shape, tuple) and shape[dim] == len(terms):
+            return ("gather", base, dim)
+    return ("stack", list(terms))
+
+
+def scan_states_plan(root: Any) -> dict | None:
+    """Recognise the stacked-map form of an unrolled diagonal scan,
+
+        applyd(aff_diag(stack(affd_a f_0 .. f_(T-1), dim=D), stack(affd_b f_0 .. f_(T-1), dim=D)), h)
+
+    with ``f_t`` the prefix maps of one leaf sequence ``aff_diag(a_t, b_t)`` — what
+    ``gather_applyd_stack`` (catopt_carriers/xcarrier.py:2252-2275) offers for
+    ``stack(h_1 .. h_T)`` once ``lift_scan_to_applyd`` has written every ``h_t`` as an
+    application to the shared initial state.  Its value is every state of
+    ``h_t = a_t*h_(t-1) + b_t``, stacked along ``D``.
+
+    Also recognised, one level up: the per-step readout ``sum(mul(<that form>, c), dim=-1)``
+    of a ``[B, D, N]`` state stacked along dim 1 whose offsets are ``b * unsqueeze(x_t, -1)``
+    with ``x_t = select(x, 1, t)`` — benchmark config 3's recurrence
+    ``y_t = sum_n c*h_t``, which is exactly ``cb2_diag_scan_fwd``.
+
+    Returns ``{a, b, h, n, stack_dim, state_shape, readout}`` (``a``/``b`` as
+    ``_per_step_operand`` tuples; ``readout`` ``None`` or ``{x, b, c}``), or ``None``."""
+    memo: dict = {}
+    readout_c = None
+    states = root
+    if isinstance(root, Op) and root.op == "sum" and len(root.args) == 1 and not root.attrs.get("keepdim"):
+        body = root.args[0]
+        rdim = root.attrs.get("dim")
+        if isinstance(rdim, (tuple, list)) and len(rdim) == 1:
+            rdim = rdim[0]
+        rd = _norm_dim(body, rdim, memo)
+        if rd != -1 or not (isinstance(body, Op) and body.op == "mul" and len(body.args) == 2):
+            return None
+        x0, x1 = body.args
+        states, readout_c = (x0, x1) if isinstance(x0, Op) and x0.op == "applyd" else (x1, x0)
+    if not (isinstance(states, Op) and states.op == "applyd" and len(states.args) == 2):
+        return None
+    fmap, h = states.args
+    if not (isinstance(fmap, Op) and fmap.op == "aff_diag" and len(fmap.args) == 2):
+        return None
+    sa, sb = fmap.args
+    if not all(isinstance(t, Op) and t.op == "stack" and len(t.args) >= 2 for t in (sa, sb)):
+        return None
+    if len(sa.args) != len(sb.args) or sa.attrs.get("dim", 0) != sb.attrs.get("dim", 0):
+        return None
+    fs = []
+    for pa, pb in zip(sa.args, sb.args):
+        if not (isinstance(pa, Op) and pa.op == "affd_a" and isinstance(pb, Op) and pb.op == "affd_b"
+                and len(pa.args) == 1 and pa.args == pb.args):
+            return None
+        fs.append(pa.args[0])
+    leaves = _prefix_chain_leaves(fs)
+    if leaves is None:
+        return None
+    T = len(leaves)
+    shapes = {_shape_of(lf.args[0], memo) for lf in leaves} | {_shape_of(lf.args[1], memo) for lf in leaves}
+    if len(shapes) != 1:
+        return None
+    state_shape = shapes.pop()
+    if not (isinstance(state_shape, tuple) and state_shape and all(isinstance(z, int) for z in state_shape)):
+        return None
+    hshape = _shape_of(h, memo)
+    try:
+        if not isinstance(hshape, tuple) or torch.broadcast_shapes(hshape, state_shape) != torch.Size(state_shape):
+            return None
+    except RuntimeError:
+        return None
+    sd = sa.attrs.get("dim", 0)
+    if not isinstance(sd, int):
+        return None
+    sd = sd % (len(state_shape) + 1)
+    plan = {"a": _per_step_operand([lf.args[0] for lf in leaves], memo),
+            "b": _per_step_operand([lf.args[1] for lf in leaves], memo),
+            "h": h, "n": T, "stack_dim": sd, "state_shape": state_shape, "readout": None}
+    if readout_c is None:
+        return plan
+    # the readout form must be the kernel's own recurrence
+    if len(state_shape) != 3 or sd != 1 or _shape_of(readout_c, memo) != state_shape[1:]:
+        return None
+    xs, bcoef = [], None
+    for lf in leaves:
+        u = lf.args[1]
+        if not (isinstance(u, Op) and u.op == "mul" and len(u.args) == 2):
+            return None
+        for coef, xt in (u.args, u.args[::-1]):
+            if isinstance(xt, Op) and xt.op == "unsqueeze" and _norm_dim(xt, xt.attrs.get("dim"), memo) == -1 \
+                    and _shape_of(coef, memo) == state_shape[1:]:
+                break
+        else:
+            return None
+        if bcoef is not None and coef != bcoef:
+            return None
+        bcoef = coef
+        xs.append(xt.args[0])
+    xop = _per_step_operand(xs, memo)
+    if xop[0] != "gather" or xop[2] != -2 or plan["a"][0] != "gather" or plan["a"][2] != -3:
+        return None
+    plan["readout"] = {"x": xop[1], "b": bcoef, "c": readout_c}
+    return plan
+
+
+class B200ScanStatesModule(_EvalBase):
+    """Executor for ``scan_states_plan`` terms.  The reference has no batched module
+    for them (its generic ``IRModule`` composes one prefix map per step, T launches);
+    here the step operands are taken whole — a ``select`` sequence hands over its base
+    tensor, a shared operand is read in place — and every state comes out of one
+    ``cb2_diag_scan_states`` pass, or, for the readout form, every ``y_t`` out of one
+    ``cb2_diag_scan_fwd`` pass (the kernel of benchmark config 3).  fp64 tensors and a
+    non-matching IR degrade to ``eval_mod``."""
+
+    def __init__(self, ir: IR, param_values: dict | None = None) -> None:
+        super().__init__(ir, param_values)
+        self._plan = scan_states_plan(self.eval_mod._root)
+        self.kernel_calls = 0
+
+    @property
+    def is_batched(self) -> bool:
+        return self._plan is not None
+
+    @property
+    def n_levels(self) -> int:
+        return 0 if self._plan is None else 1
+
+    @staticmethod
+    def _rows(spec: tuple, ev: Any, T: int) -> torch.Tensor:
+        """The step operand as a ``[T, ...]`` tensor (a view when it can be one)."""
+        if spec[0] == "shared":
+            v = ev(spec[1])
+            return v.unsqueeze(0).expand(T, *v.shape)
+        if spec[0] == "gather":
+            return ev(spec[1]).movedim(spec[2], 0)
+        return torch.stack([ev(t) for t in spec[1]])
+
+    def _forward_impl(self, *xs: torch.Tensor) -> Any:
+        plan = self._plan
+        if plan is None:
+            return self.eval_mod(*xs)
+        ev = self._ev(xs)
+        T = plan["n"]
+        rd = plan["readout"]
+        if rd is not None:
+            a, x, b, c, h = ev(plan["a"][1]), ev(rd["x"]), ev(rd["b"]), ev(rd["c"]), ev(plan["h"])
+            if not a.is_cuda:
+                raise B200Error("B200ScanStatesModule runs on CUDA tensors only (no CPU fallback)")
+            dt = a.dtype
+            if dt not in (torch.float32, torch.bfloat16) or not (x.dtype == b.dtype == c.dtype == dt):
+                return self.eval_mod(*xs)
+            B_, D_, N_ = plan["state_shape"]
+            h0 = torch.as_tensor(h, device=a.device).to(torch.float32).expand(B_, D_, N_).contiguous()
+            out = ops.diag_scan_fwd(a.contiguous(), x.contiguous(), b.contiguous(), c.contiguous(), h0)
+            self.kernel_calls += 1
+            return out
+        a_rows, b_rows, h = self._rows(plan["a"], ev, T), self._rows(plan["b"], ev, T), ev(plan["h"])
+        if not b_rows.is_cuda:
+            raise B200Error("B200ScanStatesModule runs on CUDA tensors only (no CPU fallback)")
+        out = ops.diag_scan_states(a_rows, b_rows, torch.as_tensor(h, device=b_rows.device))
+        if out is None:                    # fp64: the generic module on the same device
+            return self.eval_mod(*xs)
+        self.kernel_calls += 1
+        return out.movedim(0, plan["stack_dim"])
+
+
 # --------------------------------------------------------------------------- omd (deferred-affine attention)
 def _make_omd_module():
     from catopt_carriers.omd_lower import BatchedOmdModule
@@ -893,6 +1110,14 @@ class B200Sink(TorchSink):
                     lambda term: om_causal_plan(term) is not None,
                     lambda m: bool(getattr(m, "is_streaming", False)),
                     (frozenset({"om_apply"}), frozenset({"om_compose"}), frozenset({"om", "om_elem"})),
+                ),
+                "b200_scan_all": ExecutorSpec(
+                    "b200_scan_all",
+                    lambda ir, p: B200ScanStatesModule(ir, param_values=p),
+                    lambda term: scan_states_plan(term) is not None,
+                    _engaged,
+                    (frozenset({"applyd", "sum"}), frozenset({"affd_compose", "stack", "affd_a", "affd_b"}),
+                     frozenset({"aff_diag"})),
                 ),
                 "b200_scan": ExecutorSpec(
                     "b200_scan",

@@ -243,6 +243,21 @@ int cb2_diag_prefix_maps(const void* a_rows, const void* b_rows, void* pa, void*
                          long long b_step_stride, int dtype, void* scratch,
                          size_t scratch_bytes, void* stream);
 
+/* Every state of the recurrence over rows in time order: out[t] = a_t*out[t-1] + b_t,
+ * out[-1] = h.  This is the value of the stacked-map form
+ * `applyd(aff_diag(stack(affd_a f_t), stack(affd_b f_t)), h)` with f_t the prefix
+ * maps of an unrolled scan, which `gather_applyd_stack`
+ * (packages/catopt-carriers/src/catopt_carriers/xcarrier.py:2252-2275, engine
+ * 2125-2249) offers for a `stack` of per-step states and the reference's generic
+ * module evaluates with one `affd_compose` per step.  a_rows, b_rows: [n,S] with the
+ * step strides of cb2_diag_fold_apply; h: [S]; out: [n,S]; fp32 running state;
+ * 3 units of traffic per step.  Scratch: cb2_diag_prefix_maps_scratch_bytes (segments
+ * when the state alone cannot fill the GPU), may be NULL. */
+int cb2_diag_scan_states(const void* a_rows, const void* b_rows, const void* h, void* out,
+                         long long n, long long S, long long a_step_stride,
+                         long long b_step_stride, int dtype, void* scratch,
+                         size_t scratch_bytes, void* stream);
+
 /* -------------------------------------------------------------------------
  * Gated contraction  o[b] = (s[b] * g[gate(b)]) @ v[b] :  the body of the
  * reference's `om_decayed` element, `(s * d) @ v`

@@ -287,6 +287,23 @@ def seq_fold(a_rows, b_rows, h, axis: int = 0):
     return acc
 
 
+def scan_states(a_rows, b_rows, h):
+    """Every state of the sequence form: `h_t = applyd(aff_diag(a_t, b_t), h_(t-1))`
+    stacked along dim 0 — the value of the stacked-map member
+    `applyd(aff_diag(stack(affd_a f_t), stack(affd_b f_t)), h)` that
+    `gather_applyd_stack` offers (catopt_carriers/xcarrier.py:2252-2275), whose
+    prefix maps f_t the reference composes with `affd_compose`
+    (torch_bridge.py:1896-1899: `(f0*g0, f0*g1 + f1)`, g applied first)."""
+    full = torch.broadcast_shapes(a_rows.shape, b_rows.shape, (1, *h.shape))
+    a_rows, b_rows = a_rows.expand(full), b_rows.expand(full)
+    fa, fb = a_rows[0], b_rows[0]
+    out = [applyd((fa, fb), h)]
+    for t in range(1, full[0]):
+        fa, fb = affd_compose((a_rows[t], b_rows[t]), (fa, fb))
+        out.append(applyd((fa, fb), h))
+    return torch.stack(out)
+
+
 def fused_diag_levels(a_seq, b_seq, h):
     """`fused_diag_levels` (catopt_carriers/scan_fused.py:100-120): leaves in
     product order (latest step first), identity padding to a power of two,

@@ -259,6 +259,35 @@ def gen_verify() -> None:
     np.savez_compressed(HERE / "verify.npz", **out)
 
 
+def gen_states() -> None:
+    """The stacked-map member `applyd(aff_diag(stack(affd_a f_t), stack(affd_b f_t)), h)` over the
+    prefix chain f_t = affd_compose(leaf_t, f_(t-1)) — the form `gather_applyd_stack` offers
+    (catopt_carriers/xcarrier.py:2252-2275) — evaluated by the reference's generic module."""
+    from catopt_core.ir import IR, Op, TensorType, Var
+    from catopt_torch.torch_bridge import IRModule
+
+    out = {}
+    for name in ("per_step_f32", "shared_decay_f32", "per_step_bf16"):
+        a, b, h = cases.fold_inputs(name)
+        n, state = cases.FOLD_CASES[name][:2]
+        tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+        av, bv, hv = Var("a", tt(*a.shape)), Var("b", tt(*b.shape)), Var("h", tt(*state))
+        step = lambda v, full, t: Op.make("select", v, dim=0, index=t) if full else v  # noqa: E731
+        leaves = [Op.make("aff_diag", step(av, a.dim() == len(state) + 1, t), step(bv, b.dim() == len(state) + 1, t))
+                  for t in range(n)]
+        fs = [leaves[0]]
+        for lf in leaves[1:]:
+            fs.append(Op.make("affd_compose", lf, fs[-1]))
+        root = Op.make("applyd", Op.make("aff_diag", Op.make("stack", *(Op.make("affd_a", f) for f in fs), dim=0),
+                                         Op.make("stack", *(Op.make("affd_b", f) for f in fs), dim=0)), hv)
+        ir = IR(root=root, inputs=[av, bv, hv], input_names={"a", "b", "h"}, params={})
+        with torch.no_grad():
+            val = IRModule(ir, None)(a, b, h)
+        out[f"states.{name}"] = _np(val)
+        print(f"states {name}: {tuple(val.shape)} {val.dtype}")
+    np.savez_compressed(HERE / "states.npz", **out)
+
+
 if __name__ == "__main__":
     if len(sys.argv) < 2:
         raise SystemExit(__doc__)
@@ -267,7 +296,7 @@ if __name__ == "__main__":
     _add_reference(sys.argv[1])
     torch.manual_seed(0)
     only = set(sys.argv[2:])
-    for nm, fn in (("verify", gen_verify), ("scan", gen_scan), ("om_causal", gen_om_causal), ("gated", gen_gated),
-                   ("decayed", gen_decayed), ("chain", gen_chain)):
+    for nm, fn in (("verify", gen_verify), ("scan", gen_scan), ("states", gen_states), ("om_causal", gen_om_causal),
+                   ("gated", gen_gated), ("decayed", gen_decayed), ("chain", gen_chain)):
         if not only or nm in only:
             fn()

@@ -1006,6 +1006,38 @@ def test_diag_prefix_maps_one_pass_shapes(dev, dtype, T, state):
     assert torch.equal(sa, fa) and torch.equal(sb, fb)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,state", [(37, (8, 12)), (4096, (2, 64)), (1000, (3, 5)), (64, (4, 8192)), (1, (16,))])
+def test_diag_scan_states_vs_oracle(dev, dtype, T, state):
+    """Every state of the recurrence in one pass (cb2_diag_scan_states): vector and scalar layouts,
+    one pass and segments (a small state with many steps), against the oracle's composition of the
+    prefix maps and against the plain recurrence in fp64; the last state is the whole fold."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(9 + T)
+    A = torch.sigmoid(2 + torch.randn(T, *state, generator=g)).to(dtype)
+    Bv = torch.randn(T, *state, generator=g).to(dtype)
+    h = torch.randn(state, generator=g).to(dtype)
+    got = ops.diag_scan_states(A.to(dev), Bv.to(dev), h.to(dev))
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert got.dtype == dtype and got.shape == (T, *state)
+    hh, rows = h.double(), []
+    for t in range(T):
+        hh = A[t].double() * hh + Bv[t].double()
+        rows.append(hh)
+    want = torch.stack(rows)
+    assert rel_to_max(got, want) <= tol
+    if T <= 64:
+        assert rel_to_max(got, oracle.scan_states(A.float(), Bv.float(), h.float())) <= tol
+    assert rel_to_max(got[-1], ops.diag_fold_apply(A.to(dev), Bv.to(dev), h.to(dev))) <= tol
+    # an operand every step shares is read in place: same bits as the expanded copy
+    if T > 1:
+        shared = A[:1].to(dev).expand(T, *state)
+        assert torch.equal(ops.diag_scan_states(shared, Bv.to(dev), h.to(dev)),
+                           ops.diag_scan_states(shared.contiguous(), Bv.to(dev), h.to(dev)))
+    assert ops.diag_scan_states(A.double().to(dev), Bv.double().to(dev), h.double().to(dev)) is None
+
+
 def test_gated_contract_past_two_billion_scores(dev):
     """2^31 + 2^27 score elements (4.6 GB): batch and row offsets must not wrap.  The last batch,
     computed alone, gives the same bits as inside the large call, and scaling one batch's values

@@ -401,3 +401,80 @@ def test_sink_verify_delegates_what_the_kernel_does_not_take():
     lin32 = torch.nn.Linear(8, 8).to(DEV)
     rep = sink.verify(lin32, lin32, x.float())
     assert rep.passed and verify.kernel_gate_calls == n0 + 1
+
+
+# --------------------------------------------------------------------------- scan, every state (stacked-map form)
+def _stacked_map_term(leaves, h, dim):
+    """applyd(aff_diag(stack(affd_a f_t), stack(affd_b f_t)), h) over the prefix chain of ``leaves``
+    — the member ``gather_applyd_stack`` offers (catopt_carriers/xcarrier.py:2252-2275)."""
+    fs = [leaves[0]]
+    for lf in leaves[1:]:
+        fs.append(Op.make("affd_compose", lf, fs[-1]))
+    sa = Op.make("stack", *(Op.make("affd_a", f) for f in fs), dim=dim)
+    sb = Op.make("stack", *(Op.make("affd_b", f) for f in fs), dim=dim)
+    return Op.make("applyd", Op.make("aff_diag", sa, sb), h)
+
+
+def test_every_state_of_a_scan_through_b200_scan_all_matches_the_reference_evaluation():
+    from catopt_torch.torch_bridge import IRModule
+
+    T, d = 128, 8192
+    a_p, x_v, h = Param("p_a", _tt(T, d)), Var("x", _tt(T, d)), Param("h0", _tt(d))
+    leaves = [Op.make("aff_diag", Op.make("select", a_p, dim=0, index=t), Op.make("select", x_v, dim=0, index=t))
+              for t in range(T)]
+    ir = IR(root=_stacked_map_term(leaves, h, 0), inputs=[x_v], input_names={"x"}, params={"p_a": a_p, "h0": h})
+    g = torch.Generator().manual_seed(21)
+    vals = {"p_a": torch.sigmoid(3 + torch.randn(T, d, generator=g)).to(DEV), "h0": torch.randn(d, generator=g).to(DEV)}
+    x = torch.randn(T, d, generator=g).to(DEV)
+    spec = _route(b200.B200Sink(), ir.root)
+    assert spec.name == "b200_scan_all"
+    mod = spec.lower(ir, vals)
+    assert spec.engaged(mod) and mod._plan["a"][0] == "gather" and mod._plan["b"][0] == "gather"
+    with torch.no_grad():
+        got = mod(x)
+        want = IRModule(ir, vals)(x)            # the reference's eager evaluation of the same term, same device
+    assert mod.kernel_calls == 1 and got.shape == want.shape == (T, d)
+    assert _rel(got, want) <= 1e-5
+    hh, rows = vals["h0"].double(), []
+    for t in range(T):
+        hh = vals["p_a"][t].double() * hh + x[t].double()
+        rows.append(hh)
+    assert _rel(got, torch.stack(rows)) <= 1e-5
+    ops.check_device_status(DEV)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_config3_recurrence_as_a_term_runs_on_the_scan_kernel(dtype, tol):
+    """``y_t = sum_n c*h_t``, ``h_t = a_t*h_(t-1) + b*x_t`` spelled as the readout of the
+    stacked-map form: routed to ``b200_scan_all`` and run by ``cb2_diag_scan_fwd``."""
+    from catopt_torch.torch_bridge import IRModule
+
+    from oracle import oracle
+
+    B, T, D, N = 2, 48, 64, 16
+    a_v, x_v = Var("a", _tt(B, T, D, N)), Var("x", _tt(B, T, D))
+    b_p, c_p, h_p = Param("p_b", _tt(D, N)), Param("p_c", _tt(D, N)), Param("p_h0", _tt(N))
+    leaves = [Op.make("aff_diag", Op.make("select", a_v, dim=1, index=t),
+                      Op.make("mul", b_p, Op.make("unsqueeze", Op.make("select", x_v, dim=1, index=t), dim=-1)))
+              for t in range(T)]
+    states = _stacked_map_term(leaves, h_p, 1)
+    root = Op.make("sum", Op.make("mul", states, c_p), dim=(-1,))
+    ir = IR(root=root, inputs=[a_v, x_v], input_names={"a", "x"}, params={"p_b": b_p, "p_c": c_p, "p_h0": h_p})
+    g = torch.Generator().manual_seed(22)
+    a = torch.sigmoid(4 + 0.5 * torch.randn(B, T, D, N, generator=g)).to(dtype)
+    x = torch.randn(B, T, D, generator=g).to(dtype)
+    vals = {"p_b": (torch.randn(D, N, generator=g) / 4).to(dtype), "p_c": (torch.randn(D, N, generator=g) / 4).to(dtype),
+            "p_h0": torch.zeros(N, dtype=dtype)}
+    spec = _route(b200.B200Sink(), ir.root)
+    assert spec.name == "b200_scan_all"
+    mod = spec.lower(ir, {k: v.to(DEV) for k, v in vals.items()})
+    assert spec.engaged(mod) and mod._plan["readout"] is not None
+    with torch.no_grad():
+        got = mod(a.to(DEV), x.to(DEV))
+        # the reference's eager evaluation of the same term in fp32 on the (rounded) inputs
+        want = IRModule(ir, {k: v.float().to(DEV) for k, v in vals.items()})(a.float().to(DEV), x.float().to(DEV))
+    assert mod.kernel_calls == 1 and got.dtype == dtype and got.shape == (B, T, D)
+    assert _rel(got, want) <= tol
+    wy, _ = oracle.diag_scan_serial(a, x, vals["p_b"], vals["p_c"])
+    assert _rel(got, wy) <= tol
+    ops.check_device_status(DEV)

@@ -148,3 +148,13 @@ def test_seq_fold_bitwise_vs_reference(name):
     ar = a if a.dim() == h.dim() + 1 else a.expand(n, *a.shape)
     br = b if b.dim() == h.dim() + 1 else b.expand(n, *b.shape)
     assert torch.equal(oracle.seq_fold(ar, br, h), want)
+
+
+@pytest.mark.parametrize("name", ["per_step_f32", "shared_decay_f32", "per_step_bf16"])
+def test_scan_states_bitwise_vs_reference_evaluation_of_the_stacked_map_form(name):
+    a, b, h = cases.fold_inputs(name)
+    want = _from_gold(_load("states.npz")[f"states.{name}"], h.dtype)
+    n = cases.FOLD_CASES[name][0]
+    ar = a if a.dim() == h.dim() + 1 else a.expand(n, *a.shape)
+    br = b if b.dim() == h.dim() + 1 else b.expand(n, *b.shape)
+    assert torch.equal(oracle.scan_states(ar, br, h), want)

@@ -33,8 +33,8 @@ def _route(sink, term):
 def test_b200_specs_come_first_and_are_executor_specs():
     s = b200.B200Sink()
     names = list(s.executors)
-    assert names[:6] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_om_streaming", "b200_scan", "b200_omd",
-                         "b200_linear_chain"]
+    assert names[:7] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_om_streaming", "b200_scan_all",
+                         "b200_scan", "b200_omd", "b200_linear_chain"]
     assert "om_decayed_chunked" in names and names[-1] == "generic"
     assert all(isinstance(v, ExecutorSpec) for v in s.executors.values())
 
@@ -627,3 +627,124 @@ def test_equivalent_spellings_of_the_cross_gate_are_accepted_and_other_functions
     for fn in (drop_gate, second_rate):
         other = _mutate(chunked, fn)
         assert other != chunked.root and b200.decayed_plan(other) is None, fn.__name__
+
+
+# --------------------------------------------------------------------------- scan, every state (stacked-map form)
+def _gathered_scan_terms(readout: bool, T=5, B=2, D=8, N=4):
+    """Export an unrolled diagonal scan that returns every state (or the per-step readout
+    of the stacked states), saturate, and run the reference's own non-local lifts
+    (machinery.py:73-103: lift_scan_to_applyd + gather_applyd_stack); returns the model,
+    its inputs, the export and the term with the offered stacked-map member in place."""
+    from catopt_carriers.trace_lift import lift_scan_to_applyd
+    from catopt_carriers.xcarrier import gather_applyd_stack
+    from catopt_core.egraph import EGraph
+    from catopt_torch.regime import default_rules
+    from catopt_torch.torch_bridge import export_to_ir
+
+    class States(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Parameter(torch.rand(T, D) * 0.5 + 0.5)
+            self.h0 = torch.nn.Parameter(torch.randn(D) * 0.1)
+
+        def forward(self, x):
+            h, outs = self.h0, []
+            for t in range(x.shape[0]):
+                h = self.a[t] * h + x[t]
+                outs.append(h)
+            return torch.stack(outs)
+
+    class Readout(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.b = torch.nn.Parameter(torch.randn(D, N) / 4)
+            self.c = torch.nn.Parameter(torch.randn(D, N) / 4)
+            self.h0 = torch.nn.Parameter(torch.zeros(N))
+
+        def forward(self, a, x):
+            h, hs = self.h0, []
+            for t in range(x.shape[1]):
+                h = a[:, t] * h + self.b * x[:, t].unsqueeze(-1)
+                hs.append(h)
+            return (torch.stack(hs, 1) * self.c).sum(-1)
+
+    torch.manual_seed(0)
+    if readout:
+        model, xs = Readout().eval().double(), (torch.rand(B, T, D, N, dtype=torch.float64) * 0.5 + 0.5,
+                                                torch.randn(B, T, D, dtype=torch.float64))
+    else:
+        model, xs = States().eval().double(), (torch.randn(T, D, dtype=torch.float64),)
+    ir, leaves = export_to_ir(model, xs if len(xs) > 1 else xs[0])
+    eg = EGraph()
+    root = eg.add_term(ir.root)
+    eg.run(default_rules(), root, max_iterations=4, max_nodes=200_000)
+    lift_scan_to_applyd(eg)
+    eg.rebuild()
+    offers = gather_applyd_stack(eg)
+    assert len(offers) == 1
+    member = offers[0]["term"]
+    if readout:   # the source root with the offered member in the stack's place
+        body = ir.root.args[0]
+        member = Op.make("sum", Op.make("mul", *[member if getattr(z, "op", None) == "stack" else z
+                                                 for z in body.args]), **dict(ir.root.attrs))
+    return model, xs, ir, leaves, member
+
+
+@pytest.mark.parametrize("readout", [False, True])
+def test_stacked_map_form_from_the_reference_machinery_routes_to_b200_scan_all(readout):
+    from catopt_torch.torch_bridge import IRModule
+
+    from oracle import oracle
+
+    model, xs, ir, leaves, term = _gathered_scan_terms(readout)
+    s = b200.B200Sink()
+    spec = _route(s, term)
+    assert spec.name == "b200_scan_all"
+    plan = b200.scan_states_plan(term)
+    assert plan["n"] == 5 and plan["a"][0] == "gather"
+    assert (plan["readout"] is not None) == readout
+    ex_ir = IR(root=term, inputs=list(ir.inputs), input_names=set(ir.input_names), params=dict(ir.params))
+    mod = spec.lower(ex_ir, leaves)
+    assert isinstance(mod, BatchedExecutor) and spec.engaged(mod)
+    from catopt_b200 import B200Error
+
+    with pytest.raises(B200Error):
+        mod(*xs)
+    # the term means the source model (reference bindings), and what the module would hand to
+    # the kernel reproduces it through the serial oracle
+    with torch.no_grad():
+        want = model(*xs)
+        assert (IRModule(ex_ir, leaves)(*xs) - want).abs().max().item() < 1e-12
+        ev = mod._ev(xs)
+        if readout:
+            a, x, b, c = ev(plan["a"][1]), ev(plan["readout"]["x"]), ev(plan["readout"]["b"]), ev(plan["readout"]["c"])
+            y, _ = oracle.diag_scan_serial(a, x, b, c, ev(plan["h"]).expand(plan["state_shape"]))
+            assert (y.double() - want).abs().max().item() < 1e-5        # the oracle folds in fp32
+        else:
+            a_rows, b_rows = mod._rows(plan["a"], ev, 5), mod._rows(plan["b"], ev, 5)
+            h, hs = ev(plan["h"]), []
+            for t in range(5):
+                h = a_rows[t] * h + b_rows[t]
+                hs.append(h)
+            assert (torch.stack(hs).movedim(0, plan["stack_dim"]) - want).abs().max().item() < 1e-12
+
+
+def test_stacked_map_lookalikes_are_declined():
+    _, _, _, _, term = _gathered_scan_terms(False)
+    fmap, h = term.args
+    sa, sb = fmap.args
+    # the two stacks list different maps, a step is missing from the chain, independent maps (no scan)
+    swapped = Op.make("stack", *sb.args[::-1], **dict(sb.attrs))
+    assert b200.scan_states_plan(Op.make("applyd", Op.make("aff_diag", sa, swapped), h)) is None
+    fs = [p.args[0] for p in sa.args]
+    gap = fs[:2] + fs[3:]
+    mk = lambda proj: Op.make("stack", *(Op.make(proj, f) for f in gap), **dict(sa.attrs))  # noqa: E731
+    assert b200.scan_states_plan(Op.make("applyd", Op.make("aff_diag", mk("affd_a"), mk("affd_b")), h)) is None
+    leaves = [fs[0]] + [f.args[0] for f in fs[1:]]
+    mk = lambda proj: Op.make("stack", *(Op.make(proj, f) for f in leaves), **dict(sa.attrs))  # noqa: E731
+    indep = Op.make("applyd", Op.make("aff_diag", mk("affd_a"), mk("affd_b")), h)
+    assert b200.scan_states_plan(indep) is None
+    # and a plain scan application still goes to b200_scan
+    ir = _scan_term()
+    assert _route(b200.B200Sink(), ir.root).name == "b200_scan"
+    assert b200.scan_states_plan(ir.root) is None
