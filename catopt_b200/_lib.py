@@ -20,6 +20,7 @@ CB2_BF16 = 1
 SIGNATURES: dict[str, tuple] = {
     "cb2_version": (C.c_int, []),
     "cb2_status_str": (C.c_char_p, [C.c_int]),
+    "cb2_wait_for_flag": (C.c_int, [C.c_void_p, C.c_uint, C.c_void_p, C.c_void_p]),
     "cb2_verify_reduce": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p],

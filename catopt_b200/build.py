@@ -32,6 +32,7 @@ SOURCES = [
     "gated_contract_tc.cu",
     "om_causal.cu",
     "om_causal_tc.cu",
+    "device_wait.cu",
 ]
 
 NVCC_FLAGS = [

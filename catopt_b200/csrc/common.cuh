@@ -117,6 +117,27 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
   }
 }
 
+// Bounded wait for a flag in global memory that another CTA (or an earlier kernel) sets
+// (acquire).  Gives up after `budget_ns` of wall time, or as soon as a sibling thread has
+// raised the shared `*abort` word; on expiry it raises `*abort` itself.  Never traps.
+__device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile int* abort,
+                                                    unsigned long long budget_ns = 2000000000ull) {
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; ++it) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v != 0) return true;
+    if (*abort) return false;
+    if ((it & 63u) == 63u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) { *abort = 1; return false; }
+      __nanosleep(200);
+    }
+  }
+}
+
 // ---- bulk asynchronous copies (TMA engine, untiled form) -------------------
 // global -> shared, completion counted in bytes on `bar`.  Both addresses must
 // be 16-byte aligned and `bytes` a multiple of 16.

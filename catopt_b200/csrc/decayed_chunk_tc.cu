@@ -88,26 +88,6 @@ struct Bars {
   uint64_t* wg_sync;   // barrier among the 256 compute threads
 };
 
-// Bounded wait for a flag another CTA of this launch sets (acquire).  On expiry
-// (or when a sibling thread already gave up) the shared abort word is set.
-__device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile int* abort,
-                                                    unsigned long long budget_ns = 2000000000ull) {
-  unsigned long long t0 = 0;
-  for (unsigned it = 0;; ++it) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v != 0) return true;
-    if (*abort) return false;
-    if ((it & 63u) == 63u) {
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > budget_ns) { *abort = 1; return false; }
-      __nanosleep(200);
-    }
-  }
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,

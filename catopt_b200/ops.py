@@ -54,6 +54,19 @@ def check_device_status(device: torch.device | None = None) -> None:
         raise B200Error(f"device status: {_lib.status_str(code)} (status {code})")
 
 
+def wait_for_flag(flag: torch.Tensor, budget_us: int = 1000) -> None:
+    """Order the current stream behind a device flag with a bound: ``cb2_wait_for_flag``
+    polls ``flag`` (int32, one element) until it is non-zero or ``budget_us`` microseconds
+    have passed; an expired wait leaves ``CB2_WAIT_TIMEOUT`` in the device status word
+    (``check_device_status`` raises it) and the stream carries on."""
+    require_cuda(flag)
+    if flag.dtype != torch.int32 or flag.numel() != 1:
+        raise B200Error("wait_for_flag takes one int32 flag")
+    rc = _lib.load().cb2_wait_for_flag(flag.data_ptr(), int(budget_us), device_status(flag.device).data_ptr(),
+                                       stream_ptr())
+    check(rc, "cb2_wait_for_flag")
+
+
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 

@@ -51,6 +51,16 @@ int cb2_version(void);
 /* Static string for a status code. */
 const char* cb2_status_str(int status);
 
+/* Stream-ordered bounded wait for a device flag (no counterpart in the reference,
+ * whose modules never hand work between kernels): a one-thread kernel polls `*flag`
+ * (device int, acquire loads) until it is non-zero or `budget_us` microseconds
+ * (1 .. 2,000,000) have passed; on expiry it stores CB2_WAIT_TIMEOUT into
+ * `*dev_status` and ends — no trap, nothing in flight, the stream and the context
+ * stay usable.  It is the hand-off wait of the segmented decayed kernel as a launch
+ * of its own: a caller orders a stream behind a flag another stream's kernel sets,
+ * and a host-side failure test makes a wait run out against a flag nobody sets. */
+int cb2_wait_for_flag(const int* flag, unsigned budget_us, int* dev_status, void* stream);
+
 /* -------------------------------------------------------------------------
  * (d) verify reduction.
  * Replaces the four eager passes of `_verify_pair`

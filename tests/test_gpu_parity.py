@@ -873,6 +873,42 @@ def test_diag_prefix_maps_vs_reference_prefix_scan(dev):
     assert ops.diag_prefix_maps(A.double().to(dev), Bv.double().to(dev)) is None     # fp64: caller keeps its scan
 
 
+def test_bounded_device_wait_runs_out_and_surfaces_as_an_error(dev):
+    """The timeout route end to end, without faulting or hanging anything: a bounded wait
+    against a flag nobody sets gives up after its budget (1 ms), the kernel ends by itself
+    with CB2_WAIT_TIMEOUT in the status word, ``check_device_status`` raises ``B200Error``
+    (a message catopt's failure taxonomy files under "timeout"), the word is cleared, and
+    the next launches on the same stream — a satisfied wait and a real kernel — are clean."""
+    import time
+
+    from catopt_b200 import B200Error, _lib, ops
+
+    ops.check_device_status(dev)                      # nothing pending from earlier tests
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    t0 = time.perf_counter()
+    ops.wait_for_flag(flag, budget_us=1000)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0            # gave up after about a millisecond, by itself
+    assert int(ops.device_status(dev).item()) == _lib.CB2_WAIT_TIMEOUT
+    with pytest.raises(B200Error, match="timed out") as err:
+        ops.check_device_status(dev)
+    msg = str(err.value).lower()
+    assert "timed out" in msg or "timeout" in msg    # what catopt_core.failures.classify reads as TIMEOUT
+    assert int(ops.device_status(dev).item()) == 0   # the check consumed the status
+    # the same stream is usable: a wait whose flag is set returns at once, then a real kernel
+    flag.fill_(1)
+    ops.wait_for_flag(flag, budget_us=1000)
+    ref = torch.randn(4096, device=dev)
+    res = ops.verify_reduce(ref, ref + 0.5, 1).cpu()
+    assert res[0, 0].item() == 0.5 and res[0, 2:].sum() == 0
+    ops.check_device_status(dev)
+    # argument errors are return codes, not launches
+    lib = _lib.load()
+    assert lib.cb2_wait_for_flag(None, 10, None, None) != 0
+    assert lib.cb2_wait_for_flag(flag.data_ptr(), 0, None, None) != 0
+    assert lib.cb2_wait_for_flag(flag.data_ptr(), 3_000_000, None, None) != 0
+
+
 def test_device_status_clean(dev):
     """No kernel in this file ran into a bounded-wait timeout."""
     from catopt_b200 import ops

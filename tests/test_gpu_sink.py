@@ -478,3 +478,24 @@ def test_config3_recurrence_as_a_term_runs_on_the_scan_kernel(dtype, tol):
     wy, _ = oracle.diag_scan_serial(a, x, vals["p_b"], vals["p_c"])
     assert _rel(got, wy) <= tol
     ops.check_device_status(DEV)
+
+
+def test_an_expired_device_wait_fails_the_sink_gate_as_a_timeout():
+    """A bounded wait that ran out in some earlier kernel is reported where the
+    catopt-facing layer next synchronises — the verify gate's read-back — as a
+    ``B200Error`` that ``catopt_core.failures.classify`` buckets as TIMEOUT
+    (failures.py:74-112); the gate after it is clean."""
+    from catopt_core.failures import FailureClass, classify
+
+    from catopt_b200 import B200Error
+
+    sink = b200.B200Sink()
+    lin = torch.nn.Linear(8, 8).to(DEV)
+    x = torch.randn(4, 8, device=DEV)
+    assert sink.verify(lin, lin, x).passed
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.wait_for_flag(flag, budget_us=500)            # nobody sets the flag: the wait gives up
+    with pytest.raises(B200Error) as err:
+        sink.verify(lin, lin, x)
+    assert classify(err.value) == FailureClass.TIMEOUT
+    assert sink.verify(lin, lin, x).passed            # status consumed, stream and context intact
