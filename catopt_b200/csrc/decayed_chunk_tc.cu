@@ -32,39 +32,33 @@
 // warps 2..9 = the 256-thread compute group (thread = one TMEM lane = one row,
 // half of the columns).
 // Operand tiles (32 KiB each, K_i / Q_i / V_i in that order) stream through a
-// 5-slot shared-memory ring with full/empty mbarriers; a slot is released by
-// the tcgen05.commit of the last MMA that reads it, so up to two tiles of the
-// next chunk are in flight while a chunk computes.  HBM traffic is exactly the
+// shared-memory ring with full/empty mbarriers; a slot is released by the
+// tcgen05.commit of the last MMA that reads it.  The common-case roles use six
+// slots — two whole chunks, so the loads of chunk i+1 are issued about a chunk
+// ahead of their use (a tile lands 2-3 k cycles after its request; with less
+// lookahead the chunk time is that latency, not the work) — and stage o_i over
+// the chunk's own Q tile once MMA1 and MMA3 have read it; the every-rate roles
+// keep five slots and a separate staging tile.  HBM traffic is exactly the
 // algorithmic bytes: q, k, v read once, o written once.
 #include "umma.cuh"
 
 namespace cb2 {
 namespace {
 
-// Optional phase timeline of CTA 0 (compute-group thread 0), for tuning builds
-// only: compile with -DCB2_TIMELINE and read g_timeline back from the host.
-#ifdef CB2_TIMELINE
-__device__ long long g_timeline[64][12];
-#define CB2_TL(i, k)                                                   \
-  do {                                                                 \
-    if (blockIdx.x == 0 && threadIdx.x == 96 && (i) < 64) g_timeline[i][k] = clock64(); \
-  } while (0)
-#else
-#define CB2_TL(i, k) do {} while (0)
-#endif
-
 constexpr int kC = 128;                 // chunk rows = dk = dv
-constexpr int kSlots = 5;
+constexpr int kSlots = 5;                     // ring depth of the every-rate roles
+constexpr int kSlotsFast = 6;                 // ring depth of the common-case roles (two whole chunks)
+constexpr int kSlotsMax = 6;
 constexpr int kThreads = 320;                 // 2 single-lane role warps + 8 compute warps
 constexpr int kComputeThreads = 256;
 constexpr uint32_t kTile = umma::kTileBytes;      // 32 KiB
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffRing = 0;
-constexpr uint32_t kOffO = kSlots * kTile;          // output staging tile
-constexpr uint32_t kOffSb = kOffO + kTile;
+constexpr uint32_t kOffO = kSlots * kTile;          // output staging tile of the every-rate roles (= the sixth ring tile)
+constexpr uint32_t kOffSb = kSlotsMax * kTile;
 constexpr uint32_t kOffPow = kOffSb + kTile;                 // float[32 zeros | g^0 .. g^128]
 constexpr uint32_t kOffBars = kOffPow + 704;                 // 8-byte aligned
-constexpr int kNumBars = 2 * kSlots + 8;
+constexpr int kNumBars = 2 * kSlotsMax + 8;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;       // tmem base, abort flag
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slack
 
@@ -76,8 +70,8 @@ constexpr uint32_t kColS = 0, kColO1 = 128, kColO2 = 256, kColSt = 384;
 __host__ __device__ constexpr uint32_t p_col(uint32_t c) { return (c & 64u) + ((c & 63u) >> 1); }
 
 struct Bars {
-  uint64_t* full;      // [kSlots] TMA -> MMA
-  uint64_t* empty;     // [kSlots] MMA -> TMA
+  uint64_t* full;      // [kSlotsMax] TMA -> MMA
+  uint64_t* empty;     // [kSlotsMax] MMA -> TMA
   uint64_t* s_ready;   // MMA1 done            (MMA -> WG)
   uint64_t* p_ready;   // P written            (WG -> MMA, 256 arrivals)
   uint64_t* kw_ready;  // K scaled in place    (WG -> MMA, 256)
@@ -88,11 +82,389 @@ struct Bars {
   uint64_t* wg_sync;   // barrier among the 256 compute threads
 };
 
+
+// The state a later segment starts from (this thread's 64 elements of row r: columns cb0*32 ..
+// +63), ready before the launch.  pieces_per_seg == 0: the finished start state sits in slot
+// seg-1 (written by the scan kernel of decayed_seg_state.cu).  Otherwise the slots hold the end
+// states E_p (from zero) of consecutive pieces of `piece_rows` rows, pieces_per_seg of them per
+// segment, and the start state is their fold  S = g^(piece_rows) S + E_p  over the pieces before
+// this segment (at most four: a fold in every CTA is then cheaper than one more launch).
+__device__ __forceinline__ void load_start_state(const float* seg_state, int seg, int n_bh, int bh, int r, int cb0,
+                                                 int pieces_per_seg, float g_piece, uint32_t (&va)[32],
+                                                 uint32_t (&vb)[32]) {
+  const size_t elem = size_t(r) * kC + cb0 * 32;
+  if (pieces_per_seg == 0) {
+    const float4* src = reinterpret_cast<const float4*>(seg_state + (size_t(seg - 1) * n_bh + bh) * (kC * kC) + elem);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 x = __ldcg(src + j), y = __ldcg(src + 8 + j);
+      va[4 * j] = __float_as_uint(x.x); va[4 * j + 1] = __float_as_uint(x.y);
+      va[4 * j + 2] = __float_as_uint(x.z); va[4 * j + 3] = __float_as_uint(x.w);
+      vb[4 * j] = __float_as_uint(y.x); vb[4 * j + 1] = __float_as_uint(y.y);
+      vb[4 * j + 2] = __float_as_uint(y.z); vb[4 * j + 3] = __float_as_uint(y.w);
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) va[j] = vb[j] = 0u;
+  const int n = seg * pieces_per_seg;
+  for (int p = 0; p < n; ++p) {
+    const float4* src = reinterpret_cast<const float4*>(seg_state + (size_t(p) * n_bh + bh) * (kC * kC) + elem);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 x = __ldcg(src + j), y = __ldcg(src + 8 + j);
+      va[4 * j] = __float_as_uint(fmaf(g_piece, __uint_as_float(va[4 * j]), x.x));
+      va[4 * j + 1] = __float_as_uint(fmaf(g_piece, __uint_as_float(va[4 * j + 1]), x.y));
+      va[4 * j + 2] = __float_as_uint(fmaf(g_piece, __uint_as_float(va[4 * j + 2]), x.z));
+      va[4 * j + 3] = __float_as_uint(fmaf(g_piece, __uint_as_float(va[4 * j + 3]), x.w));
+      vb[4 * j] = __float_as_uint(fmaf(g_piece, __uint_as_float(vb[4 * j]), y.x));
+      vb[4 * j + 1] = __float_as_uint(fmaf(g_piece, __uint_as_float(vb[4 * j + 1]), y.y));
+      vb[4 * j + 2] = __float_as_uint(fmaf(g_piece, __uint_as_float(vb[4 * j + 2]), y.z));
+      vb[4 * j + 3] = __float_as_uint(fmaf(g_piece, __uint_as_float(vb[4 * j + 3]), y.w));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Roles of the common case: decay rates close enough to one (g >= 0.74) that the powers
+// g^(-c) of a whole chunk fit comfortably in bf16/fp32 range.  Writing the decay mask as
+// g^(r-c) = g^r . g^(-c) moves every per-element multiply out of the compute group:
+//
+//   K~_i  = K_i . g^(-c - C.mi)          (row c of the tile scaled once, BEFORE MMA1; the same
+//                                         tile feeds MMA1 and MMA4; mi = chunk index mod m)
+//   MMA1  S' = Q_i K~_i^T
+//   WG    P' = bf16(S') below the diagonal, 0 above      (a select, no table, no multiply)
+//   MMA2  O' = P' V_i          MMA3  O' += Q_i Sb         (ONE accumulator: both terms carry
+//   WG    o_i = g^(r + C.mi) / scale . O'  -> global       the same row factor)
+//   MMA4  A += K~_i^T V_i      (the raw accumulator: true state = g^(C.mi' - 1) . A)
+//   WG    Sb = bf16(A) for the next chunk; every m chunks A <- g^(C.m) A  (m = the largest
+//         power of two with g^(-C.m) <= 2^56, so A never leaves fp32 range; m = 8 at g = 0.969)
+//
+// Per chunk the compute group now loads 192 and stores 32 TMEM words per thread (was 256 and
+// 96) and multiplies 128 values (was 320); the state chain (MMA4 -> Sb -> MMA3) no longer
+// passes through a rescale of the accumulator.  Issue order per chunk: MMA1, MMA4, MMA2, MMA3 —
+// MMA4 needs nothing from the mask, so it fills the tensor core's wait for P'.
+// The renormalisation points are multiples of m in the GLOBAL chunk index and a flagged
+// hand-off passes the raw accumulator, so a head cut into segments that wait for one another
+// gives the same bits as one CTA walking the head.
+struct FastCtx {
+  unsigned char* smem;
+  Bars B;
+  uint32_t tmem;
+  const CUtensorMap *map_q, *map_k, *map_v, *map_o;
+  int bh, seg, n_bh, n_seg, nchunk, chunk0, dv, prestaged, pieces_per_seg;
+  float g_piece;            // g^(rows of a precomputed piece)
+  bool has_in;
+  float lg, inv_scale;      // lg = -log2(g)
+  float* seg_state;
+  int* seg_flag;
+  volatile int* s_abort;
+};
+
+__device__ __forceinline__ void fast_roles(const FastCtx& c) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const Bars& B = c.B;
+  unsigned char* smem = c.smem;
+  volatile int* s_abort = c.s_abort;
+  const int nchunk = c.nchunk;
+  const bool has_in = c.has_in;
+  const uint32_t tmem = c.tmem;
+  const uint32_t ring_addr = smem_u32(smem + kOffRing);
+  const uint32_t sb_addr = smem_u32(smem + kOffSb);
+  constexpr uint32_t kColO = kColO1, kColA = kColSt;
+  // renormalisation period: the largest power of two m <= 64 with C.m.lg <= 56
+  int m = 1;
+  while (m < 64 && float(2 * m * kC) * c.lg <= 56.f) m *= 2;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      umma::tma_prefetch_desc(c.map_q);
+      umma::tma_prefetch_desc(c.map_k);
+      umma::tma_prefetch_desc(c.map_v);
+      umma::tma_prefetch_desc(c.map_o);
+      const int ntiles = 3 * nchunk;
+      for (int t = 0; t < ntiles; ++t) {
+        const int slot = t % kSlotsFast, use = t / kSlotsFast;
+        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort)) break;
+        const int i = t / 3, which = t % 3;  // 0: K, 1: Q, 2: V
+        const CUtensorMap* mp = which == 0 ? c.map_k : (which == 1 ? c.map_q : c.map_v);
+        unsigned char* dst = smem + kOffRing + slot * kTile;
+        const int row = (c.chunk0 + i) * kC;
+        mbar_arrive_expect_tx(&B.full[slot], kTile);
+        umma::tma_load_3d(dst, mp, 0, row, c.bh, &B.full[slot]);
+        umma::tma_load_3d(dst + umma::kSubTileBytes, mp, 64, row, c.bh, &B.full[slot]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = umma::instr_desc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_kn = umma::instr_desc_bf16(128, 128, false, true);
+      constexpr uint32_t idesc_nn = umma::instr_desc_bf16(128, 128, true, true);
+      for (int i = 0; i < nchunk; ++i) {
+        const uint32_t ph = i & 1;
+        const int tk = 3 * i, tq = tk + 1, tv = tk + 2;
+        const uint32_t k_addr = ring_addr + (tk % kSlotsFast) * kTile;
+        const uint32_t q_addr = ring_addr + (tq % kSlotsFast) * kTile;
+        const uint32_t v_addr = ring_addr + (tv % kSlotsFast) * kTile;
+        // MMA1: S' = Q K~^T  (K~ is ready once the compute group has scaled the tile)
+        if (!mbar_wait_abortable(B.kw_ready, ph, s_abort)) break;
+        if (!mbar_wait_abortable(&B.full[tq % kSlotsFast], (tq / kSlotsFast) & 1, s_abort)) break;
+        umma::fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_bf16(tmem + kColS, umma::desc_kmajor(q_addr, ks), umma::desc_kmajor(k_addr, ks),
+                         idesc_kk, ks > 0);
+        umma::mma_commit(B.s_ready);
+        // MMA4: A (+)= K~^T V.  Issued ahead of MMA2/MMA3: it does not depend on the mask, so the
+        // tensor core works through it while the compute group turns S' into P'.  The compute
+        // group must have finished copying the previous accumulator into Sb first.
+        if (!mbar_wait_abortable(&B.full[tv % kSlotsFast], (tv / kSlotsFast) & 1, s_abort)) break;
+        if (i > 0 || has_in) {
+          if (!mbar_wait_abortable(B.sb_ready, (has_in ? i : i - 1) & 1, s_abort)) break;
+        }
+        umma::fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_bf16(tmem + kColA, umma::desc_mnmajor(k_addr, ks), umma::desc_mnmajor(v_addr, ks),
+                         idesc_nn, (i > 0) || has_in || (ks > 0));
+        umma::mma_commit(&B.empty[tk % kSlotsFast]);
+        // MMA2: O' = P' V
+        if (!mbar_wait_abortable(B.p_ready, ph, s_abort)) break;
+        if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
+        umma::fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_bf16_ts(tmem + kColO, tmem + kColS + p_col(ks * 16),
+                            umma::desc_mnmajor(v_addr, ks), idesc_kn, ks > 0);
+        umma::mma_commit(&B.empty[tv % kSlotsFast]);
+        // MMA3: O' += Q Sb  (no state before the first chunk of the sequence)
+        if (i > 0 || has_in) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma::mma_bf16(tmem + kColO, umma::desc_kmajor(q_addr, ks),
+                           umma::desc_mnmajor(sb_addr, ks), idesc_kn, true);
+        }
+        umma::mma_commit(B.o_ready);     // every MMA of the chunk is done (the Q slot is released by the
+        umma::mma_commit(B.st_ready);    // compute group: it stages o_i there)
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ compute group
+    const int q4 = warp & 3;                 // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;        // 0: columns 0..63, 1: columns 64..127
+    const int r = q4 * 32 + lane;            // row of the chunk / lane of TMEM
+    const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
+    unsigned char* sb_tile = smem + kOffSb;
+    const float g_renorm = exp2f(-c.lg * float(m * kC));        // g^(C.m)
+    uint32_t va[32], vb[32];
+    uint32_t wg_phase = 0;
+    auto store_block = [&](unsigned char* tile, int col0, const uint32_t (&w)[16]) {
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8)
+        *reinterpret_cast<uint4*>(tile + umma::tile_chunk_offset(r, col0 + c8 * 8)) =
+            make_uint4(w[4 * c8], w[4 * c8 + 1], w[4 * c8 + 2], w[4 * c8 + 3]);
+    };
+    // K~_j = K_j . g^(-r - C.mj), in place, as soon as the tile has landed
+    auto scale_k = [&](int j) -> bool {
+      const int tk = 3 * j;
+      bool ok = mbar_wait_abortable(&B.full[tk % kSlotsFast], (tk / kSlotsFast) & 1, s_abort);
+      if (!__all_sync(0xffffffffu, ok)) return false;
+      const float kf = exp2f(c.lg * float(r + kC * ((c.chunk0 + j) % m)));
+      unsigned char* k_tile = smem + kOffRing + (tk % kSlotsFast) * kTile;
+      uint4 x[8];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj)
+        x[jj] = *reinterpret_cast<const uint4*>(k_tile + umma::tile_chunk_offset(r, half * 64 + jj * 8));
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        x[jj].x = pack_bf16x2(bf16lo_to_f32(x[jj].x) * kf, bf16hi_to_f32(x[jj].x) * kf);
+        x[jj].y = pack_bf16x2(bf16lo_to_f32(x[jj].y) * kf, bf16hi_to_f32(x[jj].y) * kf);
+        x[jj].z = pack_bf16x2(bf16lo_to_f32(x[jj].z) * kf, bf16hi_to_f32(x[jj].z) * kf);
+        x[jj].w = pack_bf16x2(bf16lo_to_f32(x[jj].w) * kf, bf16hi_to_f32(x[jj].w) * kf);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj)
+        *reinterpret_cast<uint4*>(k_tile + umma::tile_chunk_offset(r, half * 64 + jj * 8)) = x[jj];
+      fence_proxy_async_smem();
+      mbar_arrive(B.kw_ready);
+      return true;
+    };
+    bool alive = scale_k(0);
+    for (int i = 0; alive && i < nchunk; ++i) {
+      const uint32_t ph = i & 1;
+      const int mi = (c.chunk0 + i) % m;
+      bool ok = true;
+      // (s) Sb = bf16(A) for this chunk's MMA3.  First thing in the iteration: the accumulator is
+      // final and Sb is free once every MMA of the previous chunk has completed, and the copy then
+      // runs under MMA1 of this chunk (operands from shared memory: the tensor-memory read port is
+      // free); MMA4 of this chunk waits for it
+      if (i > 0 || has_in) {
+        const int cb0 = half * 2;
+        float mult = 1.f;
+        bool writeback = false;
+        if (i > 0) {
+          // (o_ready of the previous chunk, which this thread has waited for, covers its MMA3 and MMA4)
+          umma::tmem_ld32(lane_base + kColA + cb0 * 32, va);
+          umma::tmem_ld32(lane_base + kColA + cb0 * 32 + 32, vb);
+          umma::tmem_wait_ld();
+          if (mi == 0) { mult = g_renorm; writeback = true; }
+        } else {
+          // first chunk of a later segment: prestaged = the true state before this chunk,
+          // computed ahead of the launch; otherwise the predecessor CTA's raw accumulator
+          if (!c.prestaged) {
+            const int* flag = c.seg_flag + size_t(c.seg - 1) * c.n_bh + c.bh;
+            ok = wait_flag_abortable(flag, s_abort);
+            if (!__all_sync(0xffffffffu, ok)) break;
+          }
+          load_start_state(c.seg_state, c.seg, c.n_bh, c.bh, r, cb0, c.prestaged ? c.pieces_per_seg : 0, c.g_piece,
+                           va, vb);
+          writeback = true;
+          mult = c.prestaged ? exp2f(c.lg * float(kC * mi - 1)) : (mi == 0 ? g_renorm : 1.f);
+        }
+        if (mult != 1.f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            va[j] = __float_as_uint(__uint_as_float(va[j]) * mult);
+            vb[j] = __float_as_uint(__uint_as_float(vb[j]) * mult);
+          }
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          w[j >> 1] = pack_bf16x2(__uint_as_float(va[j]), __uint_as_float(va[j + 1]));
+        store_block(sb_tile, cb0 * 32, w);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          w[j >> 1] = pack_bf16x2(__uint_as_float(vb[j]), __uint_as_float(vb[j + 1]));
+        store_block(sb_tile, cb0 * 32 + 32, w);
+        if (writeback) {
+          umma::tmem_st32(lane_base + kColA + cb0 * 32, va);
+          umma::tmem_st32(lane_base + kColA + cb0 * 32 + 32, vb);
+          umma::tmem_wait_st();
+        }
+        umma::fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(B.sb_ready);
+      }
+      ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      umma::fence_after_sync();
+      // (a) P' = bf16(S') at and below the diagonal, 0 above, packed into TMEM over S'
+      {
+        const int cb0 = half * 2, cb1 = cb0 + 1;
+        if (cb0 <= q4) umma::tmem_ld32(lane_base + kColS + cb0 * 32, va);
+        if (cb1 <= q4) umma::tmem_ld32(lane_base + kColS + cb1 * 32, vb);
+        if (cb0 <= q4) umma::tmem_wait_ld();
+        auto mask_block = [&](int cb, const uint32_t (&v)[32]) {
+          uint32_t w[16];
+          if (cb < q4) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+              w[j >> 1] = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+          } else if (cb == q4) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+              w[j >> 1] = pack_bf16x2(j <= lane ? __uint_as_float(v[j]) : 0.f,
+                                      j + 1 <= lane ? __uint_as_float(v[j + 1]) : 0.f);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[j] = 0u;
+          }
+          umma::tmem_st16(lane_base + kColS + p_col(cb * 32), w);
+        };
+        mask_block(cb0, va);
+        mask_block(cb1, vb);
+        umma::tmem_wait_st();
+      }
+      umma::fence_before_sync();
+      mbar_arrive(B.p_ready);
+      // the previous chunk's output has left the ring tile it was staged in (that chunk's Q
+      // tile): hand the slot back to the producer
+      if (tid == 64 && i > 0) {
+        bulk_wait_read<0>();
+        mbar_arrive(&B.empty[(3 * (i - 1) + 1) % kSlotsFast]);
+      }
+      // (k) the next chunk's K tile, scaled ahead of its MMA1
+      if (i + 1 < nchunk && !scale_k(i + 1)) break;
+      // (c) o_i = g^(r + C.mi) / scale . O'
+      ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      umma::fence_after_sync();
+      // staged in the chunk's own Q tile (MMA1 and MMA3 are done with it) in the swizzled layout the
+      // TMA store expects.  (Storing straight from registers — every thread owns 128 contiguous
+      // bytes of its row — was measured at 3 k cycles per chunk for this phase: 32 rows a warp,
+      // 256 bytes apart, is the worst case for the store path.)
+      unsigned char* o_tile = smem + kOffRing + ((3 * i + 1) % kSlotsFast) * kTile;
+      {
+        const float f = exp2f(-c.lg * float(r + kC * mi)) * c.inv_scale;
+        const int cb0 = half * 2;
+        umma::tmem_ld32(lane_base + kColO + cb0 * 32, va);
+        umma::tmem_ld32(lane_base + kColO + cb0 * 32 + 32, vb);
+        umma::tmem_wait_ld();
+        umma::fence_before_sync();
+        mbar_arrive(B.o_free);                 // O' is in registers: MMA2 of the next chunk may start
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          w[j >> 1] = pack_bf16x2(__uint_as_float(va[j]) * f, __uint_as_float(va[j + 1]) * f);
+        store_block(o_tile, cb0 * 32, w);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          w[j >> 1] = pack_bf16x2(__uint_as_float(vb[j]) * f, __uint_as_float(vb[j + 1]) * f);
+        store_block(o_tile, cb0 * 32 + 32, w);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(B.wg_sync);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      wg_phase ^= 1;
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (tid == 64) {
+        const int row = (c.chunk0 + i) * kC;   // the store is clipped at T
+        umma::tma_store_3d(c.map_o, 0, row, c.bh, o_tile);
+        if (c.dv > 64) umma::tma_store_3d(c.map_o, 64, row, c.bh, o_tile + umma::kSubTileBytes);
+        bulk_commit();
+      }
+    }
+    // hand the raw accumulator to the next segment of this head
+    if (c.seg + 1 < c.n_seg && !c.prestaged) {
+      bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
+      if (__all_sync(0xffffffffu, ok)) {
+        umma::fence_after_sync();
+        const int cb0 = half * 2;
+        umma::tmem_ld32(lane_base + kColA + cb0 * 32, va);
+        umma::tmem_ld32(lane_base + kColA + cb0 * 32 + 32, vb);
+        umma::tmem_wait_ld();
+        float4* dst = reinterpret_cast<float4*>(c.seg_state + (size_t(c.seg) * c.n_bh + c.bh) * (kC * kC) +
+                                                r * kC + cb0 * 32);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          __stcg(dst + j, make_float4(__uint_as_float(va[4 * j]), __uint_as_float(va[4 * j + 1]),
+                                      __uint_as_float(va[4 * j + 2]), __uint_as_float(va[4 * j + 3])));
+          __stcg(dst + 8 + j, make_float4(__uint_as_float(vb[4 * j]), __uint_as_float(vb[4 * j + 1]),
+                                          __uint_as_float(vb[4 * j + 2]), __uint_as_float(vb[4 * j + 3])));
+        }
+        __threadfence();
+        mbar_arrive(B.wg_sync);
+        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+        wg_phase ^= 1;
+        if (ok && tid == 64) {
+          int* flag = c.seg_flag + size_t(c.seg) * c.n_bh + c.bh;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+        }
+      }
+    }
+    if (tid == 64) bulk_wait_all<0>();  // the staged output has left shared memory
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int n_bh, int n_seg,
-                  float* __restrict__ seg_state, int* __restrict__ seg_flag, int prestaged, int* dev_status) {
+                  float* __restrict__ seg_state, int* __restrict__ seg_flag, int prestaged, int pieces_per_seg,
+                  int piece_rows, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
   // __shared__ array keeps every access a shared-space (LDS/STS) access
@@ -103,9 +475,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
-  Bars B{bars, bars + kSlots, bars + 2 * kSlots, bars + 2 * kSlots + 1, bars + 2 * kSlots + 2,
-         bars + 2 * kSlots + 3, bars + 2 * kSlots + 4, bars + 2 * kSlots + 5, bars + 2 * kSlots + 6,
-         bars + 2 * kSlots + 7};
+  Bars B{bars, bars + kSlotsMax, bars + 2 * kSlotsMax, bars + 2 * kSlotsMax + 1, bars + 2 * kSlotsMax + 2,
+         bars + 2 * kSlotsMax + 3, bars + 2 * kSlotsMax + 4, bars + 2 * kSlotsMax + 5, bars + 2 * kSlotsMax + 6,
+         bars + 2 * kSlotsMax + 7};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x % n_bh;
@@ -118,7 +490,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const uint32_t sb_addr = smem_u32(smem + kOffSb);
 
   if (tid == 0) {
-    for (int s = 0; s < kSlots; ++s) {
+    for (int s = 0; s < kSlotsMax; ++s) {
       mbar_init(&B.full[s], 1);
       mbar_init(&B.empty[s], 1);
     }
@@ -148,7 +520,15 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   umma::fence_after_sync();
   const uint32_t tmem = *s_tmem;
 
-  if (warp == 0) {
+  // decay rates in [0.74, 1]: the cheaper formulation (see fast_roles); anything else keeps
+  // the chunk-local decaying powers below, which are safe for every rate
+  const float lg = -log2f(g);
+  const bool fast = g > 0.f && g <= 1.f && float(kC) * lg <= 56.f;
+  if (fast) {
+    fast_roles(FastCtx{smem, B, tmem, &map_q, &map_k, &map_v, &map_o, bh, seg, n_bh, n_seg, nchunk, chunk0, dv,
+                       prestaged, pieces_per_seg, exp2f(-lg * float(piece_rows)), has_in, lg, inv_scale, seg_state,
+                       seg_flag, s_abort});
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       umma::tma_prefetch_desc(&map_q);
@@ -246,11 +626,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
     for (int i = 0; i < nchunk; ++i) {
       const uint32_t ph = i & 1;
-      CB2_TL(i, 0);
       bool ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
-      CB2_TL(i, 1);
       // (a) P = bf16(S . decay), packed into TMEM over S: one table load and one
       // multiply per element (the table is 0 for negative exponents = masked).
       {
@@ -258,7 +636,6 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (cb0 <= q4) umma::tmem_ld32(lane_base + kColS + cb0 * 32, va);  // warp-uniform:
         if (cb1 <= q4) umma::tmem_ld32(lane_base + kColS + cb1 * 32, vb);  // blocks right of the
         if (cb0 <= q4) umma::tmem_wait_ld();                               // diagonal are zero
-        CB2_TL(i, 8);
         auto decay_block = [&](int cb, const uint32_t (&v)[32]) {
           uint32_t w[16];
           if (cb <= q4) {
@@ -274,9 +651,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         };
         decay_block(cb0, va);
         decay_block(cb1, vb);
-        CB2_TL(i, 9);
         umma::tmem_wait_st();
-        CB2_TL(i, 10);
       }
       // The staging tile of the previous chunk's output must have been read by
       // its TMA store before (c) rewrites it; making the issuing thread wait
@@ -285,7 +660,6 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (tid == 64) bulk_wait_read<0>();
       umma::fence_before_sync();
       mbar_arrive(B.p_ready);
-      CB2_TL(i, 2);
       // (d) state pass of the previous chunk, placed here so that it runs while
       // MMA2 (P.V) of this chunk executes and MMA3 (Q.Sb) can follow it directly:
       // Sb_i = bf16(St);  St <- g^C St  (ready for this chunk's MMA4)
@@ -306,18 +680,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             ok = wait_flag_abortable(flag, s_abort);
             if (!__all_sync(0xffffffffu, ok)) break;
           }
-          const float4* src = reinterpret_cast<const float4*>(
-              seg_state + (size_t(seg - 1) * n_bh + bh) * (kC * kC) + r * kC + cb0 * 32);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 x = __ldcg(src + j), y = __ldcg(src + 8 + j);
-            va[4 * j] = __float_as_uint(x.x); va[4 * j + 1] = __float_as_uint(x.y);
-            va[4 * j + 2] = __float_as_uint(x.z); va[4 * j + 3] = __float_as_uint(x.w);
-            vb[4 * j] = __float_as_uint(y.x); vb[4 * j + 1] = __float_as_uint(y.y);
-            vb[4 * j + 2] = __float_as_uint(y.z); vb[4 * j + 3] = __float_as_uint(y.w);
-          }
+          load_start_state(seg_state, seg, n_bh, bh, r, cb0, prestaged ? pieces_per_seg : 0,
+                           powf(g, float(piece_rows)), va, vb);
         }
-        CB2_TL(i, 6);
         auto state_block = [&](int cb, uint32_t (&v)[32]) {
           uint32_t w[16];
 #pragma unroll
@@ -334,7 +699,6 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         umma::fence_before_sync();
         fence_proxy_async_smem();
         mbar_arrive(B.sb_ready);
-        CB2_TL(i, 7);
       }
       // (b) K_i <- K_i . g^(C-1-r), in place (MMA1 has finished reading it);
       // this thread owns the 8 chunks of row r that lie in its column half.
@@ -357,13 +721,11 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       fence_proxy_async_smem();
       mbar_arrive(B.kw_ready);
-      CB2_TL(i, 3);
       // (c) o_i = (O1 + g^(r+1) O2) / scale, staged in shared memory in the
       // swizzled layout the TMA store expects
       ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
-      CB2_TL(i, 4);
 #pragma unroll 1
       for (int cbi = 0; cbi < 2; ++cbi) {
         const int cb = half * 2 + cbi;
@@ -395,7 +757,6 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (dv > 64) umma::tma_store_3d(&map_o, 64, row, bh, o_tile + umma::kSubTileBytes);
         bulk_commit();
       }
-      CB2_TL(i, 5);
     }
     // hand the state to the next segment of this head: St after the last MMA4
     if (seg + 1 < n_seg && !prestaged) {
@@ -471,7 +832,7 @@ int decayed_tc_segments(int n_bh, int nchunk, int sms) {
 }
 
 int decayed_seg_states_run(const void* k, const void* v, const float* gamma, int B, int H, int T, int dk,
-                           int dv, int n_seg, float* seg_state, int* dev_status, cudaStream_t st);
+                           int dv, int n_seg, int sub, float* seg_state, int* dev_status, cudaStream_t st);
 
 // Parallel segments per head when heads are fewer than half the SMs: the largest power of
 // two that keeps all CTAs in one wave, divides the chunk count and leaves four chunks or
@@ -488,6 +849,21 @@ int decayed_tc_parallel_segments(int n_bh, int nchunk, int sms) {
   return best;
 }
 
+// How the start states of n parallel segments are prepared.  With at most four pieces to fold,
+// the pre-pass writes the end state of every piece and each attention CTA folds the pieces before
+// its segment itself (no scan launch); the pieces are then made as short as one wave of CTAs
+// allows (`sub` per segment), because the pre-pass is a chain of chunk latencies too.  With more
+// pieces a scan kernel turns end states into start states (sub = 0).
+int decayed_tc_pieces_per_segment(int n_bh, int nchunk, int n_seg, int sms) {
+  if (n_seg <= 1 || n_seg - 1 > 4) return 0;
+  const int per = nchunk / n_seg;
+  int sub = 1;
+  while ((n_seg - 1) * sub * 2 <= 4 && n_bh * (n_seg - 1) * sub * 2 <= sms && per % (sub * 2) == 0 &&
+         per / (sub * 2) >= 4)
+    sub *= 2;
+  return sub;
+}
+
 namespace {
 int device_sms() {
   int dev = 0, sms = 148;
@@ -500,8 +876,12 @@ int device_sms() {
 // Scratch that lets heads be cut into segments: (n_seg - 1) * B*H states of
 // 128 x 128 fp32, then as many flags.
 size_t decayed_tc_scratch_bytes(int B, int H, int T) {
-  const int n_par = decayed_tc_parallel_segments(B * H, (T + kC - 1) / kC, device_sms());
-  if (n_par > 1) return size_t(n_par - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
+  const int nchunk = (T + kC - 1) / kC;
+  const int n_par = decayed_tc_parallel_segments(B * H, nchunk, device_sms());
+  if (n_par > 1) {
+    const int sub = decayed_tc_pieces_per_segment(B * H, nchunk, n_par, device_sms());
+    return size_t(n_par - 1) * (sub > 0 ? sub : 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
+  }
   const int n_seg = decayed_tc_segments(B * H, (T + kC - 1) / kC, device_sms());
   return size_t(n_seg - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
 }
@@ -525,14 +905,18 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
     return CB2_LAUNCH_FAIL;
   const int n_bh = B * H;
   // few heads: parallel segments, start states computed up front
-  const int n_par = decayed_tc_parallel_segments(n_bh, (T + kC - 1) / kC, device_sms());
+  const int nchunk = (T + kC - 1) / kC;
+  const int n_par = decayed_tc_parallel_segments(n_bh, nchunk, device_sms());
+  const int sub = decayed_tc_pieces_per_segment(n_bh, nchunk, n_par, device_sms());
   if (n_par > 1 && scratch && aligned16(scratch) &&
-      scratch_bytes >= size_t(n_par - 1) * n_bh * size_t(kC) * kC * sizeof(float)) {
+      scratch_bytes >= size_t(n_par - 1) * (sub > 0 ? sub : 1) * n_bh * size_t(kC) * kC * sizeof(float)) {
     float* states = static_cast<float*>(scratch);
-    rc = decayed_seg_states_run(k, v, gamma, B, H, T, dk, dv, n_par, states, dev_status, st);
+    rc = decayed_seg_states_run(k, v, gamma, B, H, T, dk, dv, n_par, sub, states, dev_status, st);
     if (rc != CB2_OK) return rc;
+    const int piece_rows = sub > 0 ? nchunk / n_par / sub * kC : 0;
     decayed_tc_kernel<<<n_bh * n_par, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
-                                                                 n_bh, n_par, states, nullptr, 1, dev_status);
+                                                                 n_bh, n_par, states, nullptr, 1, sub, piece_rows,
+                                                                 dev_status);
     CB2_LAUNCH_CHECK();
     return CB2_OK;
   }
@@ -546,7 +930,8 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
   int* seg_flag = n_seg > 1 ? reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + state_bytes) : nullptr;
   if (n_seg > 1 && cudaMemsetAsync(seg_flag, 0, flag_bytes, st) != cudaSuccess) return CB2_LAUNCH_FAIL;
   decayed_tc_kernel<<<n_bh * n_seg, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
-                                                               n_bh, n_seg, seg_state, seg_flag, 0, dev_status);
+                                                               n_bh, n_seg, seg_state, seg_flag, 0, 0, 0,
+                                                               dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

@@ -12,7 +12,9 @@
 //      keeps their relative precision down to underflow, where the term is nil);
 //   2. this file, kernel 2: the start states by the scan  S_s = g^L S_(s-1) + E_(s-1),
 //      S_0 = 0, in fp32, written where the attention kernel expects a segment's
-//      incoming state;
+//      incoming state (skipped when there are at most four pieces to fold: the attention
+//      CTAs then fold the end states themselves, and the pre-pass cuts every segment into
+//      shorter pieces so that it fills the GPU too);
 //   3. decayed_chunk_tc.cu with all segments launched at once, each starting from its
 //      S_s instead of waiting for its predecessor.
 // K and V are read once more than in the one-pass form (6 units of traffic instead of
@@ -189,14 +191,18 @@ decayed_seg_scan_kernel(float* __restrict__ seg_state, const float* __restrict__
 
 }  // namespace
 
-// Phase 1 and 2 of the chunk-parallel form: afterwards slot s-1 of seg_state holds the
-// state segment s starts from (s = 1 .. n_seg-1).
+// Phase 1 and 2 of the chunk-parallel form.  sub == 0: afterwards slot s-1 of seg_state holds the
+// state segment s starts from (s = 1 .. n_seg-1).  sub > 0: every segment but the last is cut
+// into `sub` pieces, slot p holds the end state (from zero) of piece p, and the attention kernel
+// folds the pieces before a segment itself (no scan launch).
 int decayed_seg_states_run(const void* k, const void* v, const float* gamma, int B, int H, int T, int dk,
-                           int dv, int n_seg, float* seg_state, int* dev_status, cudaStream_t st) {
+                           int dv, int n_seg, int sub, float* seg_state, int* dev_status, cudaStream_t st) {
   const uint64_t heads = uint64_t(B) * H;
   const int n_bh = B * H;
   const int nchunk = (T + kSC - 1) / kSC;
   const int per = nchunk / n_seg;
+  const int pieces = (n_seg - 1) * (sub > 0 ? sub : 1);
+  const int piece_chunks = sub > 0 ? per / sub : per;
   CUtensorMap mk, mv;
   int rc = umma::make_map_3d(&mk, k, true, dk, T, heads, 64, 128, true);
   if (rc == CB2_OK) rc = umma::make_map_3d(&mv, v, true, dv, T, heads, 64, 128, true);
@@ -204,9 +210,10 @@ int decayed_seg_states_run(const void* k, const void* v, const float* gamma, int
   if (cudaFuncSetAttribute(decayed_seg_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSsSmem)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
-  decayed_seg_state_kernel<<<unsigned(n_bh * (n_seg - 1)), kSsThreads, kSsSmem, st>>>(mk, mv, gamma, H, n_bh, per,
-                                                                                      seg_state, dev_status);
+  decayed_seg_state_kernel<<<unsigned(n_bh * pieces), kSsThreads, kSsSmem, st>>>(mk, mv, gamma, H, n_bh, piece_chunks,
+                                                                                seg_state, dev_status);
   CB2_LAUNCH_CHECK();
+  if (sub > 0) return CB2_OK;
   decayed_seg_scan_kernel<<<dim3(kSC * kSC / 256, unsigned(n_bh)), 256, 0, st>>>(seg_state, gamma, H, n_bh, n_seg,
                                                                                  per * kSC);
   CB2_LAUNCH_CHECK();
