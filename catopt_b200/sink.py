@@ -63,7 +63,7 @@ from ._lib import B200Error
 from .executors import _GraphMixin, causal_softmax_blocks, decayed_whole_sequence, softmax_blocks_state
 
 __all__ = ["B200Sink", "b200_backend", "b200_target_profile", "decayed_state_carry_plan", "decayed_ragged_plan",
-           "decayed_plan", "om_causal_plan", "linear_chain_plan", "scan_diag_plan",
+           "decayed_plan", "uniform_decayed_term", "om_causal_plan", "linear_chain_plan", "scan_diag_plan",
            "scan_states_plan", "B200ChunkedDecayModule", "B200CausalSoftmaxModule", "B200LinearChainModule",
            "B200ScanStatesModule"]
 
@@ -445,6 +445,46 @@ def decayed_ragged_plan(root: Any) -> dict | None:
             "n": len(pieces), "chunk": None, "scale": scales.pop()}
 
 
+def uniform_decayed_term(B: int, H: int, T: int, d: int, chunk: int, per_head: bool = True, scale: float = 1.0,
+                         dv: int | None = None) -> IR:
+    """The uniform K-chunk decayed-attention term over inputs ``q, k, v`` ``[B,H,T,d]`` and a
+    rate parameter ``g`` (``[H]`` or scalar), spelled exactly as the right-hand side of
+    ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152) with every summand divided by
+    the constant ``scale`` — the form the reference's own executor tests build by hand
+    (tests/test_decayed_lower.py:55-196 there).  ``B200Sink().executors`` routes it to
+    ``b200_om_decayed_chunked``; benchmarks and examples use it to obtain the module a catopt
+    user is handed for a decayed-attention block of these sizes."""
+    from catopt_core.ir import TensorType
+
+    K = T // chunk
+    if K * chunk != T or K < 1:
+        raise ValueError("T must be a multiple of chunk")
+    dv = d if dv is None else dv
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    q, k = Var("q", tt(B, H, T, d)), Var("k", tt(B, H, T, d))
+    v = Var("v", tt(B, H, T, dv))
+    g = Param("g", tt(H)) if per_head else Param("g", tt())
+    sc = Const(float(scale))
+    sizes = [chunk] * K
+    part = lambda t, i: Op.make("split", t, dim=-2, index=i, sizes=sizes)  # noqa: E731
+    kt = Op.make("transpose", k, dim0=-1, dim1=-2)
+    dec = Op.make("decay", g, t=chunk)
+    col = Op.make("unsqueeze", Op.make("decay_vec", g, t=chunk, sign=-1, offset=0), dim=-1)
+    states = [Op.make("matmul", Op.make("transpose", Op.make("mul", part(k, j), col), dim0=-1, dim1=-2), part(v, j))
+              for j in range(K - 1)]
+    arms = []
+    for i in range(K):
+        arm = Op.make("div", Op.make("om_decayed", Op.make("matmul", part(q, i),
+                                                           Op.make("split", kt, dim=-1, index=i, sizes=sizes)),
+                                     dec, part(v, i)), sc)
+        for j in range(i):
+            row = Op.make("unsqueeze", Op.make("decay_vec", g, t=chunk, sign=1, offset=(i - j) * chunk), dim=-1)
+            arm = Op.make("add", arm, Op.make("mul", row, Op.make("div", Op.make("matmul", part(q, i), states[j]), sc)))
+        arms.append(arm)
+    root = arms[0] if K == 1 else Op.make("concat", *arms, dim=-2)
+    return IR(root=root, inputs=[q, k, v], input_names={"q", "k", "v"}, params={"g": g})
+
+
 def decayed_plan(root: Any) -> dict | None:
     """Uniform K-chunk term first (the reference's own parser), then any ragged partition."""
     plan = decayed_state_carry_plan(root)
@@ -459,6 +499,17 @@ class _EvalBase(_GraphMixin, torch.nn.Module):
         self._inputs = ir.inputs
         self.eval_mod = IRModule(ir, param_values)
         self._init_graph_state()
+
+    # what catopt's autotuner reads off a delivered module to re-lower the same term through
+    # another executor (``_recover_ir``, catopt_orchestrator/autotune.py:279-310); the reference's
+    # batched executors delegate these to their embedded module in the same way
+    @property
+    def _root(self) -> Any:
+        return self.eval_mod._root
+
+    @property
+    def _param_map(self) -> Any:
+        return self.eval_mod._param_map
 
     def _input_env(self, xs: tuple) -> tuple:
         """``(x, env)`` as the reference's batched modules build it
@@ -729,6 +780,7 @@ class B200LinearChainModule(_EvalBase):
         plan = linear_chain_plan(ir.root)
         super().__init__(ir, param_values)
         self._plan = plan
+        self._unfolded_root, self._unfolded_params = ir.root, dict(param_values or {})
         if plan is None:
             return
         vals = param_values or {}
@@ -752,6 +804,16 @@ class B200LinearChainModule(_EvalBase):
     @property
     def is_batched(self) -> bool:
         return self._plan is not None
+
+    # the embedded module has folded the weight tree away; a re-lowering of "the same term"
+    # (catopt's autotuner) must see the chain, or no chain executor could ever take it again
+    @property
+    def _root(self) -> Any:
+        return self._unfolded_root
+
+    @property
+    def _param_map(self) -> Any:
+        return self._unfolded_params
 
     def _forward_impl(self, *xs: torch.Tensor) -> Any:
         if self._plan is None:

@@ -355,6 +355,31 @@ def test_decayed_bf16_extreme_rates(dev, gam):
     assert rel_to_max(out, want) <= BF16_TOL
 
 
+@pytest.mark.parametrize("B,H,T", [(1, 8, 4096), (2, 80, 1024)])
+def test_decayed_bf16_mixed_rates_take_both_formulations(dev, B, H, T):
+    """Rates on both sides of the kernel's switch (about 0.74: above it keys are scaled by
+    g^-c once and the accumulator is renormalised every 1, 2, 8 or 64 chunks depending on the
+    rate; below it the chunk-local decaying powers are used), mixed over the heads of ONE
+    launch — with few heads (parallel segments from precomputed pieces) and with more heads
+    than SMs (segments that wait for one another) — against the spelled quadratic form."""
+    from catopt_b200 import ops
+
+    g = torch.Generator().manual_seed(77 + H)
+    d = 128
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(math.sqrt(d)).bfloat16() for _ in range(3))
+    base = torch.tensor([0.3, 0.6, 0.735, 0.745, 0.8, 0.9, 0.97, 1.0])
+    gamma = base.repeat((H + 7) // 8)[:H].contiguous()
+    out = ops.decayed_chunk_fwd(q.to(dev), k.to(dev), v.to(dev), gamma.to(dev), 128, 2.0).cpu()
+    assert torch.isfinite(out.float()).all()
+    heads = range(H) if H <= 8 else (0, 3, 4, 6, 7, 72, 75, 78, 79)
+    for b in (0, B - 1):
+        for h in heads:
+            want = oracle.decayed_quadratic(q[b:b + 1, h:h + 1].float(), k[b:b + 1, h:h + 1].float(),
+                                            v[b:b + 1, h:h + 1].float(), gamma[h:h + 1], 2.0)
+            assert rel_to_max(out[b:b + 1, h:h + 1], want) <= BF16_TOL, (b, h, float(gamma[h]))
+    ops.check_device_status(dev)
+
+
 def test_decayed_bf16_many_heads_and_scale(dev):
     """More heads than SMs (several waves of CTAs) and a non-unit divisor."""
     from catopt_b200 import ops

@@ -513,3 +513,68 @@ def test_an_expired_device_wait_fails_the_sink_gate_as_a_timeout():
         sink.verify(lin, lin, x)
     assert classify(err.value) == FailureClass.TIMEOUT
     assert sink.verify(lin, lin, x).passed            # status consumed, stream and context intact
+
+
+# --------------------------------------------------------------------------- autotuner and measured profile
+def test_autotuned_verifies_times_and_ships_the_b200_candidate_and_feeds_the_profile():
+    """``Autotuned`` (optimize.py:2543-2621, autotune.py) on config 1 with the B200 executor as a
+    named candidate: one search, every candidate re-lowered from the delivered module's term,
+    gated by ``B200Sink.verify`` and timed by the backend's ``Meter``; the winner ships.  With
+    ``profile=`` the medians land in ``TargetProfile.measured_ns`` through the reference's own
+    ``record_measured`` under this input's shape bucket."""
+    from catopt_core.profile import measured_price_ns, record_measured, shape_bucket
+    from catopt_orchestrator.optimize import Autotuned, Optimizer
+
+    ws, x = cases.chain_inputs("c1")
+    seq = torch.nn.Sequential(*[torch.nn.Linear(512, 512, bias=False) for _ in ws])
+    with torch.no_grad():
+        for lin, w in zip(seq, ws):
+            lin.weight.copy_(w)
+    seq, xc = seq.to(DEV).eval(), x.to(DEV)
+    prof = b200.b200_target_profile()
+    assert prof.op_kernel_ns.get("matmul") and prof.measured_ns     # shipped with measured entries
+    gates0 = verify.kernel_gate_calls
+    res = Optimizer(backend=b200.b200_backend()).optimize(
+        seq, xc, strategy=Autotuned(candidates=("eager", "generic", "b200_linear_chain"), n_calls=20, warmup=5,
+                                    profile=prof))
+    at = res.stats["autotune"]
+    recs = at["candidates"]
+    rec = recs["b200_linear_chain"]
+    assert rec["status"] == "timed" and rec["verified"] and rec["max_rel"] < 1e-5, rec
+    assert rec["median_s"] > 0 and rec["n_calls"] == 20
+    assert verify.kernel_gate_calls - gates0 >= 3             # every candidate went through the kernel gate
+    timed = {n: r["median_s"] for n, r in recs.items() if r.get("status") == "timed"}
+    assert set(timed) == {"eager", "generic", "b200_linear_chain"}
+    assert at["winner"] == min(timed, key=timed.get) and not at.get("fallback")
+    bucket = shape_bucket(xc)
+    new_prof = at["profile"]
+    assert new_prof.measured_ns["b200_linear_chain"][bucket]["median_ns"] == pytest.approx(rec["median_s"] * 1e9)
+    # against the unlowered model alone the B200 module wins and is what ships
+    res2 = Optimizer(backend=b200.b200_backend()).optimize(
+        seq, xc, strategy=Autotuned(candidates=("eager", "b200_linear_chain"), n_calls=20, warmup=5))
+    at2 = res2.stats["autotune"]
+    assert at2["winner"] == "b200_linear_chain", {n: r.get("median_s") for n, r in at2["candidates"].items()}
+    assert isinstance(res2.module, b200.B200LinearChainModule) and res2.module.is_batched
+    z = np.load(os.path.join(GOLDEN, "chain.npz"))
+    with torch.no_grad():
+        assert _rel(res2.module(xc), torch.from_numpy(z["c1.y_folded"])) <= 1e-5
+
+    # config 2's term: the B200 executor and the reference's own, both timed by the backend's meter;
+    # the measurement goes into the profile the same way and prices the candidate afterwards
+    from catopt_torch.adapters import TorchSink
+    from catopt_torch.meter import TorchMeter
+
+    q, k, v, gamma, C, scale = cases.decayed_inputs("c2_f32")
+    ir = b200.uniform_decayed_term(2, 4, 1024, 64, C, per_head=False, scale=scale)
+    ins = (q.to(DEV), k.to(DEV), v.to(DEV))
+    ours = _route(b200.B200Sink(), ir.root).lower(ir, {"g": gamma.to(DEV)})
+    theirs = _route(TorchSink(), ir.root).lower(ir, {"g": gamma.to(DEV)})
+    meter = TorchMeter()
+    t_ours = meter.time(ours, ins, warmup=5, n_calls=20)
+    t_theirs = meter.time(theirs, ins, warmup=5, n_calls=20)
+    assert t_ours.failure == "ok" and t_theirs.failure == "ok"
+    assert t_ours.median_s < t_theirs.median_s                 # one launch against the all-pairs schedule
+    b2 = shape_bucket(ins)
+    p2 = record_measured(new_prof, "b200_om_decayed_chunked", b2, t_ours.median_s * 1e9)
+    assert measured_price_ns(p2, "b200_om_decayed_chunked", b2, None) == pytest.approx(t_ours.median_s * 1e9)
+    ops.check_device_status(DEV)

@@ -147,6 +147,31 @@ def test_b200_target_profile_prices_with_the_reference_cost_model():
     assert callable(cost)
 
 
+def test_b200_target_profile_carries_measurements_where_the_cost_model_reads_them():
+    """The executor times sit in ``op_kernel_ns`` / ``measured_ns`` (not in free-form notes):
+    the roofline's measured-kernel floor finds config 1's GEMM, and the autotuner's price lookup
+    finds every B200 executor under its shape bucket."""
+    from catopt_core.cost.roofline import _kernel_lookup
+    from catopt_core.profile import corrected_price_ns, measured_price_ns, shape_bucket
+
+    prof = b200.b200_target_profile()
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    lin = Op.make("linear", Var("input", tt(64, 512)), Param("fused_14", tt(512, 512)))
+    kns = _kernel_lookup(prof.op_kernel_ns)
+    assert kns is not None and kns(lin, {}) == prof.op_kernel_ns["matmul"]["64x512x512"] > 0
+    names = set(prof.measured_ns)
+    assert {"b200_om_decayed_chunked", "b200_linear_chain", "b200_scan_all", "b200_scan", "b200_omd",
+            "b200_om_causal", "b200_om_streaming"} <= names
+    assert names <= set(b200.B200Sink().executors)           # every candidate name is a spec of the sink
+    bucket = shape_bucket(torch.empty(64, 512))
+    assert bucket.endswith("2^15")
+    cuda_bucket = "cuda:0:2^15"
+    want = prof.measured_ns["b200_linear_chain"][cuda_bucket]["median_ns"]
+    assert measured_price_ns(prof, "b200_linear_chain", cuda_bucket, None) == want
+    assert corrected_price_ns(prof, "b200_linear_chain", cuda_bucket, None) == want
+    assert not prof.meta.get("executors_us")                 # nothing left in free-form notes
+
+
 # --------------------------------------------------------------------------- ragged partitions
 def _ragged_term(T, d, arms, sources, scale=2.0, nested=False, per_head=False, B=2, H=2):
     """Hand-built chunked decayed term over a non-uniform partition.
