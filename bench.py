@@ -832,6 +832,11 @@ def run_profile_case(args) -> None:
         gamma = c4_gamma(8).to(dev)
         o = torch.empty_like(v)
         fn = lambda: ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0, out=o)  # noqa: E731
+    elif args.profile_case == "decayed_strong":  # one rank's share of config 4 cut over 8 GPUs: 64 units (537 MB)
+        q, k, v = (_randn_bf16((64, 8192 * 128), gen, 1 / math.sqrt(128)).view(2, 32, 8192, 128) for _ in range(3))
+        gamma = c4_gamma(32).to(dev)
+        o = torch.empty_like(v)
+        fn = lambda: ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0, out=o)  # noqa: E731
     elif args.profile_case == "scan_few":     # config 3 with one batch entry (151 MB): 8 segments side by side
         x = _randn_bf16((1, 4096 * 1024), gen).view(1, 4096, 1024)
         a = torch.sigmoid(4 + 0.5 * torch.randn(1, 4096, 1024, 16, device=dev, generator=gen)).bfloat16()
@@ -874,7 +879,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
+                    choices=["decayed", "decayed_strong", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
