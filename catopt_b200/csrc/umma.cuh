@@ -141,7 +141,7 @@ __device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// ---- tiled TMA load (no multicast): one {64 x 128} box into a sub-tile ------
+// ---- tiled TMA load (plain, one destination CTA): one {64 x 128} box into a sub-tile ------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y,
                                             uint64_t* bar) {
   asm volatile(
