@@ -29,7 +29,13 @@ SIGNATURES: dict[str, tuple] = {
     "cb2_linear_f32": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
-         C.c_void_p, C.c_size_t, C.c_void_p],
+         C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p],
+    ),
+    "cb2_linear_f32_split_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "cb2_linear_f32_split_weight": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "cb2_linear_f32_presplit": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
     ),
     "cb2_matmul_f32": (
         C.c_int,

@@ -24,6 +24,9 @@ bool linear_tf32x3_supported(const float* x, const float* w, const float* bias, 
 size_t linear_tf32x3_scratch_bytes(int n_in, int n_out);
 int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* y, int R, int n_in,
                       int n_out, void* scratch, int* dev_status, cudaStream_t st);
+int linear_tf32x3_split(const float* w, float* w_split, int n_in, int n_out, cudaStream_t st);
+int linear_tf32x3_run_presplit(const float* x, const float* w_split, const float* bias, float* y, int R, int n_in,
+                               int n_out, int* dev_status, cudaStream_t st);
 
 namespace {
 
@@ -321,15 +324,42 @@ extern "C" size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_f
 
 extern "C" int cb2_linear_f32(const float* x, const float* w, const float* bias, float* y, int R,
                               int in_features, int out_features, void* scratch,
-                              size_t scratch_bytes, void* stream) {
+                              size_t scratch_bytes, int* dev_status, void* stream) {
   if (!x || !w || !y) return CB2_NULL_PTR;
   if (R <= 0 || in_features <= 0 || out_features <= 0) return CB2_BAD_SHAPE;
   if (cb2::linear_tf32x3_supported(x, w, bias, y, R, in_features, out_features, scratch, scratch_bytes))
-    return cb2::linear_tf32x3_run(x, w, bias, y, R, in_features, out_features, scratch, nullptr,
+    return cb2::linear_tf32x3_run(x, w, bias, y, R, in_features, out_features, scratch, dev_status,
                                   static_cast<cudaStream_t>(stream));
   return cb2::gemm<true>(x, w, bias, y, R, out_features, in_features,
                          static_cast<float*>(scratch), scratch_bytes,
                          static_cast<cudaStream_t>(stream));
+}
+
+// A weight that never changes (a folded chain) is split into its TF32 parts ONCE:
+// cb2_linear_f32_split_weight writes hi then lo ([out, in] fp32 each) into w_split, and
+// cb2_linear_f32_presplit runs the tensor-core GEMM on it without re-splitting (3 x the weight
+// bytes of traffic saved per call).  Only the shapes the tensor-core path takes.
+extern "C" size_t cb2_linear_f32_split_bytes(int in_features, int out_features) {
+  if (in_features <= 0 || out_features <= 0 || in_features % 4 || out_features % 4) return 0;
+  return cb2::linear_tf32x3_scratch_bytes(in_features, out_features);
+}
+
+extern "C" int cb2_linear_f32_split_weight(const float* w, float* w_split, int in_features, int out_features,
+                                           void* stream) {
+  if (!w || !w_split) return CB2_NULL_PTR;
+  if (in_features <= 0 || out_features <= 0 || in_features % 4 || out_features % 4) return CB2_BAD_SHAPE;
+  if (!cb2::aligned16(w) || !cb2::aligned16(w_split)) return CB2_BAD_ALIGN;
+  return cb2::linear_tf32x3_split(w, w_split, in_features, out_features, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cb2_linear_f32_presplit(const float* x, const float* w_split, const float* bias, float* y, int R,
+                                       int in_features, int out_features, int* dev_status, void* stream) {
+  if (!x || !w_split || !y) return CB2_NULL_PTR;
+  if (R < 256 || in_features <= 0 || out_features <= 0 || in_features % 4 || out_features % 4) return CB2_BAD_SHAPE;
+  if (!cb2::aligned16(x) || !cb2::aligned16(w_split) || !cb2::aligned16(y) || (bias && !cb2::aligned16(bias)))
+    return CB2_BAD_ALIGN;
+  return cb2::linear_tf32x3_run_presplit(x, w_split, bias, y, R, in_features, out_features, dev_status,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cb2_matmul_f32(const float* a, const float* b, float* c, int M, int N, int K,

@@ -339,15 +339,23 @@ bool linear_tf32x3_supported(const float* x, const float* w, const float* bias, 
 // Bytes of scratch for the split weight (hi then lo, each [out, in] fp32).
 size_t linear_tf32x3_scratch_bytes(int n_in, int n_out) { return size_t(2) * n_in * n_out * sizeof(float); }
 
-int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* y, int R, int n_in,
-                      int n_out, void* scratch, int* dev_status, cudaStream_t st) {
+// w -> TF32 hi part and exact remainder, [out, in] fp32 each, hi then lo in `w_split`.
+int linear_tf32x3_split(const float* w, float* w_split, int n_in, int n_out, cudaStream_t st) {
   const size_t wn = size_t(n_in) * n_out;
-  float* w_hi = static_cast<float*>(scratch);
-  float* w_lo = w_hi + wn;
   const size_t n4 = wn / 4;   // n_in % 4 == 0
   w_split_kernel<<<unsigned(std::min<size_t>((n4 + 255) / 256, 592)), 256, 0, st>>>(
-      reinterpret_cast<const float4*>(w), reinterpret_cast<float4*>(w_hi), reinterpret_cast<float4*>(w_lo), n4);
+      reinterpret_cast<const float4*>(w), reinterpret_cast<float4*>(w_split),
+      reinterpret_cast<float4*>(w_split + wn), n4);
   CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
+// The GEMM on an already split weight (a module whose weight never changes splits it once).
+int linear_tf32x3_run_presplit(const float* x, const float* w_split, const float* bias, float* y, int R, int n_in,
+                               int n_out, int* dev_status, cudaStream_t st) {
+  const size_t wn = size_t(n_in) * n_out;
+  const float* w_hi = w_split;
+  const float* w_lo = w_hi + wn;
   CUtensorMap mx, mwhi, mwlo;
   int rc = make_f32_map(&mx, x, R, n_in);
   if (rc == CB2_OK) rc = make_f32_map(&mwhi, w_hi, n_out, n_in);
@@ -367,6 +375,14 @@ int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* 
                                                            int(n_tiles), dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
+}
+
+int linear_tf32x3_run(const float* x, const float* w, const float* bias, float* y, int R, int n_in,
+                      int n_out, void* scratch, int* dev_status, cudaStream_t st) {
+  float* w_split = static_cast<float*>(scratch);
+  const int rc = linear_tf32x3_split(w, w_split, n_in, n_out, st);
+  if (rc != CB2_OK) return rc;
+  return linear_tf32x3_run_presplit(x, w_split, bias, y, R, n_in, n_out, dev_status, st);
 }
 
 }  // namespace cb2

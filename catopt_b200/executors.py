@@ -95,6 +95,9 @@ class B200FoldedLinear(_GraphMixin, torch.nn.Module):
         idx = 2 * len(ws) - 2 if fused_index is None else fused_index
         self.fused_name = f"fused_{idx}"
         self.register_parameter(self.fused_name, torch.nn.Parameter(fused, requires_grad=False))
+        # the folded weight never changes: its TF32 split for the tensor-core path is made once
+        split = ops.linear_split_weight(fused)
+        self.register_buffer("fused_split", split, persistent=False)
         self.bias = None if bias is None else torch.nn.Parameter(
             bias.detach().to(torch.float32).contiguous(), requires_grad=False)
         self._plan: dict | None = {"kind": "folded_linear", "k": len(ws),
@@ -110,7 +113,7 @@ class B200FoldedLinear(_GraphMixin, torch.nn.Module):
         return getattr(self, self.fused_name)
 
     def _forward_impl(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear_f32(x, self.weight, self.bias)
+        return ops.linear_f32(x, self.weight, self.bias, w_split=self.fused_split)
 
 
 class B200ChunkedDecay(_GraphMixin, torch.nn.Module):

@@ -96,10 +96,27 @@ def verify_reduce(ref: torch.Tensor, out: torch.Tensor, n_seg: int = 1,
 
 
 # --------------------------------------------------------------------------- chain
+def linear_split_weight(w: torch.Tensor) -> torch.Tensor | None:
+    """The TF32 hi/lo split of an fp32 weight ``[out, in]`` as one ``[2, out, in]`` tensor, for
+    ``linear_f32(..., w_split=...)``: a module whose weight never changes splits it once instead
+    of on every call.  ``None`` when the tensor-core path cannot take the shape."""
+    require_cuda(w)
+    if w.dtype != torch.float32 or w.dim() != 2:
+        raise B200Error("linear_split_weight takes a float32 matrix")
+    lib = _lib.load()
+    if lib.cb2_linear_f32_split_bytes(w.shape[1], w.shape[0]) == 0:
+        return None
+    out = torch.empty(2, *w.shape, dtype=torch.float32, device=w.device)
+    check(lib.cb2_linear_f32_split_weight(w.data_ptr(), out.data_ptr(), w.shape[1], w.shape[0], stream_ptr()),
+          "cb2_linear_f32_split_weight")
+    return out
+
+
 def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-               out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ w.T (+ bias)`` for fp32 ``x[..., in]``, ``w[out, in]``."""
-    require_cuda(x, w, bias, out)
+               out: torch.Tensor | None = None, w_split: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for fp32 ``x[..., in]``, ``w[out, in]``; ``w_split``
+    (``linear_split_weight(w)``) spares the per-call split on the tensor-core path."""
+    require_cuda(x, w, bias, out, w_split)
     if x.dtype != torch.float32 or w.dtype != torch.float32:
         raise B200Error("linear_f32 takes float32 tensors")
     if w.dim() != 2 or x.shape[-1] != w.shape[1]:
@@ -109,10 +126,18 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
     if out is None:
         out = torch.empty(*x.shape[:-1], n_out, dtype=torch.float32, device=x.device)
     lib = _lib.load()
+    status = device_status(x.device)
+    if w_split is not None and rows >= 256:
+        if tuple(w_split.shape) != (2, n_out, n_in) or w_split.dtype != torch.float32:
+            raise B200Error("w_split must be linear_split_weight(w)")
+        rc = lib.cb2_linear_f32_presplit(x.data_ptr(), w_split.data_ptr(), _ptr(bias), out.data_ptr(), rows, n_in,
+                                         n_out, status.data_ptr(), stream_ptr())
+        check(rc, "cb2_linear_f32_presplit")
+        return out
     need = lib.cb2_linear_f32_scratch_bytes(rows, n_in, n_out)
     scratch = _scratch_buf("linear", need, x.device)
     rc = lib.cb2_linear_f32(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), rows, n_in,
-                            n_out, _ptr(scratch), need, stream_ptr())
+                            n_out, _ptr(scratch), need, status.data_ptr(), stream_ptr())
     check(rc, "cb2_linear_f32")
     return out
 

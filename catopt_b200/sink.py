@@ -799,6 +799,8 @@ class B200LinearChainModule(_EvalBase):
                 return val(t) if isinstance(t, Param) else ops.matmul_f32(fold(t.args[0]), fold(t.args[1]))
             fused = fold(plan["weight_tree"])
         self.fused_weight = torch.nn.Parameter(fused, requires_grad=False)
+        # constant weight: its TF32 split for the tensor-core path is made once, here
+        self.register_buffer("fused_split", ops.linear_split_weight(fused), persistent=False)
         self.bias = None if plan["bias"] is None else torch.nn.Parameter(val(plan["bias"]), requires_grad=False)
 
     @property
@@ -824,7 +826,7 @@ class B200LinearChainModule(_EvalBase):
         if x.dtype != torch.float32 or x.device != self.fused_weight.device:
             return self.eval_mod(*xs)       # bf16 / fp64 activations: generic module, same device
         with torch.cuda.device(x.device):
-            return ops.linear_f32(x.contiguous(), self.fused_weight, self.bias)
+            return ops.linear_f32(x.contiguous(), self.fused_weight, self.bias, w_split=self.fused_split)
 
 
 # --------------------------------------------------------------------------- scan

@@ -100,7 +100,20 @@ int cb2_verify_reduce(const void* ref, const void* out, int64_t numel_per_seg,
 size_t cb2_linear_f32_scratch_bytes(int R, int in_features, int out_features);
 int cb2_linear_f32(const float* x, const float* w, const float* bias, float* y,
                    int R, int in_features, int out_features, void* scratch,
-                   size_t scratch_bytes, void* stream);
+                   size_t scratch_bytes, int* dev_status, void* stream);
+
+/* The folded weight of a chain never changes (`_fold_weight_chains` registers it once as
+ * `fused_N`, torch_bridge.py:2485-2510), so its TF32 split can be done once as well:
+ * cb2_linear_f32_split_weight writes the hi then the lo part ([out,in] fp32 each,
+ * cb2_linear_f32_split_bytes bytes, 16-byte aligned) and cb2_linear_f32_presplit is
+ * cb2_linear_f32's tensor-core path on that buffer (R >= 256, in/out multiples of 4;
+ * other shapes return CB2_BAD_SHAPE and the caller uses cb2_linear_f32). */
+size_t cb2_linear_f32_split_bytes(int in_features, int out_features);
+int cb2_linear_f32_split_weight(const float* w, float* w_split, int in_features,
+                                int out_features, void* stream);
+int cb2_linear_f32_presplit(const float* x, const float* w_split, const float* bias, float* y,
+                            int R, int in_features, int out_features, int* dev_status,
+                            void* stream);
 
 /* cb2_matmul_f32: c[M,N] = a[M,K] . b[K,N], the `matmul` binding
  * (torch_bridge.py:1147) for two dense fp32 matrices. */

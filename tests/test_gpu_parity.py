@@ -1099,6 +1099,70 @@ def test_diag_scan_states_vs_oracle(dev, dtype, T, state):
     assert ops.diag_scan_states(A.double().to(dev), Bv.double().to(dev), h.double().to(dev)) is None
 
 
+def test_linear_with_a_weight_split_once_equals_the_per_call_split(dev):
+    """A module's constant weight is split into its TF32 parts once (cb2_linear_f32_split_weight) and
+    every forward runs cb2_linear_f32_presplit: same kernel on the same parts, so the same bits as
+    cb2_linear_f32; small row counts keep the FMA path."""
+    from catopt_b200 import _lib, ops
+    from catopt_b200.executors import B200FoldedLinear
+
+    g = torch.Generator().manual_seed(61)
+    w = (torch.randn(384, 512, generator=g) / 16).to(dev)
+    b = torch.randn(384, generator=g).to(dev)
+    split = ops.linear_split_weight(w)
+    assert split is not None and split.shape == (2, 384, 512)
+    assert torch.equal(split[0] + split[1], w)                  # hi + lo is the weight exactly
+    for rows in (256, 1000, 4096):
+        x = torch.randn(rows, 512, generator=g).to(dev)
+        assert torch.equal(ops.linear_f32(x, w, b, w_split=split), ops.linear_f32(x, w, b))
+        want = oracle.linear(x.double().cpu(), w.double().cpu(), b.double().cpu())
+        assert rel_to_max(ops.linear_f32(x, w, b, w_split=split), want) <= FP32_TOL
+    x = torch.randn(64, 512, generator=g).to(dev)               # below the tensor-core path: split ignored
+    assert torch.equal(ops.linear_f32(x, w, b, w_split=split), ops.linear_f32(x, w, b))
+    assert ops.linear_split_weight(torch.randn(10, 6, device=dev)) is None
+    ws = [(torch.randn(256, 256, generator=g) / 16).to(dev) for _ in range(3)]
+    mod = B200FoldedLinear(ws)
+    assert mod.fused_split is not None
+    xx = torch.randn(2048, 256, generator=g).to(dev)
+    assert rel_to_max(mod(xx), oracle.chain_eager(xx.double().cpu(), [t.double().cpu() for t in ws])) <= FP32_TOL
+    lib = _lib.load()
+    assert lib.cb2_linear_f32_presplit(xx.data_ptr(), split.data_ptr(), None, xx.data_ptr(), 64, 512, 384, None,
+                                       None) != 0              # too few rows: an error code, not a launch
+    ops.check_device_status(dev)
+
+
+def test_host_pipeline_runs_the_lowered_module_slab_by_slab(dev):
+    """``DecayedHostPipeline``: pinned host tensors in, the module's forward per slab of batch entries on
+    three streams, pinned result out — equal to one call of the same module on the whole batch."""
+    from catopt_b200.executors import B200ChunkedDecay
+    from catopt_b200.host_api import DecayedHostPipeline
+
+    g = torch.Generator().manual_seed(62)
+    B, H, T, d = 6, 4, 512, 64
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(8).bfloat16().pin_memory() for _ in range(3))
+    gamma = torch.tensor([0.9, 0.95, 0.97, 0.99])
+    mod = B200ChunkedDecay(gamma, H, 128).to(dev)
+    out = torch.empty(B, H, T, d, dtype=torch.bfloat16).pin_memory()
+    pipe = DecayedHostPipeline(B, H, T, d, d, torch.bfloat16, n_slabs=4, device=dev, module=mod)
+    assert [e - b for b, e in pipe.bounds] == [2, 2, 2]
+    pipe.run(q, k, v, out)
+    torch.cuda.synchronize()
+    whole = mod(q.to(dev), k.to(dev), v.to(dev)).cpu()
+    assert rel_to_max(out, whole) <= 2.0 ** -7            # same function; segmenting may differ between the calls
+    want = oracle.decayed_state_carry(q.float(), k.float(), v.float(), gamma, 128, 1.0)
+    assert rel_to_max(out, want) <= BF16_TOL
+    pipe.run(k, q, v, out)                                # buffers and events are reusable
+    torch.cuda.synchronize()
+    assert rel_to_max(out, mod(k.to(dev), q.to(dev), v.to(dev)).cpu()) <= 2.0 ** -7
+    built = DecayedHostPipeline(B, H, T, d, d, torch.bfloat16, gamma, 128, 1.0, n_slabs=2, device=dev)
+    built.run(q, k, v, out)
+    torch.cuda.synchronize()
+    assert rel_to_max(out, want) <= BF16_TOL
+    ops_err = pytest.raises(Exception)
+    with ops_err:
+        pipe.run(q.to(dev), k, v, out)                    # device tensors are not what it takes
+
+
 def test_gated_contract_past_two_billion_scores(dev):
     """2^31 + 2^27 score elements (4.6 GB): batch and row offsets must not wrap.  The last batch,
     computed alone, gives the same bits as inside the large call, and scaling one batch's values
