@@ -666,12 +666,11 @@ def run_ours(args) -> None:
 
     # strong scaling: config 4 ITSELF (global batch 16, 512 (batch, head) units) cut over the ranks;
     # every rank runs its contiguous share of the units (64 per rank at 8 GPUs), no collective
-    from catopt_b200.sharding import shard_range
+    from catopt_b200.sharding import shard_units_of_heads
 
-    u0, u1 = shard_range(B * H, rank, world)
+    u0, u1, gs = shard_units_of_heads(gamma, B, rank, world)
     nu = u1 - u0
     qs, ks, vs = (t.view(B * H, T, d)[u0:u1].unsqueeze(0) for t in (q, k, v))     # [1, units, T, d] views
-    gs = gamma.repeat(B)[u0:u1].contiguous()
     os_ = torch.empty(1, nu, T, d, dtype=torch.bfloat16, device=dev)
     lib = _lib.load()
     sbytes = lib.cb2_decayed_chunk_scratch_bytes(1, nu, T, d, d, C, code)

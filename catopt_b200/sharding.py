@@ -34,3 +34,16 @@ def shard_leading(t, rank: int, world: int, n_leading: int = 1):
     flat = t.reshape(units, *t.shape[n_leading:])
     b, e = shard_range(units, rank, world)
     return flat[b:e].contiguous()
+
+
+def shard_units_of_heads(gamma, batch: int, rank: int, world: int):
+    """Sharding decayed attention ``[B,H,T,d]`` by (batch, head) unit: ``(begin, end, rates)``
+    with ``[begin, end)`` this rank's contiguous range of the ``B*H`` flattened units and
+    ``rates`` the decay rate of each of them (unit ``u`` belongs to head ``u % H``), ready to
+    be passed as the per-head rates of a ``[1, end-begin, T, d]`` view of the rank's slice —
+    the kernels take one rate per row of the head axis, so a shard that starts or ends in the
+    middle of a batch entry needs no special case."""
+    H = int(gamma.numel())
+    begin, end = shard_range(batch * H, rank, world)
+    rates = gamma.reshape(-1).repeat(batch)[begin:end].contiguous()
+    return begin, end, rates

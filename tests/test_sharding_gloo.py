@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from catopt_b200.sharding import shard_leading, shard_range
+from catopt_b200.sharding import shard_leading, shard_range, shard_units_of_heads
 
 
 def test_shard_range_tiles_the_axis():
@@ -29,6 +29,32 @@ def test_shard_leading_by_batch_times_head():
     parts = [shard_leading(t, r, 3, n_leading=2) for r in range(3)]
     assert [p.shape[0] for p in parts] == [3, 3, 2]
     assert torch.equal(torch.cat(parts), t.reshape(8, 3, 5))
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_decayed_attention_sharded_by_unit_equals_the_whole(world):
+    """Config 4's partition (contiguous ranges of the batch x head axis, ranks exchange nothing):
+    every rank runs its units as a [1, units, T, d] problem with one rate per unit; the shards,
+    concatenated in rank order, are the unsharded result (CPU oracle stands in for the kernel:
+    this test is about the partition, including shards that cut a batch entry)."""
+    from oracle import oracle
+
+    g = torch.Generator().manual_seed(5)
+    B, H, T, d = 3, 4, 64, 8
+    q, k, v = (torch.randn(B, H, T, d, generator=g, dtype=torch.float64) for _ in range(3))
+    gamma = torch.tensor([0.8, 0.9, 0.95, 0.99], dtype=torch.float64)
+    whole = oracle.decayed_state_carry(q, k, v, gamma, 16, 1.0)
+    parts, covered = [], 0
+    for r in range(world):
+        u0, u1, rates = shard_units_of_heads(gamma, B, r, world)
+        assert u0 == covered and rates.numel() == u1 - u0
+        covered = u1
+        if u1 == u0:
+            continue
+        sl = lambda t: t.reshape(B * H, T, d)[u0:u1].unsqueeze(0)  # noqa: E731
+        parts.append(oracle.decayed_state_carry(sl(q), sl(k), sl(v), rates, 16, 1.0)[0])
+    assert covered == B * H
+    assert torch.equal(torch.cat(parts).reshape(B, H, T, d), whole)
 
 
 def _free_port():
