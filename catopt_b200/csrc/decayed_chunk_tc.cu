@@ -855,7 +855,7 @@ int decayed_tc_parallel_segments(int n_bh, int nchunk, int sms) {
 // allows (`sub` per segment), because the pre-pass is a chain of chunk latencies too.  With more
 // pieces a scan kernel turns end states into start states (sub = 0).
 int decayed_tc_pieces_per_segment(int n_bh, int nchunk, int n_seg, int sms) {
-  if (n_seg <= 1 || n_seg - 1 > 15) return 0;
+  if (n_seg <= 1 || n_seg - 1 > 4) return 0;    // (folding 7 pieces in every CTA measured slower than the scan launch: 81 vs 63 us at 16 heads)
   const int per = nchunk / n_seg;
   int sub = 1;
   while ((n_seg - 1) * sub * 2 <= 4 && n_bh * (n_seg - 1) * sub * 2 <= sms && per % (sub * 2) == 0 &&
