@@ -244,6 +244,126 @@ __global__ void add_bias_kernel(const float* __restrict__ bias, float* __restric
   if (i < size_t(M) * N) y[i] += bias[i % N];
 }
 
+// A handful of rows (M <= 64: config 1's x [64, 512]) through a weight in nn.Linear layout.
+// The generic tile kernels above stage operands through scalar, conflicting shared-memory
+// stores; here both operands stay K-contiguous the way they lie in memory:
+//   CTA = 64 rows x 32 output columns x one K slice of a cluster of up to 8 ranks (16 x 8 = 128
+//   CTAs for 512 -> 512); 128 threads; a 64-deep slice of x (16 KB) and of w (8 KB) is fetched
+//   with every 16-byte load in flight at once and parked in shared memory as rows of 16 float4
+//   with the float4 index XORed by (row & 15), so that the micro-tile reads below are conflict
+//   free; thread = rows {ty + 16 i} x columns {tx + 8 j} (4 x 4), 64 FMAs per 8 LDS.128;
+//   partial tiles are reduced through distributed shared memory in rank order (deterministic).
+constexpr int kSmallM = 64, kSmallN = 32, kSmallK = 64, kSmallThreads = 128;
+
+__global__ void __launch_bounds__(kSmallThreads)
+sgemm_small_rows_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                        float* __restrict__ out, int M, int N, int K, int k_per_split) {
+  namespace cg = cooperative_groups;
+  __shared__ __align__(16) float4 As[kSmallM][16];
+  __shared__ __align__(16) float4 Bs[kSmallN][16];
+  __shared__ __align__(16) float part[kSmallM][kSmallN + 4];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x, tx = tid % 8, ty = tid / 8;
+  const int n0 = blockIdx.x * kSmallN;
+  const int kb = blockIdx.z * k_per_split;
+  const int ke = min(K, kb + k_per_split);
+  float acc[4][4] = {};
+  for (int k0 = kb; k0 < ke; k0 += kSmallK) {
+    float4 av[8], bv[4];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const int idx = tid + kSmallThreads * p, r = idx >> 4, k4 = idx & 15, gk = k0 + 4 * k4;
+      av[p] = (r < M && gk < ke) ? __ldg(reinterpret_cast<const float4*>(A + size_t(r) * K + gk))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int idx = tid + kSmallThreads * p, r = idx >> 4, k4 = idx & 15, gk = k0 + 4 * k4;
+      bv[p] = (n0 + r < N && gk < ke) ? __ldg(reinterpret_cast<const float4*>(W + size_t(n0 + r) * K + gk))
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (k0 > kb) __syncthreads();          // the previous slice has been consumed
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const int idx = tid + kSmallThreads * p, r = idx >> 4, k4 = idx & 15;
+      As[r][k4 ^ (r & 15)] = av[p];
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int idx = tid + kSmallThreads * p, r = idx >> 4, k4 = idx & 15;
+      Bs[r][k4 ^ (r & 15)] = bv[p];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k4 = 0; k4 < 16; ++k4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[ty + 16 * i][k4 ^ ty];          // (ty + 16 i) & 15 == ty
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[tx + 8 * j][k4 ^ ((tx + 8 * j) & 15)];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+          acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+          acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+          acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+        }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) part[ty + 16 * i][tx + 8 * j] = acc[i][j];
+  cluster.sync();   // every rank's partial tile is complete and visible cluster-wide
+  const unsigned S = cluster.num_blocks(), rank = cluster.block_rank();
+  const int rows_per = kSmallM / int(S);
+  for (int e = tid; e < rows_per * (kSmallN / 4); e += kSmallThreads) {
+    const int row = int(rank) * rows_per + e / (kSmallN / 4), c4 = (e % (kSmallN / 4)) * 4;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (unsigned z = 0; z < S; ++z) {
+      const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(&part[row][c4], z));
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    if (row < M) {
+      const float o4[4] = {sum.x, sum.y, sum.z, sum.w};
+      for (int j = 0; j < 4; ++j) {
+        const int gn = n0 + c4 + j;
+        if (gn < N) out[size_t(row) * N + gn] = o4[j] + (bias ? bias[gn] : 0.f);
+      }
+    }
+  }
+  cluster.sync();   // nobody leaves while a peer may still read its shared memory
+}
+
+// 0 = the shape is not this kernel's; otherwise the cluster size (1, 2, 4 or 8 K slices).
+int small_rows_splits(const float* A, const float* W, int M, int N, int K) {
+  if (M > kSmallM || K % 4 != 0 || K < kSmallK || !aligned16(A) || !aligned16(W)) return 0;
+  const int tiles = (N + kSmallN - 1) / kSmallN;
+  int s = 1;
+  while (s < 8 && tiles * s * 2 <= kNumSMs && K / (s * 2) >= kSmallK) s *= 2;
+  return s;
+}
+
+int small_rows_run(const float* A, const float* W, const float* bias, float* C, int M, int N, int K, int splits,
+                   cudaStream_t st) {
+  const int kps = (((K + splits - 1) / splits + 3) / 4) * 4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + kSmallN - 1) / kSmallN, 1, splits);
+  cfg.blockDim = dim3(kSmallThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 1;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = splits;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, sgemm_small_rows_kernel, A, W, bias, C, M, N, K, kps) == cudaSuccess ? CB2_OK
+                                                                                                      : CB2_LAUNCH_FAIL;
+}
+
 // Number of K splits that brings the grid up to about one CTA per SM.
 int pick_splits(int M, int N, int K) {
   const int tiles = ((M + kTile - 1) / kTile) * ((N + kTile - 1) / kTile);
@@ -258,6 +378,13 @@ int pick_splits(int M, int N, int K) {
 template <bool B_NK>
 int gemm(const float* A, const float* Bm, const float* bias, float* C, int M, int N, int K,
          float* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (B_NK) {   // a handful of rows through an nn.Linear weight: the K-contiguous kernel
+    const int s = small_rows_splits(A, Bm, M, N, K);
+    if (s > 0) {
+      if (small_rows_run(A, Bm, bias, C, M, N, K, s, st) == CB2_OK) return CB2_OK;
+      (void)cudaGetLastError();   // cluster launch refused: the generic kernels below
+    }
+  }
   const int splits = pick_splits(M, N, K);
   dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile, 1);
   if (splits > 1) {
