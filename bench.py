@@ -574,7 +574,8 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
     # config 5: verify 13 checks x 256 probes x [4,512,1024] bf16; probes sharded over ranks.
     # The pairs are real decoder outputs: the bf16 original against its optimized graph, per block
     # and end to end, for every probe of this rank (built once, outside the timed region).
-    p0, p1 = shard_range(256, rank, world)
+    n_probes = args.probes
+    p0, p1 = shard_range(n_probes, rank, world)
     probes = p1 - p0
     ref, outp = decoder_pairs(range(p0, p1), dev)
     res = torch.empty(13, 4, device=dev)
@@ -600,7 +601,8 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
               "13 checks per step (12 block pairs + 1 end-to-end pair of real decoder outputs: bf16 original vs "
               "its optimized graph); ends with one max all-reduce when sharded; result checked against eager maxima",
               traffic_key="verify")
-    e["tokens_per_s"] = 256 * 4 * 512 * 13 / (ms / K / 1e3)  # probe tokens x checks, whole job
+    e["tokens_per_s"] = n_probes * 4 * 512 * 13 / (ms / K / 1e3)  # probe tokens x checks, whole job
+    e["probes"] = n_probes
     e["max_rel_per_check"] = [round(v, 6) for v in max_rel]
     e["checks_within_rtol_2e-2"] = f"{sum(v < 2e-2 for v in max_rel)} of 13 (the end-to-end pair carries the bf16 rounding of all 12 blocks)"
     out["config5_verify_bf16"] = e
@@ -885,6 +887,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel lines")
+    ap.add_argument("--probes", type=int, default=256,
+                    help="probes of config 5's verify step (256 = the benchmark config; fewer for profiler runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.profile_case:
