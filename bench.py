@@ -692,9 +692,11 @@ def run_ours(args) -> None:
               "tokens_per_s": tokens / t_strong, "speedup_over_one_gpu_sized_step": t_step / t_strong,
               "note": "speedup = this run's own 512-unit step time (the headline step, one GPU's worth) over the "
                       "sharded step time, max over ranks",
-              "path": ("one CTA per unit" if sbytes == 0 else
-                       "parallel segments from precomputed start states" if nu * 2 <= 148 else
-                       "segments handing their state over in scratch"),
+              "path": {-1: "not on the tensor cores", 0: "one CTA per unit",
+                       1: "segments of a unit handing their state over in scratch",
+                       2: "parallel segments from start states computed by a pre-pass",
+                       3: "two CTAs per unit in one launch, the second accumulating the first's state itself"}[
+                  lib.cb2_decayed_chunk_plan(1, nu, T, d, d, C, code)],
               "scratch_bytes": int(sbytes), "vs_full_launch_max_rel": rep_s.max_rel,
               "hbm_floor_ms": 4 * nu * T * d * 2 / (pk["hbm_gbs"] * 1e9) * 1e3}
     del qs, ks, vs, os_, fl

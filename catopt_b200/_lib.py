@@ -86,6 +86,10 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_int,
          C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
     ),
+    "cb2_decayed_chunk_plan": (
+        C.c_int,
+        [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
+    ),
     "cb2_decayed_chunk_on_tensor_cores": (
         C.c_int,
         [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],

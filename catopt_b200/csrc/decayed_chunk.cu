@@ -17,6 +17,7 @@ int decayed_small_run(const void* q, const void* k, const void* v, void* o, cons
                       cudaStream_t st);
 bool decayed_tc_supported(int B, int H, int T, int dk, int dv, int C, int dtype);
 size_t decayed_tc_scratch_bytes(int B, int H, int T);
+int decayed_tc_plan(int B, int H, int T);
 int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
                    int H, int T, int dk, int dv, int C, float scale, void* scratch, size_t scratch_bytes,
                    int* dev_status, cudaStream_t st);
@@ -43,6 +44,11 @@ extern "C" int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, in
                  cb2::decayed_tc_supported(B, H, T, dk, dv, chunk, dtype)
              ? 1
              : 0;
+}
+
+extern "C" int cb2_decayed_chunk_plan(int B, int H, int T, int dk, int dv, int chunk, int dtype) {
+  if (!cb2_decayed_chunk_on_tensor_cores(B, H, T, dk, dv, chunk, dtype)) return -1;
+  return cb2::decayed_tc_plan(B, H, T);
 }
 
 extern "C" int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,

@@ -159,6 +159,7 @@ struct FastCtx {
   float* seg_state;
   int* seg_flag;
   volatile int* s_abort;
+  int pre;                  // leading chunks (an even count) walked for their state only
 };
 
 __device__ __forceinline__ void fast_roles(const FastCtx& c) {
@@ -168,6 +169,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
   volatile int* s_abort = c.s_abort;
   const int nchunk = c.nchunk;
   const bool has_in = c.has_in;
+  const int pre = c.pre;
   const uint32_t tmem = c.tmem;
   const uint32_t ring_addr = smem_u32(smem + kOffRing);
   const uint32_t sb_addr = smem_u32(smem + kOffSb);
@@ -185,9 +187,11 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
       umma::tma_prefetch_desc(c.map_o);
       const int ntiles = 3 * nchunk;
       for (int t = 0; t < ntiles; ++t) {
-        const int slot = t % kSlotsFast, use = t / kSlotsFast;
-        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort)) break;
         const int i = t / 3, which = t % 3;  // 0: K, 1: Q, 2: V
+        if (which == 1 && i < pre) continue;       // state-only chunk: no Q
+        // K and V slots are used by every chunk; the two Q slots only from chunk `pre` (even) on
+        const int slot = t % kSlotsFast, use = which == 1 ? (i - pre) / 2 : t / kSlotsFast;
+        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort)) break;
         const CUtensorMap* mp = which == 0 ? c.map_k : (which == 1 ? c.map_q : c.map_v);
         unsigned char* dst = smem + kOffRing + slot * kTile;
         const int row = (c.chunk0 + i) * kC;
@@ -208,15 +212,18 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         const uint32_t k_addr = ring_addr + (tk % kSlotsFast) * kTile;
         const uint32_t q_addr = ring_addr + (tq % kSlotsFast) * kTile;
         const uint32_t v_addr = ring_addr + (tv % kSlotsFast) * kTile;
+        const bool state_only = i < pre;
         // MMA1: S' = Q K~^T  (K~ is ready once the compute group has scaled the tile)
         if (!mbar_wait_abortable(B.kw_ready, ph, s_abort)) break;
-        if (!mbar_wait_abortable(&B.full[tq % kSlotsFast], (tq / kSlotsFast) & 1, s_abort)) break;
-        umma::fence_after_sync();
+        if (!state_only) {
+          if (!mbar_wait_abortable(&B.full[tq % kSlotsFast], ((i - pre) / 2) & 1, s_abort)) break;
+          umma::fence_after_sync();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma::mma_bf16(tmem + kColS, umma::desc_kmajor(q_addr, ks), umma::desc_kmajor(k_addr, ks),
-                         idesc_kk, ks > 0);
-        umma::mma_commit(B.s_ready);
+          for (int ks = 0; ks < 8; ++ks)
+            umma::mma_bf16(tmem + kColS, umma::desc_kmajor(q_addr, ks), umma::desc_kmajor(k_addr, ks),
+                           idesc_kk, ks > 0);
+          umma::mma_commit(B.s_ready);
+        }
         // MMA4: A (+)= K~^T V.  Issued ahead of MMA2/MMA3: it does not depend on the mask, so the
         // tensor core works through it while the compute group turns S' into P'.  The compute
         // group must have finished copying the previous accumulator into Sb first.
@@ -230,9 +237,15 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
           umma::mma_bf16(tmem + kColA, umma::desc_mnmajor(k_addr, ks), umma::desc_mnmajor(v_addr, ks),
                          idesc_nn, (i > 0) || has_in || (ks > 0));
         umma::mma_commit(&B.empty[tk % kSlotsFast]);
+        if (state_only) {                 // nothing else in a state-only chunk
+          umma::mma_commit(&B.empty[tv % kSlotsFast]);
+          umma::mma_commit(B.o_ready);
+          umma::mma_commit(B.st_ready);
+          continue;
+        }
         // MMA2: O' = P' V
         if (!mbar_wait_abortable(B.p_ready, ph, s_abort)) break;
-        if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
+        if (i > pre && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -295,7 +308,35 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
     for (int i = 0; alive && i < nchunk; ++i) {
       const uint32_t ph = i & 1;
       const int mi = (c.chunk0 + i) % m;
+      const bool state_only = i < pre;
       bool ok = true;
+      if (state_only) {
+        // K and V only: the accumulator just grows (MMA4); every m chunks it is renormalised here.
+        // (o_ready of the previous chunk, waited for below, says its MMA4 has completed.)
+        if (i > 0) {
+          if (mi == 0) {
+            const int cb0 = half * 2;
+            umma::tmem_ld32(lane_base + kColA + cb0 * 32, va);
+            umma::tmem_ld32(lane_base + kColA + cb0 * 32 + 32, vb);
+            umma::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              va[j] = __float_as_uint(__uint_as_float(va[j]) * g_renorm);
+              vb[j] = __float_as_uint(__uint_as_float(vb[j]) * g_renorm);
+            }
+            umma::tmem_st32(lane_base + kColA + cb0 * 32, va);
+            umma::tmem_st32(lane_base + kColA + cb0 * 32 + 32, vb);
+            umma::tmem_wait_st();
+          }
+          umma::fence_before_sync();
+          mbar_arrive(B.sb_ready);
+        }
+        if (i + 1 < nchunk && !scale_k(i + 1)) break;
+        ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        umma::fence_after_sync();
+        continue;
+      }
       // (s) Sb = bf16(A) for this chunk's MMA3.  First thing in the iteration: the accumulator is
       // final and Sb is free once every MMA of the previous chunk has completed, and the copy then
       // runs under MMA1 of this chunk (operands from shared memory: the tensor-memory read port is
@@ -382,7 +423,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
       mbar_arrive(B.p_ready);
       // the previous chunk's output has left the ring tile it was staged in (that chunk's Q
       // tile): hand the slot back to the producer
-      if (tid == 64 && i > 0) {
+      if (tid == 64 && i > pre) {
         bulk_wait_read<0>();
         mbar_arrive(&B.empty[(3 * (i - 1) + 1) % kSlotsFast]);
       }
@@ -464,7 +505,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int n_bh, int n_seg,
                   float* __restrict__ seg_state, int* __restrict__ seg_flag, int prestaged, int pieces_per_seg,
-                  int piece_rows, int* dev_status) {
+                  int piece_rows, int self_split, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
   // __shared__ array keeps every access a shared-space (LDS/STS) access
@@ -482,10 +523,28 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x % n_bh;
   const int seg = blockIdx.x / n_bh;               // segment-major launch order
-  const int nchunk = (T + kC - 1) / kC / n_seg;    // chunks of this segment
-  const int chunk0 = seg * nchunk;                 // first chunk of the segment in the sequence
-  const bool has_in = seg > 0;                     // starts from a predecessor's state
   const float g = gamma[bh % H];
+  // decay rates in [0.74, 1]: the cheaper formulation (see fast_roles); anything else keeps
+  // the chunk-local decaying powers, which are safe for every rate
+  const float lg = -log2f(g);
+  const bool fast = g > 0.f && g <= 1.f && float(kC) * lg <= 56.f;
+  int nchunk = (T + kC - 1) / kC / n_seg;          // chunks of this segment
+  int chunk0 = seg * nchunk;                       // first chunk of the segment in the sequence
+  bool has_in = seg > 0;                           // starts from a predecessor's state
+  int pre = 0;                                     // leading chunks walked for their state only
+  if (self_split > 0) {
+    // Two CTAs per head, no scratch, no flags, one launch: the first walks chunks [0, self_split);
+    // the second walks the whole head but only accumulates the state over those chunks (K and V
+    // alone, no scores, no output) and produces chunks [self_split, end).  (n_seg == 1 here.)
+    chunk0 = 0;
+    has_in = false;
+    if (fast) {
+      pre = seg == 0 ? 0 : self_split;
+      nchunk = seg == 0 ? self_split : nchunk;
+    } else if (seg != 0) {
+      nchunk = 0;                                  // the every-rate roles walk the head in one CTA
+    }
+  }
   const uint32_t ring_addr = smem_u32(smem + kOffRing);
   const uint32_t sb_addr = smem_u32(smem + kOffSb);
 
@@ -520,14 +579,10 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   umma::fence_after_sync();
   const uint32_t tmem = *s_tmem;
 
-  // decay rates in [0.74, 1]: the cheaper formulation (see fast_roles); anything else keeps
-  // the chunk-local decaying powers below, which are safe for every rate
-  const float lg = -log2f(g);
-  const bool fast = g > 0.f && g <= 1.f && float(kC) * lg <= 56.f;
   if (fast) {
     fast_roles(FastCtx{smem, B, tmem, &map_q, &map_k, &map_v, &map_o, bh, seg, n_bh, n_seg, nchunk, chunk0, dv,
                        prestaged, pieces_per_seg, exp2f(-lg * float(piece_rows)), has_in, lg, inv_scale, seg_state,
-                       seg_flag, s_abort});
+                       seg_flag, s_abort, pre});
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -790,7 +845,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   // Teardown: everyone meets, the last MMA4 is drained, TMEM goes back.
   __syncwarp();
-  if (warp == 1 && lane == 0 && !*s_abort) {
+  if (warp == 1 && lane == 0 && !*s_abort && nchunk > 0) {
     // the final commit (st_ready of the last chunk) covers every MMA issued
     mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
   }
@@ -864,6 +919,19 @@ int decayed_tc_pieces_per_segment(int n_bh, int nchunk, int n_seg, int sms) {
   return sub;
 }
 
+// Between a quarter and half as many heads as SMs, long sequences: two CTAs per head in ONE launch with
+// no scratch — the second walks the first `split` chunks for their state only (K and V: about half
+// the time of a full chunk when the GPU is busy) before producing the rest, so the split sits past the middle; even, so
+// that the two Q slots of the ring keep alternating.  Bit-identical to one CTA per head.  0 = not
+// this case.
+int decayed_tc_self_split(int n_bh, int nchunk, int sms) {
+  if (n_bh * 2 > sms || n_bh * 4 <= sms || nchunk < 16) return 0;
+  // measured at 64 heads x 64 chunks: split 28: 143 us, 36: 135, 40: 131, 44: 125, 48: 131, 56: 150
+  const int split = 2 * ((nchunk * 11 + 16) / 32);     // about 0.69 of the chunks
+  if (split < 2 || split > nchunk - 2) return 0;
+  return split;
+}
+
 namespace {
 int device_sms() {
   int dev = 0, sms = 148;
@@ -877,6 +945,7 @@ int device_sms() {
 // 128 x 128 fp32, then as many flags.
 size_t decayed_tc_scratch_bytes(int B, int H, int T) {
   const int nchunk = (T + kC - 1) / kC;
+  if (decayed_tc_self_split(B * H, nchunk, device_sms()) > 0) return 0;
   const int n_par = decayed_tc_parallel_segments(B * H, nchunk, device_sms());
   if (n_par > 1) {
     const int sub = decayed_tc_pieces_per_segment(B * H, nchunk, n_par, device_sms());
@@ -884,6 +953,17 @@ size_t decayed_tc_scratch_bytes(int B, int H, int T) {
   }
   const int n_seg = decayed_tc_segments(B * H, (T + kC - 1) / kC, device_sms());
   return size_t(n_seg - 1) * B * H * (size_t(kC) * kC * sizeof(float) + sizeof(int));
+}
+
+// How a call of these sizes is cut into CTAs (with the scratch decayed_tc_scratch_bytes asks for):
+// 0 one CTA per head; 1 segments of a head handing their state over in scratch (more heads than SMs);
+// 2 parallel segments from start states computed by a pre-pass; 3 two CTAs per head, the second
+// accumulating the first's state by itself (no scratch).
+int decayed_tc_plan(int B, int H, int T) {
+  const int nchunk = (T + kC - 1) / kC, n_bh = B * H, sms = device_sms();
+  if (decayed_tc_self_split(n_bh, nchunk, sms) > 0) return 3;
+  if (decayed_tc_parallel_segments(n_bh, nchunk, sms) > 1) return 2;
+  return decayed_tc_segments(n_bh, nchunk, sms) > 1 ? 1 : 0;
 }
 
 int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B,
@@ -904,8 +984,15 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
   const int n_bh = B * H;
-  // few heads: parallel segments, start states computed up front
   const int nchunk = (T + kC - 1) / kC;
+  // two CTAs per head, the second accumulating the first's state by itself: one launch, no scratch
+  if (const int split = decayed_tc_self_split(n_bh, nchunk, device_sms())) {
+    decayed_tc_kernel<<<n_bh * 2, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale, n_bh, 1,
+                                                             nullptr, nullptr, 1, 0, 0, split, dev_status);
+    CB2_LAUNCH_CHECK();
+    return CB2_OK;
+  }
+  // few heads: parallel segments, start states computed up front
   const int n_par = decayed_tc_parallel_segments(n_bh, nchunk, device_sms());
   const int sub = decayed_tc_pieces_per_segment(n_bh, nchunk, n_par, device_sms());
   if (n_par > 1 && scratch && aligned16(scratch) &&
@@ -916,7 +1003,7 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
     const int piece_rows = sub > 0 ? nchunk / n_par / sub * kC : 0;
     decayed_tc_kernel<<<n_bh * n_par, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
                                                                  n_bh, n_par, states, nullptr, 1, sub, piece_rows,
-                                                                 dev_status);
+                                                                 0, dev_status);
     CB2_LAUNCH_CHECK();
     return CB2_OK;
   }
@@ -931,7 +1018,7 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
   if (n_seg > 1 && cudaMemsetAsync(seg_flag, 0, flag_bytes, st) != cudaSuccess) return CB2_LAUNCH_FAIL;
   decayed_tc_kernel<<<n_bh * n_seg, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
                                                                n_bh, n_seg, seg_state, seg_flag, 0, 0, 0,
-                                                               dev_status);
+                                                               0, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

@@ -456,15 +456,8 @@ int launch_scan_tma(const void* a, const void* x, const void* b, const void* c, 
   return CB2_OK;
 }
 
-// Lanes per channel on the fast path: 4 n per thread by default; the
-// environment variable CB2_SCAN_NPT=8 selects 8 n per thread (a tuning knob).
-inline int scan_npt() {
-  static int v = [] {
-    const char* e = getenv("CB2_SCAN_NPT");
-    return (e && e[0] == '8') ? 8 : 4;
-  }();
-  return v;
-}
+// n per thread on the fast path: 4 (8 n per thread was measured and is no faster).
+inline int scan_npt() { return 4; }
 
 // ---------------------------------------------------------------------------
 // `a` shared over n ([B,T,D]), fast path (D a multiple of 32).  With one decay

@@ -181,6 +181,14 @@ size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv,
  * state on chip), 0 when it takes the fp32 FMA path (three launches). */
 int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, int dv,
                                       int chunk, int dtype);
+/* How the tensor-core path cuts a call of these sizes into CTAs, given the scratch the size
+ * query asks for: 0 one CTA per (batch, head); 1 a head's segments handing their state over
+ * in scratch (more heads than SMs: fills the last wave); 2 parallel segments from start
+ * states computed by a pre-pass (few heads); 3 two CTAs per head in one launch, the second
+ * accumulating the first's state from K and V by itself (a quarter to half as many heads as
+ * SMs; no scratch).  -1: the call does not run on the tensor cores.  0, 1 and 3 give the
+ * same bits. */
+int cb2_decayed_chunk_plan(int B, int H, int T, int dk, int dv, int chunk, int dtype);
 int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
                           const float* gamma, int B, int H, int T, int dk, int dv,
                           int chunk, float scale, int dtype, void* scratch,

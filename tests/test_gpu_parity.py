@@ -380,6 +380,40 @@ def test_decayed_bf16_mixed_rates_take_both_formulations(dev, B, H, T):
     ops.check_device_status(dev)
 
 
+def test_decayed_bf16_two_ctas_per_head_without_scratch_give_one_pass_bits(dev):
+    """Between a quarter and half as many heads as SMs (one rank's share of config 4 cut over 8
+    GPUs): two CTAs per head in one launch, the second accumulating the state of the first's
+    chunks from K and V alone before producing the rest — no scratch, no flags.  The same heads
+    inside a launch with more heads than SMs (where a head's segments hand their state over and
+    the bits are those of one CTA per head) must come out bit-identical; rates on both sides of
+    the formulation switch; values against the state-carry oracle."""
+    from catopt_b200 import _lib, ops
+
+    g = torch.Generator().manual_seed(91)
+    B, H, T, d = 5, 32, 2048, 128
+    q, k, v = (torch.randn(B, H, T, d, generator=g).div_(math.sqrt(d)).bfloat16().to(dev) for _ in range(3))
+    gamma = (1 - torch.exp2(-5 - 8 * torch.arange(H) / H)).float()
+    gamma[5], gamma[17] = 0.5, 0.745
+    gamma = gamma.to(dev)
+    lib = _lib.load()
+    assert lib.cb2_decayed_chunk_scratch_bytes(2, H, T, d, d, 128, 1) == 0      # 64 heads: nothing to allocate
+    whole = ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0)
+    part = ops.decayed_chunk_fwd(q[:2].contiguous(), k[:2].contiguous(), v[:2].contiguous(), gamma, 128, 1.0)
+    assert torch.equal(part.view(torch.int16), whole[:2].view(torch.int16))
+    for b, h in ((0, 0), (1, 5), (0, 17), (1, 31)):
+        want = oracle.decayed_state_carry(q[b:b + 1, h:h + 1].float().cpu(), k[b:b + 1, h:h + 1].float().cpu(),
+                                          v[b:b + 1, h:h + 1].float().cpu(), gamma[h:h + 1].cpu(), 128, 1.0)
+        assert rel_to_max(part[b:b + 1, h:h + 1], want) <= BF16_TOL, (b, h)
+    # a ragged length on the same path (the last chunk is partial)
+    T2 = 2048 + 77
+    q2, k2, v2 = (torch.randn(2, H, T2, d, generator=g).div_(math.sqrt(d)).bfloat16().to(dev) for _ in range(3))
+    o2 = ops.decayed_chunk_fwd(q2, k2, v2, gamma, 1, 1.0)
+    want = oracle.decayed_quadratic(q2[1:, 30:31].float().cpu(), k2[1:, 30:31].float().cpu(), v2[1:, 30:31].float().cpu(),
+                                    gamma[30:31].cpu(), 1.0)
+    assert rel_to_max(o2[1:, 30:31], want) <= BF16_TOL
+    ops.check_device_status(dev)
+
+
 def test_decayed_bf16_many_heads_and_scale(dev):
     """More heads than SMs (several waves of CTAs) and a non-unit divisor."""
     from catopt_b200 import ops
