@@ -517,7 +517,15 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
         ms, 8 * Tp, 4 * Tp * St * 4, 1,
         "one pass: 2 reads + 2 writes of [1024, 8*1024*16] fp32 (2.1 GB > L2); includes the allocation of the two outputs",
         flops=3 * Tp * St)
-    del ap, bp
+    # every state of the same 1024 steps from an initial state (the stacked-map form of an unrolled
+    # scan, spec b200_scan_all): a and b read once, the states written once (3 x 0.54 GB)
+    hp = torch.randn(St, device=dev, generator=gen)
+    ms = time_steps(lambda: ops.diag_scan_states(ap, bp, hp), K, W, world)
+    out["config3_all_states_fp32_T1024"] = entry(
+        ms, 8 * Tp, 3 * Tp * St * 4, 1,
+        "one pass: 2 reads + 1 write of [1024, 8*1024*16] fp32 (1.6 GB > L2); includes the allocation of the output",
+        flops=2 * Tp * St)
+    del ap, bp, hp
 
     # causal online-softmax executor (no config of its own in the benchmark spec), bf16, d=128:
     # a long-sequence case that fills the GPU (268 MB > L2) and a short one (256 CTAs: tail-bound)
@@ -856,6 +864,11 @@ def run_profile_case(args) -> None:
         ap_ = torch.sigmoid(4 + 0.5 * torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen))
         bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
         fn = lambda: ops.diag_prefix_maps(ap_, bp_)  # noqa: E731
+    elif args.profile_case == "states":     # every state of 256 steps over config 3's state, fp32: 403 MB
+        ap_ = torch.sigmoid(4 + 0.5 * torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen))
+        bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
+        hp_ = torch.randn(8 * 1024 * 16, device=dev, generator=gen)
+        fn = lambda: ops.diag_scan_states(ap_, bp_, hp_)  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
         ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
         outp = ref.clone()
@@ -882,7 +895,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "decayed_strong", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
+                    choices=["decayed", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -37,6 +37,7 @@ EXECUTORS = {
     "config3_diag_scan_bf16": ("b200_scan_all", 8 * 4096 * 1024 * 16 + 8 * 4096 * 1024),
     "config3_shared_decay_bf16": ("b200_scan_all", 2 * 8 * 4096 * 1024),
     "config3_scan_tree_final_state_fp32": ("b200_scan", 2 * 4096 * 8 * 1024 * 16),
+    "config3_all_states_fp32_T1024": ("b200_scan_all", 2 * 1024 * 8 * 1024 * 16 + 8 * 1024 * 16),
     "config3_all_prefix_maps_fp32_T1024": ("b200_omd", 2 * 1024 * 8 * 1024 * 16),
     "om_causal_bf16_B1_H32_T8192_d128": ("b200_om_causal", 3 * 32 * 8192 * 128),
     "om_causal_bf16_B2_H8_T2048_d128": ("b200_om_causal", 3 * 16 * 2048 * 128),

@@ -611,9 +611,11 @@ def om_causal_plan(root: Any) -> dict | None:
     with ``S_i = (q * scale) @ k_i^T`` and ``M_i`` the columns ``[o_i, o_i + n_i)``
     of ``cmask(<any [.., Tq, sum n] tensor>)`` (bad where ``j > t``; o_i the keys
     before block i).  Leaves are read left to right = key order; every block must
-    share q and the scale and appear once.  Returns ``{q, k_blocks, v_blocks,
-    sizes, scale, n, causal}`` or ``None`` (offset masks, explicit attention
-    biases, mixed trees: the reference's own om executors keep them)."""
+    share q and the scale and appear once; all masks slice ONE ``cmask``, whose
+    offset ``off`` (key j visible to query t iff ``j + off <= t``, om.py:1023-1029)
+    is part of the plan.  Returns ``{q, k_blocks, v_blocks, sizes, scale, n, causal,
+    off}`` or ``None`` (explicit attention biases, mixed trees: the reference's own
+    om executors keep them)."""
     if not (isinstance(root, Op) and root.op == "om_apply" and len(root.args) == 1):
         return None
     leaves = _flatten(root.args[0], "om_compose")
@@ -623,6 +625,7 @@ def om_causal_plan(root: Any) -> dict | None:
     q = scale = None
     ks, vs, sizes, pos, total = [], [], [], 0, None
     causal = None
+    mask_base, off = None, 0
     for leaf in leaves:
         if not (isinstance(leaf, Op) and leaf.op == "om_elem" and len(leaf.args) == 2):
             return None
@@ -649,8 +652,12 @@ def om_causal_plan(root: Any) -> dict | None:
             if r is None:
                 return None
             base, start, length, tot = r
-            if not (isinstance(base, Op) and base.op == "cmask" and int(base.attrs.get("off", 0) or 0) == 0):
+            if not (isinstance(base, Op) and base.op == "cmask"):
                 return None
+            o_i = base.attrs.get("off", 0) or 0
+            if not isinstance(o_i, int) or (mask_base is not None and base != mask_base):
+                return None
+            mask_base, off = base, o_i
             if (start, length) != (pos, n_i) or (total is not None and tot != total):
                 return None
             total = tot
@@ -677,7 +684,7 @@ def om_causal_plan(root: Any) -> dict | None:
     if kb is not None and vb is not None:
         ks, vs = [kb], [vb]
     return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(sizes),
-            "causal": bool(causal)}
+            "causal": bool(causal), "off": off}
 
 
 def _flatten(t: Any, op: str) -> list:
@@ -723,14 +730,22 @@ class B200CausalSoftmaxModule(_EvalBase):
             return self.eval_mod(*xs)
         ev = self._ev(xs)
         return softmax_blocks_state(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
-                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"])
+                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"],
+                                    key_offset=plan["off"])
 
     def _forward_impl(self, *xs: torch.Tensor) -> Any:
         plan = self._plan
         if plan is None:
             return self.eval_mod(*xs)
         ev = self._ev(xs)
-        out = causal_softmax_blocks(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
+        q = ev(plan["q"])
+        if plan["off"] and isinstance(q, torch.Tensor) and q.dtype in (torch.float32, torch.bfloat16):
+            # a shifted causal mask: the streaming step carries the key offset (cb2_om_step);
+            # rows that see no key come out NaN, as the reference's unclamped a / l does
+            st = softmax_blocks_state(q, [ev(t) for t in plan["k_blocks"]], [ev(t) for t in plan["v_blocks"]],
+                                      plan["scale"], True, key_offset=plan["off"])
+            return ops.om_apply_state(st).to(q.dtype)
+        out = causal_softmax_blocks(q, [ev(t) for t in plan["k_blocks"]],
                                     [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"])
         return self.eval_mod(*xs) if out is None else out     # fp64: generic module, same device
 

@@ -578,3 +578,43 @@ def test_autotuned_verifies_times_and_ships_the_b200_candidate_and_feeds_the_pro
     p2 = record_measured(new_prof, "b200_om_decayed_chunked", b2, t_ours.median_s * 1e9)
     assert measured_price_ns(p2, "b200_om_decayed_chunked", b2, None) == pytest.approx(t_ours.median_s * 1e9)
     ops.check_device_status(DEV)
+
+
+@pytest.mark.parametrize("off", [1, -3])
+def test_om_causal_term_with_a_shifted_mask_matches_the_reference_executor(off):
+    """``cmask(x, off)`` hides key j from query t when ``j + off > t`` (om.py:1023-1029); the
+    offset travels to ``cb2_om_step`` as its key offset.  With off > 0 the first rows see no key
+    at all and are NaN in the reference (unclamped a / l) and here."""
+    from catopt_torch.adapters import TorchSink
+
+    ksizes, Tq, d, dv, batch, scale = (96, 160), 256, 64, 64, (2, 2), 0.125
+    q = Var("q", _tt(*batch, Tq, d))
+    ks = [Var(f"k{i}", _tt(*batch, n, d)) for i, n in enumerate(ksizes)]
+    vs = [Var(f"v{i}", _tt(*batch, n, dv)) for i, n in enumerate(ksizes)]
+
+    def scores(k):
+        return Op.make("om_decayed", q, Op.make("fill", q, value=scale), Op.make("transpose", k, dim0=-2, dim1=-1))
+
+    cm = Op.make("cmask", scores(Op.make("concat", *ks, dim=-2)), off=off)
+    leaves = [Op.make("om_elem", Op.make("masked_fill", scores(k), Op.make("split", cm, dim=3, index=i, sizes=ksizes),
+                                         Const(float("-inf"))), v) for i, (k, v) in enumerate(zip(ks, vs))]
+    ins = [q, *ks, *vs]
+    ir = IR(root=Op.make("om_apply", Op.make("om_compose", *leaves)), inputs=ins,
+            input_names={t.name for t in ins}, params={})
+    g = torch.Generator().manual_seed(14 + off)
+    tq = torch.randn(*batch, Tq, d, generator=g).to(DEV)
+    tks = [torch.randn(*batch, n, d, generator=g).to(DEV) for n in ksizes]
+    tvs = [torch.randn(*batch, n, dv, generator=g).to(DEV) for n in ksizes]
+    spec = _route(b200.B200Sink(), ir.root)
+    assert spec.name == "b200_om_causal"
+    mod = spec.lower(ir, None)
+    assert mod._plan["off"] == off
+    ref = _route(TorchSink(), ir.root).lower(ir, None)
+    with torch.no_grad():
+        got, want = mod(tq, *tks, *tvs), ref(tq, *tks, *tvs)
+    assert torch.equal(torch.isnan(got), torch.isnan(want))
+    if off > 0:
+        assert torch.isnan(want[..., :off, :]).all() and not torch.isnan(want[..., off:, :]).any()
+    ok = ~torch.isnan(want)
+    assert _rel(got[ok], want[ok]) <= 1e-5
+    ops.check_device_status(DEV)

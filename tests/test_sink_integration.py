@@ -447,7 +447,9 @@ def test_om_causal_lookalikes_are_declined():
     assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", a, Op.make("om_compose", a, c)))) is None
     assert b200.om_causal_plan(Op.make("om_apply", Op.make("om_compose", a, b_))) is None      # keys 8..12 missing
     shifted, _ = _om_causal_term((4, 4, 4), 12, off=1)
-    assert b200.om_causal_plan(shifted.root) is None
+    ps = b200.om_causal_plan(shifted.root)       # a shifted causal mask is taken, with its offset
+    assert ps is not None and ps["off"] == 1 and ps["causal"]
+    assert b200.om_causal_plan(_om_causal_term((4, 4, 4), 12)[0].root)["off"] == 0
     plain = Op.make("om_apply", Op.make("om_compose", *[Op.make("om_elem", lf.args[0].args[0], lf.args[1])
                                                          for lf in leaves[:2]]))
     pp = b200.om_causal_plan(plain)              # the unmasked carrier is plain softmax attention
