@@ -147,6 +147,13 @@ __device__ __forceinline__ void load_start_state(const float* seg_state, int seg
 // The renormalisation points are multiples of m in the GLOBAL chunk index and a flagged
 // hand-off passes the raw accumulator, so a head cut into segments that wait for one another
 // gives the same bits as one CTA walking the head.
+// Heads served by several CTAs of one launch without scratch: CTA j of a head produces chunks
+// [s[j], s[j+1]) and first walks [0, s[j]) for the state only.  ways == 0: not used.
+struct SelfSplit {
+  int ways;
+  int s[5];
+};
+
 struct FastCtx {
   unsigned char* smem;
   Bars B;
@@ -505,7 +512,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const float* __restrict__ gamma, int H, int T, int dv, float inv_scale, int n_bh, int n_seg,
                   float* __restrict__ seg_state, int* __restrict__ seg_flag, int prestaged, int pieces_per_seg,
-                  int piece_rows, int self_split, int* dev_status) {
+                  int piece_rows, const SelfSplit self, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles; plain offset arithmetic on the
   // __shared__ array keeps every access a shared-space (LDS/STS) access
@@ -532,15 +539,15 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   int chunk0 = seg * nchunk;                       // first chunk of the segment in the sequence
   bool has_in = seg > 0;                           // starts from a predecessor's state
   int pre = 0;                                     // leading chunks walked for their state only
-  if (self_split > 0) {
-    // Two CTAs per head, no scratch, no flags, one launch: the first walks chunks [0, self_split);
-    // the second walks the whole head but only accumulates the state over those chunks (K and V
-    // alone, no scores, no output) and produces chunks [self_split, end).  (n_seg == 1 here.)
+  if (self.ways > 0) {
+    // Several CTAs per head, no scratch, no flags, one launch: CTA j walks chunks [0, s[j]) only to
+    // accumulate their state (K and V alone, no scores, no output) and produces [s[j], s[j+1]).
+    // (n_seg == 1 here.)
     chunk0 = 0;
     has_in = false;
     if (fast) {
-      pre = seg == 0 ? 0 : self_split;
-      nchunk = seg == 0 ? self_split : nchunk;
+      pre = self.s[seg];
+      nchunk = self.s[seg + 1];
     } else if (seg != 0) {
       nchunk = 0;                                  // the every-rate roles walk the head in one CTA
     }
@@ -919,17 +926,27 @@ int decayed_tc_pieces_per_segment(int n_bh, int nchunk, int n_seg, int sms) {
   return sub;
 }
 
-// Between a quarter and half as many heads as SMs, long sequences: two CTAs per head in ONE launch with
-// no scratch — the second walks the first `split` chunks for their state only (K and V: about half
-// the time of a full chunk when the GPU is busy) before producing the rest, so the split sits past the middle; even, so
-// that the two Q slots of the ring keep alternating.  Bit-identical to one CTA per head.  0 = not
-// this case.
-int decayed_tc_self_split(int n_bh, int nchunk, int sms) {
-  if (n_bh * 2 > sms || n_bh * 4 <= sms || nchunk < 16) return 0;
-  // measured at 64 heads x 64 chunks: split 28: 143 us, 36: 135, 40: 131, 44: 125, 48: 131, 56: 150
-  const int split = 2 * ((nchunk * 11 + 16) / 32);     // about 0.69 of the chunks
-  if (split < 2 || split > nchunk - 2) return 0;
-  return split;
+// A quarter to half as many heads as SMs, long sequences: two CTAs per head in ONE launch with no
+// scratch — the second walks the first's chunks for their state only (K and V: about half the time
+// of a full chunk when the GPU is busy) before producing the rest, so the split sits past the
+// middle; split points are even, so that the two Q slots of the ring keep alternating.
+// Bit-identical to one CTA per head.  ways == 0: not this case.
+SelfSplit decayed_tc_self_split(int n_bh, int nchunk, int sms) {
+  SelfSplit sp{0, {0, 0, 0, 0, 0}};
+  if (n_bh * 2 > sms || nchunk < 16) return sp;
+  if (n_bh * 4 > sms) {
+    // measured at 64 heads x 64 chunks: split 28: 143 us, 36: 135, 40: 131, 44: 125, 48: 131, 56: 150
+    const int split = 2 * ((nchunk * 11 + 16) / 32);     // about 0.69 of the chunks
+    if (split < 2 || split > nchunk - 2) return sp;
+    sp.ways = 2;
+    sp.s[1] = split;
+    sp.s[2] = nchunk;
+    return sp;
+  }
+  // (four CTAs per head for an eighth to a quarter as many heads as SMs, split at 0.57 / 0.83 / 0.95 of
+  // the chunks, measured 102 us at 32 heads x 64 chunks against 93 us for parallel segments from a
+  // pre-pass: the state-only walks re-read too much)
+  return sp;
 }
 
 namespace {
@@ -945,7 +962,7 @@ int device_sms() {
 // 128 x 128 fp32, then as many flags.
 size_t decayed_tc_scratch_bytes(int B, int H, int T) {
   const int nchunk = (T + kC - 1) / kC;
-  if (decayed_tc_self_split(B * H, nchunk, device_sms()) > 0) return 0;
+  if (decayed_tc_self_split(B * H, nchunk, device_sms()).ways > 0) return 0;
   const int n_par = decayed_tc_parallel_segments(B * H, nchunk, device_sms());
   if (n_par > 1) {
     const int sub = decayed_tc_pieces_per_segment(B * H, nchunk, n_par, device_sms());
@@ -961,7 +978,7 @@ size_t decayed_tc_scratch_bytes(int B, int H, int T) {
 // accumulating the first's state by itself (no scratch).
 int decayed_tc_plan(int B, int H, int T) {
   const int nchunk = (T + kC - 1) / kC, n_bh = B * H, sms = device_sms();
-  if (decayed_tc_self_split(n_bh, nchunk, sms) > 0) return 3;
+  if (decayed_tc_self_split(n_bh, nchunk, sms).ways > 0) return 3;
   if (decayed_tc_parallel_segments(n_bh, nchunk, sms) > 1) return 2;
   return decayed_tc_segments(n_bh, nchunk, sms) > 1 ? 1 : 0;
 }
@@ -985,10 +1002,14 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
     return CB2_LAUNCH_FAIL;
   const int n_bh = B * H;
   const int nchunk = (T + kC - 1) / kC;
-  // two CTAs per head, the second accumulating the first's state by itself: one launch, no scratch
-  if (const int split = decayed_tc_self_split(n_bh, nchunk, device_sms())) {
-    decayed_tc_kernel<<<n_bh * 2, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale, n_bh, 1,
-                                                             nullptr, nullptr, 1, 0, 0, split, dev_status);
+  // several CTAs per head, each accumulating the state of the chunks before its own by itself: one
+  // launch, no scratch
+  const SelfSplit none{0, {0, 0, 0, 0, 0}};
+  const SelfSplit self = decayed_tc_self_split(n_bh, nchunk, device_sms());
+  if (self.ways > 0) {
+    decayed_tc_kernel<<<n_bh * self.ways, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
+                                                                     n_bh, 1, nullptr, nullptr, 1, 0, 0, self,
+                                                                     dev_status);
     CB2_LAUNCH_CHECK();
     return CB2_OK;
   }
@@ -1003,7 +1024,7 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
     const int piece_rows = sub > 0 ? nchunk / n_par / sub * kC : 0;
     decayed_tc_kernel<<<n_bh * n_par, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
                                                                  n_bh, n_par, states, nullptr, 1, sub, piece_rows,
-                                                                 0, dev_status);
+                                                                 none, dev_status);
     CB2_LAUNCH_CHECK();
     return CB2_OK;
   }
@@ -1018,7 +1039,7 @@ int decayed_tc_run(const void* q, const void* k, const void* v, void* o, const f
   if (n_seg > 1 && cudaMemsetAsync(seg_flag, 0, flag_bytes, st) != cudaSuccess) return CB2_LAUNCH_FAIL;
   decayed_tc_kernel<<<n_bh * n_seg, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dv, 1.0f / scale,
                                                                n_bh, n_seg, seg_state, seg_flag, 0, 0, 0,
-                                                               0, dev_status);
+                                                               none, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }
