@@ -26,6 +26,7 @@ SOURCES = [
     "decayed_chunk_ffma.cu",
     "decayed_chunk_small.cu",
     "decayed_chunk_tc.cu",
+    "decayed_chunk_tf32.cu",
     "decayed_seg_state.cu",
     "decayed_chunk.cu",
     "gated_contract.cu",

@@ -1,0 +1,551 @@
+// Chunked decayed attention for fp32 tensors on the tensor cores (dk, dv <= 64):
+//
+//   o[t] = sum_{s<=t} g^(t-s) (q_t . k_s) v_s / scale          per (batch, head)
+//
+// (ChunkedDecayModule, catopt_carriers/decayed_lower.py:671-700) evaluated with
+// the state-carry recurrence over 128-row chunks, one CTA per (batch, head):
+//   S    = Q K^T                                   (MMA1, 128 x 128 x dk)
+//   O2   = Q St          St = state before the chunk, [dk x dv]   (MMA4)
+//   P    = tril(S . g^(r-c))                       (score warps, in registers)
+//   O1   = P V                                     (MMA2, 128 x dv x 128)
+//   D    = V^T (K . g^(127-c))                     (MMA3, dv x dk x 128) = transposed state increment
+//   o    = (O1 + g^(r+1) O2) / scale ,  St <- g^128 St + D^T
+// A single TF32 pass keeps 10 mantissa bits, far from the 1e-5 this path
+// promises, so every product is taken in three passes on operands split into
+//   hi = operand rounded to TF32,  lo = operand - hi (exact in fp32):
+//   hi.hi + hi.lo + lo.hi, accumulated in fp32 tensor memory.
+// The state itself is carried in fp32 by the score warps (hi + lo tiles hold it
+// exactly), so its error does not grow with the number of chunks.
+//
+// Shared memory (224 KiB, one CTA per SM): K hi | K lo | V hi | V lo | Q | output
+// staging (32 KiB tiles of 128 rows x 64 fp32, two 128-byte-swizzled sub-tiles
+// of 32 columns each, the layout a TMA box {32, 128} writes) and the state hi |
+// lo tiles (64 x 64).  K and V land in their hi tiles and are split in place.
+// A tf32 operand whose rows run along the reduction (V in MMA2, V and K in MMA3:
+// "MN-major") must sit in the 128-byte swizzle with 32-byte atoms, so the V
+// split and the K rescale, which rewrite their tiles anyway, move each row's
+// chunks from the TMA's 16-byte-atom pattern to that one (a permutation inside
+// the row's 128 bytes, so each thread stays within the row it owns).
+// Tensor memory (512 columns): S / P hi 0-127, P lo 128-255, O1 256-319,
+// O2 320-383, Q hi 384-447 (reused for D once MMA4 has run), Q lo 448-511.  Q and
+// P are A operands taken from tensor memory: an MMA with both tf32 operands in
+// shared memory would need more than the 128 B/clk its port delivers.
+//
+// Roles: warp 0 loads tiles with TMA; warp 1 issues the MMAs; warps 2-5
+// (operand warps) split Q into tensor memory, split K and V in place and,
+// once MMA1 has read K, rescale it for the state increment; warps 6-9 (score
+// warps) mask and decay S into P, carry the state and write the output.
+// Every wait is bounded: on expiry the CTA records CB2_WAIT_TIMEOUT and leaves.
+#include <algorithm>
+
+#include "umma.cuh"
+
+namespace cb2 {
+namespace {
+
+constexpr int kC = 128;
+constexpr int kThreads = 320;
+constexpr uint32_t kSub = 128 * 128;           // 128 rows x 32 fp32
+constexpr uint32_t kTile = 2 * kSub;           // 128 rows x 64 fp32
+constexpr uint32_t kSubS = 64 * 128;           // state sub-tile: 64 rows x 32 fp32
+constexpr uint32_t kOffKhi = 0;
+constexpr uint32_t kOffKlo = kTile;
+constexpr uint32_t kOffVhi = 2 * kTile;
+constexpr uint32_t kOffVlo = 3 * kTile;
+constexpr uint32_t kOffQ = 4 * kTile;
+constexpr uint32_t kOffO = 5 * kTile;
+constexpr uint32_t kOffShi = 6 * kTile;
+constexpr uint32_t kOffSlo = kOffShi + 2 * kSubS;
+constexpr uint32_t kOffBars = 7 * kTile;       // 224 KiB of tiles
+constexpr int kNumBars = 14;
+constexpr uint32_t kOffPow = kOffBars + kNumBars * 8;      // g^0 .. g^128
+constexpr uint32_t kOffMisc = kOffPow + 132 * 4;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
+
+constexpr uint32_t kColS = 0, kColPlo = 128, kColO1 = 256, kColO2 = 320, kColQhi = 384, kColQlo = 448;
+constexpr uint32_t kColD = kColQhi;
+
+struct Bars {
+  uint64_t *q_full, *k_full, *v_full;      // TMA -> operand warps
+  uint64_t *q_ready, *k_ready, *v_ready;   // operand warps -> MMA (q_ready also frees the Q tile for the next load)
+  uint64_t* k2_ready;                      // K rescaled for the state increment
+  uint64_t* s_ready;                       // MMA1 done
+  uint64_t* p_ready;                       // P in tensor memory
+  uint64_t* c_done;                        // every MMA of the chunk done (also frees the K and V tiles)
+  uint64_t* st_ready;                      // state tiles written, D read
+  uint64_t* o_free;                        // O1 / O2 read
+  uint64_t* wg_sync;                       // among the score warps
+  uint64_t* spare;
+};
+
+__host__ __device__ constexpr uint32_t instr_desc_tf32(uint32_t M, uint32_t N, bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(a_mn) << 15) | (uint32_t(b_mn) << 16) |
+         ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+__device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate))
+      : "memory");
+}
+// A operand from tensor memory: lane = row, one tf32 per column, 8 columns per 8-deep step.
+__device__ __forceinline__ void mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate))
+      : "memory");
+}
+
+// Nearest TF32 value; v - tf32_rn(v) is exact in fp32.
+__device__ __forceinline__ float tf32_rn(float v) {
+  return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
+}
+__device__ __forceinline__ void split4(const float4 v, float4& h, float4& l) {
+  h.x = tf32_rn(v.x); l.x = v.x - h.x;
+  h.y = tf32_rn(v.y); l.y = v.y - h.y;
+  h.z = tf32_rn(v.z); l.z = v.z - h.z;
+  h.w = tf32_rn(v.w); l.w = v.w - h.w;
+}
+// Byte offset of 16-byte chunk j (0..15) of `row` in a two-sub-tile swizzled tile.
+__device__ __forceinline__ uint32_t chunk_off(uint32_t row, uint32_t j, uint32_t sub_bytes) {
+  return (j >> 3) * sub_bytes + row * 128u + (((j & 7u) ^ (row & 7u)) << 4);
+}
+// Same for the 128-byte swizzle with 32-byte atoms: 32-byte chunk c of a row sits at c ^ (row % 4).
+__device__ __forceinline__ uint32_t chunk_off32(uint32_t row, uint32_t j, uint32_t sub_bytes) {
+  return (j >> 3) * sub_bytes + row * 128u + ((((((j & 7u) >> 1) ^ (row & 3u)) << 1) | (j & 1u)) << 4);
+}
+// Shared-memory matrix descriptor with the layout type given (2: 128-byte swizzle, 1: 128-byte swizzle
+// with 32-byte atoms).
+__device__ __forceinline__ uint64_t smem_desc_lt(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                 uint32_t layout_type) {
+  return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) |
+         (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(layout_type) << 61);
+}
+// K-major operand, 8-deep step ks of a swizzled tile: 8-row groups 1024 B apart, the step advances
+// 32 B inside the 128-byte row and moves to the second sub-tile after four steps.
+__device__ __forceinline__ uint64_t desc_k(uint32_t tile_addr, int ks, uint32_t sub_bytes) {
+  return umma::smem_desc(tile_addr + (ks >> 2) * sub_bytes + (ks & 3) * 32u, 16u, 1024u);
+}
+// MN-major operand (32-byte-atom swizzle), 8-deep step ks: the 8 K-rows of the step are two groups of
+// four rows, 512 B apart (stride offset); the second 32 MN elements sit in the second sub-tile
+// (leading offset).
+__device__ __forceinline__ uint64_t desc_mn(uint32_t tile_addr, int ks) {
+  return smem_desc_lt(tile_addr + ks * 1024u, kSub, 512u, 1u);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                    const float* __restrict__ gamma, int H, int T, int dk, int dv, float inv_scale,
+                    int* dev_status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
+  const Bars B{bars,     bars + 1, bars + 2, bars + 3,  bars + 4,  bars + 5,  bars + 6,
+               bars + 7, bars + 8, bars + 9, bars + 10, bars + 11, bars + 12, bars + 13};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x;
+  const float g = gamma[bh % H];
+  const int nchunk = (T + kC - 1) / kC;
+  const int nks = (dk + 7) / 8;                 // 8-deep steps over the key dimension
+
+  if (tid == 0) {
+    mbar_init(B.q_full, 1);
+    mbar_init(B.k_full, 1);
+    mbar_init(B.v_full, 1);
+    mbar_init(B.q_ready, 128);
+    mbar_init(B.k_ready, 128);
+    mbar_init(B.v_ready, 128);
+    mbar_init(B.k2_ready, 128);
+    mbar_init(B.s_ready, 1);
+    mbar_init(B.p_ready, 128);
+    mbar_init(B.c_done, 1);
+    mbar_init(B.st_ready, 128);
+    mbar_init(B.o_free, 128);
+    mbar_init(B.wg_sync, 128);
+    mbar_init(B.spare, 1);
+    *s_abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    umma::tmem_alloc(s_tmem, 512);
+  }
+  if (tid >= 64 && tid < 64 + 129) s_pow[tid - 64] = powf(g, float(tid - 64));
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = *s_tmem;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      umma::tma_prefetch_desc(&map_q);
+      umma::tma_prefetch_desc(&map_k);
+      umma::tma_prefetch_desc(&map_v);
+      umma::tma_prefetch_desc(&map_o);
+      int issued = 0;
+      for (int i = 0; i < nchunk; ++i) {
+        const int row = i * kC;                  // rows past T arrive as zeros
+        if (i > 0 && !mbar_wait_abortable(B.q_ready, (i - 1) & 1, s_abort)) break;
+        mbar_arrive_expect_tx(B.q_full, kTile);
+        umma::tma_load_3d(smem + kOffQ, &map_q, 0, row, bh, B.q_full);
+        umma::tma_load_3d(smem + kOffQ + kSub, &map_q, 32, row, bh, B.q_full);
+        if (i > 0 && !mbar_wait_abortable(B.c_done, (i - 1) & 1, s_abort)) {
+          mbar_wait_bounded(B.q_full, i & 1);    // the copy just issued must land before the CTA leaves
+          break;
+        }
+        mbar_arrive_expect_tx(B.k_full, kTile);
+        umma::tma_load_3d(smem + kOffKhi, &map_k, 0, row, bh, B.k_full);
+        umma::tma_load_3d(smem + kOffKhi + kSub, &map_k, 32, row, bh, B.k_full);
+        mbar_arrive_expect_tx(B.v_full, kTile);
+        umma::tma_load_3d(smem + kOffVhi, &map_v, 0, row, bh, B.v_full);
+        umma::tma_load_3d(smem + kOffVhi + kSub, &map_v, 32, row, bh, B.v_full);
+        issued = i + 1;
+      }
+      if (*s_abort && issued > 0) {
+        // leaving early: let the copies in flight land first (bounded)
+        mbar_wait_bounded(B.q_full, (issued - 1) & 1);
+        mbar_wait_bounded(B.k_full, (issued - 1) & 1);
+        mbar_wait_bounded(B.v_full, (issued - 1) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc_tf32(128, 128, false, false);
+      constexpr uint32_t idesc_o2 = instr_desc_tf32(128, 64, false, false);
+      constexpr uint32_t idesc_o1 = instr_desc_tf32(128, 64, false, true);
+      constexpr uint32_t idesc_d = instr_desc_tf32(64, 64, true, true);
+      const uint32_t khi = smem_u32(smem + kOffKhi), klo = smem_u32(smem + kOffKlo);
+      const uint32_t vhi = smem_u32(smem + kOffVhi), vlo = smem_u32(smem + kOffVlo);
+      const uint32_t shi = smem_u32(smem + kOffShi), slo = smem_u32(smem + kOffSlo);
+      for (int i = 0; i < nchunk; ++i) {
+        const uint32_t ph = i & 1;
+        // MMA1: S = Q K^T (small terms first)
+        if (!mbar_wait_abortable(B.q_ready, ph, s_abort)) break;
+        if (!mbar_wait_abortable(B.k_ready, ph, s_abort)) break;
+        umma::fence_after_sync();
+        for (int ks = 0; ks < nks; ++ks) {
+          const uint64_t bh_ = desc_k(khi, ks, kSub), bl_ = desc_k(klo, ks, kSub);
+          mma_tf32_ts(tmem + kColS, tmem + kColQlo + ks * 8, bh_, idesc_s, ks > 0);
+          mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, bl_, idesc_s, true);
+          mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, bh_, idesc_s, true);
+        }
+        umma::mma_commit(B.s_ready);
+        // MMA4: O2 = Q St
+        if (!mbar_wait_abortable(B.st_ready, ph, s_abort)) break;
+        if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
+        umma::fence_after_sync();
+        for (int ks = 0; ks < nks; ++ks) {
+          const uint64_t bh_ = desc_k(shi, ks, kSubS), bl_ = desc_k(slo, ks, kSubS);
+          mma_tf32_ts(tmem + kColO2, tmem + kColQlo + ks * 8, bh_, idesc_o2, ks > 0);
+          mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, bl_, idesc_o2, true);
+          mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, bh_, idesc_o2, true);
+        }
+        // MMA2: O1 = P V
+        if (!mbar_wait_abortable(B.p_ready, ph, s_abort)) break;
+        if (!mbar_wait_abortable(B.v_ready, ph, s_abort)) break;
+        umma::fence_after_sync();
+#pragma unroll 4
+        for (int ks = 0; ks < 16; ++ks) {
+          const uint64_t bh_ = desc_mn(vhi, ks), bl_ = desc_mn(vlo, ks);
+          mma_tf32_ts(tmem + kColO1, tmem + kColPlo + ks * 8, bh_, idesc_o1, ks > 0);
+          mma_tf32_ts(tmem + kColO1, tmem + kColS + ks * 8, bl_, idesc_o1, true);
+          mma_tf32_ts(tmem + kColO1, tmem + kColS + ks * 8, bh_, idesc_o1, true);
+        }
+        // MMA3: D = V^T K' (not needed after the last chunk); lands where Q hi was
+        if (i + 1 < nchunk) {
+          if (!mbar_wait_abortable(B.k2_ready, ph, s_abort)) break;
+          umma::fence_after_sync();
+#pragma unroll 4
+          for (int ks = 0; ks < 16; ++ks) {
+            const uint64_t ah = desc_mn(vhi, ks), al = desc_mn(vlo, ks);
+            const uint64_t bh_ = desc_mn(khi, ks), bl_ = desc_mn(klo, ks);
+            mma_tf32_ss(tmem + kColD, al, bh_, idesc_d, ks > 0);
+            mma_tf32_ss(tmem + kColD, ah, bl_, idesc_d, true);
+            mma_tf32_ss(tmem + kColD, ah, bh_, idesc_d, true);
+          }
+        }
+        umma::mma_commit(B.c_done);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- operand warps
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;                // row of every tile this thread owns
+    const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
+    unsigned char* qt = smem + kOffQ;
+    unsigned char* kh = smem + kOffKhi;
+    unsigned char* kl = smem + kOffKlo;
+    unsigned char* vh = smem + kOffVhi;
+    unsigned char* vl = smem + kOffVlo;
+    const float w = s_pow[kC - 1 - r];           // decay of key r to the end of the chunk
+    bool ok = true;
+    for (int i = 0; ok && i < nchunk; ++i) {
+      const uint32_t ph = i & 1;
+      // Q -> tensor memory (hi, lo); the columns are free once the state warps have read D
+      ok = mbar_wait_abortable(B.q_full, ph, s_abort) && mbar_wait_abortable(B.st_ready, ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      umma::fence_after_sync();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t hi[32], lo[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 v = *reinterpret_cast<const float4*>(qt + chunk_off(r, half * 8 + j, kSub));
+          float4 h, l;
+          split4(v, h, l);
+          hi[4 * j] = __float_as_uint(h.x); hi[4 * j + 1] = __float_as_uint(h.y);
+          hi[4 * j + 2] = __float_as_uint(h.z); hi[4 * j + 3] = __float_as_uint(h.w);
+          lo[4 * j] = __float_as_uint(l.x); lo[4 * j + 1] = __float_as_uint(l.y);
+          lo[4 * j + 2] = __float_as_uint(l.z); lo[4 * j + 3] = __float_as_uint(l.w);
+        }
+        umma::tmem_st32(lane_base + kColQhi + half * 32, hi);
+        umma::tmem_st32(lane_base + kColQlo + half * 32, lo);
+      }
+      umma::tmem_wait_st();
+      umma::fence_before_sync();
+      mbar_arrive(B.q_ready);
+      // K: split in place
+      ok = mbar_wait_abortable(B.k_full, ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint32_t off = chunk_off(r, j, kSub);
+        float4 h, l;
+        split4(*reinterpret_cast<const float4*>(kh + off), h, l);
+        *reinterpret_cast<float4*>(kh + off) = h;
+        *reinterpret_cast<float4*>(kl + off) = l;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(B.k_ready);
+      // V: split in place, moved to the 32-byte-atom pattern
+      ok = mbar_wait_abortable(B.v_full, ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float4 x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = *reinterpret_cast<const float4*>(vh + chunk_off(r, half * 8 + j, kSub));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t off = chunk_off32(r, half * 8 + j, kSub);
+          float4 h, l;
+          split4(x[j], h, l);
+          *reinterpret_cast<float4*>(vh + off) = h;
+          *reinterpret_cast<float4*>(vl + off) = l;
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(B.v_ready);
+      // K' = K g^(127-r), moved to the 32-byte-atom pattern, once MMA1 has read K
+      if (i + 1 < nchunk) {
+        ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float4 x[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t off = chunk_off(r, half * 8 + j, kSub);
+            const float4 a = *reinterpret_cast<const float4*>(kh + off);
+            const float4 b = *reinterpret_cast<const float4*>(kl + off);
+            x[j] = make_float4((a.x + b.x) * w, (a.y + b.y) * w, (a.z + b.z) * w, (a.w + b.w) * w);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t off = chunk_off32(r, half * 8 + j, kSub);
+            float4 h, l;
+            split4(x[j], h, l);
+            *reinterpret_cast<float4*>(kh + off) = h;
+            *reinterpret_cast<float4*>(kl + off) = l;
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(B.k2_ready);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- score / state / output warps
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const int wt = tid - 192;                    // 0..127 among these warps
+    const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
+    unsigned char* sh = smem + kOffShi;
+    unsigned char* sl = smem + kOffSlo;
+    unsigned char* ot = smem + kOffO;
+    const float gC = s_pow[kC];
+    const float fcross = s_pow[r + 1];
+    uint32_t wg_phase = 0;
+    bool ok = true;
+    // the state starts at zero
+    for (int j = 0; j < 16; ++j)
+      *reinterpret_cast<float4*>(sh + (wt * 16 + j) * 16) = make_float4(0.f, 0.f, 0.f, 0.f);   // hi and lo, 32 KiB
+    fence_proxy_async_smem();
+    mbar_arrive(B.st_ready);
+    for (int i = 0; ok && i < nchunk; ++i) {
+      const uint32_t ph = i & 1;
+      ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      umma::fence_after_sync();
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t v[32], lo[32];
+        umma::tmem_ld32(lane_base + kColS + cb * 32, v);
+        umma::tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int c = cb * 32 + j;
+          const int e = r - c;
+          const float p = e >= 0 ? __uint_as_float(v[j]) * s_pow[e] : 0.f;
+          const float h = tf32_rn(p);
+          v[j] = __float_as_uint(h);
+          lo[j] = __float_as_uint(p - h);
+        }
+        umma::tmem_st32(lane_base + kColS + cb * 32, v);
+        umma::tmem_st32(lane_base + kColPlo + cb * 32, lo);
+      }
+      umma::tmem_wait_st();
+      umma::fence_before_sync();
+      mbar_arrive(B.p_ready);
+
+      ok = mbar_wait_abortable(B.c_done, ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      umma::fence_after_sync();
+      if (i + 1 < nchunk) {
+        // state: St <- g^128 St + D^T; a 64-row accumulator keeps row n in lane (n % 16) of
+        // lane quarter n / 16
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t d[32];
+          umma::tmem_ld32(lane_base + kColD + half * 32, d);
+          umma::tmem_wait_ld();
+          if (lane < 16) {
+            const uint32_t n = q4 * 16 + lane;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t off = chunk_off(n, half * 8 + j, kSubS);
+              const float4 a = *reinterpret_cast<const float4*>(sh + off);
+              const float4 b = *reinterpret_cast<const float4*>(sl + off);
+              float4 h, l;
+              split4(make_float4(fmaf(gC, a.x + b.x, __uint_as_float(d[4 * j])),
+                                 fmaf(gC, a.y + b.y, __uint_as_float(d[4 * j + 1])),
+                                 fmaf(gC, a.z + b.z, __uint_as_float(d[4 * j + 2])),
+                                 fmaf(gC, a.w + b.w, __uint_as_float(d[4 * j + 3]))),
+                     h, l);
+              *reinterpret_cast<float4*>(sh + off) = h;
+              *reinterpret_cast<float4*>(sl + off) = l;
+            }
+          }
+        }
+        umma::fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(B.st_ready);
+      }
+      // output: o = (O1 + g^(r+1) O2) / scale, staged as a swizzled tile and stored by TMA
+      if (wt == 0) bulk_wait_read<0>();          // the previous store has read the staging tile
+      mbar_arrive(B.wg_sync);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      wg_phase ^= 1;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[32], b[32];
+        umma::tmem_ld32(lane_base + kColO1 + half * 32, a);
+        umma::tmem_ld32(lane_base + kColO2 + half * 32, b);
+        umma::tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = (__uint_as_float(a[4 * j]) + fcross * __uint_as_float(b[4 * j])) * inv_scale;
+          o.y = (__uint_as_float(a[4 * j + 1]) + fcross * __uint_as_float(b[4 * j + 1])) * inv_scale;
+          o.z = (__uint_as_float(a[4 * j + 2]) + fcross * __uint_as_float(b[4 * j + 2])) * inv_scale;
+          o.w = (__uint_as_float(a[4 * j + 3]) + fcross * __uint_as_float(b[4 * j + 3])) * inv_scale;
+          *reinterpret_cast<float4*>(ot + chunk_off(r, half * 8 + j, kSub)) = o;
+        }
+      }
+      umma::fence_before_sync();
+      mbar_arrive(B.o_free);
+      fence_proxy_async_smem();
+      mbar_arrive(B.wg_sync);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      wg_phase ^= 1;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (wt == 0) {
+        umma::tma_store_3d(&map_o, 0, i * kC, bh, ot);
+        if (dv > 32) umma::tma_store_3d(&map_o, 32, i * kC, bh, ot + kSub);
+        bulk_commit();
+      }
+    }
+    if (wt == 0) bulk_wait_all<0>();
+  }
+  __syncwarp();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  if (tid == 0 && *s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+  if (warp == 1) {
+    __syncwarp();
+    umma::tmem_dealloc(tmem, 512);
+  }
+}
+
+int device_sms() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+}  // namespace
+
+// fp32 tensors with both head dimensions at most 64 (multiples of 4, so that rows are 16-byte
+// aligned for TMA) and enough (batch, head) units for one CTA each to be worth it: below about a
+// sixth of the SMs the FMA path, which spreads a head's chunks over CTAs, is faster.
+bool decayed_tf32_supported(int B, int H, int T, int dk, int dv, int dtype) {
+  if (dtype != CB2_F32) return false;
+  if (dk < 4 || dv < 4 || dk > 64 || dv > 64 || dk % 4 || dv % 4) return false;
+  if (T < 1) return false;
+  return int64_t(B) * H >= 24 && int64_t(B) * H < (int64_t(1) << 31);
+}
+
+int decayed_tf32_run(const void* q, const void* k, const void* v, void* o, const float* gamma, int B, int H,
+                     int T, int dk, int dv, float scale, int* dev_status, cudaStream_t st) {
+  const uint64_t heads = uint64_t(B) * H;
+  CUtensorMap mq, mk, mv, mo;
+  int rc = umma::make_map_3d(&mq, q, false, dk, T, heads, 32, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mk, k, false, dk, T, heads, 32, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mv, v, false, dv, T, heads, 32, 128, true);
+  if (rc == CB2_OK) rc = umma::make_map_3d(&mo, o, false, dv, T, heads, 32, 128, true);
+  if (rc != CB2_OK) return rc;
+  if (cudaFuncSetAttribute(decayed_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           int(kSmemBytes)) != cudaSuccess)
+    return CB2_LAUNCH_FAIL;
+  (void)device_sms;
+  decayed_tf32_kernel<<<unsigned(heads), kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dk, dv,
+                                                                     1.0f / scale, dev_status);
+  CB2_LAUNCH_CHECK();
+  return CB2_OK;
+}
+
+}  // namespace cb2
