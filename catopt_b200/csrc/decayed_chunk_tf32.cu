@@ -12,29 +12,36 @@
 //   o    = (O1 + g^(r+1) O2) / scale ,  St <- g^128 St + D^T
 // A single TF32 pass keeps 10 mantissa bits, far from the 1e-5 this path
 // promises, so every product is taken in three passes on operands split into
-//   hi = operand rounded to TF32,  lo = operand - hi (exact in fp32):
+//   hi = the fp32 value itself (the tensor core reads its upper 19 bits, i.e. truncates it to TF32),
+//   lo = value - truncated value (exact in fp32):
 //   hi.hi + hi.lo + lo.hi, accumulated in fp32 tensor memory.
-// The state itself is carried in fp32 by the score warps (hi + lo tiles hold it
-// exactly), so its error does not grow with the number of chunks.
+// The state itself is carried in fp32 by the score warps (its hi tile is the
+// fp32 state), so its error does not grow with the number of chunks.
 //
-// Shared memory (224 KiB, one CTA per SM): K hi | K lo | V hi | V lo | Q | output
-// staging (32 KiB tiles of 128 rows x 64 fp32, two 128-byte-swizzled sub-tiles
-// of 32 columns each, the layout a TMA box {32, 128} writes) and the state hi |
-// lo tiles (64 x 64).  K and V land in their hi tiles and are split in place.
+// Shared memory (224 KiB, one CTA per SM), 32 KiB tiles of 128 rows x 64 fp32 as
+// two 128-byte-swizzled sub-tiles of 32 columns (what a TMA box {32, 128}
+// writes): K of even chunks | K of odd chunks | K lo | V | V lo | Q (later the
+// staged output), and the state hi | lo tiles (64 x 64).  K is loaded a whole
+// chunk ahead into the tile the chunk before last has left, so that only the lo
+// tile has to be built between two chunks.
 // A tf32 operand whose rows run along the reduction (V in MMA2, V and K in MMA3:
 // "MN-major") must sit in the 128-byte swizzle with 32-byte atoms, so the V
-// split and the K rescale, which rewrite their tiles anyway, move each row's
-// chunks from the TMA's 16-byte-atom pattern to that one (a permutation inside
-// the row's 128 bytes, so each thread stays within the row it owns).
+// split and the K rescale move each row's chunks from the TMA's 16-byte-atom
+// pattern to that one (a permutation inside the row's 128 bytes, so each thread
+// stays within the row it owns).
 // Tensor memory (512 columns): S / P hi 0-127, P lo 128-255, O1 256-319,
 // O2 320-383, Q hi 384-447 (reused for D once MMA4 has run), Q lo 448-511.  Q and
 // P are A operands taken from tensor memory: an MMA with both tf32 operands in
 // shared memory would need more than the 128 B/clk its port delivers.
+// Measured cost of one tcgen05.mma kind::tf32 with an 8-deep step: 66 cycles at
+// N = 128, 46 at N = 64 (M = 64 and M = 128 alike): 7.1 k cycles of tensor pipe
+// per chunk at dk = dv = 64.
 //
-// Roles: warp 0 loads tiles with TMA; warp 1 issues the MMAs; warps 2-5
-// (operand warps) split Q into tensor memory, split K and V in place and,
-// once MMA1 has read K, rescale it for the state increment; warps 6-9 (score
-// warps) mask and decay S into P, carry the state and write the output.
+// Roles: warp 0 loads tiles with TMA; warp 1 issues the MMAs (MMA1, MMA4, MMA3,
+// MMA2: the state increment keeps the pipe busy while P is being built); warps
+// 2-5 (operand warps) put Q into tensor memory, build K lo and V lo and, once
+// MMA1 has read K, rescale K for the state increment; warps 6-9 (score warps)
+// mask and decay S into P, carry the state and write the output.
 // Every wait is bounded: on expiry the CTA records CB2_WAIT_TIMEOUT and leaves.
 #include <algorithm>
 
@@ -48,16 +55,16 @@ constexpr int kThreads = 320;
 constexpr uint32_t kSub = 128 * 128;           // 128 rows x 32 fp32
 constexpr uint32_t kTile = 2 * kSub;           // 128 rows x 64 fp32
 constexpr uint32_t kSubS = 64 * 128;           // state sub-tile: 64 rows x 32 fp32
-constexpr uint32_t kOffKhi = 0;
-constexpr uint32_t kOffKlo = kTile;
-constexpr uint32_t kOffVhi = 2 * kTile;
-constexpr uint32_t kOffVlo = 3 * kTile;
-constexpr uint32_t kOffQ = 4 * kTile;
-constexpr uint32_t kOffO = 5 * kTile;
+constexpr uint32_t kOffK0 = 0;                 // K of even chunks | K lo | K of odd chunks: a chunk's K and
+constexpr uint32_t kOffKlo = kTile;            // the lo tile are neighbours either way
+constexpr uint32_t kOffK1 = 2 * kTile;
+constexpr uint32_t kOffVhi = 3 * kTile;
+constexpr uint32_t kOffVlo = 4 * kTile;
+constexpr uint32_t kOffQ = 5 * kTile;          // Q, then the staged output
 constexpr uint32_t kOffShi = 6 * kTile;
 constexpr uint32_t kOffSlo = kOffShi + 2 * kSubS;
 constexpr uint32_t kOffBars = 7 * kTile;       // 224 KiB of tiles
-constexpr int kNumBars = 14;
+constexpr int kNumBars = 16;
 constexpr uint32_t kOffPow = kOffBars + kNumBars * 8;      // g^0 .. g^128
 constexpr uint32_t kOffMisc = kOffPow + 132 * 4;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
@@ -67,16 +74,17 @@ constexpr uint32_t kColS = 0, kColPlo = 128, kColO1 = 256, kColO2 = 320, kColQhi
 constexpr uint32_t kColD = kColQhi;
 
 struct Bars {
-  uint64_t *q_full, *k_full, *v_full;      // TMA -> operand warps
-  uint64_t *q_ready, *k_ready, *v_ready;   // operand warps -> MMA (q_ready also frees the Q tile for the next load)
+  uint64_t *q_full, *k_full, *v_full;      // TMA -> operand warps (k_full[2]: one per K tile)
+  uint64_t *q_ready, *k_ready, *v_ready;   // operand warps -> MMA
   uint64_t* k2_ready;                      // K rescaled for the state increment
   uint64_t* s_ready;                       // MMA1 done
   uint64_t* p_ready;                       // P in tensor memory
-  uint64_t* c_done;                        // every MMA of the chunk done (also frees the K and V tiles)
-  uint64_t* st_ready;                      // state tiles written, D read
+  uint64_t* c_done;                        // every MMA of the chunk done (frees K lo, V and this chunk's K tile)
+  uint64_t* st_ready;                      // state tiles written
   uint64_t* o_free;                        // O1 / O2 read
   uint64_t* wg_sync;                       // among the score warps
-  uint64_t* spare;
+  uint64_t* d_free;                        // D read into registers (the Q columns may be rewritten)
+  uint64_t* qtile_free;                    // the staged output has left the Q tile
 };
 
 __host__ __device__ constexpr uint32_t instr_desc_tf32(uint32_t M, uint32_t N, bool a_mn, bool b_mn) {
@@ -103,15 +111,12 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       : "memory");
 }
 
-// Nearest TF32 value; v - tf32_rn(v) is exact in fp32.
-__device__ __forceinline__ float tf32_rn(float v) {
-  return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
+// What a tf32 operand loses: v minus v truncated to TF32 (exact in fp32).
+__device__ __forceinline__ float tf32_rest(float v) {
+  return v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
 }
-__device__ __forceinline__ void split4(const float4 v, float4& h, float4& l) {
-  h.x = tf32_rn(v.x); l.x = v.x - h.x;
-  h.y = tf32_rn(v.y); l.y = v.y - h.y;
-  h.z = tf32_rn(v.z); l.z = v.z - h.z;
-  h.w = tf32_rn(v.w); l.w = v.w - h.w;
+__device__ __forceinline__ float4 rest4(const float4 v) {
+  return make_float4(tf32_rest(v.x), tf32_rest(v.y), tf32_rest(v.z), tf32_rest(v.w));
 }
 // Byte offset of 16-byte chunk j (0..15) of `row` in a two-sub-tile swizzled tile.
 __device__ __forceinline__ uint32_t chunk_off(uint32_t row, uint32_t j, uint32_t sub_bytes) {
@@ -151,8 +156,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
-  const Bars B{bars,     bars + 1, bars + 2, bars + 3,  bars + 4,  bars + 5,  bars + 6,
-               bars + 7, bars + 8, bars + 9, bars + 10, bars + 11, bars + 12, bars + 13};
+  const Bars B{bars,     bars + 1, bars + 3,  bars + 4,  bars + 5,  bars + 6,  bars + 7,
+               bars + 8, bars + 9, bars + 10, bars + 11, bars + 12, bars + 13, bars + 14, bars + 15};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x;
@@ -162,10 +167,11 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (tid == 0) {
     mbar_init(B.q_full, 1);
-    mbar_init(B.k_full, 1);
+    mbar_init(&B.k_full[0], 1);
+    mbar_init(&B.k_full[1], 1);
     mbar_init(B.v_full, 1);
     mbar_init(B.q_ready, 128);
-    mbar_init(B.k_ready, 128);
+    mbar_init(B.k_ready, 256);
     mbar_init(B.v_ready, 128);
     mbar_init(B.k2_ready, 128);
     mbar_init(B.s_ready, 1);
@@ -174,7 +180,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     mbar_init(B.st_ready, 128);
     mbar_init(B.o_free, 128);
     mbar_init(B.wg_sync, 128);
-    mbar_init(B.spare, 1);
+    mbar_init(B.d_free, 128);
+    mbar_init(B.qtile_free, 1);
     *s_abort = 0;
     mbar_fence_init();
   }
@@ -195,30 +202,50 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tma_prefetch_desc(&map_k);
       umma::tma_prefetch_desc(&map_v);
       umma::tma_prefetch_desc(&map_o);
-      int issued = 0;
-      for (int i = 0; i < nchunk; ++i) {
-        const int row = i * kC;                  // rows past T arrive as zeros
-        if (i > 0 && !mbar_wait_abortable(B.q_ready, (i - 1) & 1, s_abort)) break;
+      int nq = 0, nv = 0, nk0 = 0, nk1 = 0;       // copies issued per barrier
+      auto load_q = [&](int i) {
         mbar_arrive_expect_tx(B.q_full, kTile);
-        umma::tma_load_3d(smem + kOffQ, &map_q, 0, row, bh, B.q_full);
-        umma::tma_load_3d(smem + kOffQ + kSub, &map_q, 32, row, bh, B.q_full);
-        if (i > 0 && !mbar_wait_abortable(B.c_done, (i - 1) & 1, s_abort)) {
-          mbar_wait_bounded(B.q_full, i & 1);    // the copy just issued must land before the CTA leaves
-          break;
-        }
-        mbar_arrive_expect_tx(B.k_full, kTile);
-        umma::tma_load_3d(smem + kOffKhi, &map_k, 0, row, bh, B.k_full);
-        umma::tma_load_3d(smem + kOffKhi + kSub, &map_k, 32, row, bh, B.k_full);
+        umma::tma_load_3d(smem + kOffQ, &map_q, 0, i * kC, bh, B.q_full);
+        umma::tma_load_3d(smem + kOffQ + kSub, &map_q, 32, i * kC, bh, B.q_full);
+        ++nq;
+      };
+      auto load_k = [&](int i) {
+        const int b = i & 1;
+        unsigned char* dst = smem + (b ? kOffK1 : kOffK0);
+        mbar_arrive_expect_tx(&B.k_full[b], kTile);
+        umma::tma_load_3d(dst, &map_k, 0, i * kC, bh, &B.k_full[b]);
+        umma::tma_load_3d(dst + kSub, &map_k, 32, i * kC, bh, &B.k_full[b]);
+        if (b) ++nk1; else ++nk0;
+      };
+      auto load_v = [&](int i) {
         mbar_arrive_expect_tx(B.v_full, kTile);
-        umma::tma_load_3d(smem + kOffVhi, &map_v, 0, row, bh, B.v_full);
-        umma::tma_load_3d(smem + kOffVhi + kSub, &map_v, 32, row, bh, B.v_full);
-        issued = i + 1;
+        umma::tma_load_3d(smem + kOffVhi, &map_v, 0, i * kC, bh, B.v_full);
+        umma::tma_load_3d(smem + kOffVhi + kSub, &map_v, 32, i * kC, bh, B.v_full);
+        ++nv;
+      };
+      // rows past T arrive as zeros
+      load_q(0);
+      load_k(0);
+      load_v(0);
+      if (nchunk > 1) load_k(1);
+      for (int i = 0; i + 1 < nchunk; ++i) {
+        // the Q tile is free once Q_i sits in tensor memory (first chunk) or the output of
+        // chunk i-1, staged there, has left
+        if (!(i == 0 ? mbar_wait_abortable(B.q_ready, 0, s_abort)
+                     : mbar_wait_abortable(B.qtile_free, (i - 1) & 1, s_abort)))
+          break;
+        load_q(i + 1);
+        // chunk i done: V and this chunk's K tile are free
+        if (!mbar_wait_abortable(B.c_done, i & 1, s_abort)) break;
+        load_v(i + 1);
+        if (i + 2 < nchunk) load_k(i + 2);
       }
-      if (*s_abort && issued > 0) {
+      if (*s_abort) {
         // leaving early: let the copies in flight land first (bounded)
-        mbar_wait_bounded(B.q_full, (issued - 1) & 1);
-        mbar_wait_bounded(B.k_full, (issued - 1) & 1);
-        mbar_wait_bounded(B.v_full, (issued - 1) & 1);
+        if (nq) mbar_wait_bounded(B.q_full, (nq - 1) & 1);
+        if (nv) mbar_wait_bounded(B.v_full, (nv - 1) & 1);
+        if (nk0) mbar_wait_bounded(&B.k_full[0], (nk0 - 1) & 1);
+        if (nk1) mbar_wait_bounded(&B.k_full[1], (nk1 - 1) & 1);
       }
     }
   } else if (warp == 1) {
@@ -228,55 +255,70 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_o2 = instr_desc_tf32(128, 64, false, false);
       constexpr uint32_t idesc_o1 = instr_desc_tf32(128, 64, false, true);
       constexpr uint32_t idesc_d = instr_desc_tf32(64, 64, true, true);
-      const uint32_t khi = smem_u32(smem + kOffKhi), klo = smem_u32(smem + kOffKlo);
-      const uint32_t vhi = smem_u32(smem + kOffVhi), vlo = smem_u32(smem + kOffVlo);
-      const uint32_t shi = smem_u32(smem + kOffShi), slo = smem_u32(smem + kOffSlo);
+      constexpr uint32_t idesc_d2 = instr_desc_tf32(64, 128, true, true);
+      // descriptors of step 0; a step adds a constant to the start-address field (a lone thread issues
+      // every MMA, so the issue loops are unrolled down to one add per MMA)
+      const uint32_t k0 = smem_u32(smem + kOffK0);
+      const uint64_t klo_k = desc_k(smem_u32(smem + kOffKlo), 0, kSub), klo_m = desc_mn(smem_u32(smem + kOffKlo), 0);
+      const uint64_t shi_k = desc_k(smem_u32(smem + kOffShi), 0, kSubS), slo_k = desc_k(smem_u32(smem + kOffSlo), 0, kSubS);
+      const uint64_t vhi_m = desc_mn(smem_u32(smem + kOffVhi), 0), vlo_m = desc_mn(smem_u32(smem + kOffVlo), 0);
       for (int i = 0; i < nchunk; ++i) {
         const uint32_t ph = i & 1;
+        const uint64_t khi_k = desc_k(k0 + ph * 2 * kTile, 0, kSub), khi_m = desc_mn(k0 + ph * 2 * kTile, 0);
+        // K' hi and lo side by side as one 128-wide operand: hi | lo for even chunks, lo | hi for odd ones
+        const uint64_t kboth_m = ph ? klo_m : khi_m;
         // MMA1: S = Q K^T (small terms first)
         if (!mbar_wait_abortable(B.q_ready, ph, s_abort)) break;
         if (!mbar_wait_abortable(B.k_ready, ph, s_abort)) break;
         umma::fence_after_sync();
-        for (int ks = 0; ks < nks; ++ks) {
-          const uint64_t bh_ = desc_k(khi, ks, kSub), bl_ = desc_k(klo, ks, kSub);
-          mma_tf32_ts(tmem + kColS, tmem + kColQlo + ks * 8, bh_, idesc_s, ks > 0);
-          mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, bl_, idesc_s, true);
-          mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, bh_, idesc_s, true);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          if (ks < nks) {
+            const uint32_t off = ((ks >> 2) * kSub + (ks & 3) * 32u) >> 4;
+            mma_tf32_ts(tmem + kColS, tmem + kColQlo + ks * 8, khi_k + off, idesc_s, ks > 0);
+            mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, klo_k + off, idesc_s, true);
+            mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, khi_k + off, idesc_s, true);
+          }
         }
         umma::mma_commit(B.s_ready);
         // MMA4: O2 = Q St
         if (!mbar_wait_abortable(B.st_ready, ph, s_abort)) break;
         if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
         umma::fence_after_sync();
-        for (int ks = 0; ks < nks; ++ks) {
-          const uint64_t bh_ = desc_k(shi, ks, kSubS), bl_ = desc_k(slo, ks, kSubS);
-          mma_tf32_ts(tmem + kColO2, tmem + kColQlo + ks * 8, bh_, idesc_o2, ks > 0);
-          mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, bl_, idesc_o2, true);
-          mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, bh_, idesc_o2, true);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          if (ks < nks) {
+            const uint32_t off = ((ks >> 2) * kSubS + (ks & 3) * 32u) >> 4;
+            mma_tf32_ts(tmem + kColO2, tmem + kColQlo + ks * 8, shi_k + off, idesc_o2, ks > 0);
+            mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, slo_k + off, idesc_o2, true);
+            mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, shi_k + off, idesc_o2, true);
+          }
+        }
+        // MMA3: D = V^T K' (not needed after the last chunk); lands where Q was.  Issued before
+        // MMA2 so that the tensor pipe has work while the score warps build P.
+        if (i + 1 < nchunk) {
+          if (!mbar_wait_abortable(B.v_ready, ph, s_abort)) break;
+          if (!mbar_wait_abortable(B.k2_ready, ph, s_abort)) break;
+          umma::fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 16; ++ks) {
+            const uint32_t off = (ks * 1024u) >> 4;
+            // V hi against [K' hi | K' lo] in one 128-wide MMA (two of the three products; the state warps
+            // add the halves), then V lo against K' hi
+            mma_tf32_ss(tmem + kColD, vhi_m + off, kboth_m + off, idesc_d2, ks > 0);
+            mma_tf32_ss(tmem + kColD, vlo_m + off, khi_m + off, idesc_d, true);
+          }
         }
         // MMA2: O1 = P V
         if (!mbar_wait_abortable(B.p_ready, ph, s_abort)) break;
         if (!mbar_wait_abortable(B.v_ready, ph, s_abort)) break;
         umma::fence_after_sync();
-#pragma unroll 4
+#pragma unroll
         for (int ks = 0; ks < 16; ++ks) {
-          const uint64_t bh_ = desc_mn(vhi, ks), bl_ = desc_mn(vlo, ks);
-          mma_tf32_ts(tmem + kColO1, tmem + kColPlo + ks * 8, bh_, idesc_o1, ks > 0);
-          mma_tf32_ts(tmem + kColO1, tmem + kColS + ks * 8, bl_, idesc_o1, true);
-          mma_tf32_ts(tmem + kColO1, tmem + kColS + ks * 8, bh_, idesc_o1, true);
-        }
-        // MMA3: D = V^T K' (not needed after the last chunk); lands where Q hi was
-        if (i + 1 < nchunk) {
-          if (!mbar_wait_abortable(B.k2_ready, ph, s_abort)) break;
-          umma::fence_after_sync();
-#pragma unroll 4
-          for (int ks = 0; ks < 16; ++ks) {
-            const uint64_t ah = desc_mn(vhi, ks), al = desc_mn(vlo, ks);
-            const uint64_t bh_ = desc_mn(khi, ks), bl_ = desc_mn(klo, ks);
-            mma_tf32_ss(tmem + kColD, al, bh_, idesc_d, ks > 0);
-            mma_tf32_ss(tmem + kColD, ah, bl_, idesc_d, true);
-            mma_tf32_ss(tmem + kColD, ah, bh_, idesc_d, true);
-          }
+          const uint32_t off = (ks * 1024u) >> 4;
+          mma_tf32_ts(tmem + kColO1, tmem + kColPlo + ks * 8, vhi_m + off, idesc_o1, ks > 0);
+          mma_tf32_ts(tmem + kColO1, tmem + kColS + ks * 8, vlo_m + off, idesc_o1, true);
+          mma_tf32_ts(tmem + kColO1, tmem + kColS + ks * 8, vhi_m + off, idesc_o1, true);
         }
         umma::mma_commit(B.c_done);
       }
@@ -287,7 +329,6 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int r = q4 * 32 + lane;                // row of every tile this thread owns
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
     unsigned char* qt = smem + kOffQ;
-    unsigned char* kh = smem + kOffKhi;
     unsigned char* kl = smem + kOffKlo;
     unsigned char* vh = smem + kOffVhi;
     unsigned char* vl = smem + kOffVlo;
@@ -295,8 +336,10 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     bool ok = true;
     for (int i = 0; ok && i < nchunk; ++i) {
       const uint32_t ph = i & 1;
-      // Q -> tensor memory (hi, lo); the columns are free once the state warps have read D
-      ok = mbar_wait_abortable(B.q_full, ph, s_abort) && mbar_wait_abortable(B.st_ready, ph, s_abort);
+      unsigned char* kh = smem + (ph ? kOffK1 : kOffK0);
+      // Q -> tensor memory (value, remainder); the columns are free once the score warps have read D
+      ok = mbar_wait_abortable(B.q_full, ph, s_abort) &&
+           (i == 0 || mbar_wait_abortable(B.d_free, (i - 1) & 1, s_abort));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       umma::fence_after_sync();
@@ -306,10 +349,9 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float4 v = *reinterpret_cast<const float4*>(qt + chunk_off(r, half * 8 + j, kSub));
-          float4 h, l;
-          split4(v, h, l);
-          hi[4 * j] = __float_as_uint(h.x); hi[4 * j + 1] = __float_as_uint(h.y);
-          hi[4 * j + 2] = __float_as_uint(h.z); hi[4 * j + 3] = __float_as_uint(h.w);
+          const float4 l = rest4(v);
+          hi[4 * j] = __float_as_uint(v.x); hi[4 * j + 1] = __float_as_uint(v.y);
+          hi[4 * j + 2] = __float_as_uint(v.z); hi[4 * j + 3] = __float_as_uint(v.w);
           lo[4 * j] = __float_as_uint(l.x); lo[4 * j + 1] = __float_as_uint(l.y);
           lo[4 * j + 2] = __float_as_uint(l.z); lo[4 * j + 3] = __float_as_uint(l.w);
         }
@@ -319,21 +361,21 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tmem_wait_st();
       umma::fence_before_sync();
       mbar_arrive(B.q_ready);
-      // K: split in place
-      ok = mbar_wait_abortable(B.k_full, ph, s_abort);
+      // K lo (the K tile itself is the hi operand); the lo tile is free once the chunk before is done
+      ok = mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort) &&
+           (i == 0 || mbar_wait_abortable(B.c_done, (i - 1) & 1, s_abort));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      // (columns 0-31 here, 32-63 by the score warps: this is the one step between two chunks during
+      // which the tensor pipe has nothing to do)
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < 8; ++j) {
         const uint32_t off = chunk_off(r, j, kSub);
-        float4 h, l;
-        split4(*reinterpret_cast<const float4*>(kh + off), h, l);
-        *reinterpret_cast<float4*>(kh + off) = h;
-        *reinterpret_cast<float4*>(kl + off) = l;
+        *reinterpret_cast<float4*>(kl + off) = rest4(*reinterpret_cast<const float4*>(kh + off));
       }
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
-      // V: split in place, moved to the 32-byte-atom pattern
+      // V: moved to the 32-byte-atom pattern in place, and its lo tile
       ok = mbar_wait_abortable(B.v_full, ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -345,10 +387,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const uint32_t off = chunk_off32(r, half * 8 + j, kSub);
-          float4 h, l;
-          split4(x[j], h, l);
-          *reinterpret_cast<float4*>(vh + off) = h;
-          *reinterpret_cast<float4*>(vl + off) = l;
+          *reinterpret_cast<float4*>(vh + off) = x[j];
+          *reinterpret_cast<float4*>(vl + off) = rest4(x[j]);
         }
       }
       fence_proxy_async_smem();
@@ -363,18 +403,14 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           float4 x[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const uint32_t off = chunk_off(r, half * 8 + j, kSub);
-            const float4 a = *reinterpret_cast<const float4*>(kh + off);
-            const float4 b = *reinterpret_cast<const float4*>(kl + off);
-            x[j] = make_float4((a.x + b.x) * w, (a.y + b.y) * w, (a.z + b.z) * w, (a.w + b.w) * w);
+            const float4 a = *reinterpret_cast<const float4*>(kh + chunk_off(r, half * 8 + j, kSub));
+            x[j] = make_float4(a.x * w, a.y * w, a.z * w, a.w * w);
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint32_t off = chunk_off32(r, half * 8 + j, kSub);
-            float4 h, l;
-            split4(x[j], h, l);
-            *reinterpret_cast<float4*>(kh + off) = h;
-            *reinterpret_cast<float4*>(kl + off) = l;
+            *reinterpret_cast<float4*>(kh + off) = x[j];
+            *reinterpret_cast<float4*>(kl + off) = rest4(x[j]);
           }
         }
         fence_proxy_async_smem();
@@ -389,9 +425,12 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
     unsigned char* sh = smem + kOffShi;
     unsigned char* sl = smem + kOffSlo;
-    unsigned char* ot = smem + kOffO;
+    unsigned char* ot = smem + kOffQ;            // the output is staged where Q was
     const float gC = s_pow[kC];
     const float fcross = s_pow[r + 1];
+    float gp[32];                                // g^(31-j)
+#pragma unroll
+    for (int j = 0; j < 32; ++j) gp[j] = s_pow[31 - j];
     uint32_t wg_phase = 0;
     bool ok = true;
     // the state starts at zero
@@ -399,6 +438,23 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       *reinterpret_cast<float4*>(sh + (wt * 16 + j) * 16) = make_float4(0.f, 0.f, 0.f, 0.f);   // hi and lo, 32 KiB
     fence_proxy_async_smem();
     mbar_arrive(B.st_ready);
+    // columns 32-63 of the first chunk's K lo tile
+    auto k_lo_half = [&](int chunk) -> bool {
+      bool fine = mbar_wait_abortable(&B.k_full[chunk & 1], (chunk >> 1) & 1, s_abort);
+      fine = __all_sync(0xffffffffu, fine);
+      if (!fine) return false;
+      const unsigned char* kh = smem + ((chunk & 1) ? kOffK1 : kOffK0);
+      unsigned char* kl = smem + kOffKlo;
+#pragma unroll
+      for (int j = 8; j < 16; ++j) {
+        const uint32_t off = chunk_off(r, j, kSub);
+        *reinterpret_cast<float4*>(kl + off) = rest4(*reinterpret_cast<const float4*>(kh + off));
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(B.k_ready);
+      return true;
+    };
+    ok = k_lo_half(0);
     for (int i = 0; ok && i < nchunk; ++i) {
       const uint32_t ph = i & 1;
       ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
@@ -408,16 +464,33 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t v[32], lo[32];
+        if (cb > q4) {
+          // every key of the block is after every row of this warp
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+          umma::tmem_st32(lane_base + kColS + cb * 32, v);
+          umma::tmem_st32(lane_base + kColPlo + cb * 32, v);
+          continue;
+        }
         umma::tmem_ld32(lane_base + kColS + cb * 32, v);
         umma::tmem_wait_ld();
+        if (cb < q4) {
+          // all keys visible: g^(r-c) = g^(r - 32 cb - 31) g^(31-j)
+          const float a = s_pow[r - 32 * cb - 31];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int c = cb * 32 + j;
-          const int e = r - c;
-          const float p = e >= 0 ? __uint_as_float(v[j]) * s_pow[e] : 0.f;
-          const float h = tf32_rn(p);
-          v[j] = __float_as_uint(h);
-          lo[j] = __float_as_uint(p - h);
+          for (int j = 0; j < 32; ++j) {
+            const float p = __uint_as_float(v[j]) * (a * gp[j]);
+            v[j] = __float_as_uint(p);
+            lo[j] = __float_as_uint(tf32_rest(p));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int e = lane - j;             // r - c on the diagonal block
+            const float p = e >= 0 ? __uint_as_float(v[j]) * s_pow[e] : 0.f;
+            v[j] = __float_as_uint(p);
+            lo[j] = __float_as_uint(tf32_rest(p));
+          }
         }
         umma::tmem_st32(lane_base + kColS + cb * 32, v);
         umma::tmem_st32(lane_base + kColPlo + cb * 32, lo);
@@ -432,38 +505,45 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::fence_after_sync();
       if (i + 1 < nchunk) {
         // state: St <- g^128 St + D^T; a 64-row accumulator keeps row n in lane (n % 16) of
-        // lane quarter n / 16
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t d[32];
-          umma::tmem_ld32(lane_base + kColD + half * 32, d);
-          umma::tmem_wait_ld();
-          if (lane < 16) {
-            const uint32_t n = q4 * 16 + lane;
+        // lane quarter n / 16.  D is read first so that the next Q can take its columns.
+        // D arrives as two 64-column halves (products with K' hi and K' lo) to be added.
+        float d[64];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t off = chunk_off(n, half * 8 + j, kSubS);
-              const float4 a = *reinterpret_cast<const float4*>(sh + off);
-              const float4 b = *reinterpret_cast<const float4*>(sl + off);
-              float4 h, l;
-              split4(make_float4(fmaf(gC, a.x + b.x, __uint_as_float(d[4 * j])),
-                                 fmaf(gC, a.y + b.y, __uint_as_float(d[4 * j + 1])),
-                                 fmaf(gC, a.z + b.z, __uint_as_float(d[4 * j + 2])),
-                                 fmaf(gC, a.w + b.w, __uint_as_float(d[4 * j + 3]))),
-                     h, l);
-              *reinterpret_cast<float4*>(sh + off) = h;
-              *reinterpret_cast<float4*>(sl + off) = l;
-            }
-          }
+        for (int half = 0; half < 2; ++half) {
+          uint32_t a[32], b[32];
+          umma::tmem_ld32(lane_base + kColD + half * 32, a);
+          umma::tmem_ld32(lane_base + kColD + 64 + half * 32, b);
+          umma::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[half * 32 + j] = __uint_as_float(a[j]) + __uint_as_float(b[j]);
         }
         umma::fence_before_sync();
+        mbar_arrive(B.d_free);
+        // the next chunk's K is in shared memory already: half of its lo tile
+        if (!k_lo_half(i + 1)) { ok = false; break; }
+        if (lane < 16) {
+          const uint32_t n = q4 * 16 + lane;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t off = chunk_off(n, j, kSubS);
+            const float4 a = *reinterpret_cast<const float4*>(sh + off);
+            const float4 x = make_float4(fmaf(gC, a.x, d[4 * j]),
+                                         fmaf(gC, a.y, d[4 * j + 1]),
+                                         fmaf(gC, a.z, d[4 * j + 2]),
+                                         fmaf(gC, a.w, d[4 * j + 3]));
+            *reinterpret_cast<float4*>(sh + off) = x;
+            *reinterpret_cast<float4*>(sl + off) = rest4(x);
+          }
+        }
         fence_proxy_async_smem();
         mbar_arrive(B.st_ready);
       }
-      // output: o = (O1 + g^(r+1) O2) / scale, staged as a swizzled tile and stored by TMA
+      // output: o = (O1 + g^(r+1) O2) / scale, staged as a swizzled tile where Q was (the next Q
+      // is in tensor memory by then) and stored by TMA
       if (wt == 0) bulk_wait_read<0>();          // the previous store has read the staging tile
+      if (i + 1 < nchunk) ok = mbar_wait_abortable(B.q_ready, (i + 1) & 1, s_abort);
       mbar_arrive(B.wg_sync);
-      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort) && ok;
       wg_phase ^= 1;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -495,6 +575,10 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         umma::tma_store_3d(&map_o, 0, i * kC, bh, ot);
         if (dv > 32) umma::tma_store_3d(&map_o, 32, i * kC, bh, ot + kSub);
         bulk_commit();
+        if (i + 1 < nchunk) {
+          bulk_wait_read<0>();
+          mbar_arrive(B.qtile_free);             // the next but one Q may be loaded
+        }
       }
     }
     if (wt == 0) bulk_wait_all<0>();
