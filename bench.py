@@ -468,6 +468,21 @@ def bench_extras(args, rank: int, world: int, pk: dict, flush: torch.Tensor) -> 
                                                                      K, W, world, flush)
     del q, k, v, o2
 
+    # fp32 decayed attention at many heads (B=16 H=32 T=2048 d=64): three-pass TF32 on the tensor cores.
+    # Flops: per 128-row chunk Q.K^T and P.V (2*128*128*64 each), Q.St and K^T.V (2*128*64*64 each),
+    # each taken three times.
+    Bf, Hf, Tf, df = 16, 32, 2048, 64
+    qf, kf, vf = (torch.randn(Bf, Hf, Tf, df, device=dev, generator=gen) / 8 for _ in range(3))
+    gf = c4_gamma(Hf).to(dev)
+    of = torch.empty_like(vf)
+    ms = time_steps(lambda: ops.decayed_chunk_fwd(qf, kf, vf, gf, 128, 1.0, out=of), K, W, world)
+    out["decayed_fp32_B16_H32_T2048_d64"] = entry(
+        ms, Bf * Tf, 4 * Bf * Hf * Tf * df * 4, 1,
+        "fp32 tensors, 3xTF32 tcgen05 (one CTA per unit, 512 units = 3.5 waves); 1.07 GB exceed L2; tflops counts "
+        "the three passes",
+        flops=3 * Bf * Hf * (Tf // 128) * (2 * 2 * 128 * 128 * df + 2 * 2 * 128 * df * df))
+    del qf, kf, vf, of
+
     # config 3: scan B=8 D=1024 N=16 T=4096 bf16; ranks own channel blocks of the (b,d) axis
     B, T, D, N = 8, 4096, 1024, 16
     x3 = _randn_bf16((B, T, D), gen)
@@ -843,6 +858,11 @@ def run_profile_case(args) -> None:
         gamma = c4_gamma(8).to(dev)
         o = torch.empty_like(v)
         fn = lambda: ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0, out=o)  # noqa: E731
+    elif args.profile_case == "decayed_fp32":  # 148 heads x T=2048, d=64 fp32 (310 MB): three-pass TF32 kernel
+        q, k, v = (torch.randn(2, 74, 2048, 64, device=dev, generator=gen) / 8 for _ in range(3))
+        gamma = c4_gamma(74).to(dev)
+        o = torch.empty_like(v)
+        fn = lambda: ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0, out=o)  # noqa: E731
     elif args.profile_case == "decayed_strong":  # one rank's share of config 4 cut over 8 GPUs: 64 units (537 MB)
         q, k, v = (_randn_bf16((64, 8192 * 128), gen, 1 / math.sqrt(128)).view(2, 32, 8192, 128) for _ in range(3))
         gamma = c4_gamma(32).to(dev)
@@ -895,7 +915,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
+                    choices=["decayed", "decayed_fp32", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -39,9 +39,10 @@
 //
 // Roles: warp 0 loads tiles with TMA; warp 1 issues the MMAs (MMA1, MMA4, MMA3,
 // MMA2: the state increment keeps the pipe busy while P is being built); warps
-// 2-5 (operand warps) put Q into tensor memory, build K lo and V lo and, once
-// MMA1 has read K, rescale K for the state increment; warps 6-9 (score warps)
-// mask and decay S into P, carry the state and write the output.
+// 2-5 put Q into tensor memory, build half of K lo, carry the state and, once
+// MMA1 has read K, rescale K for the state increment; warps 6-9 build the other
+// half of K lo, write the output of the chunk before, build V lo, and mask and
+// decay S into P.
 // Every wait is bounded: on expiry the CTA records CB2_WAIT_TIMEOUT and leaves.
 #include <algorithm>
 
@@ -83,7 +84,7 @@ struct Bars {
   uint64_t* st_ready;                      // state tiles written
   uint64_t* o_free;                        // O1 / O2 read
   uint64_t* wg_sync;                       // among the score warps
-  uint64_t* d_free;                        // D read into registers (the Q columns may be rewritten)
+  uint64_t* spare;
   uint64_t* qtile_free;                    // the staged output has left the Q tile
 };
 
@@ -125,6 +126,27 @@ __device__ __forceinline__ uint32_t chunk_off(uint32_t row, uint32_t j, uint32_t
 // Same for the 128-byte swizzle with 32-byte atoms: 32-byte chunk c of a row sits at c ^ (row % 4).
 __device__ __forceinline__ uint32_t chunk_off32(uint32_t row, uint32_t j, uint32_t sub_bytes) {
   return (j >> 3) * sub_bytes + row * 128u + ((((((j & 7u) >> 1) ^ (row & 3u)) << 1) | (j & 1u)) << 4);
+}
+// Rows r and r + 4 of that pattern keep a given chunk in the same banks, so a quarter-warp writing
+// chunk j of eight consecutive rows would hit every bank twice: lanes 4-7 of each eight take the
+// two chunks of a 32-byte pair in the other order.  x holds the eight chunks of columns
+// [32 half, 32 half + 32) of `row`; REST also writes their truncation remainders to the lo tile.
+template <bool REST>
+__device__ __forceinline__ void store_half_32b(unsigned char* hi_tile, unsigned char* lo_tile, uint32_t row,
+                                               int half, const float4 (&x)[8], uint32_t sub_bytes) {
+  const bool flip = (row >> 2) & 1u;
+#pragma unroll
+  for (int pr = 0; pr < 4; ++pr) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      // t-th store of the pair: chunk 2 pr + (t ^ flip)
+      const float4 a = x[2 * pr + t], b = x[2 * pr + (t ^ 1)];
+      const float4 v = flip ? b : a;
+      const uint32_t off = chunk_off32(row, half * 8 + 2 * pr + (t ^ int(flip)), sub_bytes);
+      *reinterpret_cast<float4*>(hi_tile + off) = v;
+      if (REST) *reinterpret_cast<float4*>(lo_tile + off) = rest4(v);
+    }
+  }
 }
 // Shared-memory matrix descriptor with the layout type given (2: 128-byte swizzle, 1: 128-byte swizzle
 // with 32-byte atoms).
@@ -180,7 +202,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     mbar_init(B.st_ready, 128);
     mbar_init(B.o_free, 128);
     mbar_init(B.wg_sync, 128);
-    mbar_init(B.d_free, 128);
+    mbar_init(B.spare, 1);
     mbar_init(B.qtile_free, 1);
     *s_abort = 0;
     mbar_fence_init();
@@ -324,25 +346,45 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   } else if (warp < 6) {
-    // ---------------------------------------------------------------- operand warps
+    // ---------------------------------------------------------------- operand / state warps
+    // Per chunk: read the state increment of the chunk before, put Q into tensor memory, build half of
+    // K lo (-> MMA1 can start), carry the state (-> MMA4), rescale K once MMA1 is done (-> MMA3).
     const int q4 = warp & 3;
     const int r = q4 * 32 + lane;                // row of every tile this thread owns
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
     unsigned char* qt = smem + kOffQ;
     unsigned char* kl = smem + kOffKlo;
-    unsigned char* vh = smem + kOffVhi;
-    unsigned char* vl = smem + kOffVlo;
+    unsigned char* sh = smem + kOffShi;
+    unsigned char* sl = smem + kOffSlo;
     const float w = s_pow[kC - 1 - r];           // decay of key r to the end of the chunk
+    const float gC = s_pow[kC];
     bool ok = true;
     for (int i = 0; ok && i < nchunk; ++i) {
       const uint32_t ph = i & 1;
       unsigned char* kh = smem + (ph ? kOffK1 : kOffK0);
-      // Q -> tensor memory (value, remainder); the columns are free once the score warps have read D
-      ok = mbar_wait_abortable(B.q_full, ph, s_abort) &&
-           (i == 0 || mbar_wait_abortable(B.d_free, (i - 1) & 1, s_abort));
+      // D of the chunk before: two 64-column halves (products with K' hi and K' lo) to be added.  A
+      // 64-row accumulator keeps row n in lane (n % 16) of lane quarter n / 16.  Read first: Q goes
+      // into the same columns.
+      float d[64];
+      if (i > 0) {
+        ok = mbar_wait_abortable(B.c_done, (i - 1) & 1, s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        umma::fence_after_sync();
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t a[32], b[32];
+          umma::tmem_ld32(lane_base + kColD + half * 32, a);
+          umma::tmem_ld32(lane_base + kColD + 64 + half * 32, b);
+          umma::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[half * 32 + j] = __uint_as_float(a[j]) + __uint_as_float(b[j]);
+        }
+      }
+      // Q -> tensor memory (value, remainder)
+      ok = mbar_wait_abortable(B.q_full, ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      umma::fence_after_sync();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t hi[32], lo[32];
@@ -361,13 +403,11 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tmem_wait_st();
       umma::fence_before_sync();
       mbar_arrive(B.q_ready);
-      // K lo (the K tile itself is the hi operand); the lo tile is free once the chunk before is done
-      ok = mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort) &&
-           (i == 0 || mbar_wait_abortable(B.c_done, (i - 1) & 1, s_abort));
+      // K lo, columns 0-31 (the K tile itself is the hi operand; the other warpgroup does columns
+      // 32-63: this is the one step between two chunks during which the tensor pipe has nothing to do)
+      ok = mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // (columns 0-31 here, 32-63 by the score warps: this is the one step between two chunks during
-      // which the tensor pipe has nothing to do)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const uint32_t off = chunk_off(r, j, kSub);
@@ -375,24 +415,24 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
-      // V: moved to the 32-byte-atom pattern in place, and its lo tile
-      ok = mbar_wait_abortable(B.v_full, ph, s_abort);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      // state: St <- g^128 St + D^T (zero before the first chunk); the hi tile is the fp32 state
+      if (i == 0) {
+        for (int j = 0; j < 16; ++j)
+          *reinterpret_cast<float4*>(sh + ((tid - 64) * 16 + j) * 16) = make_float4(0.f, 0.f, 0.f, 0.f);   // hi and lo
+      } else if (lane < 16) {
+        const uint32_t n = q4 * 16 + lane;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float4 x[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = *reinterpret_cast<const float4*>(vh + chunk_off(r, half * 8 + j, kSub));
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t off = chunk_off32(r, half * 8 + j, kSub);
-          *reinterpret_cast<float4*>(vh + off) = x[j];
-          *reinterpret_cast<float4*>(vl + off) = rest4(x[j]);
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t off = chunk_off(n, j, kSubS);
+          const float4 a = *reinterpret_cast<const float4*>(sh + off);
+          const float4 x = make_float4(fmaf(gC, a.x, d[4 * j]), fmaf(gC, a.y, d[4 * j + 1]),
+                                       fmaf(gC, a.z, d[4 * j + 2]), fmaf(gC, a.w, d[4 * j + 3]));
+          *reinterpret_cast<float4*>(sh + off) = x;
+          *reinterpret_cast<float4*>(sl + off) = rest4(x);
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(B.v_ready);
+      mbar_arrive(B.st_ready);
       // K' = K g^(127-r), moved to the 32-byte-atom pattern, once MMA1 has read K
       if (i + 1 < nchunk) {
         ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
@@ -406,57 +446,112 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float4 a = *reinterpret_cast<const float4*>(kh + chunk_off(r, half * 8 + j, kSub));
             x[j] = make_float4(a.x * w, a.y * w, a.z * w, a.w * w);
           }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t off = chunk_off32(r, half * 8 + j, kSub);
-            *reinterpret_cast<float4*>(kh + off) = x[j];
-            *reinterpret_cast<float4*>(kl + off) = rest4(x[j]);
-          }
+          store_half_32b<true>(kh, kl, r, half, x, kSub);
         }
         fence_proxy_async_smem();
         mbar_arrive(B.k2_ready);
       }
     }
   } else {
-    // ---------------------------------------------------------------- score / state / output warps
+    // ---------------------------------------------------------------- score / output warps
+    // Per chunk: the other half of K lo, the output of the chunk before (-> MMA4 may overwrite O2), V
+    // into its MMA layout with its lo tile (-> MMA3), then P from S (-> MMA2).
     const int q4 = warp & 3;
     const int r = q4 * 32 + lane;
     const int wt = tid - 192;                    // 0..127 among these warps
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
-    unsigned char* sh = smem + kOffShi;
-    unsigned char* sl = smem + kOffSlo;
+    unsigned char* kl = smem + kOffKlo;
+    unsigned char* vh = smem + kOffVhi;
+    unsigned char* vl = smem + kOffVlo;
     unsigned char* ot = smem + kOffQ;            // the output is staged where Q was
-    const float gC = s_pow[kC];
     const float fcross = s_pow[r + 1];
     float gp[32];                                // g^(31-j)
 #pragma unroll
     for (int j = 0; j < 32; ++j) gp[j] = s_pow[31 - j];
     uint32_t wg_phase = 0;
     bool ok = true;
-    // the state starts at zero
-    for (int j = 0; j < 16; ++j)
-      *reinterpret_cast<float4*>(sh + (wt * 16 + j) * 16) = make_float4(0.f, 0.f, 0.f, 0.f);   // hi and lo, 32 KiB
-    fence_proxy_async_smem();
-    mbar_arrive(B.st_ready);
-    // columns 32-63 of the first chunk's K lo tile
-    auto k_lo_half = [&](int chunk) -> bool {
-      bool fine = mbar_wait_abortable(&B.k_full[chunk & 1], (chunk >> 1) & 1, s_abort);
+    // o = (O1 + g^(r+1) O2) / scale of chunk `c`, staged as a swizzled tile where Q was (the next Q is
+    // in tensor memory by then) and stored by TMA
+    auto write_output = [&](int c, bool more) -> bool {
+      if (wt == 0) bulk_wait_read<0>();          // the previous store has read the staging tile
+      mbar_arrive(B.wg_sync);
+      bool fine = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      wg_phase ^= 1;
       fine = __all_sync(0xffffffffu, fine);
       if (!fine) return false;
-      const unsigned char* kh = smem + ((chunk & 1) ? kOffK1 : kOffK0);
-      unsigned char* kl = smem + kOffKlo;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[32], b[32];
+        umma::tmem_ld32(lane_base + kColO1 + half * 32, a);
+        umma::tmem_ld32(lane_base + kColO2 + half * 32, b);
+        umma::tmem_wait_ld();
 #pragma unroll
-      for (int j = 8; j < 16; ++j) {
-        const uint32_t off = chunk_off(r, j, kSub);
-        *reinterpret_cast<float4*>(kl + off) = rest4(*reinterpret_cast<const float4*>(kh + off));
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = (__uint_as_float(a[4 * j]) + fcross * __uint_as_float(b[4 * j])) * inv_scale;
+          o.y = (__uint_as_float(a[4 * j + 1]) + fcross * __uint_as_float(b[4 * j + 1])) * inv_scale;
+          o.z = (__uint_as_float(a[4 * j + 2]) + fcross * __uint_as_float(b[4 * j + 2])) * inv_scale;
+          o.w = (__uint_as_float(a[4 * j + 3]) + fcross * __uint_as_float(b[4 * j + 3])) * inv_scale;
+          *reinterpret_cast<float4*>(ot + chunk_off(r, half * 8 + j, kSub)) = o;
+        }
+      }
+      umma::fence_before_sync();
+      mbar_arrive(B.o_free);
+      fence_proxy_async_smem();
+      mbar_arrive(B.wg_sync);
+      fine = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      wg_phase ^= 1;
+      fine = __all_sync(0xffffffffu, fine);
+      if (!fine) return false;
+      if (wt == 0) {
+        umma::tma_store_3d(&map_o, 0, c * kC, bh, ot);
+        if (dv > 32) umma::tma_store_3d(&map_o, 32, c * kC, bh, ot + kSub);
+        bulk_commit();
+        if (more) {
+          bulk_wait_read<0>();
+          mbar_arrive(B.qtile_free);             // the next but one Q may be loaded
+        }
+      }
+      return true;
+    };
+    for (int i = 0; ok && i < nchunk; ++i) {
+      const uint32_t ph = i & 1;
+      // K lo, columns 32-63 (every MMA of the chunk before is done: the loop ends on that wait)
+      ok = mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      {
+        const unsigned char* kh = smem + (ph ? kOffK1 : kOffK0);
+#pragma unroll
+        for (int j = 8; j < 16; ++j) {
+          const uint32_t off = chunk_off(r, j, kSub);
+          *reinterpret_cast<float4*>(kl + off) = rest4(*reinterpret_cast<const float4*>(kh + off));
+        }
       }
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
-      return true;
-    };
-    ok = k_lo_half(0);
-    for (int i = 0; ok && i < nchunk; ++i) {
-      const uint32_t ph = i & 1;
+      // output of the chunk before, once this chunk's Q has left its tile
+      if (i > 0) {
+        ok = mbar_wait_abortable(B.q_ready, ph, s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        umma::fence_after_sync();
+        if (!write_output(i - 1, true)) { ok = false; break; }
+      }
+      // V: moved to the 32-byte-atom pattern in place, and its lo tile
+      ok = mbar_wait_abortable(B.v_full, ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float4 x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = *reinterpret_cast<const float4*>(vh + chunk_off(r, half * 8 + j, kSub));
+        store_half_32b<true>(vh, vl, r, half, x, kSub);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(B.v_ready);
+      // P = tril(S . g^(r-c)) as value + remainder
       ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -503,84 +598,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       umma::fence_after_sync();
-      if (i + 1 < nchunk) {
-        // state: St <- g^128 St + D^T; a 64-row accumulator keeps row n in lane (n % 16) of
-        // lane quarter n / 16.  D is read first so that the next Q can take its columns.
-        // D arrives as two 64-column halves (products with K' hi and K' lo) to be added.
-        float d[64];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t a[32], b[32];
-          umma::tmem_ld32(lane_base + kColD + half * 32, a);
-          umma::tmem_ld32(lane_base + kColD + 64 + half * 32, b);
-          umma::tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) d[half * 32 + j] = __uint_as_float(a[j]) + __uint_as_float(b[j]);
-        }
-        umma::fence_before_sync();
-        mbar_arrive(B.d_free);
-        // the next chunk's K is in shared memory already: half of its lo tile
-        if (!k_lo_half(i + 1)) { ok = false; break; }
-        if (lane < 16) {
-          const uint32_t n = q4 * 16 + lane;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t off = chunk_off(n, j, kSubS);
-            const float4 a = *reinterpret_cast<const float4*>(sh + off);
-            const float4 x = make_float4(fmaf(gC, a.x, d[4 * j]),
-                                         fmaf(gC, a.y, d[4 * j + 1]),
-                                         fmaf(gC, a.z, d[4 * j + 2]),
-                                         fmaf(gC, a.w, d[4 * j + 3]));
-            *reinterpret_cast<float4*>(sh + off) = x;
-            *reinterpret_cast<float4*>(sl + off) = rest4(x);
-          }
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(B.st_ready);
-      }
-      // output: o = (O1 + g^(r+1) O2) / scale, staged as a swizzled tile where Q was (the next Q
-      // is in tensor memory by then) and stored by TMA
-      if (wt == 0) bulk_wait_read<0>();          // the previous store has read the staging tile
-      if (i + 1 < nchunk) ok = mbar_wait_abortable(B.q_ready, (i + 1) & 1, s_abort);
-      mbar_arrive(B.wg_sync);
-      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort) && ok;
-      wg_phase ^= 1;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        uint32_t a[32], b[32];
-        umma::tmem_ld32(lane_base + kColO1 + half * 32, a);
-        umma::tmem_ld32(lane_base + kColO2 + half * 32, b);
-        umma::tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float4 o;
-          o.x = (__uint_as_float(a[4 * j]) + fcross * __uint_as_float(b[4 * j])) * inv_scale;
-          o.y = (__uint_as_float(a[4 * j + 1]) + fcross * __uint_as_float(b[4 * j + 1])) * inv_scale;
-          o.z = (__uint_as_float(a[4 * j + 2]) + fcross * __uint_as_float(b[4 * j + 2])) * inv_scale;
-          o.w = (__uint_as_float(a[4 * j + 3]) + fcross * __uint_as_float(b[4 * j + 3])) * inv_scale;
-          *reinterpret_cast<float4*>(ot + chunk_off(r, half * 8 + j, kSub)) = o;
-        }
-      }
-      umma::fence_before_sync();
-      mbar_arrive(B.o_free);
-      fence_proxy_async_smem();
-      mbar_arrive(B.wg_sync);
-      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
-      wg_phase ^= 1;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (wt == 0) {
-        umma::tma_store_3d(&map_o, 0, i * kC, bh, ot);
-        if (dv > 32) umma::tma_store_3d(&map_o, 32, i * kC, bh, ot + kSub);
-        bulk_commit();
-        if (i + 1 < nchunk) {
-          bulk_wait_read<0>();
-          mbar_arrive(B.qtile_free);             // the next but one Q may be loaded
-        }
-      }
     }
+    if (ok) write_output(nchunk - 1, false);
     if (wt == 0) bulk_wait_all<0>();
   }
   __syncwarp();

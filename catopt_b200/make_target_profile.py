@@ -31,6 +31,7 @@ EXECUTORS = {
     "headline": ("b200_om_decayed_chunked", 3 * 16 * 32 * 8192 * 128),
     "config2_decayed_fp32": ("b200_om_decayed_chunked", 3 * 2 * 4 * 1024 * 64),
     "decayed_bf16_few_heads_B2_H8_T8192_d128": ("b200_om_decayed_chunked", 3 * 2 * 8 * 8192 * 128),
+    "decayed_fp32_B16_H32_T2048_d64": ("b200_om_decayed_chunked", 3 * 16 * 32 * 2048 * 64),
     "config1_folded_chain_fp32": ("b200_linear_chain", 64 * 512),
     "folded_chain_fp32_R4096": ("b200_linear_chain", 4096 * 512),
     "folded_chain_fp32_R16384_2048x2048": ("b200_linear_chain", 16384 * 2048),

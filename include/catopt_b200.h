@@ -178,7 +178,9 @@ int cb2_chain_fold_f32_noalloc(const float* const* weights, const int* dims, int
 size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv,
                                        int chunk, int dtype);
 /* 1 when cb2_decayed_chunk_fwd runs these sizes on the tensor cores (one launch,
- * state on chip), 0 when it takes the fp32 FMA path (three launches). */
+ * state on chip: bf16 with head dims up to 128, or fp32 with head dims up to 64
+ * (multiples of 4) and at least 24 (batch, head) units, in three TF32 passes at
+ * fp32 accuracy), 0 when it takes the fp32 FMA path. */
 int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, int dv,
                                       int chunk, int dtype);
 /* How the tensor-core path cuts a call of these sizes into CTAs, given the scratch the size
@@ -187,7 +189,7 @@ int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, int dv,
  * states computed by a pre-pass (few heads); 3 two CTAs per head in one launch, the second
  * accumulating the first's state from K and V by itself (a quarter to half as many heads as
  * SMs; no scratch).  -1: the call does not run on the tensor cores.  0, 1 and 3 give the
- * same bits. */
+ * same bits.  fp32 calls on the tensor cores are always 0. */
 int cb2_decayed_chunk_plan(int B, int H, int T, int dk, int dv, int chunk, int dtype);
 int cb2_decayed_chunk_fwd(const void* q, const void* k, const void* v, void* o,
                           const float* gamma, int B, int H, int T, int dk, int dv,

@@ -54,6 +54,10 @@ def test_argument_errors_without_a_device(lib_path):
     assert lib.cb2_linear_f32_scratch_bytes(4096, 512, 512) == 2 * 512 * 512 * 4   # w split into hi + lo
     assert lib.cb2_decayed_chunk_on_tensor_cores(16, 32, 8192, 128, 128, 128, 1) == 1
     assert lib.cb2_decayed_chunk_on_tensor_cores(2, 4, 1024, 64, 64, 64, 0) == 0
+    # fp32 with enough (batch, head) units and head dims up to 64: three-pass TF32, no scratch
+    assert lib.cb2_decayed_chunk_on_tensor_cores(16, 32, 2048, 64, 64, 128, 0) == 1
+    assert lib.cb2_decayed_chunk_on_tensor_cores(16, 32, 2048, 128, 128, 128, 0) == 0
+    assert lib.cb2_decayed_chunk_scratch_bytes(16, 32, 2048, 64, 64, 128, 0) == 0
 
 
 def test_no_cpu_fallback():

@@ -164,6 +164,117 @@ def test_decayed_f64_case_in_fp32(dev):
     assert rel_to_max(out, torch.from_numpy(g["tiny_f64.chunked"])) <= FP32_TOL
 
 
+# fp32 tensors with dk, dv <= 64 and at least 24 (batch, head) units run on the tensor cores in three
+# TF32 passes; fewer units stay on the FMA pipes.
+def _decayed_fp64(q, k, v, gamma, scale):
+    """All-pairs evaluation in fp64 on the device (the reference's quadratic form)."""
+    B, H, T, _ = q.shape
+    t = torch.arange(T, device=q.device, dtype=torch.float64)
+    e = (t[:, None] - t[None, :]).clamp(min=0)
+    out = torch.empty(B, H, T, v.shape[-1], dtype=torch.float64, device=q.device)
+    for h in range(H):
+        g = torch.tensor(float(gamma[h]), dtype=torch.float64, device=q.device)
+        dm = torch.tril(torch.pow(g, e))
+        out[:, h] = ((q[:, h].double() @ k[:, h].double().transpose(-1, -2)) * dm) @ v[:, h].double() / scale
+    return out
+
+
+@pytest.mark.parametrize("name", ["tiny_f32_scalar", "odd_f32", "c2_f32"])
+def test_decayed_fp32_tensor_core_path_vs_reference_fixture(dev, name):
+    """The reference's stored outputs, with the case repeated over the batch until the call has
+    enough units for the tensor-core kernel: every copy must match the fixture."""
+    from catopt_b200 import _lib, ops
+
+    g = np.load(GOLD / "decayed.npz")
+    q, k, v, gamma, C, scale = cases.decayed_inputs(name)
+    B, H, T, d = q.shape
+    reps = -(-24 // (B * H))
+    qq, kk, vv = (t.repeat(reps, 1, 1, 1).contiguous().to(dev) for t in (q, k, v))
+    gam = (gamma if gamma.dim() else gamma.repeat(H)).float().to(dev)
+    assert _lib.load().cb2_decayed_chunk_on_tensor_cores(B * reps, H, T, d, d, C, _lib.CB2_F32) == 1
+    out = ops.decayed_chunk_fwd(qq, kk, vv, gam, C, scale)
+    ops.check_device_status(dev)
+    stride = cases.ROW_STRIDE.get(name, 1)
+    want = torch.from_numpy(g[f"{name}.chunked"])
+    for rep in range(reps):
+        assert rel_to_max(out[rep * B:(rep + 1) * B, :, ::stride], want) <= FP32_TOL
+
+
+@pytest.mark.parametrize("B,H,T,dk,dv,C,scale", [(1, 24, 128, 64, 64, 128, 1.0), (2, 16, 512, 64, 64, 64, 1.0),
+                                                 (1, 24, 384, 32, 32, 128, 1.0), (1, 24, 192, 48, 24, 64, 1.0),
+                                                 (1, 24, 200, 64, 64, 8, 8.0), (3, 8, 136, 4, 60, 8, 0.5)])
+def test_decayed_fp32_tensor_core_path_vs_fp64(dev, B, H, T, dk, dv, C, scale):
+    """Shapes off the tile grid (ragged last chunk, head dims below 64, dk != dv) and a scale."""
+    from catopt_b200 import _lib, ops
+
+    gen = torch.Generator(device="cuda").manual_seed(B * 7 + T + dk)
+    q = torch.randn(B, H, T, dk, device=dev, generator=gen) / math.sqrt(dk)
+    k = torch.randn(B, H, T, dk, device=dev, generator=gen) / math.sqrt(dk)
+    v = torch.randn(B, H, T, dv, device=dev, generator=gen)
+    gamma = torch.tensor([1 - 2.0 ** (-5 - 3 * h / H) for h in range(H)], dtype=torch.float32, device=dev)
+    assert _lib.load().cb2_decayed_chunk_on_tensor_cores(B, H, T, dk, dv, C, _lib.CB2_F32) == 1
+    out = ops.decayed_chunk_fwd(q, k, v, gamma, C, scale)
+    ops.check_device_status(dev)
+    assert rel_to_max(out, _decayed_fp64(q, k, v, gamma, scale)) <= FP32_TOL
+
+
+def test_decayed_fp32_tensor_core_path_takes_every_rate(dev):
+    """Rates for which rescaled keys would overflow or vanish (0, 0.05, negative, 1): the kernel decays
+    scores by g^(r-c) directly, so it needs no second formulation."""
+    from catopt_b200 import ops
+
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v = (torch.randn(1, 24, 512, 64, device=dev, generator=gen) / 8 for _ in range(3))
+    gamma = torch.tensor([0.5, 1.0, 0.9, 0.05, 0.0, 0.999, -0.7, 0.74] * 3, dtype=torch.float32, device=dev)
+    out = ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0)
+    ops.check_device_status(dev)
+    want = _decayed_fp64(q, k, v, gamma, 1.0)
+    for h in range(24):
+        assert rel_to_max(out[:, h], want[:, h]) <= FP32_TOL, (h, float(gamma[h]))
+
+
+def test_decayed_fp32_tensor_core_path_agrees_with_the_fma_path_and_the_oracle(dev):
+    """The same heads through the tensor-core kernel (32 units) and, four at a time, through the FMA
+    path; two of them against the oracle's chunked pairwise executor."""
+    from catopt_b200 import _lib, ops
+
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    q, k, v = (torch.randn(2, 16, 1024, 64, device=dev, generator=gen) / 8 for _ in range(3))
+    gamma = torch.tensor([1 - 2.0 ** (-5 - h / 4) for h in range(16)], dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    assert lib.cb2_decayed_chunk_on_tensor_cores(2, 16, 1024, 64, 64, 64, _lib.CB2_F32) == 1
+    assert lib.cb2_decayed_chunk_on_tensor_cores(1, 4, 1024, 64, 64, 64, _lib.CB2_F32) == 0
+    out = ops.decayed_chunk_fwd(q, k, v, gamma, 64, 1.0)
+    for h0 in range(0, 16, 4):
+        part = ops.decayed_chunk_fwd(q[:1, h0:h0 + 4].contiguous(), k[:1, h0:h0 + 4].contiguous(),
+                                     v[:1, h0:h0 + 4].contiguous(), gamma[h0:h0 + 4].contiguous(), 64, 1.0)
+        assert rel_to_max(out[:1, h0:h0 + 4], part) <= FP32_TOL
+    want = oracle.decayed_chunked_pairwise(q[1:, 14:].cpu(), k[1:, 14:].cpu(), v[1:, 14:].cpu(), gamma[14:].cpu(), 64, 1.0)
+    assert rel_to_max(out[1:, 14:], want) <= FP32_TOL
+
+
+def test_decayed_fp32_tensor_core_path_long_sequence_and_full_waves(dev):
+    """B16 H32 T2048 d64 (512 units: several waves of CTAs) against fp64 on sampled units, and T = 8192
+    (64 chunks of carried state) on 24 units."""
+    from catopt_b200 import ops
+
+    gen = torch.Generator(device="cuda").manual_seed(13)
+    q, k, v = (torch.randn(16, 32, 2048, 64, device=dev, generator=gen) / 8 for _ in range(3))
+    gamma = torch.tensor([1 - 2.0 ** (-5 - 8 * h / 32) for h in range(32)], dtype=torch.float32, device=dev)
+    out = ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0)
+    ops.check_device_status(dev)
+    for b in (0, 7, 15):
+        want = _decayed_fp64(q[b:b + 1], k[b:b + 1], v[b:b + 1], gamma, 1.0)
+        assert rel_to_max(out[b:b + 1], want) <= FP32_TOL
+    q, k, v = (torch.randn(1, 24, 8192, 64, device=dev, generator=gen) / 8 for _ in range(3))
+    gamma = torch.tensor([1 - 2.0 ** (-5 - 8 * h / 24) for h in range(24)], dtype=torch.float32, device=dev)
+    out = ops.decayed_chunk_fwd(q, k, v, gamma, 128, 1.0)
+    ops.check_device_status(dev)
+    for h in (0, 11, 23):
+        want = _decayed_fp64(q[:, h:h + 1], k[:, h:h + 1], v[:, h:h + 1], gamma[h:h + 1], 1.0)
+        assert rel_to_max(out[:, h:h + 1], want) <= FP32_TOL
+
+
 @pytest.mark.parametrize("B,H,T,d,C", [(1, 2, 512, 128, 128), (2, 3, 256, 64, 64), (1, 1, 128, 128, 128),
                                        (1, 2, 96, 32, 32), (2, 2, 1024, 64, 64), (1, 3, 384, 16, 32),
                                        (1, 2, 256, 96, 128), (1, 1, 256, 8, 64)])
