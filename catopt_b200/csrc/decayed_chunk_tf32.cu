@@ -289,17 +289,26 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint64_t khi_k = desc_k(k0 + ph * 2 * kTile, 0, kSub), khi_m = desc_mn(k0 + ph * 2 * kTile, 0);
         // K' hi and lo side by side as one 128-wide operand: hi | lo for even chunks, lo | hi for odd ones
         const uint64_t kboth_m = ph ? klo_m : khi_m;
-        // MMA1: S = Q K^T (small terms first)
+        // MMA1: S = Q K^T.  The two products against K itself start as soon as Q is in tensor memory
+        // and the K tile has landed; the one against K lo follows when the warps have built that tile.
         if (!mbar_wait_abortable(B.q_ready, ph, s_abort)) break;
-        if (!mbar_wait_abortable(B.k_ready, ph, s_abort)) break;
+        if (!mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           if (ks < nks) {
             const uint32_t off = ((ks >> 2) * kSub + (ks & 3) * 32u) >> 4;
             mma_tf32_ts(tmem + kColS, tmem + kColQlo + ks * 8, khi_k + off, idesc_s, ks > 0);
-            mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, klo_k + off, idesc_s, true);
             mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, khi_k + off, idesc_s, true);
+          }
+        }
+        if (!mbar_wait_abortable(B.k_ready, ph, s_abort)) break;
+        umma::fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          if (ks < nks) {
+            const uint32_t off = ((ks >> 2) * kSub + (ks & 3) * 32u) >> 4;
+            mma_tf32_ts(tmem + kColS, tmem + kColQhi + ks * 8, klo_k + off, idesc_s, true);
           }
         }
         umma::mma_commit(B.s_ready);
@@ -538,16 +547,19 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         umma::fence_after_sync();
         if (!write_output(i - 1, true)) { ok = false; break; }
       }
-      // V: moved to the 32-byte-atom pattern in place, and its lo tile
+      // V lo (the TMA wrote V in the 32-byte-atom pattern already, and the tile itself is the hi operand)
       ok = mbar_wait_abortable(B.v_full, ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      {
+        // (lanes 4-7 of each eight take the two chunks of a 32-byte pair in the other order: rows r and
+        // r + 4 keep a chunk in the same banks)
+        const uint32_t flip = (r >> 2) & 1u;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float4 x[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = *reinterpret_cast<const float4*>(vh + chunk_off(r, half * 8 + j, kSub));
-        store_half_32b<true>(vh, vl, r, half, x, kSub);
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t off = chunk_off32(r, uint32_t(j) ^ flip, kSub);
+          *reinterpret_cast<float4*>(vl + off) = rest4(*reinterpret_cast<const float4*>(vh + off));
+        }
       }
       fence_proxy_async_smem();
       mbar_arrive(B.v_ready);
@@ -613,6 +625,33 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   }
 }
 
+// fp32 [heads, T, d] tensor, box {32, 128, 1}, 128-byte swizzle with 16-byte atoms (the usual one) or with
+// 32-byte atoms (the pattern a tf32 operand whose rows run along the reduction must have).
+int make_map(CUtensorMap* out, const void* base, uint64_t d, uint64_t T, uint64_t heads, bool atom32) {
+  using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                          const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                          CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !p)
+      return CB2_LAUNCH_FAIL;
+    fn = reinterpret_cast<Fn>(p);
+  }
+  const cuuint64_t gdim[3] = {d, T, heads};
+  const cuuint64_t gstride[2] = {d * 4, d * T * 4};
+  const cuuint32_t box[3] = {32, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE,
+            atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+             ? CB2_OK
+             : CB2_LAUNCH_FAIL;
+}
+
 int device_sms() {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -636,10 +675,10 @@ int decayed_tf32_run(const void* q, const void* k, const void* v, void* o, const
                      int T, int dk, int dv, float scale, int* dev_status, cudaStream_t st) {
   const uint64_t heads = uint64_t(B) * H;
   CUtensorMap mq, mk, mv, mo;
-  int rc = umma::make_map_3d(&mq, q, false, dk, T, heads, 32, 128, true);
-  if (rc == CB2_OK) rc = umma::make_map_3d(&mk, k, false, dk, T, heads, 32, 128, true);
-  if (rc == CB2_OK) rc = umma::make_map_3d(&mv, v, false, dv, T, heads, 32, 128, true);
-  if (rc == CB2_OK) rc = umma::make_map_3d(&mo, o, false, dv, T, heads, 32, 128, true);
+  int rc = make_map(&mq, q, dk, T, heads, false);
+  if (rc == CB2_OK) rc = make_map(&mk, k, dk, T, heads, false);
+  if (rc == CB2_OK) rc = make_map(&mv, v, dv, T, heads, true);
+  if (rc == CB2_OK) rc = make_map(&mo, o, dv, T, heads, false);
   if (rc != CB2_OK) return rc;
   if (cudaFuncSetAttribute(decayed_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
