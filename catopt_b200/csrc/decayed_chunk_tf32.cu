@@ -3,7 +3,8 @@
 //   o[t] = sum_{s<=t} g^(t-s) (q_t . k_s) v_s / scale          per (batch, head)
 //
 // (ChunkedDecayModule, catopt_carriers/decayed_lower.py:671-700) evaluated with
-// the state-carry recurrence over 128-row chunks, one CTA per (batch, head):
+// the state-carry recurrence over 128-row chunks, a persistent CTA per SM taking
+// (batch, head) units one after the other:
 //   S    = Q K^T                                   (MMA1, 128 x 128 x dk)
 //   O2   = Q St          St = state before the chunk, [dk x dv]   (MMA4)
 //   P    = tril(S . g^(r-c))                       (score warps, in registers)
@@ -66,7 +67,7 @@ constexpr uint32_t kOffShi = 6 * kTile;
 constexpr uint32_t kOffSlo = kOffShi + 2 * kSubS;
 constexpr uint32_t kOffBars = 7 * kTile;       // 224 KiB of tiles
 constexpr int kNumBars = 16;
-constexpr uint32_t kOffPow = kOffBars + kNumBars * 8;      // g^0 .. g^128
+constexpr uint32_t kOffPow = kOffBars + kNumBars * 8;      // g^0 .. g^31 of the current unit
 constexpr uint32_t kOffMisc = kOffPow + 132 * 4;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
 static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
@@ -170,22 +171,26 @@ __device__ __forceinline__ uint64_t desc_mn(uint32_t tile_addr, int ks) {
 __global__ void __launch_bounds__(kThreads, 1)
 decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                    const float* __restrict__ gamma, int H, int T, int dk, int dv, float inv_scale,
+                    const float* __restrict__ gamma, int H, int T, int dk, int dv, float inv_scale, int n_bh,
                     int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
-  float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
+  float* s_diag = reinterpret_cast<float*>(smem + kOffPow);    // g^0 .. g^31 of the head being scored
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
   const Bars B{bars,     bars + 1, bars + 3,  bars + 4,  bars + 5,  bars + 6,  bars + 7,
                bars + 8, bars + 9, bars + 10, bars + 11, bars + 12, bars + 13, bars + 14, bars + 15};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.x;
-  const float g = gamma[bh % H];
   const int nchunk = (T + kC - 1) / kC;
   const int nks = (dk + 7) / 8;                 // 8-deep steps over the key dimension
+  // Persistent CTA: units blockIdx.x, blockIdx.x + gridDim.x, ... one after the other as ONE stream of
+  // chunks (index t), so that the loads, the output of the last chunk and the first products of the
+  // next unit overlap; only the state restarts at a unit's first chunk.
+  const int n_mine = (n_bh - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+  const int total = n_mine * nchunk;
+  auto unit_of = [&](int t) { return int(blockIdx.x) + (t / nchunk) * int(gridDim.x); };
 
   if (tid == 0) {
     mbar_init(B.q_full, 1);
@@ -211,7 +216,6 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncwarp();
     umma::tmem_alloc(s_tmem, 512);
   }
-  if (tid >= 64 && tid < 64 + 129) s_pow[tid - 64] = powf(g, float(tid - 64));
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
@@ -225,42 +229,47 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tma_prefetch_desc(&map_v);
       umma::tma_prefetch_desc(&map_o);
       int nq = 0, nv = 0, nk0 = 0, nk1 = 0;       // copies issued per barrier
-      auto load_q = [&](int i) {
+      // rows past T arrive as zeros
+      auto load_q = [&](int t) {
+        const int row = (t % nchunk) * kC, bh = unit_of(t);
         mbar_arrive_expect_tx(B.q_full, kTile);
-        umma::tma_load_3d(smem + kOffQ, &map_q, 0, i * kC, bh, B.q_full);
-        umma::tma_load_3d(smem + kOffQ + kSub, &map_q, 32, i * kC, bh, B.q_full);
+        umma::tma_load_3d(smem + kOffQ, &map_q, 0, row, bh, B.q_full);
+        umma::tma_load_3d(smem + kOffQ + kSub, &map_q, 32, row, bh, B.q_full);
         ++nq;
       };
-      auto load_k = [&](int i) {
-        const int b = i & 1;
+      auto load_k = [&](int t) {
+        const int row = (t % nchunk) * kC, bh = unit_of(t);
+        const int b = t & 1;
         unsigned char* dst = smem + (b ? kOffK1 : kOffK0);
         mbar_arrive_expect_tx(&B.k_full[b], kTile);
-        umma::tma_load_3d(dst, &map_k, 0, i * kC, bh, &B.k_full[b]);
-        umma::tma_load_3d(dst + kSub, &map_k, 32, i * kC, bh, &B.k_full[b]);
+        umma::tma_load_3d(dst, &map_k, 0, row, bh, &B.k_full[b]);
+        umma::tma_load_3d(dst + kSub, &map_k, 32, row, bh, &B.k_full[b]);
         if (b) ++nk1; else ++nk0;
       };
-      auto load_v = [&](int i) {
+      auto load_v = [&](int t) {
+        const int row = (t % nchunk) * kC, bh = unit_of(t);
         mbar_arrive_expect_tx(B.v_full, kTile);
-        umma::tma_load_3d(smem + kOffVhi, &map_v, 0, i * kC, bh, B.v_full);
-        umma::tma_load_3d(smem + kOffVhi + kSub, &map_v, 32, i * kC, bh, B.v_full);
+        umma::tma_load_3d(smem + kOffVhi, &map_v, 0, row, bh, B.v_full);
+        umma::tma_load_3d(smem + kOffVhi + kSub, &map_v, 32, row, bh, B.v_full);
         ++nv;
       };
-      // rows past T arrive as zeros
-      load_q(0);
-      load_k(0);
-      load_v(0);
-      if (nchunk > 1) load_k(1);
-      for (int i = 0; i + 1 < nchunk; ++i) {
-        // the Q tile is free once Q_i sits in tensor memory (first chunk) or the output of
-        // chunk i-1, staged there, has left
-        if (!(i == 0 ? mbar_wait_abortable(B.q_ready, 0, s_abort)
-                     : mbar_wait_abortable(B.qtile_free, (i - 1) & 1, s_abort)))
+      if (total > 0) {
+        load_q(0);
+        load_k(0);
+        load_v(0);
+      }
+      if (total > 1) load_k(1);
+      for (int t = 0; t + 1 < total; ++t) {
+        // the Q tile is free once Q_t sits in tensor memory (first chunk) or the output of
+        // chunk t-1, staged there, has left
+        if (!(t == 0 ? mbar_wait_abortable(B.q_ready, 0, s_abort)
+                     : mbar_wait_abortable(B.qtile_free, (t - 1) & 1, s_abort)))
           break;
-        load_q(i + 1);
-        // chunk i done: V and this chunk's K tile are free
-        if (!mbar_wait_abortable(B.c_done, i & 1, s_abort)) break;
-        load_v(i + 1);
-        if (i + 2 < nchunk) load_k(i + 2);
+        load_q(t + 1);
+        // chunk t done: V and this chunk's K tile are free
+        if (!mbar_wait_abortable(B.c_done, t & 1, s_abort)) break;
+        load_v(t + 1);
+        if (t + 2 < total) load_k(t + 2);
       }
       if (*s_abort) {
         // leaving early: let the copies in flight land first (bounded)
@@ -284,15 +293,17 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint64_t klo_k = desc_k(smem_u32(smem + kOffKlo), 0, kSub), klo_m = desc_mn(smem_u32(smem + kOffKlo), 0);
       const uint64_t shi_k = desc_k(smem_u32(smem + kOffShi), 0, kSubS), slo_k = desc_k(smem_u32(smem + kOffSlo), 0, kSubS);
       const uint64_t vhi_m = desc_mn(smem_u32(smem + kOffVhi), 0), vlo_m = desc_mn(smem_u32(smem + kOffVlo), 0);
-      for (int i = 0; i < nchunk; ++i) {
-        const uint32_t ph = i & 1;
+      int ci = 0;                                // chunk within the unit
+      uint32_t k2_phase = 0;                     // k2_ready skips a unit's last chunk, so it keeps its own count
+      for (int t = 0; t < total; ++t, ci = (ci + 1 == nchunk ? 0 : ci + 1)) {
+        const uint32_t ph = t & 1;
         const uint64_t khi_k = desc_k(k0 + ph * 2 * kTile, 0, kSub), khi_m = desc_mn(k0 + ph * 2 * kTile, 0);
         // K' hi and lo side by side as one 128-wide operand: hi | lo for even chunks, lo | hi for odd ones
         const uint64_t kboth_m = ph ? klo_m : khi_m;
         // MMA1: S = Q K^T.  The two products against K itself start as soon as Q is in tensor memory
         // and the K tile has landed; the one against K lo follows when the warps have built that tile.
         if (!mbar_wait_abortable(B.q_ready, ph, s_abort)) break;
-        if (!mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort)) break;
+        if (!mbar_wait_abortable(&B.k_full[ph], (t >> 1) & 1, s_abort)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -314,7 +325,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         umma::mma_commit(B.s_ready);
         // MMA4: O2 = Q St
         if (!mbar_wait_abortable(B.st_ready, ph, s_abort)) break;
-        if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
+        if (t > 0 && !mbar_wait_abortable(B.o_free, (t - 1) & 1, s_abort)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -325,11 +336,12 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mma_tf32_ts(tmem + kColO2, tmem + kColQhi + ks * 8, shi_k + off, idesc_o2, true);
           }
         }
-        // MMA3: D = V^T K' (not needed after the last chunk); lands where Q was.  Issued before
+        // MMA3: D = V^T K' (not needed after a unit's last chunk); lands where Q was.  Issued before
         // MMA2 so that the tensor pipe has work while the score warps build P.
-        if (i + 1 < nchunk) {
+        if (ci + 1 < nchunk) {
           if (!mbar_wait_abortable(B.v_ready, ph, s_abort)) break;
-          if (!mbar_wait_abortable(B.k2_ready, ph, s_abort)) break;
+          if (!mbar_wait_abortable(B.k2_ready, k2_phase, s_abort)) break;
+          k2_phase ^= 1;
           umma::fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < 16; ++ks) {
@@ -357,7 +369,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   } else if (warp < 6) {
     // ---------------------------------------------------------------- operand / state warps
     // Per chunk: read the state increment of the chunk before, put Q into tensor memory, build half of
-    // K lo (-> MMA1 can start), carry the state (-> MMA4), rescale K once MMA1 is done (-> MMA3).
+    // K lo (-> MMA1 can finish), carry the state (-> MMA4), rescale K once MMA1 is done (-> MMA3).
     const int q4 = warp & 3;
     const int r = q4 * 32 + lane;                // row of every tile this thread owns
     const uint32_t lane_base = tmem + (uint32_t(q4 * 32) << 16);
@@ -365,21 +377,29 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     unsigned char* kl = smem + kOffKlo;
     unsigned char* sh = smem + kOffShi;
     unsigned char* sl = smem + kOffSlo;
-    const float w = s_pow[kC - 1 - r];           // decay of key r to the end of the chunk
-    const float gC = s_pow[kC];
+    float w = 0.f, gC = 0.f;                     // g^(127-r): decay of key r to the end of the chunk; g^128
     bool ok = true;
-    for (int i = 0; ok && i < nchunk; ++i) {
-      const uint32_t ph = i & 1;
+    int ci = 0;
+    for (int t = 0; ok && t < total; ++t, ci = (ci + 1 == nchunk ? 0 : ci + 1)) {
+      const uint32_t ph = t & 1;
       unsigned char* kh = smem + (ph ? kOffK1 : kOffK0);
+      if (ci == 0) {
+        const float g = gamma[unit_of(t) % H];
+        w = powf(g, float(kC - 1 - r));
+        gC = powf(g, float(kC));
+      }
+      // every MMA of the chunk before is done: K lo and the Q columns are free
+      if (t > 0) {
+        ok = mbar_wait_abortable(B.c_done, (t - 1) & 1, s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        umma::fence_after_sync();
+      }
       // D of the chunk before: two 64-column halves (products with K' hi and K' lo) to be added.  A
       // 64-row accumulator keeps row n in lane (n % 16) of lane quarter n / 16.  Read first: Q goes
       // into the same columns.
       float d[64];
-      if (i > 0) {
-        ok = mbar_wait_abortable(B.c_done, (i - 1) & 1, s_abort);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        umma::fence_after_sync();
+      if (ci > 0) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t a[32], b[32];
@@ -412,9 +432,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tmem_wait_st();
       umma::fence_before_sync();
       mbar_arrive(B.q_ready);
-      // K lo, columns 0-31 (the K tile itself is the hi operand; the other warpgroup does columns
-      // 32-63: this is the one step between two chunks during which the tensor pipe has nothing to do)
-      ok = mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort);
+      // K lo, columns 0-31 (the K tile itself is the hi operand; the other warpgroup does columns 32-63)
+      ok = mbar_wait_abortable(&B.k_full[ph], (t >> 1) & 1, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
 #pragma unroll
@@ -424,8 +443,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
-      // state: St <- g^128 St + D^T (zero before the first chunk); the hi tile is the fp32 state
-      if (i == 0) {
+      // state: St <- g^128 St + D^T (zero before a unit's first chunk); the hi tile is the fp32 state
+      if (ci == 0) {
         for (int j = 0; j < 16; ++j)
           *reinterpret_cast<float4*>(sh + ((tid - 64) * 16 + j) * 16) = make_float4(0.f, 0.f, 0.f, 0.f);   // hi and lo
       } else if (lane < 16) {
@@ -443,7 +462,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       fence_proxy_async_smem();
       mbar_arrive(B.st_ready);
       // K' = K g^(127-r), moved to the 32-byte-atom pattern, once MMA1 has read K
-      if (i + 1 < nchunk) {
+      if (ci + 1 < nchunk) {
         ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -463,8 +482,8 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else {
     // ---------------------------------------------------------------- score / output warps
-    // Per chunk: the other half of K lo, the output of the chunk before (-> MMA4 may overwrite O2), V
-    // into its MMA layout with its lo tile (-> MMA3), then P from S (-> MMA2).
+    // Per chunk: the other half of K lo, the output of the chunk before (-> MMA4 may overwrite O2), V lo
+    // (-> MMA3), then P from S (-> MMA2).
     const int q4 = warp & 3;
     const int r = q4 * 32 + lane;
     const int wt = tid - 192;                    // 0..127 among these warps
@@ -473,21 +492,22 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     unsigned char* vh = smem + kOffVhi;
     unsigned char* vl = smem + kOffVlo;
     unsigned char* ot = smem + kOffQ;            // the output is staged where Q was
-    const float fcross = s_pow[r + 1];
+    float fcross = 0.f;                          // g^(r+1)
     float gp[32];                                // g^(31-j)
-#pragma unroll
-    for (int j = 0; j < 32; ++j) gp[j] = s_pow[31 - j];
+    float acb[3] = {0.f, 0.f, 0.f};              // g^(r - 32 cb - 31) for the key blocks before the diagonal one
     uint32_t wg_phase = 0;
     bool ok = true;
-    // o = (O1 + g^(r+1) O2) / scale of chunk `c`, staged as a swizzled tile where Q was (the next Q is
-    // in tensor memory by then) and stored by TMA
-    auto write_output = [&](int c, bool more) -> bool {
-      if (wt == 0) bulk_wait_read<0>();          // the previous store has read the staging tile
+    auto wg_barrier = [&]() -> bool {
       mbar_arrive(B.wg_sync);
       bool fine = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
       wg_phase ^= 1;
-      fine = __all_sync(0xffffffffu, fine);
-      if (!fine) return false;
+      return __all_sync(0xffffffffu, fine);
+    };
+    // o = (O1 + g^(r+1) O2) / scale of chunk `row / 128` of unit `bh`, staged as a swizzled tile where Q
+    // was (the next Q is in tensor memory by then) and stored by TMA
+    auto write_output = [&](int row, int bh, bool more) -> bool {
+      if (wt == 0) bulk_wait_read<0>();          // the previous store has read the staging tile
+      if (!wg_barrier()) return false;
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t a[32], b[32];
@@ -507,14 +527,10 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::fence_before_sync();
       mbar_arrive(B.o_free);
       fence_proxy_async_smem();
-      mbar_arrive(B.wg_sync);
-      fine = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
-      wg_phase ^= 1;
-      fine = __all_sync(0xffffffffu, fine);
-      if (!fine) return false;
+      if (!wg_barrier()) return false;
       if (wt == 0) {
-        umma::tma_store_3d(&map_o, 0, c * kC, bh, ot);
-        if (dv > 32) umma::tma_store_3d(&map_o, 32, c * kC, bh, ot + kSub);
+        umma::tma_store_3d(&map_o, 0, row, bh, ot);
+        if (dv > 32) umma::tma_store_3d(&map_o, 32, row, bh, ot + kSub);
         bulk_commit();
         if (more) {
           bulk_wait_read<0>();
@@ -523,10 +539,12 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       return true;
     };
-    for (int i = 0; ok && i < nchunk; ++i) {
-      const uint32_t ph = i & 1;
+    int ci = 0, prev_row = 0, prev_bh = 0;
+    for (int t = 0; ok && t < total; ++t, ci = (ci + 1 == nchunk ? 0 : ci + 1)) {
+      const uint32_t ph = t & 1;
+      const int bh = unit_of(t);
       // K lo, columns 32-63 (every MMA of the chunk before is done: the loop ends on that wait)
-      ok = mbar_wait_abortable(&B.k_full[ph], (i >> 1) & 1, s_abort);
+      ok = mbar_wait_abortable(&B.k_full[ph], (t >> 1) & 1, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       {
@@ -540,12 +558,25 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
       // output of the chunk before, once this chunk's Q has left its tile
-      if (i > 0) {
+      if (t > 0) {
         ok = mbar_wait_abortable(B.q_ready, ph, s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         umma::fence_after_sync();
-        if (!write_output(i - 1, true)) { ok = false; break; }
+        if (!write_output(prev_row, prev_bh, true)) { ok = false; break; }
+      }
+      prev_row = ci * kC;
+      prev_bh = bh;
+      if (ci == 0) {
+        // a new unit: its rate's powers (after the output above, which still belongs to the unit before)
+        const float g = gamma[bh % H];
+        if (wt < 32) s_diag[wt] = powf(g, float(wt));
+        fcross = powf(g, float(r + 1));
+#pragma unroll
+        for (int cb = 0; cb < 3; ++cb) acb[cb] = cb < q4 ? powf(g, float(r - 32 * cb - 31)) : 0.f;
+        if (!wg_barrier()) { ok = false; break; }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) gp[j] = s_diag[31 - j];
       }
       // V lo (the TMA wrote V in the 32-byte-atom pattern already, and the tile itself is the hi operand)
       ok = mbar_wait_abortable(B.v_full, ph, s_abort);
@@ -583,7 +614,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         umma::tmem_wait_ld();
         if (cb < q4) {
           // all keys visible: g^(r-c) = g^(r - 32 cb - 31) g^(31-j)
-          const float a = s_pow[r - 32 * cb - 31];
+          const float a = cb == 0 ? acb[0] : (cb == 1 ? acb[1] : acb[2]);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float p = __uint_as_float(v[j]) * (a * gp[j]);
@@ -594,7 +625,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int e = lane - j;             // r - c on the diagonal block
-            const float p = e >= 0 ? __uint_as_float(v[j]) * s_pow[e] : 0.f;
+            const float p = e >= 0 ? __uint_as_float(v[j]) * s_diag[e] : 0.f;
             v[j] = __float_as_uint(p);
             lo[j] = __float_as_uint(tf32_rest(p));
           }
@@ -611,7 +642,7 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!ok) break;
       umma::fence_after_sync();
     }
-    if (ok) write_output(nchunk - 1, false);
+    if (ok && total > 0) write_output(prev_row, prev_bh, false);
     if (wt == 0) bulk_wait_all<0>();
   }
   __syncwarp();
@@ -683,9 +714,10 @@ int decayed_tf32_run(const void* q, const void* k, const void* v, void* o, const
   if (cudaFuncSetAttribute(decayed_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
-  (void)device_sms;
-  decayed_tf32_kernel<<<unsigned(heads), kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dk, dv,
-                                                                     1.0f / scale, dev_status);
+  // one persistent CTA per SM walks its units one after the other
+  const unsigned grid = unsigned(std::min<uint64_t>(heads, uint64_t(device_sms())));
+  decayed_tf32_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, gamma, H, T, dk, dv, 1.0f / scale,
+                                                          int(heads), dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }
