@@ -190,7 +190,6 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   // next unit overlap; only the state restarts at a unit's first chunk.
   const int n_mine = (n_bh - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
   const int total = n_mine * nchunk;
-  auto unit_of = [&](int t) { return int(blockIdx.x) + (t / nchunk) * int(gridDim.x); };
 
   if (tid == 0) {
     mbar_init(B.q_full, 1);
@@ -230,15 +229,24 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma::tma_prefetch_desc(&map_o);
       int nq = 0, nv = 0, nk0 = 0, nk1 = 0;       // copies issued per barrier
       // rows past T arrive as zeros
-      auto load_q = [&](int t) {
-        const int row = (t % nchunk) * kC, bh = unit_of(t);
+      // each of the three load streams keeps its own (chunk, unit) position: no division per load
+      struct Pos { int ci, bh; };
+      const int step = int(gridDim.x);
+      auto advance = [&](Pos& p) {
+        if (++p.ci == nchunk) { p.ci = 0; p.bh += step; }
+      };
+      Pos pq{0, int(blockIdx.x)}, pk{0, int(blockIdx.x)}, pv{0, int(blockIdx.x)};
+      auto load_q = [&](int) {
+        const int row = pq.ci * kC, bh = pq.bh;
+        advance(pq);
         mbar_arrive_expect_tx(B.q_full, kTile);
         umma::tma_load_3d(smem + kOffQ, &map_q, 0, row, bh, B.q_full);
         umma::tma_load_3d(smem + kOffQ + kSub, &map_q, 32, row, bh, B.q_full);
         ++nq;
       };
       auto load_k = [&](int t) {
-        const int row = (t % nchunk) * kC, bh = unit_of(t);
+        const int row = pk.ci * kC, bh = pk.bh;
+        advance(pk);
         const int b = t & 1;
         unsigned char* dst = smem + (b ? kOffK1 : kOffK0);
         mbar_arrive_expect_tx(&B.k_full[b], kTile);
@@ -246,8 +254,9 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         umma::tma_load_3d(dst + kSub, &map_k, 32, row, bh, &B.k_full[b]);
         if (b) ++nk1; else ++nk0;
       };
-      auto load_v = [&](int t) {
-        const int row = (t % nchunk) * kC, bh = unit_of(t);
+      auto load_v = [&](int) {
+        const int row = pv.ci * kC, bh = pv.bh;
+        advance(pv);
         mbar_arrive_expect_tx(B.v_full, kTile);
         umma::tma_load_3d(smem + kOffVhi, &map_v, 0, row, bh, B.v_full);
         umma::tma_load_3d(smem + kOffVhi + kSub, &map_v, 32, row, bh, B.v_full);
@@ -379,12 +388,13 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     unsigned char* sl = smem + kOffSlo;
     float w = 0.f, gC = 0.f;                     // g^(127-r): decay of key r to the end of the chunk; g^128
     bool ok = true;
-    int ci = 0;
-    for (int t = 0; ok && t < total; ++t, ci = (ci + 1 == nchunk ? 0 : ci + 1)) {
+    int ci = 0, bh = int(blockIdx.x);
+    for (int t = 0; ok && t < total; ++t, ++ci) {
+      if (ci == nchunk) { ci = 0; bh += int(gridDim.x); }
       const uint32_t ph = t & 1;
       unsigned char* kh = smem + (ph ? kOffK1 : kOffK0);
       if (ci == 0) {
-        const float g = gamma[unit_of(t) % H];
+        const float g = gamma[bh % H];
         w = powf(g, float(kC - 1 - r));
         gC = powf(g, float(kC));
       }
@@ -539,10 +549,10 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       return true;
     };
-    int ci = 0, prev_row = 0, prev_bh = 0;
-    for (int t = 0; ok && t < total; ++t, ci = (ci + 1 == nchunk ? 0 : ci + 1)) {
+    int ci = 0, bh = int(blockIdx.x), prev_row = 0, prev_bh = 0;
+    for (int t = 0; ok && t < total; ++t, ++ci) {
+      if (ci == nchunk) { ci = 0; bh += int(gridDim.x); }
       const uint32_t ph = t & 1;
-      const int bh = unit_of(t);
       // K lo, columns 32-63 (every MMA of the chunk before is done: the loop ends on that wait)
       ok = mbar_wait_abortable(&B.k_full[ph], (t >> 1) & 1, s_abort);
       ok = __all_sync(0xffffffffu, ok);
