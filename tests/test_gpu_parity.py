@@ -218,6 +218,24 @@ def test_decayed_fp32_tensor_core_path_vs_fp64(dev, B, H, T, dk, dv, C, scale):
     assert rel_to_max(out, _decayed_fp64(q, k, v, gamma, scale)) <= FP32_TOL
 
 
+@pytest.mark.parametrize("B,H,T,d", [(10, 32, 200, 64), (40, 8, 128, 32), (5, 64, 392, 48)])
+def test_decayed_fp32_tensor_core_path_streams_several_units_per_cta(dev, B, H, T, d):
+    """More units than SMs: a persistent CTA walks several units as one stream of chunks, so the state
+    must restart, the rate must change and a ragged last chunk must be clipped at every unit boundary."""
+    from catopt_b200 import ops
+
+    gen = torch.Generator(device="cuda").manual_seed(T + d)
+    q, k, v = (torch.randn(B, H, T, d, device=dev, generator=gen) / math.sqrt(d) for _ in range(3))
+    gamma = torch.tensor([0.6 + 0.399 * h / (H - 1) for h in range(H)], dtype=torch.float32, device=dev)
+    out = ops.decayed_chunk_fwd(q, k, v, gamma, 8, 1.0)
+    ops.check_device_status(dev)
+    assert rel_to_max(out, _decayed_fp64(q, k, v, gamma, 1.0)) <= FP32_TOL
+    # a unit's result does not depend on which units share its CTA (enough units for the same kernel)
+    nb = -(-24 // H)
+    part = ops.decayed_chunk_fwd(q[B - nb:].contiguous(), k[B - nb:].contiguous(), v[B - nb:].contiguous(), gamma, 8, 1.0)
+    assert torch.equal(part, out[B - nb:])
+
+
 def test_decayed_fp32_tensor_core_path_takes_every_rate(dev):
     """Rates for which rescaled keys would overflow or vanish (0, 0.05, negative, 1): the kernel decays
     scores by g^(r-c) directly, so it needs no second formulation."""
