@@ -110,6 +110,11 @@ SIGNATURES: dict[str, tuple] = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
          C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
     ),
+    "cb2_om_bias_fwd": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
+         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
+    ),
     "cb2_om_step_scratch_bytes": (C.c_size_t, [C.c_int] * 5),
     "cb2_om_step": (
         C.c_int,

@@ -138,6 +138,16 @@ __device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile in
   }
 }
 
+// ---- additive attention bias -------------------------------------------------
+// fp32 bias added to the scaled scores of softmax attention (torch's attn_mask in its additive
+// form, -inf = key hidden): element (b, h, t, j) at p[b sb + h sh + t sq + j], strides in
+// elements, 0 for a broadcast axis; p == nullptr: no bias.
+struct OmBias {
+  const float* p;
+  long long sb, sh, sq;
+  int H;
+};
+
 // ---- bulk asynchronous copies (TMA engine, untiled form) -------------------
 // global -> shared, completion counted in bytes on `bar`.  Both addresses must
 // be 16-byte aligned and `bytes` a multiple of 16.

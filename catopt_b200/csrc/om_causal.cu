@@ -21,7 +21,7 @@ bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dt
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
                      int dk, int dv, float scale, int causal, int key_offset, const float* m_in,
                      const float* l_in, const float* a_in, float* m_out, float* l_out, float* a_out,
-                     int* dev_status, cudaStream_t st);
+                     const OmBias& bias, int* dev_status, cudaStream_t st);
 
 namespace {
 
@@ -49,7 +49,7 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
                  void* __restrict__ o, int Tq, int Tk, int dk, int dv, float scale, int causal,
                  int key_offset, const float* __restrict__ m_in, const float* __restrict__ l_in,
                  const float* __restrict__ a_in, float* __restrict__ m_out, float* __restrict__ l_out,
-                 float* __restrict__ a_out, int split_len) {
+                 float* __restrict__ a_out, int split_len, const OmBias bias) {
   extern __shared__ __align__(16) float sm[];
   constexpr int kLd = kBlk + 4;
   float* Qt = sm;
@@ -122,6 +122,8 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
       for (int j = 0; j < 4; ++j) {
         const int c = k0 + tx * 4 + j;
         if ((causal && c + key_offset > t) || c >= k_lim) s[i][j] = -INFINITY;
+        else if (bias.p && t < Tq)       // an explicit attention mask in additive form (scores are scaled already)
+          s[i][j] += __ldg(bias.p + (bh / bias.H) * bias.sb + (bh % bias.H) * bias.sh + (long long)t * bias.sq + c);
         mb = fmaxf(mb, s[i][j]);
       }
 #pragma unroll
@@ -433,13 +435,9 @@ int om_step_splits(int B, int H, int Tq, int Tk) {
   return z < 2 ? 1 : int(z);
 }
 
-}  // namespace
-}  // namespace cb2
-
-extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq,
-                          int Tk, int dk, int dv, float scale, int causal, int dtype, int* dev_status,
-                          void* stream) {
-  using namespace cb2;
+// Softmax attention of whole sequences, with or without an additive bias.
+int om_fwd_impl(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk, int dk, int dv,
+                float scale, int causal, int dtype, const OmBias& bias, int* dev_status, void* stream) {
   if (!q || !k || !v || !o) return CB2_NULL_PTR;
   if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0) return CB2_BAD_SHAPE;
   if (dk > kMaxD || dv > kMaxD) return CB2_BAD_SHAPE;
@@ -450,24 +448,44 @@ extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, 
   if (om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) && aligned16(k) &&
       aligned16(v) && aligned16(o))
     return om_causal_tc_run(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr,
-                            nullptr, nullptr, nullptr, dev_status, st);
+                            nullptr, nullptr, nullptr, bias, dev_status, st);
   if (dtype == CB2_BF16) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr, nullptr,
-                                                               nullptr, nullptr, 0);
+                                                               nullptr, nullptr, 0, bias);
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, o, Tq, Tk, dk, dv, scale, causal ? 1 : 0, 0, nullptr, nullptr, nullptr, nullptr,
-                                                               nullptr, nullptr, 0);
+                                                               nullptr, nullptr, 0, bias);
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }
   CB2_LAUNCH_CHECK();
   return CB2_OK;
+}
+
+}  // namespace
+}  // namespace cb2
+
+extern "C" int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq,
+                          int Tk, int dk, int dv, float scale, int causal, int dtype, int* dev_status,
+                          void* stream) {
+  return cb2::om_fwd_impl(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, causal, dtype, cb2::OmBias{nullptr, 0, 0, 0, 1},
+                          dev_status, stream);
+}
+
+extern "C" int cb2_om_bias_fwd(const void* q, const void* k, const void* v, void* o, const float* bias,
+                               long long bias_stride_b, long long bias_stride_h, long long bias_stride_q, int B,
+                               int H, int Tq, int Tk, int dk, int dv, float scale, int causal, int dtype,
+                               int* dev_status, void* stream) {
+  if (!bias) return CB2_NULL_PTR;
+  if (bias_stride_b < 0 || bias_stride_h < 0 || bias_stride_q < 0) return CB2_BAD_SHAPE;
+  return cb2::om_fwd_impl(q, k, v, o, B, H, Tq, Tk, dk, dv, scale, causal, dtype,
+                          cb2::OmBias{bias, bias_stride_b, bias_stride_h, bias_stride_q, H}, dev_status, stream);
 }
 
 extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int H,
@@ -526,7 +544,7 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
   if (Tq > kDecRows && om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) &&
       aligned16(k) && aligned16(v) && aligned16(a_out) && (!a_in || aligned16(a_in)))
     return om_causal_tc_run(q, k, v, nullptr, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, key_offset, m_in, l_in,
-                            a_in, m_out, l_out, a_out, dev_status, st);
+                            a_in, m_out, l_out, a_out, OmBias{nullptr, 0, 0, 0, 1}, dev_status, st);
   // few query tiles: cut the keys over extra CTAs, then fold the partial carriers
   int Z = om_step_splits(B, H, Tq, Tk);
   if (Z > 1 && (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) ||
@@ -549,13 +567,13 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
-                                                               key_offset, mi, li, ai, mo, lo, ao, split_len);
+                                                               key_offset, mi, li, ai, mo, lo, ao, split_len, OmBias{nullptr, 0, 0, 0, 1});
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
-                                                              key_offset, mi, li, ai, mo, lo, ao, split_len);
+                                                              key_offset, mi, li, ai, mo, lo, ao, split_len, OmBias{nullptr, 0, 0, 0, 1});
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }

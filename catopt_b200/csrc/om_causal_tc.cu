@@ -52,7 +52,8 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                     int Tq, int Tk, int dk, int dv, int n_bh, int causal, float scale_log2e, int key_offset,
                     const float* __restrict__ m_in, const float* __restrict__ l_in, const float* __restrict__ a_in,
-                    float* __restrict__ m_out, float* __restrict__ l_out, float* __restrict__ a_out, int* dev_status) {
+                    float* __restrict__ m_out, float* __restrict__ l_out, float* __restrict__ a_out,
+                    const OmBias bias, int* dev_status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -202,6 +203,20 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int c = 0; c < 32; ++c)
             if (cb * 32 + c > lim) sv[cb][c] = 0xff800000u;
+      }
+      // additive bias (an explicit attention mask): scores here are unscaled, so the bias goes in divided
+      // by the scale; -inf hides the key like the causal mask does
+      if (bias.p) {
+        const float* brow = bias.p + (bh / bias.H) * bias.sb + (bh % bias.H) * bias.sh +
+                            (long long)min(tq, Tq - 1) * bias.sq + k0;
+        const float unscale = kLog2e / scale_log2e;
+        const int nvis = min(kQ, Tk - k0);
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb)
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (cb * 32 + c < nvis)
+              sv[cb][c] = __float_as_uint(fmaf(__ldg(brow + cb * 32 + c), unscale, __uint_as_float(sv[cb][c])));
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -363,7 +378,7 @@ bool om_causal_tc_supported(int B, int H, int Tq, int Tk, int dk, int dv, int dt
 int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B, int H, int Tq, int Tk,
                      int dk, int dv, float scale, int causal, int key_offset, const float* m_in,
                      const float* l_in, const float* a_in, float* m_out, float* l_out, float* a_out,
-                     int* dev_status, cudaStream_t st) {
+                     const OmBias& bias, int* dev_status, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mo;
   const uint64_t bh = uint64_t(B) * H;
   int rc = umma::make_map_3d(&mq, q, true, dk, Tq, bh, 64, 128, true);
@@ -380,7 +395,7 @@ int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B
   const unsigned grid = unsigned(((Tq + kQ - 1) / kQ) * bh);
   om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh), causal,
                                                          scale * 1.4426950408889634f, key_offset, m_in, l_in, a_in,
-                                                         m_out, l_out, a_out, dev_status);
+                                                         m_out, l_out, a_out, bias, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }

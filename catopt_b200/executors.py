@@ -237,9 +237,11 @@ def decayed_whole_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ga
 
 
 def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale: float,
-                          causal: bool = True) -> torch.Tensor | None:
+                          causal: bool = True, mask: torch.Tensor | None = None) -> torch.Tensor | None:
     """Softmax attention (causal by default) of ``q [..., Tq, d]`` over key/value
-    blocks joined along the key axis, through ``cb2_om_fwd``; ``None`` for fp64."""
+    blocks joined along the key axis, through ``cb2_om_fwd``; ``None`` for fp64.
+    ``mask``: an explicit attention mask (bool keep-mask or float bias, broadcastable to
+    ``[..., Tq, Tk]``) added to the scaled scores through ``cb2_om_bias_fwd``."""
     if not q.is_cuda:
         raise B200Error("causal softmax executor runs on CUDA tensors only (no CPU fallback)")
     if q.dtype not in (torch.float32, torch.bfloat16):
@@ -250,7 +252,16 @@ def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale
     H = lead[-1] if lead else 1
     q4, k4, v4 = (t.expand(*lead, *t.shape[-2:]).reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous()
                   for t in (q, k, v))
-    out = ops.om_causal_fwd(q4, k4, v4, scale, causal=causal)
+    if mask is None:
+        out = ops.om_causal_fwd(q4, k4, v4, scale, causal=causal)
+    else:
+        bias = ops.attn_bias(mask)
+        if bias.dim() > 2 and any(s != 1 for s in bias.shape[:-2]):
+            # leading axes line up with q's: make them the same [-1, H] pair (broadcast axes stay unmaterialised)
+            bias = bias.expand(*lead, *bias.shape[-2:]).reshape(-1, H, *bias.shape[-2:])
+        else:
+            bias = bias.reshape(bias.shape[-2:]) if bias.dim() >= 2 else bias
+        out = ops.om_bias_fwd(q4, k4, v4, bias, scale, causal=causal)
     return out.reshape(*lead, out.shape[-2], out.shape[-1])
 
 

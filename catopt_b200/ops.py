@@ -254,6 +254,55 @@ def om_causal_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
     return out
 
 
+def attn_bias(mask: torch.Tensor) -> torch.Tensor:
+    """An attention mask in additive fp32 form, the reference's ``attnbias`` coercion
+    (catopt_carriers/om.py:1036-1050): a floating mask is the bias, a bool keep-mask is
+    0 where True and -inf where False."""
+    if mask.dtype == torch.bool:
+        return torch.zeros(mask.shape, dtype=torch.float32, device=mask.device).masked_fill_(~mask, float("-inf"))
+    return mask.float()
+
+
+def om_bias_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.Tensor, scale: float | None = None,
+                out: torch.Tensor | None = None, causal: bool = False) -> torch.Tensor:
+    """Softmax attention with an explicit mask: ``softmax(scale * q k^T + bias) v`` —
+    the carrier ``om_apply(om_elem(add(scores, attnbias(m)), v))`` of the reference's
+    masked sdpa law (om.py:1313-1362).  ``bias`` is fp32 (see :func:`attn_bias` for bool
+    masks) and broadcasts to ``[B,H,Tq,Tk]``; broadcast axes are not materialised."""
+    require_cuda(q, k, v, out)
+    require_device(bias)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise B200Error("om_bias_fwd takes rank-4 q, k, v")
+    B, H, Tq, dk = q.shape
+    if k.shape[:2] != (B, H) or k.shape[3] != dk or v.shape[:3] != k.shape[:3]:
+        raise B200Error("om_bias_fwd: q [B,H,Tq,dk], k [B,H,Tk,dk], v [B,H,Tk,dv]")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise B200Error("q, k, v must share one dtype")
+    Tk, dv = k.shape[2], v.shape[3]
+    if bias.dtype != torch.float32 or bias.dim() > 4:
+        raise B200Error("bias must be float32 of rank <= 4")
+    bb = bias.reshape(1) if bias.dim() == 0 else bias
+    if bb.shape[-1] == 1 and Tk > 1:
+        bb = bb.expand(*bb.shape[:-1], Tk)            # one value for every key of a row
+    if Tk > 1 and bb.stride(-1) != 1:
+        bb = bb.contiguous()                          # the kernel reads a row's keys contiguously
+    try:
+        b4 = torch.broadcast_to(bb, (B, H, Tq, Tk))   # the other broadcast axes keep stride 0
+    except RuntimeError as e:
+        raise B200Error(f"bias of shape {tuple(bias.shape)} does not broadcast to {(B, H, Tq, Tk)}") from e
+    if any(st < 0 for st in b4.stride()):
+        raise B200Error("bias with negative strides")
+    sc = float(scale) if scale is not None else 1.0 / float(dk) ** 0.5
+    if out is None:
+        out = torch.empty(B, H, Tq, dv, dtype=q.dtype, device=q.device)
+    rc = _lib.load().cb2_om_bias_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b4.data_ptr(),
+                                     b4.stride(0), b4.stride(1), b4.stride(2), B, H, Tq, Tk, dk, dv, sc,
+                                     1 if causal else 0, dtype_code(q.dtype),
+                                     device_status(q.device).data_ptr(), stream_ptr())
+    check(rc, "cb2_om_bias_fwd")
+    return out
+
+
 def om_empty_state(shape: tuple, dv: int, device: torch.device | str) -> tuple:
     """The identity carrier ``(m, l, a) = (-inf, 0, 0)`` for queries of leading shape
     ``shape = (B, H, Tq)`` (``om_empty_state``, catopt_carriers/om_lower.py:871-893);

@@ -590,13 +590,50 @@ def _scaled_scores(t: Any) -> tuple | None:
     if not isinstance(t, Op):
         return None
     if t.op == "matmul" and len(t.args) == 2 and _is_swap_last_two(t.args[1]):
-        return t.args[0], t.args[1].args[0], 1.0
+        q = t.args[0]
+        if isinstance(q, Op) and q.op == "mul" and len(q.args) == 2:
+            # (q * fill(q, scale)) @ k^T: the spelling of the masked sdpa law (om.py:1325-1331)
+            for a, f in (q.args, q.args[::-1]):
+                if isinstance(f, Op) and f.op == "fill" and len(f.args) == 1 and f.args[0] == a \
+                        and isinstance(f.attrs.get("value"), (int, float)):
+                    return a, t.args[1].args[0], float(f.attrs["value"])
+        return q, t.args[1].args[0], 1.0
     if t.op == "om_decayed" and len(t.args) == 3 and _is_swap_last_two(t.args[2]):
         q, f = t.args[0], t.args[1]
         if isinstance(f, Op) and f.op == "fill" and len(f.args) == 1 and f.args[0] == q \
                 and isinstance(f.attrs.get("value"), (int, float)):
             return q, t.args[2].args[0], float(f.attrs["value"])
     return None
+
+
+def _score_blocks(t: Any) -> list | None:
+    """Scores over one or more key blocks: a single block or ``concat(..., dim=-1)`` of blocks ->
+    ``[(q, k, scale), ...]`` in key order."""
+    if isinstance(t, Op) and t.op == "concat" and t.attrs.get("dim") == -1 and len(t.args) >= 1:
+        out = [_scaled_scores(a) for a in t.args]
+        return None if any(b is None for b in out) else out
+    one = _scaled_scores(t)
+    return None if one is None else [one]
+
+
+def _bias_piece(t: Any, memo: dict) -> tuple | None:
+    """``attnbias(m)`` or a column range of one -> ``(base, start, length | None)`` (None: all columns)."""
+    if isinstance(t, Op) and t.op == "attnbias" and len(t.args) == 1:
+        return t, 0, None
+    r = _range_of(t, -1, memo)
+    if r is not None and isinstance(r[0], Op) and r[0].op == "attnbias" and len(r[0].args) == 1:
+        return r[0], r[1], r[2]
+    return None
+
+
+def _split_bias(sterm: Any, memo: dict) -> tuple:
+    """``add(scores, <attention bias>)`` in either order -> (scores, bias piece); else (sterm, None)."""
+    if isinstance(sterm, Op) and sterm.op == "add" and len(sterm.args) == 2:
+        for a, b in (sterm.args, sterm.args[::-1]):
+            bp = _bias_piece(b, memo)
+            if bp is not None:
+                return a, bp
+    return sterm, None
 
 
 def om_causal_plan(root: Any) -> dict | None:
@@ -613,19 +650,27 @@ def om_causal_plan(root: Any) -> dict | None:
     before block i).  Leaves are read left to right = key order; every block must
     share q and the scale and appear once; all masks slice ONE ``cmask``, whose
     offset ``off`` (key j visible to query t iff ``j + off <= t``, om.py:1023-1029)
-    is part of the plan.  Returns ``{q, k_blocks, v_blocks, sizes, scale, n, causal,
-    off}`` or ``None`` (explicit attention biases, mixed trees: the reference's own
-    om executors keep them)."""
+    is part of the plan.  An explicit attention mask in the form the masked sdpa law
+    leaves (om.py:1313-1362) is taken too:
+
+        om_apply(om_elem(add(concat(S_1, .., dim=-1), attnbias(m)), v))              one leaf
+        om_apply(<om_compose tree of om_elem(add(S_i, <columns of attnbias(m)>), v_i)>)
+
+    (the pieces must tile ONE ``attnbias(m)`` in key order; ``m`` is evaluated at run
+    time: a bool keep-mask or a float bias).  Returns ``{q, k_blocks, v_blocks, sizes,
+    scale, n, causal, off, bias}`` or ``None`` (a mask together with ``cmask``, mixed
+    trees: the reference's own om executors keep them)."""
     if not (isinstance(root, Op) and root.op == "om_apply" and len(root.args) == 1):
         return None
     leaves = _flatten(root.args[0], "om_compose")
-    if len(leaves) < 2 or len(set(leaves)) != len(leaves):
+    if len(set(leaves)) != len(leaves):
         return None
     memo: dict = {}
     q = scale = None
-    ks, vs, sizes, pos, total = [], [], [], 0, None
+    ks, vs, sizes, vsizes, pos, total = [], [], [], [], 0, None
     causal = None
     mask_base, off = None, 0
+    bias_base, biased = None, None
     for leaf in leaves:
         if not (isinstance(leaf, Op) and leaf.op == "om_elem" and len(leaf.args) == 2):
             return None
@@ -637,17 +682,29 @@ def om_causal_plan(root: Any) -> dict | None:
             return None
         if masked and not (len(sterm.args) == 3 and _const_value(sterm.args[2]) == float("-inf")):
             return None
-        sc = _scaled_scores(sterm.args[0] if masked else sterm)
-        kshape = None if sc is None else _shape_of(sc[1], memo)
-        if sc is None or not isinstance(kshape, tuple) or len(kshape) < 2 or not isinstance(kshape[-2], int):
+        score_part, bp = _split_bias(sterm.args[0] if masked else sterm, memo)
+        if biased is None:
+            biased = bp is not None
+        if biased != (bp is not None) or (biased and masked):
             return None
-        n_i = kshape[-2]
-        if q is None:
-            q, scale = sc[0], sc[2]
-        elif sc[0] != q or sc[2] != scale:
+        blocks = _score_blocks(score_part)
+        if blocks is None:
             return None
+        leaf_pos = pos
+        for sc in blocks:
+            kshape = _shape_of(sc[1], memo)
+            if not isinstance(kshape, tuple) or len(kshape) < 2 or not isinstance(kshape[-2], int):
+                return None
+            if q is None:
+                q, scale = sc[0], sc[2]
+            elif sc[0] != q or sc[2] != scale:
+                return None
+            ks.append(sc[1])
+            sizes.append(kshape[-2])
+            pos += kshape[-2]
+        n_i = pos - leaf_pos
         if masked:
-            # the mask: columns [pos, pos + n_i) of one cmask over the whole score tensor
+            # the mask: columns [leaf_pos, leaf_pos + n_i) of one cmask over the whole score tensor
             r = _range_of(sterm.args[1], -1, memo)
             if r is None:
                 return None
@@ -658,33 +715,40 @@ def om_causal_plan(root: Any) -> dict | None:
             if not isinstance(o_i, int) or (mask_base is not None and base != mask_base):
                 return None
             mask_base, off = base, o_i
-            if (start, length) != (pos, n_i) or (total is not None and tot != total):
+            if (start, length) != (leaf_pos, n_i) or (total is not None and tot != total):
                 return None
             total = tot
-        ks.append(sc[1])
+        if bp is not None:
+            base, start, length = bp
+            if (bias_base is not None and base != bias_base) or start != leaf_pos or (length is not None and length != n_i):
+                return None
+            if length is None and len(leaves) != 1:
+                return None                     # an unsliced bias belongs to a single leaf
+            bias_base = base
         vs.append(v)
-        sizes.append(n_i)
-        pos += n_i
+        vsizes.append(n_i)
+    if len(leaves) < 2 and not biased:
+        return None
     if not causal:
         total = pos
     if pos != total:
         return None
 
-    def whole(blocks):
+    def whole(blocks, sizes_):
         """The one tensor the blocks are consecutive row slices of, if they tile it: no join needed."""
         base, at = None, 0
-        for t, n_i in zip(blocks, sizes):
+        for t, n_i in zip(blocks, sizes_):
             r = _range_of(t, -2, memo)
             if r is None or (base is not None and r[0] != base) or r[1] != at or r[2] != n_i or r[3] != total:
                 return None
             base, at = r[0], at + n_i
         return base
 
-    kb, vb = whole(ks), whole(vs)
+    kb, vb = whole(ks, sizes), whole(vs, vsizes)
     if kb is not None and vb is not None:
         ks, vs = [kb], [vb]
     return {"q": q, "k_blocks": ks, "v_blocks": vs, "sizes": tuple(sizes), "scale": scale, "n": len(sizes),
-            "causal": bool(causal), "off": off}
+            "causal": bool(causal), "off": off, "bias": None if bias_base is None else bias_base.args[0]}
 
 
 def _flatten(t: Any, op: str) -> list:
@@ -719,14 +783,14 @@ class B200CausalSoftmaxModule(_EvalBase):
 
     @property
     def is_streaming(self) -> bool:
-        return self._plan is not None
+        return self._plan is not None and self._plan["bias"] is None
 
     def forward_state(self, *xs: torch.Tensor) -> Any:
         """The raw carrier ``(m, l, a)`` (fp32) after folding the blocks one kernel
         call at a time — ``StreamingOMModule.forward_state`` (om_lower.py:1003-1040);
         ``ops.om_apply_state`` reads it out, ``ops.om_step_qk`` extends it."""
         plan = self._plan
-        if plan is None:
+        if plan is None or plan["bias"] is not None:     # (the streaming step takes no explicit mask)
             return self.eval_mod(*xs)
         ev = self._ev(xs)
         return softmax_blocks_state(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
@@ -746,7 +810,8 @@ class B200CausalSoftmaxModule(_EvalBase):
                                       plan["scale"], True, key_offset=plan["off"])
             return ops.om_apply_state(st).to(q.dtype)
         out = causal_softmax_blocks(q, [ev(t) for t in plan["k_blocks"]],
-                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"])
+                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"],
+                                    mask=None if plan["bias"] is None else ev(plan["bias"]))
         return self.eval_mod(*xs) if out is None else out     # fp64: generic module, same device
 
 

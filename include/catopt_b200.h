@@ -341,6 +341,18 @@ int cb2_om_causal_fwd(const void* q, const void* k, const void* v, void* o, int 
 int cb2_om_fwd(const void* q, const void* k, const void* v, void* o, int B, int H,
                int Tq, int Tk, int dk, int dv, float scale, int causal, int dtype,
                int* dev_status, void* stream);
+/* The same with an explicit attention mask in torch's additive form — the carrier the
+ * reference's masked sdpa-over-concat law produces,
+ * `om_apply(om_elem(add(scaled scores, attnbias(m)), v))` (catopt_carriers/om.py:1313-1362;
+ * `attnbias`, om.py:1036-1050: a float mask is the bias itself, a bool keep-mask is 0 / -inf):
+ *     o = softmax(scale * q k^T + bias) v .
+ * bias: fp32, element (b, h, t, j) at bias[b*stride_b + h*stride_h + t*stride_q + j] (strides
+ * in elements, 0 on a broadcast axis, keys contiguous).  A key with bias -inf is hidden exactly
+ * like a causally masked one; a row whose keys are all hidden is NaN, as in the reference. */
+int cb2_om_bias_fwd(const void* q, const void* k, const void* v, void* o, const float* bias,
+                    long long bias_stride_b, long long bias_stride_h, long long bias_stride_q,
+                    int B, int H, int Tq, int Tk, int dk, int dv, float scale, int causal,
+                    int dtype, int* dev_status, void* stream);
 
 /* One streaming step of the same monoid: fold a block of keys/values into a
  * running carrier (m, l, a) — `om_step_qk` / `StreamingOMModule.forward_state`

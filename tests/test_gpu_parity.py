@@ -138,6 +138,56 @@ def test_linear_is_linear_at_published_size(dev):
     assert rel_to_max(lhs, rhs) <= FP32_TOL
 
 
+# --------------------------------------------------------------------------- explicit attention masks
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("B,H,Tq,Tk,d,mshape", [(2, 4, 384, 384, 128, (384, 384)), (1, 3, 200, 333, 64, (1, 3, 200, 333)),
+                                               (2, 2, 128, 512, 64, (2, 1, 128, 512)), (1, 2, 130, 70, 32, (130, 1)),
+                                               (2, 2, 64, 256, 128, (1, 1, 1, 256))])
+def test_om_bias_fwd_vs_torch_sdpa_in_fp64(dev, dtype, tol, B, H, Tq, Tk, d, mshape):
+    """softmax(scale q k^T + bias) v with biases of every broadcast shape (per (t, j), with a head or a
+    batch axis, one value per row, one per key), some keys hidden by -inf, against torch's own masked
+    attention in fp64 on the same (rounded) inputs."""
+    import torch.nn.functional as F
+
+    from catopt_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(Tq + Tk)
+    q, k, v = (torch.randn(B, H, T, d, device=dev, generator=g).to(dtype) for T in (Tq, Tk, Tk))
+    bias = torch.randn(*mshape, device=dev, generator=g)
+    hide = torch.rand(*mshape, device=dev, generator=g) < 0.3
+    if mshape[-1] > 1:
+        hide[..., 0] = False                                  # every row keeps a key
+        bias = bias.masked_fill(hide, float("-inf"))
+    got = ops.om_bias_fwd(q, k, v, bias, 0.125)
+    ops.check_device_status(dev)
+    want = F.scaled_dot_product_attention(q.double(), k.double(), v.double(), attn_mask=bias.double(), scale=0.125)
+    assert got.dtype == dtype and rel_to_max(got, want) <= tol
+
+
+def test_om_bias_fwd_bool_mask_hidden_rows_and_the_causal_flag(dev):
+    """A bool keep-mask goes in as 0 / -inf (the reference's ``attnbias``); a row with no visible key is
+    NaN, as the reference's unclamped a / l; with the causal flag the two masks combine."""
+    import torch.nn.functional as F
+
+    from catopt_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(77)
+    q, k, v = (torch.randn(1, 2, 256, 64, device=dev, generator=g).bfloat16() for _ in range(3))
+    keep = torch.rand(256, 256, device=dev, generator=g) < 0.5
+    keep[7] = False
+    got = ops.om_bias_fwd(q, k, v, ops.attn_bias(keep), 0.125)
+    want = F.scaled_dot_product_attention(q.double(), k.double(), v.double(), attn_mask=keep, scale=0.125)
+    assert torch.isnan(got[:, :, 7]).all()        # (torch's own kernels differ among themselves on such rows)
+    rows = [t for t in range(256) if t != 7]
+    assert rel_to_max(got[:, :, rows], want[:, :, rows]) <= BF16_TOL
+    keep[:, 0] = True
+    both = keep & torch.ones(256, 256, dtype=torch.bool, device=dev).tril()
+    got = ops.om_bias_fwd(q, k, v, ops.attn_bias(keep), 0.125, causal=True)
+    want = F.scaled_dot_product_attention(q.double(), k.double(), v.double(), attn_mask=both, scale=0.125)
+    assert rel_to_max(got, want) <= BF16_TOL
+    ops.check_device_status(dev)
+
+
 # --------------------------------------------------------------------------- (b) decayed
 @pytest.mark.parametrize("name", [n for n in cases.DECAYED_CASES if n != "tiny_f64"])
 def test_decayed_fp32_vs_reference_fixture(dev, name):

@@ -618,3 +618,79 @@ def test_om_causal_term_with_a_shifted_mask_matches_the_reference_executor(off):
     ok = ~torch.isnan(want)
     assert _rel(got[ok], want[ok]) <= 1e-5
     ops.check_device_status(DEV)
+
+
+# --------------------------------------------------------------------------- explicit attention masks
+def _om_masked_term(ksizes, Tq, d, dv, batch, scale, mask_shape, one_leaf):
+    q = Var("q", _tt(*batch, Tq, d))
+    ks = [Var(f"k{i}", _tt(*batch, n, d)) for i, n in enumerate(ksizes)]
+    vs = [Var(f"v{i}", _tt(*batch, n, dv)) for i, n in enumerate(ksizes)]
+    m = Var("m", _tt(*mask_shape))
+    bias = Op.make("attnbias", m)
+    if one_leaf:
+        qs = Op.make("mul", q, Op.make("fill", q, value=scale))
+        sc = Op.make("concat", *(Op.make("matmul", qs, Op.make("transpose", k, dim0=-2, dim1=-1)) for k in ks), dim=-1)
+        tree = Op.make("om_elem", Op.make("add", sc, bias), Op.make("concat", *vs, dim=-2))
+    else:
+        def scores(k):
+            return Op.make("om_decayed", q, Op.make("fill", q, value=scale), Op.make("transpose", k, dim0=-2, dim1=-1))
+
+        leaves = [Op.make("om_elem", Op.make("add", scores(k), Op.make("split", bias, dim=len(mask_shape) - 1, index=i,
+                                                                       sizes=tuple(ksizes))), v)
+                  for i, (k, v) in enumerate(zip(ks, vs))]
+        tree = leaves[-1]
+        for lf in reversed(leaves[:-1]):
+            tree = Op.make("om_compose", lf, tree)
+    ins = [q, *ks, *vs, m]
+    return IR(root=Op.make("om_apply", tree), inputs=ins, input_names={t.name for t in ins}, params={})
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("kind", ["bool", "additive", "finite", "per_batch", "per_head"])
+@pytest.mark.parametrize("one_leaf", [False, True])
+def test_om_term_with_an_explicit_mask_on_the_b200_module_matches_the_reference_executor(dtype, tol, kind, one_leaf):
+    """The carrier of sdpa with an attn_mask (``add(scores, attnbias(m))``, om.py:1313-1362) through the
+    routed B200 module against the reference's own executor for the same term on the same device: bool
+    keep-masks, additive 0/-inf masks, finite biases, masks with a batch or a head axis.  Rows whose keys
+    are all hidden are NaN in both."""
+    from catopt_torch.adapters import TorchSink
+
+    ksizes, Tq, d, dv, batch, scale = (128, 64, 192), 320, 64, 64, (2, 4), 0.125
+    Tk = sum(ksizes)
+    g = torch.Generator().manual_seed(21)
+    if kind == "bool":
+        shape, m = (Tq, Tk), torch.rand(Tq, Tk, generator=g) < 0.6
+        m[5] = False                                   # one row sees no key at all
+    elif kind == "additive":
+        shape = (Tq, Tk)
+        m = torch.where(torch.rand(Tq, Tk, generator=g) < 0.35, torch.tensor(float("-inf")), torch.zeros(()))
+    elif kind == "finite":
+        shape, m = (Tq, Tk), torch.randn(Tq, Tk, generator=g)
+    elif kind == "per_batch":
+        shape = (2, 1, Tq, Tk)
+        m = torch.where(torch.rand(*shape, generator=g) < 0.35, torch.tensor(float("-inf")), torch.zeros(()))
+    else:
+        shape, m = (1, 4, Tq, Tk), torch.randn(1, 4, Tq, Tk, generator=g)
+    ir = _om_masked_term(ksizes, Tq, d, dv, batch, scale, shape, one_leaf)
+    q = torch.randn(*batch, Tq, d, generator=g).to(dtype).to(DEV)
+    ks = [torch.randn(*batch, n, d, generator=g).to(dtype).to(DEV) for n in ksizes]
+    vs = [torch.randn(*batch, n, dv, generator=g).to(dtype).to(DEV) for n in ksizes]
+    m = m.to(DEV)
+    spec = _route(b200.B200Sink(), ir.root)
+    assert spec.name == "b200_om_causal"
+    mod = spec.lower(ir, None)
+    assert mod.is_batched and mod._plan["bias"] is not None
+    from catopt_torch.torch_bridge import IRModule
+
+    rspec = _route(TorchSink(), ir.root)
+    ref = rspec.lower(ir, None) if rspec is not None else IRModule(ir, None).to(DEV)
+    with torch.no_grad():
+        got = mod(q, *ks, *vs, m)
+        want = ref(*(t.float() for t in (q, *ks, *vs)), m if m.dtype == torch.bool else m.float())
+    assert got.dtype == dtype
+    assert torch.equal(torch.isnan(got), torch.isnan(want))
+    if kind == "bool":
+        assert torch.isnan(want[..., 5, :]).all()
+    ok = ~torch.isnan(want)
+    assert _rel(got[ok], want[ok]) <= tol
+    ops.check_device_status(DEV)

@@ -501,6 +501,114 @@ def test_om_causal_real_saturation_member_is_accepted():
     assert plan is not None and plan["causal"] is False and plan["sizes"] == (3, 6)
 
 
+def _om_masked_term(ksizes, Tq, d=4, dv=6, batch=(2, 3), scale=0.5, one_leaf=False, mask_shape=None):
+    """The carrier the reference's masked sdpa law leaves (catopt_carriers/om.py:1313-1362): one
+    ``om_elem`` over the concatenated scores plus ``attnbias(m)``, or its chunked form with the
+    bias sliced per key block."""
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    q = Var("q", tt(*batch, Tq, d))
+    ks = [Var(f"k{i}", tt(*batch, n, d)) for i, n in enumerate(ksizes)]
+    vs = [Var(f"v{i}", tt(*batch, n, dv)) for i, n in enumerate(ksizes)]
+    mask_shape = mask_shape or (Tq, sum(ksizes))
+    m = Var("m", tt(*mask_shape))
+    bias = Op.make("attnbias", m)
+    rank = len(mask_shape)                     # the mask is sliced along ITS key axis
+    if one_leaf:
+        qs = Op.make("mul", q, Op.make("fill", q, value=scale))
+        sc = Op.make("concat", *(Op.make("matmul", qs, Op.make("transpose", k, dim0=-2, dim1=-1)) for k in ks), dim=-1)
+        tree = Op.make("om_elem", Op.make("add", sc, bias), Op.make("concat", *vs, dim=-2))
+    else:
+        def scores(k):
+            return Op.make("om_decayed", q, Op.make("fill", q, value=scale), Op.make("transpose", k, dim0=-2, dim1=-1))
+
+        leaves = [Op.make("om_elem", Op.make("add", scores(k), Op.make("split", bias, dim=rank - 1, index=i,
+                                                                       sizes=tuple(ksizes))), v)
+                  for i, (k, v) in enumerate(zip(ks, vs))]
+        tree = leaves[-1]
+        for lf in reversed(leaves[:-1]):
+            tree = Op.make("om_compose", lf, tree)
+    inputs = [q, *ks, *vs, m]
+    return IR(root=Op.make("om_apply", tree), inputs=inputs, input_names={v.name for v in inputs}, params={})
+
+
+@pytest.mark.parametrize("one_leaf", [False, True])
+def test_om_carrier_with_an_explicit_mask_is_recognised_and_means_masked_attention(one_leaf):
+    import torch.nn.functional as F
+    from catopt_torch.torch_bridge import IRModule
+
+    ksizes, Tq = (3, 6), 5
+    ir = _om_masked_term(ksizes, Tq, one_leaf=one_leaf)
+    plan = b200.om_causal_plan(ir.root)
+    assert plan is not None and plan["sizes"] == ksizes and plan["scale"] == 0.5 and not plan["causal"]
+    assert plan["bias"].name == "m" and [k.name for k in plan["k_blocks"]] == ["k0", "k1"]
+    spec = _route(b200.B200Sink(), ir.root)
+    assert spec.name == "b200_om_causal"
+    mod = spec.lower(ir, None)
+    assert mod.is_batched and not mod.is_streaming        # the streaming step takes no explicit mask
+    # the term evaluates (reference bindings, fp64) to torch's masked attention, bool and float masks alike
+    gen = torch.Generator().manual_seed(4)
+    q = torch.randn(2, 3, Tq, 4, dtype=torch.float64, generator=gen)
+    ks = [torch.randn(2, 3, n, 4, dtype=torch.float64, generator=gen) for n in ksizes]
+    vs = [torch.randn(2, 3, n, 6, dtype=torch.float64, generator=gen) for n in ksizes]
+    keep = torch.rand(Tq, 9, generator=gen) < 0.6
+    keep[:, 0] = True
+    for m in (keep, torch.randn(Tq, 9, dtype=torch.float64, generator=gen)):
+        with torch.no_grad():
+            got = IRModule(ir, None)(q, *ks, *vs, m)
+        want = F.scaled_dot_product_attention(q, torch.cat(ks, -2), torch.cat(vs, -2), attn_mask=m, scale=0.5)
+        assert (got - want).abs().max().item() < 1e-12
+    with pytest.raises(b200.B200Error):                   # no CPU fallback inside the executor
+        mod(q.float(), *(t.float() for t in ks), *(t.float() for t in vs), keep)
+
+
+def test_om_masked_lookalikes_are_declined():
+    ir = _om_masked_term((4, 4, 4), 12)
+    a, b_, c = b200._flatten(ir.root.args[0], "om_compose")
+    mk = lambda *ls: Op.make("om_apply", Op.make("om_compose", ls[0], Op.make("om_compose", *ls[1:])))  # noqa: E731
+    assert b200.om_causal_plan(mk(a, b_, c)) is not None
+    assert b200.om_causal_plan(mk(b_, a, c)) is None                    # mask columns out of key order
+    other = _om_masked_term((4, 4, 4), 12, mask_shape=(1, 12))
+    o_leaves = b200._flatten(other.root.args[0], "om_compose")
+    # (same spelling, so the pieces are equal terms; a second mask needs another variable)
+    tt = lambda *sh: TensorType(tuple(sh))  # noqa: E731
+    m2 = Op.make("attnbias", Var("m2", tt(12, 12)))
+    sterm = o_leaves[1].args[0]
+    swapped = Op.make("om_elem", Op.make("add", sterm.args[0], Op.make("split", m2, dim=1, index=1, sizes=(4, 4, 4))),
+                      o_leaves[1].args[1])
+    assert b200.om_causal_plan(mk(a, swapped, c)) is None               # two different masks
+    plain = _om_causal_term((4, 4, 4), 12)[1]
+    assert b200.om_causal_plan(mk(a, plain[1], c)) is None              # a masked and a causal leaf
+    both = Op.make("om_elem", Op.make("masked_fill", a.args[0], plain[0].args[0].args[1], Const(float("-inf"))), a.args[1])
+    assert b200.om_causal_plan(mk(both, b_, c)) is None                 # cmask and an explicit mask together
+
+
+def test_om_masked_real_saturation_members_are_accepted():
+    """Saturate sdpa(q, cat k, cat v, attn_mask) with the reference's om laws and extract the chunked
+    carrier with the reference's own test helper (tests/test_mask_chunk.py there): additive 0/-inf
+    masks, finite biases, bool keep-masks, three uneven blocks, a (B,1,T,K) mask over heads."""
+    import importlib.util
+
+    path = os.path.join(_REF, "tests", "test_mask_chunk.py")
+    if not os.path.exists(path):
+        pytest.skip("reference test helpers not available")
+    spec = importlib.util.spec_from_file_location("_ref_test_mask_chunk", path)
+    helper = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(helper)
+
+    def head_mask(T, K):
+        return torch.where(torch.rand(2, 1, T, K) < 0.35, torch.tensor(float("-inf"), dtype=torch.float64),
+                           torch.zeros(2, 1, T, K, dtype=torch.float64))
+
+    for ksizes, fn, kw in (((3, 6), helper._addmask_fn(), {}), ((2, 3, 4), helper._boolmask_fn, {}),
+                           ((3, 6), helper._finite_bias_fn, {"spelling": "kwarg", "scale": 0.5}),
+                           ((1, 8), helper._addmask_fn(), {}), ((2, 5), head_mask, {"batch": (2, 3)})):
+        _, term, _, _, _ = helper._mask_chunked_ok(list(ksizes), fn, **kw)
+        plan = b200.om_causal_plan(term)
+        assert plan is not None and plan["sizes"] == tuple(ksizes) and not plan["causal"], (ksizes, kw)
+        assert plan["bias"] is not None and plan["bias"].name == "m"
+        assert _route(b200.B200Sink(), term).name == "b200_om_causal"
+
+
 # --------------------------------------------------------------------------- omd: prefix-scan hook
 def _omd_chain_term(T=8, Tq=3, d=4):
     """omd_apply(omd_elem(s, stack(affd_a f_i), stack(affd_b f_i)), h) over the shared
