@@ -47,6 +47,9 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// BIAS: with an additive attention bias (a separate instantiation, so that the plain kernel keeps
+// its register budget)
+template <bool BIAS>
 __global__ void __launch_bounds__(kThreads, 2)
 om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -206,7 +209,7 @@ om_causal_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       // additive bias (an explicit attention mask): scores here are unscaled, so the bias goes in divided
       // by the scale; -inf hides the key like the causal mask does
-      if (bias.p) {
+      if (BIAS) {
         const float* brow = bias.p + (bh / bias.H) * bias.sb + (bh % bias.H) * bias.sh +
                             (long long)min(tq, Tq - 1) * bias.sq + k0;
         const float unscale = kLog2e / scale_log2e;
@@ -389,13 +392,13 @@ int om_causal_tc_run(const void* q, const void* k, const void* v, void* o, int B
     else mo = mq;                                   // unused in the streaming form
   }
   if (rc != CB2_OK) return rc;
-  if (cudaFuncSetAttribute(om_causal_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           int(kSmemBytes)) != cudaSuccess)
+  auto* kernel = bias.p ? om_causal_tc_kernel<true> : om_causal_tc_kernel<false>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)) != cudaSuccess)
     return CB2_LAUNCH_FAIL;
   const unsigned grid = unsigned(((Tq + kQ - 1) / kQ) * bh);
-  om_causal_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh), causal,
-                                                         scale * 1.4426950408889634f, key_offset, m_in, l_in, a_in,
-                                                         m_out, l_out, a_out, bias, dev_status);
+  kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, mo, Tq, Tk, dk, dv, int(bh), causal,
+                                             scale * 1.4426950408889634f, key_offset, m_in, l_in, a_in, m_out, l_out,
+                                             a_out, bias, dev_status);
   CB2_LAUNCH_CHECK();
   return CB2_OK;
 }
