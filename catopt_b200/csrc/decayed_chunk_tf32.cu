@@ -446,10 +446,14 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       ok = mbar_wait_abortable(&B.k_full[ph], (t >> 1) & 1, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      {
+        // (all loads before the first store: the tiles may alias as far as the compiler knows, and a
+        // load behind a store would wait for it)
+        float4 x[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t off = chunk_off(r, j, kSub);
-        *reinterpret_cast<float4*>(kl + off) = rest4(*reinterpret_cast<const float4*>(kh + off));
+        for (int j = 0; j < 8; ++j) x[j] = *reinterpret_cast<const float4*>(kh + chunk_off(r, j, kSub));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(kl + chunk_off(r, j, kSub)) = rest4(x[j]);
       }
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
@@ -460,13 +464,19 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       } else if (lane < 16) {
         const uint32_t n = q4 * 16 + lane;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t off = chunk_off(n, j, kSubS);
-          const float4 a = *reinterpret_cast<const float4*>(sh + off);
-          const float4 x = make_float4(fmaf(gC, a.x, d[4 * j]), fmaf(gC, a.y, d[4 * j + 1]),
-                                       fmaf(gC, a.z, d[4 * j + 2]), fmaf(gC, a.w, d[4 * j + 3]));
-          *reinterpret_cast<float4*>(sh + off) = x;
-          *reinterpret_cast<float4*>(sl + off) = rest4(x);
+        for (int half = 0; half < 2; ++half) {
+          float4 a[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] = *reinterpret_cast<const float4*>(sh + chunk_off(n, half * 8 + j, kSubS));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int e = 4 * (half * 8 + j);
+            const uint32_t off = chunk_off(n, half * 8 + j, kSubS);
+            const float4 x = make_float4(fmaf(gC, a[j].x, d[e]), fmaf(gC, a[j].y, d[e + 1]),
+                                         fmaf(gC, a[j].z, d[e + 2]), fmaf(gC, a[j].w, d[e + 3]));
+            *reinterpret_cast<float4*>(sh + off) = x;
+            *reinterpret_cast<float4*>(sl + off) = rest4(x);
+          }
         }
       }
       fence_proxy_async_smem();
@@ -559,11 +569,11 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!ok) break;
       {
         const unsigned char* kh = smem + (ph ? kOffK1 : kOffK0);
+        float4 x[8];
 #pragma unroll
-        for (int j = 8; j < 16; ++j) {
-          const uint32_t off = chunk_off(r, j, kSub);
-          *reinterpret_cast<float4*>(kl + off) = rest4(*reinterpret_cast<const float4*>(kh + off));
-        }
+        for (int j = 0; j < 8; ++j) x[j] = *reinterpret_cast<const float4*>(kh + chunk_off(r, 8 + j, kSub));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(kl + chunk_off(r, 8 + j, kSub)) = rest4(x[j]);
       }
       fence_proxy_async_smem();
       mbar_arrive(B.k_ready);
@@ -597,9 +607,14 @@ decayed_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // r + 4 keep a chunk in the same banks)
         const uint32_t flip = (r >> 2) & 1u;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t off = chunk_off32(r, uint32_t(j) ^ flip, kSub);
-          *reinterpret_cast<float4*>(vl + off) = rest4(*reinterpret_cast<const float4*>(vh + off));
+        for (int half = 0; half < 2; ++half) {
+          float4 x[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            x[j] = *reinterpret_cast<const float4*>(vh + chunk_off32(r, uint32_t(half * 8 + j) ^ flip, kSub));
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(vl + chunk_off32(r, uint32_t(half * 8 + j) ^ flip, kSub)) = rest4(x[j]);
         }
       }
       fence_proxy_async_smem();
