@@ -116,6 +116,11 @@ SIGNATURES: dict[str, tuple] = {
          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_void_p],
     ),
     "cb2_om_step_scratch_bytes": (C.c_size_t, [C.c_int] * 5),
+    "cb2_om_bias_step": (
+        C.c_int,
+        [C.c_void_p] * 4 + [C.c_longlong] * 3 + [C.c_void_p] * 6 + [C.c_int] * 6 +
+        [C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p],
+    ),
     "cb2_om_step": (
         C.c_int,
         [C.c_void_p] * 9 + [C.c_int] * 6 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,

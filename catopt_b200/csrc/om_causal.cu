@@ -500,11 +500,13 @@ extern "C" size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv
   return (z > 1 || (Tq <= cb2::kDecRows && Tk >= 256)) ? size_t(z) * B * H * Tq * (size_t(dv) + 2) * sizeof(float) : 0;
 }
 
-extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
-                           const float* a_in, float* m_out, float* l_out, float* a_out, int B, int H, int Tq,
-                           int Tk, int dk, int dv, float scale, int causal, int key_offset, int dtype,
-                           void* scratch, size_t scratch_bytes, int* dev_status, void* stream) {
-  using namespace cb2;
+namespace cb2 {
+namespace {
+// One streaming step, with or without an additive bias over this block's keys.
+int om_step_impl(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
+                 const float* a_in, float* m_out, float* l_out, float* a_out, int B, int H, int Tq, int Tk, int dk,
+                 int dv, float scale, int causal, int key_offset, int dtype, const OmBias& bias, void* scratch,
+                 size_t scratch_bytes, int* dev_status, void* stream) {
   if (!q || !k || !v || !m_out || !l_out || !a_out) return CB2_NULL_PTR;
   if ((m_in == nullptr) != (l_in == nullptr) || (m_in == nullptr) != (a_in == nullptr)) return CB2_NULL_PTR;
   if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dk <= 0 || dv <= 0) return CB2_BAD_SHAPE;
@@ -512,8 +514,8 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
   const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t rows = size_t(B) * H * Tq;
-  // a handful of query rows against many keys: the streaming (memory-bound) kernel
-  if (om_decode_shape(Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && scratch &&
+  // a handful of query rows against many keys: the streaming (memory-bound) kernel (it takes no bias)
+  if (!bias.p && om_decode_shape(Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && scratch &&
       !(reinterpret_cast<uintptr_t>(scratch) & 15u)) {
     int Zd = om_decode_splits(B, H, Tk);
     if (scratch_bytes >= size_t(Zd) * rows * (size_t(dv) + 2) * sizeof(float)) {
@@ -544,7 +546,7 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
   if (Tq > kDecRows && om_causal_tc_supported(B, H, Tq, Tk, dk, dv, dtype) && scale > 0.f && aligned16(q) &&
       aligned16(k) && aligned16(v) && aligned16(a_out) && (!a_in || aligned16(a_in)))
     return om_causal_tc_run(q, k, v, nullptr, B, H, Tq, Tk, dk, dv, scale, causal ? 1 : 0, key_offset, m_in, l_in,
-                            a_in, m_out, l_out, a_out, OmBias{nullptr, 0, 0, 0, 1}, dev_status, st);
+                            a_in, m_out, l_out, a_out, bias, dev_status, st);
   // few query tiles: cut the keys over extra CTAs, then fold the partial carriers
   int Z = om_step_splits(B, H, Tq, Tk);
   if (Z > 1 && (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) ||
@@ -567,13 +569,13 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_BF16><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
-                                                               key_offset, mi, li, ai, mo, lo, ao, split_len, OmBias{nullptr, 0, 0, 0, 1});
+                                                               key_offset, mi, li, ai, mo, lo, ao, split_len, bias);
   } else if (dtype == CB2_F32) {
     if (cudaFuncSetAttribute(om_causal_kernel<CB2_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(smem)) != cudaSuccess)
       return CB2_LAUNCH_FAIL;
     om_causal_kernel<CB2_F32><<<grid, kOmThreads, smem, st>>>(q, k, v, nullptr, Tq, Tk, dk, dv, scale, causal ? 1 : 0,
-                                                              key_offset, mi, li, ai, mo, lo, ao, split_len, OmBias{nullptr, 0, 0, 0, 1});
+                                                              key_offset, mi, li, ai, mo, lo, ao, split_len, bias);
   } else {
     return CB2_UNSUPPORTED_DTYPE;
   }
@@ -585,4 +587,28 @@ extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const fl
     CB2_LAUNCH_CHECK();
   }
   return CB2_OK;
+}
+}  // namespace
+}  // namespace cb2
+
+extern "C" int cb2_om_step(const void* q, const void* k, const void* v, const float* m_in, const float* l_in,
+                           const float* a_in, float* m_out, float* l_out, float* a_out, int B, int H, int Tq,
+                           int Tk, int dk, int dv, float scale, int causal, int key_offset, int dtype,
+                           void* scratch, size_t scratch_bytes, int* dev_status, void* stream) {
+  return cb2::om_step_impl(q, k, v, m_in, l_in, a_in, m_out, l_out, a_out, B, H, Tq, Tk, dk, dv, scale, causal,
+                           key_offset, dtype, cb2::OmBias{nullptr, 0, 0, 0, 1}, scratch, scratch_bytes, dev_status,
+                           stream);
+}
+
+extern "C" int cb2_om_bias_step(const void* q, const void* k, const void* v, const float* bias,
+                                long long bias_stride_b, long long bias_stride_h, long long bias_stride_q,
+                                const float* m_in, const float* l_in, const float* a_in, float* m_out, float* l_out,
+                                float* a_out, int B, int H, int Tq, int Tk, int dk, int dv, float scale, int causal,
+                                int key_offset, int dtype, void* scratch, size_t scratch_bytes, int* dev_status,
+                                void* stream) {
+  if (!bias) return CB2_NULL_PTR;
+  if (bias_stride_b < 0 || bias_stride_h < 0 || bias_stride_q < 0) return CB2_BAD_SHAPE;
+  return cb2::om_step_impl(q, k, v, m_in, l_in, a_in, m_out, l_out, a_out, B, H, Tq, Tk, dk, dv, scale, causal,
+                           key_offset, dtype, cb2::OmBias{bias, bias_stride_b, bias_stride_h, bias_stride_q, H},
+                           scratch, scratch_bytes, dev_status, stream);
 }

@@ -255,18 +255,22 @@ def causal_softmax_blocks(q: torch.Tensor, k_blocks: list, v_blocks: list, scale
     if mask is None:
         out = ops.om_causal_fwd(q4, k4, v4, scale, causal=causal)
     else:
-        bias = ops.attn_bias(mask)
-        if bias.dim() > 2 and any(s != 1 for s in bias.shape[:-2]):
-            # leading axes line up with q's: make them the same [-1, H] pair (broadcast axes stay unmaterialised)
-            bias = bias.expand(*lead, *bias.shape[-2:]).reshape(-1, H, *bias.shape[-2:])
-        else:
-            bias = bias.reshape(bias.shape[-2:]) if bias.dim() >= 2 else bias
-        out = ops.om_bias_fwd(q4, k4, v4, bias, scale, causal=causal)
+        out = ops.om_bias_fwd(q4, k4, v4, _mask_as_bias(mask, lead, H), scale, causal=causal)
     return out.reshape(*lead, out.shape[-2], out.shape[-1])
 
 
+def _mask_as_bias(mask: torch.Tensor, lead: tuple, H: int) -> torch.Tensor:
+    """An attention mask (bool keep-mask or float bias, broadcastable to ``[*lead, Tq, Tk]``) as an fp32
+    bias whose leading axes are the ``[-1, H]`` pair the kernels index (broadcast axes unmaterialised)."""
+    bias = ops.attn_bias(mask)
+    if bias.dim() > 2 and any(s != 1 for s in bias.shape[:-2]):
+        return bias.expand(*lead, *bias.shape[-2:]).reshape(-1, H, *bias.shape[-2:])
+    return bias.reshape(bias.shape[-2:]) if bias.dim() >= 2 else bias
+
+
 def softmax_blocks_state(q: torch.Tensor, k_blocks: list, v_blocks: list, scale: float, causal: bool = True,
-                         state: tuple | None = None, key_offset: int = 0) -> tuple:
+                         state: tuple | None = None, key_offset: int = 0,
+                         mask: torch.Tensor | None = None) -> tuple:
     """Streaming fold of key/value blocks into the online-softmax carrier
     ``(m, l, a)`` (fp32), one ``cb2_om_step`` per block — the state a decode loop
     checkpoints (``StreamingOMModule.forward_state``, catopt_carriers/om_lower.py:
@@ -278,11 +282,18 @@ def softmax_blocks_state(q: torch.Tensor, k_blocks: list, v_blocks: list, scale:
     H = lead[-1] if lead else 1
 
     def r4(t):
-        return t.expand(*lead, *t.shape[-2:]).reshape(-1, H, t.shape[-2], t.shape[-1])
+        return t.expand(*lead, *t.shape[-2:]).reshape(-1, H, t.shape[-2], t.shape[-1]).contiguous()
 
     if state is not None:
         state = tuple(r4(t) for t in state)
+    bias = None if mask is None else _mask_as_bias(mask, lead, H)
+    col = 0                                          # this call's first key among the mask's columns
     for kb, vb in zip(k_blocks, v_blocks):
-        state = ops.om_step_qk(state, r4(q), r4(kb), r4(vb), scale, causal, key_offset)
-        key_offset += kb.shape[-2]
+        n = kb.shape[-2]
+        piece = None
+        if bias is not None:
+            piece = bias if bias.dim() == 0 or bias.shape[-1] == 1 else bias[..., col:col + n]
+        state = ops.om_step_qk(state, r4(q), r4(kb), r4(vb), scale, causal, key_offset, bias=piece)
+        key_offset += n
+        col += n
     return tuple(t.reshape(*lead, *t.shape[-2:]) for t in state)

@@ -279,19 +279,7 @@ def om_bias_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.T
     if not (q.dtype == k.dtype == v.dtype):
         raise B200Error("q, k, v must share one dtype")
     Tk, dv = k.shape[2], v.shape[3]
-    if bias.dtype != torch.float32 or bias.dim() > 4:
-        raise B200Error("bias must be float32 of rank <= 4")
-    bb = bias.reshape(1) if bias.dim() == 0 else bias
-    if bb.shape[-1] == 1 and Tk > 1:
-        bb = bb.expand(*bb.shape[:-1], Tk)            # one value for every key of a row
-    if Tk > 1 and bb.stride(-1) != 1:
-        bb = bb.contiguous()                          # the kernel reads a row's keys contiguously
-    try:
-        b4 = torch.broadcast_to(bb, (B, H, Tq, Tk))   # the other broadcast axes keep stride 0
-    except RuntimeError as e:
-        raise B200Error(f"bias of shape {tuple(bias.shape)} does not broadcast to {(B, H, Tq, Tk)}") from e
-    if any(st < 0 for st in b4.stride()):
-        raise B200Error("bias with negative strides")
+    b4 = _bias4(bias, B, H, Tq, Tk)
     sc = float(scale) if scale is not None else 1.0 / float(dk) ** 0.5
     if out is None:
         out = torch.empty(B, H, Tq, dv, dtype=q.dtype, device=q.device)
@@ -312,8 +300,27 @@ def om_empty_state(shape: tuple, dv: int, device: torch.device | str) -> tuple:
         torch.zeros(*shape, dv, dtype=torch.float32, device=device)
 
 
+def _bias4(bias: torch.Tensor, B: int, H: int, Tq: int, Tk: int) -> torch.Tensor:
+    """``bias`` (fp32, rank <= 4, broadcastable) as a ``[B,H,Tq,Tk]`` view with contiguous keys; the
+    other broadcast axes keep stride 0."""
+    if bias.dtype != torch.float32 or bias.dim() > 4:
+        raise B200Error("bias must be float32 of rank <= 4")
+    bb = bias.reshape(1) if bias.dim() == 0 else bias
+    if bb.shape[-1] == 1 and Tk > 1:
+        bb = bb.expand(*bb.shape[:-1], Tk)            # one value for every key of a row
+    if Tk > 1 and bb.stride(-1) != 1:
+        bb = bb.contiguous()                          # the kernel reads a row's keys contiguously
+    try:
+        b4 = torch.broadcast_to(bb, (B, H, Tq, Tk))
+    except RuntimeError as e:
+        raise B200Error(f"bias of shape {tuple(bias.shape)} does not broadcast to {(B, H, Tq, Tk)}") from e
+    if any(st < 0 for st in b4.stride()):
+        raise B200Error("bias with negative strides")
+    return b4
+
+
 def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float = 1.0,
-               causal: bool = False, key_offset: int = 0) -> tuple:
+               causal: bool = False, key_offset: int = 0, bias: torch.Tensor | None = None) -> tuple:
     """``state (+) om_elem(scale * q @ k^T, v)``: fold one block of keys/values into
     the running carrier (``om_step_qk``, om_lower.py:911-922; the reference takes
     unscaled, unmasked scores — ``scale`` and the causal mask with its key offset
@@ -322,8 +329,10 @@ def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.T
     With ``causal`` key j of this block is hidden from query row t when
     ``key_offset + j > t``: ``key_offset`` = keys folded in before this block minus
     the sequence position of query row 0 (negative in a decode step whose queries
-    are the newest positions)."""
+    are the newest positions).  ``bias``: fp32 additive mask over THIS block's keys,
+    broadcastable to ``[B,H,Tq,Tk]`` (``cb2_om_bias_step``)."""
     require_cuda(q, k, v)
+    require_device(bias)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise B200Error("om_step_qk takes rank-4 q, k, v")
     B, H, Tq, dk = q.shape
@@ -345,6 +354,15 @@ def om_step_qk(state: tuple | None, q: torch.Tensor, k: torch.Tensor, v: torch.T
     lib = _lib.load()
     need = lib.cb2_om_step_scratch_bytes(B, H, Tq, Tk, dv)
     scratch = _scratch_buf("om_step", need, q.device)
+    if bias is not None:
+        b4 = _bias4(bias, B, H, Tq, Tk)
+        rc = lib.cb2_om_bias_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), b4.data_ptr(), b4.stride(0), b4.stride(1),
+                                  b4.stride(2), *ptrs, m_out.data_ptr(), l_out.data_ptr(), a_out.data_ptr(), B, H,
+                                  Tq, Tk, dk, dv, float(scale), 1 if causal else 0, int(key_offset),
+                                  dtype_code(q.dtype), _ptr(scratch), need, device_status(q.device).data_ptr(),
+                                  stream_ptr())
+        check(rc, "cb2_om_bias_step")
+        return m_out, l_out, a_out
     rc = lib.cb2_om_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), *ptrs, m_out.data_ptr(),
                          l_out.data_ptr(), a_out.data_ptr(), B, H, Tq, Tk, dk, dv, float(scale),
                          1 if causal else 0, int(key_offset), dtype_code(q.dtype), _ptr(scratch), need,

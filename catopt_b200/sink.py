@@ -783,19 +783,21 @@ class B200CausalSoftmaxModule(_EvalBase):
 
     @property
     def is_streaming(self) -> bool:
-        return self._plan is not None and self._plan["bias"] is None
+        return self._plan is not None
 
     def forward_state(self, *xs: torch.Tensor) -> Any:
         """The raw carrier ``(m, l, a)`` (fp32) after folding the blocks one kernel
         call at a time — ``StreamingOMModule.forward_state`` (om_lower.py:1003-1040);
         ``ops.om_apply_state`` reads it out, ``ops.om_step_qk`` extends it."""
         plan = self._plan
-        if plan is None or plan["bias"] is not None:     # (the streaming step takes no explicit mask)
+        if plan is None:
             return self.eval_mod(*xs)
         ev = self._ev(xs)
-        return softmax_blocks_state(ev(plan["q"]), [ev(t) for t in plan["k_blocks"]],
-                                    [ev(t) for t in plan["v_blocks"]], plan["scale"], plan["causal"],
-                                    key_offset=plan["off"])
+        ks, vs = [ev(t) for t in plan["k_blocks"]], [ev(t) for t in plan["v_blocks"]]
+        if len(ks) != len(vs):                           # (one joined value tensor: cut it like the keys)
+            vs = list(torch.split(vs[0] if len(vs) == 1 else torch.cat(vs, dim=-2), [k.shape[-2] for k in ks], dim=-2))
+        return softmax_blocks_state(ev(plan["q"]), ks, vs, plan["scale"], plan["causal"], key_offset=plan["off"],
+                                    mask=None if plan["bias"] is None else ev(plan["bias"]))
 
     def _forward_impl(self, *xs: torch.Tensor) -> Any:
         plan = self._plan

@@ -381,6 +381,17 @@ int cb2_om_step(const void* q, const void* k, const void* v,
                 int B, int H, int Tq, int Tk, int dk, int dv, float scale,
                 int causal, int key_offset, int dtype, void* scratch,
                 size_t scratch_bytes, int* dev_status, void* stream);
+/* The same step for a carrier with an explicit attention mask (see cb2_om_bias_fwd):
+ *     state' = state (+) om_elem(scale * q k^T + bias, v)
+ * `bias` points at the columns of THIS block's keys: element (b, h, t, j) of the block at
+ * bias[b*stride_b + h*stride_h + t*stride_q + j]. */
+int cb2_om_bias_step(const void* q, const void* k, const void* v, const float* bias,
+                     long long bias_stride_b, long long bias_stride_h, long long bias_stride_q,
+                     const float* m_in, const float* l_in, const float* a_in,
+                     float* m_out, float* l_out, float* a_out,
+                     int B, int H, int Tq, int Tk, int dk, int dv, float scale,
+                     int causal, int key_offset, int dtype, void* scratch,
+                     size_t scratch_bytes, int* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -164,6 +164,35 @@ def test_om_bias_fwd_vs_torch_sdpa_in_fp64(dev, dtype, tol, B, H, Tq, Tk, d, msh
     assert got.dtype == dtype and rel_to_max(got, want) <= tol
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("Tq,mshape", [(256, (256, 640)), (3, (1, 2, 3, 640)), (70, (2, 1, 70, 640))])
+def test_om_step_with_a_mask_folds_blocks_into_the_masked_attention(dev, dtype, tol, Tq, mshape):
+    """Three key blocks folded one ``cb2_om_bias_step`` at a time (tile kernels for many rows, and for a
+    handful of rows too, since the decode kernel takes no mask), each with its columns of the mask:
+    the readout equals masked attention over the joined keys."""
+    import torch.nn.functional as F
+
+    from catopt_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(Tq)
+    B, H, d, sizes = 2, 2, 64, (128, 320, 192)
+    q = torch.randn(B, H, Tq, d, device=dev, generator=g).to(dtype)
+    ks = [torch.randn(B, H, n, d, device=dev, generator=g).to(dtype) for n in sizes]
+    vs = [torch.randn(B, H, n, d, device=dev, generator=g).to(dtype) for n in sizes]
+    bias = torch.randn(*mshape, device=dev, generator=g)
+    hide = torch.rand(*mshape, device=dev, generator=g) < 0.3
+    hide[..., 0] = False
+    bias = bias.masked_fill(hide, float("-inf"))
+    state, col = None, 0
+    for kb, vb in zip(ks, vs):
+        state = ops.om_step_qk(state, q, kb, vb, 0.125, False, col, bias=bias[..., col:col + kb.shape[2]])
+        col += kb.shape[2]
+    ops.check_device_status(dev)
+    want = F.scaled_dot_product_attention(q.double(), torch.cat(ks, 2).double(), torch.cat(vs, 2).double(),
+                                          attn_mask=bias.double(), scale=0.125)
+    assert rel_to_max(ops.om_apply_state(state), want) <= tol
+
+
 def test_om_bias_fwd_bool_mask_hidden_rows_and_the_causal_flag(dev):
     """A bool keep-mask goes in as 0 / -inf (the reference's ``attnbias``); a row with no visible key is
     NaN, as the reference's unclamped a / l; with the causal flag the two masks combine."""

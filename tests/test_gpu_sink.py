@@ -687,8 +687,12 @@ def test_om_term_with_an_explicit_mask_on_the_b200_module_matches_the_reference_
     with torch.no_grad():
         got = mod(q, *ks, *vs, m)
         want = ref(*(t.float() for t in (q, *ks, *vs)), m if m.dtype == torch.bool else m.float())
+        state = mod.forward_state(q, *ks, *vs, m)     # the streaming fold: one cb2_om_bias_step per key block
     assert got.dtype == dtype
     assert torch.equal(torch.isnan(got), torch.isnan(want))
+    streamed = ops.om_apply_state(state)
+    assert torch.equal(torch.isnan(streamed), torch.isnan(want))
+    assert _rel(streamed[~torch.isnan(want)], want[~torch.isnan(want)]) <= tol
     if kind == "bool":
         assert torch.isnan(want[..., 5, :]).all()
     ok = ~torch.isnan(want)

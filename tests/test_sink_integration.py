@@ -544,7 +544,7 @@ def test_om_carrier_with_an_explicit_mask_is_recognised_and_means_masked_attenti
     spec = _route(b200.B200Sink(), ir.root)
     assert spec.name == "b200_om_causal"
     mod = spec.lower(ir, None)
-    assert mod.is_batched and not mod.is_streaming        # the streaming step takes no explicit mask
+    assert mod.is_batched and mod.is_streaming
     # the term evaluates (reference bindings, fp64) to torch's masked attention, bool and float masks alike
     gen = torch.Generator().manual_seed(4)
     q = torch.randn(2, 3, Tq, 4, dtype=torch.float64, generator=gen)
