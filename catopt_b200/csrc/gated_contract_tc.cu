@@ -35,27 +35,10 @@
 namespace cb2 {
 namespace {
 
-// Optional per-stage timeline of one CTA, for tuning builds only: compile with
-// -DCB2_GC_TIMELINE and read g_gc_timeline back from the host.  Columns: 0 producer
-// about to issue, 1 group saw the stage land, 2 group signalled P, 3 MMA thread saw P,
-// 4 MMA thread issued its commit.
-#ifdef CB2_GC_TIMELINE
-__device__ long long g_gc_timeline[64][5];
-#define CB2_GC_TL(i, k, who)                                                              \
-  do {                                                                                    \
-    if (blockIdx.x == gridDim.x / 2 && threadIdx.x == (who) && (i) < 64) g_gc_timeline[i][k] = clock64(); \
-  } while (0)
-#else
-#define CB2_GC_TL(i, k, who) do {} while (0)
-#endif
-
 constexpr int kRows = 128;                    // query rows per CTA
 constexpr int kKeys = 64;                     // keys per stage
-#ifndef CB2_GC_STAGES
-#define CB2_GC_STAGES 2
-#define CB2_GC_CTAS_PER_SM 2
-#endif
-constexpr int kStages = CB2_GC_STAGES;
+constexpr int kStages = 2;                    // ring slots per CTA
+constexpr int kCtasPerSm = 2;
 constexpr int kGcThreads = 320;
 constexpr int kGcCompute = 256;
 constexpr uint32_t kSBytes = kRows * kKeys * 2;          // 16 KiB score sub-tile
@@ -71,7 +54,7 @@ constexpr uint32_t kGcSmemBytes = kGcOffMisc + 16 + 1024;
 constexpr uint32_t kColP = 128;
 constexpr uint32_t kGcTmemCols = 256;
 
-__global__ void __launch_bounds__(kGcThreads, CB2_GC_CTAS_PER_SM)
+__global__ void __launch_bounds__(kGcThreads, kCtasPerSm)
 gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_g,
                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                          int K, int dv, int row_tiles, int g_div, int g_mod, int* dev_status) {
@@ -125,7 +108,6 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
         if (use > 0 && !mbar_wait_abortable(&empty[slot], (use - 1) & 1, s_abort)) break;
         unsigned char* dst = smem + slot * kStageBytes;
         const int k0 = i * kKeys;
-        CB2_GC_TL(i, 0, 0);
         mbar_arrive_expect_tx(&full[slot], bytes);
         umma::tma_load_3d(dst, &map_s, k0, row0, b, &full[slot]);
         umma::tma_load_3d(dst + kSBytes, &map_g, k0, row0, gb, &full[slot]);
@@ -145,7 +127,6 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
         ok = mbar_wait_abortable(&full[slot], use & 1, s_abort) &&      // V_j landed
              mbar_wait_abortable(&p_ready[slot], use & 1, s_abort);     // P_j in tensor memory
         if (!ok) break;
-        CB2_GC_TL(i, 3, 32);
         umma::fence_after_sync();
         const uint32_t v_addr = ring + slot * kStageBytes + 2 * kSBytes;
         const uint32_t p_addr = tmem + kColP + slot * 32;
@@ -158,7 +139,6 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
           umma::mma_bf16_ts(tmem, p_addr + ks * 8, bdesc, idesc, i > 0 || ks > 0);
         }
         umma::mma_commit(&empty[slot]);
-        CB2_GC_TL(i, 4, 32);
       }
       if (ok) umma::mma_commit(acc_ready);
     }
@@ -173,7 +153,6 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
       const int slot = i % kStages, use = i / kStages;
       bool ok = mbar_wait_abortable(&full[slot], use & 1, s_abort);
       if (!__all_sync(0xffffffffu, ok)) break;
-      CB2_GC_TL(i, 1, 64);
       // P = bf16(s * g) for this thread's 32 keys of row r -> 16 packed columns of TMEM
       // (scores and gate share one swizzled layout; rows of a warp hit distinct banks)
       const unsigned char* s_tile = smem + slot * kStageBytes;
@@ -198,7 +177,6 @@ gated_contract_tc_kernel(const __grid_constant__ CUtensorMap map_s, const __grid
       umma::tmem_wait_st();
       umma::fence_before_sync();
       mbar_arrive(&p_ready[slot]);
-      CB2_GC_TL(i, 2, 64);
     }
     // epilogue: thread = (row, column half); accumulator -> bf16 -> staged tile -> TMA store
     bool ok = mbar_wait_abortable(acc_ready, 0, s_abort);

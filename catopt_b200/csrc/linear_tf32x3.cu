@@ -53,9 +53,6 @@ constexpr uint32_t kColX = 256;                        // x slots: 64 columns pe
 // (the first segment stores y, the others add to it), which keeps the error at the 512-deep level
 // whatever the depth.
 constexpr int kSegBlocks = 32;
-#ifndef CB2_LIN_PROBE
-#define CB2_LIN_PROBE 0   // tuning builds only: 1 = skip the MMAs, 2 = skip the split arithmetic and TMEM stores
-#endif
 
 __host__ __device__ constexpr uint32_t instr_desc_tf32(uint32_t M, uint32_t N) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
@@ -208,7 +205,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             const uint32_t wbase = smem_u32(smem + s * kStageB + kTileB);
             const uint32_t xh = tmem + kColX + s * 64u, xl = xh + 32u;
 #pragma unroll
-            for (int ks = 0; ks < (CB2_LIN_PROBE == 1 ? 0 : 4); ++ks) {
+            for (int ks = 0; ks < 4; ++ks) {
               const uint64_t wh = umma::smem_desc(wbase + ks * 32u, 16u, 1024u);
               const uint64_t wl = umma::smem_desc(wbase + kTileB + ks * 32u, 16u, 1024u);
               mma_tf32_ts(acc, xl + ks * 8u, wh, idesc, (kb > kb0) || (ks > 0));   // small terms first
@@ -234,10 +231,6 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         ok = mbar_wait_abortable(&full[s], (it / kStages) & 1, s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (CB2_LIN_PROBE == 2) {
-          mbar_arrive(&split[s]);
-          continue;
-        }
         const unsigned char* xrow = smem + s * kStageB + r * 128u;
         uint32_t hi[32], lo[32];
 #pragma unroll
