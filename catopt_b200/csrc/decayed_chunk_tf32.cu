@@ -16,20 +16,20 @@
 //   hi = the fp32 value itself (the tensor core reads its upper 19 bits, i.e. truncates it to TF32),
 //   lo = value - truncated value (exact in fp32):
 //   hi.hi + hi.lo + lo.hi, accumulated in fp32 tensor memory.
-// The state itself is carried in fp32 by the score warps (its hi tile is the
-// fp32 state), so its error does not grow with the number of chunks.
+// The state itself is carried in fp32 by warps 2-5 (its hi tile is the fp32
+// state), so its error does not grow with the number of chunks.
 //
 // Shared memory (224 KiB, one CTA per SM), 32 KiB tiles of 128 rows x 64 fp32 as
 // two 128-byte-swizzled sub-tiles of 32 columns (what a TMA box {32, 128}
-// writes): K of even chunks | K of odd chunks | K lo | V | V lo | Q (later the
+// writes): K of even chunks | K lo | K of odd chunks | V | V lo | Q (later the
 // staged output), and the state hi | lo tiles (64 x 64).  K is loaded a whole
 // chunk ahead into the tile the chunk before last has left, so that only the lo
 // tile has to be built between two chunks.
 // A tf32 operand whose rows run along the reduction (V in MMA2, V and K in MMA3:
-// "MN-major") must sit in the 128-byte swizzle with 32-byte atoms, so the V
-// split and the K rescale move each row's chunks from the TMA's 16-byte-atom
-// pattern to that one (a permutation inside the row's 128 bytes, so each thread
-// stays within the row it owns).
+// "MN-major") must sit in the 128-byte swizzle with 32-byte atoms: V's tensor
+// map asks the TMA for that pattern, and the K rescale moves each row's chunks
+// from the 16-byte-atom pattern MMA1 needs to that one (a permutation inside the
+// row's 128 bytes, so each thread stays within the row it owns).
 // Tensor memory (512 columns): S / P hi 0-127, P lo 128-255, O1 256-319,
 // O2 320-383, Q hi 384-447 (reused for D once MMA4 has run), Q lo 448-511.  Q and
 // P are A operands taken from tensor memory: an MMA with both tf32 operands in
@@ -38,12 +38,13 @@
 // N = 128, 46 at N = 64 (M = 64 and M = 128 alike): 7.1 k cycles of tensor pipe
 // per chunk at dk = dv = 64.
 //
-// Roles: warp 0 loads tiles with TMA; warp 1 issues the MMAs (MMA1, MMA4, MMA3,
-// MMA2: the state increment keeps the pipe busy while P is being built); warps
-// 2-5 put Q into tensor memory, build half of K lo, carry the state and, once
-// MMA1 has read K, rescale K for the state increment; warps 6-9 build the other
-// half of K lo, write the output of the chunk before, build V lo, and mask and
-// decay S into P.
+// Roles: warp 0 loads tiles with TMA; warp 1 issues the MMAs (MMA1 — its two
+// products against K itself as soon as K has landed, the one against K lo when
+// that tile is built —, MMA4, MMA3, MMA2: the state increment keeps the pipe busy
+// while P is being built); warps 2-5 put Q into tensor memory, build half of K lo,
+// carry the state and, once MMA1 has read K, rescale K for the state increment;
+// warps 6-9 build the other half of K lo, write the output of the chunk before,
+// build V lo, and mask and decay S into P.
 // Every wait is bounded: on expiry the CTA records CB2_WAIT_TIMEOUT and leaves.
 #include <algorithm>
 
