@@ -680,9 +680,17 @@ def run_ours(args) -> None:
     def step():
         ops.decayed_chunk_fwd(q, k, v, gamma, C, 1.0, out=o)
 
+    def region_status(region: str) -> None:
+        """A bounded device wait that ran out inside a timed region invalidates it: say which."""
+        try:
+            ops.check_device_status(dev)
+        except Exception as e:  # noqa: BLE001
+            raise SystemExit(f"rank {rank}: {e} after {region}") from e
+
     clk = ClockSampler(local)
     with clk:
         ms = time_steps(step, args.steps, args.warmup, world)
+    region_status("the headline region")
     ops.check_device_status(dev)
     tokens = B * T
     t_step = ms / args.steps / 1e3
@@ -730,6 +738,7 @@ def run_ours(args) -> None:
     clk_sus = ClockSampler(local)
     with clk_sus:
         ms_sus = time_steps(step, n_sus, 3, world)
+    region_status("the sustained loop")
     sus = clk_sus.summary()
     t_sus = ms_sus / n_sus / 1e3
     chunks_per_sm = B * H * (T // 128) / 148.0
@@ -750,6 +759,7 @@ def run_ours(args) -> None:
     clk_e2e = ClockSampler(local)   # its own sampler: this region is PCIe-bound and barely loads the SMs
     with clk_e2e:
         ms_e2e = time_steps(lambda: pipe.run(hq, hk, hv, ho), args.steps, args.warmup, world)
+    region_status("the end-to-end region")
     # same function, other segmenting (a slab has few heads: its segments start from precomputed
     # states): equal within bf16 rounding, checked with the library's own gate
     rep = verify.verify_equiv(o, ho.to(dev), rtol=1e-2)

@@ -92,24 +92,40 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar,
   return false;
 }
 
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
+// A wait's budget is counted on the SM's own cycle counter AND in polls: the wait gives up only
+// when more than `budget_ns` x 2 cycles have passed (2 s = 4e9 cycles: 2 s at 2 GHz, 3 s at a
+// power-capped 1.3 GHz) and it has really polled that long (at least budget / 128 ns polls, capped
+// at 2^20).  A wall-clock timer that the driver steps, or a stretch during which the context was
+// not running, therefore cannot end a wait that would have been satisfied.
+__device__ __forceinline__ long long sm_cycles() {
+  long long c;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
+  return c;
 }
-// Wait for kernels whose roles wait on one another: gives up after
-// `budget_ns` of wall time, or as soon as another role has raised `*abort`
-// (so one expired wait ends the whole CTA quickly instead of cascading).
+struct WaitBudget {
+  long long c0, cycles;
+  uint32_t min_polls;
+  __device__ __forceinline__ explicit WaitBudget(unsigned long long budget_ns)
+      : c0(sm_cycles()), cycles((long long)(budget_ns * 2ull)),
+        min_polls(budget_ns / 128ull > (1ull << 20) ? (1u << 20) : uint32_t(budget_ns / 128ull)) {}
+  __device__ __forceinline__ bool spent(uint32_t polls) const {
+    return polls >= min_polls && sm_cycles() - c0 > cycles;
+  }
+};
+
+// Wait for kernels whose roles wait on one another: gives up when its budget is spent (see
+// WaitBudget), or as soon as another role has raised `*abort` (so one expired wait ends the
+// whole CTA quickly instead of cascading).
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity,
                                                     volatile int* abort,
                                                     uint64_t budget_ns = 2000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  const WaitBudget budget(budget_ns);
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 31u) == 0) {
       if (*abort) return false;
-      if (globaltimer_ns() - t0 > budget_ns) {
+      if (budget.spent(i)) {
         *abort = 1;
         return false;
       }
@@ -118,21 +134,18 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
 }
 
 // Bounded wait for a flag in global memory that another CTA (or an earlier kernel) sets
-// (acquire).  Gives up after `budget_ns` of wall time, or as soon as a sibling thread has
+// (acquire).  Gives up when its budget is spent, or as soon as a sibling thread has
 // raised the shared `*abort` word; on expiry it raises `*abort` itself.  Never traps.
 __device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile int* abort,
                                                     unsigned long long budget_ns = 2000000000ull) {
-  unsigned long long t0 = 0;
-  for (unsigned it = 0;; ++it) {
+  const WaitBudget budget(budget_ns);
+  for (uint32_t it = 0;; ++it) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v != 0) return true;
     if (*abort) return false;
     if ((it & 63u) == 63u) {
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > budget_ns) { *abort = 1; return false; }
+      if (budget.spent(it)) { *abort = 1; return false; }
       __nanosleep(200);
     }
   }

@@ -154,16 +154,13 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
       int ok = 1;
       if (tid < i) {
         const int* f = flags + size_t(bh) * nchunk + tid;
-        unsigned long long t0 = 0;
-        for (unsigned it = 0;; ++it) {
+        const WaitBudget budget(2000000000ull);
+        for (uint32_t it = 0;; ++it) {
           int val;
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(val) : "l"(f) : "memory");
           if (val != 0) break;
           if ((it & 63u) == 63u) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) { ok = 0; break; }
+            if (budget.spent(it)) { ok = 0; break; }
             __nanosleep(100);
           }
         }

@@ -1,5 +1,5 @@
 // cb2_wait_for_flag: the bounded hand-off wait of the segmented kernels as a launch of its own.
-// One thread polls a device flag with `wait_flag_abortable` (acquire loads, wall-clock budget);
+// One thread polls a device flag with `wait_flag_abortable` (acquire loads, a budget counted in SM cycles and polls);
 // when the flag is non-zero the kernel simply ends, when the budget runs out it stores
 // CB2_WAIT_TIMEOUT into the caller's status word and ends as well.  Nothing is in flight when
 // it gives up (no copies, no tensor memory), so the context stays usable and the next launch
