@@ -92,11 +92,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar,
   return false;
 }
 
+// Default budget of a wait inside a kernel.  Long on purpose: memory traffic of a running kernel can
+// stand still for seconds while the driver rebuilds page tables (observed: eight processes with peer
+// access enabled, one of them in cudaMalloc, held a kernel's TMA stores for more than two seconds);
+// a wait that would have been satisfied must outlast that, and a real deadlock still ends.
+constexpr unsigned long long kDefaultWaitNs = 10000000000ull;
+
 // A wait's budget is counted on the SM's own cycle counter AND in polls: the wait gives up only
-// when more than `budget_ns` x 2 cycles have passed (2 s = 4e9 cycles: 2 s at 2 GHz, 3 s at a
-// power-capped 1.3 GHz) and it has really polled that long (at least budget / 128 ns polls, capped
-// at 2^20).  A wall-clock timer that the driver steps, or a stretch during which the context was
-// not running, therefore cannot end a wait that would have been satisfied.
+// when more than `budget_ns` x 2 cycles have passed (10 s at 2 GHz, 15 s at a power-capped 1.3 GHz
+// for the default) and it has really polled that long (at least budget / 128 ns polls, capped at
+// 2^20).  A wall-clock timer that the driver steps, or a stretch during which the context was not
+// running, therefore cannot end a wait that would have been satisfied.
 __device__ __forceinline__ long long sm_cycles() {
   long long c;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
@@ -115,10 +121,11 @@ struct WaitBudget {
 
 // Wait for kernels whose roles wait on one another: gives up when its budget is spent (see
 // WaitBudget), or as soon as another role has raised `*abort` (so one expired wait ends the
-// whole CTA quickly instead of cascading).
+// whole CTA quickly instead of cascading).  The wait that gives up leaves `site` (non-zero: a
+// kernel may pass the source line, so that the host can say which wait it was) in `*abort`.
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity,
                                                     volatile int* abort,
-                                                    uint64_t budget_ns = 2000000000ull) {
+                                                    uint64_t budget_ns = kDefaultWaitNs, int site = 1) {
   if (mbar_try_wait(bar, parity)) return true;
   const WaitBudget budget(budget_ns);
   for (uint32_t i = 1;; ++i) {
@@ -126,7 +133,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
     if ((i & 31u) == 0) {
       if (*abort) return false;
       if (budget.spent(i)) {
-        *abort = 1;
+        *abort = site;
         return false;
       }
     }
@@ -137,7 +144,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
 // (acquire).  Gives up when its budget is spent, or as soon as a sibling thread has
 // raised the shared `*abort` word; on expiry it raises `*abort` itself.  Never traps.
 __device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile int* abort,
-                                                    unsigned long long budget_ns = 2000000000ull) {
+                                                    unsigned long long budget_ns = kDefaultWaitNs, int site = 1) {
   const WaitBudget budget(budget_ns);
   for (uint32_t it = 0;; ++it) {
     int v;
@@ -145,7 +152,7 @@ __device__ __forceinline__ bool wait_flag_abortable(const int* flag, volatile in
     if (v != 0) return true;
     if (*abort) return false;
     if ((it & 63u) == 63u) {
-      if (budget.spent(it)) { *abort = 1; return false; }
+      if (budget.spent(it)) { *abort = site; return false; }
       __nanosleep(200);
     }
   }

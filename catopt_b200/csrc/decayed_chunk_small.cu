@@ -154,7 +154,7 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
       int ok = 1;
       if (tid < i) {
         const int* f = flags + size_t(bh) * nchunk + tid;
-        const WaitBudget budget(2000000000ull);
+        const WaitBudget budget(kDefaultWaitNs);
         for (uint32_t it = 0;; ++it) {
           int val;
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(val) : "l"(f) : "memory");

@@ -46,6 +46,7 @@ namespace cb2 {
 namespace {
 
 constexpr int kC = 128;                 // chunk rows = dk = dv
+constexpr unsigned long long kWaitNs = kDefaultWaitNs;   // budget of every wait; a wait that runs out reports its source line
 constexpr int kSlots = 5;                     // ring depth of the every-rate roles
 constexpr int kSlotsFast = 6;                 // ring depth of the common-case roles (two whole chunks)
 constexpr int kSlotsMax = 6;
@@ -198,7 +199,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         if (which == 1 && i < pre) continue;       // state-only chunk: no Q
         // K and V slots are used by every chunk; the two Q slots only from chunk `pre` (even) on
         const int slot = t % kSlotsFast, use = which == 1 ? (i - pre) / 2 : t / kSlotsFast;
-        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort)) break;
+        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort, kWaitNs, __LINE__)) break;
         const CUtensorMap* mp = which == 0 ? c.map_k : (which == 1 ? c.map_q : c.map_v);
         unsigned char* dst = smem + kOffRing + slot * kTile;
         const int row = (c.chunk0 + i) * kC;
@@ -221,9 +222,9 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         const uint32_t v_addr = ring_addr + (tv % kSlotsFast) * kTile;
         const bool state_only = i < pre;
         // MMA1: S' = Q K~^T  (K~ is ready once the compute group has scaled the tile)
-        if (!mbar_wait_abortable(B.kw_ready, ph, s_abort)) break;
+        if (!mbar_wait_abortable(B.kw_ready, ph, s_abort, kWaitNs, __LINE__)) break;
         if (!state_only) {
-          if (!mbar_wait_abortable(&B.full[tq % kSlotsFast], ((i - pre) / 2) & 1, s_abort)) break;
+          if (!mbar_wait_abortable(&B.full[tq % kSlotsFast], ((i - pre) / 2) & 1, s_abort, kWaitNs, __LINE__)) break;
           umma::fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
@@ -234,9 +235,9 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         // MMA4: A (+)= K~^T V.  Issued ahead of MMA2/MMA3: it does not depend on the mask, so the
         // tensor core works through it while the compute group turns S' into P'.  The compute
         // group must have finished copying the previous accumulator into Sb first.
-        if (!mbar_wait_abortable(&B.full[tv % kSlotsFast], (tv / kSlotsFast) & 1, s_abort)) break;
+        if (!mbar_wait_abortable(&B.full[tv % kSlotsFast], (tv / kSlotsFast) & 1, s_abort, kWaitNs, __LINE__)) break;
         if (i > 0 || has_in) {
-          if (!mbar_wait_abortable(B.sb_ready, (has_in ? i : i - 1) & 1, s_abort)) break;
+          if (!mbar_wait_abortable(B.sb_ready, (has_in ? i : i - 1) & 1, s_abort, kWaitNs, __LINE__)) break;
         }
         umma::fence_after_sync();
 #pragma unroll
@@ -251,8 +252,8 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
           continue;
         }
         // MMA2: O' = P' V
-        if (!mbar_wait_abortable(B.p_ready, ph, s_abort)) break;
-        if (i > pre && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
+        if (!mbar_wait_abortable(B.p_ready, ph, s_abort, kWaitNs, __LINE__)) break;
+        if (i > pre && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort, kWaitNs, __LINE__)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -289,7 +290,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
     // K~_j = K_j . g^(-r - C.mj), in place, as soon as the tile has landed
     auto scale_k = [&](int j) -> bool {
       const int tk = 3 * j;
-      bool ok = mbar_wait_abortable(&B.full[tk % kSlotsFast], (tk / kSlotsFast) & 1, s_abort);
+      bool ok = mbar_wait_abortable(&B.full[tk % kSlotsFast], (tk / kSlotsFast) & 1, s_abort, kWaitNs, __LINE__);
       if (!__all_sync(0xffffffffu, ok)) return false;
       const float kf = exp2f(c.lg * float(r + kC * ((c.chunk0 + j) % m)));
       unsigned char* k_tile = smem + kOffRing + (tk % kSlotsFast) * kTile;
@@ -339,7 +340,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
           mbar_arrive(B.sb_ready);
         }
         if (i + 1 < nchunk && !scale_k(i + 1)) break;
-        ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
+        ok = mbar_wait_abortable(B.o_ready, ph, s_abort, kWaitNs, __LINE__);
         if (!__all_sync(0xffffffffu, ok)) break;
         umma::fence_after_sync();
         continue;
@@ -363,7 +364,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
           // computed ahead of the launch; otherwise the predecessor CTA's raw accumulator
           if (!c.prestaged) {
             const int* flag = c.seg_flag + size_t(c.seg - 1) * c.n_bh + c.bh;
-            ok = wait_flag_abortable(flag, s_abort);
+            ok = wait_flag_abortable(flag, s_abort, kWaitNs, __LINE__);
             if (!__all_sync(0xffffffffu, ok)) break;
           }
           load_start_state(c.seg_state, c.seg, c.n_bh, c.bh, r, cb0, c.prestaged ? c.pieces_per_seg : 0, c.g_piece,
@@ -396,7 +397,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         fence_proxy_async_smem();
         mbar_arrive(B.sb_ready);
       }
-      ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
+      ok = mbar_wait_abortable(B.s_ready, ph, s_abort, kWaitNs, __LINE__);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       // (a) P' = bf16(S') at and below the diagonal, 0 above, packed into TMEM over S'
@@ -437,7 +438,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
       // (k) the next chunk's K tile, scaled ahead of its MMA1
       if (i + 1 < nchunk && !scale_k(i + 1)) break;
       // (c) o_i = g^(r + C.mi) / scale . O'
-      ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
+      ok = mbar_wait_abortable(B.o_ready, ph, s_abort, kWaitNs, __LINE__);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       // staged in the chunk's own Q tile (MMA1 and MMA3 are done with it) in the swizzled layout the
@@ -465,7 +466,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
       }
       fence_proxy_async_smem();
       mbar_arrive(B.wg_sync);
-      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort, kWaitNs, __LINE__);
       wg_phase ^= 1;
       if (!__all_sync(0xffffffffu, ok)) break;
       if (tid == 64) {
@@ -477,7 +478,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
     }
     // hand the raw accumulator to the next segment of this head
     if (c.seg + 1 < c.n_seg && !c.prestaged) {
-      bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
+      bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort, kWaitNs, __LINE__);
       if (__all_sync(0xffffffffu, ok)) {
         umma::fence_after_sync();
         const int cb0 = half * 2;
@@ -495,7 +496,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         }
         __threadfence();
         mbar_arrive(B.wg_sync);
-        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort, kWaitNs, __LINE__);
         wg_phase ^= 1;
         if (ok && tid == 64) {
           int* flag = c.seg_flag + size_t(c.seg) * c.n_bh + c.bh;
@@ -600,7 +601,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const int ntiles = 3 * nchunk;
       for (int t = 0; t < ntiles; ++t) {
         const int slot = t % kSlots, use = t / kSlots;
-        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort)) break;
+        if (use > 0 && !mbar_wait_abortable(&B.empty[slot], (use - 1) & 1, s_abort, kWaitNs, __LINE__)) break;
         const int i = t / 3, which = t % 3;  // 0: K, 1: Q, 2: V
         const CUtensorMap* m = which == 0 ? &map_k : (which == 1 ? &map_q : &map_v);
         unsigned char* dst = smem + kOffRing + slot * kTile;
@@ -623,8 +624,8 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t q_addr = ring_addr + (tq % kSlots) * kTile;
         const uint32_t v_addr = ring_addr + (tv % kSlots) * kTile;
         // MMA1: S = Q K^T
-        if (!mbar_wait_abortable(&B.full[tk % kSlots], (tk / kSlots) & 1, s_abort)) break;
-        if (!mbar_wait_abortable(&B.full[tq % kSlots], (tq / kSlots) & 1, s_abort)) break;
+        if (!mbar_wait_abortable(&B.full[tk % kSlots], (tk / kSlots) & 1, s_abort, kWaitNs, __LINE__)) break;
+        if (!mbar_wait_abortable(&B.full[tq % kSlots], (tq / kSlots) & 1, s_abort, kWaitNs, __LINE__)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -632,9 +633,9 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                          idesc_kk, ks > 0);
         umma::mma_commit(B.s_ready);
         // MMA2: O1 = P V
-        if (!mbar_wait_abortable(B.p_ready, ph, s_abort)) break;
-        if (!mbar_wait_abortable(&B.full[tv % kSlots], (tv / kSlots) & 1, s_abort)) break;
-        if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort)) break;
+        if (!mbar_wait_abortable(B.p_ready, ph, s_abort, kWaitNs, __LINE__)) break;
+        if (!mbar_wait_abortable(&B.full[tv % kSlots], (tv / kSlots) & 1, s_abort, kWaitNs, __LINE__)) break;
+        if (i > 0 && !mbar_wait_abortable(B.o_free, (i - 1) & 1, s_abort, kWaitNs, __LINE__)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -642,7 +643,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             umma::desc_mnmajor(v_addr, ks), idesc_kn, ks > 0);
         // MMA3: O2 = Q Sb   (the state is zero before the first chunk of the sequence)
         if (i > 0 || has_in) {
-          if (!mbar_wait_abortable(B.sb_ready, (has_in ? i : i - 1) & 1, s_abort)) break;
+          if (!mbar_wait_abortable(B.sb_ready, (has_in ? i : i - 1) & 1, s_abort, kWaitNs, __LINE__)) break;
           umma::fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
@@ -652,7 +653,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         umma::mma_commit(B.o_ready);
         umma::mma_commit(&B.empty[tq % kSlots]);
         // MMA4: St (+)= Kw^T V
-        if (!mbar_wait_abortable(B.kw_ready, ph, s_abort)) break;
+        if (!mbar_wait_abortable(B.kw_ready, ph, s_abort, kWaitNs, __LINE__)) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -688,7 +689,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
     for (int i = 0; i < nchunk; ++i) {
       const uint32_t ph = i & 1;
-      bool ok = mbar_wait_abortable(B.s_ready, ph, s_abort);
+      bool ok = mbar_wait_abortable(B.s_ready, ph, s_abort, kWaitNs, __LINE__);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
       // (a) P = bf16(S . decay), packed into TMEM over S: one table load and one
@@ -728,7 +729,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (i > 0 || has_in) {
         const int cb0 = half * 2;
         if (i > 0) {
-          ok = mbar_wait_abortable(B.st_ready, (i - 1) & 1, s_abort);
+          ok = mbar_wait_abortable(B.st_ready, (i - 1) & 1, s_abort, kWaitNs, __LINE__);
           if (!__all_sync(0xffffffffu, ok)) break;
           umma::fence_after_sync();
           umma::tmem_ld32(lane_base + kColSt + cb0 * 32, va);
@@ -739,7 +740,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           // (prestaged: every segment's start state was computed before this launch)
           if (!prestaged) {
             const int* flag = seg_flag + size_t(seg - 1) * n_bh + bh;
-            ok = wait_flag_abortable(flag, s_abort);
+            ok = wait_flag_abortable(flag, s_abort, kWaitNs, __LINE__);
             if (!__all_sync(0xffffffffu, ok)) break;
           }
           load_start_state(seg_state, seg, n_bh, bh, r, cb0, prestaged ? pieces_per_seg : 0,
@@ -785,7 +786,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_arrive(B.kw_ready);
       // (c) o_i = (O1 + g^(r+1) O2) / scale, staged in shared memory in the
       // swizzled layout the TMA store expects
-      ok = mbar_wait_abortable(B.o_ready, ph, s_abort);
+      ok = mbar_wait_abortable(B.o_ready, ph, s_abort, kWaitNs, __LINE__);
       if (!__all_sync(0xffffffffu, ok)) break;
       umma::fence_after_sync();
 #pragma unroll 1
@@ -810,7 +811,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_arrive(B.o_free);
       fence_proxy_async_smem();
       mbar_arrive(B.wg_sync);
-      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+      ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort, kWaitNs, __LINE__);
       wg_phase ^= 1;
       if (!__all_sync(0xffffffffu, ok)) break;
       if (tid == 64) {  // whole tile written: two {64 x 128} boxes go out asynchronously
@@ -822,7 +823,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
     // hand the state to the next segment of this head: St after the last MMA4
     if (seg + 1 < n_seg && !prestaged) {
-      bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
+      bool ok = mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort, kWaitNs, __LINE__);
       if (__all_sync(0xffffffffu, ok)) {
         umma::fence_after_sync();
         const int cb0 = half * 2;
@@ -839,7 +840,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         __threadfence();
         mbar_arrive(B.wg_sync);
-        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort);
+        ok = mbar_wait_abortable(B.wg_sync, wg_phase, s_abort, kWaitNs, __LINE__);
         wg_phase ^= 1;
         if (ok && tid == 64) {
           int* flag = seg_flag + size_t(seg) * n_bh + bh;
@@ -854,12 +855,12 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __syncwarp();
   if (warp == 1 && lane == 0 && !*s_abort && nchunk > 0) {
     // the final commit (st_ready of the last chunk) covers every MMA issued
-    mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort);
+    mbar_wait_abortable(B.st_ready, (nchunk - 1) & 1, s_abort, kWaitNs, __LINE__);
   }
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
-  if (tid == 0 && *s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT);
+  if (tid == 0 && *s_abort && dev_status) atomicExch(dev_status, CB2_WAIT_TIMEOUT | (*s_abort << 8));   // which wait: its source line
   if (warp == 1) {
     __syncwarp();
     umma::tmem_dealloc(tmem, 512);

@@ -51,7 +51,8 @@ def check_device_status(device: torch.device | None = None) -> None:
     code = int(w.item())
     if code != 0:
         w.zero_()
-        raise B200Error(f"device status: {_lib.status_str(code)} (status {code})")
+        site = f", wait at source line {code >> 8} of the kernel" if code >> 8 else ""
+        raise B200Error(f"device status: {_lib.status_str(code & 0xff)} (status {code & 0xff}{site})")
 
 
 def wait_for_flag(flag: torch.Tensor, budget_us: int = 1000) -> None:

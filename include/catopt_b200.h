@@ -18,7 +18,10 @@
  *     sized by the matching *_scratch_bytes() query;
  *   - kernels that wait on an asynchronous copy bound the wait; when a wait
  *     runs out they store CB2_WAIT_TIMEOUT into `*dev_status` (device int,
- *     may be NULL) and return early instead of spinning.
+ *     may be NULL) and return early instead of spinning.  The status is the
+ *     low byte of that word; the decayed-attention kernel puts the source line
+ *     of the wait that ran out into the bits above it (status >> 8), as a
+ *     diagnostic.
  */
 #ifndef CATOPT_B200_H
 #define CATOPT_B200_H
