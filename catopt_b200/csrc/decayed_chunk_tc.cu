@@ -59,7 +59,7 @@ constexpr uint32_t kOffO = kSlots * kTile;          // output staging tile of th
 constexpr uint32_t kOffSb = kSlotsMax * kTile;
 constexpr uint32_t kOffPow = kOffSb + kTile;                 // float[32 zeros | g^0 .. g^128]
 constexpr uint32_t kOffBars = kOffPow + 704;                 // 8-byte aligned
-constexpr int kNumBars = 2 * kSlotsMax + 8;
+constexpr int kNumBars = 2 * kSlotsMax + 9;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;       // tmem base, abort flag
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;        // + alignment slack
 
@@ -81,6 +81,7 @@ struct Bars {
   uint64_t* st_ready;  // MMA4 done            (MMA -> WG)
   uint64_t* sb_ready;  // Sb written, St scaled (WG -> MMA, 256)
   uint64_t* wg_sync;   // barrier among the 256 compute threads
+  uint64_t* kw_taken;  // the MMA thread has seen kw_ready of a chunk (MMA -> WG)
 };
 
 
@@ -223,6 +224,7 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
         const bool state_only = i < pre;
         // MMA1: S' = Q K~^T  (K~ is ready once the compute group has scaled the tile)
         if (!mbar_wait_abortable(B.kw_ready, ph, s_abort, kWaitNs, __LINE__)) break;
+        mbar_arrive(B.kw_taken);            // (see scale_k: the group may now signal the chunk after this one)
         if (!state_only) {
           if (!mbar_wait_abortable(&B.full[tq % kSlotsFast], ((i - pre) / 2) & 1, s_abort, kWaitNs, __LINE__)) break;
           umma::fence_after_sync();
@@ -309,6 +311,14 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
       for (int jj = 0; jj < 8; ++jj)
         *reinterpret_cast<uint4*>(k_tile + umma::tile_chunk_offset(r, half * 64 + jj * 8)) = x[jj];
       fence_proxy_async_smem();
+      // One signal ahead of the MMA thread at most: a waiter on a phase parity cannot tell phase j - 1 from
+      // phase j + 1, and in a state-only chunk nothing else keeps this group from signalling chunk j before
+      // the MMA thread has looked at the signal of chunk j - 1 (it then waits for a phase that needs it to
+      // move first).  Seen as waits running out on idle, down-clocked GPUs (eight ranks, host pipeline).
+      if (j > 0) {
+        ok = mbar_wait_abortable(B.kw_taken, (j - 1) & 1, s_abort, kWaitNs, __LINE__);
+        if (!__all_sync(0xffffffffu, ok)) return false;
+      }
       mbar_arrive(B.kw_ready);
       return true;
     };
@@ -526,7 +536,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
   Bars B{bars, bars + kSlotsMax, bars + 2 * kSlotsMax, bars + 2 * kSlotsMax + 1, bars + 2 * kSlotsMax + 2,
          bars + 2 * kSlotsMax + 3, bars + 2 * kSlotsMax + 4, bars + 2 * kSlotsMax + 5, bars + 2 * kSlotsMax + 6,
-         bars + 2 * kSlotsMax + 7};
+         bars + 2 * kSlotsMax + 7, bars + 2 * kSlotsMax + 8};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x % n_bh;
@@ -569,6 +579,7 @@ decayed_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(B.st_ready, 1);
     mbar_init(B.sb_ready, kComputeThreads);
     mbar_init(B.wg_sync, kComputeThreads);
+    mbar_init(B.kw_taken, 1);
     *s_abort = 0;
     mbar_fence_init();
   }
