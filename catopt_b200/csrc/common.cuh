@@ -92,14 +92,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar,
   return false;
 }
 
-// Default budget of a wait inside a kernel.  Long on purpose: memory traffic of a running kernel can
-// stand still for seconds while the driver rebuilds page tables (observed: eight processes with peer
-// access enabled, one of them in cudaMalloc, held a kernel's TMA stores for more than two seconds);
-// a wait that would have been satisfied must outlast that, and a real deadlock still ends.
-constexpr unsigned long long kDefaultWaitNs = 10000000000ull;
+// Default budget of a wait inside a kernel: far beyond any legitimate latency, short enough that a
+// protocol error shows up as a status word within seconds instead of a hung GPU.
+constexpr unsigned long long kDefaultWaitNs = 4000000000ull;
 
 // A wait's budget is counted on the SM's own cycle counter AND in polls: the wait gives up only
-// when more than `budget_ns` x 2 cycles have passed (10 s at 2 GHz, 15 s at a power-capped 1.3 GHz
+// when more than `budget_ns` x 2 cycles have passed (4 s at 2 GHz, 6 s at a power-capped 1.3 GHz
 // for the default) and it has really polled that long (at least budget / 128 ns polls, capped at
 // 2^20).  A wall-clock timer that the driver steps, or a stretch during which the context was not
 // running, therefore cannot end a wait that would have been satisfied.

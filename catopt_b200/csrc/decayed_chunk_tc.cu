@@ -314,7 +314,9 @@ __device__ __forceinline__ void fast_roles(const FastCtx& c) {
       // One signal ahead of the MMA thread at most: a waiter on a phase parity cannot tell phase j - 1 from
       // phase j + 1, and in a state-only chunk nothing else keeps this group from signalling chunk j before
       // the MMA thread has looked at the signal of chunk j - 1 (it then waits for a phase that needs it to
-      // move first).  Seen as waits running out on idle, down-clocked GPUs (eight ranks, host pipeline).
+      // move first, and every wait of the CTA runs out).  Happened with eight ranks on one node in the host
+      // pipeline, never on one to four GPUs; holding the MMA thread back 40 us at its start makes it certain
+      // without this wait and impossible with it.
       if (j > 0) {
         ok = mbar_wait_abortable(B.kw_taken, (j - 1) & 1, s_abort, kWaitNs, __LINE__);
         if (!__all_sync(0xffffffffu, ok)) return false;

@@ -45,16 +45,6 @@ class DecayedHostPipeline:
         self.module = module
         mk = lambda d: [torch.empty(self.slab, H, T, d, dtype=dtype, device=self.device) for _ in range(2)]  # noqa: E731
         self.dq, self.dk_, self.dv_ = mk(dk), mk(dk), mk(dv)
-        # Let the caching allocator hold blocks of the result's size before the first forward: a
-        # cudaMalloc in the middle of the pipeline rebuilds page tables (on every peer, when peer access
-        # is enabled) and can hold up the memory traffic of the kernel that is running meanwhile.
-        warm = [torch.empty(self.slab, H, T, dv, dtype=dtype, device=self.device) for _ in range(3)]
-        del warm
-        # ... and one forward on the (still uninitialised) staging buffers, so that the module's own
-        # first-call allocations (constants, scratch, status word) are behind us as well
-        with torch.no_grad():
-            self.module(self.dq[0], self.dk_[0], self.dv_[0])
-        torch.cuda.synchronize(self.device)
         self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
         self.ev_in = [torch.cuda.Event() for _ in range(2)]
         self.ev_comp = [torch.cuda.Event() for _ in range(2)]
