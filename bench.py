@@ -899,6 +899,10 @@ def run_profile_case(args) -> None:
         bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
         hp_ = torch.randn(8 * 1024 * 16, device=dev, generator=gen)
         fn = lambda: ops.diag_scan_states(ap_, bp_, hp_)  # noqa: E731
+    elif args.profile_case == "decode":     # one query row per head against 32768 keys, bf16: K + V = 537 MB
+        qd = _randn_bf16((32, 128), gen).view(1, 32, 1, 128)
+        kd, vd = (_randn_bf16((32 * 32768, 128), gen).view(1, 32, 32768, 128) for _ in range(2))
+        fn = lambda: ops.om_step_qk(None, qd, kd, vd, 0.1, True, -(32768 - 1))  # noqa: E731
     elif args.profile_case == "verify":     # 13 checks x 4 probes of config 5's tensor: 436 MB
         ref = _randn_bf16((13, 4 * 4 * 512 * 1024), gen)
         outp = ref.clone()
@@ -925,7 +929,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "decayed_fp32", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep"],
+                    choices=["decayed", "decayed_fp32", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep", "decode"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

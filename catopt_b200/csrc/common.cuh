@@ -31,6 +31,15 @@ __host__ __device__ inline bool aligned16(const void* p) {
 
 // ---- bf16 <-> fp32 --------------------------------------------------------
 // A bf16 is the upper half of an fp32: widening is exact and is a shift/mask.
+// 16-byte asynchronous copy global -> shared (bypasses L1 and the register file), commit / wait groups.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ float bf16lo_to_f32(uint32_t packed) {
   return __uint_as_float(packed << 16);
 }

@@ -194,28 +194,45 @@ om_causal_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
 
 // Decode shapes (at most kDecRows query rows, many keys): the step is a stream over
 // K and V, so it is laid out for memory bandwidth instead of for tiles.  A warp
-// takes 32 keys at a time.  Scores: lane = key, the lane walks its key's row in
-// 16-byte pieces against the query rows kept in shared memory (no cross-lane
-// traffic, ~6 instructions per key).  Softmax: one warp max and one warp sum per
-// query row and batch.  Values: lane = four value columns, the 32 probabilities are
-// broadcast one by one with a shuffle while the value rows stream in coalesced.
-// The eight warps of a CTA fold their carriers in shared memory and write one
-// partial carrier per key split.
+// takes 32 keys at a time.  Keys: asynchronous 16-byte copies, coalesced (a copy
+// instruction = 128 bytes of four neighbouring rows), into a swizzled shared-memory
+// slot, two 128-byte segments of the 32 rows in flight ahead of the one in use (with
+// lane = key straight from global memory every load instruction touched 32 cache
+// lines, and the L1 tag stage, not DRAM, set the pace: 5.0 TB/s; now 6.5).  Scores:
+// lane = key, the lane walks its key's row in the slot in 16-byte pieces against the
+// query rows kept in shared memory (no cross-lane traffic).  Softmax: one warp max
+// and one warp sum per query row and batch.  Values: lane = four value columns, the
+// rows stream in coalesced in register batches (the next batch in flight while one is
+// used, the first one already during the scores), the 32 probabilities broadcast one
+// by one with a shuffle.  The eight warps of a CTA fold their carriers in shared
+// memory and write one partial carrier per key split.
 constexpr int kDecRows = 8;
 constexpr int kDecWarps = 8;
+constexpr int kDecSlot = 32 * 128;   // a warp's key slot: 128 bytes of 32 key rows
+constexpr int kDecSmem = kDecWarps * 2 * kDecSlot;   // two slots per warp (>= the carriers of 8 rows x 8 warps)
+static_assert(kDecSmem >= kDecWarps * kDecRows * 128 * 4, "the warps' carriers reuse the key slots");
+// CTAs per SM the decode kernel is compiled for (registers: two batches of value rows in flight per
+// thread plus ROWS carriers; three CTAs would spill) and its key splits are sized for.  One query row
+// of bf16 keys, B1 H32 Tk 65536 d128: 165 us at two CTAs per SM, 203 us at three.
+__host__ __device__ constexpr int dec_ctas_per_sm(int rows) { return rows <= 4 ? 2 : 1; }
 
 template <int DTYPE>
 struct DecLd;
 template <>
 struct DecLd<CB2_BF16> {
   static constexpr int kPiece = 8;    // elements per 16-byte piece
-  __device__ static void piece(const void* p, size_t i, float (&x)[8]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + i);
+  __device__ static void piece(const uint4 u, float (&x)[8]) {
     x[0] = bf16lo_to_f32(u.x); x[1] = bf16hi_to_f32(u.x); x[2] = bf16lo_to_f32(u.y); x[3] = bf16hi_to_f32(u.y);
     x[4] = bf16lo_to_f32(u.z); x[5] = bf16hi_to_f32(u.z); x[6] = bf16lo_to_f32(u.w); x[7] = bf16hi_to_f32(u.w);
   }
-  __device__ static void four(const void* p, size_t i, float (&x)[4]) {
-    const uint2 u = __ldcs(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i));
+  // four value columns: loaded raw (kept in registers while in flight), converted at use
+  using Raw4 = uint2;
+  static constexpr int kValueRows = 16;    // value rows per register batch (32 registers)
+  __device__ static Raw4 four_raw(const void* p, size_t i) {
+    return __ldcs(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i));
+  }
+  __device__ static Raw4 zero_raw() { return make_uint2(0u, 0u); }
+  __device__ static void four(const Raw4 u, float (&x)[4]) {
     x[0] = bf16lo_to_f32(u.x); x[1] = bf16hi_to_f32(u.x); x[2] = bf16lo_to_f32(u.y); x[3] = bf16hi_to_f32(u.y);
   }
   __device__ static float one(const void* p, size_t i) {
@@ -225,12 +242,16 @@ struct DecLd<CB2_BF16> {
 template <>
 struct DecLd<CB2_F32> {
   static constexpr int kPiece = 4;
-  __device__ static void piece(const void* p, size_t i, float (&x)[4]) {
-    const float4 u = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
-    x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+  __device__ static void piece(const uint4 u, float (&x)[4]) {
+    x[0] = __uint_as_float(u.x); x[1] = __uint_as_float(u.y); x[2] = __uint_as_float(u.z); x[3] = __uint_as_float(u.w);
   }
-  __device__ static void four(const void* p, size_t i, float (&x)[4]) {
-    const float4 u = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+  using Raw4 = float4;
+  static constexpr int kValueRows = 8;
+  __device__ static Raw4 four_raw(const void* p, size_t i) {
+    return __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+  }
+  __device__ static Raw4 zero_raw() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ static void four(const Raw4 u, float (&x)[4]) {
     x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
   }
   __device__ static float one(const void* p, size_t i) { return static_cast<const float*>(p)[i]; }
@@ -239,7 +260,7 @@ struct DecLd<CB2_F32> {
 // dk a multiple of the 16-byte piece (8 bf16 / 4 fp32), dv a multiple of 4, both <= 128;
 // Tq <= ROWS (1, 2, 4 or 8).
 template <int DTYPE, int ROWS>
-__global__ void __launch_bounds__(kDecWarps * 32)
+__global__ void __launch_bounds__(kDecWarps * 32, dec_ctas_per_sm(ROWS))
 om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v, int Tq,
                  int Tk, int dk, int dv, float scale, int causal, int key_offset, int split_len,
                  float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pa) {
@@ -247,8 +268,11 @@ om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
   constexpr int P = L::kPiece;
   __shared__ __align__(16) float s_q[ROWS][128];
   __shared__ float s_m[kDecWarps][ROWS], s_l[kDecWarps][ROWS];
-  __shared__ float s_a[kDecWarps][ROWS][128];
+  // two 4 KB key slots per warp while the keys stream; the warps' carriers afterwards
+  extern __shared__ __align__(128) unsigned char s_buf[];
+  float (*s_a)[ROWS][128] = reinterpret_cast<float (*)[ROWS][128]>(s_buf);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* slots = s_buf + warp * (2 * kDecSlot);
   const int bh = blockIdx.y, z = blockIdx.x;
   const int c0 = lane * 4;
   const bool vcol = c0 < dv;
@@ -268,26 +292,78 @@ om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
     for (int e = 0; e < 4; ++e) a[r][e] = 0.f;
   }
   const int npiece = dk / P;
-  for (int j0 = k_beg + warp * 32; j0 < k_lim; j0 += kDecWarps * 32) {
+  const int nseg = (npiece + 7) / 8;             // 128-byte segments of a key row
+  const size_t rowb = size_t(dk) * (16 / P);     // bytes of a key row
+  const unsigned char* kb = static_cast<const unsigned char*>(k) + kbase * (16 / P);
+  // Keys come in coalesced and asynchronously: one copy instruction moves 128 bytes of four
+  // neighbouring key rows (lane = 16-byte piece), eight instructions one segment of the warp's 32 keys,
+  // straight into one of the warp's two shared-memory slots (chunk c of row r at c ^ (r % 8):
+  // conflict-free for the copy and for the read-back with lane = key).  Two segments are always in
+  // flight ahead of the one being scored.
+  const int j_first = k_beg + warp * 32;
+  const int nblk = j_first < k_lim ? (k_lim - j_first + kDecWarps * 32 - 1) / (kDecWarps * 32) : 0;
+  int is_blk = 0, is_seg = 0, is_n = 0;          // next (block, segment) to copy, and how many were
+  auto k_issue = [&]() {
+    if (is_blk < nblk) {
+      const int pc = is_seg * 8 + (lane & 7);
+      if (pc < npiece) {
+        const int jb = j_first + is_blk * (kDecWarps * 32);
+        unsigned char* dst = slots + (is_n & 1) * kDecSlot;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int row = u * 4 + (lane >> 3);
+          const int jr = min(jb + row, k_lim - 1);
+          cp_async16(dst + row * 128 + (((lane & 7) ^ (row & 7)) << 4), kb + size_t(jr) * rowb + size_t(pc) * 16);
+        }
+      }
+      if (++is_seg == nseg) { is_seg = 0; ++is_blk; }
+    }
+    ++is_n;
+    cp_async_commit();                            // one group per call, empty past the end
+  };
+  k_issue();
+  k_issue();
+  constexpr int kVB = L::kValueRows;
+  typename L::Raw4 va[kVB], vb[kVB];
+  int use_n = 0;
+  for (int j0 = j_first; j0 < k_lim; j0 += kDecWarps * 32) {
     // ---- scores of this lane's key against every query row
     const int j = j0 + lane;
     const bool live = j < k_lim;
-    const size_t krow = kbase + size_t(live ? j : k_lim - 1) * dk;
+    auto v_issue = [&](typename L::Raw4 (&buf)[kVB], int jj0) {
+#pragma unroll
+      for (int u = 0; u < kVB; ++u) {
+        const int jr = min(j0 + jj0 + u, k_lim - 1);
+        buf[u] = vcol ? L::four_raw(v, vbase + size_t(jr) * dv + c0) : L::zero_raw();
+      }
+    };
     float sc[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) sc[r] = 0.f;
-#pragma unroll 8
-    for (int pc = 0; pc < npiece; ++pc) {
-      float x[P];
-      L::piece(k, krow + size_t(pc) * P, x);
+    for (int seg = 0; seg < nseg; ++seg, ++use_n) {
+      cp_async_wait_one();                        // all but the newest group: this segment has landed
+      __syncwarp();
+      if (seg + 1 == nseg) v_issue(va, 0);        // the first value rows fly during the scores and the softmax
+      const unsigned char* slot = slots + (use_n & 1) * kDecSlot;
+      const int nc = min(8, npiece - seg * 8);
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
+      for (int c = 0; c < 8; ++c) {
+        if (c < nc) {
+          float x[P];
+          L::piece(*reinterpret_cast<const uint4*>(slot + lane * 128 + ((c ^ (lane & 7)) << 4)), x);
+          const int e0 = (seg * 8 + c) * P;
 #pragma unroll
-        for (int e4 = 0; e4 < P; e4 += 4) {
-          const float4 qq = *reinterpret_cast<const float4*>(&s_q[r][pc * P + e4]);   // broadcast read
-          sc[r] = fmaf(qq.x, x[e4], fmaf(qq.y, x[e4 + 1], fmaf(qq.z, x[e4 + 2], fmaf(qq.w, x[e4 + 3], sc[r]))));
+          for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+            for (int e4 = 0; e4 < P; e4 += 4) {
+              const float4 qq = *reinterpret_cast<const float4*>(&s_q[r][e0 + e4]);   // broadcast read
+              sc[r] = fmaf(qq.x, x[e4], fmaf(qq.y, x[e4 + 1], fmaf(qq.z, x[e4 + 2], fmaf(qq.w, x[e4 + 3], sc[r]))));
+            }
+          }
         }
       }
+      __syncwarp();
+      k_issue();                                  // into the slot just read
     }
     // ---- softmax bookkeeping per row: p of this lane's key, running (m, l), rescaled a
     float p[ROWS];
@@ -309,29 +385,32 @@ om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
       for (int e = 0; e < 4; ++e) a[r][e] *= alpha;
       m[r] = mn;
     }
-    // ---- values: a[r][lane's 4 columns] += sum_jj p_jj[r] * v_jj[columns]
-    const int nlive = min(32, k_lim - j0);
-#pragma unroll 1
-    for (int jj0 = 0; jj0 < nlive; jj0 += 8) {
-      float vx[8][4];
+    // ---- values: a[r][lane's 4 columns] += sum_jj p_jj[r] * v_jj[columns]; the rows come in register
+    // batches, the next batch in flight while one is used (rows past the end repeat the last row: p = 0)
+    auto v_use = [&](const typename L::Raw4 (&buf)[kVB], int jj0) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int jr = min(j0 + jj0 + u, k_lim - 1);
-        if (vcol) L::four(v, vbase + size_t(jr) * dv + c0, vx[u]);
-        else vx[u][0] = vx[u][1] = vx[u][2] = vx[u][3] = 0.f;
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < kVB; ++u) {
+        float vx[4];
+        L::four(buf[u], vx);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-          const float pj = __shfl_sync(0xffffffffu, p[r], jj0 + u);   // 0 for keys past the end
+          const float pj = __shfl_sync(0xffffffffu, p[r], jj0 + u);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) a[r][e] = fmaf(pj, vx[u][e], a[r][e]);
+          for (int e = 0; e < 4; ++e) a[r][e] = fmaf(pj, vx[e], a[r][e]);
         }
       }
+    };
+#pragma unroll
+    for (int b = 0; b < 32 / kVB; b += 2) {
+      v_issue(vb, (b + 1) * kVB);
+      v_use(va, b * kVB);
+      if (b + 2 < 32 / kVB) v_issue(va, (b + 2) * kVB);
+      v_use(vb, (b + 1) * kVB);
     }
   }
+  cp_async_wait_all();
   // fold the eight warps' carriers (in warp order, so the result is deterministic)
+  __syncthreads();   // the carriers take the place of the key slots
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     if (lane == 0) {
@@ -411,10 +490,11 @@ __global__ void om_combine_kernel(const float* __restrict__ m_in, const float* _
   }
 }
 
-// Key splits of the decode kernel: as many as fit in ONE wave of four CTAs per SM
+// Key splits of the decode kernel: as many as fit in ONE wave of resident CTAs
 // (rounding up would leave a second, nearly empty wave), at least 256 keys each.
-int om_decode_splits(int B, int H, int Tk) {
-  long long z = (4 * 148) / ((long long)B * H);
+int om_decode_splits(int B, int H, int Tq, int Tk) {
+  const int rows = Tq <= 1 ? 1 : Tq <= 2 ? 2 : Tq <= 4 ? 4 : 8;
+  long long z = (dec_ctas_per_sm(rows) * 148) / ((long long)B * H);
   const long long most = (Tk + 255) / 256;
   if (z > most) z = most;
   if (z > 65535) z = 65535;
@@ -496,7 +576,7 @@ extern "C" int cb2_om_causal_fwd(const void* q, const void* k, const void* v, vo
 
 extern "C" size_t cb2_om_step_scratch_bytes(int B, int H, int Tq, int Tk, int dv) {
   if (B <= 0 || H <= 0 || Tq <= 0 || Tk <= 0 || dv <= 0) return 0;
-  const int z = Tq <= cb2::kDecRows && Tk >= 256 ? cb2::om_decode_splits(B, H, Tk) : cb2::om_step_splits(B, H, Tq, Tk);
+  const int z = Tq <= cb2::kDecRows && Tk >= 256 ? cb2::om_decode_splits(B, H, Tq, Tk) : cb2::om_step_splits(B, H, Tq, Tk);
   return (z > 1 || (Tq <= cb2::kDecRows && Tk >= 256)) ? size_t(z) * B * H * Tq * (size_t(dv) + 2) * sizeof(float) : 0;
 }
 
@@ -517,7 +597,7 @@ int om_step_impl(const void* q, const void* k, const void* v, const float* m_in,
   // a handful of query rows against many keys: the streaming (memory-bound) kernel (it takes no bias)
   if (!bias.p && om_decode_shape(Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && scratch &&
       !(reinterpret_cast<uintptr_t>(scratch) & 15u)) {
-    int Zd = om_decode_splits(B, H, Tk);
+    int Zd = om_decode_splits(B, H, Tq, Tk);
     if (scratch_bytes >= size_t(Zd) * rows * (size_t(dv) + 2) * sizeof(float)) {
       const int len = (Tk + Zd - 1) / Zd;
       Zd = (Tk + len - 1) / len;
@@ -526,9 +606,14 @@ int om_step_impl(const void* q, const void* k, const void* v, const float* m_in,
       float* da = dl + size_t(Zd) * rows;
       const dim3 dgrid(Zd, B * H);
       if (dtype != CB2_BF16 && dtype != CB2_F32) return CB2_UNSUPPORTED_DTYPE;
-#define CB2_DECODE(DT, R)                                                                                  \
-  om_decode_kernel<DT, R><<<dgrid, kDecWarps * 32, 0, st>>>(q, k, v, Tq, Tk, dk, dv, scale, causal ? 1 : 0, \
-                                                            key_offset, len, dm, dl, da)
+#define CB2_DECODE(DT, R)                                                                                       \
+  do {                                                                                                           \
+    if (cudaFuncSetAttribute(om_decode_kernel<DT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                             kDecSmem) != cudaSuccess)                                                           \
+      return CB2_LAUNCH_FAIL;                                                                                    \
+    om_decode_kernel<DT, R><<<dgrid, kDecWarps * 32, kDecSmem, st>>>(q, k, v, Tq, Tk, dk, dv, scale,            \
+                                                                     causal ? 1 : 0, key_offset, len, dm, dl, da); \
+  } while (0)
       const bool bf = dtype == CB2_BF16;
       if (Tq == 1) { if (bf) CB2_DECODE(CB2_BF16, 1); else CB2_DECODE(CB2_F32, 1); }
       else if (Tq == 2) { if (bf) CB2_DECODE(CB2_BF16, 2); else CB2_DECODE(CB2_F32, 2); }

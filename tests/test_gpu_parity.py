@@ -1033,6 +1033,40 @@ def test_om_step_decode_shapes_split_the_keys(dev, Tq, Tk, causal):
     assert (st[0].double().cpu() - want[0]).abs().max() <= 1e-5
 
 
+@pytest.mark.parametrize("dtype,Tq,Tk,dk,dv", [
+    (torch.bfloat16, 1, 5001, 128, 128),     # two full 128-byte segments per key row
+    (torch.bfloat16, 2, 4100, 72, 100),      # second segment holds one 16-byte piece; dv off the lane grid
+    (torch.bfloat16, 4, 3000, 8, 4),         # one piece per key row
+    (torch.bfloat16, 8, 2600, 64, 64),
+    (torch.float32, 1, 5001, 128, 128),      # four segments
+    (torch.float32, 1, 700, 20, 36),         # five pieces
+    (torch.float32, 3, 2049, 100, 8),        # four segments, the last with one piece
+    (torch.float32, 7, 1000, 32, 128),
+])
+def test_om_step_decode_key_row_layouts(dev, dtype, Tq, Tk, dk, dv):
+    """The decode kernel copies key rows into shared memory in 128-byte segments: row lengths on and off
+    that grid, every query-row count, key counts off the 32-key batches, against fp64 attention of the
+    newest Tq positions over all Tk keys."""
+    from catopt_b200 import _lib, ops
+
+    B, H = 2, 3
+    assert _lib.load().cb2_om_step_scratch_bytes(B, H, Tq, Tk, dv) > 0
+    gen = torch.Generator(device="cuda").manual_seed(Tk + dk)
+    q = torch.randn(B, H, Tq, dk, device=dev, generator=gen).to(dtype)
+    k = torch.randn(B, H, Tk, dk, device=dev, generator=gen).to(dtype)
+    v = torch.randn(B, H, Tk, dv, device=dev, generator=gen).to(dtype)
+    scale = 1 / math.sqrt(dk)
+    st = ops.om_step_qk(None, q, k, v, scale, True, -(Tk - Tq))
+    ops.check_device_status(dev)
+    sc = (q.double() @ k.double().transpose(-1, -2)) * scale
+    t = torch.arange(Tq, device=dev).view(Tq, 1)
+    j = torch.arange(Tk, device=dev).view(1, Tk)
+    sc = sc.masked_fill(j - (Tk - Tq) > t, float("-inf"))
+    want = torch.softmax(sc, -1) @ v.double()
+    assert rel_to_max(ops.om_apply_state(st), want) <= FP32_TOL
+    assert (st[0].double() - sc.amax(-1)).abs().max() <= 1e-5
+
+
 def test_om_streaming_prefill_chunks_on_the_tensor_cores(dev):
     """bf16 prefill in chunks against a growing cache: every chunk of queries is folded
     against the cached keys and its own keys with the carrier passed along, on the
