@@ -582,6 +582,56 @@ class B200ChunkedDecayModule(_EvalBase):
         return self.eval_mod(*xs) if out is None else out     # fp64 / awkward length: generic module, same device
 
 
+def decayed_pairwise_plan(root: Any) -> dict | None:
+    """The reference's pairwise plan (``build_decayed_plan``, decayed_lower.py:353-368) for
+    the members that are NOT decayed attention of one sequence at one rate per head — a row
+    gate on the intra element, another decay mask per arm, a missing cross pair — and so
+    have no state-carry form."""
+    return build_decayed_plan(root)
+
+
+def _make_pairwise_decay_module():
+    from catopt_carriers.decayed_lower import ChunkedDecayModule
+
+    class B200PairwiseDecayModule(ChunkedDecayModule):
+        """``ChunkedDecayModule`` (decayed_lower.py:381-724) with the intra-chunk element
+        ``(s * d) @ v`` of every arm in ``cb2_gated_contract_fwd``: the stacked scores are
+        gated and contracted in one kernel (the product lives in tensor memory as the MMA's
+        A operand and is never written out), one decay mask shared by all arms indexed in
+        place.  Plan, operand stacking, row gates, scales, the cross pairs and the assembly
+        stay the reference's own code.  fp64 tensors take the reference's eager product on
+        the same device; host tensors are refused."""
+
+        def __init__(self, ir: IR, param_values: dict | None = None) -> None:
+            super().__init__(ir, param_values)
+            self.kernel_calls = 0
+
+        def _forward_intra(self, plan, ev, env, x, like):
+            if not like.is_cuda:
+                raise B200Error("B200PairwiseDecayModule runs on CUDA tensors only (no CPU fallback)")
+            if like.dtype not in (torch.float32, torch.bfloat16):
+                return super()._forward_intra(plan, ev, env, x, like)
+            ab = plan["score_ab"]
+            if ab is None:
+                scores = self._stack_terms(plan["score_terms"], ev)
+            else:
+                scores = torch.matmul(self._stack_terms([a for a, _ in ab], ev),
+                                      self._stack_terms([b for _, b in ab], ev))
+            masks = plan["decay_terms"]
+            if all(m == masks[0] for m in masks):
+                gate = self._const(masks[0], like)
+            else:
+                gate = self._pad_stacked(torch.stack([self._const(m, like) for m in masks]), scores.dim())
+            out = ops.gated_contract(scores, gate.to(scores.dtype), self._stack_terms(plan["v_intra"], ev))
+            self.kernel_calls += 1
+            if any(r is not None for r in plan["intra_row"]):
+                out = self._row_stack(plan["intra_row"], like, len(plan["chunk"])) * out
+            div = self._scales("intra", plan["intra_scale"], env, x, like)
+            return out / div.reshape(-1, *((1,) * (out.dim() - 1)))
+
+    return B200PairwiseDecayModule
+
+
 # --------------------------------------------------------------------------- om causal
 def _scaled_scores(t: Any) -> tuple | None:
     """Scores of one key block -> (q, k, scale).  Spellings: ``matmul(q, k^T)``
@@ -1239,6 +1289,14 @@ class B200Sink(TorchSink):
                     "b200_om_decayed_chunked",
                     lambda ir, p: B200ChunkedDecayModule(ir, param_values=p),
                     lambda term: decayed_plan(term) is not None,
+                    _engaged,
+                    (frozenset({"concat"}), frozenset({"add", "mul", "div", "matmul"}),
+                     frozenset({"om_decayed", "decay", "decay_vec"})),
+                ),
+                "b200_om_decayed_pairwise": ExecutorSpec(
+                    "b200_om_decayed_pairwise",
+                    lambda ir, p: _make_pairwise_decay_module()(ir, param_values=p),
+                    lambda term: decayed_pairwise_plan(term) is not None,
                     _engaged,
                     (frozenset({"concat"}), frozenset({"add", "mul", "div", "matmul"}),
                      frozenset({"om_decayed", "decay", "decay_vec"})),

@@ -208,6 +208,44 @@ def test_really_extracted_ragged_decayed_term_runs_on_the_kernel_and_matches_the
     ops.check_device_status(DEV)
 
 
+@pytest.mark.parametrize("kw", [dict(intra_row=True), dict(second_rate=True), dict(drop_pair=True),
+                                dict(intra_row=True, second_rate=True)])
+@pytest.mark.parametrize("dtype,shape,tol", [(torch.float32, (2, 3, 48, 8, 16), 1e-5),
+                                             (torch.float32, (1, 4, 256, 64, 64), 1e-5),
+                                             (torch.bfloat16, (2, 4, 256, 64, 64), 2e-2)])
+def test_row_gated_and_two_rate_decayed_arms_on_the_pairwise_module_match_the_reference_executor(kw, dtype, shape, tol):
+    """The members of the decayed family that have no state-carry form (a decay-row gate on the intra
+    element, a second rate in the later arms, a missing cross pair): routed to `b200_om_decayed_pairwise`,
+    the intra products of all arms run in one `cb2_gated_contract_fwd`, and the result equals the
+    reference's own pairwise executor and its generic evaluation on the same device."""
+    from catopt_torch.adapters import TorchSink
+    from catopt_torch.torch_bridge import IRModule
+    from decayed_variants import variant_term
+
+    B, H, T, d, C = shape
+    ir = variant_term(B, H, T, d, C, 4.0, **kw)
+    gen = torch.Generator().manual_seed(T + d)
+    q, k, v = (torch.randn(B, H, T, d, generator=gen).div(d ** 0.25).to(dtype).to(DEV) for _ in range(3))
+    rates = {"g": torch.linspace(0.85, 0.98, H).to(dtype).to(DEV), "g2": torch.linspace(0.6, 0.9, H).to(dtype).to(DEV)}
+    vals = {n: rates[n] for n in ir.params}
+    spec = _route(b200.B200Sink(), ir.root)
+    assert spec.name == "b200_om_decayed_pairwise"
+    mod = spec.lower(ir, vals)
+    assert isinstance(mod, BatchedExecutor) and spec.engaged(mod) and mod.n_blocks == T // C
+    rspec = _route(TorchSink(), ir.root)
+    assert rspec.name == "om_decayed_chunked"
+    ref = rspec.lower(ir, vals)
+    with torch.no_grad():
+        got = mod(q, k, v)
+        want = ref(q, k, v)
+        plain = IRModule(ir, vals)(q, k, v)
+    assert mod.kernel_calls == 1
+    assert got.dtype == want.dtype and got.shape == want.shape
+    assert _rel(got, want) <= tol
+    assert _rel(got, plain) <= tol
+    ops.check_device_status(DEV)
+
+
 # --------------------------------------------------------------------------- (c) scan, omd, om causal
 def _scan_term(T, d):
     """applyd(affd_compose(... aff_diag(a_t, select(u, 0, t)) ...), h) over T steps, per-step decays."""

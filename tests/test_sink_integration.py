@@ -33,8 +33,8 @@ def _route(sink, term):
 def test_b200_specs_come_first_and_are_executor_specs():
     s = b200.B200Sink()
     names = list(s.executors)
-    assert names[:7] == ["b200_om_decayed_chunked", "b200_om_causal", "b200_om_streaming", "b200_scan_all",
-                         "b200_scan", "b200_omd", "b200_linear_chain"]
+    assert names[:8] == ["b200_om_decayed_chunked", "b200_om_decayed_pairwise", "b200_om_causal",
+                         "b200_om_streaming", "b200_scan_all", "b200_scan", "b200_omd", "b200_linear_chain"]
     assert "om_decayed_chunked" in names and names[-1] == "generic"
     assert all(isinstance(v, ExecutorSpec) for v in s.executors.values())
 
@@ -52,9 +52,11 @@ def test_uniform_chunked_term_routes_to_b200(per_head):
     assert b200.decayed_state_carry_plan(quad.root) is None
 
 
-def test_non_state_carry_variants_are_declined():
+def test_non_state_carry_variants_go_to_the_pairwise_spec():
     """Terms the reference's pairwise executor accepts but that are not the
-    uniform state-carry form fall through to the reference's own spec."""
+    uniform state-carry form are declined by the state-carry spec and taken by
+    the pairwise one (the reference's module with its intra element in the
+    gated-contraction kernel), ahead of the reference's own spec."""
     chunked, _ = make_golden._decayed_terms(1, 2, 48, 8, 16, True, 1.0)
     arms = list(chunked.root.args)
     # drop one cross summand from the last arm: pair (2,0) is missing
@@ -63,7 +65,35 @@ def test_non_state_carry_variants_are_declined():
     broken = Op.make("concat", *arms[:-1], last.args[0], dim=-2)
     s = b200.B200Sink()
     assert b200.decayed_state_carry_plan(broken) is None
-    assert _route(s, broken).name == "om_decayed_chunked"
+    assert _route(s, broken).name == "b200_om_decayed_pairwise"
+    assert s.executors["om_decayed_chunked"].accepts(broken)
+
+
+@pytest.mark.parametrize("kw", [dict(intra_row=True), dict(second_rate=True), dict(drop_pair=True),
+                                dict(intra_row=True, second_rate=True)])
+def test_row_gated_and_two_rate_arms_route_to_the_pairwise_spec(kw):
+    """The variants of the reference's own executor tests (tests/test_decayed_lower.py:440-482
+    there): a decay-row gate on the intra element, a second rate in the later arms' masks, a
+    missing cross pair.  None is decayed attention at one rate, so the state-carry plans decline
+    them; the pairwise spec lowers them to the reference's module with the B200 intra element,
+    which refuses host tensors like every other B200 module."""
+    from catopt_b200 import B200Error
+    from decayed_variants import variant_term
+
+    ir = variant_term(2, 3, 48, 8, 16, 2.0, **kw)
+    s = b200.B200Sink()
+    assert b200.decayed_plan(ir.root) is None
+    spec = _route(s, ir.root)
+    assert spec.name == "b200_om_decayed_pairwise"
+    pv = {"g": torch.tensor([0.9, 0.95, 0.8]), "g2": torch.tensor([0.7, 0.85, 0.99])}
+    mod = spec.lower(ir, {n: pv[n] for n in ir.params})
+    assert isinstance(mod, BatchedExecutor) and spec.engaged(mod) and mod.n_blocks == 3
+    q, k, v = (torch.randn(2, 3, 48, 8) for _ in range(3))
+    with pytest.raises(B200Error):
+        mod(q, k, v)
+    # the plain uniform term and the gate written inside the division keep the state-carry spec
+    assert _route(s, variant_term(2, 3, 48, 8, 16, 2.0).root).name == "b200_om_decayed_chunked"
+    assert _route(s, variant_term(2, 3, 48, 8, 16, 2.0, gate_inside=True).root).name == "b200_om_decayed_chunked"
 
 
 def test_lowered_module_conforms_to_ports_and_refuses_cpu():
@@ -128,7 +158,7 @@ def _scan_term(T=6, d=8):
 def test_scan_term_routes_to_b200_scan_and_keeps_reference_plan():
     ir = _scan_term()
     s = b200.B200Sink()
-    assert "b200_scan" in list(s.executors)[:5]
+    assert "b200_scan" in list(s.executors)[:6]
     spec = _route(s, ir.root)
     assert spec.name == "b200_scan"
     vals = {"a": torch.full((8,), 0.9), "h0": torch.ones(8)}
