@@ -3,7 +3,7 @@
 catopt routes an extracted term to the first ``ExecutorSpec`` of
 ``Sink.executors`` whose ``carrier`` is not ``None`` and whose ``accepts(term)``
 is true (catopt_orchestrator/optimize.py:485-495); mapping order is routing
-order.  ``B200Sink`` puts seven B200 specs in front of the torch ones:
+order.  ``B200Sink`` puts eight B200 specs in front of the torch ones:
 
 * ``b200_om_decayed_chunked`` — the uniform K-chunk decayed term of
   ``om_decayed_kway_blocks`` (catopt_carriers/om.py:3076-3152).  ``accepts``
@@ -15,8 +15,14 @@ order.  ``B200Sink`` puts seven B200 specs in front of the torch ones:
   sign=-1)``, one constant scale.  Terms over a ragged partition — what
   extraction really returns when the K-way law fires at two levels, e.g. pieces
   of 32,32,32,32,128,128,128 rows, which the reference's executor declines — are
-  recognised by ``decayed_ragged_plan``.  Anything else is declined, so the
-  reference's pairwise executor (or the generic module) still takes it.
+  recognised by ``decayed_ragged_plan``.  Anything else is declined and goes to
+  the next spec.
+* ``b200_om_decayed_pairwise`` — whatever else ``build_decayed_plan`` accepts: a
+  decay-row gate on the intra element, a second rate in some arms' masks, a missing
+  cross pair (tests/test_decayed_lower.py:440-482 there).  These are not decayed
+  attention of one sequence at one rate and have no state-carry form; they run the
+  reference's ``ChunkedDecayModule`` with the intra element ``(s * d) @ v`` of all
+  arms in one ``cb2_gated_contract_fwd``.
 * ``b200_om_causal`` — causal softmax attention over a sequence of key/value blocks in
   its online-softmax carrier form ``om_apply(<om_compose tree of om_elem(masked
   scores_i, v_i)>)`` (``om_causal_plan``), causal or unmasked; one ``cb2_om_fwd``.
@@ -40,7 +46,7 @@ order.  ``B200Sink`` puts seven B200 specs in front of the torch ones:
   (catopt_core/laws/tensor.py:1293-1300) before ``_fold_weight_chains``
   (torch_bridge.py:2456-2510) folds it.
 
-Both modules embed a plain ``IRModule`` (``eval_mod``) to evaluate operand
+The modules embed a plain ``IRModule`` (``eval_mod``) to evaluate operand
 sub-terms, as every batched module of the reference does, and make one C-ABI
 call for the hot part.  ``B200Sink.verify`` is the GPU verify gate.
 """
