@@ -259,11 +259,12 @@ struct DecLd<CB2_F32> {
 
 // dk a multiple of the 16-byte piece (8 bf16 / 4 fp32), dv a multiple of 4, both <= 128;
 // Tq <= ROWS (1, 2, 4 or 8).
-template <int DTYPE, int ROWS>
+// BIAS: an additive fp32 mask over this block's keys (-inf hides a key), read through strides.
+template <int DTYPE, int ROWS, bool BIAS>
 __global__ void __launch_bounds__(kDecWarps * 32, dec_ctas_per_sm(ROWS))
 om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v, int Tq,
                  int Tk, int dk, int dv, float scale, int causal, int key_offset, int split_len,
-                 float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pa) {
+                 float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pa, const OmBias bias) {
   using L = DecLd<DTYPE>;
   constexpr int P = L::kPiece;
   __shared__ __align__(16) float s_q[ROWS][128];
@@ -369,8 +370,12 @@ om_decode_kernel(const void* __restrict__ q, const void* __restrict__ k, const v
     float p[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      const bool hidden = !live || r >= Tq || (causal && j + key_offset > r);
+      bool hidden = !live || r >= Tq || (causal && j + key_offset > r);
       float sv = hidden ? -INFINITY : sc[r];
+      if (BIAS && !hidden) {                      // lane = key: one coalesced row of the mask per query row
+        sv += __ldg(bias.p + (bh / bias.H) * bias.sb + (bh % bias.H) * bias.sh + (long long)r * bias.sq + j);
+        hidden = sv == -INFINITY;
+      }
       float mb = sv;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, off));
@@ -594,8 +599,8 @@ int om_step_impl(const void* q, const void* k, const void* v, const float* m_in,
   const size_t smem = (size_t(2 * dk) * (kBlk + 4) + size_t(kBlk) * dv + size_t(kBlk) * (kBlk + 4)) * sizeof(float);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t rows = size_t(B) * H * Tq;
-  // a handful of query rows against many keys: the streaming (memory-bound) kernel (it takes no bias)
-  if (!bias.p && om_decode_shape(Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && scratch &&
+  // a handful of query rows against many keys: the streaming (memory-bound) kernel
+  if (om_decode_shape(Tq, Tk, dk, dv, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && scratch &&
       !(reinterpret_cast<uintptr_t>(scratch) & 15u)) {
     int Zd = om_decode_splits(B, H, Tq, Tk);
     if (scratch_bytes >= size_t(Zd) * rows * (size_t(dv) + 2) * sizeof(float)) {
@@ -606,19 +611,25 @@ int om_step_impl(const void* q, const void* k, const void* v, const float* m_in,
       float* da = dl + size_t(Zd) * rows;
       const dim3 dgrid(Zd, B * H);
       if (dtype != CB2_BF16 && dtype != CB2_F32) return CB2_UNSUPPORTED_DTYPE;
-#define CB2_DECODE(DT, R)                                                                                       \
+#define CB2_DECODE_B(DT, R, HAS)                                                                                 \
   do {                                                                                                           \
-    if (cudaFuncSetAttribute(om_decode_kernel<DT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+    if (cudaFuncSetAttribute(om_decode_kernel<DT, R, HAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                              kDecSmem) != cudaSuccess)                                                           \
       return CB2_LAUNCH_FAIL;                                                                                    \
-    om_decode_kernel<DT, R><<<dgrid, kDecWarps * 32, kDecSmem, st>>>(q, k, v, Tq, Tk, dk, dv, scale,            \
-                                                                     causal ? 1 : 0, key_offset, len, dm, dl, da); \
+    om_decode_kernel<DT, R, HAS><<<dgrid, kDecWarps * 32, kDecSmem, st>>>(                                      \
+        q, k, v, Tq, Tk, dk, dv, scale, causal ? 1 : 0, key_offset, len, dm, dl, da, bias);                      \
+  } while (0)
+#define CB2_DECODE(DT, R)                                                                                        \
+  do {                                                                                                           \
+    if (bias.p) CB2_DECODE_B(DT, R, true);                                                                       \
+    else CB2_DECODE_B(DT, R, false);                                                                             \
   } while (0)
       const bool bf = dtype == CB2_BF16;
       if (Tq == 1) { if (bf) CB2_DECODE(CB2_BF16, 1); else CB2_DECODE(CB2_F32, 1); }
       else if (Tq == 2) { if (bf) CB2_DECODE(CB2_BF16, 2); else CB2_DECODE(CB2_F32, 2); }
       else if (Tq <= 4) { if (bf) CB2_DECODE(CB2_BF16, 4); else CB2_DECODE(CB2_F32, 4); }
       else { if (bf) CB2_DECODE(CB2_BF16, 8); else CB2_DECODE(CB2_F32, 8); }
+#undef CB2_DECODE_B
 #undef CB2_DECODE
       CB2_LAUNCH_CHECK();
       om_combine_kernel<<<unsigned((rows * 32 + 255) / 256), 256, 0, st>>>(m_in, l_in, a_in, dm, dl, da, m_out,

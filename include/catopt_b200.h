@@ -387,7 +387,8 @@ int cb2_om_step(const void* q, const void* k, const void* v,
 /* The same step for a carrier with an explicit attention mask (see cb2_om_bias_fwd):
  *     state' = state (+) om_elem(scale * q k^T + bias, v)
  * `bias` points at the columns of THIS block's keys: element (b, h, t, j) of the block at
- * bias[b*stride_b + h*stride_h + t*stride_q + j]. */
+ * bias[b*stride_b + h*stride_h + t*stride_q + j].  Every path of cb2_om_step takes it, the
+ * streaming decode kernel (at most 8 query rows, 256 keys or more) included. */
 int cb2_om_bias_step(const void* q, const void* k, const void* v, const float* bias,
                      long long bias_stride_b, long long bias_stride_h, long long bias_stride_q,
                      const float* m_in, const float* l_in, const float* a_in,

@@ -167,9 +167,9 @@ def test_om_bias_fwd_vs_torch_sdpa_in_fp64(dev, dtype, tol, B, H, Tq, Tk, d, msh
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL)])
 @pytest.mark.parametrize("Tq,mshape", [(256, (256, 640)), (3, (1, 2, 3, 640)), (70, (2, 1, 70, 640))])
 def test_om_step_with_a_mask_folds_blocks_into_the_masked_attention(dev, dtype, tol, Tq, mshape):
-    """Three key blocks folded one ``cb2_om_bias_step`` at a time (tile kernels for many rows, and for a
-    handful of rows too, since the decode kernel takes no mask), each with its columns of the mask:
-    the readout equals masked attention over the joined keys."""
+    """Three key blocks folded one ``cb2_om_bias_step`` at a time (tile kernels for many rows; a handful
+    of rows takes the tile kernel for the short blocks and the streaming decode kernel for the 320-key
+    one), each with its columns of the mask: the readout equals masked attention over the joined keys."""
     import torch.nn.functional as F
 
     from catopt_b200 import ops
@@ -1065,6 +1065,44 @@ def test_om_step_decode_key_row_layouts(dev, dtype, Tq, Tk, dk, dv):
     want = torch.softmax(sc, -1) @ v.double()
     assert rel_to_max(ops.om_apply_state(st), want) <= FP32_TOL
     assert (st[0].double().reshape(B, H, Tq) - sc.amax(-1)).abs().max() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype,Tq,Tk,dk,dv,causal", [(torch.bfloat16, 1, 5001, 128, 128, False),
+                                                       (torch.bfloat16, 4, 3000, 64, 64, True),
+                                                       (torch.float32, 2, 2049, 72, 40, True),
+                                                       (torch.float32, 8, 1000, 32, 128, False)])
+def test_om_step_decode_with_a_mask(dev, dtype, Tq, Tk, dk, dv, causal):
+    """The streaming decode kernel with an additive mask over the block's keys (float bias with hidden
+    entries, broadcast over heads; whole 32-key batches hidden, so a warp sees batches without a visible
+    key), alone and combined with the causal flag, against fp64 attention."""
+    from catopt_b200 import ops
+
+    B, H = 2, 3
+    gen = torch.Generator(device="cuda").manual_seed(Tk + dv)
+    q = torch.randn(B, H, Tq, dk, device=dev, generator=gen).to(dtype)
+    k = torch.randn(B, H, Tk, dk, device=dev, generator=gen).to(dtype)
+    v = torch.randn(B, H, Tk, dv, device=dev, generator=gen).to(dtype)
+    bias = torch.randn(B, 1, Tq, Tk, device=dev, generator=gen)
+    bias = bias.masked_fill(torch.rand(B, 1, Tq, Tk, device=dev, generator=gen) < 0.3, float("-inf"))
+    bias[..., 64:160] = float("-inf")
+    bias[..., 0] = 0.0
+    scale = 1 / math.sqrt(dk)
+    st = ops.om_step_qk(None, q, k, v, scale, causal, -(Tk - Tq), bias=bias)
+    ops.check_device_status(dev)
+    sc = (q.double() @ k.double().transpose(-1, -2)) * scale + bias.double()
+    if causal:
+        t = torch.arange(Tq, device=dev).view(Tq, 1)
+        j = torch.arange(Tk, device=dev).view(1, Tk)
+        sc = sc.masked_fill(j - (Tk - Tq) > t, float("-inf"))
+    want = torch.softmax(sc, -1) @ v.double()
+    assert rel_to_max(ops.om_apply_state(st), want) <= FP32_TOL
+    assert (st[0].double().reshape(B, H, Tq) - sc.amax(-1)).abs().max() <= 1e-5
+    # the same step through the tile kernel (keys in two short blocks) gives the same carrier readout
+    half = 200
+    k0, v0, k1, v1 = (t.contiguous() for t in (k[:, :, :half], v[:, :, :half], k[:, :, half:], v[:, :, half:]))
+    s2 = ops.om_step_qk(None, q, k0, v0, scale, causal, -(Tk - Tq), bias=bias[..., :half])
+    s2 = ops.om_step_qk(s2, q, k1, v1, scale, causal, half - (Tk - Tq), bias=bias[..., half:])
+    assert rel_to_max(ops.om_apply_state(s2), want) <= FP32_TOL
 
 
 def test_om_streaming_prefill_chunks_on_the_tensor_cores(dev):
