@@ -142,7 +142,9 @@ def test_linear_is_linear_at_published_size(dev):
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL)])
 @pytest.mark.parametrize("B,H,Tq,Tk,d,mshape", [(2, 4, 384, 384, 128, (384, 384)), (1, 3, 200, 333, 64, (1, 3, 200, 333)),
                                                (2, 2, 128, 512, 64, (2, 1, 128, 512)), (1, 2, 130, 70, 32, (130, 1)),
-                                               (2, 2, 64, 256, 128, (1, 1, 1, 256))])
+                                               (2, 2, 64, 256, 128, (1, 1, 1, 256)),
+                                               (2, 3, 1, 2000, 64, (2, 1, 1, 2000)),       # decode rows: the streaming kernel
+                                               (1, 2, 5, 1500, 128, (5, 1500))])
 def test_om_bias_fwd_vs_torch_sdpa_in_fp64(dev, dtype, tol, B, H, Tq, Tk, d, mshape):
     """softmax(scale q k^T + bias) v with biases of every broadcast shape (per (t, j), with a head or a
     batch axis, one value per row, one per key), some keys hidden by -inf, against torch's own masked
