@@ -58,6 +58,12 @@ def test_argument_errors_without_a_device(lib_path):
     assert lib.cb2_decayed_chunk_on_tensor_cores(16, 32, 2048, 64, 64, 128, 0) == 1
     assert lib.cb2_decayed_chunk_on_tensor_cores(16, 32, 2048, 128, 128, 128, 0) == 0
     assert lib.cb2_decayed_chunk_scratch_bytes(16, 32, 2048, 64, 64, 128, 0) == 0
+    # streaming step in the decode regime: partial carriers (m, l, a) of one wave of key splits — two
+    # CTAs per SM for up to four query rows, one for eight
+    assert lib.cb2_om_step_scratch_bytes(1, 32, 1, 65536, 128) == (2 * 148 // 32) * 32 * 1 * (128 + 2) * 4
+    assert lib.cb2_om_step_scratch_bytes(1, 32, 8, 65536, 128) == (148 // 32) * 32 * 8 * (128 + 2) * 4
+    assert lib.cb2_om_step_scratch_bytes(1, 32, 1, 512, 64) == 2 * 32 * 1 * (64 + 2) * 4      # at least 256 keys per split
+    assert lib.cb2_om_step_scratch_bytes(0, 32, 1, 512, 64) == 0
 
 
 def test_no_cpu_fallback():
