@@ -1,9 +1,10 @@
 // C-ABI front of the chunked decayed-attention executor: argument checks and
 // the choice between the tensor-core kernels (bf16, dk and dv multiples of 8 up to
 // 128: state kept on chip, optional scratch for cutting heads into segments;
-// fp32 with dk, dv <= 64 and enough heads: three-pass TF32) and the fp32 FMA
-// paths (everything else): one fused launch for a few small chunks, three
-// launches with the state in scratch otherwise.
+// fp32 with dk, dv <= 64 and enough heads: three-pass TF32) and the other
+// paths: one fused launch with warp-level three-pass TF32 products for a few
+// small chunks, three launches on the fp32 FMA pipes with the state in scratch
+// otherwise.
 #include "common.cuh"
 
 namespace cb2 {

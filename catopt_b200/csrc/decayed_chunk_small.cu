@@ -1,10 +1,16 @@
-// Chunked decayed attention in ONE launch for small problems on the fp32 FMA
-// pipes (chunk, dk, dv <= 64; a few thousand (batch, head, chunk) units at most):
-// the shapes where the three-launch path (decayed_chunk_ffma.cu) spends its time
-// on launch gaps and global round trips rather than arithmetic.
+// Chunked decayed attention in ONE launch for small problems (chunk, dk, dv <= 64;
+// a few thousand (batch, head, chunk) units at most): the shapes where the
+// three-launch path (decayed_chunk_ffma.cu) spends its time on launch gaps and
+// global round trips rather than arithmetic.  The four 64 x 64 x 64 products of a
+// chunk run as warp-level TF32 MMAs in three passes (value and truncation
+// remainder of both operands: fp32 accuracy, fp32 accumulation): a chunk is one
+// tile, so what counts is the latency of a product, and the tile-sized tensor-memory
+// pipeline of the large kernels has nothing to amortise its set-up over here (on the
+// FMA pipes a product took 2.3-3.6 us, two thirds of the kernel).
 //
 // CTA = one chunk i of one (batch, head).  It stages Q_i, K_i, V_i in shared
-// memory once and then, entirely from shared memory,
+// memory once (as stored: the MMA fragments are read with scalar loads, so no transposed
+// copy is needed) and then, entirely from shared memory,
 //   KV_i = (K_i . g^(C-1-r))^T V_i        -> global scratch, then a release flag
 //   P_i  = (Q_i K_i^T) . tril(g^(r-c))
 //   O    = P_i V_i
@@ -16,7 +22,7 @@
 // a CTA's predecessors have lower block indices and are running or finished
 // whenever it runs; the wait is bounded and reports through the status word.
 // The same arithmetic as the reference's state-carry recurrence
-// (lab/probes/retnet_baseline_probe.py:77-110), fp32 throughout.
+// (lab/probes/retnet_baseline_probe.py:77-110) at fp32 accuracy.
 #include "common.cuh"
 
 namespace cb2 {
@@ -26,7 +32,7 @@ constexpr int kT = 64;            // tile edge: chunk, dk, dv <= 64
 constexpr int kLd = kT + 4;       // padded leading dimension (floats)
 constexpr int kSmallThreads = 256;
 constexpr int kArr = kT * kLd;    // floats per staged array
-constexpr size_t kSmallSmem = (6 * kArr + kT + 8) * sizeof(float);
+constexpr size_t kSmallSmem = (5 * kArr + kT + 8) * sizeof(float);
 
 template <int DTYPE>
 __device__ __forceinline__ float ld_e(const void* p, size_t i) {
@@ -41,24 +47,52 @@ __device__ __forceinline__ void st_e(void* p, size_t i, float v) {
     static_cast<float*>(p)[i] = v;
 }
 
-// acc[i][j] += sum_k At[k][ty*4+i] * scale_k * B[k][tx*4+j], operands in shared memory.
-template <bool SCALED>
-__device__ __forceinline__ void smem_gemm(float (&acc)[4][4], const float* At, const float* B, int kdim,
-                                          const float* kscale, int ty, int tx) {
-#pragma unroll 4
-  for (int k = 0; k < kdim; ++k) {
-    float4 av = *reinterpret_cast<const float4*>(At + k * kLd + ty * 4);
-    const float4 bv = *reinterpret_cast<const float4*>(B + k * kLd + tx * 4);
-    if (SCALED) {
-      const float w = kscale[k];
-      av.x *= w; av.y *= w; av.z *= w; av.w *= w;
+// What a tf32 operand keeps of an fp32 value (the tensor core ignores the low 13 bits) and what it loses.
+__device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
+  hi = __float_as_uint(x) & 0xffffe000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_m16n8k8_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// One warp's 16 x 32 tile (rows m0.., columns n0..: four 8-wide MMA tiles) of acc += A B over kdim
+// (a multiple of 8), operands in shared memory with arbitrary strides: A(m,k) = Ap[m*a_m + k*a_k],
+// B(k,n) = Bp[k*b_k + n*b_n].  WEIGHTED: row k of B is scaled by wrev[-k] (0 from row wlim on).
+// Fragment layout of mma.m16n8k8 (g = lane / 4, t = lane % 4): a = A[g | g+8][t | t+4],
+// b = B[t | t+4][g], d = D[g | g+8][2t, 2t+1].  Three passes: lo*hi, hi*lo, hi*hi.
+template <bool WEIGHTED>
+__device__ __forceinline__ void warp_gemm(float (&acc)[4][4], const float* Ap, int a_m, int a_k, const float* Bp,
+                                          int b_k, int b_n, int kdim, const float* wrev, int wlim, int m0,
+                                          int n0, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const float* a_lo = Ap + (m0 + g) * a_m + t * a_k;
+  const float* b_lo = Bp + t * b_k + (n0 + g) * b_n;
+#pragma unroll 2
+  for (int k0 = 0; k0 < kdim; k0 += 8) {
+    uint32_t ah[4], al[4];
+    tf32_split(a_lo[k0 * a_k], ah[0], al[0]);
+    tf32_split(a_lo[k0 * a_k + 8 * a_m], ah[1], al[1]);
+    tf32_split(a_lo[(k0 + 4) * a_k], ah[2], al[2]);
+    tf32_split(a_lo[(k0 + 4) * a_k + 8 * a_m], ah[3], al[3]);
+    float w0 = 1.f, w1 = 1.f;
+    if (WEIGHTED) {
+      const int r0 = k0 + t, r1 = r0 + 4;
+      w0 = r0 < wlim ? wrev[-r0] : 0.f;
+      w1 = r1 < wlim ? wrev[-r1] : 0.f;
     }
-    const float a4[4] = {av.x, av.y, av.z, av.w};
-    const float b4[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a4[i], b4[j], acc[i][j]);
+    for (int nt = 0; nt < 4; ++nt) {
+      uint32_t bh[2], bl[2];
+      tf32_split(b_lo[k0 * b_k + nt * 8 * b_n] * w0, bh[0], bl[0]);
+      tf32_split(b_lo[(k0 + 4) * b_k + nt * 8 * b_n] * w1, bh[1], bl[1]);
+      mma_m16n8k8_tf32(acc[nt], al, bh);
+      mma_m16n8k8_tf32(acc[nt], ah, bl);
+      mma_m16n8k8_tf32(acc[nt], ah, bh);
+    }
   }
 }
 
@@ -69,20 +103,23 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
                      int* __restrict__ flags, int n_bh, int H, int T, int dk, int dv, int C, float inv_scale,
                      int* dev_status) {
   extern __shared__ __align__(16) float sm[];
-  float* Qt = sm;               // [e][r]  Q transposed
-  float* Kt = Qt + kArr;        // [e][c]  K transposed
-  float* Kn = Kt + kArr;        // [r][e]  K as stored
-  float* Vn = Kn + kArr;        // [c][f]  V as stored
-  float* Pt = Vn + kArr;        // [c][r]  P transposed
-  float* Ss = Pt + kArr;        // [e][f]  state before this chunk
+  float* Qn = sm;               // [r][e]  Q
+  float* Kn = Qn + kArr;        // [r][e]  K
+  float* Vn = Kn + kArr;        // [c][f]  V
+  float* Pn = Vn + kArr;        // [r][c]  P
+  float* Ss = Pn + kArr;        // [e][f]  state before this chunk
   float* pw = Ss + kArr;        // g^0 .. g^C
   int* s_ok = reinterpret_cast<int*>(pw + kT + 4);
 
   const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int m0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;     // this warp's 16 x 32 tile of every product
+  const int fg = lane >> 2, ft = lane & 3;                    // fragment row group / column pair
   const int nchunk = T / C;
   const int i = blockIdx.x / n_bh, bh = blockIdx.x % n_bh;    // chunk-major launch order
   const float g = gamma[bh % H];
   const size_t row0 = size_t(bh) * T + size_t(i) * C;
+  const int C8 = (C + 7) & ~7, dk8 = (dk + 7) & ~7;           // reduction lengths in whole MMA steps (tiles are zero-padded)
 
   for (int x = tid; x <= C; x += kSmallThreads) pw[x] = powf(g, float(x));
   // stage the three tiles, zero-padded to 64 x 64: all of a thread's loads are issued
@@ -101,8 +138,7 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
       const int x = tid + u * kSmallThreads, r = x / kT, e = x % kT;
-      Qt[e * kLd + r] = qv[u];
-      Kt[e * kLd + r] = kv[u];
+      Qn[r * kLd + e] = qv[u];
       Kn[r * kLd + e] = kv[u];
       Vn[r * kLd + e] = vv[u];
     }
@@ -113,14 +149,13 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
   float* kv_mine = kv_all + (size_t(bh) * nchunk + i) * (kT * kT);
   if (i + 1 < nchunk) {
     float acc[4][4] = {};
-    // per-row weights g^(C-1-r), reusing Ss as scratch for the reversed table
-    for (int x = tid; x < kT; x += kSmallThreads) Ss[x] = x < C ? pw[C - 1 - x] : 0.f;
-    __syncthreads();
-    smem_gemm<true>(acc, Kn, Vn, C, Ss, ty, tx);
+    warp_gemm<true>(acc, Kn, 1, kLd, Vn, kLd, 1, C8, pw + (C - 1), C, m0, n0, lane);
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii)
-      __stcg(reinterpret_cast<float4*>(kv_mine + (ty * 4 + ii) * kT + tx * 4),
-             make_float4(acc[ii][0], acc[ii][1], acc[ii][2], acc[ii][3]));
+    for (int nt = 0; nt < 4; ++nt) {
+      float* dst = kv_mine + (m0 + fg) * kT + n0 + nt * 8 + 2 * ft;
+      __stcg(reinterpret_cast<float2*>(dst), make_float2(acc[nt][0], acc[nt][1]));
+      __stcg(reinterpret_cast<float2*>(dst + 8 * kT), make_float2(acc[nt][2], acc[nt][3]));
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -129,23 +164,24 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
     }
   }
 
-  // P = (Q K^T) . tril(g^(r-c)), kept transposed for the next product
+  // P = (Q K^T) . tril(g^(r-c))
   {
     float acc[4][4] = {};
-    smem_gemm<false>(acc, Qt, Kt, dk, nullptr, ty, tx);
+    warp_gemm<false>(acc, Qn, kLd, 1, Kn, 1, kLd, dk8, nullptr, 0, m0, n0, lane);
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii) {
-      const int r = ty * 4 + ii;
+    for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int c = tx * 4 + jj;
-        Pt[c * kLd + r] = (c <= r && r < C) ? acc[ii][jj] * pw[r - c] : 0.f;
+      for (int h = 0; h < 2; ++h) {
+        const int r = m0 + fg + 8 * h, c = n0 + nt * 8 + 2 * ft;
+        const float p0 = (c <= r && r < C) ? acc[nt][2 * h] * pw[r - c] : 0.f;
+        const float p1 = (c + 1 <= r && r < C) ? acc[nt][2 * h + 1] * pw[r - c - 1] : 0.f;
+        *reinterpret_cast<float2*>(Pn + r * kLd + c) = make_float2(p0, p1);
       }
     }
   }
   __syncthreads();
   float out[4][4] = {};
-  smem_gemm<false>(out, Pt, Vn, C, nullptr, ty, tx);      // O = P V
+  warp_gemm<false>(out, Pn, kLd, 1, Vn, kLd, 1, C8, nullptr, 0, m0, n0, lane);      // O = P V
 
   if (i > 0) {
     // wait (bounded) until every earlier chunk of this head has published its KV: lane j of
@@ -174,54 +210,58 @@ decayed_small_kernel(const void* __restrict__ q, const void* __restrict__ k, con
       return;
     }
     // S_i = sum_j g^(C (i-1-j)) KV_j, Horner in chunk order; this thread's 4 x 4 block.
-    // Four chunks' loads are issued before their dependent FMAs.
+    // Four chunks' loads are issued before their dependent FMAs (eight at a time measured the same).
+    constexpr int kBatch = 4;
     const float gC = pw[C];
-    float s[4][4] = {};
+    float st[4][4] = {};
     const float* kv_head = kv_all + size_t(bh) * nchunk * (kT * kT) + (ty * 4) * kT + tx * 4;
-    for (int j0 = 0; j0 < i; j0 += 4) {
-      float4 x[4][4];
+    for (int j0 = 0; j0 < i; j0 += kBatch) {
+      float4 x[kBatch][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < kBatch; ++u)
 #pragma unroll
         for (int ii = 0; ii < 4; ++ii)
           x[u][ii] = (j0 + u < i) ? __ldcg(reinterpret_cast<const float4*>(kv_head + size_t(j0 + u) * (kT * kT) + ii * kT))
                                   : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kBatch; ++u) {
         if (j0 + u < i) {
 #pragma unroll
           for (int ii = 0; ii < 4; ++ii) {
-            s[ii][0] = fmaf(gC, s[ii][0], x[u][ii].x);
-            s[ii][1] = fmaf(gC, s[ii][1], x[u][ii].y);
-            s[ii][2] = fmaf(gC, s[ii][2], x[u][ii].z);
-            s[ii][3] = fmaf(gC, s[ii][3], x[u][ii].w);
+            st[ii][0] = fmaf(gC, st[ii][0], x[u][ii].x);
+            st[ii][1] = fmaf(gC, st[ii][1], x[u][ii].y);
+            st[ii][2] = fmaf(gC, st[ii][2], x[u][ii].z);
+            st[ii][3] = fmaf(gC, st[ii][3], x[u][ii].w);
           }
         }
       }
     }
-    __syncthreads();   // Ss was used as the weight table above
 #pragma unroll
     for (int ii = 0; ii < 4; ++ii)
       *reinterpret_cast<float4*>(Ss + (ty * 4 + ii) * kLd + tx * 4) =
-          make_float4(s[ii][0], s[ii][1], s[ii][2], s[ii][3]);
+          make_float4(st[ii][0], st[ii][1], st[ii][2], st[ii][3]);
     __syncthreads();
     float cross[4][4] = {};
-    smem_gemm<false>(cross, Qt, Ss, dk, nullptr, ty, tx);   // Q S
+    warp_gemm<false>(cross, Qn, kLd, 1, Ss, kLd, 1, dk8, nullptr, 0, m0, n0, lane);   // Q S
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii) {
-      const float gr = pw[min(ty * 4 + ii + 1, C)];
+    for (int h = 0; h < 2; ++h) {
+      const float gr = pw[min(m0 + fg + 8 * h + 1, C)];
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) out[ii][jj] = fmaf(gr, cross[ii][jj], out[ii][jj]);
+      for (int nt = 0; nt < 4; ++nt) {
+        out[nt][2 * h] = fmaf(gr, cross[nt][2 * h], out[nt][2 * h]);
+        out[nt][2 * h + 1] = fmaf(gr, cross[nt][2 * h + 1], out[nt][2 * h + 1]);
+      }
     }
   }
 #pragma unroll
-  for (int ii = 0; ii < 4; ++ii) {
-    const int r = ty * 4 + ii;
+  for (int h = 0; h < 2; ++h) {
+    const int r = m0 + fg + 8 * h;
     if (r >= C) continue;
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-      const int f = tx * 4 + jj;
-      if (f < dv) st_e<DTYPE>(o, (row0 + r) * dv + f, out[ii][jj] * inv_scale);
+    for (int nt = 0; nt < 4; ++nt) {
+      const int f = n0 + nt * 8 + 2 * ft;
+      if (f < dv) st_e<DTYPE>(o, (row0 + r) * dv + f, out[nt][2 * h] * inv_scale);
+      if (f + 1 < dv) st_e<DTYPE>(o, (row0 + r) * dv + f + 1, out[nt][2 * h + 1] * inv_scale);
     }
   }
 }

@@ -183,7 +183,8 @@ size_t cb2_decayed_chunk_scratch_bytes(int B, int H, int T, int dk, int dv,
 /* 1 when cb2_decayed_chunk_fwd runs these sizes on the tensor cores (one launch,
  * state on chip: bf16 with head dims up to 128, or fp32 with head dims up to 64
  * (multiples of 4) and at least 24 (batch, head) units, in three TF32 passes at
- * fp32 accuracy), 0 when it takes the fp32 FMA path. */
+ * fp32 accuracy), 0 when it takes one of the other paths (one launch with
+ * warp-level TF32 products for a few small chunks, the fp32 FMA pipes otherwise). */
 int cb2_decayed_chunk_on_tensor_cores(int B, int H, int T, int dk, int dv,
                                       int chunk, int dtype);
 /* How the tensor-core path cuts a call of these sizes into CTAs, given the scratch the size
