@@ -899,6 +899,11 @@ def run_profile_case(args) -> None:
         bp_ = torch.randn(256, 8 * 1024 * 16, device=dev, generator=gen)
         hp_ = torch.randn(8 * 1024 * 16, device=dev, generator=gen)
         fn = lambda: ops.diag_scan_states(ap_, bp_, hp_)  # noqa: E731
+    elif args.profile_case == "decayed_small":  # config 2 itself (2 MB: a latency case, not a bandwidth one)
+        qs, ks, vs = (torch.randn(2, 4, 1024, 64, device=dev, generator=gen) / 8 for _ in range(3))
+        gs = torch.full((4,), 0.97, device=dev)
+        os_ = torch.empty_like(vs)
+        fn = lambda: ops.decayed_chunk_fwd(qs, ks, vs, gs, 64, 8.0, out=os_)  # noqa: E731
     elif args.profile_case == "decode":     # one query row per head against 32768 keys, bf16: K + V = 537 MB
         qd = _randn_bf16((32, 128), gen).view(1, 32, 1, 128)
         kd, vd = (_randn_bf16((32 * 32768, 128), gen).view(1, 32, 32768, 128) for _ in range(2))
@@ -929,7 +934,7 @@ def run_profile_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["decayed", "decayed_fp32", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep", "decode"],
+                    choices=["decayed", "decayed_fp32", "decayed_strong", "states", "scan", "scan_shared", "verify", "linear", "om_causal", "compose", "gated", "prefix", "decayed_few", "scan_few", "linear_deep", "decode", "decayed_small"],
                     help="run a small case of one kernel only (for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
